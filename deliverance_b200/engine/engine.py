@@ -1,0 +1,425 @@
+"""Continuous-batching generation engine.
+
+The reference runs one independent ``generate`` loop per request (core/.../model/GenerationEngine.java:81-176; no request
+batching, web/.../ChatCompletionController.java:373-383). Here one engine owns the model replica, the paged KV pool and
+all in-flight requests: every :meth:`Engine.step` is either a chunked-prefill step over waiting requests or one decode
+step over every running request (captured in a CUDA graph per batch-size bucket on GPUs). Per-request behaviour is kept:
+prompt-length check against ``ntokens`` (GenerationEngine.java:98-104), prefix-cache lookup/store with salted keys, replay
+of the last prompt token on a full-prompt hit (GenerationCursor.java:40-60), TTFT/throughput accounting (:249-268), and the
+stop order max_tokens -> guided-choice complete -> stop strings -> tool-parser end of turn -> EOS (:189-219).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from .. import ops
+from ..kv.paged import KvCacheSettings, PagedKVCache, compose_salt
+from ..models.batch import ForwardBatch, make_batch
+from ..params import FinishReason, GeneratorParameters, Response, TokenLogProb
+from .sampler import Sampler, SamplingState
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass
+class Request:
+    rid: int
+    prompt: list[int]
+    params: GeneratorParameters
+    on_token: Optional[Callable[[int, "Request"], None]] = None
+    state: str = WAITING
+    pages: list[int] = field(default_factory=list)
+    computed: int = 0  # tokens whose KV is in the cache
+    output: list[int] = field(default_factory=list)
+    logprobs: list[TokenLogProb] = field(default_factory=list)
+    sampling: Optional[SamplingState] = None
+    guide: object = None  # guided-decoding logits processor (allowed-mask provider)
+    stopper: object = None  # text-level stop detector (stop strings, tool parser)
+    finish_reason: Optional[FinishReason] = None
+    prefix_hit: int = 0
+    state_slot: int = -1
+    salt: str = ""
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    t_done: float = 0.0
+    limit: int = 0  # absolute position limit
+    cancelled: bool = False
+    error: Optional[str] = None
+    state_snapshots: dict = field(default_factory=dict)
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    def response(self) -> Response:
+        r = Response()
+        r.token_ids = list(self.output)
+        r.prompt_tokens = len(self.prompt)
+        r.generated_tokens = len(self.output)
+        r.finish_reason = self.finish_reason or FinishReason.MAX_TOKENS
+        r.sampler_returns = list(self.logprobs)
+        r.ttft_ms = (self.t_first - self.t_submit) * 1e3 if self.t_first else 0.0
+        r.total_ms = ((self.t_done or time.perf_counter()) - self.t_submit) * 1e3
+        r.avg_ms_per_token = r.total_ms / max(1, r.generated_tokens)
+        r.prefix_hit_tokens = self.prefix_hit
+        return r
+
+
+@dataclass
+class EngineConfig:
+    max_batch_tokens: int = 8192  # prefill token budget per step (the reference chunks prompts at 512, AbstractModel.java:87)
+    max_seqs: int = 128
+    num_pages: Optional[int] = None  # default: sized from free device memory
+    kv_memory_fraction: float = 0.85
+    cuda_graphs: bool = True
+    kv: KvCacheSettings = field(default_factory=KvCacheSettings)
+    max_state_slots: int = 0
+
+
+_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+class Engine:
+    def __init__(self, model, config: Optional[EngineConfig] = None, eos_ids=(), special_ids=(), decode_token=None):
+        self.model = model
+        self.cfg = model.cfg
+        self.config = config or EngineConfig()
+        self.device = model.device
+        self.eos_ids = frozenset(eos_ids or self.cfg.eos_token_ids)
+        self.special_ids = frozenset(special_ids)
+        self.sampler = Sampler(decode_token)
+        layout = model.kv_layout()
+        pages = self.config.num_pages or self._auto_pages(layout)
+        mamba_shapes = None
+        slots = self.config.max_state_slots
+        if any(k == "mamba" for k in layout["layer_kinds"]):
+            c = self.cfg
+            mamba_shapes = {"conv": (c.mamba_conv_dim, c.mamba_d_conv - 1), "ssm": (c.mamba_n_heads, c.mamba_d_head, c.mamba_d_state)}
+            slots = slots or self.config.max_seqs
+        self.kv = PagedKVCache(layout, pages, self.device, model.dtype, self.config.kv, slots, mamba_shapes)
+        self.page_size = self.kv.page_size
+        self.max_pages_per_seq = (self.cfg.max_position_embeddings + self.page_size - 1) // self.page_size
+        self.waiting: list[Request] = []
+        self.running: list[Request] = []
+        self._next_id = 0
+        self._graphs: dict[int, dict] = {}
+        self.metrics = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "prefill_tokens": 0, "decode_tokens": 0,
+                        "graph_replays": 0, "kernel_launches": 0}
+        self.use_graphs = bool(self.config.cuda_graphs and self.device.type == "cuda")
+        self.hybrid = mamba_shapes is not None
+        if self.device.type == "cuda":
+            e = ops.require_ext()
+            e.init_scratch(self.device.index if self.device.index is not None else torch.cuda.current_device())
+
+    def _auto_pages(self, layout) -> int:
+        per = max(1, PagedKVCache.bytes_per_page(layout, self.config.kv.block_size, self.model.dtype))
+        if self.device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(self.device)
+            budget = int(free * self.config.kv_memory_fraction)
+            # enough for max_seqs full contexts, never more than the budget
+            want = self.config.max_seqs * ((self.cfg.max_position_embeddings + self.config.kv.block_size - 1) // self.config.kv.block_size) + 1
+            return max(2, min(want, budget // per))
+        return 2048
+
+    # ------------------------------------------------------------------------------------------------ requests
+    def add_request(self, prompt: list[int], params: Optional[GeneratorParameters] = None, on_token=None, guide=None,
+                    stopper=None) -> Request:
+        params = params or GeneratorParameters()
+        params.validate()
+        ctx = self.cfg.max_position_embeddings
+        limit = min(params.ntokens or ctx, ctx)
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt) >= limit:
+            raise ValueError(f"prompt has {len(prompt)} tokens, which does not fit ntokens={limit}")
+        for t in prompt:
+            if not 0 <= int(t) < self.cfg.vocab_size:
+                raise ValueError(f"token id {t} outside the vocabulary")
+        r = Request(self._next_id, [int(t) for t in prompt], params, on_token)
+        self._next_id += 1
+        r.sampling = SamplingState.create(params, self.special_ids)
+        r.guide = guide
+        r.stopper = stopper
+        r.limit = limit
+        r.t_submit = time.perf_counter()
+        r.salt = compose_salt(params.cache_salt, params.lora_adapter or getattr(self.model, "active_lora", None),
+                              self.model.tp.rank, self.model.tp.size)
+        self.waiting.append(r)
+        return r
+
+    def abort(self, r: Request, reason: FinishReason = FinishReason.CANCELLED) -> None:
+        r.cancelled = True
+        if r.state == WAITING and r in self.waiting:
+            self.waiting.remove(r)
+            self._finish(r, reason)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------------------------------------ scheduling
+    def _admit(self, r: Request) -> bool:
+        """Prefix lookup + page reservation for a waiting request."""
+        if len(self.running) >= self.config.max_seqs:
+            return False
+        need_pages = (len(r.prompt) + 1 + self.page_size - 1) // self.page_size
+        if not self.kv.can_allocate(need_pages):
+            return False
+        if self.hybrid:
+            if not self.kv.free_slots:
+                return False
+            r.state_slot = self.kv.alloc_state_slot()
+        hit = self.kv.prefix.lookup(r.salt, r.prompt)
+        if hit is not None:
+            r.pages = hit.pages
+            r.prefix_hit = hit.length
+            r.computed = hit.length
+            if self.hybrid and hit.state is not None:
+                self.kv.restore_state(r.state_slot, hit.state)
+            if r.computed >= len(r.prompt):
+                r.computed = len(r.prompt) - 1  # full hit: replay the last prompt token to get logits
+        r.state = RUNNING
+        self.running.append(r)
+        return True
+
+    def _finish(self, r: Request, reason: FinishReason) -> None:
+        r.finish_reason = reason
+        r.state = FINISHED
+        r.t_done = time.perf_counter()
+        if r in self.running:
+            self.running.remove(r)
+        self.kv.release_pages(r.pages)
+        if r.state_slot >= 0:
+            self.kv.free_state_slot(r.state_slot)
+            r.state_slot = -1
+
+    def step(self) -> list[Request]:
+        """Run one engine step; returns the requests that finished in it."""
+        self.metrics["steps"] += 1
+        for r in [x for x in self.running if x.cancelled]:
+            self._finish(r, FinishReason.CANCELLED)
+        while self.waiting and self._admit(self.waiting[0]):
+            self.waiting.pop(0)
+        prefill = [r for r in self.running if r.computed < len(r.prompt)]
+        if prefill:
+            return self._prefill_step(prefill)
+        if self.running:
+            return self._decode_step(list(self.running))
+        if self.waiting:
+            raise MemoryError("waiting requests cannot be admitted: KV cache too small for the prompt")
+        return []
+
+    # ------------------------------------------------------------------------------------------------ prefill
+    def _prefill_step(self, reqs: list[Request]) -> list[Request]:
+        budget = self.config.max_batch_tokens
+        seqs, chosen = [], []
+        for r in reqs:
+            if budget <= 0:
+                break
+            n = min(len(r.prompt) - r.computed, budget)
+            if self.hybrid:
+                # recurrent state can only be snapshotted at chunk ends: stop chunks at the prefix-cache checkpoints
+                for L in self.kv.settings.checkpoint_lengths(len(r.prompt)):
+                    if r.computed < L < r.computed + n:
+                        n = L - r.computed
+                        break
+            self.kv.ensure_pages(r.pages, r.computed + n)
+            seqs.append({"tokens": r.prompt[r.computed : r.computed + n], "start": r.computed, "pages": r.pages,
+                         "state_slot": max(r.state_slot, 0)})
+            chosen.append((r, n))
+            budget -= n
+        batch = make_batch(seqs, self.page_size, self.device)
+        logits = self.model.forward(batch, self.kv)
+        self.metrics["prefill_steps"] += 1
+        self.metrics["prefill_tokens"] += batch.num_tokens
+        done_rows, done_reqs = [], []
+        for i, (r, n) in enumerate(chosen):
+            r.computed += n
+            if self.hybrid and r.computed in self.kv.settings.checkpoint_lengths(len(r.prompt)):
+                r.state_snapshots[r.computed] = self.kv.snapshot_state(r.state_slot)
+            if r.computed >= len(r.prompt):
+                self.kv.prefix.store(r.salt, r.prompt, r.pages, r.state_snapshots if self.hybrid else None)
+                done_rows.append(i)
+                done_reqs.append(r)
+        finished = []
+        if done_reqs:
+            sub = logits.index_select(0, torch.tensor(done_rows, device=logits.device)) if len(done_rows) != logits.shape[0] else logits
+            finished = self._sample_and_advance(done_reqs, sub)
+        return finished
+
+    # ------------------------------------------------------------------------------------------------ decode
+    def _decode_inputs(self, reqs: list[Request]):
+        seqs = []
+        for r in reqs:
+            pos = r.total_len - 1  # position of the token being fed (the last sampled one)
+            self.kv.ensure_pages(r.pages, pos + 1)
+            seqs.append({"tokens": [r.output[-1]], "start": pos, "pages": r.pages, "state_slot": max(r.state_slot, 0)})
+        return seqs
+
+    def _decode_step(self, reqs: list[Request]) -> list[Request]:
+        seqs = self._decode_inputs(reqs)
+        B = len(seqs)
+        self.metrics["decode_steps"] += 1
+        self.metrics["decode_tokens"] += B
+        if self.use_graphs and B <= _BUCKETS[-1]:
+            logits = self._graph_decode(seqs)[:B]
+        else:
+            batch = make_batch(seqs, self.page_size, self.device)
+            batch.decode_splits = self._splits(B)
+            logits = self.model.forward(batch, self.kv)
+        return self._sample_and_advance(reqs, logits)
+
+    def _splits(self, B: int) -> int:
+        kvh = self.model.n_kv
+        ctas = max(1, B * kvh)
+        sms = 148
+        return int(max(1, min(32, (2 * sms) // ctas)))
+
+    def _graph_decode(self, seqs: list[dict]) -> torch.Tensor:
+        B = len(seqs)
+        bucket = next(b for b in _BUCKETS if b >= B)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._capture(bucket)
+        # stage inputs on the host, one H2D copy per tensor
+        ps = self.page_size
+        tok = torch.zeros(bucket, dtype=torch.int32)
+        pos = torch.zeros(bucket, dtype=torch.int32)
+        slots = torch.zeros(bucket, dtype=torch.int64)
+        ctx = torch.ones(bucket, dtype=torch.int32)
+        bt = torch.zeros(bucket, self.max_pages_per_seq, dtype=torch.int32)
+        st = torch.zeros(bucket, dtype=torch.int64)
+        for i, s in enumerate(seqs):
+            p = s["start"]
+            tok[i] = s["tokens"][0]
+            pos[i] = p
+            slots[i] = s["pages"][p // ps] * ps + p % ps
+            ctx[i] = p + 1
+            bt[i, : len(s["pages"])] = torch.tensor(s["pages"], dtype=torch.int32)
+            st[i] = s["state_slot"]
+        for i in range(B, bucket):
+            slots[i] = i % ps  # padded rows write into the scratch page
+        b: ForwardBatch = g["batch"]
+        b.token_ids.copy_(tok, non_blocking=True)
+        b.positions.copy_(pos, non_blocking=True)
+        b.slots.copy_(slots, non_blocking=True)
+        b.ctx_len.copy_(ctx, non_blocking=True)
+        b.block_tables.copy_(bt, non_blocking=True)
+        if b.state_slots is not None:
+            b.state_slots.copy_(st, non_blocking=True)
+        g["graph"].replay()
+        self.metrics["graph_replays"] += 1
+        return g["logits"]
+
+    def _capture(self, bucket: int) -> dict:
+        dev = self.device
+        batch = ForwardBatch(
+            token_ids=torch.zeros(bucket, dtype=torch.int32, device=dev),
+            positions=torch.zeros(bucket, dtype=torch.int32, device=dev),
+            slots=torch.arange(bucket, dtype=torch.int64, device=dev) % self.page_size,
+            q_start=torch.arange(bucket, dtype=torch.int32, device=dev),
+            q_len=torch.ones(bucket, dtype=torch.int32, device=dev),
+            ctx_len=torch.ones(bucket, dtype=torch.int32, device=dev),
+            block_tables=torch.zeros(bucket, self.max_pages_per_seq, dtype=torch.int32, device=dev),
+            is_decode=True,
+            logits_rows=torch.arange(bucket, dtype=torch.int64, device=dev),
+            decode_splits=self._splits(bucket),
+            state_slots=torch.zeros(bucket, dtype=torch.int64, device=dev) if self.hybrid else None,
+        )
+        # warm up outside capture (lazy handles, function attributes, scratch), then capture
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.model.forward(batch, self.kv)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(batch, self.kv)
+        g = {"graph": graph, "batch": batch, "logits": logits}
+        self._graphs[bucket] = g
+        return g
+
+    # ------------------------------------------------------------------------------------------------ sampling / stops
+    def _sample_and_advance(self, reqs: list[Request], logits: torch.Tensor) -> list[Request]:
+        cfg = self.cfg
+        mask = None
+        if any(r.guide is not None for r in reqs):
+            words = (cfg.vocab_size + 31) // 32
+            m = torch.full((len(reqs), words), -1, dtype=torch.int32)
+            for i, r in enumerate(reqs):
+                if r.guide is not None:
+                    m[i] = r.guide.allowed_mask()
+            mask = m.to(logits.device, non_blocking=True)
+        inv_scale = 1.0 / cfg.logits_scaling if cfg.logits_scaling not in (0.0, 1.0) else 1.0
+        all_greedy_plain = mask is None and all(r.sampling.greedy and not r.params.logprobs for r in reqs)
+        if all_greedy_plain:
+            idx, _ = ops.argmax(logits)  # softcap and positive scaling keep the argmax
+            tokens = idx.tolist()
+            lps = [None] * len(reqs)
+        else:
+            if mask is not None or cfg.final_softcap > 0 or inv_scale != 1.0:
+                logits = ops.logits_post(logits if not self.use_graphs else logits.clone(), mask, cfg.final_softcap, inv_scale)
+            tokens, lps = self.sampler.sample(logits, [r.sampling for r in reqs])
+        now = time.perf_counter()
+        finished = []
+        for r, tok, lp in zip(reqs, tokens, lps):
+            if not r.output:
+                r.t_first = now
+            r.output.append(int(tok))
+            if lp is not None:
+                r.logprobs.append(lp)
+            if r.guide is not None:
+                r.guide.accept(int(tok))
+            reason = self._stop_reason(r, int(tok))
+            if r.on_token is not None:
+                try:
+                    r.on_token(int(tok), r)
+                except Exception as e:  # a failing callback cancels only its own request
+                    r.error = repr(e)
+                    reason = reason or FinishReason.ERROR
+            if reason is None and r.stopper is not None:
+                reason = r.stopper.check(r)
+            if reason is None and int(tok) in self.eos_ids:
+                reason = FinishReason.STOP_TOKEN
+            if reason is None and r.total_len >= r.limit:
+                reason = FinishReason.MAX_TOKENS
+            if reason is None and r.cancelled:
+                reason = FinishReason.CANCELLED
+            if reason is not None:
+                self._finish(r, reason)
+                finished.append(r)
+        return finished
+
+    def _stop_reason(self, r: Request, tok: int) -> Optional[FinishReason]:
+        if r.params.max_tokens is not None and len(r.output) >= r.params.max_tokens:
+            return FinishReason.MAX_TOKENS
+        if r.guide is not None and getattr(r.guide, "is_complete", lambda: False)():
+            return FinishReason.GUIDED_COMPLETE
+        return None
+
+    # ------------------------------------------------------------------------------------------------ conveniences
+    def run(self, reqs: Optional[list[Request]] = None) -> None:
+        while self.has_work() and (reqs is None or any(r.state != FINISHED for r in reqs)):
+            self.step()
+
+    def generate(self, prompt: list[int], params: Optional[GeneratorParameters] = None, on_token=None, guide=None,
+                 stopper=None) -> Response:
+        r = self.add_request(prompt, params, on_token, guide, stopper)
+        self.run([r])
+        if self.device.type == "cuda":
+            ops.check_status(self.device.index)
+        return r.response()
+
+    def generate_batch(self, prompts: list[list[int]], params: Optional[GeneratorParameters] = None) -> list[Response]:
+        import copy
+
+        rs = [self.add_request(p, copy.deepcopy(params) if params else None) for p in prompts]
+        self.run(rs)
+        if self.device.type == "cuda":
+            ops.check_status(self.device.index)
+        return [r.response() for r in rs]

@@ -1,0 +1,273 @@
+"""Paged KV pool with a block-hash prefix cache that shares pages by reference count.
+
+Semantics kept from the reference's ``KvBufferCache`` (core/.../tensor/KvBufferCache.java:129-143,256-298,457-507;
+core/PrefixCache.md:45-84): the key of a cached prefix is ``(salt, exact token prefix)``; hits happen only at multiples of
+the block size (32 tokens); the probed/stored lengths follow a checkpoint policy (``FIXED_BLOCKS`` = every multiple,
+``START_AND_END`` = ``{32, 64, L-32, L}``, ``ANCHORS`` = 32/64/128-aligned anchors + L); lookup returns the longest hit; a
+full-prompt hit replays the last prompt token; entries are evicted LRU beyond ``max_entries``. Salts compose as
+``cache_salt`` -> ``lora:<id>|salt`` -> ``tp:size=N:rank=R|...`` (LocalGenerationBackend.java:36-50,
+InProcessTensorParallelRankService.java:96-103).
+
+What differs by design: the reference copies a full KV snapshot per checkpoint; here a prefix is a chain of page ids
+whose reference counts are bumped, so a hit costs no copy and no extra memory, and the 512-token cap
+(``max_prefix_tokens``) is a setting, not a limit of the data structure.
+
+Layout per attention layer: ``k[pages, KV, page_size, D]`` and ``v[...]`` in the working dtype; page 0 is a scratch page
+that padded batch rows write to. Recurrent (mamba) layers get per-sequence state slots instead of pages.
+"""
+from __future__ import annotations
+
+import hashlib
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+PAGE_SIZE = 32
+
+
+@dataclass
+class KvCacheSettings:
+    """Defaults follow core/.../tensor/KvBufferCacheSettings.java:20-31,45 (block 32, 512 prefix tokens, 10,000 entries)."""
+
+    block_size: int = PAGE_SIZE
+    max_prefix_tokens: int = 512
+    max_entries: int = 10_000
+    policy: str = "START_AND_END"  # FIXED_BLOCKS | START_AND_END | ANCHORS
+    checkpoints: int = 4
+    enabled: bool = True
+    compression: str = "NONE"  # NONE | LZ4 | MSE_TURBOQUANT (host snapshots only, see kv.snapshot)
+
+    def checkpoint_lengths(self, n_tokens: int) -> list[int]:
+        b = self.block_size
+        L = (min(n_tokens, self.max_prefix_tokens) // b) * b
+        if L <= 0:
+            return []
+        if self.policy == "FIXED_BLOCKS":
+            return list(range(b, L + 1, b))
+        if self.policy == "START_AND_END":
+            c = {b, 2 * b, L - b, L}
+            return sorted(x for x in c if 0 < x <= L)
+        if self.policy == "ANCHORS":
+            c = {L}
+            for a in (32, 64, 128):
+                a = (a // b) * b
+                if 0 < a <= L:
+                    c.add(a)
+            return sorted(c)
+        raise ValueError(f"unknown checkpoint policy {self.policy}")
+
+
+class PageAllocator:
+    """Free list + reference counts over page ids ``1 .. num_pages - 1`` (page 0 is scratch)."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self.free = list(range(num_pages - 1, 0, -1))
+        self.ref = [0] * num_pages
+
+    def available(self) -> int:
+        return len(self.free)
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise MemoryError("KV cache is out of pages")
+        p = self.free.pop()
+        self.ref[p] = 1
+        return p
+
+    def retain(self, p: int) -> None:
+        self.ref[p] += 1
+
+    def release(self, p: int) -> None:
+        self.ref[p] -= 1
+        if self.ref[p] == 0:
+            self.free.append(p)
+        elif self.ref[p] < 0:
+            raise RuntimeError(f"page {p} released more often than retained")
+
+
+@dataclass
+class PrefixEntry:
+    pages: list[int]
+    length: int
+    state: Optional[dict] = None  # recurrent-state snapshot for hybrid models
+
+
+class PrefixCache:
+    """LRU map ``hash(salt, tokens[:L]) -> pages`` holding one reference per cached page."""
+
+    def __init__(self, settings: KvCacheSettings, allocator: PageAllocator):
+        self.settings = settings
+        self.alloc = allocator
+        self.entries: "OrderedDict[bytes, PrefixEntry]" = OrderedDict()
+        self.metrics = {"lookup": 0, "hits": 0, "misses": 0, "evict": 0, "stored": 0, "hit_tokens": 0}
+
+    @staticmethod
+    def key(salt: str, tokens: list[int]) -> bytes:
+        h = hashlib.blake2b(digest_size=20)
+        h.update(salt.encode("utf-8"))
+        h.update(b"\x00")
+        h.update(torch.tensor(tokens, dtype=torch.int64).numpy().tobytes())
+        return h.digest()
+
+    def lookup(self, salt: str, tokens: list[int]) -> Optional[PrefixEntry]:
+        """Longest cached prefix among the policy's checkpoint lengths (retains its pages for the caller)."""
+        self.metrics["lookup"] += 1
+        if not self.settings.enabled:
+            self.metrics["misses"] += 1
+            return None
+        best = None
+        for L in sorted(self.settings.checkpoint_lengths(len(tokens)), reverse=True):
+            k = self.key(salt, tokens[:L])
+            e = self.entries.get(k)
+            if e is not None:
+                self.entries.move_to_end(k)
+                best = e
+                break
+        if best is None:
+            self.metrics["misses"] += 1
+            return None
+        self.metrics["hits"] += 1
+        self.metrics["hit_tokens"] += best.length
+        for p in best.pages:
+            self.alloc.retain(p)
+        return PrefixEntry(list(best.pages), best.length, best.state)
+
+    def store(self, salt: str, tokens: list[int], pages: list[int], state_at: Optional[dict] = None) -> int:
+        """Register the checkpoint prefixes of a prompt whose KV now lives in ``pages``. Returns entries added."""
+        if not self.settings.enabled:
+            return 0
+        added = 0
+        b = self.settings.block_size
+        for L in self.settings.checkpoint_lengths(len(tokens)):
+            k = self.key(salt, tokens[:L])
+            if k in self.entries:
+                self.entries.move_to_end(k)
+                continue
+            if state_at is not None and L not in state_at:
+                continue  # hybrid models can only resume where a recurrent-state snapshot exists
+            chain = pages[: L // b]
+            for p in chain:
+                self.alloc.retain(p)
+            self.entries[k] = PrefixEntry(list(chain), L, None if state_at is None else state_at[L])
+            added += 1
+            self.metrics["stored"] += 1
+        while len(self.entries) > self.settings.max_entries:
+            self.evict_one()
+        return added
+
+    def evict_one(self) -> bool:
+        if not self.entries:
+            return False
+        _, e = self.entries.popitem(last=False)
+        for p in e.pages:
+            self.alloc.release(p)
+        self.metrics["evict"] += 1
+        return True
+
+    def clear(self) -> None:
+        while self.evict_one():
+            pass
+
+
+class PagedKVCache:
+    """Device storage + allocator + prefix cache for one model replica (one tensor-parallel rank)."""
+
+    def __init__(self, layout: dict, num_pages: int, device, dtype, settings: Optional[KvCacheSettings] = None,
+                 max_state_slots: int = 0, mamba_shapes: Optional[dict] = None):
+        self.settings = settings or KvCacheSettings()
+        self.page_size = self.settings.block_size
+        if self.page_size % 32:
+            raise ValueError("page size must be a multiple of 32")
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.num_pages = num_pages
+        self.layout = layout
+        kinds = layout["layer_kinds"]
+        self.k: list[Optional[torch.Tensor]] = []
+        self.v: list[Optional[torch.Tensor]] = []
+        shape = (num_pages, layout["kv_heads"], self.page_size, layout["head_dim"])
+        for kind in kinds:
+            if kind == "mamba":
+                self.k.append(None)
+                self.v.append(None)
+            else:
+                self.k.append(torch.zeros(shape, dtype=dtype, device=self.device))
+                self.v.append(torch.zeros(shape, dtype=dtype, device=self.device))
+        self.allocator = PageAllocator(num_pages)
+        self.prefix = PrefixCache(self.settings, self.allocator)
+        # recurrent state (hybrid models): per layer conv_state [slots, convDim, K-1] and ssm_state [slots, H, d_head, S]
+        self.conv_state: dict[int, torch.Tensor] = {}
+        self.ssm_state: dict[int, torch.Tensor] = {}
+        self.free_slots = list(range(max_state_slots - 1, -1, -1))
+        if mamba_shapes and max_state_slots > 0:
+            for i, kind in enumerate(kinds):
+                if kind == "mamba":
+                    self.conv_state[i] = torch.zeros((max_state_slots,) + tuple(mamba_shapes["conv"]), dtype=torch.float32, device=self.device)
+                    self.ssm_state[i] = torch.zeros((max_state_slots,) + tuple(mamba_shapes["ssm"]), dtype=torch.float32, device=self.device)
+
+    def layer(self, i: int):
+        return self.k[i], self.v[i]
+
+    @staticmethod
+    def bytes_per_page(layout: dict, page_size: int, dtype) -> int:
+        n_attn = sum(1 for k in layout["layer_kinds"] if k != "mamba")
+        return 2 * n_attn * layout["kv_heads"] * page_size * layout["head_dim"] * torch.empty((), dtype=dtype).element_size()
+
+    # -- per-sequence page management ---------------------------------------------------------------------------
+    def ensure_pages(self, pages: list[int], n_tokens: int) -> None:
+        need = (n_tokens + self.page_size - 1) // self.page_size
+        while len(pages) < need:
+            if self.allocator.available() == 0 and not self.prefix.evict_one():
+                raise MemoryError("KV cache is out of pages")
+            if self.allocator.available() == 0:
+                continue
+            pages.append(self.allocator.alloc())
+
+    def release_pages(self, pages: list[int]) -> None:
+        for p in pages:
+            self.allocator.release(p)
+        pages.clear()
+
+    def can_allocate(self, n_pages: int) -> bool:
+        cached = sum(len(e.pages) for e in self.prefix.entries.values())
+        return self.allocator.available() + cached >= n_pages
+
+    def alloc_state_slot(self) -> int:
+        if not self.free_slots:
+            raise MemoryError("no free recurrent-state slot")
+        s = self.free_slots.pop()
+        for t in list(self.conv_state.values()) + list(self.ssm_state.values()):
+            t[s].zero_()
+        return s
+
+    def free_state_slot(self, s: int) -> None:
+        self.free_slots.append(s)
+
+    def snapshot_state(self, slot: int) -> dict:
+        return {"conv": {i: t[slot].clone() for i, t in self.conv_state.items()},
+                "ssm": {i: t[slot].clone() for i, t in self.ssm_state.items()}}
+
+    def restore_state(self, slot: int, snap: dict) -> None:
+        for i, t in snap["conv"].items():
+            self.conv_state[i][slot].copy_(t)
+        for i, t in snap["ssm"].items():
+            self.ssm_state[i][slot].copy_(t)
+
+    def gather_rows(self, layer: int, pages: list[int], n_tokens: int):
+        """Dense ``[KV, n_tokens, D]`` copies of K and V (tests, snapshots, debugging)."""
+        idx = torch.tensor(pages[: (n_tokens + self.page_size - 1) // self.page_size], device=self.device, dtype=torch.long)
+        k = self.k[layer][idx].permute(1, 0, 2, 3).reshape(self.layout["kv_heads"], -1, self.layout["head_dim"])[:, :n_tokens]
+        v = self.v[layer][idx].permute(1, 0, 2, 3).reshape(self.layout["kv_heads"], -1, self.layout["head_dim"])[:, :n_tokens]
+        return k, v
+
+
+def compose_salt(cache_salt: str = "", lora_id: Optional[str] = None, tp_rank: int = 0, tp_size: int = 1) -> str:
+    salt = cache_salt or ""
+    if lora_id:
+        salt = f"lora:{lora_id}|{salt}"
+    if tp_size > 1:
+        salt = f"tp:size={tp_size}:rank={tp_rank}|{salt}"
+    return salt

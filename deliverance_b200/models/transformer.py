@@ -1,0 +1,363 @@
+"""Decoder-only model graph shared by llama, mistral, qwen2, qwen3, gemma2, mixtral, qwen3_moe and granitemoehybrid.
+
+One graph, configured by :class:`~deliverance_b200.config.ModelConfig` flags, over the ragged-batch op surface in
+:mod:`deliverance_b200.ops`. Per layer (reference: core/.../generator/TransformerBlock.java:161-200):
+pre-attention norm -> fused qkv projection -> per-head q/k norm + RoPE + paged KV write -> paged attention -> o_proj
+[-> tensor-parallel all-reduce] [-> gemma2 post-attention norm] -> residual -> pre-FF norm -> gate|up -> act*mul ->
+down [-> all-reduce] [-> post-FF norm] -> residual. Residual adds are folded into the following norm kernel.
+
+Tensor names per family follow the loader contract of the reference (LlamaModel.java:45-183, Qwen2Model.java:79-81,
+Qwen3Model.java:60-125, Qwen3MoeModel.java:67-123, MixtralModel.java:79-96, Gemma2Model.java:56-172,
+GraniteMoeHybridModel.java:118-181). Tensor-parallel shards: q/k/v/gate/up by output rows, o/down by input columns,
+everything else replicated (DefaultTransformerWeightPolicyResolver.java:10-26).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from .. import ops
+from ..ckpt.loader import ShardSpec, WeightLoader
+from ..ckpt.safetensors_io import Q4Tensor
+from ..config import ModelConfig
+from ..ops import LinearWeight, ref
+from ..parallel.context import SINGLE, TensorParallelContext, TensorParallelPlanner
+from .batch import ForwardBatch
+
+
+@dataclass
+class LoraSlot:
+    """Runtime LoRA delta for one projection: ``out += (x @ A^T) @ (scale * B)^T``."""
+
+    a: torch.Tensor  # [r, in]
+    b_scaled: torch.Tensor  # [out, r]
+
+
+@dataclass
+class LayerWeights:
+    kind: str = "attention"  # "attention" | "sliding" | "mamba"
+    input_norm: Optional[torch.Tensor] = None
+    qkv: Optional[LinearWeight] = None
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    o: Optional[LinearWeight] = None
+    post_attn_norm: Optional[torch.Tensor] = None  # gemma2 only
+    pre_ff_norm: Optional[torch.Tensor] = None
+    post_ff_norm: Optional[torch.Tensor] = None  # gemma2 only
+    gate_up: Optional[LinearWeight] = None
+    down: Optional[LinearWeight] = None
+    # MoE
+    router: Optional[LinearWeight] = None
+    experts_gate_up: list = field(default_factory=list)  # per local expert
+    experts_down: list = field(default_factory=list)
+    shared_gate_up: Optional[LinearWeight] = None  # granite shared MLP
+    shared_down: Optional[LinearWeight] = None
+    # mamba2
+    mamba: Optional[dict] = None
+    lora: dict = field(default_factory=dict)  # projection name -> LoraSlot
+
+
+def _cat_weights(parts: list) -> "torch.Tensor | Q4Tensor":
+    """Concatenate projection weights along output rows (all dense or all JQ4)."""
+    if all(isinstance(p, Q4Tensor) for p in parts):
+        packed = torch.cat([p.packed for p in parts], dim=0)
+        scales = torch.cat([p.scales for p in parts], dim=0)
+        return Q4Tensor(packed, scales, (packed.shape[0], packed.shape[1] * 2))
+    dense = [p.dequantize(torch.float32) if isinstance(p, Q4Tensor) else p for p in parts]
+    dt = dense[0].dtype
+    return torch.cat([d.to(dt) for d in dense], dim=0)
+
+
+class DecoderModel:
+    """Weights + forward for one rank."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None,
+                 tp: TensorParallelContext = SINGLE):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        self.tp = tp
+        TensorParallelPlanner.validate(cfg, tp.size)
+        self.n_heads = cfg.num_heads // tp.size
+        self.n_kv = cfg.num_kv_heads // tp.size
+        self.layers: list[LayerWeights] = []
+        self.embed: Optional[torch.Tensor] = None
+        self.final_norm: Optional[torch.Tensor] = None
+        self.lm_head: Optional[LinearWeight] = None
+        self.cos = self.sin = None
+        self.layer_hook: Optional[Callable[[int, str, torch.Tensor], None]] = None  # debug / trace hook
+        self.profiler = None
+        self.active_lora: Optional[str] = None
+        self._moe_impl = None
+
+    # ------------------------------------------------------------------------------------------------ loading
+    def _dev(self, t: torch.Tensor, dtype=None) -> torch.Tensor:
+        return t.to(device=self.device, dtype=dtype or self.dtype).contiguous()
+
+    def _lin(self, w, bias=None) -> LinearWeight:
+        lw = LinearWeight(w if isinstance(w, Q4Tensor) else w.to(self.dtype), None if bias is None else bias.float())
+        return lw.to(self.device, self.dtype)
+
+    def load(self, loader: WeightLoader, head_quant: Optional[str] = None, prefix: str = "model.") -> "DecoderModel":
+        cfg, tp = self.cfg, self.tp
+        row = lambda groups=1: ShardSpec("row", tp.rank, tp.size, groups) if tp.enabled else None  # noqa: E731
+        col = ShardSpec("col", tp.rank, tp.size) if tp.enabled else None
+
+        def get(name, shard=None):
+            return loader.load(name, shard)
+
+        def vec(name):
+            t = loader.load(name)
+            return self._dev(t.reshape(-1) if not isinstance(t, Q4Tensor) else t.dequantize().reshape(-1))
+
+        emb = loader.load(prefix + "embed_tokens.weight")
+        emb_dense = emb.dequantize(torch.float32) if isinstance(emb, Q4Tensor) else emb
+        self.embed = self._dev(emb_dense)
+        for i in range(cfg.num_layers):
+            p = f"{prefix}layers.{i}."
+            lw = LayerWeights(kind=cfg.layer_type(i))
+            lw.input_norm = vec(p + "input_layernorm.weight")
+            if lw.kind == "mamba":
+                lw.mamba = self._load_mamba(loader, p + "mamba.")
+            else:
+                parts = [get(p + f"self_attn.{n}_proj.weight", row()) for n in ("q", "k", "v")]
+                bias = None
+                if cfg.qkv_bias and loader.has(p + "self_attn.q_proj.bias"):
+                    bias = torch.cat([loader.load(p + f"self_attn.{n}_proj.bias", row()).float().reshape(-1) for n in ("q", "k", "v")])
+                lw.qkv = self._lin(_cat_weights(parts), bias)
+                if cfg.qk_norm:
+                    lw.q_norm = vec(p + "self_attn.q_norm.weight")
+                    lw.k_norm = vec(p + "self_attn.k_norm.weight")
+                lw.o = self._lin(get(p + "self_attn.o_proj.weight", col))
+            if cfg.post_norms:
+                lw.post_attn_norm = vec(p + "post_attention_layernorm.weight")
+                lw.pre_ff_norm = vec(p + "pre_feedforward_layernorm.weight")
+                lw.post_ff_norm = vec(p + "post_feedforward_layernorm.weight")
+            else:
+                lw.pre_ff_norm = vec(p + "post_attention_layernorm.weight")
+            self._load_ff(loader, lw, i, p, get, row, col)
+            self.layers.append(lw)
+        self.final_norm = vec(prefix + "norm.weight")
+        # output head: lm_head.weight, else tied to the embedding table; optional load-time JQ4 quantisation
+        if not cfg.tie_word_embeddings and loader.has("lm_head.weight"):
+            head = loader.load("lm_head.weight")
+        else:
+            head = emb
+        if head_quant and head_quant.upper() == "Q4" and not isinstance(head, Q4Tensor):
+            from ..ckpt.jq4 import q4_quantize
+
+            hp, hs = q4_quantize(head.float())
+            head = Q4Tensor(hp, hs, tuple(head.shape))
+        if isinstance(head, Q4Tensor) or head is not emb or self.device.type != "cuda":
+            self.lm_head = self._lin(head)
+        else:
+            self.lm_head = LinearWeight(self.embed)  # share storage with the embedding table
+        if cfg.use_rope:
+            cos, sin = ref.rope_tables(cfg.head_dim, cfg.max_position_embeddings, cfg.rope_theta, cfg.rope_factor)
+            self.cos, self.sin = cos.to(self.device), sin.to(self.device)
+        return self
+
+    def _load_ff(self, loader, lw, i, p, get, row, col):
+        cfg = self.cfg
+        mt = cfg.model_type
+        if mt == "mixtral":
+            lw.router = self._lin(loader.load(p + "block_sparse_moe.gate.weight"))
+            for e in range(cfg.num_experts):
+                ep = p + f"block_sparse_moe.experts.{e}."
+                lw.experts_gate_up.append(self._lin(_cat_weights([get(ep + "w1.weight"), get(ep + "w3.weight")])))
+                lw.experts_down.append(self._lin(get(ep + "w2.weight")))
+        elif mt == "qwen3_moe" and cfg.is_sparse_layer(i):
+            lw.router = self._lin(loader.load(p + "mlp.gate.weight"))
+            for e in range(cfg.num_experts):
+                ep = p + f"mlp.experts.{e}."
+                lw.experts_gate_up.append(self._lin(_cat_weights([get(ep + "gate_proj.weight"), get(ep + "up_proj.weight")])))
+                lw.experts_down.append(self._lin(get(ep + "down_proj.weight")))
+        elif mt == "granitemoehybrid":
+            lw.shared_gate_up = self._lin(get(p + "shared_mlp.input_linear.weight"))
+            lw.shared_down = self._lin(get(p + "shared_mlp.output_linear.weight"))
+            if cfg.num_experts > 0:
+                lw.router = self._lin(loader.load(p + "block_sparse_moe.router.layer.weight"))
+                win = get(p + "block_sparse_moe.input_linear.weight")  # [E, 2I, hidden]
+                wout = get(p + "block_sparse_moe.output_linear.weight")  # [E, hidden, I]
+                for e in range(cfg.num_experts):
+                    lw.experts_gate_up.append(self._lin(_slice_expert(win, e)))
+                    lw.experts_down.append(self._lin(_slice_expert(wout, e)))
+        else:
+            parts = [get(p + "mlp.gate_proj.weight", row()), get(p + "mlp.up_proj.weight", row())]
+            lw.gate_up = self._lin(_cat_weights(parts))
+            lw.down = self._lin(get(p + "mlp.down_proj.weight", col))
+
+    def _load_mamba(self, loader, p) -> dict:
+        f32 = lambda n: self._dev(loader.load_dense(p + n), torch.float32)  # noqa: E731
+        m = {
+            "in_proj": self._lin(loader.load(p + "in_proj.weight")),
+            "out_proj": self._lin(loader.load(p + "out_proj.weight")),
+            "conv_w": f32("conv1d.weight"),
+            "conv_b": f32("conv1d.bias") if loader.has(p + "conv1d.bias") else None,
+            "dt_bias": f32("dt_bias").reshape(-1),
+            "A_log": f32("A_log").reshape(-1),
+            "D": f32("D").reshape(-1),
+            "norm_w": f32("norm.weight").reshape(-1),
+        }
+        return m
+
+    # ------------------------------------------------------------------------------------------------ forward
+    def _trace(self, layer: int, stage: str, t: torch.Tensor) -> None:
+        if self.layer_hook is not None:
+            self.layer_hook(layer, stage, t)
+
+    def _stage(self, name: str):
+        return self.profiler.stage(name) if self.profiler is not None else _NULL
+
+    def embed_tokens(self, batch: ForwardBatch) -> torch.Tensor:
+        return ops.embedding(self.embed, batch.token_ids, self.cfg.embedding_multiplier, dtype=self.dtype)
+
+    def _lora(self, lw: LayerWeights, name: str, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        slot = lw.lora.get(name)
+        if slot is None:
+            return y
+        from ..ckpt.lora import apply_lora_delta
+
+        return apply_lora_delta(x, y, slot.a, slot.b_scaled)
+
+    def attention(self, i: int, lw: LayerWeights, x: torch.Tensor, batch: ForwardBatch, kv) -> torch.Tensor:
+        cfg = self.cfg
+        with self._stage("causalselfattention.qkv_projection"):
+            qkv = ops.linear(x, lw.qkv)
+            if lw.lora:
+                qkv = self._lora(lw, "qkv", x, qkv)
+        k_cache, v_cache = kv.layer(i)
+        with self._stage("causalselfattention.rope"):
+            q = ops.rope_kv(qkv, batch.positions, batch.slots, lw.q_norm, lw.k_norm, self.cos, self.sin, k_cache, v_cache,
+                            self.n_heads, self.n_kv, cfg.head_dim, cfg.norm_eps, cfg.norm_weight_offset)
+        window = cfg.window(i)
+        with self._stage("causalselfattention.score_value"):
+            if batch.is_decode:
+                a = ops.decode_attention(q, k_cache, v_cache, batch.block_tables, batch.ctx_len, self.n_heads, cfg.scale,
+                                         cfg.attn_softcap, window, batch.decode_splits)
+            else:
+                a = ops.prefill_attention(q, k_cache, v_cache, batch.block_tables, batch.q_start, batch.q_len, batch.ctx_len,
+                                          self.n_heads, cfg.scale, cfg.attn_softcap, window, True, batch.tile_seq, batch.tile_q0)
+        with self._stage("causalselfattention.output_projection"):
+            o = self._row_parallel(a, lw.o, f"layer.{i}.self_attn.o_proj")
+            if lw.lora:
+                o = self._lora(lw, "o", a, o)
+        return o
+
+    def _row_parallel(self, x: torch.Tensor, w: LinearWeight, key: str) -> torch.Tensor:
+        """Row-parallel projection followed by the tensor-parallel sum."""
+        if self.tp.enabled and self.tp.fused is not None and x.device.type == "cuda":
+            return self.tp.fused.linear_all_reduce(x, w, key)
+        y = ops.linear(x, w)
+        if self.tp.enabled:
+            with self._stage("causalselfattention.all_reduce" if "attn" in key else "mlpblock.all_reduce"):
+                y = self.tp.all_reduce(key, y)
+        return y
+
+    def feed_forward(self, i: int, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        if lw.router is not None and cfg.model_type != "granitemoehybrid":
+            return self.moe(i, lw, x)
+        if cfg.model_type == "granitemoehybrid":
+            with self._stage("mlpblock.shared"):
+                h = ops.act_mul(ops.linear(x, lw.shared_gate_up), cfg.hidden_act)
+                y = ops.linear(h, lw.shared_down)
+            if lw.router is not None:
+                y = y + self.moe(i, lw, x)
+            return y
+        with self._stage("mlpblock.gate_up_projection"):
+            gu = ops.linear(x, lw.gate_up)
+            if lw.lora:
+                gu = self._lora(lw, "gate_up", x, gu)
+        with self._stage("mlpblock.activation_multiply"):
+            h = ops.act_mul(gu, cfg.hidden_act)
+        with self._stage("mlpblock.down_projection"):
+            d = self._row_parallel(h, lw.down, f"layer.{i}.mlp.down_proj")
+            if lw.lora:
+                d = self._lora(lw, "down", h, d)
+        return d
+
+    def moe(self, i: int, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+        from .moe import moe_forward
+
+        with self._stage("moe.forward"):
+            return moe_forward(self, i, lw, x)
+
+    def mamba(self, i: int, lw: LayerWeights, x: torch.Tensor, batch: ForwardBatch, kv) -> torch.Tensor:
+        from .mamba import mamba_forward
+
+        with self._stage("mamba.forward"):
+            return mamba_forward(self, i, lw, x, batch, kv)
+
+    def forward_hidden(self, batch: ForwardBatch, kv) -> torch.Tensor:
+        """Run every layer; returns the final-normed hidden states ``[T, hidden]``."""
+        cfg = self.cfg
+        residual = self.embed_tokens(batch)
+        self._trace(-1, "embed", residual)
+        eps, off, rm = cfg.norm_eps, cfg.norm_weight_offset, cfg.residual_multiplier
+        x = ops.rmsnorm(residual, self.layers[0].input_norm, eps, off)
+        for i, lw in enumerate(self.layers):
+            if lw.kind == "mamba":
+                a = self.mamba(i, lw, x, batch, kv)
+            else:
+                a = self.attention(i, lw, x, batch, kv)
+            if lw.post_attn_norm is not None:
+                a = ops.rmsnorm(a, lw.post_attn_norm, eps, off)
+            self._trace(i, "attn", a)
+            x = ops.add_rmsnorm(a, residual, lw.pre_ff_norm, eps, off, rm)
+            f = self.feed_forward(i, lw, x)
+            if lw.post_ff_norm is not None:
+                f = ops.rmsnorm(f, lw.post_ff_norm, eps, off)
+            self._trace(i, "ff", f)
+            nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
+            x = ops.add_rmsnorm(f, residual, nxt, eps, off, rm)
+            self._trace(i, "out", residual)
+        return x
+
+    def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
+        """Full-vocabulary fp32 logits (before logit scaling / softcap, which the sampler applies)."""
+        with self._stage("sampler.output_projection"):
+            return ops.linear(hidden_rows, self.lm_head, out_f32=True)
+
+    def forward(self, batch: ForwardBatch, kv, all_rows: bool = False) -> torch.Tensor:
+        h = self.forward_hidden(batch, kv)
+        if not all_rows and batch.logits_rows is not None and not batch.is_decode:
+            h = h.index_select(0, batch.logits_rows)
+        return self.logits(h.contiguous())
+
+    # ------------------------------------------------------------------------------------------------ misc
+    def kv_layout(self) -> dict:
+        cfg = self.cfg
+        return {"layers": cfg.num_layers, "kv_heads": self.n_kv, "head_dim": cfg.head_dim,
+                "layer_kinds": [cfg.layer_type(i) for i in range(cfg.num_layers)]}
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * self.embed.element_size()
+        for lw in self.layers:
+            for w in (lw.qkv, lw.o, lw.gate_up, lw.down, lw.router, lw.shared_gate_up, lw.shared_down):
+                if w is not None:
+                    n += w.nbytes()
+            for w in lw.experts_gate_up + lw.experts_down:
+                n += w.nbytes()
+        if self.lm_head is not None and (self.lm_head.q4 or self.lm_head.w is not self.embed):
+            n += self.lm_head.nbytes()
+        return n
+
+
+def _slice_expert(w, e: int):
+    if isinstance(w, Q4Tensor):
+        return Q4Tensor(w.packed[e], w.scales[e], tuple(w.shape[1:]))
+    return w[e]
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+_NULL = _Null()

@@ -1,0 +1,276 @@
+"""Op surface of the framework.
+
+Every function dispatches on the device of its inputs: CUDA tensors run the hand-written sm_100a kernels of the in-tree
+extension (and raise if that extension is missing — there is no silent eager fallback on a GPU box); CPU tensors run the
+plain PyTorch statements in :mod:`.ref` (fp32 oracle, CPU tests, the TinyLlama-shape fp32 plumbing configuration).
+
+The surface mirrors the reference's ``TensorOperations`` SPI (tensor/.../operations/TensorOperations.java:12-283):
+GEMM with shared-input batches (fused qkv / gate|up weights), accumulate/scale (folded into norm + residual kernels),
+quantize, activation-multiply, gather-rows-add (embedding), paged decode attention.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import ref
+from .build import load_extension
+from ..ckpt.safetensors_io import Q4Tensor
+
+_ext = None
+_ext_checked = False
+
+
+def ext():
+    """The compiled extension, or ``None`` when it has not been built."""
+    global _ext, _ext_checked
+    if not _ext_checked:
+        _ext = load_extension()
+        _ext_checked = True
+    return _ext
+
+
+def require_ext():
+    e = ext()
+    if e is None:
+        raise RuntimeError(
+            "deliverance_b200 CUDA extension is not built: run `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(or `python -m deliverance_b200.ops.build`) before using CUDA tensors")
+    return e
+
+
+def _cuda(t: torch.Tensor) -> bool:
+    return t.device.type == "cuda"
+
+
+def check_status(device: Optional[int] = None) -> None:
+    """Raise if a kernel on ``device`` recorded a wait that ran out (bounded mbarrier / flag waits)."""
+    e = ext()
+    if e is None or not torch.cuda.is_available():
+        return
+    dev = torch.cuda.current_device() if device is None else device
+    code = e.take_status(dev)
+    if code:
+        names = {1: "an mbarrier wait ran out of time", 2: "a peer-flag wait ran out of time", 3: "bad kernel arguments"}
+        raise RuntimeError(f"deliverance_b200 kernel status {code}: {names.get(code, 'unknown')}")
+
+
+# ---------------------------------------------------------------------------------------------------------- linear
+class LinearWeight:
+    """A ``[N, K]`` projection weight, dense (bf16 on CUDA, fp32 on CPU) or JQ4 (packed + scales)."""
+
+    def __init__(self, w: "torch.Tensor | Q4Tensor", bias: Optional[torch.Tensor] = None):
+        self.bias = bias
+        self._handle = None
+        if isinstance(w, Q4Tensor):
+            self.q4 = True
+            self.packed = w.packed.reshape(-1, w.packed.shape[-1]).contiguous()
+            self.scales = w.scales.reshape(-1, w.scales.shape[-1]).contiguous().to(torch.float32)
+            self.N, self.K = int(self.packed.shape[0]), int(self.packed.shape[1]) * 2
+            self.w = None
+        else:
+            self.q4 = False
+            self.w = w.contiguous()
+            self.N, self.K = int(w.shape[0]), int(w.shape[1])
+            self.packed = self.scales = None
+
+    @property
+    def device(self) -> torch.device:
+        return (self.packed if self.q4 else self.w).device
+
+    def to(self, device, dtype: Optional[torch.dtype] = None) -> "LinearWeight":
+        bias = None if self.bias is None else self.bias.to(device=device, dtype=torch.float32)
+        if self.q4:
+            out = LinearWeight.__new__(LinearWeight)
+            out.q4, out.N, out.K, out.w, out._handle = True, self.N, self.K, None, None
+            out.packed = self.packed.to(device)
+            sc = self.scales
+            if torch.device(device).type == "cuda" and sc.shape[1] % 4:
+                # TMA needs a 16-byte row pitch for the scale sidecar: pad K/32 to a multiple of 4 columns
+                pad = 4 - sc.shape[1] % 4
+                sc = torch.nn.functional.pad(sc, (0, pad))
+            out.scales = sc.to(device).contiguous()
+            out.bias = bias
+            return out
+        return LinearWeight(self.w.to(device=device, dtype=dtype or self.w.dtype), bias)
+
+    def dense(self, dtype=torch.float32) -> torch.Tensor:
+        if self.q4:
+            from ..ckpt.jq4 import q4_dequantize
+
+            return q4_dequantize(self.packed, self.scales[:, : self.K // 32], dtype)
+        return self.w.to(dtype)
+
+    def handle(self):
+        if self._handle is None:
+            e = require_ext()
+            if self.q4:
+                self._handle = e.GemmWeight(self.packed, self.scales, self.K)
+            else:
+                if self.w.dtype != torch.bfloat16:
+                    self.w = self.w.to(torch.bfloat16)
+                self._handle = e.GemmWeight(self.w, None, self.K)
+            if self.bias is not None and self.bias.dtype != torch.float32:
+                self.bias = self.bias.float()
+        return self._handle
+
+    def nbytes(self) -> int:
+        if self.q4:
+            return self.packed.numel() + self.scales.numel() * 4
+        return self.w.numel() * self.w.element_size()
+
+
+def linear(x: torch.Tensor, w: LinearWeight, out_f32: bool = False, impl: int = 0, force_splits: int = 0,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [T, K] @ W[N, K]^T (+ bias)``."""
+    if _cuda(x):
+        return w.handle().run(x, out, w.bias, out_f32, impl, force_splits)
+    if w.q4:
+        y = ref.linear_q4(x, w.packed, w.scales[:, : w.K // 32], w.bias)
+    else:
+        y = ref.linear_dense(x, w.w, w.bias)
+    return y.float() if out_f32 else y
+
+
+# ---------------------------------------------------------------------------------------------------------- norms etc.
+def rmsnorm(x, w, eps, offset=0.0):
+    if _cuda(x):
+        return require_ext().rmsnorm(x, w, eps, offset)
+    return ref.rmsnorm(x, w, eps, offset)
+
+
+def add_rmsnorm(x, residual, w, eps, offset=0.0, res_mult=1.0):
+    """``residual += x * res_mult`` in place; returns ``rmsnorm(residual)``."""
+    if _cuda(x):
+        return require_ext().add_rmsnorm(x, residual, w, eps, offset, res_mult)
+    return ref.add_rmsnorm(x, residual, w, eps, offset, res_mult)
+
+
+def layernorm(x, w, b, eps):
+    if _cuda(x):
+        return require_ext().layernorm(x, w, b, eps)
+    return ref.layernorm(x, w, b, eps)
+
+
+def act_mul(gate_up, act):
+    if _cuda(gate_up):
+        return require_ext().act_mul(gate_up, act)
+    return ref.act_mul(gate_up, act)
+
+
+def activation(x, act):
+    if _cuda(x):
+        return require_ext().activation(x.contiguous(), act)
+    return ref.act_fn(act)(x.float()).to(x.dtype)
+
+
+def embedding(table, ids, scale=1.0, pos_table=None, pos=None, type_table=None, types=None, dtype=None):
+    if _cuda(table):
+        return require_ext().embedding(table, ids.to(torch.int32), scale, pos_table, None if pos is None else pos.to(torch.int32),
+                                       type_table, None if types is None else types.to(torch.int32))
+    out = ref.embedding(table, ids, scale, torch.float32)
+    if pos_table is not None:
+        out = out + pos_table[pos.long()].float()
+    if type_table is not None:
+        out = out + (type_table[types.long()].float() if types is not None else type_table[0].float())
+    return out.to(dtype or table.dtype)
+
+
+def rope_kv(qkv, positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset=0.0):
+    """Per-head q/k RMSNorm (optional) + RoPE (optional) + paged cache write. Returns q ``[T, H*D]`` (a view on CUDA)."""
+    if _cuda(qkv):
+        require_ext().rope_kv(qkv, positions.to(torch.int32), slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps,
+                              norm_offset)
+        return qkv[:, : H * D]
+    q = ref.qk_prepare_and_cache(qkv, positions.long(), slots.long(), H, KV, D, q_norm_w, k_norm_w, eps, norm_offset, cos, sin,
+                                 k_cache, v_cache)
+    return q.reshape(qkv.shape[0], H * D)
+
+
+def decode_splits(num_seqs: int, kv_heads: int, max_ctx: int, sms: int = 148) -> int:
+    """Split-KV factor: enough CTAs for two waves, at least four 32-key tiles per split."""
+    ctas = max(1, num_seqs * kv_heads)
+    want = max(1, (2 * sms + ctas - 1) // ctas)
+    tiles = max(1, (max_ctx + 31) // 32)
+    return int(max(1, min(want, tiles // 4 if tiles >= 8 else 1, 64)))
+
+
+def decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, H, scale, softcap=0.0, window=0, splits=1):
+    """One query row per sequence against the paged cache. q ``[B, H*D]`` -> ``[B, H*D]``."""
+    if _cuda(q):
+        return require_ext().decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, H, scale, softcap, window, splits)
+    B = q.shape[0]
+    D = k_cache.shape[-1]
+    qs = torch.arange(B)
+    o = ref.paged_attention(q.reshape(B, H, D), k_cache, v_cache, block_tables, qs, torch.ones(B, dtype=torch.long), ctx_lens,
+                            scale, softcap, window, True)
+    return o.reshape(B, H * D)
+
+
+def prefill_tiles(q_lens: list[int], tile: int = 64) -> tuple[list[int], list[int]]:
+    seqs, q0s = [], []
+    for i, n in enumerate(q_lens):
+        for s in range(0, n, tile):
+            seqs.append(i)
+            q0s.append(s)
+    return seqs, q0s
+
+
+def prefill_attention(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens, H, scale, softcap=0.0, window=0, causal=True,
+                      tile_seq=None, tile_q0=None):
+    """Ragged query rows against the paged cache (K/V of the new tokens are already in the cache)."""
+    if _cuda(q):
+        if tile_seq is None:
+            ts, t0 = prefill_tiles([int(v) for v in q_len.tolist()])
+            tile_seq = torch.tensor(ts, dtype=torch.int32, device=q.device)
+            tile_q0 = torch.tensor(t0, dtype=torch.int32, device=q.device)
+        return require_ext().prefill_attention(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens, tile_seq, tile_q0, H, scale,
+                                               softcap, window, causal)
+    T = q.shape[0]
+    D = k_cache.shape[-1]
+    o = ref.paged_attention(q.reshape(T, H, D), k_cache, v_cache, block_tables, q_start, q_len, ctx_lens, scale, softcap, window, causal)
+    return o.reshape(T, H * D)
+
+
+def argmax(logits, mask=None, softcap=0.0, inv_scale=1.0):
+    """First-maximum argmax over allowed tokens; returns (index int64 [B], post-processed value [B])."""
+    if _cuda(logits):
+        idx, val = require_ext().argmax(logits, mask, softcap, inv_scale)
+        return idx, val
+    lf = logits_post(logits.clone().float(), mask, softcap, inv_scale)
+    val, idx = torch.max(lf, dim=-1)  # torch CPU max returns the first maximal index
+    return idx, val
+
+
+def logits_post(logits, mask=None, softcap=0.0, inv_scale=1.0):
+    """In place: ``softcap(logits * inv_scale)``, disallowed tokens -> -inf. ``mask`` is an int32 allow-bitmask."""
+    if _cuda(logits):
+        require_ext().logits_post(logits, mask, softcap, inv_scale)
+        return logits
+    if inv_scale != 1.0:
+        logits.mul_(inv_scale)
+    if softcap and softcap > 0:
+        logits.copy_(torch.tanh(logits / softcap) * softcap)
+    if mask is not None:
+        V = logits.shape[-1]
+        bits = unpack_mask(mask, V)
+        logits.masked_fill_(~bits, float("-inf"))
+    return logits
+
+
+def unpack_mask(mask: torch.Tensor, V: int) -> torch.Tensor:
+    """int32 bitmask ``[B, ceil(V/32)]`` -> bool ``[B, V]``."""
+    m = mask.to(torch.int64) & 0xFFFFFFFF
+    shifts = torch.arange(32, device=mask.device, dtype=torch.int64)
+    bits = ((m.unsqueeze(-1) >> shifts) & 1).bool().reshape(mask.shape[0], -1)
+    return bits[:, :V]
+
+
+def q4_quantize(w: torch.Tensor):
+    if _cuda(w):
+        p, s = require_ext().q4_quantize(w.contiguous())
+        return p, s
+    from ..ckpt.jq4 import q4_quantize as host
+
+    return host(w)

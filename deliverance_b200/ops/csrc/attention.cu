@@ -1,0 +1,532 @@
+// Paged-KV attention.
+//   * decode: one query token per sequence, split-KV, all query heads of a GQA group share one pass over K/V
+//     (the kernel is KV-bandwidth bound; CUDA-core math keeps up with HBM for group sizes <= 8), merge kernel.
+//   * prefill: flash-style tiles of 64 query rows x 64 keys, online softmax in registers, causal + sliding window +
+//     logit softcap, K/V fetched from the paged cache with cp.async into swizzled shared memory.
+// KV cache layout: [num_pages, KV, page_size, D] bf16, page_size % 32 == 0. Queries are read in place from the fused
+// qkv activation (row stride given). Scores: softmax(softcap(scale * q.k)), key j visible to position p iff j <= p
+// and (window == 0 or j > p - window)  (reference: core/.../generator/CausalSelfAttention.java:458-532,
+// tensor/.../operations/TensorOperations.java:225-271, tensor/.../VectorTensorMathUtils.java:34-78).
+#include "common.cuh"
+
+namespace dlv {
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ float softcap_apply(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
+// =====================================================================================================================
+// Decode
+// =====================================================================================================================
+// grid (num_seqs, KV, splits), 128 threads. GP = padded group size (power of two >= H / KV).
+template <int D, int GP>
+__global__ void __launch_bounds__(128) decode_attn_kernel(
+    const __nv_bfloat16* __restrict__ q, long long q_stride,  // q row t at q + t * q_stride, heads contiguous [H, D]
+    const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+    const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ ctx_lens,
+    __nv_bfloat16* __restrict__ out,          // [num_seqs, H, D] (used when splits == 1)
+    float* __restrict__ part_o,               // [num_seqs, H, splits, D]
+    float* __restrict__ part_ml,              // [num_seqs, H, splits, 2]
+    int H, int KV, int page_size, float scale, float softcap, int window, int splits) {
+  constexpr int KSTRIDE = D + 32;  // bf16 elements; +64 B keeps the 4-lane key groups on distinct banks
+  constexpr int DP = D / 2;        // bf16x2 columns
+  constexpr int KGROUPS = 128 / DP > 0 ? 128 / DP : 1;
+  extern __shared__ __align__(16) uint8_t dsm[];
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dsm);        // [2][32][KSTRIDE]
+  __nv_bfloat16* sV = sK + 2 * 32 * KSTRIDE;                         // [2][32][D]
+  float* sQ = reinterpret_cast<float*>(sV + 2 * 32 * D);             // [GP][D]
+  float* sS = sQ + GP * D;                                           // [GP][32]
+  float* sM = sS + GP * 32;                                          // [GP] running max
+  float* sL = sM + GP;                                               // [GP] running sum
+  float* sA = sL + GP;                                               // [GP] rescale factor of this tile
+  float* sRed = sA + GP;                                             // [KGROUPS][GP][D] cross-group reduction (aliases sK)
+
+  const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = H / KV;
+  const int ctx = ctx_lens[b];
+  const int first_key = (window > 0 && ctx > window) ? ctx - window : 0;
+  const int tile_lo = first_key / 32, tile_hi = (ctx + 31) / 32;
+  const int ntiles = tile_hi - tile_lo;
+  const int per = (ntiles + splits - 1) / splits;
+  const int t0 = tile_lo + sp * per, t1 = min(tile_hi, t0 + per);
+
+  for (int i = tid; i < GP * D; i += 128) {
+    const int g = i / D, d = i % D;
+    sQ[i] = g < G ? bf2f(q[b * q_stride + static_cast<long long>(kvh * G + g) * D + d]) * scale : 0.f;
+  }
+  if (tid < GP) {
+    sM[tid] = -INFINITY;
+    sL[tid] = 0.f;
+  }
+  float acc[GP][2];
+#pragma unroll
+  for (int g = 0; g < GP; ++g) acc[g][0] = acc[g][1] = 0.f;
+
+  auto load_tile = [&](int tile, int buf) {
+    const int key0 = tile * 32;
+    const int page = block_tables[static_cast<long long>(b) * bt_stride + key0 / page_size];
+    const long long base = ((static_cast<long long>(page) * KV + kvh) * page_size + key0 % page_size) * D;
+    constexpr int CPR = D / 8;  // 16 B chunks per row
+    for (int c = tid; c < 32 * CPR; c += 128) {
+      const int r = c / CPR, cc = c % CPR;
+      const bool valid = key0 + r < ctx;
+      cp_async16(smem_u32(sK + (buf * 32 + r) * KSTRIDE + cc * 8), k_cache + base + r * D + cc * 8, valid);
+      cp_async16(smem_u32(sV + (buf * 32 + r) * D + cc * 8), v_cache + base + r * D + cc * 8, valid);
+    }
+    cp_async_commit();
+  };
+
+  if (t0 < t1) load_tile(t0, 0);
+  for (int tile = t0; tile < t1; ++tile) {
+    const int buf = (tile - t0) & 1;
+    if (tile + 1 < t1) {
+      load_tile(tile + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    // ---- scores: thread (key j, part p) covers the 16 B chunks c * 4 + p of the key row
+    {
+      const int j = tid >> 2, p4 = tid & 3;
+      float s[GP];
+#pragma unroll
+      for (int g = 0; g < GP; ++g) s[g] = 0.f;
+      const __nv_bfloat16* krow = sK + (buf * 32 + j) * KSTRIDE;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        const int d0 = (c * 4 + p4) * 8;
+        const uint4 kv = *reinterpret_cast<const uint4*>(krow + d0);
+        const uint32_t* ku = reinterpret_cast<const uint32_t*>(&kv);
+        float kf[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 f = unpack_bf162(ku[e]);
+          kf[2 * e] = f.x;
+          kf[2 * e + 1] = f.y;
+        }
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+          const float4 qa = *reinterpret_cast<const float4*>(sQ + g * D + d0);
+          const float4 qb = *reinterpret_cast<const float4*>(sQ + g * D + d0 + 4);
+          s[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] + qb.y * kf[5] + qb.z * kf[6] +
+                  qb.w * kf[7];
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GP; ++g) {
+        s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
+        s[g] += __shfl_xor_sync(0xffffffffu, s[g], 2);
+      }
+      if (p4 == 0) {
+        const int key = tile * 32 + j;
+        const bool vis = key < ctx && key >= first_key;
+#pragma unroll
+        for (int g = 0; g < GP; ++g) sS[g * 32 + j] = vis ? softcap_apply(s[g], softcap) : -INFINITY;
+      }
+    }
+    __syncthreads();
+    // ---- online softmax: warp w owns heads w, w + 4, ...
+    for (int g = warp; g < GP; g += 4) {
+      const float sv = sS[g * 32 + lane];
+      const float m_old = sM[g];
+      const float m_new = fmaxf(m_old, warp_max(sv));
+      const float pexp = (sv == -INFINITY) ? 0.f : __expf(sv - m_new);
+      const float psum = warp_sum(pexp);
+      sS[g * 32 + lane] = pexp;
+      if (lane == 0) {
+        const float alpha = (m_old == -INFINITY) ? 0.f : __expf(m_old - m_new);
+        sA[g] = alpha;
+        sM[g] = m_new;
+        sL[g] = sL[g] * alpha + psum;
+      }
+    }
+    __syncthreads();
+    // ---- P.V: thread (column pair dp, key group kg)
+    {
+      const int dp = tid % DP, kg = tid / DP;
+      if (kg < KGROUPS) {
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+          const float a = sA[g];
+          acc[g][0] *= a;
+          acc[g][1] *= a;
+        }
+        for (int j = kg; j < 32; j += KGROUPS) {
+          const float2 v = unpack_bf162(*reinterpret_cast<const uint32_t*>(sV + (buf * 32 + j) * D + 2 * dp));
+#pragma unroll
+          for (int g = 0; g < GP; ++g) {
+            const float pj = sS[g * 32 + j];
+            acc[g][0] += pj * v.x;
+            acc[g][1] += pj * v.y;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // ---- reduce key groups, write (partial) output
+  if (KGROUPS > 1) {
+    const int dp = tid % DP, kg = tid / DP;
+#pragma unroll
+    for (int g = 0; g < GP; ++g) {
+      sRed[(kg * GP + g) * D + 2 * dp] = acc[g][0];
+      sRed[(kg * GP + g) * D + 2 * dp + 1] = acc[g][1];
+    }
+    __syncthreads();
+  }
+  for (int i = tid; i < G * D; i += 128) {
+    const int g = i / D, d = i % D;
+    float o;
+    if (KGROUPS > 1) {
+      o = 0.f;
+      for (int kg = 0; kg < KGROUPS; ++kg) o += sRed[(kg * GP + g) * D + d];
+    } else {
+      // KGROUPS == 1: thread dp holds columns 2dp, 2dp + 1 -> stage through sRed for a uniform write loop
+      o = 0.f;
+    }
+    const int h = kvh * G + g;
+    if (KGROUPS > 1) {
+      if (splits == 1) {
+        const float l = sL[g];
+        out[(static_cast<long long>(b) * H + h) * D + d] = f2bf(l > 0.f ? o / l : 0.f);
+      } else {
+        part_o[((static_cast<long long>(b) * H + h) * splits + sp) * D + d] = o;
+      }
+    }
+  }
+  if (KGROUPS == 1) {
+    const int dp = tid;  // 128 threads == D / 2 (D == 256)
+#pragma unroll
+    for (int g = 0; g < GP; ++g) {
+      if (g < G) {
+        const int h = kvh * G + g;
+        if (splits == 1) {
+          const float l = sL[g];
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          *reinterpret_cast<uint32_t*>(out + (static_cast<long long>(b) * H + h) * D + 2 * dp) =
+              pack_bf162(acc[g][0] * inv, acc[g][1] * inv);
+        } else {
+          float* po = part_o + ((static_cast<long long>(b) * H + h) * splits + sp) * D + 2 * dp;
+          po[0] = acc[g][0];
+          po[1] = acc[g][1];
+        }
+      }
+    }
+  }
+  if (splits > 1 && tid < G) {
+    const int h = kvh * G + tid;
+    float* ml = part_ml + ((static_cast<long long>(b) * H + h) * splits + sp) * 2;
+    ml[0] = sM[tid];
+    ml[1] = sL[tid];
+  }
+}
+
+// grid (num_seqs, H), D threads
+__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, int H, int D, int splits) {
+  const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const long long base = (static_cast<long long>(b) * H + h) * splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(base + s) * 2];
+    const float w = (ms == -INFINITY) ? 0.f : __expf(ms - m);
+    num += w * part_o[(base + s) * D + d];
+    den += w * part_ml[(base + s) * 2 + 1];
+  }
+  out[(static_cast<long long>(b) * H + h) * D + d] = f2bf(den > 0.f ? num / den : 0.f);
+}
+
+template <int D, int GP>
+static size_t decode_smem_bytes() {
+  constexpr int KSTRIDE = D + 32;
+  constexpr int DP = D / 2;
+  constexpr int KGROUPS = 128 / DP > 0 ? 128 / DP : 1;
+  size_t kv = (2 * 32 * KSTRIDE + 2 * 32 * D) * 2;
+  size_t fl = (GP * D + GP * 32 + 3 * GP + KGROUPS * GP * D) * 4;
+  return kv + fl;
+}
+
+template <int D, int GP>
+static int launch_decode_t(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
+                           const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int page, float scale,
+                           float cap, int window, int splits, cudaStream_t st) {
+  const size_t smem = decode_smem_bytes<D, GP>();
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(decode_attn_kernel<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    attr_done = true;
+  }
+  dim3 grid(B, KV, splits);
+  decode_attn_kernel<D, GP><<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), q_stride,
+                                                      static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc),
+                                                      bt, bt_stride, ctx, static_cast<__nv_bfloat16*>(out), po, pml, H, KV, page,
+                                                      scale, cap, window, splits);
+  if (splits > 1) {
+    dim3 g2(B, H);
+    decode_merge_kernel<<<g2, D, 0, st>>>(po, pml, static_cast<__nv_bfloat16*>(out), H, D, splits);
+  }
+  return 0;
+}
+
+int launch_decode_attention(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
+                            const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int D, int page, float scale,
+                            float cap, int window, int splits, cudaStream_t st) {
+  if (B == 0) return 0;
+  const int G = H / KV;
+  int gp = 1;
+  while (gp < G) gp <<= 1;
+#define DLV_DEC(DD, GG) \
+  return launch_decode_t<DD, GG>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, B, H, KV, page, scale, cap, window, splits, st)
+#define DLV_DEC_D(DD)                \
+  switch (gp) {                      \
+    case 1: DLV_DEC(DD, 1);          \
+    case 2: DLV_DEC(DD, 2);          \
+    case 4: DLV_DEC(DD, 4);          \
+    case 8: DLV_DEC(DD, 8);          \
+    default: return 2;               \
+  }
+  switch (D) {
+    case 64: DLV_DEC_D(64)
+    case 128: DLV_DEC_D(128)
+    case 256: DLV_DEC_D(256)
+    default: return 1;
+  }
+#undef DLV_DEC_D
+#undef DLV_DEC
+}
+
+// =====================================================================================================================
+// Prefill (flash, mma.sync m16n8k16 bf16 -> fp32)
+// =====================================================================================================================
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// tile (row-major [rows][D] bf16, 16 B chunks XOR-swizzled with row % 8): byte offset of (row, chunk)
+template <int D>
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+  return static_cast<uint32_t>(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+// grid (num_q_tiles, H), 128 threads; tile i covers query rows [tile_q0[i], tile_q0[i] + 64) of sequence tile_seq[i]
+template <int D>
+__global__ void __launch_bounds__(128) prefill_attn_kernel(
+    const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ k_cache,
+    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int bt_stride,
+    const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ ctx_lens,
+    const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, __nv_bfloat16* __restrict__ out,  // [T, H, D]
+    int H, int KV, int page_size, float scale, float softcap, int window, int causal) {
+  constexpr int BM = 64, BN = 64, CPR = D / 8;
+  extern __shared__ __align__(128) uint8_t psm[];
+  uint8_t* sQ = psm;                       // BM * D * 2
+  uint8_t* sK = sQ + BM * D * 2;           // 2 buffers
+  uint8_t* sV = sK + 2 * BN * D * 2;       // 2 buffers
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x], h = blockIdx.y;
+  const int kvh = h / (H / KV);
+  const int qs = q_start[seq], ql = q_len[seq], ctx = ctx_lens[seq];
+  const int pos0 = ctx - ql;  // position of query row 0 of this sequence
+  const int rows = min(BM, ql - q0);
+  // key range needed by this tile
+  const int last_pos = causal ? pos0 + q0 + rows - 1 : ctx - 1;
+  const int first_pos = pos0 + q0;
+  const int key_hi = min(ctx, last_pos + 1);
+  const int key_lo = (window > 0) ? max(0, first_pos - window + 1) : 0;
+  const int kt0 = key_lo / BN, kt1 = (key_hi + BN - 1) / BN;
+
+  // ---- Q tile
+  for (int c = tid; c < BM * CPR; c += 128) {
+    const int r = c / CPR, cc = c % CPR;
+    const bool valid = r < rows;
+    const __nv_bfloat16* src = q + static_cast<long long>(qs + q0 + (valid ? r : 0)) * q_stride + static_cast<long long>(h) * D + cc * 8;
+    cp_async16(smem_u32(sQ) + swz<D>(r, cc), src, valid);
+  }
+  auto load_kv = [&](int kt, int buf) {
+    for (int c = tid; c < BN * CPR; c += 128) {
+      const int r = c / CPR, cc = c % CPR;
+      const int key = kt * BN + r;
+      const bool valid = key < ctx;
+      const int kk = valid ? key : 0;
+      const int page = block_tables[static_cast<long long>(seq) * bt_stride + kk / page_size];
+      const long long off = ((static_cast<long long>(page) * KV + kvh) * page_size + kk % page_size) * D + cc * 8;
+      cp_async16(smem_u32(sK) + buf * BN * D * 2 + swz<D>(r, cc), k_cache + off, valid);
+      cp_async16(smem_u32(sV) + buf * BN * D * 2 + swz<D>(r, cc), v_cache + off, valid);
+    }
+    cp_async_commit();
+  };
+  if (kt0 < kt1) load_kv(kt0, 0); else cp_async_commit();
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int g = lane >> 2, t4 = lane & 3;
+  const int row_a = warp * 16 + g, row_b = row_a + 8;           // rows inside the tile
+  const int pos_a = first_pos + row_a, pos_b = first_pos + row_b;  // absolute positions (first_pos = pos0 + q0)
+
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int buf = (kt - kt0) & 1;
+    if (kt + 1 < kt1) {
+      load_kv(kt + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t kbase = smem_u32(sK) + buf * BN * D * 2, vbase = smem_u32(sV) + buf * BN * D * 2;
+    // ---- S = Q K^T (16 rows x 64 keys per warp)
+    float s[BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(smem_u32(sQ) + swz<D>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)), a[0], a[1], a[2], a[3]);
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; nt += 2) {
+        // two key tiles (nt, nt + 1) x this k-step: matrices (keys nt, d lo), (keys nt, d hi), (keys nt+1, d lo), (keys nt+1, d hi)
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(kbase + swz<D>(nt * 8 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+        mma_bf16_16816(s[nt], a, b0, b1);
+        mma_bf16_16816(s[nt + 1], a, b2, b3);
+      }
+    }
+    // ---- scale, softcap, mask, online softmax
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = kt * BN + nt * 8 + 2 * t4 + (e & 1);
+        const int pos = (e < 2) ? pos_a : pos_b;
+        float v = softcap_apply(s[nt][e] * scale, softcap);
+        bool vis = key < ctx;
+        if (causal) vis = vis && key <= pos;
+        if (window > 0) vis = vis && key > pos - window;
+        v = vis ? v : -INFINITY;
+        s[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float alpha[2], m_new[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      m_new[r] = fmaxf(m_run[r], mx[r]);
+      alpha[r] = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - m_new[r]);
+      m_run[r] = m_new[r];
+    }
+    float rs[2] = {0.f, 0.f};
+    uint32_t pa[BN / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+      float p[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mm = m_new[e >> 1];
+        p[e] = (s[nt][e] == -INFINITY || mm == -INFINITY) ? 0.f : __expf(s[nt][e] - mm);
+        rs[e >> 1] += p[e];
+      }
+      pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf162(p[0], p[1]);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf162(p[2], p[3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+      l_run[r] = l_run[r] * alpha[r] + rs[r];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= alpha[0];
+      o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1];
+      o[i][3] *= alpha[1];
+    }
+    // ---- O += P V
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+      for (int dt = 0; dt < D / 8; dt += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vbase + swz<D>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dt + (lane >> 4)), b0, b1, b2, b3);
+        mma_bf16_16816(o[dt], pa[kk], b0, b1);
+        mma_bf16_16816(o[dt + 1], pa[kk], b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  // ---- write
+  const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+#pragma unroll
+  for (int dt = 0; dt < D / 8; ++dt) {
+    const int d = dt * 8 + 2 * t4;
+    if (row_a < rows)
+      *reinterpret_cast<uint32_t*>(out + (static_cast<long long>(qs + q0 + row_a) * H + h) * D + d) = pack_bf162(o[dt][0] * inv_a, o[dt][1] * inv_a);
+    if (row_b < rows)
+      *reinterpret_cast<uint32_t*>(out + (static_cast<long long>(qs + q0 + row_b) * H + h) * D + d) = pack_bf162(o[dt][2] * inv_b, o[dt][3] * inv_b);
+  }
+}
+
+template <int D>
+static int launch_prefill_t(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
+                            const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,
+                            int num_tiles, void* out, int H, int KV, int page, float scale, float cap, int window, int causal,
+                            cudaStream_t st) {
+  const size_t smem = static_cast<size_t>(64 * D * 2) * 5;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(prefill_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    attr_done = true;
+  }
+  dim3 grid(num_tiles, H);
+  prefill_attn_kernel<D><<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), q_stride, static_cast<const __nv_bfloat16*>(kc),
+                                                   static_cast<const __nv_bfloat16*>(vc), bt, bt_stride, q_start, q_len, ctx, tile_seq,
+                                                   tile_q0, static_cast<__nv_bfloat16*>(out), H, KV, page, scale, cap, window, causal);
+  return 0;
+}
+
+int launch_prefill_attention(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
+                             const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,
+                             int num_tiles, void* out, int H, int KV, int D, int page, float scale, float cap, int window,
+                             int causal, cudaStream_t st) {
+  if (num_tiles == 0) return 0;
+  switch (D) {
+    case 64:
+      return launch_prefill_t<64>(q, q_stride, kc, vc, bt, bt_stride, q_start, q_len, ctx, tile_seq, tile_q0, num_tiles, out, H, KV,
+                                  page, scale, cap, window, causal, st);
+    case 128:
+      return launch_prefill_t<128>(q, q_stride, kc, vc, bt, bt_stride, q_start, q_len, ctx, tile_seq, tile_q0, num_tiles, out, H, KV,
+                                   page, scale, cap, window, causal, st);
+    case 256:
+      return launch_prefill_t<256>(q, q_stride, kc, vc, bt, bt_stride, q_start, q_len, ctx, tile_seq, tile_q0, num_tiles, out, H, KV,
+                                   page, scale, cap, window, causal, st);
+    default:
+      return 1;
+  }
+}
+
+}  // namespace dlv

@@ -1,0 +1,450 @@
+// torch <-> kernel-launcher glue. Every entry validates device, dtype, contiguity and alignment on the host before a
+// launch (no kernel is started on arguments that could fault), and launches on the current CUDA stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <memory>
+#include <unordered_map>
+
+#include "gemm_api.h"
+
+namespace {
+
+using torch::Tensor;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+void check_bf16(const Tensor& t, const char* name) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+}
+void check_last_error(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+}
+int act_code(const std::string& a) {
+  if (a == "silu" || a == "swish") return 0;
+  if (a == "gelu_pytorch_tanh" || a == "gelu_new" || a == "gelu_tanh" || a == "gelu_fast") return 1;
+  if (a == "gelu") return 2;
+  if (a == "relu") return 3;
+  if (a == "tanh") return 4;
+  TORCH_CHECK(false, "unknown activation ", a);
+}
+
+// ---- per-device scratch for split-K partials, tile counters and the kernel status word ---------------------------
+struct DeviceScratch {
+  Tensor ws;        // fp32
+  Tensor counters;  // int32, zero between launches
+  Tensor status;    // int32 [1]
+};
+DeviceScratch& scratch_for(int device) {
+  static std::unordered_map<int, DeviceScratch> table;
+  auto it = table.find(device);
+  if (it == table.end()) {
+    DeviceScratch s;
+    auto fopt = torch::TensorOptions().device(torch::kCUDA, device).dtype(torch::kFloat32);
+    auto iopt = torch::TensorOptions().device(torch::kCUDA, device).dtype(torch::kInt32);
+    s.ws = torch::empty({static_cast<long>(8) * 1024 * 1024}, fopt);  // 32 MB
+    s.counters = torch::zeros({8192}, iopt);
+    s.status = torch::zeros({1}, iopt);
+    it = table.emplace(device, std::move(s)).first;
+  }
+  return it->second;
+}
+
+// ---- GEMM weight handle -------------------------------------------------------------------------------------------
+class GemmWeight {
+ public:
+  // dense: w bf16 [N, K]; JQ4: packed uint8 [N, K/2] + scales fp32 [N, pitch] (pitch % 4 == 0, pitch >= K/32)
+  GemmWeight(Tensor w, c10::optional<Tensor> scales, int64_t K) {
+    check_cuda(w, "weight");
+    desc_.is_q4 = scales.has_value();
+    if (desc_.is_q4) {
+      TORCH_CHECK(w.scalar_type() == at::kByte && w.dim() == 2, "JQ4 packed weight must be uint8 [N, K/2]");
+      TORCH_CHECK(w.size(1) * 2 == K, "packed width does not match K");
+      scales_ = scales.value();
+      check_cuda(scales_, "scales");
+      TORCH_CHECK(scales_.scalar_type() == at::kFloat && scales_.dim() == 2 && scales_.size(0) == w.size(0), "scales must be fp32 [N, pitch]");
+      TORCH_CHECK(scales_.size(1) % 4 == 0 && scales_.size(1) * 32 >= K, "scale pitch must be a multiple of 4 and cover K/32");
+      desc_.scales = scales_.data_ptr<float>();
+      desc_.scale_pitch = static_cast<int>(scales_.size(1));
+    } else {
+      TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.size(1) == K, "dense weight must be bf16 [N, K]");
+    }
+    w_ = w;
+    desc_.N = static_cast<int>(w.size(0));
+    desc_.K = static_cast<int>(K);
+    desc_.data = w.data_ptr();
+    c10::cuda::CUDAGuard guard(w.device());
+    dlv::gemm_weight_init(&desc_);
+  }
+
+  // out[m, :] = x[m, :] @ W^T (+ bias). impl: 0 = auto, 1 = tcgen05, 2 = CUDA-core GEMV
+  Tensor run(const Tensor& x, c10::optional<Tensor> out_opt, c10::optional<Tensor> bias, bool out_f32, int64_t impl,
+             int64_t force_splits) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2, "x must be bf16 [M, K] on CUDA");
+    TORCH_CHECK(x.size(1) == desc_.K && x.stride(1) == 1, "x inner dimension must be K and dense");
+    TORCH_CHECK(x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x rows must be 16-byte aligned");
+    TORCH_CHECK(x.device() == w_.device(), "x and weight live on different devices");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int M = static_cast<int>(x.size(0));
+    Tensor out;
+    if (out_opt.has_value()) {
+      out = out_opt.value();
+      TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.size(0) == M && out.size(1) == desc_.N && out.stride(1) == 1, "bad out shape");
+      TORCH_CHECK(out.scalar_type() == (out_f32 ? at::kFloat : at::kBFloat16), "bad out dtype");
+    } else {
+      out = torch::empty({M, desc_.N}, x.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+    }
+    const float* bptr = nullptr;
+    if (bias.has_value()) {
+      const Tensor& b = bias.value();
+      TORCH_CHECK(b.is_cuda() && b.scalar_type() == at::kFloat && b.numel() == desc_.N && b.is_contiguous(), "bias must be fp32 [N]");
+      bptr = b.data_ptr<float>();
+    }
+    if (M == 0) return out;
+    const bool simt = impl == 2 || (impl == 0 && M <= 1);
+    if (simt) {
+      dlv::gemv_simt_run(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), out.data_ptr(), static_cast<int>(out.stride(0)), out_f32,
+                         bptr, cur_stream());
+    } else {
+      DeviceScratch& s = scratch_for(x.device().index());
+      dlv::gemm_tc_run(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), out.data_ptr(), static_cast<int>(out.stride(0)), out_f32,
+                       bptr, s.ws.data_ptr<float>(), static_cast<size_t>(s.ws.numel()), s.counters.data_ptr<int>(),
+                       static_cast<int>(s.counters.numel()), s.status.data_ptr<int>(), static_cast<int>(force_splits), cur_stream());
+    }
+    check_last_error("gemm launch");
+    return out;
+  }
+  int64_t n() const { return desc_.N; }
+  int64_t k() const { return desc_.K; }
+  bool is_q4() const { return desc_.is_q4; }
+
+ private:
+  dlv::GemmWeightDesc desc_;
+  Tensor w_, scales_;
+};
+
+// Reads and clears the kernel status word of a device (0 = ok, 1 = barrier wait ran out, 2 = flag wait ran out).
+int64_t take_status(int64_t device) {
+  DeviceScratch& s = scratch_for(static_cast<int>(device));
+  int64_t v = s.status.item<int>();
+  if (v != 0) s.status.zero_();
+  return v;
+}
+void init_scratch(int64_t device) { scratch_for(static_cast<int>(device)); }
+
+// ---- elementwise ----------------------------------------------------------------------------------------------------
+Tensor rmsnorm(const Tensor& x, const Tensor& w, double eps, double offset) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  const int H = static_cast<int>(x.size(-1));
+  TORCH_CHECK(H % 8 == 0 && w.numel() == H, "hidden size must be a multiple of 8");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  dlv::launch_rmsnorm(x.data_ptr(), nullptr, w.data_ptr(), y.data_ptr(), static_cast<int>(x.numel() / H), H, static_cast<float>(eps),
+                      static_cast<float>(offset), 1.f, cur_stream());
+  check_last_error("rmsnorm");
+  return y;
+}
+Tensor add_rmsnorm(const Tensor& x, Tensor& residual, const Tensor& w, double eps, double offset, double res_mult) {
+  check_bf16(x, "x");
+  check_bf16(residual, "residual");
+  check_bf16(w, "w");
+  const int H = static_cast<int>(x.size(-1));
+  TORCH_CHECK(H % 8 == 0 && w.numel() == H && residual.sizes() == x.sizes(), "shape mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  dlv::launch_rmsnorm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), y.data_ptr(), static_cast<int>(x.numel() / H), H,
+                      static_cast<float>(eps), static_cast<float>(offset), static_cast<float>(res_mult), cur_stream());
+  check_last_error("add_rmsnorm");
+  return y;
+}
+Tensor layernorm(const Tensor& x, const Tensor& w, c10::optional<Tensor> b, double eps) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  const int H = static_cast<int>(x.size(-1));
+  TORCH_CHECK(w.numel() == H, "shape mismatch");
+  const void* bp = nullptr;
+  if (b.has_value()) {
+    check_bf16(b.value(), "bias");
+    bp = b.value().data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  dlv::launch_layernorm(x.data_ptr(), w.data_ptr(), bp, y.data_ptr(), static_cast<int>(x.numel() / H), H, static_cast<float>(eps), cur_stream());
+  check_last_error("layernorm");
+  return y;
+}
+Tensor act_mul(const Tensor& gate_up, const std::string& act) {
+  check_bf16(gate_up, "gate_up");
+  TORCH_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 16 == 0, "gate|up width must be a multiple of 16");
+  const int I = static_cast<int>(gate_up.size(1) / 2);
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  Tensor out = torch::empty({gate_up.size(0), I}, gate_up.options());
+  dlv::launch_act_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.size(0), I, act_code(act), cur_stream());
+  check_last_error("act_mul");
+  return out;
+}
+Tensor activation(const Tensor& x, const std::string& act) {
+  check_bf16(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty_like(x);
+  dlv::launch_act(x.data_ptr(), out.data_ptr(), x.numel(), act_code(act), cur_stream());
+  check_last_error("activation");
+  return out;
+}
+Tensor embedding(const Tensor& table, const Tensor& ids, double scale, c10::optional<Tensor> pos_table, c10::optional<Tensor> pos,
+                 c10::optional<Tensor> type_table, c10::optional<Tensor> types) {
+  check_bf16(table, "table");
+  check_cuda(ids, "ids");
+  TORCH_CHECK(ids.scalar_type() == at::kInt, "ids must be int32");
+  const int H = static_cast<int>(table.size(1));
+  TORCH_CHECK(H % 8 == 0, "hidden size must be a multiple of 8");
+  const void* pt = nullptr;
+  const int* pp = nullptr;
+  const void* tt = nullptr;
+  const int* tp = nullptr;
+  if (pos_table.has_value()) {
+    check_bf16(pos_table.value(), "pos_table");
+    TORCH_CHECK(pos.has_value() && pos.value().scalar_type() == at::kInt && pos.value().numel() == ids.numel(), "positions required");
+    check_cuda(pos.value(), "pos");
+    pt = pos_table.value().data_ptr();
+    pp = pos.value().data_ptr<int>();
+  }
+  if (type_table.has_value()) {
+    check_bf16(type_table.value(), "type_table");
+    tt = type_table.value().data_ptr();
+    if (types.has_value()) {
+      check_cuda(types.value(), "types");
+      TORCH_CHECK(types.value().scalar_type() == at::kInt && types.value().numel() == ids.numel(), "bad token types");
+      tp = types.value().data_ptr<int>();
+    }
+  }
+  c10::cuda::CUDAGuard guard(table.device());
+  Tensor out = torch::empty({ids.numel(), H}, table.options());
+  dlv::launch_embedding(table.data_ptr(), ids.data_ptr<int>(), pt, pp, tt, tp, out.data_ptr(), static_cast<int>(ids.numel()), H,
+                        static_cast<int>(table.size(0)), static_cast<float>(scale), cur_stream());
+  check_last_error("embedding");
+  return out;
+}
+
+// qkv [T, (H + 2 KV) * D] modified in place (q heads); k, v scattered into the paged cache [pages, KV, page, D]
+void rope_kv(Tensor& qkv, const Tensor& positions, c10::optional<Tensor> slots, c10::optional<Tensor> q_norm_w,
+             c10::optional<Tensor> k_norm_w, c10::optional<Tensor> cos_t, c10::optional<Tensor> sin_t, c10::optional<Tensor> k_cache,
+             c10::optional<Tensor> v_cache, int64_t H, int64_t KV, int64_t D, double eps, double norm_offset) {
+  check_bf16(qkv, "qkv");
+  check_cuda(positions, "positions");
+  TORCH_CHECK(positions.scalar_type() == at::kInt, "positions must be int32");
+  const int T = static_cast<int>(qkv.size(0));
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == (H + 2 * KV) * D && positions.numel() == T, "bad qkv shape");
+  const long long* sp = nullptr;
+  void *kc = nullptr, *vc = nullptr;
+  int page = 1;
+  if (slots.has_value()) {
+    check_cuda(slots.value(), "slots");
+    TORCH_CHECK(slots.value().scalar_type() == at::kLong && slots.value().numel() == T, "slots must be int64 [T]");
+    TORCH_CHECK(k_cache.has_value() && v_cache.has_value(), "cache tensors required with slots");
+    check_bf16(k_cache.value(), "k_cache");
+    check_bf16(v_cache.value(), "v_cache");
+    TORCH_CHECK(k_cache.value().dim() == 4 && k_cache.value().size(1) == KV && k_cache.value().size(3) == D, "cache must be [pages, KV, page, D]");
+    TORCH_CHECK(v_cache.value().sizes() == k_cache.value().sizes(), "k/v cache shape mismatch");
+    sp = reinterpret_cast<const long long*>(slots.value().data_ptr<int64_t>());
+    kc = k_cache.value().data_ptr();
+    vc = v_cache.value().data_ptr();
+    page = static_cast<int>(k_cache.value().size(2));
+  }
+  const void *qn = nullptr, *kn = nullptr;
+  if (q_norm_w.has_value()) {
+    check_bf16(q_norm_w.value(), "q_norm");
+    check_bf16(k_norm_w.value(), "k_norm");
+    TORCH_CHECK(q_norm_w.value().numel() == D && k_norm_w.value().numel() == D, "q/k norm weights must have head_dim entries");
+    qn = q_norm_w.value().data_ptr();
+    kn = k_norm_w.value().data_ptr();
+  }
+  const float *ct = nullptr, *stb = nullptr;
+  int rot_half = 0, max_pos = 1;
+  if (cos_t.has_value()) {
+    check_cuda(cos_t.value(), "cos");
+    check_cuda(sin_t.value(), "sin");
+    TORCH_CHECK(cos_t.value().scalar_type() == at::kFloat && cos_t.value().dim() == 2 && sin_t.value().sizes() == cos_t.value().sizes(), "cos/sin must be fp32 [max_pos, rot/2]");
+    ct = cos_t.value().data_ptr<float>();
+    stb = sin_t.value().data_ptr<float>();
+    rot_half = static_cast<int>(cos_t.value().size(1));
+    max_pos = static_cast<int>(cos_t.value().size(0));
+    TORCH_CHECK(rot_half * 2 <= D, "rotary dimension exceeds head_dim");
+  }
+  c10::cuda::CUDAGuard guard(qkv.device());
+  int rc = dlv::launch_rope_kv(qkv.data_ptr(), positions.data_ptr<int>(), sp, qn, kn, ct, stb, kc, vc, T, static_cast<int>(H),
+                               static_cast<int>(KV), static_cast<int>(D), page, rot_half, static_cast<float>(eps),
+                               static_cast<float>(norm_offset), max_pos, cur_stream());
+  TORCH_CHECK(rc == 0, "unsupported head_dim ", D, " (64, 128, 256)");
+  check_last_error("rope_kv");
+}
+
+// ---- attention ------------------------------------------------------------------------------------------------------
+// q: view [B, H*D] bf16 with arbitrary row stride (the q part of the fused qkv activation)
+Tensor decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables, const Tensor& ctx_lens,
+                        int64_t H, double scale, double softcap, int64_t window, int64_t splits) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 2 && q.stride(1) == 1, "q must be bf16 [B, H*D]");
+  check_bf16(k_cache, "k_cache");
+  check_bf16(v_cache, "v_cache");
+  check_cuda(block_tables, "block_tables");
+  check_cuda(ctx_lens, "ctx_lens");
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && ctx_lens.scalar_type() == at::kInt, "tables must be int32");
+  const int B = static_cast<int>(q.size(0));
+  const int KV = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
+  TORCH_CHECK(q.size(1) == H * D && H % KV == 0 && page % 32 == 0, "shape mismatch (page size must be a multiple of 32)");
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.size(0) >= B && ctx_lens.numel() >= B, "bad table shapes");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(q.data_ptr()) & 3) == 0, "q misaligned");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({B, H * D}, q.options());
+  if (splits < 1) splits = 1;
+  Tensor po, pml;
+  float *pop = nullptr, *pmlp = nullptr;
+  if (splits > 1) {
+    po = torch::empty({B, H, splits, D}, q.options().dtype(at::kFloat));
+    pml = torch::empty({B, H, splits, 2}, q.options().dtype(at::kFloat));
+    pop = po.data_ptr<float>();
+    pmlp = pml.data_ptr<float>();
+  }
+  int rc = dlv::launch_decode_attention(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(),
+                                        static_cast<int>(block_tables.stride(0)), ctx_lens.data_ptr<int>(), out.data_ptr(), pop, pmlp, B,
+                                        static_cast<int>(H), KV, D, page, static_cast<float>(scale), static_cast<float>(softcap),
+                                        static_cast<int>(window), static_cast<int>(splits), cur_stream());
+  TORCH_CHECK(rc == 0, "decode attention: unsupported head_dim / group size (code ", rc, ")");
+  check_last_error("decode_attention");
+  return out;
+}
+
+Tensor prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables, const Tensor& q_start,
+                         const Tensor& q_len, const Tensor& ctx_lens, const Tensor& tile_seq, const Tensor& tile_q0, int64_t H,
+                         double scale, double softcap, int64_t window, bool causal) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 2 && q.stride(1) == 1, "q must be bf16 [T, H*D]");
+  TORCH_CHECK(q.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(q.data_ptr()) & 15) == 0, "q rows must be 16-byte aligned");
+  check_bf16(k_cache, "k_cache");
+  check_bf16(v_cache, "v_cache");
+  for (const Tensor* t : {&block_tables, &q_start, &q_len, &ctx_lens, &tile_seq, &tile_q0}) {
+    check_cuda(*t, "index tensor");
+    TORCH_CHECK(t->scalar_type() == at::kInt, "index tensors must be int32");
+  }
+  const int T = static_cast<int>(q.size(0));
+  const int KV = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
+  TORCH_CHECK(q.size(1) == H * D && H % KV == 0 && page % 32 == 0, "shape mismatch");
+  TORCH_CHECK(tile_seq.numel() == tile_q0.numel(), "tile arrays differ in length");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({T, H * D}, q.options());
+  int rc = dlv::launch_prefill_attention(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(),
+                                         static_cast<int>(block_tables.stride(0)), q_start.data_ptr<int>(), q_len.data_ptr<int>(),
+                                         ctx_lens.data_ptr<int>(), tile_seq.data_ptr<int>(), tile_q0.data_ptr<int>(),
+                                         static_cast<int>(tile_seq.numel()), out.data_ptr(), static_cast<int>(H), KV, D, page,
+                                         static_cast<float>(scale), static_cast<float>(softcap), static_cast<int>(window), causal ? 1 : 0,
+                                         cur_stream());
+  TORCH_CHECK(rc == 0, "prefill attention: unsupported head_dim");
+  check_last_error("prefill_attention");
+  return out;
+}
+
+// ---- sampling ---------------------------------------------------------------------------------------------------------
+std::vector<Tensor> argmax(const Tensor& logits, c10::optional<Tensor> mask, double softcap, double inv_scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
+  const int B = static_cast<int>(logits.size(0)), V = static_cast<int>(logits.size(1));
+  const uint32_t* mp = nullptr;
+  int mld = 0;
+  if (mask.has_value()) {
+    const Tensor& m = mask.value();
+    check_cuda(m, "mask");
+    TORCH_CHECK(m.scalar_type() == at::kInt && m.dim() == 2 && m.size(0) == B && m.size(1) * 32 >= V, "mask must be int32 [B, ceil(V/32)]");
+    mp = reinterpret_cast<const uint32_t*>(m.data_ptr<int>());
+    mld = static_cast<int>(m.size(1));
+  }
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor idx = torch::empty({B}, logits.options().dtype(at::kLong));
+  Tensor val = torch::empty({B}, logits.options());
+  dlv::launch_argmax(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, mp, mld, static_cast<float>(softcap),
+                     static_cast<float>(inv_scale), reinterpret_cast<long long*>(idx.data_ptr<int64_t>()), val.data_ptr<float>(), cur_stream());
+  check_last_error("argmax");
+  return {idx, val};
+}
+void logits_post(Tensor& logits, c10::optional<Tensor> mask, double softcap, double inv_scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
+  const int B = static_cast<int>(logits.size(0)), V = static_cast<int>(logits.size(1));
+  const uint32_t* mp = nullptr;
+  int mld = 0;
+  if (mask.has_value()) {
+    const Tensor& m = mask.value();
+    check_cuda(m, "mask");
+    TORCH_CHECK(m.scalar_type() == at::kInt && m.dim() == 2 && m.size(0) == B && m.size(1) * 32 >= V, "mask must be int32 [B, ceil(V/32)]");
+    mp = reinterpret_cast<const uint32_t*>(m.data_ptr<int>());
+    mld = static_cast<int>(m.size(1));
+  }
+  c10::cuda::CUDAGuard guard(logits.device());
+  dlv::launch_logits_post(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, mp, mld, static_cast<float>(softcap),
+                          static_cast<float>(inv_scale), cur_stream());
+  check_last_error("logits_post");
+}
+
+// ---- JQ4 ------------------------------------------------------------------------------------------------------------
+std::vector<Tensor> q4_quantize(const Tensor& w) {
+  check_cuda(w, "w");
+  TORCH_CHECK(w.size(-1) % 32 == 0, "last dimension must be a multiple of 32");
+  int code = w.scalar_type() == at::kFloat ? 0 : w.scalar_type() == at::kBFloat16 ? 1 : w.scalar_type() == at::kHalf ? 2 : -1;
+  TORCH_CHECK(code >= 0, "unsupported dtype for quantisation");
+  c10::cuda::CUDAGuard guard(w.device());
+  auto shape = w.sizes().vec();
+  auto pshape = shape, sshape = shape;
+  pshape.back() = shape.back() / 2;
+  sshape.back() = shape.back() / 32;
+  Tensor packed = torch::empty(pshape, w.options().dtype(at::kByte));
+  Tensor scales = torch::empty(sshape, w.options().dtype(at::kFloat));
+  dlv::launch_q4_quantize(w.data_ptr(), code, w.numel() / 32, packed.data_ptr<uint8_t>(), scales.data_ptr<float>(), cur_stream());
+  check_last_error("q4_quantize");
+  return {packed, scales};
+}
+Tensor q4_dequantize(const Tensor& packed, const Tensor& scales, bool to_bf16) {
+  check_cuda(packed, "packed");
+  check_cuda(scales, "scales");
+  TORCH_CHECK(packed.scalar_type() == at::kByte && scales.scalar_type() == at::kFloat, "packed uint8 + fp32 scales expected");
+  TORCH_CHECK(packed.numel() == scales.numel() * 16, "packed / scale sizes do not match");
+  c10::cuda::CUDAGuard guard(packed.device());
+  auto shape = packed.sizes().vec();
+  shape.back() *= 2;
+  Tensor out = torch::empty(shape, packed.options().dtype(to_bf16 ? at::kBFloat16 : at::kFloat));
+  dlv::launch_q4_dequantize(packed.data_ptr<uint8_t>(), scales.data_ptr<float>(), scales.numel(), out.data_ptr(), to_bf16 ? 1 : 0, cur_stream());
+  check_last_error("q4_dequantize");
+  return out;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  py::class_<GemmWeight, std::shared_ptr<GemmWeight>>(m, "GemmWeight")
+      .def(py::init<Tensor, c10::optional<Tensor>, int64_t>(), py::arg("w"), py::arg("scales"), py::arg("K"))
+      .def("run", &GemmWeight::run, py::arg("x"), py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("out_f32") = false,
+           py::arg("impl") = 0, py::arg("force_splits") = 0)
+      .def_property_readonly("N", &GemmWeight::n)
+      .def_property_readonly("K", &GemmWeight::k)
+      .def_property_readonly("is_q4", &GemmWeight::is_q4);
+  m.def("take_status", &take_status);
+  m.def("init_scratch", &init_scratch);
+  m.def("num_sms", &dlv::gemm_num_sms);
+  m.def("rmsnorm", &rmsnorm);
+  m.def("add_rmsnorm", &add_rmsnorm);
+  m.def("layernorm", &layernorm);
+  m.def("act_mul", &act_mul);
+  m.def("activation", &activation);
+  m.def("embedding", &embedding, py::arg("table"), py::arg("ids"), py::arg("scale") = 1.0, py::arg("pos_table") = py::none(),
+        py::arg("pos") = py::none(), py::arg("type_table") = py::none(), py::arg("types") = py::none());
+  m.def("rope_kv", &rope_kv);
+  m.def("decode_attention", &decode_attention);
+  m.def("prefill_attention", &prefill_attention);
+  m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
+  m.def("logits_post", &logits_post, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
+  m.def("q4_quantize", &q4_quantize);
+  m.def("q4_dequantize", &q4_dequantize, py::arg("packed"), py::arg("scales"), py::arg("to_bf16") = false);
+}

@@ -1,0 +1,262 @@
+// Host side of the tcgen05 GEMM (tensor-map encoding, tile / split-K selection, launch) plus a CUDA-core GEMV used for
+// one to four tokens and as an independent implementation in the numerics tests.
+#include <mutex>
+#include <stdexcept>
+#include <string>
+
+#include "gemm_tc.cuh"
+#include "gemm_api.h"
+
+namespace dlv {
+
+// ------------------------------------------------------------------------------------------------ tensor maps
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || p == nullptr)
+      throw std::runtime_error("cuTensorMapEncodeTiled entry point not available");
+    fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `elem_bytes`-sized elements with row pitch `pitch_bytes`; box = [box_rows, box_cols].
+void encode_map_2d(CUtensorMap* map, int dtype_code, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                   uint32_t box_rows, uint32_t box_cols, int swizzle_code) {
+  CUtensorMapDataType dt = dtype_code == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : dtype_code == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUtensorMapSwizzle sw = swizzle_code == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : swizzle_code == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                               : CU_TENSOR_MAP_SWIZZLE_NONE;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) throw std::runtime_error("TMA base address must be 16-byte aligned");
+  if (pitch_bytes % 16 != 0) throw std::runtime_error("TMA row pitch must be a multiple of 16 bytes");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = get_encode()(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+}
+
+// ------------------------------------------------------------------------------------------------ weight handle
+void gemm_weight_init(GemmWeightDesc* w) {
+  if (w->is_q4) {
+    if (w->K % 32 != 0) throw std::runtime_error("JQ4 weight needs K % 32 == 0");
+    encode_map_2d(&w->map_w, 1, w->data, w->N, w->K / 2, static_cast<uint64_t>(w->K / 2), kGemmBM, 64, 64);
+    encode_map_2d(&w->map_s, 2, w->scales, w->N, w->K / 32, static_cast<uint64_t>(w->scale_pitch) * 4, kGemmBM, 4, 0);
+  } else {
+    if (w->K % 8 != 0) throw std::runtime_error("dense weight needs K % 8 == 0");
+    encode_map_2d(&w->map_w, 0, w->data, w->N, w->K, static_cast<uint64_t>(w->K) * 2, kGemmBM, 64, 128);
+    w->map_s = w->map_w;
+  }
+}
+
+int gemm_num_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+template <bool Q4, int BN>
+static void launch_tc(const GemmWeightDesc* w, const CUtensorMap& map_x, GemmParams p, cudaStream_t st) {
+  using L = GemmSmem<Q4, BN>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<Q4, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+    attr_done = true;
+  }
+  dim3 grid(p.n_tiles, p.m_tiles, p.splits);
+  gemm_tc_kernel<Q4, BN><<<grid, kGemmThreads, L::kBytes, st>>>(w->map_w, w->map_s, map_x, p);
+}
+
+size_t gemm_workspace_floats(int M, int N) {
+  // upper bound used by callers that size the split-K workspace once
+  (void)M;
+  (void)N;
+  return static_cast<size_t>(4) * 148 * 128 * 128;
+}
+
+// Choose the token tile. Small batches take the smallest UMMA N that covers them.
+static int pick_bn(int M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 128) return 128;
+  return 256;
+}
+
+void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
+                 float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st) {
+  if (M <= 0) return;
+  if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
+  const int BN = pick_bn(M);
+  GemmParams p;
+  p.M = M;
+  p.N = w->N;
+  p.K = w->K;
+  p.kb_total = (w->K + kGemmBK - 1) / kGemmBK;
+  p.n_tiles = (w->N + kGemmBM - 1) / kGemmBM;
+  p.m_tiles = (M + BN - 1) / BN;
+  const int tiles = p.n_tiles * p.m_tiles;
+  int splits = 1;
+  if (BN <= 128) {
+    const int sms = gemm_num_sms();
+    splits = sms / tiles;  // fill the machine once
+    if (splits < 1) splits = 1;
+    const int max_by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;  // keep >= 4 k-blocks per split
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 16) splits = 16;
+  }
+  if (force_splits > 0) splits = force_splits;
+  if (splits > p.kb_total) splits = p.kb_total;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  if (splits > 1) {
+    const size_t need = static_cast<size_t>(tiles) * splits * BN * kGemmBM;
+    if (ws == nullptr || counters == nullptr || need > ws_floats || tiles > n_counters) {
+      splits = 1;
+      p.kb_per_split = p.kb_total;
+    }
+  }
+  p.splits = splits;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_f32 = out_f32 ? 1 : 0;
+  p.bias = bias;
+  p.ws = ws;
+  p.counters = counters;
+  p.status = status;
+  CUtensorMap map_x;
+  encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
+#define DLV_LAUNCH(BNV)                                        \
+  if (w->is_q4) launch_tc<true, BNV>(w, map_x, p, st);         \
+  else launch_tc<false, BNV>(w, map_x, p, st)
+  switch (BN) {
+    case 16: DLV_LAUNCH(16); break;
+    case 32: DLV_LAUNCH(32); break;
+    case 64: DLV_LAUNCH(64); break;
+    case 128: DLV_LAUNCH(128); break;
+    default: DLV_LAUNCH(256); break;
+  }
+#undef DLV_LAUNCH
+}
+
+// ------------------------------------------------------------------------------------------------ CUDA-core GEMV
+// One warp per weight row, MT tokens. fp32 accumulation; JQ4 blocks are expanded in registers.
+template <int MT, bool Q4>
+__global__ void __launch_bounds__(128) gemv_simt_kernel(const void* __restrict__ wdata, const float* __restrict__ scales,
+                                                        int scale_pitch, const __nv_bfloat16* __restrict__ x, int ldx,
+                                                        void* __restrict__ out, int ldo, int out_f32, const float* __restrict__ bias,
+                                                        int N, int K) {
+  const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (n >= N) return;
+  float acc[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+  if (Q4) {
+    const uint8_t* wrow = static_cast<const uint8_t*>(wdata) + static_cast<size_t>(n) * (K / 2);
+    const float* srow = scales + static_cast<size_t>(n) * scale_pitch;
+    for (int blk = lane; blk < K / 32; blk += 32) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(wrow + blk * 16));
+      const float sc = __ldg(srow + blk);
+      const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+      float wf[32];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const uint32_t byte = (words[i] >> (8 * b)) & 0xFFu;
+          wf[4 * i + b] = static_cast<float>(static_cast<int>(byte & 0xFu) - 8) * sc;
+          wf[16 + 4 * i + b] = static_cast<float>(static_cast<int>(byte >> 4) - 8) * sc;
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const __nv_bfloat16* xr = x + static_cast<size_t>(m) * ldx + blk * 32;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xr + c * 8);
+          const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf162(xu[e]);
+            acc[m] += f.x * wf[c * 8 + 2 * e] + f.y * wf[c * 8 + 2 * e + 1];
+          }
+        }
+      }
+    }
+  } else {
+    const __nv_bfloat16* wrow = static_cast<const __nv_bfloat16*>(wdata) + static_cast<size_t>(n) * K;
+    for (int k0 = lane * 8; k0 < K; k0 += 256) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + k0));
+      const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+      float wf[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf162(wu[e]);
+        wf[2 * e] = f.x;
+        wf[2 * e + 1] = f.y;
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * ldx + k0);
+        const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf162(xu[e]);
+          acc[m] += f.x * wf[2 * e] + f.y * wf[2 * e + 1];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] = warp_sum(acc[m]);
+  if (lane == 0) {
+    const float b = bias ? bias[n] : 0.f;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      if (out_f32) static_cast<float*>(out)[static_cast<size_t>(m) * ldo + n] = acc[m] + b;
+      else static_cast<__nv_bfloat16*>(out)[static_cast<size_t>(m) * ldo + n] = f2bf(acc[m] + b);
+    }
+  }
+}
+
+void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
+                   cudaStream_t st) {
+  const unsigned grid = (w->N + 3) / 4;
+  for (int m0 = 0; m0 < M; m0 += 4) {
+    const int mt = M - m0 < 4 ? M - m0 : 4;
+    const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x) + static_cast<size_t>(m0) * ldx;
+    void* op = out_f32 ? static_cast<void*>(static_cast<float*>(out) + static_cast<size_t>(m0) * ldo)
+                       : static_cast<void*>(static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(m0) * ldo);
+#define DLV_GEMV(MT)                                                                                                          \
+  if (w->is_q4) gemv_simt_kernel<MT, true><<<grid, 128, 0, st>>>(w->data, w->scales, w->scale_pitch, xp, ldx, op, ldo, out_f32, bias, w->N, w->K); \
+  else gemv_simt_kernel<MT, false><<<grid, 128, 0, st>>>(w->data, nullptr, 0, xp, ldx, op, ldo, out_f32, bias, w->N, w->K)
+    switch (mt) {
+      case 1: DLV_GEMV(1); break;
+      case 2: DLV_GEMV(2); break;
+      case 3: DLV_GEMV(3); break;
+      default: DLV_GEMV(4); break;
+    }
+#undef DLV_GEMV
+  }
+}
+
+}  // namespace dlv

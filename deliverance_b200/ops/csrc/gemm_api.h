@@ -1,0 +1,58 @@
+// C++ interface between the torch bindings and the kernel launchers (no torch types below this line).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace dlv {
+
+struct GemmWeightDesc {
+  int N = 0, K = 0;
+  bool is_q4 = false;
+  const void* data = nullptr;     // bf16 [N, K] or packed nibbles [N, K/2]
+  const float* scales = nullptr;  // JQ4: [N, scale_pitch] fp32, scale_pitch >= K/32 and scale_pitch % 4 == 0
+  int scale_pitch = 0;
+  CUtensorMap map_w;
+  CUtensorMap map_s;
+};
+
+void gemm_weight_init(GemmWeightDesc* w);
+int gemm_num_sms();
+void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
+                 float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st);
+void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
+                   cudaStream_t st);
+
+// elementwise.cu
+void launch_rmsnorm(const void* x, void* residual, const void* w, void* y, int T, int H, float eps, float offset, float res_mult,
+                    cudaStream_t st);
+void launch_layernorm(const void* x, const void* w, const void* b, void* y, int T, int H, float eps, cudaStream_t st);
+void launch_act_mul(const void* in, void* out, long long T, int I, int act, cudaStream_t st);
+void launch_act(const void* in, void* out, long long n, int act, cudaStream_t st);
+void launch_embedding(const void* table, const int* ids, const void* pos_table, const int* pos, const void* type_table,
+                      const int* types, void* out, int T, int H, int vocab, float scale, cudaStream_t st);
+int launch_rope_kv(void* qkv, const int* positions, const long long* slots, const void* qn, const void* kn, const float* cos_t,
+                   const float* sin_t, void* k_cache, void* v_cache, int T, int H, int KV, int D, int block_size, int rot_half,
+                   float eps, float norm_offset, int max_pos, cudaStream_t st);
+
+// attention.cu
+int launch_decode_attention(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
+                            const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int D, int page, float scale,
+                            float cap, int window, int splits, cudaStream_t st);
+int launch_prefill_attention(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
+                             const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,
+                             int num_tiles, void* out, int H, int KV, int D, int page, float scale, float cap, int window,
+                             int causal, cudaStream_t st);
+
+// sampling.cu
+void launch_argmax(const float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
+                   long long* out_idx, float* out_val, cudaStream_t st);
+void launch_logits_post(float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
+                        cudaStream_t st);
+
+// quant.cu
+void launch_q4_quantize(const void* w, int src_dtype, long long n_blocks, uint8_t* packed, float* scales, cudaStream_t st);
+void launch_q4_dequantize(const uint8_t* packed, const float* scales, long long n_blocks, void* out, int dst_dtype, cudaStream_t st);
+
+}  // namespace dlv

@@ -1,0 +1,206 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 statement of the same op (deliverance_b200.ops.ref)."""
+import math
+
+import pytest
+import torch
+
+from deliverance_b200 import ops
+from deliverance_b200.ckpt.jq4 import q4_dequantize, q4_quantize
+from deliverance_b200.ckpt.safetensors_io import Q4Tensor
+from deliverance_b200.ops import LinearWeight, ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def _q4_weight(N, K, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(N, K, generator=g) * 0.05
+    p, s = q4_quantize(w)
+    return Q4Tensor(p, s, (N, K)), q4_dequantize(p, s)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("q4", [True, False])
+def test_gemv_simt(M, q4):
+    N, K = 384, 1024
+    qt, wd = _q4_weight(N, K)
+    lw = (LinearWeight(qt) if q4 else LinearWeight(wd.to(torch.bfloat16))).to(DEV, torch.bfloat16)
+    x = (torch.randn(M, K) * 0.5).to(torch.bfloat16).to(DEV)
+    y = ops.linear(x, lw, impl=2)
+    wref = wd if q4 else wd.to(torch.bfloat16).float()
+    yr = x.float().cpu() @ wref.t()
+    assert _rel(y.cpu(), yr) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K,splits", [
+    (1, 256, 512, 1), (8, 256, 1024, 1), (16, 384, 2560, 0), (17, 128, 256, 1), (64, 512, 2048, 0), (64, 2560, 9728, 0),
+    (100, 640, 1216, 1), (128, 256, 4096, 2), (300, 384, 1024, 1), (5, 200, 2560, 4), (33, 1000, 608, 0),
+])
+@pytest.mark.parametrize("q4", [True, False])
+def test_gemm_tcgen05(M, N, K, splits, q4):
+    qt, wd = _q4_weight(N, K, seed=N + K)
+    lw = (LinearWeight(qt) if q4 else LinearWeight(wd.to(torch.bfloat16))).to(DEV, torch.bfloat16)
+    x = (torch.randn(M, K) * 0.5).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(N, device=DEV) if (M % 2 == 0) else None
+    lw.bias = bias
+    y = ops.linear(x, lw, impl=1, force_splits=splits)
+    torch.cuda.synchronize()
+    ops.check_status()
+    wref = wd if q4 else wd.to(torch.bfloat16).float()
+    yr = x.float().cpu() @ wref.t()
+    if bias is not None:
+        yr = yr + bias.cpu()
+    assert y.shape == (M, N)
+    assert _rel(y.cpu(), yr) < 1.5e-2, f"rel err {_rel(y.cpu(), yr)}"
+    # fp32 output path
+    y32 = ops.linear(x, lw, out_f32=True, impl=1, force_splits=splits)
+    assert y32.dtype == torch.float32 and _rel(y32.cpu(), yr) < 1.5e-2
+    # repeated launches reuse the split-K scratch and counters
+    y2 = ops.linear(x, lw, impl=1, force_splits=splits)
+    assert torch.equal(y, y2)
+
+
+def test_rmsnorm_and_add():
+    T, H = 37, 2560
+    x = torch.randn(T, H).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(H) * 0.1 + 1).to(torch.bfloat16).to(DEV)
+    y = ops.rmsnorm(x, w, 1e-6, 0.0)
+    assert _rel(y, ref.rmsnorm(x.float(), w.float(), 1e-6)) < 5e-3
+    y1 = ops.rmsnorm(x, w, 1e-6, 1.0)
+    assert _rel(y1, ref.rmsnorm(x.float(), w.float(), 1e-6, 1.0)) < 5e-3
+    res = torch.randn(T, H).to(torch.bfloat16).to(DEV)
+    res_ref = res.clone().float()
+    y2 = ops.add_rmsnorm(x, res, w, 1e-6, 0.0, 0.5)
+    yr = ref.add_rmsnorm(x.float(), res_ref, w.float(), 1e-6, 0.0, 0.5)
+    assert _rel(res, res_ref) < 5e-3 and _rel(y2, yr) < 8e-3
+
+
+def test_layernorm_act_embedding():
+    T, H = 19, 768
+    x = torch.randn(T, H).to(torch.bfloat16).to(DEV)
+    w = torch.randn(H).to(torch.bfloat16).to(DEV)
+    b = torch.randn(H).to(torch.bfloat16).to(DEV)
+    assert _rel(ops.layernorm(x, w, b, 1e-5), ref.layernorm(x.float(), w.float(), b.float(), 1e-5)) < 5e-3
+    gu = torch.randn(T, 2 * 1024).to(torch.bfloat16).to(DEV)
+    for act in ("silu", "gelu_pytorch_tanh", "gelu"):
+        assert _rel(ops.act_mul(gu, act), ref.act_mul(gu.float(), act)) < 5e-3
+    assert _rel(ops.activation(x, "gelu_new"), ref.act_fn("gelu_new")(x.float())) < 5e-3
+    table = torch.randn(500, H).to(torch.bfloat16).to(DEV)
+    ids = torch.randint(0, 500, (T,), device=DEV)
+    assert _rel(ops.embedding(table, ids, 3.0), table[ids].float() * 3.0) < 5e-3
+    pos_t = torch.randn(64, H).to(torch.bfloat16).to(DEV)
+    pos = torch.randint(0, 64, (T,), device=DEV)
+    assert _rel(ops.embedding(table, ids, 1.0, pos_t, pos), table[ids].float() + pos_t[pos].float()) < 5e-3
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+@pytest.mark.parametrize("qk_norm", [True, False])
+def test_rope_kv(D, qk_norm):
+    T, H, KV, page, pages = 45, 8, 2, 32, 16
+    qkv = torch.randn(T, (H + 2 * KV) * D).to(torch.bfloat16).to(DEV)
+    pos = torch.randint(0, 300, (T,), dtype=torch.int32, device=DEV)
+    slots = torch.randperm(pages * page)[:T].to(torch.int64).to(DEV)
+    cos, sin = ref.rope_tables(D, 512, 1e6)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    qn = (torch.randn(D) * 0.1 + 1).to(torch.bfloat16).to(DEV) if qk_norm else None
+    kn = (torch.randn(D) * 0.1 + 1).to(torch.bfloat16).to(DEV) if qk_norm else None
+    kc = torch.zeros(pages, KV, page, D, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    kc_r, vc_r = kc.clone().float(), vc.clone().float()
+    q_r = ref.qk_prepare_and_cache(qkv.clone().float(), pos.long(), slots, H, KV, D, None if qn is None else qn.float(),
+                                   None if kn is None else kn.float(), 1e-6, 0.0, cos, sin, kc_r, vc_r)
+    q = ops.rope_kv(qkv, pos, slots, qn, kn, cos, sin, kc, vc, H, KV, D, 1e-6, 0.0)
+    assert _rel(q, q_r.reshape(T, H * D)) < 1e-2
+    assert _rel(kc, kc_r) < 1e-2 and _rel(vc, vc_r) < 1e-3
+
+
+def _paged_setup(ctx_lens, KV, D, page=32, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum((c + page - 1) // page for c in ctx_lens) + 1
+    kc = (torch.randn(n_pages, KV, page, D, generator=g) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(n_pages, KV, page, D, generator=g) * 0.5).to(torch.bfloat16)
+    width = max((c + page - 1) // page for c in ctx_lens)
+    bt = torch.zeros(len(ctx_lens), width, dtype=torch.int32)
+    perm = (torch.randperm(n_pages - 1, generator=g) + 1).tolist()
+    for i, c in enumerate(ctx_lens):
+        n = (c + page - 1) // page
+        bt[i, :n] = torch.tensor([perm.pop() for _ in range(n)], dtype=torch.int32)
+    return kc, vc, bt
+
+
+@pytest.mark.parametrize("D,H,KV", [(128, 32, 8), (64, 32, 4), (256, 16, 8), (128, 8, 8), (128, 14, 2)])
+@pytest.mark.parametrize("splits", [1, 4])
+@pytest.mark.parametrize("softcap,window", [(0.0, 0), (50.0, 0), (0.0, 48)])
+def test_decode_attention(D, H, KV, splits, softcap, window):
+    ctx = [1, 31, 32, 33, 100, 257]
+    kc, vc, bt = _paged_setup(ctx, KV, D)
+    B = len(ctx)
+    q = (torch.randn(B, H * D) * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    cl = torch.tensor(ctx, dtype=torch.int32)
+    o_ref = ref.paged_attention(q.float().reshape(B, H, D), kc.float(), vc.float(), bt, torch.arange(B), torch.ones(B, dtype=torch.long),
+                                cl, scale, softcap, window, True).reshape(B, H * D)
+    o = ops.decode_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cl.to(DEV), H, scale, softcap, window, splits)
+    assert _rel(o.cpu(), o_ref) < 1e-2
+
+
+@pytest.mark.parametrize("D,H,KV", [(128, 8, 2), (64, 8, 4), (256, 4, 2)])
+@pytest.mark.parametrize("softcap,window", [(0.0, 0), (50.0, 0), (0.0, 40)])
+def test_prefill_attention(D, H, KV, softcap, window):
+    # (q_len, ctx_len): fresh prompts, a chunk continuing a cached prefix, a single-row sequence
+    seqs = [(70, 70), (64, 64), (5, 133), (130, 200), (1, 40)]
+    ctx = [c for _, c in seqs]
+    kc, vc, bt = _paged_setup(ctx, KV, D, seed=3)
+    ql = [q for q, _ in seqs]
+    T = sum(ql)
+    qs = [sum(ql[:i]) for i in range(len(ql))]
+    q = (torch.randn(T, H * D) * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    ti = lambda v: torch.tensor(v, dtype=torch.int32)  # noqa: E731
+    o_ref = ref.paged_attention(q.float().reshape(T, H, D), kc.float(), vc.float(), bt, ti(qs), ti(ql), ti(ctx), scale, softcap, window,
+                                True).reshape(T, H * D)
+    o = ops.prefill_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), ti(qs).to(DEV), ti(ql).to(DEV), ti(ctx).to(DEV), H, scale,
+                              softcap, window, True)
+    assert _rel(o.cpu(), o_ref) < 1e-2
+
+
+def test_argmax_and_logits_post():
+    B, V = 5, 151936
+    logits = torch.randn(B, V, device=DEV)
+    logits[0, 77] = logits[0, 99999] = 50.0  # tie: the first maximum wins
+    idx, val = ops.argmax(logits)
+    assert idx.tolist() == torch.argmax(logits, dim=-1).tolist() and idx[0].item() == 77
+    mask = torch.zeros(B, (V + 31) // 32, dtype=torch.int32, device=DEV)
+    allowed = [5, 64, 31, 150000, 1]
+    for b, t in enumerate(allowed):
+        mask[b, t // 32] = 1 << (t % 32) if t % 32 != 31 else -(1 << 31)
+    idx2, _ = ops.argmax(logits, mask)
+    assert idx2.tolist() == allowed
+    l2 = logits.clone()
+    ops.logits_post(l2, mask, 30.0, 0.5)
+    exp = torch.tanh(logits * 0.5 / 30.0) * 30.0
+    for b, t in enumerate(allowed):
+        assert abs(l2[b, t].item() - exp[b, t].item()) < 1e-4
+        assert torch.isinf(l2[b]).sum().item() == V - 1
+
+
+def test_q4_quantize_bit_exact():
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(64, 256, generator=g) * 0.1
+    w[3, 32:64] = 0.0
+    w[5, 0] = -7.0
+    p_ref, s_ref = q4_quantize(w)
+    p, s = ops.q4_quantize(w.to(DEV))
+    assert torch.equal(p.cpu(), p_ref)
+    assert torch.equal(s.cpu().view(torch.int32), s_ref.view(torch.int32))
+    wb = w.to(torch.bfloat16)
+    p_ref, s_ref = q4_quantize(wb)
+    p, s = ops.q4_quantize(wb.to(DEV))
+    assert torch.equal(p.cpu(), p_ref) and torch.equal(s.cpu().view(torch.int32), s_ref.view(torch.int32))
+    d = ops.require_ext().q4_dequantize(p, s, False)
+    assert torch.equal(d.cpu(), q4_dequantize(p_ref, s_ref))
