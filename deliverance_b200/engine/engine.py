@@ -136,9 +136,8 @@ class Engine:
             raise ValueError("empty prompt")
         if len(prompt) >= limit:
             raise ValueError(f"prompt has {len(prompt)} tokens, which does not fit ntokens={limit}")
-        for t in prompt:
-            if not 0 <= int(t) < self.cfg.vocab_size:
-                raise ValueError(f"token id {t} outside the vocabulary")
+        if min(prompt) < 0 or max(prompt) >= self.cfg.vocab_size:
+            raise ValueError(f"token ids must lie in [0, {self.cfg.vocab_size})")
         r = Request(self._next_id, [int(t) for t in prompt], params, on_token)
         self._next_id += 1
         r.sampling = SamplingState.create(params, self.special_ids)
@@ -284,34 +283,44 @@ class Engine:
         g = self._graphs.get(bucket)
         if g is None:
             g = self._capture(bucket)
-        # stage inputs on the host, one H2D copy per tensor
+        # stage inputs in pinned host buffers, one H2D copy per tensor
         ps = self.page_size
-        tok = torch.zeros(bucket, dtype=torch.int32)
-        pos = torch.zeros(bucket, dtype=torch.int32)
-        slots = torch.zeros(bucket, dtype=torch.int64)
-        ctx = torch.ones(bucket, dtype=torch.int32)
-        bt = torch.zeros(bucket, self.max_pages_per_seq, dtype=torch.int32)
-        st = torch.zeros(bucket, dtype=torch.int64)
+        h = g["host"]
+        n = len(seqs)
+        starts = [s["start"] for s in seqs]
+        h["tok"][:n] = torch.tensor([s["tokens"][0] for s in seqs], dtype=torch.int32)
+        h["pos"][:n] = torch.tensor(starts, dtype=torch.int32)
+        h["slots"][:n] = torch.tensor([s["pages"][p // ps] * ps + p % ps for s, p in zip(seqs, starts)], dtype=torch.int64)
+        h["ctx"][:n] = torch.tensor([p + 1 for p in starts], dtype=torch.int32)
+        width = max(len(s["pages"]) for s in seqs)
+        bt = h["bt"]
         for i, s in enumerate(seqs):
-            p = s["start"]
-            tok[i] = s["tokens"][0]
-            pos[i] = p
-            slots[i] = s["pages"][p // ps] * ps + p % ps
-            ctx[i] = p + 1
-            bt[i, : len(s["pages"])] = torch.tensor(s["pages"], dtype=torch.int32)
-            st[i] = s["state_slot"]
-        for i in range(B, bucket):
-            slots[i] = i % ps  # padded rows write into the scratch page
+            pg = s["pages"]
+            row = s.get("bt_row")
+            if row is not None:
+                bt[i, : len(pg)] = row[: len(pg)]
+            else:
+                bt[i, : len(pg)] = torch.tensor(pg, dtype=torch.int32)
+        if self.hybrid:
+            h["st"][:n] = torch.tensor([s["state_slot"] for s in seqs], dtype=torch.int64)
+        if n < bucket:
+            h["tok"][n:] = 0
+            h["pos"][n:] = 0
+            h["ctx"][n:] = 1
+            h["slots"][n:] = torch.arange(n, bucket, dtype=torch.int64) % ps  # padded rows write into the scratch page
+            bt[n:, :1] = 0
         b: ForwardBatch = g["batch"]
-        b.token_ids.copy_(tok, non_blocking=True)
-        b.positions.copy_(pos, non_blocking=True)
-        b.slots.copy_(slots, non_blocking=True)
-        b.ctx_len.copy_(ctx, non_blocking=True)
-        b.block_tables.copy_(bt, non_blocking=True)
+        b.token_ids.copy_(h["tok"], non_blocking=True)
+        b.positions.copy_(h["pos"], non_blocking=True)
+        b.slots.copy_(h["slots"], non_blocking=True)
+        b.ctx_len.copy_(h["ctx"], non_blocking=True)
+        b.block_tables[:, :width].copy_(bt[:, :width], non_blocking=True)
         if b.state_slots is not None:
-            b.state_slots.copy_(st, non_blocking=True)
+            b.state_slots.copy_(h["st"], non_blocking=True)
+        self.metrics["h2d_bytes"] = self.metrics.get("h2d_bytes", 0) + bucket * (4 + 4 + 8 + 4 + 4 * width)
         g["graph"].replay()
         self.metrics["graph_replays"] += 1
+        self.metrics["kernel_launches"] += g["launches"]
         return g["logits"]
 
     def _capture(self, bucket: int) -> dict:
@@ -338,9 +347,20 @@ class Engine:
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         graph = torch.cuda.CUDAGraph()
+        n0 = ops.LAUNCHES[0]
         with torch.cuda.graph(graph):
             logits = self.model.forward(batch, self.kv)
-        g = {"graph": graph, "batch": batch, "logits": logits}
+        launches = ops.LAUNCHES[0] - n0
+        pin = dev.type == "cuda"
+        host = {
+            "tok": torch.zeros(bucket, dtype=torch.int32, pin_memory=pin),
+            "pos": torch.zeros(bucket, dtype=torch.int32, pin_memory=pin),
+            "slots": torch.zeros(bucket, dtype=torch.int64, pin_memory=pin),
+            "ctx": torch.ones(bucket, dtype=torch.int32, pin_memory=pin),
+            "bt": torch.zeros(bucket, self.max_pages_per_seq, dtype=torch.int32, pin_memory=pin),
+            "st": torch.zeros(bucket, dtype=torch.int64, pin_memory=pin),
+        }
+        g = {"graph": graph, "batch": batch, "logits": logits, "host": host, "launches": launches}
         self._graphs[bucket] = g
         return g
 

@@ -20,6 +20,12 @@ from ..ckpt.safetensors_io import Q4Tensor
 
 _ext = None
 _ext_checked = False
+# number of kernels of this extension launched so far (each op adds what it launches; benchmarks read the difference)
+LAUNCHES = [0]
+
+
+def _count(n: int = 1) -> None:
+    LAUNCHES[0] += n
 
 
 def ext():
@@ -125,6 +131,7 @@ def linear(x: torch.Tensor, w: LinearWeight, out_f32: bool = False, impl: int = 
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x [T, K] @ W[N, K]^T (+ bias)``."""
     if _cuda(x):
+        _count()
         return w.handle().run(x, out, w.bias, out_f32, impl, force_splits)
     if w.q4:
         y = ref.linear_q4(x, w.packed, w.scales[:, : w.K // 32], w.bias)
@@ -136,6 +143,7 @@ def linear(x: torch.Tensor, w: LinearWeight, out_f32: bool = False, impl: int = 
 # ---------------------------------------------------------------------------------------------------------- norms etc.
 def rmsnorm(x, w, eps, offset=0.0):
     if _cuda(x):
+        _count()
         return require_ext().rmsnorm(x, w, eps, offset)
     return ref.rmsnorm(x, w, eps, offset)
 
@@ -143,30 +151,35 @@ def rmsnorm(x, w, eps, offset=0.0):
 def add_rmsnorm(x, residual, w, eps, offset=0.0, res_mult=1.0):
     """``residual += x * res_mult`` in place; returns ``rmsnorm(residual)``."""
     if _cuda(x):
+        _count()
         return require_ext().add_rmsnorm(x, residual, w, eps, offset, res_mult)
     return ref.add_rmsnorm(x, residual, w, eps, offset, res_mult)
 
 
 def layernorm(x, w, b, eps):
     if _cuda(x):
+        _count()
         return require_ext().layernorm(x, w, b, eps)
     return ref.layernorm(x, w, b, eps)
 
 
 def act_mul(gate_up, act):
     if _cuda(gate_up):
+        _count()
         return require_ext().act_mul(gate_up, act)
     return ref.act_mul(gate_up, act)
 
 
 def activation(x, act):
     if _cuda(x):
+        _count()
         return require_ext().activation(x.contiguous(), act)
     return ref.act_fn(act)(x.float()).to(x.dtype)
 
 
 def embedding(table, ids, scale=1.0, pos_table=None, pos=None, type_table=None, types=None, dtype=None):
     if _cuda(table):
+        _count()
         return require_ext().embedding(table, ids.to(torch.int32), scale, pos_table, None if pos is None else pos.to(torch.int32),
                                        type_table, None if types is None else types.to(torch.int32))
     out = ref.embedding(table, ids, scale, torch.float32)
@@ -180,6 +193,7 @@ def embedding(table, ids, scale=1.0, pos_table=None, pos=None, type_table=None, 
 def rope_kv(qkv, positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset=0.0):
     """Per-head q/k RMSNorm (optional) + RoPE (optional) + paged cache write. Returns q ``[T, H*D]`` (a view on CUDA)."""
     if _cuda(qkv):
+        _count()
         require_ext().rope_kv(qkv, positions.to(torch.int32), slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps,
                               norm_offset)
         return qkv[:, : H * D]
@@ -199,6 +213,7 @@ def decode_splits(num_seqs: int, kv_heads: int, max_ctx: int, sms: int = 148) ->
 def decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, H, scale, softcap=0.0, window=0, splits=1):
     """One query row per sequence against the paged cache. q ``[B, H*D]`` -> ``[B, H*D]``."""
     if _cuda(q):
+        _count(2 if splits > 1 else 1)
         return require_ext().decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, H, scale, softcap, window, splits)
     B = q.shape[0]
     D = k_cache.shape[-1]
@@ -225,6 +240,7 @@ def prefill_attention(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_len
             ts, t0 = prefill_tiles([int(v) for v in q_len.tolist()])
             tile_seq = torch.tensor(ts, dtype=torch.int32, device=q.device)
             tile_q0 = torch.tensor(t0, dtype=torch.int32, device=q.device)
+        _count()
         return require_ext().prefill_attention(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens, tile_seq, tile_q0, H, scale,
                                                softcap, window, causal)
     T = q.shape[0]
@@ -236,6 +252,7 @@ def prefill_attention(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_len
 def argmax(logits, mask=None, softcap=0.0, inv_scale=1.0):
     """First-maximum argmax over allowed tokens; returns (index int64 [B], post-processed value [B])."""
     if _cuda(logits):
+        _count()
         idx, val = require_ext().argmax(logits, mask, softcap, inv_scale)
         return idx, val
     lf = logits_post(logits.clone().float(), mask, softcap, inv_scale)
@@ -246,6 +263,7 @@ def argmax(logits, mask=None, softcap=0.0, inv_scale=1.0):
 def logits_post(logits, mask=None, softcap=0.0, inv_scale=1.0):
     """In place: ``softcap(logits * inv_scale)``, disallowed tokens -> -inf. ``mask`` is an int32 allow-bitmask."""
     if _cuda(logits):
+        _count()
         require_ext().logits_post(logits, mask, softcap, inv_scale)
         return logits
     if inv_scale != 1.0:
@@ -269,6 +287,7 @@ def unpack_mask(mask: torch.Tensor, V: int) -> torch.Tensor:
 
 def q4_quantize(w: torch.Tensor):
     if _cuda(w):
+        _count()
         p, s = require_ext().q4_quantize(w.contiguous())
         return p, s
     from ..ckpt.jq4 import q4_quantize as host
