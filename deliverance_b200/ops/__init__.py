@@ -63,12 +63,56 @@ def check_status(device: Optional[int] = None) -> None:
 
 
 # ---------------------------------------------------------------------------------------------------------- linear
+Q4_STAGE_BYTES = 10240
+
+
+def _q4_swizzle_index(device) -> torch.Tensor:
+    r = torch.arange(128, device=device)
+    c = torch.arange(4, device=device)
+    return c.unsqueeze(0) ^ ((r >> 1) & 3).unsqueeze(1)  # [row, chunk position] -> logical 32-element block
+
+
+def prepack_q4(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """Tile-pack a JQ4 weight for the tensor-core GEMM: ``[N, K/2]`` nibbles + ``[N, K/32]`` scales ->
+    ``[ceil(N/128), ceil(K/128), 10240]`` bytes. One 10240-byte stage is a 128-row x 128-k tile: 8192 bytes of packed
+    nibbles (row ``r`` at ``r*64``; its four 16-byte blocks stored at chunk ``block ^ ((r >> 1) & 3)``, which makes the
+    shared-memory reads of the dequantising warps conflict-free) followed by 2048 bytes of fp32 scales ``[row][4]``.
+    Padding rows / k carry zero scales. A stage is one contiguous DRAM burst and one bulk copy in the kernel."""
+    N, half = packed.shape
+    K = half * 2
+    NT, KB = (N + 127) // 128, (K + 127) // 128
+    dev = packed.device
+    pk = torch.zeros(NT * 128, KB * 64, dtype=torch.uint8, device=dev)
+    pk[:N, :half] = packed
+    sc = torch.zeros(NT * 128, KB * 4, dtype=torch.float32, device=dev)
+    sc[:N, : K // 32] = scales[:, : K // 32]
+    raw = pk.view(NT, 128, KB, 4, 16).permute(0, 2, 1, 3, 4)  # nt, kb, row, block, 16 B
+    idx = _q4_swizzle_index(dev).view(1, 1, 128, 4, 1).expand(NT, KB, 128, 4, 16)
+    raw = torch.gather(raw, 3, idx).reshape(NT, KB, 8192)
+    scb = sc.view(NT, 128, KB, 4).permute(0, 2, 1, 3).contiguous().view(torch.uint8).reshape(NT, KB, 2048)
+    return torch.cat([raw, scb], dim=2).contiguous()
+
+
+def unpack_q4(tiles: torch.Tensor, N: int, K: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Inverse of :func:`prepack_q4`: returns (packed ``[N, K/2]``, scales ``[N, K/32]``)."""
+    NT, KB, _ = tiles.shape
+    dev = tiles.device
+    raw = tiles[:, :, :8192].reshape(NT, KB, 128, 4, 16)
+    idx = _q4_swizzle_index(dev).view(1, 1, 128, 4, 1).expand(NT, KB, 128, 4, 16)
+    raw = torch.gather(raw, 3, idx)  # the xor swizzle is its own inverse
+    packed = raw.permute(0, 2, 1, 3, 4).reshape(NT * 128, KB * 64)[:N, : K // 2].contiguous()
+    sc = tiles[:, :, 8192:].contiguous().view(torch.float32).reshape(NT, KB, 128, 4).permute(0, 2, 1, 3).reshape(NT * 128, KB * 4)
+    return packed, sc[:N, : K // 32].contiguous()
+
+
 class LinearWeight:
-    """A ``[N, K]`` projection weight, dense (bf16 on CUDA, fp32 on CPU) or JQ4 (packed + scales)."""
+    """A ``[N, K]`` projection weight, dense (bf16 on CUDA, fp32 on CPU) or JQ4. JQ4 weights keep the checkpoint layout
+    (packed + scales) on the CPU and the tile-packed layout of :func:`prepack_q4` on CUDA devices."""
 
     def __init__(self, w: "torch.Tensor | Q4Tensor", bias: Optional[torch.Tensor] = None):
         self.bias = bias
         self._handle = None
+        self.tiles = None
         if isinstance(w, Q4Tensor):
             self.q4 = True
             self.packed = w.packed.reshape(-1, w.packed.shape[-1]).contiguous()
@@ -83,47 +127,58 @@ class LinearWeight:
 
     @property
     def device(self) -> torch.device:
-        return (self.packed if self.q4 else self.w).device
+        if self.q4:
+            return (self.tiles if self.tiles is not None else self.packed).device
+        return self.w.device
 
     def to(self, device, dtype: Optional[torch.dtype] = None) -> "LinearWeight":
+        device = torch.device(device)
         bias = None if self.bias is None else self.bias.to(device=device, dtype=torch.float32)
         if self.q4:
             out = LinearWeight.__new__(LinearWeight)
-            out.q4, out.N, out.K, out.w, out._handle = True, self.N, self.K, None, None
-            out.packed = self.packed.to(device)
-            sc = self.scales
-            if torch.device(device).type == "cuda" and sc.shape[1] % 4:
-                # TMA needs a 16-byte row pitch for the scale sidecar: pad K/32 to a multiple of 4 columns
-                pad = 4 - sc.shape[1] % 4
-                sc = torch.nn.functional.pad(sc, (0, pad))
-            out.scales = sc.to(device).contiguous()
-            out.bias = bias
+            out.q4, out.N, out.K, out.w, out._handle, out.bias = True, self.N, self.K, None, None, bias
+            packed, scales = self.checkpoint_layout()
+            if device.type == "cuda":
+                out.tiles = prepack_q4(packed.to(device), scales.to(device))
+                out.packed = out.scales = None
+            else:
+                out.tiles = None
+                out.packed, out.scales = packed.to(device), scales.to(device)
             return out
         return LinearWeight(self.w.to(device=device, dtype=dtype or self.w.dtype), bias)
+
+    def checkpoint_layout(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """(packed ``[N, K/2]``, scales ``[N, K/32]``) whatever the resident layout is."""
+        if self.tiles is not None:
+            return unpack_q4(self.tiles, self.N, self.K)
+        return self.packed, self.scales
 
     def dense(self, dtype=torch.float32) -> torch.Tensor:
         if self.q4:
             from ..ckpt.jq4 import q4_dequantize
 
-            return q4_dequantize(self.packed, self.scales[:, : self.K // 32], dtype)
+            p, s = self.checkpoint_layout()
+            return q4_dequantize(p, s, dtype)
         return self.w.to(dtype)
 
     def handle(self):
         if self._handle is None:
             e = require_ext()
             if self.q4:
-                self._handle = e.GemmWeight(self.packed, self.scales, self.K)
+                if self.tiles is None:
+                    raise RuntimeError("JQ4 weight is not on a CUDA device")
+                self._handle = e.GemmWeight(self.tiles, True, self.N, self.K)
             else:
                 if self.w.dtype != torch.bfloat16:
                     self.w = self.w.to(torch.bfloat16)
-                self._handle = e.GemmWeight(self.w, None, self.K)
+                self._handle = e.GemmWeight(self.w, False, self.N, self.K)
             if self.bias is not None and self.bias.dtype != torch.float32:
                 self.bias = self.bias.float()
         return self._handle
 
     def nbytes(self) -> int:
         if self.q4:
-            return self.packed.numel() + self.scales.numel() * 4
+            return self.tiles.numel() if self.tiles is not None else self.packed.numel() + self.scales.numel() * 4
         return self.w.numel() * self.w.element_size()
 
 
@@ -134,7 +189,7 @@ def linear(x: torch.Tensor, w: LinearWeight, out_f32: bool = False, impl: int = 
         _count()
         return w.handle().run(x, out, w.bias, out_f32, impl, force_splits)
     if w.q4:
-        y = ref.linear_q4(x, w.packed, w.scales[:, : w.K // 32], w.bias)
+        y = ref.linear_q4(x, w.packed, w.scales, w.bias)
     else:
         y = ref.linear_dense(x, w.w, w.bias)
     return y.float() if out_f32 else y

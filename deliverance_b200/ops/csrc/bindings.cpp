@@ -60,24 +60,18 @@ DeviceScratch& scratch_for(int device) {
 // ---- GEMM weight handle -------------------------------------------------------------------------------------------
 class GemmWeight {
  public:
-  // dense: w bf16 [N, K]; JQ4: packed uint8 [N, K/2] + scales fp32 [N, pitch] (pitch % 4 == 0, pitch >= K/32)
-  GemmWeight(Tensor w, c10::optional<Tensor> scales, int64_t K) {
+  // dense: w bf16 [N, K]; JQ4: tile-packed uint8 [ceil(N/128), ceil(K/128), 10240] (ops.prepack_q4) with logical N, K
+  GemmWeight(Tensor w, bool is_q4, int64_t N, int64_t K) {
     check_cuda(w, "weight");
-    desc_.is_q4 = scales.has_value();
-    if (desc_.is_q4) {
-      TORCH_CHECK(w.scalar_type() == at::kByte && w.dim() == 2, "JQ4 packed weight must be uint8 [N, K/2]");
-      TORCH_CHECK(w.size(1) * 2 == K, "packed width does not match K");
-      scales_ = scales.value();
-      check_cuda(scales_, "scales");
-      TORCH_CHECK(scales_.scalar_type() == at::kFloat && scales_.dim() == 2 && scales_.size(0) == w.size(0), "scales must be fp32 [N, pitch]");
-      TORCH_CHECK(scales_.size(1) % 4 == 0 && scales_.size(1) * 32 >= K, "scale pitch must be a multiple of 4 and cover K/32");
-      desc_.scales = scales_.data_ptr<float>();
-      desc_.scale_pitch = static_cast<int>(scales_.size(1));
+    desc_.is_q4 = is_q4;
+    if (is_q4) {
+      TORCH_CHECK(w.scalar_type() == at::kByte && w.dim() == 3 && w.size(2) == dlv::kQ4StageBytes, "JQ4 weight must be tile-packed uint8 [nt, kb, 10240]");
+      TORCH_CHECK(w.size(0) == (N + 127) / 128 && w.size(1) == (K + 127) / 128, "tile-packed shape does not match N, K");
     } else {
-      TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.size(1) == K, "dense weight must be bf16 [N, K]");
+      TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.size(0) == N && w.size(1) == K, "dense weight must be bf16 [N, K]");
     }
     w_ = w;
-    desc_.N = static_cast<int>(w.size(0));
+    desc_.N = static_cast<int>(N);
     desc_.K = static_cast<int>(K);
     desc_.data = w.data_ptr();
     c10::cuda::CUDAGuard guard(w.device());
@@ -108,7 +102,7 @@ class GemmWeight {
       bptr = b.data_ptr<float>();
     }
     if (M == 0) return out;
-    const bool simt = impl == 2 || (impl == 0 && M <= 1);
+    const bool simt = impl == 2 || (impl == 0 && M <= 1 && !desc_.is_q4);
     if (simt) {
       dlv::gemv_simt_run(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), out.data_ptr(), static_cast<int>(out.stride(0)), out_f32,
                          bptr, cur_stream());
@@ -127,7 +121,7 @@ class GemmWeight {
 
  private:
   dlv::GemmWeightDesc desc_;
-  Tensor w_, scales_;
+  Tensor w_;
 };
 
 // Reads and clears the kernel status word of a device (0 = ok, 1 = barrier wait ran out, 2 = flag wait ran out).
@@ -138,6 +132,15 @@ int64_t take_status(int64_t device) {
   return v;
 }
 void init_scratch(int64_t device) { scratch_for(static_cast<int>(device)); }
+// Debug: CTA (0,0,0) of every later GEMM launch stamps phase times (ns) into `buf` (int64 [16] on the device); None stops it.
+void gemm_trace(c10::optional<Tensor> buf) {
+  if (!buf.has_value()) {
+    dlv::gemm_set_trace(nullptr);
+    return;
+  }
+  TORCH_CHECK(buf.value().is_cuda() && buf.value().scalar_type() == at::kLong && buf.value().numel() >= 16, "trace buffer must be int64 [16] on CUDA");
+  dlv::gemm_set_trace(reinterpret_cast<unsigned long long*>(buf.value().data_ptr<int64_t>()));
+}
 
 // ---- elementwise ----------------------------------------------------------------------------------------------------
 Tensor rmsnorm(const Tensor& x, const Tensor& w, double eps, double offset) {
@@ -424,7 +427,7 @@ Tensor q4_dequantize(const Tensor& packed, const Tensor& scales, bool to_bf16) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<GemmWeight, std::shared_ptr<GemmWeight>>(m, "GemmWeight")
-      .def(py::init<Tensor, c10::optional<Tensor>, int64_t>(), py::arg("w"), py::arg("scales"), py::arg("K"))
+      .def(py::init<Tensor, bool, int64_t, int64_t>(), py::arg("w"), py::arg("is_q4"), py::arg("N"), py::arg("K"))
       .def("run", &GemmWeight::run, py::arg("x"), py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("out_f32") = false,
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def_property_readonly("N", &GemmWeight::n)
@@ -432,6 +435,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("is_q4", &GemmWeight::is_q4);
   m.def("take_status", &take_status);
   m.def("init_scratch", &init_scratch);
+  m.def("gemm_trace", &gemm_trace);
   m.def("num_sms", &dlv::gemm_num_sms);
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);

@@ -1,5 +1,7 @@
 // Host side of the tcgen05 GEMM (tensor-map encoding, tile / split-K selection, launch) plus a CUDA-core GEMV used for
 // one to four tokens and as an independent implementation in the numerics tests.
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -52,14 +54,16 @@ void encode_map_2d(CUtensorMap* map, int dtype_code, const void* base, uint64_t 
 void gemm_weight_init(GemmWeightDesc* w) {
   if (w->is_q4) {
     if (w->K % 32 != 0) throw std::runtime_error("JQ4 weight needs K % 32 == 0");
-    encode_map_2d(&w->map_w, 1, w->data, w->N, w->K / 2, static_cast<uint64_t>(w->K / 2), kGemmBM, 64, 64);
-    encode_map_2d(&w->map_s, 2, w->scales, w->N, w->K / 32, static_cast<uint64_t>(w->scale_pitch) * 4, kGemmBM, 4, 0);
+    if ((reinterpret_cast<uintptr_t>(w->data) & 15) != 0) throw std::runtime_error("tile-packed JQ4 weights must be 16-byte aligned");
+    std::memset(&w->map_w, 0, sizeof(w->map_w));
   } else {
     if (w->K % 8 != 0) throw std::runtime_error("dense weight needs K % 8 == 0");
     encode_map_2d(&w->map_w, 0, w->data, w->N, w->K, static_cast<uint64_t>(w->K) * 2, kGemmBM, 64, 128);
-    w->map_s = w->map_w;
   }
 }
+
+unsigned long long* g_gemm_trace = nullptr;
+void gemm_set_trace(unsigned long long* p) { g_gemm_trace = p; }
 
 int gemm_num_sms() {
   static int sms = 0;
@@ -72,24 +76,107 @@ int gemm_num_sms() {
   return sms;
 }
 
+// Number of clusters of `size` CTAs of this kernel that can be resident at once (0 when such a cluster cannot be scheduled).
 template <bool Q4, int BN>
-static void launch_tc(const GemmWeightDesc* w, const CUtensorMap& map_x, GemmParams p, cudaStream_t st) {
+static int cluster_capacity(int size) {
   using L = GemmSmem<Q4, BN>;
+  static int cap[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<Q4, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     attr_done = true;
   }
-  dim3 grid(p.n_tiles, p.m_tiles, p.splits);
-  gemm_tc_kernel<Q4, BN><<<grid, kGemmThreads, L::kBytes, st>>>(w->map_w, w->map_s, map_x, p);
+  if (size < 1 || size > 8) return 0;
+  if (cap[size] < 0) {
+    if (size == 1) {
+      cap[size] = gemm_num_sms();
+    } else {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(1, 1, size);
+      cfg.blockDim = dim3(kGemmThreads);
+      cfg.dynamicSmemBytes = L::kBytes;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = size;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<Q4, BN>, &cfg);
+      (void)cudaGetLastError();
+      cap[size] = (e == cudaSuccess && n > 0) ? n : 0;
+    }
+  }
+  return cap[size];
 }
 
-size_t gemm_workspace_floats(int M, int N) {
-  // upper bound used by callers that size the split-K workspace once
-  (void)M;
-  (void)N;
-  return static_cast<size_t>(4) * 148 * 128 * 128;
+template <bool Q4, int BN>
+static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmParams p, float* ws, size_t ws_floats, int* counters,
+                   int n_counters, int force_splits, cudaStream_t st) {
+  using L = GemmSmem<Q4, BN>;
+  p.n_tiles = (w->N + kGemmBM - 1) / kGemmBM;
+  p.m_tiles = (M + BN - 1) / BN;
+  const int tiles = p.n_tiles * p.m_tiles;
+  // Split-K plan. The CTAs of one output tile form a cluster; cost model (microseconds): every wave of resident clusters
+  // pays a fixed prologue/epilogue and its share of the k-blocks, split tiles also pay the cluster reduction.
+  const bool no_cluster = force_splits < 0;  // negative: that many splits, reduced through the global workspace
+  int splits = 1;
+  if (force_splits != 0) {
+    splits = force_splits < 0 ? -force_splits : force_splits;
+  } else {
+    double best = 1e30;
+    for (int s = 1; s <= 8; ++s) {
+      if (s > 1 && p.kb_total / s < 2) break;
+      const int cap = cluster_capacity<Q4, BN>(s);
+      if (cap <= 0) continue;
+      const int waves = (tiles + cap - 1) / cap;
+      const int kb = (p.kb_total + s - 1) / s;
+      const double per_kb = 0.22 * (BN > 64 ? BN / 64.0 : 1.0);
+      const double cost = waves * (3.0 + kb * per_kb + (s > 1 ? 1.0 : 0.0));
+      if (cost < best - 1e-9) {
+        best = cost;
+        splits = s;
+      }
+    }
+  }
+  if (splits > p.kb_total) splits = p.kb_total;
+  if (splits < 1) splits = 1;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  bool cluster = splits > 1 && !no_cluster && splits <= 8 && cluster_capacity<Q4, BN>(splits) > 0;
+  if (splits > 1 && !cluster) {
+    const size_t need = static_cast<size_t>(tiles) * splits * BN * kGemmBM;
+    if (ws == nullptr || counters == nullptr || need > ws_floats || tiles > n_counters) {
+      splits = 1;
+      p.kb_per_split = p.kb_total;
+    }
+  }
+  (void)cluster_capacity<Q4, BN>(1);  // sets the shared-memory attribute
+  p.splits = splits;
+  p.cluster_reduce = cluster ? 1 : 0;
+  p.ws = ws;
+  p.counters = counters;
+  p.wq = w->is_q4 ? static_cast<const uint8_t*>(w->data) : nullptr;
+  CUtensorMap map_x;
+  encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.n_tiles, p.m_tiles, p.splits);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = L::kBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  if (cluster) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = p.splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<Q4, BN>, w->map_w, map_x, p);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("gemm launch: ") + cudaGetErrorString(e));
 }
 
 // Choose the token tile. Small batches take the smallest UMMA N that covers them.
@@ -106,47 +193,20 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
   if (M <= 0) return;
   if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
   const int BN = pick_bn(M);
-  GemmParams p;
+  GemmParams p = {};
   p.M = M;
   p.N = w->N;
   p.K = w->K;
   p.kb_total = (w->K + kGemmBK - 1) / kGemmBK;
-  p.n_tiles = (w->N + kGemmBM - 1) / kGemmBM;
-  p.m_tiles = (M + BN - 1) / BN;
-  const int tiles = p.n_tiles * p.m_tiles;
-  int splits = 1;
-  if (BN <= 128) {
-    const int sms = gemm_num_sms();
-    splits = sms / tiles;  // fill the machine once
-    if (splits < 1) splits = 1;
-    const int max_by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;  // keep >= 4 k-blocks per split
-    if (splits > max_by_k) splits = max_by_k;
-    if (splits > 16) splits = 16;
-  }
-  if (force_splits > 0) splits = force_splits;
-  if (splits > p.kb_total) splits = p.kb_total;
-  p.kb_per_split = (p.kb_total + splits - 1) / splits;
-  splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
-  if (splits > 1) {
-    const size_t need = static_cast<size_t>(tiles) * splits * BN * kGemmBM;
-    if (ws == nullptr || counters == nullptr || need > ws_floats || tiles > n_counters) {
-      splits = 1;
-      p.kb_per_split = p.kb_total;
-    }
-  }
-  p.splits = splits;
   p.out = out;
   p.ldo = ldo;
   p.out_f32 = out_f32 ? 1 : 0;
   p.bias = bias;
-  p.ws = ws;
-  p.counters = counters;
   p.status = status;
-  CUtensorMap map_x;
-  encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
-#define DLV_LAUNCH(BNV)                                        \
-  if (w->is_q4) launch_tc<true, BNV>(w, map_x, p, st);         \
-  else launch_tc<false, BNV>(w, map_x, p, st)
+  p.trace = g_gemm_trace;
+#define DLV_LAUNCH(BNV)                                                                              \
+  if (w->is_q4) run_tc<true, BNV>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, force_splits, st); \
+  else run_tc<false, BNV>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, force_splits, st)
   switch (BN) {
     case 16: DLV_LAUNCH(16); break;
     case 32: DLV_LAUNCH(32); break;
@@ -160,8 +220,7 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
 // ------------------------------------------------------------------------------------------------ CUDA-core GEMV
 // One warp per weight row, MT tokens. fp32 accumulation; JQ4 blocks are expanded in registers.
 template <int MT, bool Q4>
-__global__ void __launch_bounds__(128) gemv_simt_kernel(const void* __restrict__ wdata, const float* __restrict__ scales,
-                                                        int scale_pitch, const __nv_bfloat16* __restrict__ x, int ldx,
+__global__ void __launch_bounds__(128) gemv_simt_kernel(const void* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
                                                         void* __restrict__ out, int ldo, int out_f32, const float* __restrict__ bias,
                                                         int N, int K) {
   const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -171,11 +230,13 @@ __global__ void __launch_bounds__(128) gemv_simt_kernel(const void* __restrict__
 #pragma unroll
   for (int m = 0; m < MT; ++m) acc[m] = 0.f;
   if (Q4) {
-    const uint8_t* wrow = static_cast<const uint8_t*>(wdata) + static_cast<size_t>(n) * (K / 2);
-    const float* srow = scales + static_cast<size_t>(n) * scale_pitch;
+    const int kb_total = (K + 127) / 128;
+    const int r = n & 127;
+    const uint8_t* tile_row = static_cast<const uint8_t*>(wdata) + static_cast<size_t>(n >> 7) * kb_total * kQ4StageBytes;
     for (int blk = lane; blk < K / 32; blk += 32) {
-      const uint4 w = __ldg(reinterpret_cast<const uint4*>(wrow + blk * 16));
-      const float sc = __ldg(srow + blk);
+      const uint8_t* stage = tile_row + static_cast<size_t>(blk >> 2) * kQ4StageBytes;
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(stage + r * 64 + (((blk & 3) ^ ((r >> 1) & 3)) << 4)));
+      const float sc = __ldg(reinterpret_cast<const float*>(stage + 8192 + r * 16 + (blk & 3) * 4));
       const uint32_t words[4] = {w.x, w.y, w.z, w.w};
       float wf[32];
 #pragma unroll
@@ -247,8 +308,8 @@ void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void*
     void* op = out_f32 ? static_cast<void*>(static_cast<float*>(out) + static_cast<size_t>(m0) * ldo)
                        : static_cast<void*>(static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(m0) * ldo);
 #define DLV_GEMV(MT)                                                                                                          \
-  if (w->is_q4) gemv_simt_kernel<MT, true><<<grid, 128, 0, st>>>(w->data, w->scales, w->scale_pitch, xp, ldx, op, ldo, out_f32, bias, w->N, w->K); \
-  else gemv_simt_kernel<MT, false><<<grid, 128, 0, st>>>(w->data, nullptr, 0, xp, ldx, op, ldo, out_f32, bias, w->N, w->K)
+  if (w->is_q4) gemv_simt_kernel<MT, true><<<grid, 128, 0, st>>>(w->data, xp, ldx, op, ldo, out_f32, bias, w->N, w->K); \
+  else gemv_simt_kernel<MT, false><<<grid, 128, 0, st>>>(w->data, xp, ldx, op, ldo, out_f32, bias, w->N, w->K)
     switch (mt) {
       case 1: DLV_GEMV(1); break;
       case 2: DLV_GEMV(2); break;

@@ -7,18 +7,22 @@
 
 namespace dlv {
 
+// JQ4 weights are held tile-packed on the device: [ceil(N/128)][ceil(K/128)][10240] bytes. One 10240-byte stage holds a
+// 128-row x 128-k tile: 8192 bytes of packed nibbles, row r at r*64, its four 16-byte blocks (32 elements each, split-half
+// nibble order) stored at chunk position (block ^ ((r >> 1) & 3)), followed by 2048 bytes of fp32 scales [row][4].
+// Rows / k beyond N / K are zero (zero scale).
+constexpr int kQ4StageBytes = 10240;
+
 struct GemmWeightDesc {
   int N = 0, K = 0;
   bool is_q4 = false;
-  const void* data = nullptr;     // bf16 [N, K] or packed nibbles [N, K/2]
-  const float* scales = nullptr;  // JQ4: [N, scale_pitch] fp32, scale_pitch >= K/32 and scale_pitch % 4 == 0
-  int scale_pitch = 0;
-  CUtensorMap map_w;
-  CUtensorMap map_s;
+  const void* data = nullptr;  // bf16 [N, K] or the tile-packed JQ4 bytes
+  CUtensorMap map_w;           // dense only
 };
 
 void gemm_weight_init(GemmWeightDesc* w);
 int gemm_num_sms();
+void gemm_set_trace(unsigned long long* p);  // debug: device buffer of 16 u64 that CTA (0,0,0) stamps with globaltimer
 void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
                  float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st);
 void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,

@@ -2,13 +2,24 @@
 //
 // The weight matrix is the MMA "A" operand (128 weight rows per CTA = UMMA M), the activations are the "B" operand
 // (BN tokens = UMMA N, 16..256), so that decode batches of 1..64 tokens still fill a full-height tensor-core tile and
-// the kernel is weight-bandwidth bound. W is either dense bf16 (TMA straight into 128B-swizzled tiles) or JQ4:
-// packed nibbles + per-32 fp32 scales arrive by TMA in a staging buffer, eight warps expand them into the swizzled
-// bf16 tile in shared memory ((nibble - 8) * scale), and a single elected thread issues tcgen05.mma with the
-// accumulator in TMEM. Split-K partials are reduced by the last CTA to arrive at a tile (fixed order, deterministic).
+// the kernel is weight-bandwidth bound.
 //
-// Roles per CTA (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..9 = JQ4 dequant and
-// epilogue (tcgen05.ld -> convert -> global).
+// JQ4 weights: packed nibbles + per-32 fp32 scales are pre-arranged at load time as one contiguous 10 KB chunk per
+// 128x128 tile, so a pipeline stage is a single bulk copy of consecutive DRAM bytes into a deep staging ring (up to 16
+// stages per SM). Sixteen warps expand a stage to bf16 ((nibble - 8) * scale) in registers and write it with tcgen05.st
+// straight into TENSOR MEMORY, from where tcgen05.mma reads its A operand: the dequantised weights never touch shared
+// memory, whose bandwidth (128 B/clk) would otherwise cap the kernel at about half of the HBM rate (a bf16 tile in shared
+// memory costs a 32 KB write plus a 32 KB tensor-core read per 10 KB of HBM traffic). Activations stream through their
+// own TMA ring. Dense bf16 weights take the classic path (TMA into 128B-swizzled tiles, both operands from shared memory).
+//
+// Split-K: the CTAs that share an output tile form a thread-block cluster (<= 8). Each writes its fp32 partial tile to
+// its own shared memory, and after a cluster barrier every CTA reduces a slice of the tile's columns by reading all
+// peers' partials through distributed shared memory in a fixed order (deterministic), then writes the final output.
+// A global-memory workspace + last-arriver reduction remains as the fallback when clusters cannot be scheduled.
+//
+// Roles per CTA (608 threads): warp 0 = weight producer (bulk copy / TMA), warp 1 = TMEM owner + MMA issuer,
+// warp 2 = activation TMA producer, warps 3..18 = JQ4 dequant (one 32-element block per thread and stage) and epilogue
+// (tcgen05.ld -> fp32 tile in shared memory -> reduce over the cluster -> 8/16-byte global stores).
 //
 // This replaces the reference's CPU kernels gemm_q8_q4 / gemm_bf16_q4 / gemm_bf16
 // (native/src/main/c/simd/vector_simd.c:339-633,1186-1411,1414-1668) and the WGSL gemm_q4 / gemm_i8q4_v5 shaders.
@@ -18,9 +29,13 @@
 namespace dlv {
 
 constexpr int kGemmBM = 128;       // weight rows per CTA
-constexpr int kGemmBK = 128;       // reduction elements per pipeline stage (two 64-wide swizzle atoms)
-constexpr int kGemmThreads = 320;  // 10 warps
-constexpr int kGemmEpiThreads = 256;
+constexpr int kGemmBK = 128;       // reduction elements per pipeline stage
+constexpr int kGemmThreads = 608;  // 19 warps
+constexpr int kGemmEpiThreads = 512;
+constexpr int kGemmEpiWarp0 = 3;
+constexpr int kGemmTmemCols = 512;   // whole tensor memory of the SM (one CTA per SM)
+constexpr int kGemmTmemA = 256;      // first column of the JQ4 A-operand ring (accumulator uses columns [0, BN))
+constexpr int kGemmTmemAStage = 64;  // 128 k as bf16 pairs
 
 struct GemmParams {
   int M, N, K;
@@ -28,26 +43,41 @@ struct GemmParams {
   int splits;        // split-K factor (>= 1)
   int kb_per_split;  // k-blocks handled by one split
   int n_tiles, m_tiles;
-  void* out;         // [M, ldo] bf16 or fp32
+  int cluster_reduce;  // 1: the splits of a tile are one cluster and reduce through distributed shared memory
+  void* out;           // [M, ldo] bf16 or fp32
   int ldo;
   int out_f32;
   const float* bias;  // [N] fp32 or nullptr
-  float* ws;          // split-K partials: [tile][split][BN][128] fp32
-  int* counters;      // one per tile, zero between launches (the reducing CTA resets its counter)
+  const uint8_t* wq;  // JQ4: tile-packed weights [n_tiles][kb_total][10240 B] (see gemm_api.h), else nullptr
+  float* ws;          // fallback split-K partials: [tile][split][BN][128] fp32
+  int* counters;      // fallback: one per tile, zero between launches (the reducing CTA resets its counter)
   int* status;        // kernel status word (0 = ok)
+  unsigned long long* trace;  // optional: 16 globaltimer stamps of CTA (0,0,0) (nullptr in production)
 };
 
 template <bool Q4, int BN>
 struct GemmSmem {
-  static constexpr int kWTile = kGemmBM * 128;        // one 64-wide bf16 sub-tile of W: 16 KB
-  static constexpr int kXTile = BN * 128;             // one 64-wide bf16 sub-tile of X
-  static constexpr int kRaw = Q4 ? kGemmBM * 64 : 0;  // packed nibbles for 128 k
-  static constexpr int kScales = Q4 ? kGemmBM * 16 : 0;
-  static constexpr int kStage = 2 * kWTile + 2 * kXTile + kRaw + kScales;
-  static constexpr int kMaxSmem = 232448 - 2048;
-  static constexpr int kStages = (kMaxSmem / kStage) > 8 ? 8 : (kMaxSmem / kStage);
-  static constexpr int kBytes = kStages * kStage + 2048;  // + barriers and 1024 B alignment slack
-  static constexpr uint32_t kTxBytes = Q4 ? (kRaw + kScales + 2 * kXTile) : (2 * kWTile + 2 * kXTile);
+  static constexpr int kWTile = kGemmBM * 128;  // dense: one 64-wide bf16 sub-tile of W: 16 KB
+  static constexpr int kWStage = 2 * kWTile;    // dense: 32 KB
+  static constexpr int kXStage = BN * 256;      // two 64-wide bf16 sub-tiles of X
+  static constexpr int kRawStage = kGemmBM * 64 + kGemmBM * 16;  // packed nibbles (8 KB) + scales (2 KB)
+  static constexpr int kBudget = 232448 - 2048;                  // dynamic smem minus barriers / alignment slack
+  static constexpr int kStageOut = BN * kGemmBM * 4;             // fp32 output staging tile (aliases the rings)
+  // dense: W and X rings of equal depth. JQ4: A lives in tensor memory; X ring up to 8 stages, the rest is the packed ring.
+  static constexpr int kNW = Q4 ? 0 : ((kBudget / (kWStage + kXStage)) > 6 ? 6 : (kBudget / (kWStage + kXStage)));
+  static constexpr int kNA = 4;  // JQ4: A-operand stages in tensor memory
+  static constexpr int kNX = Q4 ? (BN <= 32 ? 8 : (BN <= 64 ? 6 : (BN <= 128 ? 3 : 2))) : kNW;
+  static constexpr int kRawRoom = Q4 ? (kBudget - kNX * kXStage) / kRawStage : 0;
+  static constexpr int kNR = Q4 ? (kRawRoom > 16 ? 16 : kRawRoom) : 0;
+  static constexpr int kOffX = kNW * kWStage;
+  static constexpr int kOffRaw = kOffX + kNX * kXStage;
+  static constexpr int kOffCtrl = kOffRaw + kNR * kRawStage;
+  static constexpr int kBytes = kOffCtrl + 2048;
+  static_assert(!Q4 || kNR >= 4, "packed-weight ring too small");
+  static_assert(kNX >= 2, "activation ring too small");
+  static_assert(kStageOut <= kOffCtrl, "the fp32 output staging tile must fit in the rings");
+  static_assert(kNA == 4, "the dequant warp groups map one-to-one onto the A-operand stages");
+  static_assert(kGemmTmemA + kNA * kGemmTmemAStage <= kGemmTmemCols && BN <= kGemmTmemA, "tensor memory plan");
 };
 
 __device__ __forceinline__ uint32_t q4_pair_to_bf162(uint32_t nib4, uint32_t sel, __nv_bfloat162 s2) {
@@ -59,237 +89,365 @@ __device__ __forceinline__ uint32_t q4_pair_to_bf162(uint32_t nib4, uint32_t sel
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
+
 template <bool Q4, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // Q4: packed bytes [N, K/2]; dense: bf16 [N, K]
-               const __grid_constant__ CUtensorMap map_s,   // Q4: scales f32 [N, K/32]; dense: unused
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K] (unused for JQ4, which streams p.wq)
                const __grid_constant__ CUtensorMap map_x,   // bf16 [M, K]
                const GemmParams p) {
   using L = GemmSmem<Q4, BN>;
-  constexpr int STAGES = L::kStages;
+  constexpr int NW = L::kNW > 0 ? L::kNW : 1, NX = L::kNX, NR = L::kNR > 0 ? L::kNR : 1, NA = L::kNA;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ctrl = smem + STAGES * L::kStage;
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);
-  uint64_t* bar_empty = bar_full + STAGES;
-  uint64_t* bar_deq = bar_empty + STAGES;
-  uint64_t* bar_acc = bar_deq + STAGES;
+  uint8_t* ctrl = smem + L::kOffCtrl;
+  // "a" barriers: the MMA A operand stage (dense: bf16 tile in shared memory, JQ4: bf16 columns in tensor memory)
+  uint64_t* bar_a_full = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* bar_a_empty = bar_a_full + 8;
+  uint64_t* bar_x_full = bar_a_empty + 8;
+  uint64_t* bar_x_empty = bar_x_full + NX;
+  uint64_t* bar_r_full = bar_x_empty + NX;
+  uint64_t* bar_r_empty = bar_r_full + NR;
+  uint64_t* bar_acc = bar_r_empty + NR;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_last = const_cast<int*>(abort_flag) + 1;
+  constexpr int NAS = Q4 ? NA : NW;  // depth of the A-operand ring
 
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#define DLV_STAMP(i) do { if (tracing) p.trace[i] = globaltimer_ns(); } while (0)
+  if (threadIdx.x == 0) DLV_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
   const int n0 = n_tile * kGemmBM, m0 = m_tile * BN;
   const int kb_begin = split * p.kb_per_split;
   const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);
   const int nkb = max(0, kb_end - kb_begin);
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t TMEM_COLS = Q4 ? kGemmTmemCols : (BN < 32 ? 32 : BN);
+  // Every CTA walks its k-blocks from a different starting point: CTAs that run at the same time would otherwise all ask
+  // the L2 for the same activation lines at the same moment (the activation tile of a k-block is shared by every weight
+  // tile), and requests to one line are served one after the other.
+  const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(n_tile) * 7u + static_cast<unsigned>(m_tile) * 3u) % static_cast<unsigned>(nkb)) : 0;
 
-  auto stage_w = [&](int s, int sub) { return smem + s * L::kStage + sub * L::kWTile; };
-  auto stage_x = [&](int s, int sub) { return smem + s * L::kStage + 2 * L::kWTile + sub * L::kXTile; };
-  auto stage_raw = [&](int s) { return smem + s * L::kStage + 2 * L::kWTile + 2 * L::kXTile; };
-  auto stage_sc = [&](int s) { return smem + s * L::kStage + 2 * L::kWTile + 2 * L::kXTile + L::kRaw; };
+  auto w_tile = [&](int s, int sub) { return smem + s * L::kWStage + sub * L::kWTile; };
+  auto x_tile = [&](int s, int sub) { return smem + L::kOffX + s * L::kXStage + sub * (BN * 128); };
+  auto raw_tile = [&](int s) { return smem + L::kOffRaw + s * L::kRawStage; };
+  auto sc_tile = [&](int s) { return smem + L::kOffRaw + s * L::kRawStage + kGemmBM * 64; };
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1);
-      mbar_init(smem_u32(&bar_empty[s]), 1);
-      mbar_init(smem_u32(&bar_deq[s]), kGemmEpiThreads);
+    for (int s = 0; s < NAS; ++s) {
+      mbar_init(smem_u32(&bar_a_full[s]), Q4 ? 4 : 1);  // JQ4: one arrival per warp of the group that owns the stage
+      mbar_init(smem_u32(&bar_a_empty[s]), 1);
+    }
+    for (int s = 0; s < NX; ++s) {
+      mbar_init(smem_u32(&bar_x_full[s]), 1);
+      mbar_init(smem_u32(&bar_x_empty[s]), 1);
+    }
+    for (int s = 0; s < NR; ++s) {
+      mbar_init(smem_u32(&bar_r_full[s]), 1);
+      mbar_init(smem_u32(&bar_r_empty[s]), 4);
     }
     mbar_init(smem_u32(bar_acc), 1);
     *abort_flag = 0;
     *s_last = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&map_w);
+    if (!Q4) tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
-    if (Q4) tma_prefetch_desc(&map_s);
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) DLV_STAMP(1);
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- weight producer: packed JQ4 stages (deep ring) or dense bf16 tiles ----------------
     if (lane == 0) {
       int issued = 0;
+      constexpr int RING = Q4 ? NR : NW;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abort_flag, p.status)) break;
-        const uint32_t full = smem_u32(&bar_full[s]);
-        mbar_expect_tx(full, L::kTxBytes);
-        const int kb = kb_begin + i;
+        const int s = i % RING;
+        const uint32_t ph = (i / RING) & 1;
+        uint64_t* empty = Q4 ? &bar_r_empty[s] : &bar_a_empty[s];
+        uint64_t* fullb = Q4 ? &bar_r_full[s] : &bar_a_full[s];
+        if (!mbar_wait(smem_u32(empty), ph ^ 1, abort_flag, p.status)) break;
+        const uint32_t full = smem_u32(fullb);
+        const int kb = kb_begin + (i + rot >= nkb ? i + rot - nkb : i + rot);
         if (Q4) {
-          tma_load_2d(smem_u32(stage_raw(s)), &map_w, full, kb * 64, n0);
-          tma_load_2d(smem_u32(stage_sc(s)), &map_s, full, kb * 4, n0);
+          // one contiguous 10 KB stage: 8 KB of packed nibbles (already in the swizzled shared-memory order) + 2 KB of scales
+          mbar_expect_tx(full, L::kRawStage);
+          bulk_load_1d(smem_u32(raw_tile(s)), p.wq + (static_cast<size_t>(n_tile) * p.kb_total + kb) * L::kRawStage, L::kRawStage, full);
         } else {
-          tma_load_2d(smem_u32(stage_w(s, 0)), &map_w, full, kb * kGemmBK, n0);
-          tma_load_2d(smem_u32(stage_w(s, 1)), &map_w, full, kb * kGemmBK + 64, n0);
+          mbar_expect_tx(full, L::kWStage);
+          tma_load_2d(smem_u32(w_tile(s, 0)), &map_w, full, kb * kGemmBK, n0);
+          tma_load_2d(smem_u32(w_tile(s, 1)), &map_w, full, kb * kGemmBK + 64, n0);
         }
-        tma_load_2d(smem_u32(stage_x(s, 0)), &map_x, full, kb * kGemmBK, m0);
-        tma_load_2d(smem_u32(stage_x(s, 1)), &map_x, full, kb * kGemmBK + 64, m0);
         ++issued;
       }
       if (*abort_flag) {
-        // let copies that are still in flight land before the CTA goes away (bounded: ~50 ms per stage)
-        const int first = issued > STAGES ? issued - STAGES : 0;
+        // let copies that are still in flight land before the CTA goes away (bounded: ~20 ms per stage)
+        const int first = issued > RING ? issued - RING : 0;
         for (int i = first; i < issued; ++i) {
-          const uint32_t bar = smem_u32(&bar_full[i % STAGES]);
-          const uint32_t ph = (i / STAGES) & 1;
+          const uint32_t bar = smem_u32(Q4 ? &bar_r_full[i % RING] : &bar_a_full[i % RING]);
+          const uint32_t ph = (i / RING) & 1;
           const unsigned long long t0 = globaltimer_ns();
-          while (!mbar_try_wait(bar, ph) && globaltimer_ns() - t0 < 50000000ull) {
+          while (!mbar_try_wait(bar, ph) && globaltimer_ns() - t0 < 20000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------- activation producer ----------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % NX;
+        const uint32_t ph = (i / NX) & 1;
+        if (!mbar_wait(smem_u32(&bar_x_empty[s]), ph ^ 1, abort_flag, p.status)) break;
+        const uint32_t full = smem_u32(&bar_x_full[s]);
+        mbar_expect_tx(full, L::kXStage);
+        const int kb = kb_begin + (i + rot >= nkb ? i + rot - nkb : i + rot);
+        tma_load_2d(smem_u32(x_tile(s, 0)), &map_x, full, kb * kGemmBK, m0);
+        tma_load_2d(smem_u32(x_tile(s, 1)), &map_x, full, kb * kGemmBK + 64, m0);
+        ++issued;
+      }
+      if (*abort_flag) {
+        const int first = issued > NX ? issued - NX : 0;
+        for (int i = first; i < issued; ++i) {
+          const uint32_t bar = smem_u32(&bar_x_full[i % NX]);
+          const uint32_t ph = (i / NX) & 1;
+          const unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(bar, ph) && globaltimer_ns() - t0 < 20000000ull) {
           }
         }
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(kGemmBM, BN);
-      bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (Q4) ok = mbar_wait(smem_u32(&bar_deq[s]), ph, abort_flag, p.status);
-        ok = ok && mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag, p.status);
-        if (!ok) break;
-        tc_fence_after();
+    // ---------------- MMA issuer: the whole warp follows the barriers, one elected lane issues ----------------
+    constexpr uint32_t idesc = umma_idesc_bf16(kGemmBM, BN);
+    const uint64_t desc_w0 = umma_desc_k_sw128(smem_u32(smem));
+    const uint64_t desc_x0 = umma_desc_k_sw128(smem_u32(smem + L::kOffX));
+    bool ok = true;
+    for (int i = 0; i < nkb; ++i) {
+      const int sa = i % NAS, sx = i % NX;
+      ok = mbar_wait(smem_u32(&bar_a_full[sa]), (i / NAS) & 1, abort_flag, p.status);
+      ok = ok && mbar_wait(smem_u32(&bar_x_full[sx]), (i / NX) & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (i == 0 && lane == 0) DLV_STAMP(2);
+      if (i == 4 && lane == 0) DLV_STAMP(9);
+      if (i == 12 && lane == 0) DLV_STAMP(10);
+      tc_fence_after();
+      if (lane == 0) {
+        // descriptor start-address field counts 16-byte units: stage strides and the 32-byte k-step are added there
+        const uint64_t dx = desc_x0 + static_cast<uint64_t>((sx * L::kXStage) >> 4);
 #pragma unroll
         for (int k4 = 0; k4 < 8; ++k4) {
           const int sub = k4 >> 2, kk = k4 & 3;
-          const uint64_t da = umma_desc_k_sw128(smem_u32(stage_w(s, sub)) + kk * 32);
-          const uint64_t db = umma_desc_k_sw128(smem_u32(stage_x(s, sub)) + kk * 32);
-          umma_bf16(tmem_base, da, db, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+          const uint64_t db = dx + static_cast<uint64_t>((sub * (BN * 128) + kk * 32) >> 4);
+          const uint32_t acc = (i > 0 || k4 > 0) ? 1u : 0u;
+          if (Q4) {
+            umma_bf16_ts(tmem_base, tmem_base + kGemmTmemA + sa * kGemmTmemAStage + k4 * 8, db, idesc, acc);
+          } else {
+            const uint64_t da = desc_w0 + static_cast<uint64_t>((sa * L::kWStage + sub * L::kWTile + kk * 32) >> 4);
+            umma_bf16(tmem_base, da, db, idesc, acc);
+          }
         }
-        umma_commit(smem_u32(&bar_empty[s]));
+        umma_commit(smem_u32(&bar_a_empty[sa]));
+        umma_commit(smem_u32(&bar_x_empty[sx]));
       }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      DLV_STAMP(3);
       umma_commit(smem_u32(bar_acc));
       if (!ok) {
         // outstanding MMAs must retire before TMEM is released
         const unsigned long long t0 = globaltimer_ns();
-        while (!mbar_try_wait(smem_u32(bar_acc), 0) && globaltimer_ns() - t0 < 50000000ull) {
+        while (!mbar_try_wait(smem_u32(bar_acc), 0) && globaltimer_ns() - t0 < 20000000ull) {
         }
       }
     }
-  } else {
-    // ---------------- dequant + epilogue warps (256 threads) ----------------
-    const int t = threadIdx.x - 64;
+    __syncwarp();
+  } else if (warp >= kGemmEpiWarp0) {
+    // ---------------- dequant + epilogue warps (512 threads) ----------------
+    const int t = threadIdx.x - kGemmEpiWarp0 * 32;
+    const int we = warp - kGemmEpiWarp0;
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may access
     bool ok = true;
     if (Q4) {
-      const int r = t & 127, h = t >> 7;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag, p.status)) { ok = false; break; }
-        const uint8_t* raw = stage_raw(s) + r * 64;
-        const float4 sc4 = *reinterpret_cast<const float4*>(stage_sc(s) + r * 16);
-        const float sc[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
-        uint8_t* wrow = stage_w(s, h) + r * 128;
+      // The 16 warps form 4 groups; group g expands the k-blocks i = g, g + 4, ... so that four stages are in flight at
+      // once (one warp iteration is a chain of long-latency steps: shared-memory loads, conversion, tcgen05.st and its
+      // wait). Inside a group warp `q` owns rows 32q .. 32q+31 (its tensor-memory lane quarter) and all four 32-element
+      // blocks of the stage.
+      const int grp4 = we >> 2;
+      const int r = q * 32 + lane;
+      for (int i = grp4; i < nkb; i += 4) {
+        const int sr = i % NR, sa = i % NA;
+        if (!mbar_wait(smem_u32(&bar_r_full[sr]), (i / NR) & 1, abort_flag, p.status)) { ok = false; break; }
+        uint4 wq[4];
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-          const int blk = 2 * h + b;
-          const uint4 w = *reinterpret_cast<const uint4*>(raw + ((blk ^ ((r >> 1) & 3)) << 4));
-          const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[blk]);
-          const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+        for (int b = 0; b < 4; ++b) wq[b] = *reinterpret_cast<const uint4*>(raw_tile(sr) + r * 64 + ((b ^ ((r >> 1) & 3)) << 4));
+        const float4 sc4 = *reinterpret_cast<const float4*>(sc_tile(sr) + r * 16);
+        const float sc[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+        // the tensor-memory stage is free once the MMAs of k-block i - NA have retired
+        if (!mbar_wait(smem_u32(&bar_a_empty[sa]), ((i / NA) & 1) ^ 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tdst = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kGemmTmemA + sa * kGemmTmemAStage;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[b]);
+          const uint32_t words[4] = {wq[b].x, wq[b].y, wq[b].z, wq[b].w};
+          uint32_t o[16];  // 32 bf16: elements 0..15 from the low nibbles of bytes 0..15, 16..31 from the high nibbles
 #pragma unroll
           for (int hl = 0; hl < 2; ++hl) {
 #pragma unroll
-            for (int wp = 0; wp < 2; ++wp) {
-              const uint32_t a = (words[2 * wp] >> (4 * hl)) & 0x0F0F0F0Fu;
-              const uint32_t c = (words[2 * wp + 1] >> (4 * hl)) & 0x0F0F0F0Fu;
-              uint4 o;
-              o.x = q4_pair_to_bf162(a, 0x4140u, s2);
-              o.y = q4_pair_to_bf162(a, 0x4342u, s2);
-              o.z = q4_pair_to_bf162(c, 0x4140u, s2);
-              o.w = q4_pair_to_bf162(c, 0x4342u, s2);
-              const int chunk = 4 * b + 2 * hl + wp;
-              *reinterpret_cast<uint4*>(wrow + ((chunk ^ (r & 7)) << 4)) = o;
+            for (int wd = 0; wd < 4; ++wd) {
+              const uint32_t a = (words[wd] >> (4 * hl)) & 0x0F0F0F0Fu;
+              o[hl * 8 + wd * 2 + 0] = q4_pair_to_bf162(a, 0x4140u, s2);
+              o[hl * 8 + wd * 2 + 1] = q4_pair_to_bf162(a, 0x4342u, s2);
             }
           }
+          tmem_st_x16(tdst + b * 16, o);
         }
-        fence_proxy_async_smem();
-        mbar_arrive(smem_u32(&bar_deq[s]));
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&bar_r_empty[sr]));
+          mbar_arrive(smem_u32(&bar_a_full[sa]));
+        }
       }
     }
-    // ---- epilogue ----
+    // ---- accumulator -> fp32 tile [col][row] in shared memory (the rings are idle once the MMAs retired) ----
     if (ok) ok = mbar_wait(smem_u32(bar_acc), 0, abort_flag, p.status);
-    // All 256 threads reach this barrier; afterwards the abort flag gives a CTA-uniform decision (it is only ever
+    // All 512 threads reach this barrier; afterwards the abort flag gives a CTA-uniform decision (it is only ever
     // raised before the accumulator barrier can complete), so the named barriers below never miss a thread.
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, 512;" ::: "memory");
     ok = (*abort_flag == 0);
+    if (t == 0) DLV_STAMP(4);
     if (ok) {
       tc_fence_after();
-      const int we = warp - 2;
-      const int q = warp & 3;            // TMEM lane quarter this warp may read
-      const int half = we >> 2;          // column half
-      const int row = q * 32 + lane;
-      const int n = n0 + row;
-      constexpr int COLS = BN / 2;
+      constexpr int GROUPS = BN >= 32 ? 4 : BN / 8;  // warps that share a quarter split the columns
+      constexpr int COLS = BN / GROUPS;
       constexpr int CH = COLS >= 16 ? 16 : 8;
-      const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * COLS;
-      const int tile_id = m_tile * p.n_tiles + n_tile;
-      if (p.splits == 1) {
-        const float bias = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
-#pragma unroll 1
-        for (int c0 = 0; c0 < COLS; c0 += CH) {
-          uint32_t v[CH];
-          if constexpr (CH == 16) tmem_ld_x16(taddr0 + c0, v); else tmem_ld_x8(taddr0 + c0, v);
-          tmem_ld_wait();
-          if (n < p.N) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int m = m0 + half * COLS + c0 + j;
-              if (m < p.M) {
-                const float acc = (nkb > 0 ? __uint_as_float(v[j]) : 0.f) + bias;
-                if (p.out_f32) reinterpret_cast<float*>(p.out)[static_cast<size_t>(m) * p.ldo + n] = acc;
-                else reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(m) * p.ldo + n] = f2bf(acc);
-              }
-            }
-          }
-        }
-      } else {
-        float* part = p.ws + (static_cast<size_t>(tile_id) * p.splits + split) * (BN * kGemmBM);
+      const int grp = we >> 2;
+      if (grp < GROUPS) {
+        const int row = q * 32 + lane;
+        const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * COLS;
+        float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll 1
         for (int c0 = 0; c0 < COLS; c0 += CH) {
           uint32_t v[CH];
           if constexpr (CH == 16) tmem_ld_x16(taddr0 + c0, v); else tmem_ld_x8(taddr0 + c0, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < CH; ++j)
-            part[(half * COLS + c0 + j) * kGemmBM + row] = nkb > 0 ? __uint_as_float(v[j]) : 0.f;
-        }
-        __threadfence();
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (t == 0) {
-          const int old = atomicAdd(&p.counters[tile_id], 1);
-          *s_last = (old == p.splits - 1) ? 1 : 0;
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (*s_last) {
-          __threadfence();
-          const float bias = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
-          const float* base = p.ws + static_cast<size_t>(tile_id) * p.splits * (BN * kGemmBM);
-          for (int c = 0; c < COLS; ++c) {
-            const int col = half * COLS + c;
-            const int m = m0 + col;
-            if (m >= p.M) break;
-            float acc = 0.f;
-            for (int sp = 0; sp < p.splits; ++sp)
-              acc += __ldcg(base + (static_cast<size_t>(sp) * BN + col) * kGemmBM + row);
-            acc += bias;
-            if (n < p.N) {
-              if (p.out_f32) reinterpret_cast<float*>(p.out)[static_cast<size_t>(m) * p.ldo + n] = acc;
-              else reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(m) * p.ldo + n] = f2bf(acc);
-            }
-          }
-          if (t == 0) p.counters[tile_id] = 0;
+          for (int j = 0; j < CH; ++j) stage[(grp * COLS + c0 + j) * kGemmBM + row] = nkb > 0 ? __uint_as_float(v[j]) : 0.f;
         }
       }
     }
+    if (p.splits == 1 || !p.cluster_reduce) asm volatile("bar.sync 1, 512;" ::: "memory");
   }
+  if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(5);
+  // ---------------- reduce over the split-K cluster (distributed shared memory) and store ----------------
+  const bool clustered = p.splits > 1 && p.cluster_reduce;
+  if (clustered) cluster_sync_all();  // every CTA of the cluster has its partial tile in shared memory (or is aborting)
+  if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(6);
+  if (warp >= kGemmEpiWarp0 && *abort_flag == 0) {
+    const int t = threadIdx.x - kGemmEpiWarp0 * 32;
+    const int row4 = (t & 31) * 4, csel = t >> 5;  // 4 consecutive weight rows, column slot 0..15
+    const int n = n0 + row4;
+    const float* stage = reinterpret_cast<const float*>(smem);
+    const uint32_t stage_addr = smem_u32(smem);
+    if (p.splits > 1 && !p.cluster_reduce) {
+      // fallback: partial tiles through the global workspace, the last CTA to arrive reduces in split order
+      const int tile_id = m_tile * p.n_tiles + n_tile;
+      float* part = p.ws + (static_cast<size_t>(tile_id) * p.splits + split) * (BN * kGemmBM);
+      for (int col = csel; col < BN; col += 16)
+        *reinterpret_cast<float4*>(part + col * kGemmBM + row4) = *reinterpret_cast<const float4*>(stage + col * kGemmBM + row4);
+      __threadfence();
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      if (t == 0) {
+        const int old = atomicAdd(&p.counters[tile_id], 1);
+        *s_last = (old == p.splits - 1) ? 1 : 0;
+      }
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      if (*s_last) __threadfence();
+    }
+    const bool do_store = p.splits == 1 || p.cluster_reduce || *s_last;
+    if (do_store) {
+      const uint32_t me = clustered ? cluster_ctarank() : 0u;
+      const int stride = clustered ? p.splits : 1;
+      float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.bias != nullptr) {
+        bias.x = n + 0 < p.N ? p.bias[n + 0] : 0.f;
+        bias.y = n + 1 < p.N ? p.bias[n + 1] : 0.f;
+        bias.z = n + 2 < p.N ? p.bias[n + 2] : 0.f;
+        bias.w = n + 3 < p.N ? p.bias[n + 3] : 0.f;
+      }
+      const bool vec_ok = (n + 3 < p.N) && ((p.ldo & 3) == 0);
+      // column c of the tile is finished by cluster rank c % splits; the 16 column slots of this CTA take turns
+      for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
+        const int m = m0 + col;
+        if (m >= p.M) break;
+        float4 acc;
+        if (clustered) {
+          acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          const uint32_t a = stage_addr + static_cast<uint32_t>((col * kGemmBM + row4) * 4);
+          for (int sp = 0; sp < p.splits; ++sp) {
+            const float4 v = ld_dsmem_f32x4(a, static_cast<uint32_t>(sp));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+        } else if (p.splits > 1) {
+          acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float* base = p.ws + static_cast<size_t>(m_tile * p.n_tiles + n_tile) * p.splits * (BN * kGemmBM);
+          for (int sp = 0; sp < p.splits; ++sp) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (static_cast<size_t>(sp) * BN + col) * kGemmBM + row4));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+        } else {
+          acc = *reinterpret_cast<const float4*>(stage + col * kGemmBM + row4);
+        }
+        acc.x += bias.x; acc.y += bias.y; acc.z += bias.z; acc.w += bias.w;
+        const size_t o = static_cast<size_t>(m) * p.ldo + n;
+        if (vec_ok) {
+          if (p.out_f32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o) = acc;
+          else {
+            uint2 pk;
+            pk.x = pack_bf162(acc.x, acc.y);
+            pk.y = pack_bf162(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
+          }
+        } else {
+          const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+          for (int e = 0; e < 4; ++e) {
+            if (n + e < p.N) {
+              if (p.out_f32) reinterpret_cast<float*>(p.out)[o + e] = vals[e];
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[o + e] = f2bf(vals[e]);
+            }
+          }
+        }
+      }
+      if (p.splits > 1 && !p.cluster_reduce && t == 0) p.counters[m_tile * p.n_tiles + n_tile] = 0;
+    }
+  }
+  if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(7);
+  if (clustered) cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
@@ -297,6 +455,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // Q4: packed bytes 
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (threadIdx.x == 0) DLV_STAMP(8);
+#undef DLV_STAMP
 }
 
 }  // namespace dlv
