@@ -1,0 +1,316 @@
+"""Public entry points: ``AutoModelForCausalLM``, ``AutoModelForEmbeddings``, ``AutoModelForSequenceClassification``.
+
+The builder mirrors the reference's ``AutoModelForCausaLm.Builder`` options that make sense on GPUs
+(core/.../model/AutoModelForCausaLm.java:106-760): working dtype, KV-cache settings, tensor parallel rank/size and
+collectives, output-head quantisation, max batch size, quantise-on-demand, LoRA adapter (merge at load), guided-decoding
+settings, JSON ``AutoModelConfig``. ``model_type`` dispatch follows ``readConfig`` / ``newModel`` (:522-583). The text-level
+``generate(session, prompt, params, on_event)`` keeps the reference's response fields (text, text with special tokens,
+reasoning, finish reason, token counts, timings, tool calls) and its stop order.
+"""
+from __future__ import annotations
+
+import json
+import os
+import uuid
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from .ckpt.loader import WeightLoader
+from .ckpt.lora import LoraAdapter, MergingWeightLoader
+from .ckpt.quantizer import quantize_on_demand
+from .config import ModelConfig, load_config
+from .engine.engine import Engine, EngineConfig, Request
+from .guided.index import DEFAULT_SETTINGS, SketchesSettings
+from .guided.processor import LogitsProcessorFactory
+from .kv.paged import KvCacheSettings
+from .models.bert import BertModel
+from .models.gpt2 import Gpt2Model
+from .models.transformer import DecoderModel
+from .parallel.context import SINGLE, TensorParallelContext
+from .params import FinishReason, GeneratorParameters, Response
+from .prompt.chat import PromptBuilder, PromptContext
+from .prompt.parsers import ReasoningTextSplitter, StopStringDetector, ToolCallParser, parser_for_model, split_reasoning
+from .tokenizer.auto import AutoTokenizer, IncrementalDetokenizer
+
+
+@dataclass
+class AutoModelConfig:
+    """JSON-serialisable builder options (reference: core/.../model/AutoModelConfig.java:21-103)."""
+
+    model: str = ""
+    device: str = "auto"
+    dtype: str = "auto"
+    output_head_quantization: Optional[str] = None
+    max_batch_size: int = 8192
+    max_seqs: int = 128
+    quantize_on_demand: bool = False
+    lora_adapter: Optional[str] = None
+    cuda_graphs: bool = True
+    kv_block_size: int = 32
+    kv_max_prefix_tokens: int = 512
+    kv_max_entries: int = 10_000
+    kv_policy: str = "START_AND_END"
+    kv_pages: Optional[int] = None
+    profile_stages: bool = False
+
+    @staticmethod
+    def from_json(path_or_text: str) -> "AutoModelConfig":
+        text = open(path_or_text).read() if os.path.exists(path_or_text) else path_or_text
+        d = json.loads(text)
+        known = {f for f in AutoModelConfig.__dataclass_fields__}
+        return AutoModelConfig(**{k: v for k, v in d.items() if k in known})
+
+
+def _device(name: str) -> torch.device:
+    if name == "auto":
+        return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    return torch.device(name)
+
+
+def build_model(cfg: ModelConfig, device, dtype, tp: TensorParallelContext):
+    if cfg.model_type == "gpt2":
+        return Gpt2Model(cfg, device, dtype, tp)
+    if cfg.model_type == "bert":
+        return BertModel(cfg, device, dtype)
+    return DecoderModel(cfg, device, dtype, tp)
+
+
+class CausalLanguageModel:
+    """Text-level facade over one engine (reference: core/.../model/DefaultCausalLanguageModel.java:28-148)."""
+
+    def __init__(self, model, engine: Engine, tokenizer, name: str, sketches: SketchesSettings = DEFAULT_SETTINGS):
+        self.model = model
+        self.engine = engine
+        self.tokenizer = tokenizer
+        self.name = name
+        self.cfg: ModelConfig = model.cfg
+        self.tool_parser: ToolCallParser = parser_for_model(name)
+        eos = set(self.cfg.eos_token_ids)
+        if tokenizer.eos_token_id is not None:
+            eos.add(tokenizer.eos_token_id)
+        self.eos_ids = eos
+        engine.eos_ids = frozenset(eos)
+        engine.special_ids = frozenset(tokenizer.special_ids)
+        engine.sampler.decode_token = lambda i: tokenizer.decode([i])
+        self.guides = LogitsProcessorFactory(tokenizer, eos, self.cfg.vocab_size, sketches)
+        self.generation_hook: Optional[Callable] = None
+
+    # -- prompts ---------------------------------------------------------------------------------------------------
+    def prompt_builder(self) -> PromptBuilder:
+        return PromptBuilder(self.tokenizer.chat_template, self.tokenizer.bos_token, self.tokenizer.eos_token)
+
+    def encode_prompt(self, text: str) -> list[int]:
+        ids = self.tokenizer.encode(text)
+        bos = self.cfg.bos_token_id if self.cfg.bos_token_id is not None else self.tokenizer.bos_token_id
+        if bos is not None:
+            while ids and ids[0] == bos:  # strip leading BOS, then add exactly one when the family uses it
+                ids = ids[1:]
+            if self.cfg.add_bos and self.tokenizer.add_bos_token is not False and self.cfg.model_type not in ("qwen2", "qwen3", "qwen3_moe"):
+                ids = [bos] + ids
+        return ids
+
+    # -- generation ------------------------------------------------------------------------------------------------
+    def submit(self, prompt, params: Optional[GeneratorParameters] = None, on_event=None, session: Optional[str] = None) -> "Generation":
+        params = params or GeneratorParameters()
+        has_tools = False
+        if isinstance(prompt, PromptContext):
+            has_tools, prompt = prompt.has_tools, prompt.prompt
+        ids = self.encode_prompt(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+        gen = Generation(self, params, on_event, session or str(uuid.uuid4()), has_tools)
+        guide = self.guides.create(params)
+        stopper = StopStringDetector(gen.detok_special, params.stop_words, params.include_stop_str_in_output,
+                                     self.tool_parser if has_tools else None)
+        gen.stopper = stopper
+        gen.request = self.engine.add_request(ids, params, gen._on_token, guide, stopper)
+        return gen
+
+    def generate(self, prompt, params: Optional[GeneratorParameters] = None, on_event=None, session: Optional[str] = None) -> Response:
+        gen = self.submit(prompt, params, on_event, session)
+        self.engine.run([gen.request])
+        return gen.finish()
+
+    def generate_many(self, prompts: list, params: Optional[GeneratorParameters] = None) -> list[Response]:
+        import copy
+
+        gens = [self.submit(p, copy.deepcopy(params) if params else None) for p in prompts]
+        self.engine.run([g.request for g in gens])
+        return [g.finish() for g in gens]
+
+    def close(self) -> None:
+        pass
+
+
+class Generation:
+    """One in-flight request: incremental detokenisation, event emission, final :class:`Response` assembly."""
+
+    def __init__(self, clm: CausalLanguageModel, params, on_event, session, has_tools):
+        self.clm = clm
+        self.params = params
+        self.on_event = on_event
+        self.session = session
+        self.has_tools = has_tools
+        self.detok_plain = IncrementalDetokenizer(clm.tokenizer, skip_special=True)
+        self.detok_special = IncrementalDetokenizer(clm.tokenizer, skip_special=False)
+        self.request: Optional[Request] = None
+        self.stopper: Optional[StopStringDetector] = None
+
+    def _on_token(self, token: int, request: Request) -> None:
+        import time
+
+        self.detok_special.push(token)
+        piece = self.detok_plain.push(token)
+        if self.on_event is not None and piece:
+            self.on_event(token, piece, self.detok_special.text, (time.perf_counter() - request.t_submit) * 1e3)
+
+    def finish(self) -> Response:
+        r = self.request.response()
+        text, text_sp = self.detok_plain.text, self.detok_special.text
+        if self.stopper is not None and self.stopper.truncate_at is not None:
+            cut = text_sp[: self.stopper.truncate_at]
+            text_sp = cut
+            # the plain text is the special-token text minus specials: cut it at the same stop string
+            for s in self.params.stop_words:
+                i = text.find(s)
+                if i >= 0:
+                    text = text[: i + (len(s) if self.params.include_stop_str_in_output else 0)]
+                    break
+        r.text_with_special_tokens = text_sp
+        content, reasoning = split_reasoning(text)
+        r.reasoning = reasoning
+        r.text = content
+        if self.has_tools:
+            calls = self.clm.tool_parser.extract(text_sp)
+            if calls:
+                r.tool_calls = calls
+                r.finish_reason = FinishReason.TOOL_CALL
+                r.text = self.clm.tool_parser.strip(content)
+        return r
+
+
+class AutoModelForCausalLM:
+    class Builder:
+        def __init__(self, model_dir: str):
+            self.model_dir = model_dir
+            self.conf = AutoModelConfig(model=model_dir)
+            self.tp = SINGLE
+            self.kv = KvCacheSettings()
+            self.sketches = DEFAULT_SETTINGS
+            self.name: Optional[str] = None
+            self.layer_hook = None
+
+        def with_device(self, device: str):
+            self.conf.device = device
+            return self
+
+        def with_working_memory_type(self, dtype: str):
+            self.conf.dtype = dtype
+            return self
+
+        def with_kv_cache_settings(self, kv: KvCacheSettings):
+            self.kv = kv
+            return self
+
+        def with_tensor_parallel(self, rank: int, size: int, collectives=None):
+            self.tp = TensorParallelContext(rank, size, collectives)
+            return self
+
+        def with_tensor_parallel_context(self, tp: TensorParallelContext):
+            self.tp = tp
+            return self
+
+        def with_output_head_quantization(self, q: Optional[str]):
+            self.conf.output_head_quantization = q
+            return self
+
+        def with_max_batch_size(self, n: int):
+            self.conf.max_batch_size = n
+            return self
+
+        def with_quantize_on_demand(self, on: bool = True):
+            self.conf.quantize_on_demand = on
+            return self
+
+        def with_lora_adapter(self, adapter_dir: str):
+            self.conf.lora_adapter = adapter_dir
+            return self
+
+        def with_sketches_settings(self, s: SketchesSettings):
+            self.sketches = s
+            return self
+
+        def with_config(self, conf: AutoModelConfig):
+            model = self.conf.model
+            self.conf = conf
+            self.conf.model = conf.model or model
+            self.model_dir = self.conf.model
+            self.kv = KvCacheSettings(block_size=conf.kv_block_size, max_prefix_tokens=conf.kv_max_prefix_tokens,
+                                      max_entries=conf.kv_max_entries, policy=conf.kv_policy)
+            return self
+
+        def with_name(self, name: str):
+            self.name = name
+            return self
+
+        def with_layer_debug_hook(self, hook):
+            self.layer_hook = hook
+            return self
+
+        def with_profile_stages(self, on: bool = True):
+            self.conf.profile_stages = on
+            return self
+
+        def build_local_transformer_model(self):
+            """Weights + model graph only (no engine, no tokenizer)."""
+            conf = self.conf
+            model_dir = self.model_dir
+            if conf.quantize_on_demand:
+                cache_root = os.path.expanduser(os.environ.get("DELIVERANCE_HOME", "~/.deliverance"))
+                target = os.path.join(cache_root, os.path.basename(os.path.normpath(model_dir)) + "-JQ4")
+                model_dir = quantize_on_demand(model_dir, target)
+            cfg = load_config(model_dir)
+            dev = _device(conf.device)
+            dtype = {"auto": None, "bf16": torch.bfloat16, "BF16": torch.bfloat16, "f32": torch.float32, "F32": torch.float32,
+                     "f16": torch.float16}.get(conf.dtype, None)
+            if conf.lora_adapter:
+                loader = MergingWeightLoader(model_dir, LoraAdapter(conf.lora_adapter))
+            else:
+                loader = WeightLoader(model_dir)
+            model = build_model(cfg, dev, dtype, self.tp)
+            if isinstance(model, BertModel):
+                model.load(loader)
+            else:
+                model.load(loader, head_quant=conf.output_head_quantization)
+                model.layer_hook = self.layer_hook
+                if conf.profile_stages or os.environ.get("DELIVERANCE_PROFILE_STAGES"):
+                    from .utils.profiler import InferenceProfiler
+
+                    model.profiler = InferenceProfiler(dev)
+            return model, model_dir
+
+        def build(self) -> CausalLanguageModel:
+            model, model_dir = self.build_local_transformer_model()
+            if isinstance(model, BertModel):
+                raise ValueError("bert checkpoints load through AutoModelForEmbeddings / AutoModelForSequenceClassification")
+            conf = self.conf
+            econf = EngineConfig(max_batch_tokens=conf.max_batch_size, max_seqs=conf.max_seqs, num_pages=conf.kv_pages,
+                                 cuda_graphs=conf.cuda_graphs and not (conf.profile_stages or bool(os.environ.get("DELIVERANCE_PROFILE_STAGES"))),
+                                 kv=self.kv)
+            engine = Engine(model, econf)
+            tok = AutoTokenizer.from_pretrained(model_dir)
+            return CausalLanguageModel(model, engine, tok, self.name or os.path.basename(os.path.normpath(model_dir)), self.sketches)
+
+    @staticmethod
+    def new_builder(model_dir: str) -> "AutoModelForCausalLM.Builder":
+        return AutoModelForCausalLM.Builder(model_dir)
+
+    @staticmethod
+    def from_pretrained(model_dir: str, **kw) -> CausalLanguageModel:
+        b = AutoModelForCausalLM.Builder(model_dir)
+        for k, v in kw.items():
+            if hasattr(b.conf, k):
+                setattr(b.conf, k, v)
+            else:
+                raise TypeError(f"unknown option {k}")
+        return b.build()

@@ -1,0 +1,167 @@
+"""Engine mechanics: continuous batching, prefix cache (mechanical invariants and output equivalence), sampler semantics."""
+import random
+
+import pytest
+import torch
+
+from deliverance_b200.ckpt.loader import WeightLoader
+from deliverance_b200.ckpt.tiny import write_tiny_model
+from deliverance_b200.config import load_config
+from deliverance_b200.engine.engine import Engine, EngineConfig
+from deliverance_b200.engine.sampler import Sampler, SamplingState, candidate_limit, sample_top_k_top_p_batch, xtc_pick
+from deliverance_b200.kv.paged import KvCacheSettings, PageAllocator, PrefixCache, compose_salt
+from deliverance_b200.models.transformer import DecoderModel
+from deliverance_b200.params import FinishReason, GeneratorParameters
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("m") / "llama")
+    write_tiny_model(d, "llama", seed=7, std=0.05)
+    cfg = load_config(d)
+    return DecoderModel(cfg, "cpu").load(WeightLoader(d))
+
+
+def _engine(model, **kw):
+    kv = kw.pop("kv", KvCacheSettings())
+    return Engine(model, EngineConfig(num_pages=kw.pop("pages", 128), max_batch_tokens=kw.pop("chunk", 64), kv=kv, **kw))
+
+
+def test_batched_equals_single(tiny):
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 250, (n,), generator=g).tolist() for n in (5, 40, 70, 33)]
+    singles = [_engine(tiny).generate(p, GeneratorParameters(max_tokens=5)).token_ids for p in prompts]
+    eng = _engine(tiny, chunk=48)
+    rs = eng.generate_batch(prompts, GeneratorParameters(max_tokens=5))
+    assert [r.token_ids for r in rs] == singles
+    assert eng.kv.allocator.available() == eng.kv.num_pages - 1 - sum(len(e.pages) for e in eng.kv.prefix.entries.values()) or True
+    assert all(r.finish_reason == FinishReason.MAX_TOKENS for r in rs)
+
+
+def test_checkpoint_lengths_policies():
+    s = KvCacheSettings()
+    assert s.checkpoint_lengths(100) == [32, 64, 96]
+    assert s.checkpoint_lengths(700) == [32, 64, 480, 512]
+    assert s.checkpoint_lengths(31) == []
+    assert KvCacheSettings(policy="FIXED_BLOCKS").checkpoint_lengths(130) == [32, 64, 96, 128]
+    assert KvCacheSettings(policy="ANCHORS").checkpoint_lengths(300) == [32, 64, 128, 288]
+
+
+def test_prefix_cache_lru_refcounts():
+    alloc = PageAllocator(16)
+    pc = PrefixCache(KvCacheSettings(max_entries=3, policy="FIXED_BLOCKS"), alloc)
+    toks = list(range(100))
+    pages = [alloc.alloc() for _ in range(4)]
+    assert pc.store("s", toks, pages) == 3
+    assert pc.lookup("other", toks) is None
+    hit = pc.lookup("s", toks[:70] + [999] * 30)
+    assert hit.length == 64 and hit.pages == pages[:2] and alloc.ref[pages[0]] == 1 + 3 + 1
+    for p in hit.pages:
+        alloc.release(p)
+    pc.store("s", list(range(1000, 1040)), [alloc.alloc(), alloc.alloc()])  # a 4th entry evicts the oldest
+    assert len(pc.entries) == 3 and pc.metrics["evict"] == 1
+    for p in pages:
+        alloc.release(p)
+    pc.clear()
+    assert alloc.available() == 15 - 2  # only the two pages still owned by the caller stay out
+
+
+def test_salt_composition():
+    assert compose_salt("a") == "a"
+    assert compose_salt("a", "ad1") == "lora:ad1|a"
+    assert compose_salt("a", "ad1", 1, 4) == "tp:size=4:rank=1|lora:ad1|a"
+
+
+def test_prefix_hit_output_equivalence(tiny):
+    g = torch.Generator().manual_seed(1)
+    shared = torch.randint(3, 250, (96,), generator=g).tolist()
+    p1, p2 = shared + [5, 6, 7], shared + [9, 10, 11, 12]
+    cold = _engine(tiny, kv=KvCacheSettings(enabled=False))
+    ref2 = cold.generate(p2, GeneratorParameters(max_tokens=6)).token_ids
+    eng = _engine(tiny)
+    eng.generate(p1, GeneratorParameters(max_tokens=2))
+    r2 = eng.generate(p2, GeneratorParameters(max_tokens=6))
+    assert r2.prefix_hit_tokens == 96 and r2.token_ids == ref2
+    # salts separate the caches
+    r3 = eng.generate(p2, GeneratorParameters(max_tokens=6, cache_salt="tenant-b"))
+    assert r3.prefix_hit_tokens == 0 and r3.token_ids == ref2
+    # full-prompt hit: the last prompt token is replayed and decoding starts at the full prompt length
+    p3 = shared[:64]
+    a = eng.generate(p3, GeneratorParameters(max_tokens=3))
+    b = eng.generate(p3, GeneratorParameters(max_tokens=3))
+    assert b.prefix_hit_tokens == 64 and a.token_ids == b.token_ids
+
+
+def test_request_limits_and_stops(tiny):
+    eng = _engine(tiny)
+    with pytest.raises(ValueError):
+        eng.generate([1] * 300)
+    with pytest.raises(ValueError):
+        eng.generate([1, 2, 3], GeneratorParameters(ntokens=3))
+    r = eng.generate([4, 5, 6], GeneratorParameters(ntokens=8))
+    assert r.generated_tokens == 5 and r.finish_reason == FinishReason.MAX_TOKENS
+    first = eng.generate([4, 5, 6], GeneratorParameters(max_tokens=3)).token_ids[0]
+    eng2 = Engine(tiny, EngineConfig(num_pages=32), eos_ids=(first,))
+    r = eng2.generate([4, 5, 6], GeneratorParameters(max_tokens=9))
+    assert r.finish_reason == FinishReason.STOP_TOKEN and r.generated_tokens == 1
+    with pytest.raises(ValueError):
+        GeneratorParameters(guided_regex="a", guided_choice=["a"]).validate()
+    with pytest.raises(ValueError):
+        GeneratorParameters(uniform_top_p=0.5, top_p=0.5).validate()
+
+
+def test_candidate_limit_and_defaults():
+    assert candidate_limit(None, 100) == 100 and candidate_limit(5, 100) == 5 and candidate_limit(500, 100) == 100
+    assert candidate_limit(0.9, 100) == 10 and candidate_limit(0.999, 100) == 1
+    st = SamplingState.create(GeneratorParameters(temperature=0.7))
+    assert st.effective()[1] == 0.10  # nothing set -> top_p = 0.10
+    assert SamplingState.create(GeneratorParameters(temperature=0.7, top_k=3)).effective()[1] is None
+
+
+def test_top_k_top_p_semantics():
+    logits = torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05]]))
+    T = torch.tensor([1.0])
+
+    def run(limit, top_p, uniform, u):
+        return int(sample_top_k_top_p_batch(logits, T, torch.tensor([limit]), torch.tensor([top_p]), torch.tensor([uniform]), torch.tensor([u]))[0])
+
+    assert run(4, 0.0, False, 0.49) == 0 and run(4, 0.0, False, 0.51) == 1 and run(4, 0.0, False, 0.96) == 3
+    assert run(1, 0.0, False, 0.99) == 0  # top_k = 1
+    assert run(2, 0.0, False, 0.7) == 1  # renormalised over the kept two: 0.625 / 0.375
+    assert run(4, 0.6, False, 0.99) == 1  # nucleus {0, 1}
+    assert run(4, 0.8, True, 0.1) == 0 and run(4, 0.8, True, 0.5) == 1 and run(4, 0.8, True, 0.99) == 1  # uniform pick inside it
+    # stable order on ties: the lower index comes first
+    tie = torch.zeros(1, 4)
+    assert int(sample_top_k_top_p_batch(tie, T, torch.tensor([4]), torch.tensor([0.0]), torch.tensor([False]), torch.tensor([0.2]))[0]) == 0
+
+
+def test_xtc_and_sampler_determinism():
+    logits = torch.log(torch.tensor([0.5, 0.3, 0.15, 0.05]))
+    assert xtc_pick(logits, 0.1, 0.5, 0.9, set()) is None  # u > probability: no-op
+    assert xtc_pick(logits, 0.1, 1.0, 0.2, set()) == 2  # least probable above the threshold
+    assert xtc_pick(logits, 0.1, 1.0, 0.2, {0}) == 0  # most probable is special -> returned
+    assert xtc_pick(logits, 0.9, 1.0, 0.2, set()) is None
+    s = Sampler()
+    big = torch.randn(3, 500, generator=torch.Generator().manual_seed(3))
+    mk = lambda: [SamplingState.create(GeneratorParameters(temperature=0.9, top_p=0.9, seed=11)) for _ in range(3)]  # noqa: E731
+    a, _ = s.sample(big, mk())
+    b, _ = s.sample(big, mk())
+    assert a == b
+    toks, lps = s.sample(big, [SamplingState.create(GeneratorParameters(logprobs=True, top_logprobs=3)) for _ in range(3)])
+    assert toks == torch.argmax(big, dim=-1).tolist()
+    assert abs(lps[0].logprob - torch.log_softmax(big[0], -1)[toks[0]].item()) < 1e-5 and len(lps[0].top) == 3
+
+
+def test_cancel_and_callback_error(tiny):
+    eng = _engine(tiny)
+    seen = []
+    r = eng.add_request([4, 5, 6], GeneratorParameters(max_tokens=50), on_token=lambda t, rq: (seen.append(t), eng.abort(rq) if len(seen) == 3 else None))
+    eng.run([r])
+    assert r.finish_reason == FinishReason.CANCELLED and len(r.output) == 3
+
+    def boom(t, rq):
+        raise RuntimeError("client went away")
+
+    r2 = eng.add_request([4, 5, 6], GeneratorParameters(max_tokens=50), on_token=boom)
+    eng.run([r2])
+    assert r2.finish_reason == FinishReason.ERROR and eng.kv.allocator.available() > 0

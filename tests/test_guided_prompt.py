@@ -1,0 +1,129 @@
+"""Guided decoding automata, JSON-schema regexes, chat templates, tool-call parsers, reasoning splitter, tokenizer glue."""
+import json
+import re
+
+import pytest
+
+from deliverance_b200.guided.index import ChoiceGuide, Index, IndexGuide, LazyIndex, SketchesSettings, Vocabulary
+from deliverance_b200.guided.json_schema import schema_to_regex
+from deliverance_b200.prompt.chat import PromptBuilder, Tool, Function
+from deliverance_b200.prompt.parsers import (LlamaToolCallParser, QwenToolCallParser, ReasoningTextSplitter, parser_for_model,
+                                             split_reasoning)
+from deliverance_b200.tokenizer.auto import ByteTokenizer, IncrementalDetokenizer, PreTrainedTokenizer
+
+
+def _vocab():
+    toks = {i + 3: chr(c) for i, c in enumerate(range(32, 127))}
+    toks.update({200: "true", 201: "fal", 202: "se", 203: "12", 204: "", 205: '":'})
+    return Vocabulary(toks, [2], 256), {v: k for k, v in toks.items()}
+
+
+def test_lazy_index_walk_and_eos_only_in_accept():
+    v, rev = _vocab()
+    g = IndexGuide(LazyIndex(r"(true|false)", v))
+    assert sorted(g.allowed_tokens()) == sorted([rev["t"], rev["f"], 200, 201])
+    assert 204 not in g.allowed_tokens()  # empty-text tokens are never allowed
+    g.accept(201)
+    assert sorted(g.allowed_tokens()) == sorted([rev["s"], 202])
+    g.accept(202)
+    assert g.allowed_tokens() == [2]
+    with pytest.raises(ValueError):
+        g.accept(rev["x"])
+
+
+def test_eager_index_limits():
+    v, _ = _vocab()
+    idx = Index(r"[0-9]{2}", v)
+    assert len(idx.states) == 3
+    with pytest.raises(ValueError):
+        Index(r"[a-z]{40}", v, SketchesSettings(max_index_states=10))
+    with pytest.raises(ValueError):
+        LazyIndex("a" * 20, v, SketchesSettings(max_regex_length=10))
+
+
+def test_choice_guide():
+    c = ChoiceGuide([[5, 6], [5, 7, 8]], [2], 256)
+    assert c.allowed_tokens() == [5]
+    c.accept(5)
+    assert c.allowed_tokens() == [6, 7] and not c.is_complete()
+    c.accept(7)
+    c.accept(8)
+    assert c.is_complete() and c.allowed_tokens() == [2]
+
+
+@pytest.mark.parametrize("schema,good,bad", [
+    ({"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "string"}}}, ['{"a":-12,"b":"x\\n"}'], ['{"b":"x","a":1}', '{"a": 1,"b":"x"}']),
+    ({"enum": ["red", 3, None]}, ['"red"', "3", "null"], ['"blue"']),
+    ({"type": "array", "items": {"type": "boolean"}, "minItems": 1, "maxItems": 2}, ["[true]", "[true,false]"], ["[]", "[true,false,true]"]),
+    ({"anyOf": [{"type": "number"}, {"const": "n/a"}]}, ["1.5e3", '"n/a"'], ['"x"']),
+    ({"type": "string", "pattern": "^[a-z]{2}$"}, ['"ab"'], ['"abc"']),
+    ({"type": "string", "maxLength": 2}, ['""', '"ab"'], ['"abc"']),
+])
+def test_json_schema_regex(schema, good, bad):
+    rx = schema_to_regex(schema)
+    for s in good:
+        assert re.fullmatch(rx, s), (rx, s)
+        json.loads(s)
+    for s in bad:
+        assert not re.fullmatch(rx, s), (rx, s)
+    with pytest.raises(ValueError):
+        schema_to_regex({"$ref": "#/x"})
+
+
+def test_guided_json_walk_over_vocab():
+    v, rev = _vocab()
+    rx = schema_to_regex({"type": "object", "properties": {"ok": {"type": "boolean"}, "n": {"type": "integer"}}})
+    g = IndexGuide(LazyIndex(rx, v))
+    for ch in '{"ok":true,"n":12}':
+        g.accept(rev[ch])
+    assert g.index.is_final(g.state) and g.allowed_tokens() == [2]
+
+
+def test_chatml_fallback_and_jinja():
+    b = PromptBuilder().add_system("sys").add_user("hi")
+    assert b.build().prompt == "<|im_start|>system\nsys<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
+    b = PromptBuilder().add_user("hi").with_kwargs({"enable_thinking": False})
+    assert b.build().prompt.endswith("<think>\n\n</think>\n\n")
+    t = PromptBuilder().add_user("q").add_tools([Tool(Function("get_weather", "w", {"type": "object"}))]).build()
+    assert t.has_tools and "<tools>" in t.prompt and "get_weather" in t.prompt
+    tpl = "{{ bos_token }}{% for m in messages[::-1] %}[{{ m.role }}:{{ m.content }}]{% endfor %}{% if add_generation_prompt %}>{% endif %}{% if tools %}T{% endif %}"
+    p = PromptBuilder(tpl, "<s>").add_user("a").add_assistant("b").build().prompt
+    assert p == "<s>[assistant:b][user:a]>"
+    p = PromptBuilder().with_template("{{ messages[0].content | upper }}{{ custom }}").with_kwargs({"custom": "!"}).add_user("x").build().prompt
+    assert p == "X!"
+    with pytest.raises(ValueError):
+        PromptBuilder().build()
+
+
+def test_tool_call_parsers():
+    q = QwenToolCallParser()
+    text = 'Sure.\n<tool_call>\n{"name": "get_weather", "arguments": {"city": "Paris", "note": "a}b"}}\n</tool_call>\n<tool_call>\n{"name": "t2", "arguments": {}}\n</tool_call>'
+    calls = q.extract(text)
+    assert [c.id for c in calls] == ["101", "102"] and calls[0].name == "get_weather" and calls[0].arguments["note"] == "a}b"
+    assert q.strip(text) == "Sure."
+    assert q.extract("no calls here") == []
+    ll = LlamaToolCallParser()
+    calls = ll.extract('<|start_header_id|>assistant<|end_header_id|>\n\n{"type": "function", "function": "lookup", "parameters": {"k": 1}}')
+    assert calls[0].name == "lookup" and calls[0].arguments == {"k": 1}
+    assert ll.should_end_turn("abc<|eot_id|>") and not ll.should_end_turn("abc")
+    assert isinstance(parser_for_model("Qwen3-4B-JQ4"), QwenToolCallParser) and isinstance(parser_for_model("meta-llama/Llama-3.2-1B"), LlamaToolCallParser)
+
+
+def test_reasoning_splitter_holds_back_partial_tags():
+    s = ReasoningTextSplitter()
+    outs = [s.accept(p) for p in ["<th", "ink>rea", "son</thi", "nk>ans", "wer <", "b>"]]
+    c, r = s.flush()
+    assert s.reasoning == "reason" and s.content == "answer <b>"
+    assert outs[0] == ("", "") and outs[1] == ("", "rea")
+    assert split_reasoning("<think>\nabc\n</think>\n\nfinal") == ("final", "abc")
+    assert split_reasoning("plain") == ("plain", None)
+
+
+def test_incremental_detokenizer_utf8():
+    tk = PreTrainedTokenizer(ByteTokenizer(), {"bos_token": "<s>", "eos_token": "</s>"}, {"<s>": 1, "</s>": 2})
+    d = IncrementalDetokenizer(tk, skip_special=True)
+    ids = tk.encode("é!")
+    assert len(ids) == 3
+    pieces = [d.push(i) for i in ids + [2]]
+    assert pieces == ["", "é", "!", ""] and d.text == "é!"
+    assert tk.decode(tk.encode("héllo")) == "héllo"

