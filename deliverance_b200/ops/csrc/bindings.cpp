@@ -57,6 +57,37 @@ DeviceScratch& scratch_for(int device) {
   return it->second;
 }
 
+// ---- peer-memory state for the fused GEMM + all-reduce ------------------------------------------------------------
+class TpComm {
+ public:
+  // recv_ptrs / flag_ptrs: device addresses of every rank's receive area and flag matrix as mapped in this process
+  TpComm(int64_t rank, int64_t size, std::vector<int64_t> recv_ptrs, std::vector<int64_t> flag_ptrs, int64_t slab, int64_t ncta_max,
+         Tensor rounds, Tensor call) {
+    TORCH_CHECK(size >= 2 && size <= 8 && rank >= 0 && rank < size, "tensor-parallel size must be 2..8");
+    TORCH_CHECK(static_cast<int64_t>(recv_ptrs.size()) == size && static_cast<int64_t>(flag_ptrs.size()) == size, "one pointer per rank");
+    TORCH_CHECK(rounds.is_cuda() && rounds.scalar_type() == at::kInt && rounds.numel() >= ncta_max, "rounds must be int32 [ncta_max]");
+    TORCH_CHECK(call.is_cuda() && call.scalar_type() == at::kInt && call.numel() >= 2, "call must be int32 [2]");
+    args_.size = static_cast<int>(size);
+    args_.rank = static_cast<int>(rank);
+    args_.slab = slab;
+    args_.ncta_max = static_cast<int>(ncta_max);
+    for (int r = 0; r < 8; ++r) {
+      args_.recv[r] = r < size ? static_cast<unsigned long long>(recv_ptrs[r]) : 0ull;
+      args_.flags[r] = r < size ? static_cast<unsigned long long>(flag_ptrs[r]) : 0ull;
+      TORCH_CHECK(r >= size || ((args_.recv[r] & 15) == 0 && (args_.flags[r] & 3) == 0 && args_.recv[r] != 0 && args_.flags[r] != 0), "bad peer pointer");
+    }
+    rounds_ = rounds;
+    call_ = call;
+    args_.rounds = reinterpret_cast<unsigned int*>(rounds.data_ptr<int>());
+    args_.call = reinterpret_cast<unsigned int*>(call.data_ptr<int>());
+  }
+  const dlv::GemmTpArgs* args() const { return &args_; }
+
+ private:
+  dlv::GemmTpArgs args_;
+  Tensor rounds_, call_;
+};
+
 // ---- GEMM weight handle -------------------------------------------------------------------------------------------
 class GemmWeight {
  public:
@@ -114,6 +145,27 @@ class GemmWeight {
     }
     check_last_error("gemm launch");
     return out;
+  }
+  // Row-parallel projection fused with the tensor-parallel sum: every rank calls this with its K-shard; `out` holds the
+  // all-reduced result on every rank. Returns false (nothing launched) when the shape is outside the fused path.
+  bool run_tp(const Tensor& x, Tensor& out, const TpComm& comm, c10::optional<Tensor> bias) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(1) == desc_.K && x.stride(1) == 1, "x must be bf16 [M, K]");
+    TORCH_CHECK(x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x rows must be 16-byte aligned");
+    const int M = static_cast<int>(x.size(0));
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == M && out.size(1) == desc_.N && out.stride(1) == 1, "bad out");
+    if (!dlv::gemm_tp_supported(&desc_, M, comm.args())) return false;
+    const float* bptr = nullptr;
+    if (bias.has_value()) {
+      TORCH_CHECK(bias.value().is_cuda() && bias.value().scalar_type() == at::kFloat && bias.value().numel() == desc_.N, "bias must be fp32 [N]");
+      bptr = bias.value().data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    DeviceScratch& s = scratch_for(x.device().index());
+    dlv::gemm_tc_run(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), out.data_ptr(), static_cast<int>(out.stride(0)), false, bptr,
+                     s.ws.data_ptr<float>(), static_cast<size_t>(s.ws.numel()), s.counters.data_ptr<int>(),
+                     static_cast<int>(s.counters.numel()), s.status.data_ptr<int>(), 0, cur_stream(), comm.args());
+    check_last_error("fused tp gemm launch");
+    return true;
   }
   int64_t n() const { return desc_.N; }
   int64_t k() const { return desc_.K; }
@@ -426,10 +478,13 @@ Tensor q4_dequantize(const Tensor& packed, const Tensor& scales, bool to_bf16) {
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  py::class_<TpComm, std::shared_ptr<TpComm>>(m, "TpComm")
+      .def(py::init<int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t, Tensor, Tensor>());
   py::class_<GemmWeight, std::shared_ptr<GemmWeight>>(m, "GemmWeight")
       .def(py::init<Tensor, bool, int64_t, int64_t>(), py::arg("w"), py::arg("is_q4"), py::arg("N"), py::arg("K"))
       .def("run", &GemmWeight::run, py::arg("x"), py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("out_f32") = false,
            py::arg("impl") = 0, py::arg("force_splits") = 0)
+      .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
       .def_property_readonly("N", &GemmWeight::n)
       .def_property_readonly("K", &GemmWeight::k)
       .def_property_readonly("is_q4", &GemmWeight::is_q4);

@@ -114,7 +114,7 @@ static int cluster_capacity(int size) {
 
 template <bool Q4, int BN>
 static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmParams p, float* ws, size_t ws_floats, int* counters,
-                   int n_counters, int force_splits, cudaStream_t st) {
+                   int n_counters, int force_splits, cudaStream_t st, const GemmTpArgs* tp) {
   using L = GemmSmem<Q4, BN>;
   p.n_tiles = (w->N + kGemmBM - 1) / kGemmBM;
   p.m_tiles = (M + BN - 1) / BN;
@@ -131,6 +131,7 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
       if (s > 1 && p.kb_total / s < 2) break;
       const int cap = cluster_capacity<Q4, BN>(s);
       if (cap <= 0) continue;
+      if (tp != nullptr && tp->size > 1 && (tiles > cap || tiles * s > tp->ncta_max)) continue;  // fused all-reduce: one wave
       const int waves = (tiles + cap - 1) / cap;
       const int kb = (p.kb_total + s - 1) / s;
       const double per_kb = 0.22 * (BN > 64 ? BN / 64.0 : 1.0);
@@ -154,6 +155,25 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
     }
   }
   (void)cluster_capacity<Q4, BN>(1);  // sets the shared-memory attribute
+  if (tp != nullptr && tp->size > 1) {
+    // fused all-reduce: partial tiles must come from a single split or a cluster, and the grid must be resident at once
+    if (splits > 1 && !cluster) {
+      splits = 1;
+      p.kb_per_split = p.kb_total;
+    }
+    const int cap = cluster_capacity<Q4, BN>(splits > 1 ? splits : 1);
+    if (tiles > cap || tiles * splits > tp->ncta_max) throw std::runtime_error("fused tensor-parallel GEMM: grid does not fit in one wave");
+    p.tp_size = tp->size;
+    p.tp_rank = tp->rank;
+    p.tp_ncta_max = tp->ncta_max;
+    p.tp_slab = tp->slab;
+    for (int r = 0; r < 8; ++r) {
+      p.tp_recv[r] = tp->recv[r];
+      p.tp_flags[r] = tp->flags[r];
+    }
+    p.tp_rounds = tp->rounds;
+    p.tp_call = tp->call;
+  }
   p.splits = splits;
   p.cluster_reduce = cluster ? 1 : 0;
   p.ws = ws;
@@ -188,8 +208,18 @@ static int pick_bn(int M) {
   return 256;
 }
 
+bool gemm_tp_supported(const GemmWeightDesc* w, int M, const GemmTpArgs* tp) {
+  if (tp == nullptr || tp->size <= 1 || tp->size > 8) return false;
+  if (w->N % 4 != 0 || M <= 0 || M > 128) return false;
+  if (static_cast<long long>(M) * w->N > tp->slab) return false;
+  const int BN = pick_bn(M);
+  const int tiles = ((w->N + kGemmBM - 1) / kGemmBM) * ((M + BN - 1) / BN);
+  return tiles <= gemm_num_sms() && tiles <= tp->ncta_max;
+}
+
 void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
-                 float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st) {
+                 float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st,
+                 const GemmTpArgs* tp) {
   if (M <= 0) return;
   if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
   const int BN = pick_bn(M);
@@ -205,8 +235,8 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
   p.status = status;
   p.trace = g_gemm_trace;
 #define DLV_LAUNCH(BNV)                                                                              \
-  if (w->is_q4) run_tc<true, BNV>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, force_splits, st); \
-  else run_tc<false, BNV>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, force_splits, st)
+  if (w->is_q4) run_tc<true, BNV>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, force_splits, st, tp); \
+  else run_tc<false, BNV>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, force_splits, st, tp)
   switch (BN) {
     case 16: DLV_LAUNCH(16); break;
     case 32: DLV_LAUNCH(32); break;

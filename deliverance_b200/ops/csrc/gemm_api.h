@@ -20,11 +20,25 @@ struct GemmWeightDesc {
   CUtensorMap map_w;           // dense only
 };
 
+// Peer-memory state of the fused GEMM + all-reduce epilogue (all pointers are device addresses mapped in this process).
+struct GemmTpArgs {
+  int size = 1, rank = 0;
+  int ncta_max = 0;              // flag matrix row length
+  long long slab = 0;            // bf16 elements per (parity, source) receive slab
+  unsigned long long recv[8];    // receive area of every rank
+  unsigned long long flags[8];   // flag matrix of every rank
+  unsigned int* rounds = nullptr;  // local [ncta_max]
+  unsigned int* call = nullptr;    // local [2]
+};
+
 void gemm_weight_init(GemmWeightDesc* w);
 int gemm_num_sms();
 void gemm_set_trace(unsigned long long* p);  // debug: device buffer of 16 u64 that CTA (0,0,0) stamps with globaltimer
 void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
-                 float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st);
+                 float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st,
+                 const GemmTpArgs* tp = nullptr);
+// true when the fused all-reduce epilogue can take this problem (one wave of CTAs, rows and columns inside the slab)
+bool gemm_tp_supported(const GemmWeightDesc* w, int M, const GemmTpArgs* tp);
 void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
                    cudaStream_t st);
 

@@ -17,6 +17,14 @@
 // peers' partials through distributed shared memory in a fixed order (deterministic), then writes the final output.
 // A global-memory workspace + last-arriver reduction remains as the fallback when clusters cannot be scheduled.
 //
+// Tensor-parallel fusion (row-parallel o_proj / down_proj, decode batches): instead of writing its tile to the output, a
+// CTA stores its partial sums as bf16 straight into the receive area of EVERY rank (plain peer stores over NVLink, own rank
+// included), publishes them with one release-add per rank on that rank's flag matrix, waits (bounded) until all ranks have
+// published the same tile to it, and only then sums the tp_size partials in rank order and writes the final output: GEMM
+// and one-shot all-reduce are one kernel, and the transfer of finished tiles overlaps the math of the others. Receive
+// areas are double-buffered on the parity of a per-rank launch counter; flags are cumulative, so CUDA-graph replays need
+// no host-side reset.
+//
 // Roles per CTA (608 threads): warp 0 = weight producer (bulk copy / TMA), warp 1 = TMEM owner + MMA issuer,
 // warp 2 = activation TMA producer, warps 3..18 = JQ4 dequant (one 32-element block per thread and stage) and epilogue
 // (tcgen05.ld -> fp32 tile in shared memory -> reduce over the cluster -> 8/16-byte global stores).
@@ -52,6 +60,14 @@ struct GemmParams {
   float* ws;          // fallback split-K partials: [tile][split][BN][128] fp32
   int* counters;      // fallback: one per tile, zero between launches (the reducing CTA resets its counter)
   int* status;        // kernel status word (0 = ok)
+  // ---- fused tensor-parallel all-reduce (tp_size > 1): see the epilogue ----
+  int tp_size, tp_rank;
+  int tp_ncta_max;                 // row length of the flag matrix
+  long long tp_slab;               // elements per (parity, source) slab of the receive area
+  unsigned long long tp_recv[8];   // every rank's receive area (bf16 [2][tp_size][slab]), peer-mapped
+  unsigned long long tp_flags[8];  // every rank's flag matrix (u32 [tp_size][tp_ncta_max], cumulative counters)
+  unsigned int* tp_rounds;         // local: how many fused calls each CTA index has completed
+  unsigned int* tp_call;           // local: [0] = number of fused launches completed, [1] = CTAs done in this launch
   unsigned long long* trace;  // optional: 16 globaltimer stamps of CTA (0,0,0) (nullptr in production)
 };
 
@@ -390,60 +406,130 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       if (*s_last) __threadfence();
     }
     const bool do_store = p.splits == 1 || p.cluster_reduce || *s_last;
-    if (do_store) {
-      const uint32_t me = clustered ? cluster_ctarank() : 0u;
-      const int stride = clustered ? p.splits : 1;
-      float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (p.bias != nullptr) {
-        bias.x = n + 0 < p.N ? p.bias[n + 0] : 0.f;
-        bias.y = n + 1 < p.N ? p.bias[n + 1] : 0.f;
-        bias.z = n + 2 < p.N ? p.bias[n + 2] : 0.f;
-        bias.w = n + 3 < p.N ? p.bias[n + 3] : 0.f;
+    const bool fused_tp = p.tp_size > 1;
+    const uint32_t me = clustered ? cluster_ctarank() : 0u;
+    const int stride = clustered ? p.splits : 1;
+    const bool vec_ok = (n + 3 < p.N) && ((p.ldo & 3) == 0);
+    // reduced (over split-K) accumulator of column `col`, rows row4 .. row4+3
+    auto column_acc = [&](int col) -> float4 {
+      float4 acc;
+      if (clustered) {
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const uint32_t a = stage_addr + static_cast<uint32_t>((col * kGemmBM + row4) * 4);
+        for (int sp = 0; sp < p.splits; ++sp) {
+          const float4 v = ld_dsmem_f32x4(a, static_cast<uint32_t>(sp));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+      } else if (p.splits > 1) {
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* base = p.ws + static_cast<size_t>(m_tile * p.n_tiles + n_tile) * p.splits * (BN * kGemmBM);
+        for (int sp = 0; sp < p.splits; ++sp) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (static_cast<size_t>(sp) * BN + col) * kGemmBM + row4));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+      } else {
+        acc = *reinterpret_cast<const float4*>(stage + col * kGemmBM + row4);
       }
-      const bool vec_ok = (n + 3 < p.N) && ((p.ldo & 3) == 0);
+      return acc;
+    };
+    auto store_out = [&](int m, float4 acc) {
+      const size_t o = static_cast<size_t>(m) * p.ldo + n;
+      if (vec_ok) {
+        if (p.out_f32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o) = acc;
+        else {
+          uint2 pk;
+          pk.x = pack_bf162(acc.x, acc.y);
+          pk.y = pack_bf162(acc.z, acc.w);
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
+        }
+      } else {
+        const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+        for (int e = 0; e < 4; ++e) {
+          if (n + e < p.N) {
+            if (p.out_f32) reinterpret_cast<float*>(p.out)[o + e] = vals[e];
+            else reinterpret_cast<__nv_bfloat16*>(p.out)[o + e] = f2bf(vals[e]);
+          }
+        }
+      }
+    };
+    float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p.bias != nullptr) {
+      bias.x = n + 0 < p.N ? p.bias[n + 0] : 0.f;
+      bias.y = n + 1 < p.N ? p.bias[n + 1] : 0.f;
+      bias.z = n + 2 < p.N ? p.bias[n + 2] : 0.f;
+      bias.w = n + 3 < p.N ? p.bias[n + 3] : 0.f;
+    }
+    if (do_store && !fused_tp) {
       // column c of the tile is finished by cluster rank c % splits; the 16 column slots of this CTA take turns
       for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
         const int m = m0 + col;
         if (m >= p.M) break;
-        float4 acc;
-        if (clustered) {
-          acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          const uint32_t a = stage_addr + static_cast<uint32_t>((col * kGemmBM + row4) * 4);
-          for (int sp = 0; sp < p.splits; ++sp) {
-            const float4 v = ld_dsmem_f32x4(a, static_cast<uint32_t>(sp));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-          }
-        } else if (p.splits > 1) {
-          acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          const float* base = p.ws + static_cast<size_t>(m_tile * p.n_tiles + n_tile) * p.splits * (BN * kGemmBM);
-          for (int sp = 0; sp < p.splits; ++sp) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (static_cast<size_t>(sp) * BN + col) * kGemmBM + row4));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-          }
-        } else {
-          acc = *reinterpret_cast<const float4*>(stage + col * kGemmBM + row4);
-        }
+        float4 acc = column_acc(col);
         acc.x += bias.x; acc.y += bias.y; acc.z += bias.z; acc.w += bias.w;
-        const size_t o = static_cast<size_t>(m) * p.ldo + n;
-        if (vec_ok) {
-          if (p.out_f32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o) = acc;
-          else {
-            uint2 pk;
-            pk.x = pack_bf162(acc.x, acc.y);
-            pk.y = pack_bf162(acc.z, acc.w);
-            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
-          }
-        } else {
-          const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
-          for (int e = 0; e < 4; ++e) {
-            if (n + e < p.N) {
-              if (p.out_f32) reinterpret_cast<float*>(p.out)[o + e] = vals[e];
-              else reinterpret_cast<__nv_bfloat16*>(p.out)[o + e] = f2bf(vals[e]);
-            }
-          }
-        }
+        store_out(m, acc);
       }
       if (p.splits > 1 && !p.cluster_reduce && t == 0) p.counters[m_tile * p.n_tiles + n_tile] = 0;
+    }
+    if (fused_tp) {
+      // ---- GEMM + one-shot all-reduce over peer memory (host guarantees: N % 4 == 0, cluster or single split) ----
+      const unsigned cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+      const unsigned call = *reinterpret_cast<volatile unsigned*>(p.tp_call);
+      const long long par_off = static_cast<long long>(call & 1u) * p.tp_size * p.tp_slab;
+      // phase A: partial sums -> every rank's receive slab [parity][my rank]
+      if (n + 3 < p.N) {
+        for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
+          const int m = m0 + col;
+          if (m >= p.M) break;
+          const float4 acc = column_acc(col);
+          uint2 pk;
+          pk.x = pack_bf162(acc.x, acc.y);
+          pk.y = pack_bf162(acc.z, acc.w);
+          const long long off = par_off + static_cast<long long>(p.tp_rank) * p.tp_slab + static_cast<long long>(m) * p.N + n;
+          for (int r = 0; r < p.tp_size; ++r)
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.tp_recv[(p.tp_rank + r) % p.tp_size]) + off) = pk;
+        }
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      if (t == 0) {
+        for (int r = 0; r < p.tp_size; ++r) {
+          const int dst = (p.tp_rank + r) % p.tp_size;
+          red_release_sys_add(reinterpret_cast<uint32_t*>(p.tp_flags[dst]) + static_cast<size_t>(p.tp_rank) * p.tp_ncta_max + cta_id, 1u);
+        }
+        // phase B gate: every rank has published this CTA's region for this call
+        const unsigned round = p.tp_rounds[cta_id];
+        bool all = true;
+        const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.tp_flags[p.tp_rank]);
+        for (int src = 0; src < p.tp_size && all; ++src)
+          all = flag_wait_ge(mine + static_cast<size_t>(src) * p.tp_ncta_max + cta_id, round + 1u, p.status);
+        p.tp_rounds[cta_id] = round + 1u;
+        *s_last = all ? 1 : 0;
+      }
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      if (*s_last && n + 3 < p.N) {
+        const __nv_bfloat16* rbase = reinterpret_cast<const __nv_bfloat16*>(p.tp_recv[p.tp_rank]) + par_off;
+        for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
+          const int m = m0 + col;
+          if (m >= p.M) break;
+          float4 acc = bias;
+          for (int src = 0; src < p.tp_size; ++src) {
+            const uint2 pk = __ldcg(reinterpret_cast<const uint2*>(rbase + static_cast<long long>(src) * p.tp_slab + static_cast<long long>(m) * p.N + n));
+            const float2 a = unpack_bf162(pk.x), b = unpack_bf162(pk.y);
+            acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+          }
+          store_out(m, acc);
+        }
+      }
+      // launch bookkeeping: the last CTA of the grid to get here advances the launch counter (flips the parity)
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      if (t == 0) {
+        const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(p.tp_call + 1, 1u) == total - 1u) {
+          p.tp_call[1] = 0u;
+          __threadfence();
+          p.tp_call[0] = call + 1u;
+        }
+      }
     }
   }
   if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(7);

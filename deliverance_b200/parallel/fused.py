@@ -1,0 +1,74 @@
+"""Fused tensor-parallel paths over NVLink peer memory.
+
+``FusedTensorParallel`` owns one symmetric allocation per rank (``torch.distributed._symmetric_memory``: CUDA virtual-memory
+handles exchanged between the ranks of one node, every rank's buffer mapped into every process) that holds the receive
+slabs and the flag matrix used by the GEMM kernel's all-reduce epilogue (csrc/gemm_tc.cuh). ``linear_all_reduce`` replaces
+the reference's ``allReduceSum`` round trip through a central HTTP/TCP server after ``o_proj`` and ``down_proj``
+(core/.../generator/CausalSelfAttention.java:403-405,448-452; core/.../model/tensorparallel/TensorParallelMlp.java:169-171)
+with peer stores issued from inside the GEMM epilogue; shapes outside the fused path (prefill-size batches, grids larger
+than one wave) fall back to the GEMM followed by the NCCL all-reduce.
+
+Plain peer loads/stores only: no NVLS multimem and no TMA multicast, so a rank that leaves between steps cannot fault the
+others through a multicast binding.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .context import TensorParallelContext
+
+NCTA_MAX = 1024
+
+
+class FusedTensorParallel:
+    def __init__(self, tp: TensorParallelContext, device, max_rows: int = 128, max_cols: int = 8192):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.tp = tp
+        self.device = torch.device(device)
+        self.slab = max_rows * max_cols
+        recv_bytes = 2 * tp.size * self.slab * 2
+        flag_bytes = tp.size * NCTA_MAX * 4
+        self.recv_bytes = recv_bytes
+        total = recv_bytes + flag_bytes
+        self.buf = symm.empty(total, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm.rendezvous(self.buf, dist.group.WORLD)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.rounds = torch.zeros(NCTA_MAX, dtype=torch.int32, device=self.device)
+        self.call = torch.zeros(2, dtype=torch.int32, device=self.device)
+        e = ops.require_ext()
+        self.comm = e.TpComm(tp.rank, tp.size, ptrs, [p + recv_bytes for p in ptrs], self.slab, NCTA_MAX, self.rounds, self.call)
+        dist.barrier()
+        torch.cuda.synchronize(self.device)
+        self.stats = {"fused": 0, "fallback": 0}
+
+    @staticmethod
+    def create(tp: TensorParallelContext, device) -> "FusedTensorParallel":
+        if tp.size < 2 or tp.size > 8:
+            raise ValueError("fused tensor parallelism needs 2..8 ranks on one node")
+        return FusedTensorParallel(tp, device)
+
+    def linear_all_reduce(self, x: torch.Tensor, w, key: str) -> torch.Tensor:
+        """``all_reduce_sum(x @ W_shard^T)`` with the sum fused into the GEMM epilogue when the shape allows it."""
+        out = torch.empty(x.shape[0], w.N, dtype=torch.bfloat16, device=x.device)
+        bias = w.bias  # added once, after the sum, by the reducing epilogue of every rank
+        if x.shape[0] > 0 and w.handle().run_tp(x, out, self.comm, bias):
+            ops._count()
+            self.stats["fused"] += 1
+            return out
+        self.stats["fallback"] += 1
+        y = ops.linear(x, w) if self.tp.rank == 0 or w.bias is None else ops.linear(x, _no_bias(w))
+        return self.tp.collectives.all_reduce_sum(key, y)
+
+
+def _no_bias(w):
+    import copy
+
+    c = copy.copy(w)
+    c.bias = None
+    c._handle = w._handle
+    return c

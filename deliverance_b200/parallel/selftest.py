@@ -1,0 +1,176 @@
+"""Multi-GPU self-test of the tensor-parallel paths; run one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29511 \
+        -m deliverance_b200.parallel.selftest [--bench]
+
+Checks (1) the fused GEMM + all-reduce epilogue against an fp32 reference built from all-gathered shards, over decode
+batch sizes, JQ4 and dense weights, repeated launches and a captured CUDA graph; (2) greedy tokens of a tensor-parallel
+Qwen3-shaped model against the same model on one GPU; with ``--bench`` it also times fused vs GEMM + NCCL all-reduce
+(device time, max over ranks) and prints the fraction of the NVLink roofline. Rank 0 prints one JSON line per check.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--bench", action="store_true")
+    a = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from deliverance_b200 import ops
+    from deliverance_b200.ckpt.jq4 import q4_dequantize, q4_quantize
+    from deliverance_b200.ckpt.safetensors_io import Q4Tensor
+    from deliverance_b200.ops import LinearWeight
+    from deliverance_b200.parallel.context import TensorParallelContext, TorchCollectives
+    from deliverance_b200.parallel.fused import FusedTensorParallel
+
+    tp = TensorParallelContext(rank, world, TorchCollectives())
+    fused = FusedTensorParallel.create(tp, dev)
+    ok_all = True
+
+    def report(**kw):
+        if rank == 0:
+            print(json.dumps(kw), flush=True)
+
+    # ---------------------------------------------------------------- (1) fused linear + all-reduce numerics
+    for (N, Kfull, q4) in [(2560, 4096, True), (2560, 9728 // 2 * 2 if world != 8 else 9728, True), (1024, 2048, False)]:
+        Kfull = (Kfull // (32 * world)) * 32 * world
+        Ks = Kfull // world
+        g = torch.Generator().manual_seed(100 + N + Kfull)
+        wfull = torch.randn(N, Kfull, generator=g) * 0.05
+        wsh = wfull[:, rank * Ks : (rank + 1) * Ks].contiguous()
+        if q4:
+            p, s = q4_quantize(wsh)
+            lw = LinearWeight(Q4Tensor(p, s, (N, Ks))).to(dev)
+            wref = q4_dequantize(p, s)
+        else:
+            lw = LinearWeight(wsh.to(torch.bfloat16)).to(dev, torch.bfloat16)
+            wref = wsh.to(torch.bfloat16).float()
+        for M in (1, 8, 64, 100):
+            xfull = (torch.randn(M, Kfull, generator=g) * 0.5).to(torch.bfloat16)
+            x = xfull[:, rank * Ks : (rank + 1) * Ks].contiguous().to(dev)
+            part = (x.float().cpu() @ wref.t()).to(dev)
+            dist.all_reduce(part)
+            ys = [fused.linear_all_reduce(x, lw, "t") for _ in range(3)]
+            torch.cuda.synchronize()
+            ops.check_status(local)
+            err = max(((y.float() - part).norm() / part.norm()).item() for y in ys)
+            same = all(torch.equal(ys[0], y) for y in ys[1:])
+            gathered = [torch.empty_like(ys[0]) for _ in range(world)]
+            dist.all_gather(gathered, ys[0])
+            identical = all(torch.equal(gathered[0], t) for t in gathered)
+            good = err < 2e-2 and same and identical
+            ok_all &= good
+            report(check="fused_linear_all_reduce", N=N, K=Kfull, M=M, q4=q4, rel_err=err, repeatable=same, ranks_identical=identical, ok=good)
+    # CUDA graph capture of two fused calls back to back (parity flips between them)
+    x = (torch.randn(16, lw.K, device=dev) * 0.5).to(torch.bfloat16)
+    ref = fused.linear_all_reduce(x, lw, "g").clone()
+    gr = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fused.linear_all_reduce(x, lw, "g")
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    dist.barrier()
+    with torch.cuda.graph(gr):
+        y1 = fused.linear_all_reduce(x, lw, "g")
+        y2 = fused.linear_all_reduce(x, lw, "g")
+    for _ in range(5):
+        gr.replay()
+    torch.cuda.synchronize()
+    ops.check_status(local)
+    good = torch.equal(y1, ref) and torch.equal(y2, ref)
+    ok_all &= good
+    report(check="fused_in_cuda_graph", ok=good, fused_calls=fused.stats["fused"], fallback_calls=fused.stats["fallback"])
+
+    # ---------------------------------------------------------------- (2) tensor-parallel model vs single GPU
+    from deliverance_b200.ckpt.synthetic import SyntheticLoader
+    from deliverance_b200.config import parse_config
+    from deliverance_b200.engine.engine import Engine, EngineConfig
+    from deliverance_b200.models.transformer import DecoderModel
+    from deliverance_b200.params import GeneratorParameters
+
+    shape = dict(model_type="qwen3", vocab_size=4096, hidden_size=1024, intermediate_size=2048 * 2, num_hidden_layers=3,
+                 num_attention_heads=16, num_key_value_heads=8, head_dim=128, max_position_embeddings=1024, rms_norm_eps=1e-6,
+                 rope_theta=1e6, tie_word_embeddings=True)
+    cfg = parse_config(dict(shape))
+    prompts = [torch.randint(0, 4096, (n,), generator=torch.Generator().manual_seed(5 + n)).tolist() for n in (70, 33, 129)]
+    results = {}
+    for name, ctx in (("single", TensorParallelContext()), ("tp_nccl", TensorParallelContext(rank, world, TorchCollectives())), ("tp_fused", tp)):
+        if name == "tp_fused":
+            ctx.fused = fused
+        model = DecoderModel(cfg, dev, torch.bfloat16, ctx).load(SyntheticLoader(shape, 3, True, dev, std=0.05), head_quant="Q4")
+        ec = EngineConfig(num_pages=256, cuda_graphs=True)
+        ec.kv.enabled = False
+        eng = Engine(model, ec, eos_ids=(-1,))
+        rs = eng.generate_batch(prompts, GeneratorParameters(max_tokens=12))
+        results[name] = [r.token_ids for r in rs]
+        torch.cuda.synchronize()
+        ops.check_status(local)
+        dist.barrier()
+    agree_nccl = sum(a == b for a, b in zip(results["single"], results["tp_nccl"]))
+    agree_fused = sum(a == b for a, b in zip(results["single"], results["tp_fused"]))
+    first_tok = all(a[0] == b[0] for a, b in zip(results["single"], results["tp_fused"]))
+    # bf16 partial sums are rounded per rank, so long greedy continuations may diverge; the first tokens must agree
+    good = first_tok
+    ok_all &= good
+    report(check="tp_model_tokens", sequences=len(prompts), equal_nccl=agree_nccl, equal_fused=agree_fused, first_token_equal=first_tok, ok=good,
+           fused_calls=fused.stats["fused"], fallback_calls=fused.stats["fallback"])
+
+    # ---------------------------------------------------------------- (3) timing
+    if a.bench:
+        N, Kfull = 2560, 9728 // (32 * world) * 32 * world
+        Ks = Kfull // world
+        copies = []
+        for c in range(24):
+            w = torch.randn(N, Ks, device=dev) * 0.02
+            p, s = ops.q4_quantize(w)
+            copies.append(LinearWeight(Q4Tensor(p, s, (N, Ks))).to(dev))
+        for M in (1, 8, 64):
+            x = (torch.randn(M, Ks, device=dev) * 0.5).to(torch.bfloat16)
+            res = {}
+            for mode in ("fused", "gemm+nccl"):
+                def run(i):
+                    if mode == "fused":
+                        return fused.linear_all_reduce(x, copies[i % 24], "b")
+                    y = ops.linear(x, copies[i % 24])
+                    dist.all_reduce(y)
+                    return y
+                for i in range(24):
+                    run(i)
+                torch.cuda.synchronize()
+                dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(48):
+                    run(i)
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) * 1e3 / 48], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                res[mode] = t.item()
+            # roofline: slower of weight bytes at the measured HBM rate and bytes this GPU must send over NVLink at 770 GB/s
+            hbm_us = N * Ks * 0.5625 / 6454.3e3
+            nvl_us = (world - 1) * M * N * 2 / 770e3
+            roof = max(hbm_us, nvl_us)
+            report(check="bench_linear_all_reduce", world=world, M=M, N=N, K_per_rank=Ks, fused_us=res["fused"], gemm_nccl_us=res["gemm+nccl"],
+                   roofline_us=roof, fused_frac_of_roofline=roof / res["fused"], speedup_vs_nccl=res["gemm+nccl"] / res["fused"])
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0 if ok_all else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

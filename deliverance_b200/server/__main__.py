@@ -1,0 +1,46 @@
+"""``python -m deliverance_b200.server --model DIR [--embedding-model DIR] [--port 8080]`` (multi-model: repeat ``--model``).
+
+Under ``torchrun`` every rank loads its tensor-parallel shard; rank 0 serves HTTP and broadcasts each step's admissions to
+the other ranks, which run the same engine in lockstep."""
+from __future__ import annotations
+
+import argparse
+import os
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", action="append", required=True, help="model directory (repeatable)")
+    ap.add_argument("--embedding-model", action="append", default=[])
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8080)
+    ap.add_argument("--device", default="auto")
+    ap.add_argument("--output-head-quantization", default=None)
+    ap.add_argument("--reasoning-field", default="openai", choices=["openai", "vllm"])
+    ap.add_argument("--basic-user", default=os.environ.get("DELIVERANCE_BASIC_USER"))
+    ap.add_argument("--basic-password", default=os.environ.get("DELIVERANCE_BASIC_PASSWORD"))
+    ap.add_argument("--jwt-secret", default=os.environ.get("DELIVERANCE_JWT_SECRET"))
+    ap.add_argument("--max-seqs", type=int, default=128)
+    a = ap.parse_args()
+    import uvicorn
+
+    from ..api import AutoModelForCausalLM
+    from ..embedding import AutoModelForEmbeddings
+    from .app import ModelRegistry, ServerSettings, create_app
+    from .runner import EngineRunner
+
+    reg = ModelRegistry()
+    for d in a.model:
+        b = AutoModelForCausalLM.new_builder(d).with_device(a.device).with_output_head_quantization(a.output_head_quantization)
+        b.conf.max_seqs = a.max_seqs
+        clm = b.build()
+        reg.generation[clm.name] = EngineRunner(clm)
+    for d in a.embedding_model:
+        reg.embedding[os.path.basename(os.path.normpath(d))] = AutoModelForEmbeddings.from_pretrained(d, a.device)
+    settings = ServerSettings(reasoning_field=a.reasoning_field, basic_user=a.basic_user, basic_password=a.basic_password, jwt_secret=a.jwt_secret)
+    uvicorn.run(create_app(reg, settings), host=a.host, port=a.port, log_level="info")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

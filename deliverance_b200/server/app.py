@@ -1,0 +1,385 @@
+"""OpenAI-style HTTP API.
+
+Endpoints and payloads follow the reference's Spring controllers (web/src/main/java/net/deliverance/http/):
+``POST /chat/completions`` (ChatCompletionController.java:234-443, request mapping ChatCompletionService.java:17-128),
+``POST /v1/completions`` + ``/completions`` (:99-232), ``POST /embeddings`` (EmbeddingController.java:38-53),
+``GET /models`` (ModelController.java:26-46), ``GET /tp/status`` (TensorParallelDiagnosticsController.java:22-40).
+Streaming is SSE with ``X-Deliverance-Session``, comment heartbeats every second that also detect a closed client and cancel
+the generation, ``content`` / reasoning deltas (field ``reasoning_content`` in openai mode, ``reasoning`` in vllm mode),
+tool-call deltas after generation with content buffered while tools are present, a final chunk with ``finish_reason`` and
+``data: [DONE]``. Optional HTTP Basic / JWT (HS256) auth on ``/chat``, ``/embeddings``, ``/models``
+(auth/SecurityConfig.java:30-71). ``guided_choice`` is accepted here as well (the reference maps only regex / json).
+"""
+from __future__ import annotations
+
+import asyncio
+import base64
+import hashlib
+import hmac
+import json
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional
+
+from fastapi import Request  # module level: handler annotations are resolved from the module namespace
+
+from ..params import FinishReason, GeneratorParameters, Response
+from ..prompt.parsers import ReasoningTextSplitter
+from .runner import EngineRunner
+
+
+@dataclass
+class ServerSettings:
+    reasoning_field: str = "openai"  # openai -> reasoning_content, vllm -> reasoning
+    basic_user: Optional[str] = None
+    basic_password: Optional[str] = None
+    jwt_secret: Optional[str] = None
+    heartbeat_s: float = 1.0
+    request_timeout_s: float = 600.0
+    pre_generate: Optional[Callable[[dict, GeneratorParameters], Optional[str]]] = None  # may rewrite or reject (return error text)
+
+    @property
+    def reasoning_key(self) -> str:
+        return "reasoning" if self.reasoning_field == "vllm" else "reasoning_content"
+
+
+@dataclass
+class ModelRegistry:
+    generation: dict = field(default_factory=dict)  # name -> EngineRunner
+    embedding: dict = field(default_factory=dict)  # name -> EmbeddingModel
+    tp_status: Callable[[], dict] = lambda: {"enabled": False, "size": 1, "rank": 0}
+
+    def find(self, name: Optional[str]) -> EngineRunner:
+        if not self.generation:
+            raise KeyError("no generation model is loaded")
+        if name in self.generation:
+            return self.generation[name]
+        if name is None or name == "":
+            return next(iter(self.generation.values()))
+        raise KeyError(f"model '{name}' is not loaded (available: {', '.join(self.generation)})")
+
+
+def map_chat_request(body: dict, runner: EngineRunner):
+    """Request JSON -> (PromptContext, GeneratorParameters)."""
+    clm = runner.clm
+    msgs = body.get("messages")
+    if not isinstance(msgs, list) or not msgs:
+        raise ValueError("'messages' must be a non-empty list")
+    b = clm.prompt_builder().with_template(body.get("chat_template")).with_kwargs(body.get("chat_template_kwargs"))
+    for m in msgs:
+        role = m.get("role")
+        content = m.get("content")
+        if isinstance(content, list):  # text parts
+            content = "".join(p.get("text", "") for p in content if isinstance(p, dict) and p.get("type", "text") == "text")
+        content = content or ""
+        if role == "system":
+            b.add_system(content)
+        elif role == "user":
+            b.add_user(content)
+        elif role == "assistant":
+            b.add_assistant(content, m.get("tool_calls"))
+        elif role == "tool":
+            b.add_tool_result(m.get("tool_call_id"), content, m.get("name"))
+        else:
+            raise ValueError(f"unsupported message role '{role}'")
+    b.add_tools(body.get("tools"))
+    return b.build(), map_params(body)
+
+
+def map_params(body: dict) -> GeneratorParameters:
+    p = GeneratorParameters()
+    if body.get("temperature") is not None:
+        p.temperature = float(body["temperature"])
+    for src, dst in (("top_p", "top_p"), ("top_k", "top_k"), ("uniform_top_p", "uniform_top_p"), ("xtc_threshold", "xtc_threshold"),
+                     ("xtc_probability", "xtc_probability")):
+        if body.get(src) is not None:
+            setattr(p, dst, float(body[src]))
+    if body.get("max_tokens") is not None:
+        p.max_tokens = int(body["max_tokens"])
+    if body.get("ntokens") is not None:
+        p.ntokens = int(body["ntokens"])
+    if body.get("seed") is not None:
+        p.seed = int(body["seed"])
+    stop = body.get("stop")
+    if isinstance(stop, str):
+        p.stop_words = [stop]
+    elif isinstance(stop, list):
+        p.stop_words = [str(s) for s in stop]
+    p.logprobs = bool(body.get("logprobs", False))
+    p.top_logprobs = int(body.get("top_logprobs") or 0)
+    p.guided_regex = body.get("guided_regex")
+    p.guided_json = body.get("guided_json")
+    p.guided_choice = body.get("guided_choice")
+    p.cache_salt = str(body.get("cache_salt") or "")
+    p.validate()
+    return p
+
+
+def _finish(r: Response) -> str:
+    return r.finish_reason.wire if r.finish_reason not in (FinishReason.ERROR, FinishReason.CANCELLED) else "stop"
+
+
+def _tool_calls_json(r: Response) -> list[dict]:
+    return [{"id": c.id, "type": c.type, "function": {"name": c.name, "arguments": c.arguments if isinstance(c.arguments, str) else json.dumps(c.arguments)}}
+            for c in r.tool_calls]
+
+
+def _logprobs_json(r: Response) -> Optional[dict]:
+    if not r.sampler_returns:
+        return None
+    return {"content": [{"token": lp.token, "logprob": lp.logprob, "bytes": list(lp.token.encode("utf-8")),
+                         "top_logprobs": [{"token": t.token, "logprob": t.logprob, "bytes": list(t.token.encode("utf-8"))} for t in lp.top]}
+                        for lp in r.sampler_returns]}
+
+
+def _usage(r: Response) -> dict:
+    return {"prompt_tokens": r.prompt_tokens, "completion_tokens": r.generated_tokens, "total_tokens": r.prompt_tokens + r.generated_tokens}
+
+
+def verify_jwt_hs256(token: str, secret: str) -> bool:
+    try:
+        h, p, s = token.split(".")
+        sig = base64.urlsafe_b64decode(s + "=" * (-len(s) % 4))
+        good = hmac.new(secret.encode(), f"{h}.{p}".encode(), hashlib.sha256).digest()
+        if not hmac.compare_digest(sig, good):
+            return False
+        claims = json.loads(base64.urlsafe_b64decode(p + "=" * (-len(p) % 4)))
+        return not ("exp" in claims and float(claims["exp"]) < time.time())
+    except Exception:  # noqa: BLE001 - any malformed token is simply rejected
+        return False
+
+
+def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = None):
+    from fastapi import FastAPI
+    from fastapi.responses import HTMLResponse, JSONResponse, StreamingResponse
+
+    settings = settings or ServerSettings()
+    app = FastAPI(title="deliverance-b200")
+
+    def error(status: int, message: str):
+        return JSONResponse(status_code=status, content={"error": {"message": message, "type": "invalid_request_error" if status == 400 else "error"}})
+
+    @app.middleware("http")
+    async def auth(request: Request, call_next):
+        path = request.url.path
+        protected = path.startswith(("/chat", "/v1/chat", "/embeddings", "/v1/embeddings", "/models", "/v1/models"))
+        if protected and (settings.basic_user or settings.jwt_secret):
+            hdr = request.headers.get("authorization", "")
+            ok = False
+            if settings.basic_user and hdr.lower().startswith("basic "):
+                try:
+                    user, _, pw = base64.b64decode(hdr[6:]).decode().partition(":")
+                    ok = hmac.compare_digest(user, settings.basic_user) and hmac.compare_digest(pw, settings.basic_password or "")
+                except Exception:  # noqa: BLE001
+                    ok = False
+            if not ok and settings.jwt_secret and hdr.lower().startswith("bearer "):
+                ok = verify_jwt_hs256(hdr[7:].strip(), settings.jwt_secret)
+            if not ok:
+                return JSONResponse(status_code=401, content={"error": {"message": "unauthorized"}}, headers={"WWW-Authenticate": "Basic"})
+        return await call_next(request)
+
+    async def _body(request: Request) -> dict:
+        try:
+            b = await request.json()
+        except Exception:  # noqa: BLE001
+            raise ValueError("request body is not valid JSON")
+        if not isinstance(b, dict):
+            raise ValueError("request body must be a JSON object")
+        return b
+
+    def _sse(obj) -> bytes:
+        return ("data: " + (obj if isinstance(obj, str) else json.dumps(obj, ensure_ascii=False)) + "\n\n").encode("utf-8")
+
+    async def _stream(request: Request, runner: EngineRunner, prompt, params, session: str, make_chunk, final_chunks, has_tools: bool):
+        loop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+
+        def on_event(tok, piece, text_sp, ms):
+            loop.call_soon_threadsafe(q.put_nowait, ("tok", piece))
+
+        def on_done(sub):
+            loop.call_soon_threadsafe(q.put_nowait, ("done", sub))
+
+        sub = runner.submit(prompt, params, on_event, on_done, session)
+        splitter = ReasoningTextSplitter()
+
+        async def gen():
+            try:
+                while True:
+                    try:
+                        kind, val = await asyncio.wait_for(q.get(), timeout=settings.heartbeat_s)
+                    except asyncio.TimeoutError:
+                        if await request.is_disconnected():
+                            sub.cancel()
+                            return
+                        yield b": keep-alive\n\n"
+                        continue
+                    if kind == "tok":
+                        c, r = splitter.accept(val)
+                        if r:
+                            yield _sse(make_chunk({settings.reasoning_key: r}, None))
+                        if c and not has_tools:  # with tools the content is buffered so tool markup never leaks
+                            yield _sse(make_chunk({"content": c}, None))
+                    else:
+                        if val.error is not None:
+                            yield _sse({"error": {"message": str(val.error)}})
+                        else:
+                            c, r = splitter.flush()
+                            if r:
+                                yield _sse(make_chunk({settings.reasoning_key: r}, None))
+                            if c and not has_tools:
+                                yield _sse(make_chunk({"content": c}, None))
+                            for ch in final_chunks(val.response):
+                                yield _sse(ch)
+                        yield _sse("[DONE]")
+                        return
+            finally:
+                if not sub.done.is_set():
+                    sub.cancel()
+
+        return StreamingResponse(gen(), media_type="text/event-stream", headers={"X-Deliverance-Session": session, "Cache-Control": "no-cache"})
+
+    async def chat(request: Request):
+        try:
+            body = await _body(request)
+            runner = registry.find(body.get("model"))
+            prompt, params = map_chat_request(body, runner)
+            if settings.pre_generate is not None:
+                msg = settings.pre_generate(body, params)
+                if msg:
+                    return error(400, msg)
+        except (ValueError, KeyError, TypeError) as e:
+            return error(400, str(e.args[0]) if e.args else str(e))
+        session = request.headers.get("x-deliverance-session") or str(uuid.uuid4())
+        cid, created, model = "chatcmpl-" + uuid.uuid4().hex, int(time.time()), body.get("model") or runner.clm.name
+        if body.get("stream"):
+            first = {"sent": False}
+
+            def make_chunk(delta: dict, finish: Optional[str]):
+                if not first["sent"]:
+                    delta = {"role": "assistant", **delta}
+                    first["sent"] = True
+                return {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model,
+                        "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+
+            def final_chunks(r: Response):
+                out = []
+                if prompt.has_tools:
+                    if r.text:
+                        out.append(make_chunk({"content": r.text}, None))
+                    if r.tool_calls:
+                        out.append(make_chunk({"tool_calls": [{"index": i, **tc} for i, tc in enumerate(_tool_calls_json(r))]}, None))
+                last = make_chunk({}, _finish(r))
+                last["usage"] = _usage(r)
+                out.append(last)
+                return out
+
+            return await _stream(request, runner, prompt, params, session, make_chunk, final_chunks, prompt.has_tools)
+        try:
+            r = await asyncio.get_running_loop().run_in_executor(None, lambda: runner.generate(prompt, params, None, session, settings.request_timeout_s))
+        except Exception as e:  # noqa: BLE001
+            return error(400, str(e))
+        msg: dict[str, Any] = {"role": "assistant", "content": r.text}
+        if r.reasoning:
+            msg[settings.reasoning_key] = r.reasoning
+        if r.tool_calls:
+            msg["tool_calls"] = _tool_calls_json(r)
+        choice = {"index": 0, "message": msg, "finish_reason": _finish(r)}
+        lp = _logprobs_json(r)
+        if lp:
+            choice["logprobs"] = lp
+        return JSONResponse({"id": cid, "object": "chat.completion", "created": created, "model": model, "choices": [choice], "usage": _usage(r)},
+                            headers={"X-Deliverance-Session": session})
+
+    async def completions(request: Request):
+        try:
+            body = await _body(request)
+            runner = registry.find(body.get("model"))
+            prompt = body.get("prompt")
+            if isinstance(prompt, list) and prompt and isinstance(prompt[0], str):
+                prompt = prompt[0]
+            if not isinstance(prompt, str) or not prompt:
+                raise ValueError("'prompt' must be a non-empty string")
+            params = map_params(body)
+        except (ValueError, KeyError, TypeError) as e:
+            return error(400, str(e.args[0]) if e.args else str(e))
+        session = request.headers.get("x-deliverance-session") or str(uuid.uuid4())
+        cid, created, model = "cmpl-" + str(uuid.uuid4()), int(time.time()), body.get("model") or runner.clm.name
+        if body.get("stream"):
+            def make_chunk(delta: dict, finish):
+                return {"id": cid, "object": "text_completion", "created": created, "model": model,
+                        "choices": [{"index": 0, "text": delta.get("content") or delta.get(settings.reasoning_key) or "", "finish_reason": finish}]}
+
+            def final_chunks(r: Response):
+                return [{"id": cid, "object": "text_completion", "created": created, "model": model,
+                         "choices": [{"index": 0, "text": "", "finish_reason": _finish(r)}], "usage": _usage(r)}]
+
+            return await _stream(request, runner, prompt, params, session, make_chunk, final_chunks, False)
+        try:
+            r = await asyncio.get_running_loop().run_in_executor(None, lambda: runner.generate(prompt, params, None, session, settings.request_timeout_s))
+        except Exception as e:  # noqa: BLE001
+            return error(400, str(e))
+        text = r.text if not r.reasoning else f"<think>{r.reasoning}</think>{r.text}"
+        return JSONResponse({"id": cid, "object": "text_completion", "created": created, "model": model,
+                             "choices": [{"index": 0, "text": text, "finish_reason": _finish(r), "logprobs": _logprobs_json(r)}], "usage": _usage(r)})
+
+    async def embeddings(request: Request):
+        try:
+            body = await _body(request)
+            if not registry.embedding:
+                raise KeyError("no embedding model is loaded")
+            name = body.get("model")
+            em = registry.embedding.get(name) or next(iter(registry.embedding.values()))
+            inp = body.get("input")
+            texts = [inp] if isinstance(inp, str) else list(inp or [])
+            if not texts or not all(isinstance(t, str) for t in texts):
+                raise ValueError("'input' must be a string or a list of strings")
+        except (ValueError, KeyError, TypeError) as e:
+            return error(400, str(e.args[0]) if e.args else str(e))
+        from ..embedding import PoolingType
+
+        vecs = await asyncio.get_running_loop().run_in_executor(None, lambda: em.embed_many(texts, PoolingType.AVG).tolist())
+        return JSONResponse({"object": "list", "model": name or "embedding", "data": [{"object": "embedding", "index": i, "embedding": v} for i, v in enumerate(vecs)],
+                             "usage": {"prompt_tokens": 0, "total_tokens": 0}})
+
+    async def models():
+        data = [{"id": n, "object": "model", "owned_by": "deliverance", "type": "generation"} for n in registry.generation]
+        data += [{"id": n, "object": "model", "owned_by": "deliverance", "type": "embedding"} for n in registry.embedding]
+        return JSONResponse({"object": "list", "data": data})
+
+    async def tp_status():
+        st = dict(registry.tp_status())
+        st["runners"] = {n: dict(r.stats, engine=dict(r.clm.engine.metrics), prefix_cache=dict(r.clm.engine.kv.prefix.metrics)) for n, r in registry.generation.items()}
+        return JSONResponse(st)
+
+    async def ui():
+        return HTMLResponse(_UI)
+
+    for path in ("/chat/completions", "/v1/chat/completions"):
+        app.add_api_route(path, chat, methods=["POST"])
+    for path in ("/v1/completions", "/completions"):
+        app.add_api_route(path, completions, methods=["POST"])
+    for path in ("/embeddings", "/v1/embeddings"):
+        app.add_api_route(path, embeddings, methods=["POST"])
+    for path in ("/models", "/v1/models"):
+        app.add_api_route(path, models, methods=["GET"])
+    app.add_api_route("/tp/status", tp_status, methods=["GET"])
+    app.add_api_route("/ui", ui, methods=["GET"])
+    return app
+
+
+_UI = """<!doctype html><meta charset=utf-8><title>deliverance</title>
+<style>body{font-family:sans-serif;max-width:48em;margin:2em auto}#log{white-space:pre-wrap;border:1px solid #ccc;padding:1em;min-height:12em}</style>
+<h3>chat</h3><div id=log></div><form id=f><input id=q size=60 autofocus><button>send</button></form>
+<script>
+const log=document.getElementById('log'),msgs=[];
+document.getElementById('f').onsubmit=async e=>{e.preventDefault();const q=document.getElementById('q');msgs.push({role:'user',content:q.value});
+log.textContent+='\\n> '+q.value+'\\n';q.value='';
+const r=await fetch('/chat/completions',{method:'POST',headers:{'Content-Type':'application/json'},body:JSON.stringify({messages:msgs,stream:true,max_tokens:256})});
+const rd=r.body.getReader(),dec=new TextDecoder();let buf='',ans='';
+for(;;){const {done,value}=await rd.read();if(done)break;buf+=dec.decode(value);let i;
+while((i=buf.indexOf('\\n\\n'))>=0){const line=buf.slice(0,i);buf=buf.slice(i+2);if(!line.startsWith('data: '))continue;const d=line.slice(6);if(d==='[DONE]')continue;
+const c=JSON.parse(d).choices?.[0]?.delta?.content;if(c){ans+=c;log.textContent+=c;}}}
+msgs.push({role:'assistant',content:ans});};
+</script>"""

@@ -1,0 +1,116 @@
+"""HTTP surface against a tiny CPU model: chat / completions (blocking and SSE), embeddings, models, auth, errors."""
+import base64
+import json
+
+import pytest
+
+from deliverance_b200.api import AutoModelForCausalLM
+from deliverance_b200.ckpt.tiny import write_tiny_model
+from deliverance_b200.embedding import AutoModelForEmbeddings
+from deliverance_b200.server.app import ModelRegistry, ServerSettings, create_app, verify_jwt_hs256
+from deliverance_b200.server.runner import EngineRunner
+
+fastapi = pytest.importorskip("fastapi")
+from fastapi.testclient import TestClient  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def registry(tmp_path_factory):
+    root = tmp_path_factory.mktemp("srv")
+    d = str(root / "tiny-llama")
+    write_tiny_model(d, "llama", seed=3, std=0.05)
+    clm = AutoModelForCausalLM.from_pretrained(d, device="cpu")
+    reg = ModelRegistry()
+    reg.generation[clm.name] = EngineRunner(clm)
+    b = str(root / "tiny-bert")
+    write_tiny_model(b, "bert", seed=4, std=0.05)
+    reg.embedding["tiny-bert"] = AutoModelForEmbeddings.from_pretrained(b, "cpu")
+    yield reg
+    for r in reg.generation.values():
+        r.close()
+
+
+def _sse(resp):
+    out = []
+    for line in resp.text.split("\n"):
+        if line.startswith("data: "):
+            out.append(line[6:])
+    return out
+
+
+def test_chat_blocking_and_models(registry):
+    c = TestClient(create_app(registry))
+    r = c.post("/chat/completions", json={"messages": [{"role": "system", "content": "s"}, {"role": "user", "content": [{"type": "text", "text": "hi"}]}],
+                                          "max_tokens": 5, "logprobs": True, "top_logprobs": 2, "seed": 1})
+    assert r.status_code == 200, r.text
+    j = r.json()
+    assert j["object"] == "chat.completion" and j["choices"][0]["finish_reason"] == "length" and j["usage"]["completion_tokens"] == 5
+    assert len(j["choices"][0]["logprobs"]["content"]) == 5 and "X-Deliverance-Session" in r.headers
+    m = c.get("/models").json()["data"]
+    assert {x["id"] for x in m} == {"tiny-llama", "tiny-bert"}
+    assert c.get("/tp/status").json()["enabled"] is False
+
+
+def test_chat_streaming_sse(registry):
+    c = TestClient(create_app(registry))
+    r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "stream": True},
+               headers={"X-Deliverance-Session": "abc"})
+    assert r.status_code == 200 and r.headers["x-deliverance-session"] == "abc"
+    ev = _sse(r)
+    assert ev[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in ev[:-1]]
+    assert all(ch["object"] == "chat.completion.chunk" for ch in chunks)
+    assert chunks[-1]["choices"][0]["finish_reason"] == "length" and chunks[-1]["usage"]["completion_tokens"] == 6
+    assert chunks[0]["choices"][0]["delta"].get("role") == "assistant"
+
+
+def test_completions_and_guided(registry):
+    c = TestClient(create_app(registry))
+    r = c.post("/v1/completions", json={"prompt": "abc", "max_tokens": 4, "temperature": 0.7, "top_p": 0.9, "seed": 5})
+    assert r.status_code == 200 and r.json()["object"] == "text_completion" and r.json()["id"].startswith("cmpl-")
+    r = c.post("/completions", json={"prompt": "abc", "max_tokens": 12, "guided_regex": "[0-9]{2}x"})
+    assert r.status_code == 200 and __import__("re").fullmatch("[0-9]{2}x", r.json()["choices"][0]["text"])
+    r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "max_tokens": 30,
+                                          "guided_json": {"type": "object", "properties": {"ok": {"type": "boolean"}}}})
+    assert json.loads(r.json()["choices"][0]["message"]["content"]) in ({"ok": True}, {"ok": False})
+    r = c.post("/v1/completions", json={"prompt": "abc", "max_tokens": 3, "stream": True})
+    assert _sse(r)[-1] == "[DONE]"
+
+
+def test_errors_and_embeddings(registry):
+    c = TestClient(create_app(registry))
+    assert c.post("/chat/completions", json={"model": "nope", "messages": [{"role": "user", "content": "x"}]}).status_code == 400
+    assert c.post("/chat/completions", json={"messages": []}).status_code == 400
+    assert c.post("/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "guided_regex": "a", "guided_json": {}}).status_code == 400
+    assert c.post("/v1/completions", json={"prompt": ""}).status_code == 400
+    assert c.post("/chat/completions", content=b"{bad").status_code == 400
+    r = c.post("/embeddings", json={"input": "hello world"})
+    assert r.status_code == 200 and len(r.json()["data"][0]["embedding"]) == 64
+
+
+def test_auth_basic_and_jwt(registry):
+    import hashlib
+    import hmac
+    import time
+
+    c = TestClient(create_app(registry, ServerSettings(basic_user="u", basic_password="p", jwt_secret="s3")))
+    assert c.get("/models").status_code == 401
+    tok = base64.b64encode(b"u:p").decode()
+    assert c.get("/models", headers={"Authorization": "Basic " + tok}).status_code == 200
+    assert c.get("/models", headers={"Authorization": "Basic " + base64.b64encode(b"u:x").decode()}).status_code == 401
+
+    def jwt(claims, secret):
+        enc = lambda b: base64.urlsafe_b64encode(b).rstrip(b"=").decode()  # noqa: E731
+        h, p = enc(json.dumps({"alg": "HS256", "typ": "JWT"}).encode()), enc(json.dumps(claims).encode())
+        return f"{h}.{p}." + enc(hmac.new(secret.encode(), f"{h}.{p}".encode(), hashlib.sha256).digest())
+
+    assert c.get("/models", headers={"Authorization": "Bearer " + jwt({"sub": "a", "exp": time.time() + 60}, "s3")}).status_code == 200
+    assert not verify_jwt_hs256(jwt({"exp": time.time() - 5}, "s3"), "s3") and not verify_jwt_hs256(jwt({}, "other"), "s3")
+    assert c.get("/tp/status").status_code == 200  # diagnostics stay open
+
+
+def test_pre_generate_hook_and_reasoning_field(registry):
+    c = TestClient(create_app(registry, ServerSettings(reasoning_field="vllm", pre_generate=lambda body, p: "blocked" if body.get("user") == "bad" else None)))
+    r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "user": "bad"})
+    assert r.status_code == 400 and r.json()["error"]["message"] == "blocked"
+    assert ServerSettings(reasoning_field="vllm").reasoning_key == "reasoning" and ServerSettings().reasoning_key == "reasoning_content"
