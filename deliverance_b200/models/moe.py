@@ -36,10 +36,12 @@ def moe_forward(model, i: int, lw, x: torch.Tensor) -> torch.Tensor:
 def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act):
     e = ops.require_ext()
     T, H = x.shape
-    # weights [T, k] fp32, expert ids [T, k] int32, counts [E], offsets [E + 1], perm: sorted slot -> (token * k + j)
-    w, idx, counts, offsets, perm = e.moe_route(logits, k, 0 if mode == "softmax_topk" else 1, renorm)
+    # weights [T, k] fp32, expert ids [T, k], counts [E], offsets [E + 1], perm: grouped row -> (token * k + slot), pos: inverse
+    w, idx, counts, offsets, perm, pos = e.moe_route(logits.contiguous(), k, 0 if mode == "softmax_topk" else 1, bool(renorm))
+    ops._count(2)
     xs = e.moe_gather(x, perm, k)  # [T * k, H] rows grouped by expert
-    counts_h = counts.tolist()  # one small D2H per MoE layer; the grouped launch list needs host row counts
+    ops._count()
+    counts_h = counts.tolist()  # one small D2H per MoE layer; the per-expert launch list needs host row counts
     inter = lw.experts_gate_up[0].N // 2
     hmid = torch.empty(T * k, inter, dtype=x.dtype, device=x.device)
     ys = torch.empty(T * k, H, dtype=x.dtype, device=x.device)
@@ -52,4 +54,5 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act):
         hmid[row : row + n] = ops.act_mul(gu, act)
         ops.linear(hmid[row : row + n], lw.experts_down[ex], out=ys[row : row + n])
         row += n
-    return e.moe_combine(ys, perm, w, T, k)
+    ops._count()
+    return e.moe_combine(ys, pos, w, T, k)

@@ -80,6 +80,8 @@ class DecoderModel:
         self.dtype = dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
         self.tp = tp
         TensorParallelPlanner.validate(cfg, tp.size)
+        if self.device.type == "cuda" and cfg.num_heads and cfg.head_dim not in (64, 128, 256):
+            raise ValueError(f"head_dim {cfg.head_dim} is not supported by the CUDA attention kernels (64, 128, 256)")
         self.n_heads = cfg.num_heads // tp.size
         self.n_kv = cfg.num_kv_heads // tp.size
         self.layers: list[LayerWeights] = []

@@ -444,6 +444,87 @@ void logits_post(Tensor& logits, c10::optional<Tensor> mask, double softcap, dou
   check_last_error("logits_post");
 }
 
+// ---- MoE --------------------------------------------------------------------------------------------------------------
+// returns weights [T, k] f32, expert ids [T, k] i32, counts [E], offsets [E+1], perm [T*k], pos [T*k]
+std::vector<Tensor> moe_route(const Tensor& logits, int64_t k, int64_t mode, bool renorm) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.is_contiguous(), "router logits must be fp32 [T, E]");
+  const int T = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
+  TORCH_CHECK(k >= 1 && k <= 16 && k <= E && E <= 1024, "unsupported top-k / expert count");
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto io = logits.options().dtype(at::kInt);
+  Tensor w = torch::empty({T, k}, logits.options()), idx = torch::empty({T, k}, io), counts = torch::empty({E}, io);
+  Tensor offsets = torch::empty({E + 1}, io), perm = torch::empty({T * k}, io), pos = torch::empty({T * k}, io);
+  dlv::launch_moe_route(logits.data_ptr<float>(), T, E, static_cast<int>(k), static_cast<int>(mode), renorm ? 1 : 0, w.data_ptr<float>(),
+                        idx.data_ptr<int>(), counts.data_ptr<int>(), offsets.data_ptr<int>(), perm.data_ptr<int>(), pos.data_ptr<int>(), cur_stream());
+  check_last_error("moe_route");
+  return {w, idx, counts, offsets, perm, pos};
+}
+Tensor moe_gather(const Tensor& x, const Tensor& perm, int64_t k) {
+  check_bf16(x, "x");
+  check_cuda(perm, "perm");
+  TORCH_CHECK(perm.scalar_type() == at::kInt && x.dim() == 2 && x.size(1) % 8 == 0 && perm.numel() == x.size(0) * k, "bad gather arguments");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor xs = torch::empty({perm.numel(), x.size(1)}, x.options());
+  dlv::launch_moe_gather(x.data_ptr(), perm.data_ptr<int>(), static_cast<int>(perm.numel()), static_cast<int>(k), static_cast<int>(x.size(1)), xs.data_ptr(), cur_stream());
+  check_last_error("moe_gather");
+  return xs;
+}
+Tensor moe_combine(const Tensor& ys, const Tensor& pos, const Tensor& w, int64_t T, int64_t k) {
+  check_bf16(ys, "ys");
+  check_cuda(pos, "pos");
+  check_cuda(w, "w");
+  TORCH_CHECK(pos.scalar_type() == at::kInt && w.scalar_type() == at::kFloat && pos.numel() == T * k && w.numel() == T * k && ys.size(0) == T * k && ys.size(1) % 8 == 0, "bad combine arguments");
+  c10::cuda::CUDAGuard guard(ys.device());
+  Tensor out = torch::empty({T, ys.size(1)}, ys.options());
+  dlv::launch_moe_combine(ys.data_ptr(), pos.data_ptr<int>(), w.data_ptr<float>(), static_cast<int>(T), static_cast<int>(k), static_cast<int>(ys.size(1)), out.data_ptr(), cur_stream());
+  check_last_error("moe_combine");
+  return out;
+}
+
+// ---- Mamba2 -----------------------------------------------------------------------------------------------------------
+// meta: int32 tensors prepared on the host (row_seq [T], chunk_* [n_chunks], seq_chunk0 / seq_nchunks [S])
+Tensor mamba2_forward(const Tensor& zx, const Tensor& conv_w, c10::optional<Tensor> conv_b, const Tensor& dt_bias, const Tensor& A_log,
+                      const Tensor& D, const Tensor& norm_w, Tensor& conv_state, Tensor& ssm_state, const Tensor& slots, const Tensor& q_start,
+                      const Tensor& q_len, const Tensor& positions, const Tensor& row_seq, const Tensor& chunk_seq, const Tensor& chunk_row0,
+                      const Tensor& chunk_len, const Tensor& chunk_first, const Tensor& chunk_last, const Tensor& seq_chunk0,
+                      const Tensor& seq_nchunks, bool multi_chunk, int64_t H, int64_t d_head, int64_t G, int64_t S, double eps) {
+  check_bf16(zx, "zx");
+  const int T = static_cast<int>(zx.size(0));
+  const int I = static_cast<int>(H * d_head), conv_dim = static_cast<int>(I + 2 * G * S);
+  TORCH_CHECK(zx.dim() == 2 && zx.size(1) == I + conv_dim + H, "in_proj output has the wrong width");
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&conv_w, &dt_bias, &A_log, &D, &norm_w, &conv_state, &ssm_state}) {
+    check_cuda(*t, "mamba parameter");
+    TORCH_CHECK(t->scalar_type() == at::kFloat, "mamba parameters and states are fp32");
+  }
+  const int K = static_cast<int>(conv_w.numel() / conv_dim);
+  TORCH_CHECK(conv_state.dim() == 3 && conv_state.size(1) == conv_dim && conv_state.size(2) == K - 1, "conv_state must be [slots, convDim, K-1]");
+  TORCH_CHECK(ssm_state.dim() == 4 && ssm_state.size(1) == H && ssm_state.size(2) == d_head && ssm_state.size(3) == S, "ssm_state must be [slots, H, d_head, S]");
+  check_cuda(slots, "slots");
+  TORCH_CHECK(slots.scalar_type() == at::kLong, "slots must be int64");
+  for (const Tensor* t : {&q_start, &q_len, &positions, &row_seq, &chunk_seq, &chunk_row0, &chunk_len, &chunk_first, &chunk_last, &seq_chunk0, &seq_nchunks}) {
+    check_cuda(*t, "index tensor");
+    TORCH_CHECK(t->scalar_type() == at::kInt, "index tensors must be int32");
+  }
+  const int num_seqs = static_cast<int>(q_len.numel()), n_chunks = static_cast<int>(chunk_seq.numel());
+  c10::cuda::CUDAGuard guard(zx.device());
+  auto fo = zx.options().dtype(at::kFloat);
+  Tensor xbc = torch::empty({T, conv_dim}, fo), ybuf = torch::empty({T, I}, fo);
+  Tensor cstate = torch::empty({std::max(1, n_chunks), H, d_head, S}, fo), cdecay = torch::empty({std::max(1, n_chunks), H}, fo);
+  Tensor out = torch::empty({T, I}, zx.options());
+  const float* cb = conv_b.has_value() ? conv_b.value().data_ptr<float>() : nullptr;
+  int rc = dlv::launch_mamba2(zx.data_ptr(), static_cast<int>(zx.stride(0)), T, num_seqs, I, conv_dim, K, static_cast<int>(H), static_cast<int>(d_head),
+                              static_cast<int>(G), static_cast<int>(S), conv_w.data_ptr<float>(), cb, dt_bias.data_ptr<float>(), A_log.data_ptr<float>(),
+                              D.data_ptr<float>(), norm_w.data_ptr<float>(), static_cast<float>(eps), conv_state.data_ptr<float>(), ssm_state.data_ptr<float>(),
+                              reinterpret_cast<const long long*>(slots.data_ptr<int64_t>()), row_seq.data_ptr<int>(), q_start.data_ptr<int>(),
+                              q_len.data_ptr<int>(), positions.data_ptr<int>(), n_chunks, chunk_seq.data_ptr<int>(), chunk_row0.data_ptr<int>(),
+                              chunk_len.data_ptr<int>(), chunk_first.data_ptr<int>(), chunk_last.data_ptr<int>(), seq_chunk0.data_ptr<int>(),
+                              seq_nchunks.data_ptr<int>(), multi_chunk ? 1 : 0, xbc.data_ptr<float>(), ybuf.data_ptr<float>(), cstate.data_ptr<float>(),
+                              cdecay.data_ptr<float>(), out.data_ptr(), cur_stream());
+  TORCH_CHECK(rc == 0, "mamba2: unsupported shape (code ", rc, ")");
+  check_last_error("mamba2_forward");
+  return out;
+}
+
 // ---- JQ4 ------------------------------------------------------------------------------------------------------------
 std::vector<Tensor> q4_quantize(const Tensor& w) {
   check_cuda(w, "w");
@@ -504,6 +585,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("prefill_attention", &prefill_attention);
   m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("logits_post", &logits_post, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
+  m.def("moe_route", &moe_route);
+  m.def("moe_gather", &moe_gather);
+  m.def("moe_combine", &moe_combine);
+  m.def("mamba2_forward", &mamba2_forward);
   m.def("q4_quantize", &q4_quantize);
   m.def("q4_dequantize", &q4_dequantize, py::arg("packed"), py::arg("scales"), py::arg("to_bf16") = false);
 }

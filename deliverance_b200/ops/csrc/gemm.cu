@@ -35,6 +35,7 @@ void encode_map_2d(CUtensorMap* map, int dtype_code, const void* base, uint64_t 
                    uint32_t box_rows, uint32_t box_cols, int swizzle_code) {
   CUtensorMapDataType dt = dtype_code == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : dtype_code == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : dtype_code == 3 ? CU_TENSOR_MAP_DATA_TYPE_UINT32
                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUtensorMapSwizzle sw = swizzle_code == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                           : swizzle_code == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
@@ -55,7 +56,9 @@ void gemm_weight_init(GemmWeightDesc* w) {
   if (w->is_q4) {
     if (w->K % 32 != 0) throw std::runtime_error("JQ4 weight needs K % 32 == 0");
     if ((reinterpret_cast<uintptr_t>(w->data) & 15) != 0) throw std::runtime_error("tile-packed JQ4 weights must be 16-byte aligned");
-    std::memset(&w->map_w, 0, sizeof(w->map_w));
+    // the tile-packed bytes seen as rows of 1 KB: one stage = 10 consecutive rows = one 2-D TMA box
+    const uint64_t stages = static_cast<uint64_t>((w->N + 127) / 128) * ((w->K + 127) / 128);
+    encode_map_2d(&w->map_w, 3, w->data, stages * 10, 256, 1024, 10, 256, 0);
   } else {
     if (w->K % 8 != 0) throw std::runtime_error("dense weight needs K % 8 == 0");
     encode_map_2d(&w->map_w, 0, w->data, w->N, w->K, static_cast<uint64_t>(w->K) * 2, kGemmBM, 64, 128);

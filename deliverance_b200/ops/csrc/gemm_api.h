@@ -69,6 +69,20 @@ void launch_argmax(const float* logits, int ld, int B, int V, const uint32_t* ma
 void launch_logits_post(float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
                         cudaStream_t st);
 
+// moe.cu
+void launch_moe_route(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
+                      int* perm, int* pos, cudaStream_t st);
+void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, void* xs, cudaStream_t st);
+void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, int k, int H, void* out, cudaStream_t st);
+
+// mamba.cu
+int launch_mamba2(const void* zx, int ld, int T, int num_seqs, int I, int conv_dim, int K, int H, int d_head, int G, int S,
+                  const float* conv_w, const float* conv_b, const float* dt_bias, const float* A_log, const float* D, const float* norm_w,
+                  float eps, float* conv_state, float* ssm_state, const long long* slots, const int* row_seq, const int* q_start,
+                  const int* q_len, const int* positions, int n_chunks, const int* chunk_seq, const int* chunk_row0, const int* chunk_len,
+                  const int* chunk_first, const int* chunk_last, const int* seq_chunk0, const int* seq_nchunks, int multi_chunk,
+                  float* xbc, float* ybuf, float* chunk_state, float* chunk_decay, void* out, cudaStream_t st);
+
 // quant.cu
 void launch_q4_quantize(const void* w, int src_dtype, long long n_blocks, uint8_t* packed, float* scales, cudaStream_t st);
 void launch_q4_dequantize(const uint8_t* packed, const float* scales, long long n_blocks, void* out, int dst_dtype, cudaStream_t st);

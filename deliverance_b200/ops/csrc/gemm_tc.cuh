@@ -181,7 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     *abort_flag = 0;
     *s_last = 0;
     mbar_fence_init();
-    if (!Q4) tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -207,7 +207,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         if (Q4) {
           // one contiguous 10 KB stage: 8 KB of packed nibbles (already in the swizzled shared-memory order) + 2 KB of scales
           mbar_expect_tx(full, L::kRawStage);
-          bulk_load_1d(smem_u32(raw_tile(s)), p.wq + (static_cast<size_t>(n_tile) * p.kb_total + kb) * L::kRawStage, L::kRawStage, full);
+          tma_load_2d(smem_u32(raw_tile(s)), &map_w, full, 0, (n_tile * p.kb_total + kb) * 10);
         } else {
           mbar_expect_tx(full, L::kWStage);
           tma_load_2d(smem_u32(w_tile(s, 0)), &map_w, full, kb * kGemmBK, n0);

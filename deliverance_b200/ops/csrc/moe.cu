@@ -1,0 +1,166 @@
+// Mixture-of-experts routing and token shuffling.
+//   moe_route:   router logits [T, E] fp32 -> top-k weights / expert ids per token (softmax-all -> top-k -> optional
+//                renormalise, or top-k -> softmax over the k), per-expert histogram, exclusive offsets and the permutation
+//                that groups (token, slot) pairs by expert — one kernel launch + one small scan kernel.
+//   moe_gather:  x [T, H] -> xs [T*k, H] rows in expert-grouped order.
+//   moe_combine: ys [T*k, H] (expert outputs in grouped order) -> out [T, H] = sum_j w[t, j] * ys[pos(t, j)]  (fp32 sum in
+//                slot order: deterministic, no atomics).
+// Reference semantics: core/.../model/MixtureOfExpertsBlock.java:78-112, qwen3/Qwen3MoeFeedForward.java:107-301,
+// granitemoehybrid/GraniteMoeHybridMoeFeedForward.java:112-141.
+#include "common.cuh"
+
+namespace dlv {
+
+constexpr int kMaxTopK = 16;
+
+// one warp per token; E <= 1024
+__global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int mode, int renorm,
+                                                       float* __restrict__ w_out, int* __restrict__ idx_out, int* __restrict__ counts) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float* row = logits + static_cast<size_t>(t) * E;
+  // softmax statistics over all experts (mode 0)
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
+  mx = warp_max(mx);
+  float den = 0.f;
+  for (int e = lane; e < E; e += 32) den += __expf(row[e] - mx);
+  den = warp_sum(den);
+  // iterative top-k: each round every lane proposes its best remaining expert (ties -> lower index)
+  float sel_v[kMaxTopK];
+  int sel_i[kMaxTopK];
+  unsigned long long taken_lo = 0ull;  // bitmask of this lane's taken slots (expert e = lane + 32 * j -> bit j)
+  for (int r = 0; r < k; ++r) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane, j = 0; e < E; e += 32, ++j) {
+      if ((taken_lo >> j) & 1ull) continue;
+      const float v = row[e];
+      if (v > bv || (v == bv && e < bi)) {
+        bv = v;
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    sel_v[r] = bv;
+    sel_i[r] = bi;
+    if ((bi & 31) == lane) taken_lo |= 1ull << (bi >> 5);
+  }
+  if (lane == 0) {
+    float wts[kMaxTopK];
+    float s = 0.f;
+    if (mode == 0) {
+      for (int r = 0; r < k; ++r) {
+        wts[r] = __expf(sel_v[r] - mx) / den;
+        s += wts[r];
+      }
+      if (renorm)
+        for (int r = 0; r < k; ++r) wts[r] /= s;
+    } else {
+      for (int r = 0; r < k; ++r) {
+        wts[r] = __expf(sel_v[r] - sel_v[0]);
+        s += wts[r];
+      }
+      for (int r = 0; r < k; ++r) wts[r] /= s;
+    }
+    for (int r = 0; r < k; ++r) {
+      w_out[static_cast<size_t>(t) * k + r] = wts[r];
+      idx_out[static_cast<size_t>(t) * k + r] = sel_i[r];
+      atomicAdd(&counts[sel_i[r]], 1);
+    }
+  }
+}
+
+// single CTA: exclusive scan of counts -> offsets[E + 1]; then a stable counting sort of (token, slot) pairs by expert.
+// pos[t * k + j] = row of that pair in the grouped order; perm[row] = t * k + j.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, const int* __restrict__ counts, int T, int E, int k,
+                                                        int* __restrict__ offsets, int* __restrict__ perm, int* __restrict__ pos) {
+  extern __shared__ int sh[];  // E + 1 offsets
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      sh[e] = acc;
+      acc += counts[e];
+    }
+    sh[E] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = sh[e];
+  // stable order inside an expert: ascending (token, slot). One thread per expert walks the pairs of its expert.
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int row = sh[e];
+    if (counts[e] == 0) continue;
+    for (int p = 0; p < T * k; ++p) {
+      if (idx[p] == e) {
+        perm[row] = p;
+        pos[p] = row;
+        ++row;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ perm, int k, int H,
+                                                         __nv_bfloat16* __restrict__ xs) {
+  const int row = blockIdx.x;
+  const int t = perm[row] / k;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
+  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(row) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ pos,
+                                                          const float* __restrict__ w, int k, int H, __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const float wt = w[static_cast<size_t>(t) * k + j];
+      const uint4 v = reinterpret_cast<const uint4*>(ys + static_cast<size_t>(pos[static_cast<size_t>(t) * k + j]) * H)[i];
+      const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf162(vu[e]);
+        acc[2 * e] += wt * f.x;
+        acc[2 * e + 1] += wt * f.y;
+      }
+    }
+    uint4 o;
+    uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ou[e] = pack_bf162(acc[2 * e], acc[2 * e + 1]);
+    reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[i] = o;
+  }
+}
+
+void launch_moe_route(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
+                      int* perm, int* pos, cudaStream_t st) {
+  cudaMemsetAsync(counts, 0, sizeof(int) * E, st);
+  if (T == 0) {
+    cudaMemsetAsync(offsets, 0, sizeof(int) * (E + 1), st);
+    return;
+  }
+  moe_topk_kernel<<<(T + 7) / 8, 256, 0, st>>>(logits, T, E, k, mode, renorm, w, idx, counts);
+  moe_sort_kernel<<<1, 1024, sizeof(int) * (E + 1), st>>>(idx, counts, T, E, k, offsets, perm, pos);
+}
+void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, void* xs, cudaStream_t st) {
+  if (rows == 0) return;
+  moe_gather_kernel<<<rows, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), perm, k, H, static_cast<__nv_bfloat16*>(xs));
+}
+void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, int k, int H, void* out, cudaStream_t st) {
+  if (T == 0) return;
+  moe_combine_kernel<<<T, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(ys), pos, w, k, H, static_cast<__nv_bfloat16*>(out));
+}
+
+}  // namespace dlv

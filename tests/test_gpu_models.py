@@ -1,0 +1,92 @@
+"""GPU model paths against the CPU fp32 oracle: MoE routing kernels, Mamba2 chunked scan, whole models through the engine."""
+import pytest
+import torch
+
+from deliverance_b200 import ops
+from deliverance_b200.ckpt.loader import WeightLoader
+from deliverance_b200.ckpt.tiny import write_tiny_model
+from deliverance_b200.config import load_config
+from deliverance_b200.engine.engine import Engine, EngineConfig
+from deliverance_b200.models.batch import make_batch
+from deliverance_b200.models.gpt2 import Gpt2Model
+from deliverance_b200.models.transformer import DecoderModel
+from deliverance_b200.ops import ref
+from deliverance_b200.params import GeneratorParameters
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("E,k,mode,renorm", [(8, 2, "softmax_topk", True), (128, 8, "softmax_topk", False), (64, 6, "topk_softmax", False)])
+def test_moe_route_gather_combine(E, k, mode, renorm):
+    T, H = 77, 256
+    g = torch.Generator().manual_seed(E)
+    logits = torch.randn(T, E, generator=g)
+    w_ref, idx_ref = ref.moe_route(logits, k, mode, renorm)
+    e = ops.require_ext()
+    w, idx, counts, offsets, perm, pos = e.moe_route(logits.cuda(), k, 0 if mode == "softmax_topk" else 1, renorm)
+    assert torch.equal(idx.cpu().long(), idx_ref) and torch.allclose(w.cpu(), w_ref, atol=1e-5)
+    assert counts.cpu().tolist() == torch.bincount(idx_ref.flatten(), minlength=E).tolist()
+    assert offsets.cpu().tolist() == [0] + torch.cumsum(torch.bincount(idx_ref.flatten(), minlength=E), 0).tolist()
+    flat = idx_ref.flatten()
+    assert torch.equal(flat[perm.cpu().long()], torch.sort(flat, stable=True).values)
+    assert torch.equal(perm.cpu()[pos.cpu().long()], torch.arange(T * k, dtype=torch.int32))
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    xs = e.moe_gather(x.cuda(), perm, k)
+    assert torch.equal(xs.cpu(), x[(perm.cpu() // k).long()])
+    ys = torch.randn(T * k, H, generator=g).to(torch.bfloat16)
+    out = e.moe_combine(ys.cuda(), pos, w, T, k)
+    exp = (ys.float()[pos.cpu().long()].reshape(T, k, H) * w_ref.unsqueeze(-1)).sum(1)
+    assert ((out.cpu().float() - exp).norm() / exp.norm()).item() < 1e-2
+
+
+def _pair(tmp_path, family, **over):
+    d = str(tmp_path / family)
+    if family == "gpt2":
+        over = dict(n_embd=256, n_head=4, **over)
+    elif family == "granitemoehybrid":
+        over = dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, mamba_n_heads=8, mamba_d_head=64, mamba_d_state=64, **over)
+    elif family in ("qwen3", "qwen3_moe", "gemma2"):
+        over = dict(hidden_size=128, **over)
+    else:
+        over = dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, **over)
+    write_tiny_model(d, family, seed=11, std=0.05, **over)
+    cfg = load_config(d)
+    cls = Gpt2Model if family == "gpt2" else DecoderModel
+    cpu = cls(cfg, "cpu").load(WeightLoader(d))
+    gpu = cls(cfg, "cuda:0").load(WeightLoader(d))
+    return cfg, cpu, gpu
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen3", "gemma2", "mixtral", "qwen3_moe", "gpt2", "granitemoehybrid"])
+def test_prefill_logits_gpu_vs_cpu(tmp_path, family):
+    cfg, cpu, gpu = _pair(tmp_path, family)
+    g = torch.Generator().manual_seed(2)
+    seqs = [torch.randint(3, 250, (n,), generator=g).tolist() for n in (150, 40)]
+    outs = []
+    for m in (cpu, gpu):
+        eng = Engine(m, EngineConfig(num_pages=64, cuda_graphs=False))
+        descr, nxt = [], 1
+        for i, t in enumerate(seqs):
+            n = (len(t) + 31) // 32
+            descr.append({"tokens": t, "start": 0, "pages": list(range(nxt, nxt + n)), "state_slot": i})
+            nxt += n
+        batch = make_batch(descr, 32, m.device)
+        outs.append(m.forward(batch, eng.kv, all_rows=True).float().cpu())
+    rel = ((outs[0] - outs[1]).norm() / outs[0].norm()).item()
+    assert rel < 3e-2, rel
+    agree = (outs[0].argmax(-1) == outs[1].argmax(-1)).float().mean().item()
+    assert agree > 0.9, agree
+
+
+@pytest.mark.parametrize("family", ["qwen3", "granitemoehybrid"])
+def test_generate_gpu_graphs_vs_eager(tmp_path, family):
+    cfg, cpu, gpu = _pair(tmp_path, family)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, 250, (n,), generator=g).tolist() for n in (70, 33, 140)]
+    res = []
+    for graphs in (False, True):
+        eng = Engine(gpu, EngineConfig(num_pages=128, cuda_graphs=graphs, max_batch_tokens=96))
+        rs = eng.generate_batch(prompts, GeneratorParameters(max_tokens=10))
+        res.append([r.token_ids for r in rs])
+        ops.check_status(0)
+    assert res[0] == res[1]
