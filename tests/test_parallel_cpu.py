@@ -1,0 +1,162 @@
+"""Tensor-parallel host logic without a cluster: planner, shard loader, thread ranks, gloo ranks, socket transport, DTEN,
+and host-side failure detection (a rank that never joins, a rank that raises)."""
+import os
+import subprocess
+import sys
+import threading
+
+import pytest
+import torch
+
+from deliverance_b200.ckpt.loader import WeightLoader
+from deliverance_b200.ckpt.tiny import tiny_config, write_tiny_model
+from deliverance_b200.config import load_config, parse_config
+from deliverance_b200.engine.engine import Engine, EngineConfig
+from deliverance_b200.models.transformer import DecoderModel
+from deliverance_b200.parallel import dten
+from deliverance_b200.parallel.context import (InProcessCollectives, InProcessGroup, SingleRankCollectives, TensorParallelContext,
+                                               TensorParallelPlanner)
+from deliverance_b200.parallel.socket_collectives import CollectiveServer, SocketCollectives
+from deliverance_b200.params import GeneratorParameters
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PROMPT = list(range(5, 45))
+
+
+def test_planner():
+    cfg = parse_config(tiny_config("llama", num_attention_heads=8, num_key_value_heads=4, hidden_size=128, intermediate_size=256))
+    assert TensorParallelPlanner.compatible(cfg, 1) and TensorParallelPlanner.compatible(cfg, 2) and TensorParallelPlanner.compatible(cfg, 4)
+    assert not TensorParallelPlanner.compatible(cfg, 8) and not TensorParallelPlanner.compatible(cfg, 3)
+    assert TensorParallelPlanner.choose_size(cfg, 8) == 4 and TensorParallelPlanner.choose_size(cfg, 3) == 2
+    p = TensorParallelPlanner.plan(cfg, 1, 4)
+    assert (p.heads.begin, p.heads.end) == (2, 4) and (p.kv_heads.begin, p.kv_heads.end) == (1, 2) and p.hidden.size == 32
+    with pytest.raises(ValueError):
+        TensorParallelPlanner.plan(cfg, 0, 8)
+    assert not TensorParallelContext().enabled and TensorParallelContext(1, 2).enabled and TensorParallelContext(0, 2).is_coordinator
+
+
+def _run_rank(d, cfg, ctx, out, idx, quant_head=None):
+    try:
+        m = DecoderModel(cfg, "cpu", tp=ctx).load(WeightLoader(d), head_quant=quant_head)
+        eng = Engine(m, EngineConfig(num_pages=32, max_batch_tokens=16))
+        out[idx] = eng.generate(PROMPT, GeneratorParameters(max_tokens=5)).token_ids
+    except Exception as e:  # noqa: BLE001
+        out[idx] = e
+
+
+@pytest.mark.parametrize("family,quantize", [("llama", False), ("qwen3", True), ("gemma2", False)])
+def test_thread_ranks_match_single(tmp_path, family, quantize):
+    d = str(tmp_path / family)
+    over = dict(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=2)
+    if family != "llama":
+        over["head_dim"] = 32
+    write_tiny_model(d, family, seed=3, std=0.05, quantize=quantize, **over)
+    cfg = load_config(d)
+    single = [None]
+    _run_rank(d, cfg, TensorParallelContext(), single, 0)
+    group = InProcessGroup(2, timeout=60)
+    out = [None, None]
+    ts = [threading.Thread(target=_run_rank, args=(d, cfg, TensorParallelContext(r, 2, InProcessCollectives(group, r)), out, r)) for r in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not isinstance(out[0], Exception), out[0]
+    assert out[0] == out[1] == single[0]
+
+
+def test_in_process_group_reports_missing_rank():
+    g = InProcessGroup(2, timeout=0.3)
+    c = InProcessCollectives(g, 0)
+    with pytest.raises(TimeoutError) as e:
+        c.all_reduce_sum("layer.0.mlp.down_proj", torch.ones(2))
+    assert "arrived ranks [0] of 2" in str(e.value) and "layer.0.mlp.down_proj" in str(e.value)
+    assert SingleRankCollectives().all_reduce_sum("k", torch.ones(1)).item() == 1.0
+
+
+def test_dten_codec():
+    for t in (torch.randn(3, 5), torch.arange(6, dtype=torch.int32).reshape(2, 3), torch.randn(4).to(torch.bfloat16), torch.zeros(0, 2)):
+        b = dten.encode(t)
+        assert b[:4] == b"NETD"  # 0x4454454E little endian
+        assert torch.equal(dten.decode(b), t)
+    with pytest.raises(ValueError):
+        dten.decode(b"\x00" * 32)
+    with pytest.raises(ValueError):
+        dten.decode(dten.encode(torch.randn(4))[:-3])
+
+
+def test_socket_collectives_sum_and_timeout():
+    srv = CollectiveServer(timeout=0.5)
+    try:
+        res = [None] * 3
+
+        def rank(r):
+            c = SocketCollectives(srv.address, r, 3, session="s1")
+            t = torch.full((2, 4), float(r + 1))
+            for _ in range(3):
+                c.all_reduce_sum("layer.0.self_attn.o_proj", t)
+            res[r] = t.clone()
+            c.close()
+
+        ts = [threading.Thread(target=rank, args=(r,)) for r in range(3)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        # 1+2+3 = 6, then 18, then 54
+        assert all(torch.equal(x, torch.full((2, 4), 54.0)) for x in res)
+        lone = SocketCollectives(srv.address, 0, 2, session="s2")
+        with pytest.raises(TimeoutError) as e:
+            lone.all_reduce_sum("k", torch.ones(1))
+        assert "arrived ranks [0] of 2" in str(e.value)
+        lone.close()
+    finally:
+        srv.close()
+
+
+def test_failing_rank_does_not_wedge_the_other(tmp_path):
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=3, hidden_size=128, intermediate_size=256)
+    cfg = load_config(d)
+    group = InProcessGroup(2, timeout=1.0)
+    out = [None, None]
+
+    def bad_rank():
+        out[1] = RuntimeError("rank 1 died before its first collective")
+
+    t0 = threading.Thread(target=_run_rank, args=(d, cfg, TensorParallelContext(0, 2, InProcessCollectives(group, 0)), out, 0))
+    t1 = threading.Thread(target=bad_rank)
+    t0.start(); t1.start(); t0.join(); t1.join()
+    assert isinstance(out[0], TimeoutError) and "arrived ranks [0]" in str(out[0])
+
+
+_GLOO = r"""
+import os, sys, json, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["DLV_ROOT"])
+from deliverance_b200.ckpt.loader import WeightLoader
+from deliverance_b200.config import load_config
+from deliverance_b200.engine.engine import Engine, EngineConfig
+from deliverance_b200.models.transformer import DecoderModel
+from deliverance_b200.parallel.context import TensorParallelContext, TorchCollectives
+from deliverance_b200.params import GeneratorParameters
+dist.init_process_group("gloo")
+d = os.environ["DLV_MODEL"]
+ctx = TensorParallelContext(dist.get_rank(), dist.get_world_size(), TorchCollectives())
+m = DecoderModel(load_config(d), "cpu", tp=ctx).load(WeightLoader(d))
+r = Engine(m, EngineConfig(num_pages=32)).generate(list(range(5, 45)), GeneratorParameters(max_tokens=5))
+if dist.get_rank() == 0:
+    print("TOKENS " + json.dumps(r.token_ids))
+dist.destroy_process_group()
+"""
+
+
+def test_gloo_two_processes_match_single(tmp_path):
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=3, std=0.05, hidden_size=128, intermediate_size=256)
+    cfg = load_config(d)
+    single = [None]
+    _run_rank(d, cfg, TensorParallelContext(), single, 0)
+    script = tmp_path / "w.py"
+    script.write_text(_GLOO)
+    env = dict(os.environ, DLV_ROOT=ROOT, DLV_MODEL=d)
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29533", str(script)], env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("TOKENS ")][0]
+    assert __import__("json").loads(line[7:]) == single[0]
