@@ -25,6 +25,9 @@ __device__ __forceinline__ float softcap_apply(float s, float cap) { return cap 
 // Decode
 // =====================================================================================================================
 // grid (num_seqs, KV, splits), 128 threads. GP = padded group size (power of two >= H / KV).
+// Shared-memory traffic is the limiter of this kernel, so the queries live in registers for the whole CTA (thread
+// (key slot, part) keeps the D / PARTS query elements of all GP heads that it multiplies), K rows are read once per key with
+// 16-byte loads, and the P.V pass reads V with 8-byte loads and the probabilities four keys at a time.
 template <int D, int GP>
 __global__ void __launch_bounds__(128) decode_attn_kernel(
     const __nv_bfloat16* __restrict__ q, long long q_stride,  // q row t at q + t * q_stride, heads contiguous [H, D]
@@ -34,18 +37,23 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(
     float* __restrict__ part_o,               // [num_seqs, H, splits, D]
     float* __restrict__ part_ml,              // [num_seqs, H, splits, 2]
     int H, int KV, int page_size, float scale, float softcap, int window, int splits) {
-  constexpr int KSTRIDE = D + 32;  // bf16 elements; +64 B keeps the 4-lane key groups on distinct banks
-  constexpr int DP = D / 2;        // bf16x2 columns
-  constexpr int KGROUPS = 128 / DP > 0 ? 128 / DP : 1;
+  constexpr int PARTS0 = D * GP / 64;
+  constexpr int PARTS = PARTS0 < 8 ? 8 : (PARTS0 > 32 ? 32 : PARTS0);  // threads that share one key
+  constexpr int EPT = D / PARTS;                                       // query elements per thread and head
+  constexpr int CPT = EPT / 8;                                         // 16-byte K chunks per thread and key
+  constexpr int KPP = 128 / PARTS;                                     // keys per pass
+  constexpr int DQ = D / 4;                                            // threads that cover D in the P.V pass (4 columns each)
+  constexpr int KG = 128 / DQ;                                         // key groups in the P.V pass
+  static_assert(EPT % 8 == 0 && CPT >= 1 && 32 % KPP == 0 && 32 % KG == 0, "decode attention tiling");
   extern __shared__ __align__(16) uint8_t dsm[];
-  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dsm);        // [2][32][KSTRIDE]
-  __nv_bfloat16* sV = sK + 2 * 32 * KSTRIDE;                         // [2][32][D]
-  float* sQ = reinterpret_cast<float*>(sV + 2 * 32 * D);             // [GP][D]
-  float* sS = sQ + GP * D;                                           // [GP][32]
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(dsm);        // [2][32][D]
+  __nv_bfloat16* sV = sK + 2 * 32 * D;                               // [2][32][D]
+  float* sS = reinterpret_cast<float*>(sV + 2 * 32 * D);             // [GP][32] scores, then probabilities
   float* sM = sS + GP * 32;                                          // [GP] running max
   float* sL = sM + GP;                                               // [GP] running sum
   float* sA = sL + GP;                                               // [GP] rescale factor of this tile
-  float* sRed = sA + GP;                                             // [KGROUPS][GP][D] cross-group reduction (aliases sK)
+  constexpr int HDR = (GP * 32 + 3 * GP + 3) & ~3;                   // keep the float4 stores below 16-byte aligned
+  float* sRed = sS + HDR;                                            // [KG][GP][D] cross-group reduction
 
   const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -57,17 +65,36 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(
   const int per = (ntiles + splits - 1) / splits;
   const int t0 = tile_lo + sp * per, t1 = min(tile_hi, t0 + per);
 
-  for (int i = tid; i < GP * D; i += 128) {
-    const int g = i / D, d = i % D;
-    sQ[i] = g < G ? bf2f(q[b * q_stride + static_cast<long long>(kvh * G + g) * D + d]) * scale : 0.f;
+  // queries -> registers (pre-scaled); thread (slot = tid / PARTS, part = tid % PARTS) owns elements chunk c * PARTS + part
+  const int part = tid % PARTS, slot = tid / PARTS;
+  float qreg[GP][EPT];
+#pragma unroll
+  for (int g = 0; g < GP; ++g) {
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      const int d0 = (c * PARTS + part) * 8;
+      if (g < G) {
+        const uint4 qv = *reinterpret_cast<const uint4*>(q + b * q_stride + static_cast<long long>(kvh * G + g) * D + d0);
+        const uint32_t* qu = reinterpret_cast<const uint32_t*>(&qv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf162(qu[e]);
+          qreg[g][c * 8 + 2 * e] = f.x * scale;
+          qreg[g][c * 8 + 2 * e + 1] = f.y * scale;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qreg[g][c * 8 + e] = 0.f;
+      }
+    }
   }
   if (tid < GP) {
     sM[tid] = -INFINITY;
     sL[tid] = 0.f;
   }
-  float acc[GP][2];
+  float acc[GP][4];
 #pragma unroll
-  for (int g = 0; g < GP; ++g) acc[g][0] = acc[g][1] = 0.f;
+  for (int g = 0; g < GP; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
 
   auto load_tile = [&](int tile, int buf) {
     const int key0 = tile * 32;
@@ -77,7 +104,7 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(
     for (int c = tid; c < 32 * CPR; c += 128) {
       const int r = c / CPR, cc = c % CPR;
       const bool valid = key0 + r < ctx;
-      cp_async16(smem_u32(sK + (buf * 32 + r) * KSTRIDE + cc * 8), k_cache + base + r * D + cc * 8, valid);
+      cp_async16(smem_u32(sK + (buf * 32 + r) * D + cc * 8), k_cache + base + r * D + cc * 8, valid);
       cp_async16(smem_u32(sV + (buf * 32 + r) * D + cc * 8), v_cache + base + r * D + cc * 8, valid);
     }
     cp_async_commit();
@@ -93,39 +120,37 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(
       cp_async_wait<0>();
     }
     __syncthreads();
-    // ---- scores: thread (key j, part p) covers the 16 B chunks c * 4 + p of the key row
-    {
-      const int j = tid >> 2, p4 = tid & 3;
+    // ---- scores: KPP keys per pass, PARTS threads per key (a key's threads read 16-byte chunks that are contiguous)
+#pragma unroll
+    for (int pass = 0; pass < 32 / KPP; ++pass) {
+      const int j = pass * KPP + slot;
+      const __nv_bfloat16* krow = sK + (buf * 32 + j) * D;
       float s[GP];
 #pragma unroll
       for (int g = 0; g < GP; ++g) s[g] = 0.f;
-      const __nv_bfloat16* krow = sK + (buf * 32 + j) * KSTRIDE;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        const int d0 = (c * 4 + p4) * 8;
-        const uint4 kv = *reinterpret_cast<const uint4*>(krow + d0);
+      for (int c = 0; c < CPT; ++c) {
+        const uint4 kv = *reinterpret_cast<const uint4*>(krow + (c * PARTS + part) * 8);
         const uint32_t* ku = reinterpret_cast<const uint32_t*>(&kv);
         float kf[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float2 f = unpack_bf162(ku[e]);
+          const float2 f = unpack_bf162(ku[e]);
           kf[2 * e] = f.x;
           kf[2 * e + 1] = f.y;
         }
 #pragma unroll
         for (int g = 0; g < GP; ++g) {
-          const float4 qa = *reinterpret_cast<const float4*>(sQ + g * D + d0);
-          const float4 qb = *reinterpret_cast<const float4*>(sQ + g * D + d0 + 4);
-          s[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] + qb.y * kf[5] + qb.z * kf[6] +
-                  qb.w * kf[7];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s[g] += qreg[g][c * 8 + e] * kf[e];
         }
       }
 #pragma unroll
       for (int g = 0; g < GP; ++g) {
-        s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
-        s[g] += __shfl_xor_sync(0xffffffffu, s[g], 2);
+#pragma unroll
+        for (int o = 1; o < PARTS; o <<= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
       }
-      if (p4 == 0) {
+      if (part == 0) {
         const int key = tile * 32 + j;
         const bool vis = key < ctx && key >= first_key;
 #pragma unroll
@@ -149,23 +174,35 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(
       }
     }
     __syncthreads();
-    // ---- P.V: thread (column pair dp, key group kg)
+    // ---- P.V: thread (4 columns dq, key group kg) walks the keys kg * (32 / KG) .. in blocks of four
     {
-      const int dp = tid % DP, kg = tid / DP;
-      if (kg < KGROUPS) {
+      const int dq = tid % DQ, kg = tid / DQ;
+      constexpr int KPG = 32 / KG;  // keys per group (multiple of 4 for every supported D)
+#pragma unroll
+      for (int g = 0; g < GP; ++g) {
+        const float a = sA[g];
+        acc[g][0] *= a; acc[g][1] *= a; acc[g][2] *= a; acc[g][3] *= a;
+      }
+#pragma unroll
+      for (int jb = 0; jb < KPG; jb += 4) {
+        const int j0 = kg * KPG + jb;
+        float vf[4][4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const uint2 v = *reinterpret_cast<const uint2*>(sV + (buf * 32 + j0 + jj) * D + 4 * dq);
+          const float2 lo = unpack_bf162(v.x), hi = unpack_bf162(v.y);
+          vf[jj][0] = lo.x; vf[jj][1] = lo.y; vf[jj][2] = hi.x; vf[jj][3] = hi.y;
+        }
 #pragma unroll
         for (int g = 0; g < GP; ++g) {
-          const float a = sA[g];
-          acc[g][0] *= a;
-          acc[g][1] *= a;
-        }
-        for (int j = kg; j < 32; j += KGROUPS) {
-          const float2 v = unpack_bf162(*reinterpret_cast<const uint32_t*>(sV + (buf * 32 + j) * D + 2 * dp));
+          const float4 p4 = *reinterpret_cast<const float4*>(sS + g * 32 + j0);
+          const float pj[4] = {p4.x, p4.y, p4.z, p4.w};
 #pragma unroll
-          for (int g = 0; g < GP; ++g) {
-            const float pj = sS[g * 32 + j];
-            acc[g][0] += pj * v.x;
-            acc[g][1] += pj * v.y;
+          for (int jj = 0; jj < 4; ++jj) {
+            acc[g][0] += pj[jj] * vf[jj][0];
+            acc[g][1] += pj[jj] * vf[jj][1];
+            acc[g][2] += pj[jj] * vf[jj][2];
+            acc[g][3] += pj[jj] * vf[jj][3];
           }
         }
       }
@@ -173,52 +210,24 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(
     __syncthreads();
   }
   // ---- reduce key groups, write (partial) output
-  if (KGROUPS > 1) {
-    const int dp = tid % DP, kg = tid / DP;
+  {
+    const int dq = tid % DQ, kg = tid / DQ;
 #pragma unroll
-    for (int g = 0; g < GP; ++g) {
-      sRed[(kg * GP + g) * D + 2 * dp] = acc[g][0];
-      sRed[(kg * GP + g) * D + 2 * dp + 1] = acc[g][1];
-    }
-    __syncthreads();
+    for (int g = 0; g < GP; ++g)
+      *reinterpret_cast<float4*>(sRed + (kg * GP + g) * D + 4 * dq) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
   }
+  __syncthreads();
   for (int i = tid; i < G * D; i += 128) {
     const int g = i / D, d = i % D;
-    float o;
-    if (KGROUPS > 1) {
-      o = 0.f;
-      for (int kg = 0; kg < KGROUPS; ++kg) o += sRed[(kg * GP + g) * D + d];
-    } else {
-      // KGROUPS == 1: thread dp holds columns 2dp, 2dp + 1 -> stage through sRed for a uniform write loop
-      o = 0.f;
-    }
-    const int h = kvh * G + g;
-    if (KGROUPS > 1) {
-      if (splits == 1) {
-        const float l = sL[g];
-        out[(static_cast<long long>(b) * H + h) * D + d] = f2bf(l > 0.f ? o / l : 0.f);
-      } else {
-        part_o[((static_cast<long long>(b) * H + h) * splits + sp) * D + d] = o;
-      }
-    }
-  }
-  if (KGROUPS == 1) {
-    const int dp = tid;  // 128 threads == D / 2 (D == 256)
+    float o = 0.f;
 #pragma unroll
-    for (int g = 0; g < GP; ++g) {
-      if (g < G) {
-        const int h = kvh * G + g;
-        if (splits == 1) {
-          const float l = sL[g];
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-          *reinterpret_cast<uint32_t*>(out + (static_cast<long long>(b) * H + h) * D + 2 * dp) =
-              pack_bf162(acc[g][0] * inv, acc[g][1] * inv);
-        } else {
-          float* po = part_o + ((static_cast<long long>(b) * H + h) * splits + sp) * D + 2 * dp;
-          po[0] = acc[g][0];
-          po[1] = acc[g][1];
-        }
-      }
+    for (int kg = 0; kg < KG; ++kg) o += sRed[(kg * GP + g) * D + d];
+    const int h = kvh * G + g;
+    if (splits == 1) {
+      const float l = sL[g];
+      out[(static_cast<long long>(b) * H + h) * D + d] = f2bf(l > 0.f ? o / l : 0.f);
+    } else {
+      part_o[((static_cast<long long>(b) * H + h) * splits + sp) * D + d] = o;
     }
   }
   if (splits > 1 && tid < G) {
@@ -248,11 +257,9 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
 
 template <int D, int GP>
 static size_t decode_smem_bytes() {
-  constexpr int KSTRIDE = D + 32;
-  constexpr int DP = D / 2;
-  constexpr int KGROUPS = 128 / DP > 0 ? 128 / DP : 1;
-  size_t kv = (2 * 32 * KSTRIDE + 2 * 32 * D) * 2;
-  size_t fl = (GP * D + GP * 32 + 3 * GP + KGROUPS * GP * D) * 4;
+  constexpr int KG = 128 / (D / 4);
+  const size_t kv = static_cast<size_t>(4) * 32 * D * 2;
+  const size_t fl = (static_cast<size_t>((GP * 32 + 3 * GP + 3) & ~3) + static_cast<size_t>(KG) * GP * D) * 4;
   return kv + fl;
 }
 
