@@ -1,0 +1,130 @@
+"""Model fetcher cache layout, TurboQuant codec, KV snapshots, HTTP client, profiler, LoRA hot swap."""
+import json
+import os
+import threading
+
+import pytest
+import torch
+
+from deliverance_b200.ckpt.fetch import FINISHED, ModelFetcher
+from deliverance_b200.kv.turboquant import MseTurboQuantCodec, restore_pages, snapshot_pages
+from deliverance_b200.utils.profiler import InferenceProfiler
+
+
+def test_model_fetcher_layout_and_offline(tmp_path):
+    calls = []
+
+    def opener(url, headers):
+        calls.append((url, headers))
+        if url.endswith("/api/models/acme/tiny"):
+            return json.dumps({"siblings": [{"rfilename": "config.json"}, {"rfilename": "model.safetensors"}, {"rfilename": "notes.bin"}]}).encode()
+        return b"{}" if url.endswith("config.json") else b"\x00" * 16
+
+    f = ModelFetcher.from_id("acme/tiny", home=str(tmp_path), opener=opener)
+    assert f.model_dir == str(tmp_path / "acme_tiny") and not f.is_complete()
+    os.environ["HF_TOKEN"] = "tok"
+    try:
+        d = f.maybe_download()
+    finally:
+        del os.environ["HF_TOKEN"]
+    assert sorted(os.listdir(d)) == sorted([FINISHED, "config.json", "model.safetensors"])
+    assert calls[0][1] == {"Authorization": "Bearer tok"} and calls[1][0].endswith("/acme/tiny/resolve/main/config.json")
+    n = len(calls)
+    assert f.maybe_download() == d and len(calls) == n  # .finished short-circuits
+
+    def offline(url, headers):
+        raise OSError("network unreachable")
+
+    with pytest.raises(RuntimeError) as e:
+        ModelFetcher("acme", "other", home=str(tmp_path), opener=offline).maybe_download()
+    assert "offline" in str(e.value)
+    with pytest.raises(ValueError):
+        ModelFetcher.from_id("noslash")
+
+
+def test_turboquant_codec_error_and_size():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 128, generator=g)
+    errs = []
+    for bits in (2, 3, 4, 8):
+        c = MseTurboQuantCodec(128, bits)
+        e = c.encode(x)
+        y = c.decode(e)
+        errs.append(((y - x).norm() / x.norm()).item())
+        assert c.compressed_bytes(e) == 64 * 128 * bits // 8 + 64 * 4
+    assert errs[0] > errs[1] > errs[2] > errs[3] and errs[1] < 0.25 and errs[3] < 0.02
+    c = MseTurboQuantCodec(96, 4)  # non power-of-two rows are padded for the rotation
+    z = torch.randn(5, 96, generator=g)
+    assert ((c.decode(c.encode(z)) - z).norm() / z.norm()).item() < 0.15
+
+
+def test_kv_snapshot_roundtrip():
+    from deliverance_b200.kv.paged import PagedKVCache
+
+    layout = {"layers": 2, "kv_heads": 2, "head_dim": 64, "layer_kinds": ["attention", "attention"]}
+    kv = PagedKVCache(layout, 8, "cpu", torch.float32)
+    g = torch.Generator().manual_seed(1)
+    for t in kv.k + kv.v:
+        t.copy_(torch.randn(t.shape, generator=g))
+    k0, v0 = kv.gather_rows(1, [2, 5], 50)
+    for comp, tol in (("NONE", 0.0), ("LZ4", 0.0), ("MSE_TURBOQUANT", 0.2)):
+        snap = snapshot_pages(kv, [2, 5], 50, comp, bits=4)
+        kv2 = PagedKVCache(layout, 8, "cpu", torch.float32)
+        restore_pages(kv2, snap, [3, 4])
+        k1, v1 = kv2.gather_rows(1, [3, 4], 50)
+        assert ((k1 - k0).norm() / k0.norm()).item() <= tol + 1e-7 and ((v1 - v0).norm() / v0.norm()).item() <= tol + 1e-7
+
+
+def test_profiler_report_format():
+    p = InferenceProfiler("cpu")
+    with p.stage("mlpblock.gate_up_projection"):
+        sum(range(1000))
+    with p.stage("mlpblock.gate_up_projection"):
+        pass
+    p.count("sampler.output_weight_Q4")
+    s = p.summary()
+    assert "[profile] mlpblock.gate_up_projection count=2 total_ms=" in s and "[profile-counter] sampler.output_weight_Q4 count=1" in s
+    p.reset()
+    assert p.summary() == ""
+
+
+def test_python_client_against_server(tmp_path):
+    import socket
+    import time
+
+    import uvicorn
+
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.client import DeliveranceClient
+    from deliverance_b200.server.app import ModelRegistry, create_app
+    from deliverance_b200.server.runner import EngineRunner
+
+    d = str(tmp_path / "tiny")
+    write_tiny_model(d, "llama", seed=3, std=0.05)
+    reg = ModelRegistry()
+    runner = EngineRunner(AutoModelForCausalLM.from_pretrained(d, device="cpu"))
+    reg.generation["tiny"] = runner
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    server = uvicorn.Server(uvicorn.Config(create_app(reg), host="127.0.0.1", port=port, log_level="error"))
+    t = threading.Thread(target=server.run, daemon=True)
+    t.start()
+    for _ in range(100):
+        if server.started:
+            break
+        time.sleep(0.05)
+    try:
+        c = DeliveranceClient(f"http://127.0.0.1:{port}")
+        assert c.models() == ["tiny"]
+        r = c.chat([{"role": "user", "content": "hi"}], max_tokens=4)
+        assert r["usage"]["completion_tokens"] == 4
+        kinds = [k for k, _ in c.stream_chat([{"role": "user", "content": "hi"}], max_tokens=4)]
+        assert kinds[-1] == "finish"
+        assert c.complete("abc", max_tokens=2)["object"] == "text_completion"
+    finally:
+        server.should_exit = True
+        t.join(timeout=5)
+        runner.close()
