@@ -96,6 +96,7 @@ class CausalLanguageModel:
         engine.sampler.decode_token = lambda i: tokenizer.decode([i])
         self.guides = LogitsProcessorFactory(tokenizer, eos, self.cfg.vocab_size, sketches)
         self.generation_hook: Optional[Callable] = None
+        self.adapters: dict = {}
 
     # -- prompts ---------------------------------------------------------------------------------------------------
     def prompt_builder(self) -> PromptBuilder:
@@ -110,6 +111,23 @@ class CausalLanguageModel:
             if self.cfg.add_bos and self.tokenizer.add_bos_token is not False and self.cfg.model_type not in ("qwen2", "qwen3", "qwen3_moe"):
                 ids = [bos] + ids
         return ids
+
+    # -- LoRA hot swap ---------------------------------------------------------------------------------------------
+    def register_lora(self, adapter_dir: str, adapter_id: Optional[str] = None) -> str:
+        """Load an adapter directory and keep it ready for :meth:`activate_lora`; returns its id."""
+        ad = LoraAdapter(adapter_dir, adapter_id)
+        self.adapters[ad.id] = ad
+        return ad.id
+
+    def activate_lora(self, adapter_id: Optional[str]) -> None:
+        """Switch the run-time adapter (``None`` = base model). Allowed only between requests: all sequences of a batch share
+        one adapter. Captured decode graphs are dropped because the set of launched kernels changes."""
+        if self.engine.has_work():
+            raise RuntimeError("cannot switch the LoRA adapter while requests are in flight")
+        if adapter_id is not None and adapter_id not in self.adapters:
+            raise KeyError(f"unknown LoRA adapter '{adapter_id}' (registered: {sorted(self.adapters)})")
+        self.model.set_lora(None if adapter_id is None else self.adapters[adapter_id])
+        self.engine._graphs.clear()
 
     # -- generation ------------------------------------------------------------------------------------------------
     def submit(self, prompt, params: Optional[GeneratorParameters] = None, on_event=None, session: Optional[str] = None) -> "Generation":

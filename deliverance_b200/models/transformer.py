@@ -205,6 +205,51 @@ class DecoderModel:
         }
         return m
 
+    # ------------------------------------------------------------------------------------------------ LoRA hot swap
+    def set_lora(self, adapter=None, prefix: str = "model.") -> None:
+        """Activate (or with ``None`` clear) a run-time LoRA adapter: every targeted projection gets ``(x A^T)(sB)^T`` added
+        to its output, the base weights (JQ4 included) stay untouched. Fused projections stack the A matrices of their parts
+        and place the B matrices block-diagonally so one pair of skinny GEMMs serves q|k|v (or gate|up). The adapter id joins
+        the prefix-cache salt, so cached prefixes of another adapter are never reused
+        (reference: core/.../generator/LoraDeltaApplier.java:43-63, safetensors/.../ResolvedLoraAdapter.java:22-45)."""
+        if adapter is not None and self.tp.enabled:
+            raise ValueError("run-time LoRA is not supported under tensor parallelism")
+        for i, lw in enumerate(self.layers):
+            lw.lora = {}
+            if adapter is None or lw.kind == "mamba":
+                continue
+            p = f"{prefix}layers.{i}."
+            groups = {"qkv": [p + f"self_attn.{n}_proj.weight" for n in ("q", "k", "v")], "o": [p + "self_attn.o_proj.weight"],
+                      "gate_up": [p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"], "down": [p + "mlp.down_proj.weight"]}
+            for slot, names in groups.items():
+                w = getattr(lw, slot)
+                if w is None or not any(adapter.has(n) for n in names):
+                    continue
+                out_total, r = w.N, adapter.config.r
+                rows = self._lora_part_rows(slot, out_total)
+                a_parts, b_full = [], torch.zeros(out_total, r * len(names))
+                off = 0
+                for j, n in enumerate(names):
+                    if adapter.has(n):
+                        A, Bs = adapter.resolved(n)
+                        if Bs.shape[0] != rows[j]:
+                            raise ValueError(f"{n}: adapter B has {Bs.shape[0]} rows, the projection has {rows[j]}")
+                        a_parts.append(A)
+                        b_full[off : off + rows[j], j * r : (j + 1) * r] = Bs
+                    else:
+                        a_parts.append(torch.zeros(r, w.K))
+                    off += rows[j]
+                lw.lora[slot] = LoraSlot(self._dev(torch.cat(a_parts, 0)), self._dev(b_full))
+        self.active_lora = None if adapter is None else adapter.id
+
+    def _lora_part_rows(self, slot: str, out_total: int) -> list:
+        cfg = self.cfg
+        if slot == "qkv":
+            return [cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim]
+        if slot == "gate_up":
+            return [out_total // 2, out_total // 2]
+        return [out_total]
+
     # ------------------------------------------------------------------------------------------------ forward
     def _trace(self, layer: int, stage: str, t: torch.Tensor) -> None:
         if self.layer_hook is not None:

@@ -128,3 +128,47 @@ def test_python_client_against_server(tmp_path):
         server.should_exit = True
         t.join(timeout=5)
         runner.close()
+
+
+def test_lora_hot_swap_equals_merge(tmp_path):
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.ckpt.lora import lora_names
+    from deliverance_b200.ckpt.safetensors_io import write_safetensors
+    from deliverance_b200.ckpt.tiny import tiny_config, write_tiny_model
+    from deliverance_b200.params import GeneratorParameters
+
+    d = str(tmp_path / "base")
+    write_tiny_model(d, "llama", seed=5, std=0.08)
+    cfg = tiny_config("llama")
+    hd = cfg.get("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"])
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    shapes = {"self_attn.q_proj": (cfg["num_attention_heads"] * hd, H), "self_attn.v_proj": (cfg["num_key_value_heads"] * hd, H),
+              "self_attn.o_proj": (H, cfg["num_attention_heads"] * hd), "mlp.up_proj": (I, H), "mlp.down_proj": (H, I)}
+    g = torch.Generator().manual_seed(9)
+    r, tensors = 4, {}
+    for i in range(cfg["num_hidden_layers"]):
+        for proj, (o, k) in shapes.items():
+            a, b = lora_names(f"model.layers.{i}.{proj}.weight")
+            tensors[a] = torch.randn(r, k, generator=g) * 0.2
+            tensors[b] = torch.randn(o, r, generator=g) * 0.2
+    ad = str(tmp_path / "adapter")
+    os.makedirs(ad)
+    write_safetensors(os.path.join(ad, "adapter_model.safetensors"), tensors)
+    with open(os.path.join(ad, "adapter_config.json"), "w") as f:
+        json.dump({"r": r, "lora_alpha": 8, "target_modules": ["q_proj", "v_proj", "o_proj", "up_proj", "down_proj"]}, f)
+
+    p = GeneratorParameters(max_tokens=8, temperature=0.0)
+    prompt = [3, 9, 27, 81, 5]
+    base = AutoModelForCausalLM.from_pretrained(d, device="cpu")
+    merged = AutoModelForCausalLM.new_builder(d).with_device("cpu").with_lora_adapter(ad).build()
+    t_base = base.generate(prompt, p).token_ids
+    t_merged = merged.generate(prompt, p).token_ids
+    aid = base.register_lora(ad)
+    base.activate_lora(aid)
+    assert base.model.active_lora == "adapter"
+    t_hot = base.generate(prompt, p).token_ids
+    base.activate_lora(None)
+    assert base.generate(prompt, p).token_ids == t_base
+    assert t_hot == t_merged and t_hot != t_base
+    with pytest.raises(KeyError):
+        base.activate_lora("nope")
