@@ -132,9 +132,9 @@ class CausalLanguageModel:
     # -- generation ------------------------------------------------------------------------------------------------
     def submit(self, prompt, params: Optional[GeneratorParameters] = None, on_event=None, session: Optional[str] = None) -> "Generation":
         params = params or GeneratorParameters()
-        has_tools = False
+        has_tools = bool(getattr(prompt, "has_tools", False))
         if isinstance(prompt, PromptContext):
-            has_tools, prompt = prompt.has_tools, prompt.prompt
+            prompt = prompt.prompt
         ids = self.encode_prompt(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
         gen = Generation(self, params, on_event, session or str(uuid.uuid4()), has_tools)
         guide = self.guides.create(params)

@@ -29,12 +29,40 @@ def main() -> int:
     from .app import ModelRegistry, ServerSettings, create_app
     from .runner import EngineRunner
 
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    tp = control = None
+    if world > 1:  # one process per GPU: NCCL for tensors, a gloo side group for the control commands
+        import torch
+        import torch.distributed as dist
+
+        from ..parallel.context import TensorParallelContext, TorchCollectives
+
+        if len(a.model) != 1:
+            raise SystemExit("tensor-parallel serving hosts exactly one generation model")
+        cuda = torch.cuda.is_available() and a.device != "cpu"
+        if cuda:
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl" if cuda else "gloo")
+        control = TorchCollectives(dist.new_group(backend="gloo"))
+        tp = TensorParallelContext(dist.get_rank(), world, TorchCollectives())
     reg = ModelRegistry()
     for d in a.model:
         b = AutoModelForCausalLM.new_builder(d).with_device(a.device).with_output_head_quantization(a.output_head_quantization)
         b.conf.max_seqs = a.max_seqs
+        if tp is not None:
+            b.with_tensor_parallel_context(tp)
         clm = b.build()
-        reg.generation[clm.name] = EngineRunner(clm)
+        if tp is None:
+            reg.generation[clm.name] = EngineRunner(clm)
+        elif tp.rank == 0:
+            from .lockstep import LockstepRunner
+
+            reg.generation[clm.name] = LockstepRunner(clm, control)
+        else:
+            from .lockstep import follower_loop
+
+            follower_loop(clm, control)
+            return 0
     for d in a.embedding_model:
         reg.embedding[os.path.basename(os.path.normpath(d))] = AutoModelForEmbeddings.from_pretrained(d, a.device)
     settings = ServerSettings(reasoning_field=a.reasoning_field, basic_user=a.basic_user, basic_password=a.basic_password, jwt_secret=a.jwt_secret)

@@ -160,3 +160,50 @@ def test_gloo_two_processes_match_single(tmp_path):
     assert p.returncode == 0, p.stderr[-2000:]
     line = [l for l in p.stdout.splitlines() if l.startswith("TOKENS ")][0]
     assert __import__("json").loads(line[7:]) == single[0]
+
+
+def test_lockstep_serving_thread_ranks(tmp_path):
+    """Rank 0 runs the serving loop and broadcasts admissions; rank 1 follows. Both ranks hold half of the model."""
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.server.lockstep import LockstepRunner, follower_loop
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=3, std=0.05, hidden_size=128, intermediate_size=256)
+    single = AutoModelForCausalLM.from_pretrained(d, device="cpu")
+    p = GeneratorParameters(max_tokens=6, temperature=0.0)
+    want = [single.generate(PROMPT, p).token_ids, single.generate(PROMPT[:17], p).token_ids]
+    data, ctl = InProcessGroup(2, timeout=60.0), InProcessGroup(2, timeout=60.0)
+    clms = [None, None]
+
+    def build(rank):
+        clms[rank] = (AutoModelForCausalLM.new_builder(d).with_device("cpu")
+                      .with_tensor_parallel(rank, 2, InProcessCollectives(data, rank)).build())
+
+    ts = [threading.Thread(target=build, args=(r,)) for r in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    steps = [None]
+    err = []
+
+    def follow():
+        try:
+            steps[0] = follower_loop(clms[1], InProcessCollectives(ctl, 1))
+        except Exception as e:  # noqa: BLE001
+            err.append(e)
+
+    ft = threading.Thread(target=follow, daemon=True)
+    ft.start()
+    runner = LockstepRunner(clms[0], InProcessCollectives(ctl, 0), heartbeat=0.05)
+    a = runner.submit(PROMPT, p)
+    b = runner.submit(PROMPT[:17], p)
+    c = runner.submit(PROMPT, GeneratorParameters(max_tokens=200, temperature=0.0))
+    try:
+        got = [a.wait(60).token_ids, b.wait(60).token_ids]
+        c.cancel()
+        rc = c.wait(60)
+    finally:
+        runner.close()
+        ft.join(timeout=30)
+    assert len(rc.token_ids) < 200 and runner.stats["cancelled"] == 1
+    assert not err and not ft.is_alive()
+    assert got == want and steps[0] >= 6
