@@ -92,7 +92,7 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--impl", default="own", choices=["own", "reference", "torch"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--shape", default="qwen3-4b")
@@ -131,7 +131,7 @@ def main() -> int:
 
         dist.init_process_group("nccl", device_id=dev)
         tp = TensorParallelContext(rank, world, TorchCollectives())
-        if args.comm in ("auto", "fused"):
+        if args.impl == "own" and args.comm in ("auto", "fused"):
             try:
                 from deliverance_b200.parallel.fused import FusedTensorParallel
 
@@ -141,6 +141,40 @@ def main() -> int:
                     raise
                 if rank == 0:
                     print(f"[bench] fused TP path unavailable ({type(e).__name__}: {e}); using NCCL all-reduce", file=sys.stderr)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if args.impl == "torch":  # library baseline: cuBLAS + SDPA + NCCL, bf16 weights, none of this package's kernels
+        from deliverance_b200.bench.torch_baseline import run as torch_run
+
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        r = torch_run(args, dev, rank, world, SHAPES[args.shape], sync_all, max_over_ranks)
+        clocks = sampler.stop() if rank == 0 else {}
+        if rank == 0:
+            print(json.dumps({"impl": "torch-baseline", "metric": "decode_tokens_per_s", "value": r["decode_tok_s"], "unit": "tokens/s",
+                              "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": r["decode_tok_s"] / REFERENCE_DECODE_TOK_S,
+                              "dtype": "bf16", "data": "synthetic (uniform random prompts, random-init N(0,0.02) bf16 weights)",
+                              "config": {"model": f"{args.shape}-shape bf16", "global_batch": args.batch, "seq_len": args.prompt_len,
+                                         "parallelism": f"tp{args.gpus}", "kernels": "cuBLAS + torch SDPA + NCCL, decode step in a CUDA graph"},
+                              "clocks": clocks, "extras": {"prefill_tok_s": r["prefill_tok_s"], "prefill_ms": r["prefill_ms"]}}))
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
 
     ops.require_ext()
     shape = SHAPES[args.shape]
@@ -160,19 +194,6 @@ def main() -> int:
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g)
     pinned = prompts.to(torch.int32).pin_memory()
-
-    def sync_all():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def max_over_ranks(ms: float) -> float:
-        if dist is None:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
 
     # ---------------------------------------------------------------- prefill (device-timed, includes first-token sampling)
     params = GeneratorParameters(temperature=0.0)

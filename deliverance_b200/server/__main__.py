@@ -66,7 +66,11 @@ def main() -> int:
     for d in a.embedding_model:
         reg.embedding[os.path.basename(os.path.normpath(d))] = AutoModelForEmbeddings.from_pretrained(d, a.device)
     settings = ServerSettings(reasoning_field=a.reasoning_field, basic_user=a.basic_user, basic_password=a.basic_password, jwt_secret=a.jwt_secret)
-    uvicorn.run(create_app(reg, settings), host=a.host, port=a.port, log_level="info")
+    try:
+        uvicorn.run(create_app(reg, settings), host=a.host, port=a.port, log_level="info")
+    finally:
+        for r in reg.generation.values():  # also tells tensor-parallel followers to stop
+            r.close()
     return 0
 
 
