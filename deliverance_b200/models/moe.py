@@ -18,41 +18,49 @@ from ..ops import ref
 
 
 def moe_forward(model, i: int, lw, x: torch.Tensor) -> torch.Tensor:
+    """Routed experts of one layer. Under tensor parallelism the experts are split across ranks when their count divides
+    (expert parallelism: tokens are replicated after the attention all-reduce, so dispatch is a local selection and the
+    combine is a sum over ranks); otherwise every rank holds all experts and no communication is needed."""
     cfg = model.cfg
     E, k = cfg.num_experts, cfg.experts_per_token
     logits = ops.linear(x, lw.router, out_f32=True)
     renorm = True if cfg.model_type == "mixtral" else (cfg.norm_topk_prob if cfg.router_mode == "softmax_topk" else False)
+    e0, ne = lw.expert0, lw.n_local_experts or E
     if x.device.type == "cuda":
-        return _moe_cuda(model, lw, x, logits, E, k, cfg.router_mode, renorm, cfg.hidden_act)
-    w, idx = ref.moe_route(logits, k, cfg.router_mode, renorm)
-    return ref.moe_experts(
-        x, w, idx,
-        lambda e, rows: ops.linear(rows, lw.experts_gate_up[e]),
-        lambda e, h: ops.linear(h, lw.experts_down[e]),
-        E, cfg.hidden_act,
-    )
+        y = _moe_cuda(model, lw, x, logits, E, k, cfg.router_mode, renorm, cfg.hidden_act, e0, ne)
+    else:
+        w, idx = ref.moe_route(logits, k, cfg.router_mode, renorm)
+        local = (idx >= e0) & (idx < e0 + ne)
+        y = ref.moe_experts(
+            x, torch.where(local, w, torch.zeros_like(w)), torch.where(local, idx - e0, torch.full_like(idx, -1)),
+            lambda e, rows: ops.linear(rows, lw.experts_gate_up[e]),
+            lambda e, h: ops.linear(h, lw.experts_down[e]),
+            ne, cfg.hidden_act,
+        )
+    if ne != E:
+        y = model.tp.all_reduce(f"layer.{i}.moe.combine", y)
+    return y
 
 
-def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act):
+def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
     e = ops.require_ext()
     T, H = x.shape
+    rows = T * k
     # weights [T, k] fp32, expert ids [T, k], counts [E], offsets [E + 1], perm: grouped row -> (token * k + slot), pos: inverse
     w, idx, counts, offsets, perm, pos = e.moe_route(logits.contiguous(), k, 0 if mode == "softmax_topk" else 1, bool(renorm))
     ops._count(2)
-    xs = e.moe_gather(x, perm, k)  # [T * k, H] rows grouped by expert
+    ep = ne != E
+    rng = (offsets, e0, ne) if ep else (None, 0, 0)
+    xs = e.moe_gather(x, perm, k, *rng)  # [T * k, H] rows grouped by expert (only the local experts' rows are filled)
+    bn = ops.moe_token_tile(rows if not ep else max(1, rows * ne // E), ne)
+    max_items = min((rows + bn - 1) // bn + ne, rows) if rows >= ne else rows
+    max_items = max(1, max_items)
+    items = e.moe_items(offsets, e0, ne, bn, max_items)
+    ops._count(2)
+    gu_w, down_w = lw.experts_gate_up_grouped, lw.experts_down_grouped
+    small = bn <= 64  # decode-sized groups: split K so that more CTAs stream weights
+    gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
+    hmid = ops.act_mul(gu, act)
+    ys = down_w.run(hmid, items, bn, max(1, min(8, down_w.K // 1024)) if small else 1)
     ops._count()
-    counts_h = counts.tolist()  # one small D2H per MoE layer; the per-expert launch list needs host row counts
-    inter = lw.experts_gate_up[0].N // 2
-    hmid = torch.empty(T * k, inter, dtype=x.dtype, device=x.device)
-    ys = torch.empty(T * k, H, dtype=x.dtype, device=x.device)
-    row = 0
-    for ex in range(E):
-        n = counts_h[ex]
-        if n == 0:
-            continue
-        gu = ops.linear(xs[row : row + n], lw.experts_gate_up[ex])
-        hmid[row : row + n] = ops.act_mul(gu, act)
-        ops.linear(hmid[row : row + n], lw.experts_down[ex], out=ys[row : row + n])
-        row += n
-    ops._count()
-    return e.moe_combine(ys, pos, w, T, k)
+    return e.moe_combine(ys, pos, w, T, k, *rng)

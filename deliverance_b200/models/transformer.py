@@ -50,8 +50,12 @@ class LayerWeights:
     down: Optional[LinearWeight] = None
     # MoE
     router: Optional[LinearWeight] = None
-    experts_gate_up: list = field(default_factory=list)  # per local expert
+    experts_gate_up: list = field(default_factory=list)  # per local expert (CPU); stacked in *_grouped on CUDA
     experts_down: list = field(default_factory=list)
+    experts_gate_up_grouped: Optional[object] = None
+    experts_down_grouped: Optional[object] = None
+    expert0: int = 0  # first expert held by this rank (expert parallelism)
+    n_local_experts: int = 0  # 0 = all
     shared_gate_up: Optional[LinearWeight] = None  # granite shared MLP
     shared_down: Optional[LinearWeight] = None
     # mamba2
@@ -164,32 +168,42 @@ class DecoderModel:
     def _load_ff(self, loader, lw, i, p, get, row, col):
         cfg = self.cfg
         mt = cfg.model_type
+        E = cfg.num_experts
+        ep = self.tp.enabled and E > 0 and E % self.tp.size == 0  # expert parallelism: this rank holds E / size whole experts
+        e0, ne = ((self.tp.rank * (E // self.tp.size), E // self.tp.size) if ep else (0, E))
+        sparse = mt == "mixtral" or (mt == "qwen3_moe" and cfg.is_sparse_layer(i)) or (mt == "granitemoehybrid" and E > 0)
+        if sparse:
+            lw.expert0, lw.n_local_experts = e0, ne
         if mt == "mixtral":
             lw.router = self._lin(loader.load(p + "block_sparse_moe.gate.weight"))
-            for e in range(cfg.num_experts):
-                ep = p + f"block_sparse_moe.experts.{e}."
-                lw.experts_gate_up.append(self._lin(_cat_weights([get(ep + "w1.weight"), get(ep + "w3.weight")])))
-                lw.experts_down.append(self._lin(get(ep + "w2.weight")))
+            for e in range(e0, e0 + ne):
+                ep_ = p + f"block_sparse_moe.experts.{e}."
+                lw.experts_gate_up.append(self._lin(_cat_weights([get(ep_ + "w1.weight"), get(ep_ + "w3.weight")])))
+                lw.experts_down.append(self._lin(get(ep_ + "w2.weight")))
         elif mt == "qwen3_moe" and cfg.is_sparse_layer(i):
             lw.router = self._lin(loader.load(p + "mlp.gate.weight"))
-            for e in range(cfg.num_experts):
-                ep = p + f"mlp.experts.{e}."
-                lw.experts_gate_up.append(self._lin(_cat_weights([get(ep + "gate_proj.weight"), get(ep + "up_proj.weight")])))
-                lw.experts_down.append(self._lin(get(ep + "down_proj.weight")))
+            for e in range(e0, e0 + ne):
+                ep_ = p + f"mlp.experts.{e}."
+                lw.experts_gate_up.append(self._lin(_cat_weights([get(ep_ + "gate_proj.weight"), get(ep_ + "up_proj.weight")])))
+                lw.experts_down.append(self._lin(get(ep_ + "down_proj.weight")))
         elif mt == "granitemoehybrid":
             lw.shared_gate_up = self._lin(get(p + "shared_mlp.input_linear.weight"))
             lw.shared_down = self._lin(get(p + "shared_mlp.output_linear.weight"))
-            if cfg.num_experts > 0:
+            if E > 0:
                 lw.router = self._lin(loader.load(p + "block_sparse_moe.router.layer.weight"))
                 win = get(p + "block_sparse_moe.input_linear.weight")  # [E, 2I, hidden]
                 wout = get(p + "block_sparse_moe.output_linear.weight")  # [E, hidden, I]
-                for e in range(cfg.num_experts):
+                for e in range(e0, e0 + ne):
                     lw.experts_gate_up.append(self._lin(_slice_expert(win, e)))
                     lw.experts_down.append(self._lin(_slice_expert(wout, e)))
         else:
             parts = [get(p + "mlp.gate_proj.weight", row()), get(p + "mlp.up_proj.weight", row())]
             lw.gate_up = self._lin(_cat_weights(parts))
             lw.down = self._lin(get(p + "mlp.down_proj.weight", col))
+        if lw.experts_gate_up and self.device.type == "cuda":
+            lw.experts_gate_up_grouped = ops.GroupedLinearWeight(lw.experts_gate_up)
+            lw.experts_down_grouped = ops.GroupedLinearWeight(lw.experts_down)
+            lw.experts_gate_up, lw.experts_down = [], []
 
     def _load_mamba(self, loader, p) -> dict:
         f32 = lambda n: self._dev(loader.load_dense(p + n), torch.float32)  # noqa: E731
@@ -388,6 +402,9 @@ class DecoderModel:
                     n += w.nbytes()
             for w in lw.experts_gate_up + lw.experts_down:
                 n += w.nbytes()
+            for w in (lw.experts_gate_up_grouped, lw.experts_down_grouped):
+                if w is not None:
+                    n += w.nbytes()
         if self.lm_head is not None and (self.lm_head.q4 or self.lm_head.w is not self.embed):
             n += self.lm_head.nbytes()
         return n

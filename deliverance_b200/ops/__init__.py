@@ -348,3 +348,39 @@ def q4_quantize(w: torch.Tensor):
     from ..ckpt.jq4 import q4_quantize as host
 
     return host(w)
+
+
+# ---------------------------------------------------------------------------------------------------------- grouped (MoE)
+class GroupedLinearWeight:
+    """The projection weights of a rank's local experts stacked for the grouped tcgen05 GEMM (CUDA only): JQ4 experts are
+    concatenated tile row by tile row (each expert padded to whole 128-row tiles), dense experts row by row. One launch
+    covers every expert that has rows; the work list comes from ``moe_items`` on the device, so nothing syncs with the host."""
+
+    def __init__(self, weights: list):
+        w0 = weights[0]
+        if any(w.N != w0.N or w.K != w0.K or w.q4 != w0.q4 for w in weights):
+            raise ValueError("experts of one layer must share shape and quantisation")
+        self.E, self.N, self.K, self.q4 = len(weights), w0.N, w0.K, w0.q4
+        e = require_ext()
+        if self.q4:
+            self.data = torch.cat([w.tiles for w in weights], 0).contiguous()
+            self.handle = e.GemmWeight(self.data, True, self.E * ((self.N + 127) // 128) * 128, self.K)
+        else:
+            self.data = torch.cat([w.w for w in weights], 0).contiguous()
+            self.handle = e.GemmWeight(self.data, False, self.E * self.N, self.K)
+
+    def nbytes(self) -> int:
+        return self.data.numel() * self.data.element_size()
+
+    def run(self, xs: torch.Tensor, items: torch.Tensor, bn: int, splits: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _count()
+        return self.handle.run_grouped(xs, items, self.N, bn, splits, out)
+
+
+def moe_token_tile(rows: int, local_experts: int) -> int:
+    """Token tile (UMMA N) of the grouped GEMM for ``rows`` routed rows spread over ``local_experts`` experts."""
+    avg = rows / max(1, local_experts)
+    for bn in (16, 32, 64, 128):
+        if avg <= bn * 0.75:
+            return bn
+    return 256

@@ -146,6 +146,24 @@ class GemmWeight {
     check_last_error("gemm launch");
     return out;
   }
+  // Grouped (MoE) GEMM: `this` stacks the local experts' weights (n_per_expert rows each; JQ4: whole 128-row tiles per expert),
+  // xs holds rows sorted by expert, `items` comes from moe_items with the same token tile.
+  Tensor run_grouped(const Tensor& xs, const Tensor& items, int64_t n_per_expert, int64_t bn, int64_t splits, c10::optional<Tensor> out_opt) {
+    TORCH_CHECK(xs.is_cuda() && xs.scalar_type() == at::kBFloat16 && xs.dim() == 2 && xs.size(1) == desc_.K && xs.stride(1) == 1, "xs must be bf16 [rows, K]");
+    TORCH_CHECK(xs.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(xs.data_ptr()) & 15) == 0, "xs rows must be 16-byte aligned");
+    TORCH_CHECK(items.is_cuda() && items.scalar_type() == at::kInt && items.dim() == 2 && items.size(1) == 4 && items.is_contiguous(), "items must be int32 [n, 4]");
+    const int64_t per = desc_.is_q4 ? ((n_per_expert + 127) / 128) * 128 : n_per_expert;
+    TORCH_CHECK(n_per_expert > 0 && desc_.N % per == 0, "stacked weight rows are not a multiple of the per-expert rows");
+    c10::cuda::CUDAGuard guard(xs.device());
+    Tensor out = out_opt.has_value() ? out_opt.value() : torch::empty({xs.size(0), n_per_expert}, xs.options());
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == xs.size(0) && out.size(1) == n_per_expert && out.stride(1) == 1, "bad out");
+    DeviceScratch& s = scratch_for(xs.device().index());
+    dlv::gemm_tc_run_grouped(&desc_, static_cast<int>(n_per_expert), xs.data_ptr(), static_cast<int>(xs.size(0)), static_cast<int>(xs.stride(0)),
+                             out.data_ptr(), static_cast<int>(out.stride(0)), items.data_ptr<int>(), static_cast<int>(items.size(0)),
+                             static_cast<int>(bn), static_cast<int>(splits), s.status.data_ptr<int>(), cur_stream());
+    check_last_error("grouped gemm launch");
+    return out;
+  }
   // Row-parallel projection fused with the tensor-parallel sum: every rank calls this with its K-shard; `out` holds the
   // all-reduced result on every rank. Returns false (nothing launched) when the shape is outside the fused path.
   bool run_tp(const Tensor& x, Tensor& out, const TpComm& comm, c10::optional<Tensor> bias) {
@@ -459,24 +477,44 @@ std::vector<Tensor> moe_route(const Tensor& logits, int64_t k, int64_t mode, boo
   check_last_error("moe_route");
   return {w, idx, counts, offsets, perm, pos};
 }
-Tensor moe_gather(const Tensor& x, const Tensor& perm, int64_t k) {
+Tensor moe_items(const Tensor& offsets, int64_t e0, int64_t ne, int64_t bn, int64_t max_items) {
+  check_cuda(offsets, "offsets");
+  TORCH_CHECK(offsets.scalar_type() == at::kInt && e0 >= 0 && ne >= 1 && ne <= 1024 && e0 + ne < offsets.numel() + 0 && bn >= 16 && max_items >= 1, "bad work-list arguments");
+  c10::cuda::CUDAGuard guard(offsets.device());
+  Tensor items = torch::empty({max_items, 4}, offsets.options());
+  dlv::launch_moe_items(offsets.data_ptr<int>(), static_cast<int>(e0), static_cast<int>(ne), static_cast<int>(bn), static_cast<int>(max_items), items.data_ptr<int>(), cur_stream());
+  check_last_error("moe_items");
+  return items;
+}
+// offsets / e0 / ne (optional): only rows of the local experts [e0, e0 + ne) are touched
+Tensor moe_gather(const Tensor& x, const Tensor& perm, int64_t k, c10::optional<Tensor> offsets, int64_t e0, int64_t ne) {
   check_bf16(x, "x");
   check_cuda(perm, "perm");
   TORCH_CHECK(perm.scalar_type() == at::kInt && x.dim() == 2 && x.size(1) % 8 == 0 && perm.numel() == x.size(0) * k, "bad gather arguments");
   c10::cuda::CUDAGuard guard(x.device());
   Tensor xs = torch::empty({perm.numel(), x.size(1)}, x.options());
-  dlv::launch_moe_gather(x.data_ptr(), perm.data_ptr<int>(), static_cast<int>(perm.numel()), static_cast<int>(k), static_cast<int>(x.size(1)), xs.data_ptr(), cur_stream());
+  const int* off = nullptr;
+  if (offsets.has_value()) {
+    TORCH_CHECK(offsets.value().is_cuda() && offsets.value().scalar_type() == at::kInt && e0 + ne < offsets.value().numel(), "bad expert range");
+    off = offsets.value().data_ptr<int>();
+  }
+  dlv::launch_moe_gather(x.data_ptr(), perm.data_ptr<int>(), static_cast<int>(perm.numel()), static_cast<int>(k), static_cast<int>(x.size(1)), xs.data_ptr(), off, static_cast<int>(e0), static_cast<int>(ne), cur_stream());
   check_last_error("moe_gather");
   return xs;
 }
-Tensor moe_combine(const Tensor& ys, const Tensor& pos, const Tensor& w, int64_t T, int64_t k) {
+Tensor moe_combine(const Tensor& ys, const Tensor& pos, const Tensor& w, int64_t T, int64_t k, c10::optional<Tensor> offsets, int64_t e0, int64_t ne) {
   check_bf16(ys, "ys");
   check_cuda(pos, "pos");
   check_cuda(w, "w");
   TORCH_CHECK(pos.scalar_type() == at::kInt && w.scalar_type() == at::kFloat && pos.numel() == T * k && w.numel() == T * k && ys.size(0) == T * k && ys.size(1) % 8 == 0, "bad combine arguments");
   c10::cuda::CUDAGuard guard(ys.device());
   Tensor out = torch::empty({T, ys.size(1)}, ys.options());
-  dlv::launch_moe_combine(ys.data_ptr(), pos.data_ptr<int>(), w.data_ptr<float>(), static_cast<int>(T), static_cast<int>(k), static_cast<int>(ys.size(1)), out.data_ptr(), cur_stream());
+  const int* off = nullptr;
+  if (offsets.has_value()) {
+    TORCH_CHECK(offsets.value().is_cuda() && offsets.value().scalar_type() == at::kInt && e0 + ne < offsets.value().numel(), "bad expert range");
+    off = offsets.value().data_ptr<int>();
+  }
+  dlv::launch_moe_combine(ys.data_ptr(), pos.data_ptr<int>(), w.data_ptr<float>(), static_cast<int>(T), static_cast<int>(k), static_cast<int>(ys.size(1)), out.data_ptr(), off, static_cast<int>(e0), static_cast<int>(ne), cur_stream());
   check_last_error("moe_combine");
   return out;
 }
@@ -566,6 +604,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("run", &GemmWeight::run, py::arg("x"), py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("out_f32") = false,
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
+      .def("run_grouped", &GemmWeight::run_grouped, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits") = 1,
+           py::arg("out") = py::none())
       .def_property_readonly("N", &GemmWeight::n)
       .def_property_readonly("K", &GemmWeight::k)
       .def_property_readonly("is_q4", &GemmWeight::is_q4);
@@ -586,8 +626,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("logits_post", &logits_post, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("moe_route", &moe_route);
-  m.def("moe_gather", &moe_gather);
-  m.def("moe_combine", &moe_combine);
+  m.def("moe_items", &moe_items);
+  m.def("moe_gather", &moe_gather, py::arg("x"), py::arg("perm"), py::arg("k"), py::arg("offsets") = py::none(), py::arg("e0") = 0, py::arg("ne") = 0);
+  m.def("moe_combine", &moe_combine, py::arg("ys"), py::arg("pos"), py::arg("w"), py::arg("T"), py::arg("k"), py::arg("offsets") = py::none(),
+        py::arg("e0") = 0, py::arg("ne") = 0);
   m.def("mamba2_forward", &mamba2_forward);
   m.def("q4_quantize", &q4_quantize);
   m.def("q4_dequantize", &q4_dequantize, py::arg("packed"), py::arg("scales"), py::arg("to_bf16") = false);

@@ -250,6 +250,72 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
 #undef DLV_LAUNCH
 }
 
+// ------------------------------------------------------------------------------------------------ grouped (MoE) GEMM
+// out[r, :] = xs[r, :] @ W[expert(r)]^T for rows grouped by expert. `items` is the device work list built by
+// launch_moe_items with the same token tile `bn`; `max_items` bounds it (unused slots return at once).
+template <bool Q4, int BN>
+static void run_grouped(const GemmWeightDesc* w, const void* x, int rows, int ldx, GemmParams p, int max_items, int splits, cudaStream_t st) {
+  using L = GemmSmem<Q4, BN>;
+  if (splits > p.kb_total / 2) splits = p.kb_total / 2;
+  if (splits < 1) splits = 1;
+  while (splits > 1 && cluster_capacity<Q4, BN>(splits) <= 0) --splits;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+  (void)cluster_capacity<Q4, BN>(1);  // sets the shared-memory attribute
+  p.splits = splits;
+  p.cluster_reduce = splits > 1 ? 1 : 0;
+  p.wq = w->is_q4 ? static_cast<const uint8_t*>(w->data) : nullptr;
+  CUtensorMap map_x;
+  encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(rows), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.n_tiles, max_items, splits);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = L::kBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  if (splits > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<Q4, BN>, w->map_w, map_x, p);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("grouped gemm launch: ") + cudaGetErrorString(e));
+}
+
+void gemm_tc_run_grouped(const GemmWeightDesc* w, int n_per_expert, const void* x, int rows, int ldx, void* out, int ldo,
+                         const int* items, int max_items, int bn, int splits, int* status, cudaStream_t st) {
+  if (rows <= 0 || max_items <= 0) return;
+  if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
+  if (max_items > 65535) throw std::runtime_error("grouped gemm: work list too long");
+  GemmParams p = {};
+  p.M = rows;
+  p.N = n_per_expert;
+  p.K = w->K;
+  p.kb_total = (w->K + kGemmBK - 1) / kGemmBK;
+  p.n_tiles = (n_per_expert + kGemmBM - 1) / kGemmBM;
+  p.m_tiles = max_items;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_f32 = 0;
+  p.status = status;
+  p.grp_items = reinterpret_cast<const int4*>(items);
+#define DLV_LAUNCH(BNV)                                                              \
+  if (w->is_q4) run_grouped<true, BNV>(w, x, rows, ldx, p, max_items, splits, st);   \
+  else run_grouped<false, BNV>(w, x, rows, ldx, p, max_items, splits, st)
+  switch (bn) {
+    case 16: DLV_LAUNCH(16); break;
+    case 32: DLV_LAUNCH(32); break;
+    case 64: DLV_LAUNCH(64); break;
+    case 128: DLV_LAUNCH(128); break;
+    case 256: DLV_LAUNCH(256); break;
+    default: throw std::runtime_error("grouped gemm: token tile must be 16, 32, 64, 128 or 256");
+  }
+#undef DLV_LAUNCH
+}
+
 // ------------------------------------------------------------------------------------------------ CUDA-core GEMV
 // One warp per weight row, MT tokens. fp32 accumulation; JQ4 blocks are expanded in registers.
 template <int MT, bool Q4>

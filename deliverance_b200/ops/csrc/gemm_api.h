@@ -37,6 +37,10 @@ void gemm_set_trace(unsigned long long* p);  // debug: device buffer of 16 u64 t
 void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
                  float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st,
                  const GemmTpArgs* tp = nullptr);
+// Grouped (mixture-of-experts) GEMM over rows sorted by expert; `w` stacks the local experts (JQ4: each expert padded to whole
+// 128-row tiles), `items` is the device work list of launch_moe_items built with the same token tile `bn`.
+void gemm_tc_run_grouped(const GemmWeightDesc* w, int n_per_expert, const void* x, int rows, int ldx, void* out, int ldo,
+                         const int* items, int max_items, int bn, int splits, int* status, cudaStream_t st);
 // true when the fused all-reduce epilogue can take this problem (one wave of CTAs, rows and columns inside the slab)
 bool gemm_tp_supported(const GemmWeightDesc* w, int M, const GemmTpArgs* tp);
 void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
@@ -72,8 +76,13 @@ void launch_logits_post(float* logits, int ld, int B, int V, const uint32_t* mas
 // moe.cu
 void launch_moe_route(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
                       int* perm, int* pos, cudaStream_t st);
-void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, void* xs, cudaStream_t st);
-void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, int k, int H, void* out, cudaStream_t st);
+// `range` (optional) = offsets + first local expert and the count of local experts: rows outside
+// [offsets[e0], offsets[e0 + ne]) are skipped (expert parallelism: other ranks own them)
+void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, void* xs, const int* offsets, int e0, int ne,
+                       cudaStream_t st);
+void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, int k, int H, void* out, const int* offsets, int e0,
+                        int ne, cudaStream_t st);
+void launch_moe_items(const int* offsets, int e0, int ne, int bn, int max_items, int* items, cudaStream_t st);
 
 // mamba.cu
 int launch_mamba2(const void* zx, int ld, int T, int num_seqs, int I, int conv_dim, int K, int H, int d_head, int G, int S,

@@ -69,6 +69,10 @@ struct GemmParams {
   unsigned int* tp_rounds;         // local: how many fused calls each CTA index has completed
   unsigned int* tp_call;           // local: [0] = number of fused launches completed, [1] = CTAs done in this launch
   unsigned long long* trace;  // optional: 16 globaltimer stamps of CTA (0,0,0) (nullptr in production)
+  // ---- grouped (mixture-of-experts) mode: blockIdx.y indexes a work list instead of a token tile ----
+  // item = {expert, first row, end row, 0}; expert < 0 marks an unused slot (the CTA returns at once). The weights of all
+  // local experts are stacked (JQ4: n_tiles tile rows per expert, dense: N rows per expert); N / n_tiles are per expert.
+  const int4* grp_items;
 };
 
 template <bool Q4, int BN>
@@ -149,7 +153,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   if (threadIdx.x == 0) DLV_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
-  const int n0 = n_tile * kGemmBM, m0 = m_tile * BN;
+  const int n0 = n_tile * kGemmBM;
+  int m0 = m_tile * BN, m_lim = p.M, w_tile = n_tile, w_row0 = n0;
+  if (p.grp_items != nullptr) {
+    const int4 it = p.grp_items[blockIdx.y];
+    if (it.x < 0) return;  // uniform over the cluster (its CTAs differ in blockIdx.z only); nothing is set up yet
+    m0 = it.y;
+    m_lim = it.z;
+    w_tile = it.x * p.n_tiles + n_tile;
+    w_row0 = it.x * p.N + n0;
+  }
   const int kb_begin = split * p.kb_per_split;
   const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);
   const int nkb = max(0, kb_end - kb_begin);
@@ -159,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   // tile), and requests to one line are served one after the other.
   const int rot = nkb > 0 ? static_cast<int>((static_cast<unsigned>(n_tile) * 7u + static_cast<unsigned>(m_tile) * 3u) % static_cast<unsigned>(nkb)) : 0;
 
-  auto w_tile = [&](int s, int sub) { return smem + s * L::kWStage + sub * L::kWTile; };
+  auto w_tile_ptr = [&](int s, int sub) { return smem + s * L::kWStage + sub * L::kWTile; };
   auto x_tile = [&](int s, int sub) { return smem + L::kOffX + s * L::kXStage + sub * (BN * 128); };
   auto raw_tile = [&](int s) { return smem + L::kOffRaw + s * L::kRawStage; };
   auto sc_tile = [&](int s) { return smem + L::kOffRaw + s * L::kRawStage + kGemmBM * 64; };
@@ -207,11 +220,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         if (Q4) {
           // one contiguous 10 KB stage: 8 KB of packed nibbles (already in the swizzled shared-memory order) + 2 KB of scales
           mbar_expect_tx(full, L::kRawStage);
-          tma_load_2d(smem_u32(raw_tile(s)), &map_w, full, 0, (n_tile * p.kb_total + kb) * 10);
+          tma_load_2d(smem_u32(raw_tile(s)), &map_w, full, 0, (w_tile * p.kb_total + kb) * 10);
         } else {
           mbar_expect_tx(full, L::kWStage);
-          tma_load_2d(smem_u32(w_tile(s, 0)), &map_w, full, kb * kGemmBK, n0);
-          tma_load_2d(smem_u32(w_tile(s, 1)), &map_w, full, kb * kGemmBK + 64, n0);
+          tma_load_2d(smem_u32(w_tile_ptr(s, 0)), &map_w, full, kb * kGemmBK, w_row0);
+          tma_load_2d(smem_u32(w_tile_ptr(s, 1)), &map_w, full, kb * kGemmBK + 64, w_row0);
         }
         ++issued;
       }
@@ -463,7 +476,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       // column c of the tile is finished by cluster rank c % splits; the 16 column slots of this CTA take turns
       for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
         const int m = m0 + col;
-        if (m >= p.M) break;
+        if (m >= m_lim) break;
         float4 acc = column_acc(col);
         acc.x += bias.x; acc.y += bias.y; acc.z += bias.z; acc.w += bias.w;
         store_out(m, acc);
@@ -479,7 +492,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       if (n + 3 < p.N) {
         for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
           const int m = m0 + col;
-          if (m >= p.M) break;
+          if (m >= m_lim) break;
           const float4 acc = column_acc(col);
           uint2 pk;
           pk.x = pack_bf162(acc.x, acc.y);
@@ -510,7 +523,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         const __nv_bfloat16* rbase = reinterpret_cast<const __nv_bfloat16*>(p.tp_recv[p.tp_rank]) + par_off;
         for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
           const int m = m0 + col;
-          if (m >= p.M) break;
+          if (m >= m_lim) break;
           float4 acc = bias;
           for (int src = 0; src < p.tp_size; ++src) {
             const uint2 pk = __ldcg(reinterpret_cast<const uint2*>(rbase + static_cast<long long>(src) * p.tp_slab + static_cast<long long>(m) * p.N + n));

@@ -110,8 +110,9 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
 }
 
 __global__ void __launch_bounds__(128) moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ perm, int k, int H,
-                                                         __nv_bfloat16* __restrict__ xs) {
+                                                         __nv_bfloat16* __restrict__ xs, const int* __restrict__ offsets, int e0, int ne) {
   const int row = blockIdx.x;
+  if (offsets != nullptr && (row < offsets[e0] || row >= offsets[e0 + ne])) return;  // another rank's expert
   const int t = perm[row] / k;
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
   uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(row) * H);
@@ -119,15 +120,19 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const __nv_bfloat16* __
 }
 
 __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ pos,
-                                                          const float* __restrict__ w, int k, int H, __nv_bfloat16* __restrict__ out) {
+                                                          const float* __restrict__ w, int k, int H, __nv_bfloat16* __restrict__ out,
+                                                          const int* __restrict__ offsets, int e0, int ne) {
   const int t = blockIdx.x;
+  const int lo = offsets != nullptr ? offsets[e0] : 0, hi = offsets != nullptr ? offsets[e0 + ne] : 0x7fffffff;
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
     float acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
     for (int j = 0; j < k; ++j) {
       const float wt = w[static_cast<size_t>(t) * k + j];
-      const uint4 v = reinterpret_cast<const uint4*>(ys + static_cast<size_t>(pos[static_cast<size_t>(t) * k + j]) * H)[i];
+      const int prow = pos[static_cast<size_t>(t) * k + j];
+      if (prow < lo || prow >= hi) continue;  // computed on another rank; the all-reduce adds it
+      const uint4 v = reinterpret_cast<const uint4*>(ys + static_cast<size_t>(prow) * H)[i];
       const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -154,13 +159,41 @@ void launch_moe_route(const float* logits, int T, int E, int k, int mode, int re
   moe_topk_kernel<<<(T + 7) / 8, 256, 0, st>>>(logits, T, E, k, mode, renorm, w, idx, counts);
   moe_sort_kernel<<<1, 1024, sizeof(int) * (E + 1), st>>>(idx, counts, T, E, k, offsets, perm, pos);
 }
-void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, void* xs, cudaStream_t st) {
+void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, void* xs, const int* offsets, int e0, int ne,
+                       cudaStream_t st) {
   if (rows == 0) return;
-  moe_gather_kernel<<<rows, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), perm, k, H, static_cast<__nv_bfloat16*>(xs));
+  moe_gather_kernel<<<rows, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), perm, k, H, static_cast<__nv_bfloat16*>(xs), offsets, e0, ne);
 }
-void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, int k, int H, void* out, cudaStream_t st) {
+void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, int k, int H, void* out, const int* offsets, int e0,
+                        int ne, cudaStream_t st) {
   if (T == 0) return;
-  moe_combine_kernel<<<T, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(ys), pos, w, k, H, static_cast<__nv_bfloat16*>(out));
+  moe_combine_kernel<<<T, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(ys), pos, w, k, H, static_cast<__nv_bfloat16*>(out), offsets, e0, ne);
+}
+
+// Work list of the grouped GEMM: one item {local expert, first row, end row, 0} per `bn` rows of every local expert that has
+// rows, in expert order; the rest of the `max_items` slots get expert = -1. Single CTA (at most a few hundred items).
+__global__ void __launch_bounds__(256) moe_items_kernel(const int* __restrict__ offsets, int e0, int ne, int bn, int max_items,
+                                                        int4* __restrict__ items) {
+  __shared__ int first[1025];
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < ne; ++e) {
+      first[e] = acc;
+      acc += (offsets[e0 + e + 1] - offsets[e0 + e] + bn - 1) / bn;
+    }
+    first[ne] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < ne; e += blockDim.x) {
+    const int lo = offsets[e0 + e], hi = offsets[e0 + e + 1];
+    int it = first[e];
+    for (int r = lo; r < hi && it < max_items; r += bn, ++it) items[it] = make_int4(e, r, hi, 0);
+  }
+  for (int it = first[ne] + threadIdx.x; it < max_items; it += blockDim.x) items[it] = make_int4(-1, 0, 0, 0);
+}
+void launch_moe_items(const int* offsets, int e0, int ne, int bn, int max_items, int* items, cudaStream_t st) {
+  if (ne > 1024) return;
+  moe_items_kernel<<<1, 256, 0, st>>>(offsets, e0, ne, bn, max_items, reinterpret_cast<int4*>(items));
 }
 
 }  // namespace dlv

@@ -39,6 +39,51 @@ def test_moe_route_gather_combine(E, k, mode, renorm):
     assert ((out.cpu().float() - exp).norm() / exp.norm()).item() < 1e-2
 
 
+@pytest.mark.parametrize("q4", [False, True])
+@pytest.mark.parametrize("T,E,k,N,K,e0,ne", [(40, 8, 2, 256, 512, 0, 8), (64, 16, 4, 384, 1024, 4, 8), (700, 4, 2, 192, 256, 0, 4), (3, 8, 2, 128, 2048, 6, 2)])
+def test_grouped_gemm_matches_per_expert(T, E, k, N, K, e0, ne, q4):
+    """Grouped tcgen05 GEMM over the local experts [e0, e0 + ne) of a routed batch against a per-expert fp32 product."""
+    from deliverance_b200.ckpt.jq4 import q4_dequantize, q4_quantize
+    from deliverance_b200.ckpt.safetensors_io import Q4Tensor
+    from deliverance_b200.ops import GroupedLinearWeight, LinearWeight
+
+    e = ops.require_ext()
+    g = torch.Generator().manual_seed(T + E)
+    logits = torch.randn(T, E, generator=g)
+    ws = [torch.randn(N, K, generator=g) * 0.05 for _ in range(ne)]
+    lws, dense = [], []
+    for w in ws:
+        if q4:
+            pk, sc = q4_quantize(w)
+            dense.append(q4_dequantize(pk, sc))
+            lws.append(LinearWeight(Q4Tensor(pk, sc, (N, K))).to("cuda", torch.bfloat16))
+        else:
+            dense.append(w.to(torch.bfloat16).float())
+            lws.append(LinearWeight(w.to(torch.bfloat16)).to("cuda", torch.bfloat16))
+    grouped = GroupedLinearWeight(lws)
+    w_, idx, counts, offsets, perm, pos = e.moe_route(logits.cuda(), k, 0, True)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    xs = e.moe_gather(x.cuda(), perm, k, offsets, e0, ne)
+    off = offsets.cpu().tolist()
+    for bn, splits in ((ops.moe_token_tile(T * k * ne // E, ne), 1), (16, 2), (64, 4)):
+        max_items = (T * k + bn - 1) // bn + ne
+        items = e.moe_items(offsets, e0, ne, bn, max_items)
+        it = items.cpu()
+        want_items = [(j, r, off[e0 + j + 1]) for j in range(ne) for r in range(off[e0 + j], off[e0 + j + 1], bn)]
+        assert [tuple(v[:3]) for v in it[: len(want_items)].tolist()] == want_items and (it[len(want_items):, 0] == -1).all()
+        ys = grouped.run(xs, items, bn, splits)
+        torch.cuda.synchronize()
+        ops.check_status()
+        for j in range(ne):
+            lo, hi = off[e0 + j], off[e0 + j + 1]
+            if hi == lo:
+                continue
+            rows = x[(perm.cpu()[lo:hi] // k).long()].float()
+            exp = rows @ dense[j].t()
+            got = ys[lo:hi].cpu().float()
+            assert ((got - exp).norm() / exp.norm().clamp_min(1e-6)).item() < 2e-2, (bn, splits, j)
+
+
 def _pair(tmp_path, family, **over):
     d = str(tmp_path / family)
     if family == "gpt2":

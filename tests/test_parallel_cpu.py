@@ -63,6 +63,27 @@ def test_thread_ranks_match_single(tmp_path, family, quantize):
     assert out[0] == out[1] == single[0]
 
 
+@pytest.mark.parametrize("family", ["mixtral", "qwen3_moe"])
+def test_expert_parallel_thread_ranks_match_single(tmp_path, family):
+    """Experts are split across the two ranks (whole experts per rank), attention stays tensor parallel."""
+    d = str(tmp_path / family)
+    write_tiny_model(d, family, seed=4, std=0.05)
+    cfg = load_config(d)
+    assert cfg.num_experts % 2 == 0
+    single = [None]
+    _run_rank(d, cfg, TensorParallelContext(), single, 0)
+    group = InProcessGroup(2, timeout=60)
+    out = [None, None]
+    ts = [threading.Thread(target=_run_rank, args=(d, cfg, TensorParallelContext(r, 2, InProcessCollectives(group, r)), out, r)) for r in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not isinstance(out[0], Exception), out[0]
+    assert out[0] == out[1] == single[0]
+    m = DecoderModel(cfg, "cpu", tp=TensorParallelContext(1, 2, InProcessCollectives(group, 1))).load(WeightLoader(d))
+    sparse = [lw for lw in m.layers if lw.router is not None]
+    assert sparse and all(lw.expert0 == cfg.num_experts // 2 and len(lw.experts_gate_up) == cfg.num_experts // 2 for lw in sparse)
+
+
 def test_in_process_group_reports_missing_rank():
     g = InProcessGroup(2, timeout=0.3)
     c = InProcessCollectives(g, 0)
