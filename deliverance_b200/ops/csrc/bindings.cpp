@@ -202,13 +202,14 @@ int64_t take_status(int64_t device) {
   return v;
 }
 void init_scratch(int64_t device) { scratch_for(static_cast<int>(device)); }
-// Debug: CTA (0,0,0) of every later GEMM launch stamps phase times (ns) into `buf` (int64 [16] on the device); None stops it.
+// Debug: CTA (0,0,0) of every later GEMM launch stamps phase times (ns) into buf[0..15]; every CTA with linear index c < 2048
+// stamps start / first MMA / accumulator ready / end into buf[16 + 4c ..]. `buf` is int64 [8208] on the device; None stops it.
 void gemm_trace(c10::optional<Tensor> buf) {
   if (!buf.has_value()) {
     dlv::gemm_set_trace(nullptr);
     return;
   }
-  TORCH_CHECK(buf.value().is_cuda() && buf.value().scalar_type() == at::kLong && buf.value().numel() >= 16, "trace buffer must be int64 [16] on CUDA");
+  TORCH_CHECK(buf.value().is_cuda() && buf.value().scalar_type() == at::kLong && buf.value().numel() >= 8208, "trace buffer must be int64 [8208] on CUDA");
   dlv::gemm_set_trace(reinterpret_cast<unsigned long long*>(buf.value().data_ptr<int64_t>()));
 }
 

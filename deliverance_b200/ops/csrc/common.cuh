@@ -119,6 +119,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// Warp-wide wait: one lane polls, the others sleep at the warp barrier. Hundreds of threads polling mbarriers keep the
+// shared-memory pipe busy and slow down every arrival and wait of the CTA; a pipeline stage then costs several hundred
+// nanoseconds even when no work is attached to it. All lanes of the (converged) warp must call this.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
 // ---- proxies / fences -----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

@@ -51,6 +51,22 @@ void encode_map_2d(CUtensorMap* map, int dtype_code, const void* base, uint64_t 
   if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
 }
 
+// bf16 matrix [rows, K] (K % 64 == 0) seen as [K / 64 chunks][rows][64]: one box = `box_rows` rows x 2 chunks lands in shared
+// memory as two consecutive 128B-swizzled 64-wide sub-tiles, i.e. a whole 128-k pipeline stage with ONE copy instruction
+// (a single thread can only issue a copy every ~0.3 us, whatever its size).
+void encode_map_kchunks(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint64_t pitch_bytes, uint32_t box_rows) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) throw std::runtime_error("TMA base address must be 16-byte aligned");
+  if (pitch_bytes % 16 != 0 || K % 64 != 0) throw std::runtime_error("chunked TMA map needs K % 64 == 0 and a 16-byte row pitch");
+  cuuint64_t dims[3] = {64, rows, K / 64};
+  cuuint64_t strides[2] = {pitch_bytes, 128};
+  cuuint32_t box[3] = {64, box_rows, 2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = get_encode()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled (3-D) failed with code " + std::to_string(static_cast<int>(r)));
+}
+
 // ------------------------------------------------------------------------------------------------ weight handle
 void gemm_weight_init(GemmWeightDesc* w) {
   if (w->is_q4) {
@@ -61,12 +77,15 @@ void gemm_weight_init(GemmWeightDesc* w) {
     encode_map_2d(&w->map_w, 3, w->data, stages * 10, 256, 1024, 10, 256, 0);
   } else {
     if (w->K % 8 != 0) throw std::runtime_error("dense weight needs K % 8 == 0");
-    encode_map_2d(&w->map_w, 0, w->data, w->N, w->K, static_cast<uint64_t>(w->K) * 2, kGemmBM, 64, 128);
+    w->w3d = w->K % 64 == 0;
+    if (w->w3d) encode_map_kchunks(&w->map_w, w->data, w->N, w->K, static_cast<uint64_t>(w->K) * 2, kGemmBM);
+    else encode_map_2d(&w->map_w, 0, w->data, w->N, w->K, static_cast<uint64_t>(w->K) * 2, kGemmBM, 64, 128);
   }
 }
 
 unsigned long long* g_gemm_trace = nullptr;
 void gemm_set_trace(unsigned long long* p) { g_gemm_trace = p; }
+
 
 int gemm_num_sms() {
   static int sms = 0;
@@ -183,7 +202,10 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
   p.counters = counters;
   p.wq = w->is_q4 ? static_cast<const uint8_t*>(w->data) : nullptr;
   CUtensorMap map_x;
-  encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
+  p.w3d = w->w3d ? 1 : 0;
+  p.x3d = w->K % 64 == 0 ? 1 : 0;
+  if (p.x3d) encode_map_kchunks(&map_x, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN);
+  else encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.n_tiles, p.m_tiles, p.splits);
   cfg.blockDim = dim3(kGemmThreads);
@@ -266,7 +288,10 @@ static void run_grouped(const GemmWeightDesc* w, const void* x, int rows, int ld
   p.cluster_reduce = splits > 1 ? 1 : 0;
   p.wq = w->is_q4 ? static_cast<const uint8_t*>(w->data) : nullptr;
   CUtensorMap map_x;
-  encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(rows), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
+  p.w3d = w->w3d ? 1 : 0;
+  p.x3d = w->K % 64 == 0 ? 1 : 0;
+  if (p.x3d) encode_map_kchunks(&map_x, x, static_cast<uint64_t>(rows), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN);
+  else encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(rows), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.n_tiles, max_items, splits);
   cfg.blockDim = dim3(kGemmThreads);

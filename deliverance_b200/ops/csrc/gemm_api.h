@@ -17,7 +17,8 @@ struct GemmWeightDesc {
   int N = 0, K = 0;
   bool is_q4 = false;
   const void* data = nullptr;  // bf16 [N, K] or the tile-packed JQ4 bytes
-  CUtensorMap map_w;           // dense only
+  CUtensorMap map_w;           // dense: [N, K] (3-D chunked form when w3d); JQ4: the packed stages as rows of 1 KB
+  bool w3d = false;
 };
 
 // Peer-memory state of the fused GEMM + all-reduce epilogue (all pointers are device addresses mapped in this process).

@@ -25,8 +25,9 @@
 // areas are double-buffered on the parity of a per-rank launch counter; flags are cumulative, so CUDA-graph replays need
 // no host-side reset.
 //
-// Roles per CTA (608 threads): warp 0 = weight producer (bulk copy / TMA), warp 1 = TMEM owner + MMA issuer,
-// warp 2 = activation TMA producer, warps 3..18 = JQ4 dequant (one 32-element block per thread and stage) and epilogue
+// Roles per CTA (768 threads): warps 0 + 19 = weight producers (TMA, alternate k-blocks), warp 1 = TMEM owner, warps 1 + 21..23 =
+// MMA issuers (alternate k-blocks, one accumulator each),
+// warps 2 + 20 = activation TMA producers, warps 3..18 = JQ4 dequant (one 32-element block per thread and stage) and epilogue
 // (tcgen05.ld -> fp32 tile in shared memory -> reduce over the cluster -> 8/16-byte global stores).
 //
 // This replaces the reference's CPU kernels gemm_q8_q4 / gemm_bf16_q4 / gemm_bf16
@@ -38,11 +39,10 @@ namespace dlv {
 
 constexpr int kGemmBM = 128;       // weight rows per CTA
 constexpr int kGemmBK = 128;       // reduction elements per pipeline stage
-constexpr int kGemmThreads = 608;  // 19 warps
+constexpr int kGemmThreads = 768;  // 24 warps
 constexpr int kGemmEpiThreads = 512;
 constexpr int kGemmEpiWarp0 = 3;
 constexpr int kGemmTmemCols = 512;   // whole tensor memory of the SM (one CTA per SM)
-constexpr int kGemmTmemA = 256;      // first column of the JQ4 A-operand ring (accumulator uses columns [0, BN))
 constexpr int kGemmTmemAStage = 64;  // 128 k as bf16 pairs
 
 struct GemmParams {
@@ -73,6 +73,7 @@ struct GemmParams {
   // item = {expert, first row, end row, 0}; expert < 0 marks an unused slot (the CTA returns at once). The weights of all
   // local experts are stacked (JQ4: n_tiles tile rows per expert, dense: N rows per expert); N / n_tiles are per expert.
   const int4* grp_items;
+  int x3d, w3d;  // the activation / dense weight map is the 3-D chunked form: one copy per stage instead of two
 };
 
 template <bool Q4, int BN>
@@ -83,12 +84,18 @@ struct GemmSmem {
   static constexpr int kRawStage = kGemmBM * 64 + kGemmBM * 16;  // packed nibbles (8 KB) + scales (2 KB)
   static constexpr int kBudget = 232448 - 2048;                  // dynamic smem minus barriers / alignment slack
   static constexpr int kStageOut = BN * kGemmBM * 4;             // fp32 output staging tile (aliases the rings)
-  // dense: W and X rings of equal depth. JQ4: A lives in tensor memory; X ring up to 8 stages, the rest is the packed ring.
-  static constexpr int kNW = Q4 ? 0 : ((kBudget / (kWStage + kXStage)) > 6 ? 6 : (kBudget / (kWStage + kXStage)));
-  static constexpr int kNA = 4;  // JQ4: A-operand stages in tensor memory
-  static constexpr int kNX = Q4 ? (BN <= 32 ? 8 : (BN <= 64 ? 6 : (BN <= 128 ? 3 : 2))) : kNW;
+  // Ring depths. Every ring is shared by several producers and several consumers that take alternate k-blocks (two copy
+  // warps, four dequant groups, kNI MMA issuers). mbarrier waits only know the PARITY of a phase, so a thread must see every
+  // phase of the barriers it waits on: each ring depth is a multiple of the number of its producers and of its consumers,
+  // which ties every stage to one producer and one consumer for the whole kernel.
+  static constexpr int kNI = BN <= 64 ? 4 : (BN == 128 ? 2 : 1);  // MMA-issuing warps = accumulators (see the issuer loop)
+  static constexpr int kNW = Q4 ? 0 : (BN <= 64 ? 4 : 2);         // dense: W and X rings of equal depth
+  static constexpr int kAccCols = kNI * BN;
+  static constexpr int kTmemA = kAccCols < 64 ? 64 : kAccCols;  // JQ4: the A-operand ring in tensor memory follows the accumulators
+  static constexpr int kNA = 4;                                  // one stage per dequant group
+  static constexpr int kNX = Q4 ? (BN <= 32 ? 8 : (BN <= 128 ? 4 : 2)) : kNW;
   static constexpr int kRawRoom = Q4 ? (kBudget - kNX * kXStage) / kRawStage : 0;
-  static constexpr int kNR = Q4 ? (kRawRoom > 16 ? 16 : kRawRoom) : 0;
+  static constexpr int kNR = Q4 ? (kRawRoom >= 16 ? 16 : (kRawRoom >= 12 ? 12 : (kRawRoom >= 8 ? 8 : 4))) : 0;
   static constexpr int kOffX = kNW * kWStage;
   static constexpr int kOffRaw = kOffX + kNX * kXStage;
   static constexpr int kOffCtrl = kOffRaw + kNR * kRawStage;
@@ -96,8 +103,10 @@ struct GemmSmem {
   static_assert(!Q4 || kNR >= 4, "packed-weight ring too small");
   static_assert(kNX >= 2, "activation ring too small");
   static_assert(kStageOut <= kOffCtrl, "the fp32 output staging tile must fit in the rings");
-  static_assert(kNA == 4, "the dequant warp groups map one-to-one onto the A-operand stages");
-  static_assert(kGemmTmemA + kNA * kGemmTmemAStage <= kGemmTmemCols && BN <= kGemmTmemA, "tensor memory plan");
+  static_assert(kNX % kNI == 0 && kNX % 2 == 0 && (Q4 || kNW % kNI == 0) && (!Q4 || (kNR % 4 == 0 && kNA % kNI == 0)), "ring ownership");
+  static_assert(Q4 || (kNW * (kWStage + kXStage) <= kBudget), "dense rings do not fit");
+  static_assert(!Q4 || kRawRoom >= kNR, "packed ring does not fit");
+  static_assert(kTmemA + kNA * kGemmTmemAStage <= kGemmTmemCols && kAccCols <= kTmemA, "tensor memory plan");
 };
 
 __device__ __forceinline__ uint32_t q4_pair_to_bf162(uint32_t nib4, uint32_t sel, __nv_bfloat162 s2) {
@@ -131,7 +140,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
                const __grid_constant__ CUtensorMap map_x,   // bf16 [M, K]
                const GemmParams p) {
   using L = GemmSmem<Q4, BN>;
-  constexpr int NW = L::kNW > 0 ? L::kNW : 1, NX = L::kNX, NR = L::kNR > 0 ? L::kNR : 1, NA = L::kNA;
+  constexpr int NW = L::kNW > 0 ? L::kNW : 1, NX = L::kNX, NR = L::kNR > 0 ? L::kNR : 1, NA = L::kNA, NI = L::kNI;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ctrl = smem + L::kOffCtrl;
@@ -151,6 +160,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 #define DLV_STAMP(i) do { if (tracing) p.trace[i] = globaltimer_ns(); } while (0)
   if (threadIdx.x == 0) DLV_STAMP(0);
+  const unsigned cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+#define DLV_CTA_STAMP(j) do { if (p.trace != nullptr && cta_lin < 2048u) p.trace[16 + 4 * cta_lin + (j)] = globaltimer_ns(); } while (0)
+  if (threadIdx.x == 0) DLV_CTA_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
   const int n0 = n_tile * kGemmBM;
@@ -166,7 +178,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   const int kb_begin = split * p.kb_per_split;
   const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);
   const int nkb = max(0, kb_end - kb_begin);
-  constexpr uint32_t TMEM_COLS = Q4 ? kGemmTmemCols : (BN < 32 ? 32 : BN);
+  constexpr uint32_t TMEM_COLS = Q4 ? kGemmTmemCols : (L::kAccCols < 32 ? 32 : L::kAccCols);
   // Every CTA walks its k-blocks from a different starting point: CTAs that run at the same time would otherwise all ask
   // the L2 for the same activation lines at the same moment (the activation tile of a k-block is shared by every weight
   // tile), and requests to one line are served one after the other.
@@ -190,7 +202,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       mbar_init(smem_u32(&bar_r_full[s]), 1);
       mbar_init(smem_u32(&bar_r_empty[s]), 4);
     }
-    mbar_init(smem_u32(bar_acc), 1);
+    mbar_init(smem_u32(bar_acc), NI);
     *abort_flag = 0;
     *s_last = 0;
     mbar_fence_init();
@@ -204,12 +216,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) DLV_STAMP(1);
 
-  if (warp == 0) {
-    // ---------------- weight producer: packed JQ4 stages (deep ring) or dense bf16 tiles ----------------
+  // A single thread can only issue one bulk / tensor copy about every 0.3 us, whatever the size of the copy. So every stage
+  // is ONE copy, and two warps per operand take alternate k-blocks (warps 0 + 19: weights, warps 2 + 20: activations).
+  if (warp == 0 || warp == 19) {
+    // ---------------- weight producers: packed JQ4 stages (deep ring) or dense bf16 tiles ----------------
     if (lane == 0) {
-      int issued = 0;
       constexpr int RING = Q4 ? NR : NW;
-      for (int i = 0; i < nkb; ++i) {
+      const int first_i = warp == 0 ? 0 : 1;
+      int last_issued = -1, n_issued = 0;
+      for (int i = first_i; i < nkb; i += 2) {
         const int s = i % RING;
         const uint32_t ph = (i / RING) & 1;
         uint64_t* empty = Q4 ? &bar_r_empty[s] : &bar_a_empty[s];
@@ -223,15 +238,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
           tma_load_2d(smem_u32(raw_tile(s)), &map_w, full, 0, (w_tile * p.kb_total + kb) * 10);
         } else {
           mbar_expect_tx(full, L::kWStage);
-          tma_load_2d(smem_u32(w_tile_ptr(s, 0)), &map_w, full, kb * kGemmBK, w_row0);
-          tma_load_2d(smem_u32(w_tile_ptr(s, 1)), &map_w, full, kb * kGemmBK + 64, w_row0);
+          if (p.w3d) {
+            tma_load_3d(smem_u32(w_tile_ptr(s, 0)), &map_w, full, 0, w_row0, kb * 2);
+          } else {
+            tma_load_2d(smem_u32(w_tile_ptr(s, 0)), &map_w, full, kb * kGemmBK, w_row0);
+            tma_load_2d(smem_u32(w_tile_ptr(s, 1)), &map_w, full, kb * kGemmBK + 64, w_row0);
+          }
         }
-        ++issued;
+        last_issued = i;
+        ++n_issued;
       }
       if (*abort_flag) {
         // let copies that are still in flight land before the CTA goes away (bounded: ~20 ms per stage)
-        const int first = issued > RING ? issued - RING : 0;
-        for (int i = first; i < issued; ++i) {
+        const int keep = n_issued < (RING + 1) / 2 ? n_issued : (RING + 1) / 2;
+        for (int j = 0; j < keep; ++j) {
+          const int i = last_issued - 2 * j;
           const uint32_t bar = smem_u32(Q4 ? &bar_r_full[i % RING] : &bar_a_full[i % RING]);
           const uint32_t ph = (i / RING) & 1;
           const unsigned long long t0 = globaltimer_ns();
@@ -240,24 +261,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         }
       }
     }
-  } else if (warp == 2) {
-    // ---------------- activation producer ----------------
+  } else if (warp == 2 || warp == 20) {
+    // ---------------- activation producers ----------------
     if (lane == 0) {
-      int issued = 0;
-      for (int i = 0; i < nkb; ++i) {
+      const int first_i = warp == 2 ? 0 : 1;
+      int last_issued = -1, n_issued = 0;
+      for (int i = first_i; i < nkb; i += 2) {
         const int s = i % NX;
         const uint32_t ph = (i / NX) & 1;
         if (!mbar_wait(smem_u32(&bar_x_empty[s]), ph ^ 1, abort_flag, p.status)) break;
         const uint32_t full = smem_u32(&bar_x_full[s]);
-        mbar_expect_tx(full, L::kXStage);
         const int kb = kb_begin + (i + rot >= nkb ? i + rot - nkb : i + rot);
-        tma_load_2d(smem_u32(x_tile(s, 0)), &map_x, full, kb * kGemmBK, m0);
-        tma_load_2d(smem_u32(x_tile(s, 1)), &map_x, full, kb * kGemmBK + 64, m0);
-        ++issued;
+        mbar_expect_tx(full, L::kXStage);
+        if (p.x3d) {
+          tma_load_3d(smem_u32(x_tile(s, 0)), &map_x, full, 0, m0, kb * 2);
+        } else {
+          tma_load_2d(smem_u32(x_tile(s, 0)), &map_x, full, kb * kGemmBK, m0);
+          tma_load_2d(smem_u32(x_tile(s, 1)), &map_x, full, kb * kGemmBK + 64, m0);
+        }
+        last_issued = i;
+        ++n_issued;
       }
       if (*abort_flag) {
-        const int first = issued > NX ? issued - NX : 0;
-        for (int i = first; i < issued; ++i) {
+        const int keep = n_issued < (NX + 1) / 2 ? n_issued : (NX + 1) / 2;
+        for (int j = 0; j < keep; ++j) {
+          const int i = last_issued - 2 * j;
           const uint32_t bar = smem_u32(&bar_x_full[i % NX]);
           const uint32_t ph = (i / NX) & 1;
           const unsigned long long t0 = globaltimer_ns();
@@ -266,54 +294,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer: the whole warp follows the barriers, one elected lane issues ----------------
-    constexpr uint32_t idesc = umma_idesc_bf16(kGemmBM, BN);
-    const uint64_t desc_w0 = umma_desc_k_sw128(smem_u32(smem));
-    const uint64_t desc_x0 = umma_desc_k_sw128(smem_u32(smem + L::kOffX));
-    bool ok = true;
-    for (int i = 0; i < nkb; ++i) {
-      const int sa = i % NAS, sx = i % NX;
-      ok = mbar_wait(smem_u32(&bar_a_full[sa]), (i / NAS) & 1, abort_flag, p.status);
-      ok = ok && mbar_wait(smem_u32(&bar_x_full[sx]), (i / NX) & 1, abort_flag, p.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (i == 0 && lane == 0) DLV_STAMP(2);
-      if (i == 4 && lane == 0) DLV_STAMP(9);
-      if (i == 12 && lane == 0) DLV_STAMP(10);
-      tc_fence_after();
-      if (lane == 0) {
-        // descriptor start-address field counts 16-byte units: stage strides and the 32-byte k-step are added there
-        const uint64_t dx = desc_x0 + static_cast<uint64_t>((sx * L::kXStage) >> 4);
+  } else if (warp == 1 || warp >= 21) {
+    // ---------------- MMA issuers ----------------
+    // Issuing one tcgen05.mma costs the issuing thread about 90 cycles whatever the tile shape, so with few tokens (small
+    // UMMA N) a single issuer, not the tensor pipe or the memory system, paces the kernel (8 instructions per 128-wide
+    // k-block = 0.4 us). NI warps therefore take alternate k-blocks, each into its own accumulator (columns j*BN ..), and the
+    // epilogue adds the accumulators. The whole warp follows the barriers, one lane issues.
+    const int issuer = warp == 1 ? 0 : warp - 20;
+    if (issuer < NI) {
+      constexpr uint32_t idesc = umma_idesc_bf16(kGemmBM, BN);
+      const uint64_t desc_w0 = umma_desc_k_sw128(smem_u32(smem));
+      const uint64_t desc_x0 = umma_desc_k_sw128(smem_u32(smem + L::kOffX));
+      const uint32_t tmem_acc = tmem_base + issuer * BN;
+      bool ok = true;
+      for (int i = issuer; i < nkb; i += NI) {
+        const int sa = i % NAS, sx = i % NX;
+        ok = mbar_wait(smem_u32(&bar_a_full[sa]), (i / NAS) & 1, abort_flag, p.status);
+        ok = ok && mbar_wait(smem_u32(&bar_x_full[sx]), (i / NX) & 1, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (i == 0 && lane == 0) { DLV_STAMP(2); DLV_CTA_STAMP(1); }
+        tc_fence_after();
+        if (lane == 0) {
+          // descriptor start-address field counts 16-byte units: stage strides and the 32-byte k-step are added there
+          const uint64_t dx = desc_x0 + static_cast<uint64_t>((sx * L::kXStage) >> 4);
 #pragma unroll
-        for (int k4 = 0; k4 < 8; ++k4) {
-          const int sub = k4 >> 2, kk = k4 & 3;
-          const uint64_t db = dx + static_cast<uint64_t>((sub * (BN * 128) + kk * 32) >> 4);
-          const uint32_t acc = (i > 0 || k4 > 0) ? 1u : 0u;
-          if (Q4) {
-            umma_bf16_ts(tmem_base, tmem_base + kGemmTmemA + sa * kGemmTmemAStage + k4 * 8, db, idesc, acc);
-          } else {
-            const uint64_t da = desc_w0 + static_cast<uint64_t>((sa * L::kWStage + sub * L::kWTile + kk * 32) >> 4);
-            umma_bf16(tmem_base, da, db, idesc, acc);
+          for (int k4 = 0; k4 < 8; ++k4) {
+            const int sub = k4 >> 2, kk = k4 & 3;
+            const uint64_t db = dx + static_cast<uint64_t>((sub * (BN * 128) + kk * 32) >> 4);
+            const uint32_t acc = (i >= NI || k4 > 0) ? 1u : 0u;
+            if (Q4) {
+              umma_bf16_ts(tmem_acc, tmem_base + L::kTmemA + sa * kGemmTmemAStage + k4 * 8, db, idesc, acc);
+            } else {
+              const uint64_t da = desc_w0 + static_cast<uint64_t>((sa * L::kWStage + sub * L::kWTile + kk * 32) >> 4);
+              umma_bf16(tmem_acc, da, db, idesc, acc);
+            }
+          }
+          umma_commit(smem_u32(&bar_a_empty[sa]));
+          umma_commit(smem_u32(&bar_x_empty[sx]));
+        }
+        __syncwarp();
+      }
+      if (lane == 0) {
+        if (issuer == 0) DLV_STAMP(3);
+        umma_commit(smem_u32(bar_acc));  // one arrival per issuer
+        if (!ok) {
+          // outstanding MMAs must retire before TMEM is released
+          const unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(bar_acc), 0) && globaltimer_ns() - t0 < 20000000ull) {
           }
         }
-        umma_commit(smem_u32(&bar_a_empty[sa]));
-        umma_commit(smem_u32(&bar_x_empty[sx]));
       }
       __syncwarp();
     }
-    if (lane == 0) {
-      DLV_STAMP(3);
-      umma_commit(smem_u32(bar_acc));
-      if (!ok) {
-        // outstanding MMAs must retire before TMEM is released
-        const unsigned long long t0 = globaltimer_ns();
-        while (!mbar_try_wait(smem_u32(bar_acc), 0) && globaltimer_ns() - t0 < 20000000ull) {
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp >= kGemmEpiWarp0) {
+  } else if (warp >= kGemmEpiWarp0 && warp < kGemmEpiWarp0 + 16) {
     // ---------------- dequant + epilogue warps (512 threads) ----------------
     const int t = threadIdx.x - kGemmEpiWarp0 * 32;
     const int we = warp - kGemmEpiWarp0;
@@ -337,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         // the tensor-memory stage is free once the MMAs of k-block i - NA have retired
         if (!mbar_wait(smem_u32(&bar_a_empty[sa]), ((i / NA) & 1) ^ 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t tdst = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kGemmTmemA + sa * kGemmTmemAStage;
+        const uint32_t tdst = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + L::kTmemA + sa * kGemmTmemAStage;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           const __nv_bfloat162 s2 = __float2bfloat162_rn(sc[b]);
@@ -369,7 +403,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     // raised before the accumulator barrier can complete), so the named barriers below never miss a thread.
     asm volatile("bar.sync 1, 512;" ::: "memory");
     ok = (*abort_flag == 0);
-    if (t == 0) DLV_STAMP(4);
+    if (t == 0) { DLV_STAMP(4); DLV_CTA_STAMP(2); }
     if (ok) {
       tc_fence_after();
       constexpr int GROUPS = BN >= 32 ? 4 : BN / 8;  // warps that share a quarter split the columns
@@ -381,12 +415,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * COLS;
         float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll 1
+        const int nacc = nkb < NI ? nkb : NI;  // issuers without a k-block never wrote their accumulator
         for (int c0 = 0; c0 < COLS; c0 += CH) {
-          uint32_t v[CH];
-          if constexpr (CH == 16) tmem_ld_x16(taddr0 + c0, v); else tmem_ld_x8(taddr0 + c0, v);
-          tmem_ld_wait();
+          float sum[CH];
 #pragma unroll
-          for (int j = 0; j < CH; ++j) stage[(grp * COLS + c0 + j) * kGemmBM + row] = nkb > 0 ? __uint_as_float(v[j]) : 0.f;
+          for (int j = 0; j < CH; ++j) sum[j] = 0.f;
+          for (int a = 0; a < nacc; ++a) {
+            uint32_t v[CH];
+            if constexpr (CH == 16) tmem_ld_x16(taddr0 + a * BN + c0, v); else tmem_ld_x8(taddr0 + a * BN + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CH; ++j) sum[j] += __uint_as_float(v[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < CH; ++j) stage[(grp * COLS + c0 + j) * kGemmBM + row] = sum[j];
         }
       }
     }
@@ -397,7 +439,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   const bool clustered = p.splits > 1 && p.cluster_reduce;
   if (clustered) cluster_sync_all();  // every CTA of the cluster has its partial tile in shared memory (or is aborting)
   if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(6);
-  if (warp >= kGemmEpiWarp0 && *abort_flag == 0) {
+  if (warp >= kGemmEpiWarp0 && warp < kGemmEpiWarp0 + 16 && *abort_flag == 0) {
     const int t = threadIdx.x - kGemmEpiWarp0 * 32;
     const int row4 = (t & 31) * 4, csel = t >> 5;  // 4 consecutive weight rows, column slot 0..15
     const int n = n0 + row4;
@@ -554,8 +596,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if (threadIdx.x == 0) DLV_STAMP(8);
+  if (threadIdx.x == 0) { DLV_STAMP(8); DLV_CTA_STAMP(3); }
 #undef DLV_STAMP
+#undef DLV_CTA_STAMP
 }
 
 }  // namespace dlv
