@@ -272,10 +272,16 @@ class Engine:
         return self._sample_and_advance(reqs, logits)
 
     def _splits(self, B: int) -> int:
-        kvh = self.model.n_kv
-        ctas = max(1, B * kvh)
-        sms = 148
-        return int(max(1, min(32, (2 * sms) // ctas)))
+        """Split-KV factor of decode attention: the smallest one that fills the resident CTA slots (two CTAs per SM) evenly."""
+        ctas = max(1, B * self.model.n_kv)
+        slots = 2 * 148
+        best, best_eff = 1, 0.0
+        for s in range(1, 33):
+            n = ctas * s
+            eff = n / (-(-n // slots) * slots)
+            if eff > best_eff + 0.03:
+                best, best_eff = s, eff
+        return best
 
     def _graph_decode(self, seqs: list[dict]) -> torch.Tensor:
         B = len(seqs)

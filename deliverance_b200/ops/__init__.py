@@ -265,11 +265,12 @@ def decode_splits(num_seqs: int, kv_heads: int, max_ctx: int, sms: int = 148) ->
     return int(max(1, min(want, tiles // 4 if tiles >= 8 else 1, 64)))
 
 
-def decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, H, scale, softcap=0.0, window=0, splits=1):
-    """One query row per sequence against the paged cache. q ``[B, H*D]`` -> ``[B, H*D]``."""
+def decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, H, scale, softcap=0.0, window=0, splits=1, impl=0):
+    """One query row per sequence against the paged cache. q ``[B, H*D]`` -> ``[B, H*D]``. ``impl`` 0 = tensor-core kernel
+    (GQA group as MMA rows) when the shape allows, 1 = CUDA-core kernel."""
     if _cuda(q):
         _count(2 if splits > 1 else 1)
-        return require_ext().decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, H, scale, softcap, window, splits)
+        return require_ext().decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, H, scale, softcap, window, splits, impl)
     B = q.shape[0]
     D = k_cache.shape[-1]
     qs = torch.arange(B)

@@ -336,6 +336,281 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
   return static_cast<uint32_t>(row * D * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
+// =====================================================================================================================
+// Decode on the tensor cores (GQA groups of up to 16 query heads)
+// =====================================================================================================================
+// The CUDA-core decode kernel above needs one FMA per (key, dim, head) and is issue bound long before the KV stream reaches
+// the HBM rate. Here the G query heads that share a KV head are the rows of a 16 x D MMA A-operand (rows >= G are zero), so a
+// 16-key slice of K / V costs 2 * D / 8 mma.sync instead of 16 * D * G FMAs.
+//   grid (num_seqs, KV, splits), 4 warps. The warps work independently: warp w takes the 16-key slices w, w + 4, ... of the
+//   CTA's key range through its own three-stage cp.async ring (no CTA-wide barrier in the loop) and keeps its own online-
+//   softmax state; the four states are merged through shared memory at the end. A slice never straddles a page
+//   (page_size % 16 == 0), so it needs one block-table lookup.
+template <int D>
+struct DecodeMma {
+  static constexpr int kStages = 3;
+  static constexpr int kSliceBytes = 16 * D * 2;                 // K or V of one slice
+  static constexpr int kWarpBytes = kStages * 2 * kSliceBytes;   // ring of one warp
+  static constexpr int kQBytes = 16 * D * 2;                     // D > 128: the query tile stays in shared memory
+  static constexpr int kRing = 4 * kWarpBytes;
+  static constexpr int kMerge = 4 * 16 * (D + 2) * 4;            // per warp: 16 rows x (D + m + l) fp32 (aliases the rings)
+  static constexpr int kBytes = (kRing > kMerge ? kRing : kMerge) + (D > 128 ? kQBytes : 0);
+};
+
+template <int D>
+__global__ void __launch_bounds__(128, (D <= 128 ? 2 : 1)) decode_attn_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ k_cache,
+    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int bt_stride,
+    const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    int H, int KV, int page_size, float scale, float softcap, int window, int splits) {
+  using L = DecodeMma<D>;
+  constexpr int CPR = D / 8;  // 16-byte chunks per row
+  extern __shared__ __align__(128) uint8_t msm[];
+  const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int G = H / KV;
+  const int ctx = ctx_lens[b];
+  const int first_key = (window > 0 && ctx > window) ? ctx - window : 0;
+  // slices of 16 keys; the CTA's share of [first_key, ctx)
+  const int sl_lo = first_key / 16, sl_hi = (ctx + 15) / 16;
+  const int per = (sl_hi - sl_lo + splits - 1) / splits;
+  const int s0 = sl_lo + sp * per, s1 = min(sl_hi, s0 + per);
+  uint8_t* ring = msm + warp * L::kWarpBytes;
+  const uint32_t ring_u = smem_u32(ring);
+  const __nv_bfloat16* qrow = q + static_cast<long long>(b) * q_stride + static_cast<long long>(kvh) * G * D;
+
+  // ---- query A-fragments: registers (D <= 128) or a swizzled shared tile read with ldmatrix (D = 256)
+  uint32_t qa[D <= 128 ? D / 16 : 1][4];
+  uint8_t* sQ = msm + (L::kRing > L::kMerge ? L::kRing : L::kMerge);
+  if constexpr (D <= 128) {
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int d0 = ks * 16 + 2 * t4;
+      qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + g * D + d0) : 0u;
+      qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (g + 8) * D + d0) : 0u;
+      qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + g * D + d0 + 8) : 0u;
+      qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (g + 8) * D + d0 + 8) : 0u;
+    }
+  } else {
+    for (int c = tid; c < 16 * CPR; c += 128) {
+      const int r = c / CPR, cc = c % CPR;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < G) v = *reinterpret_cast<const uint4*>(qrow + r * D + cc * 8);
+      *reinterpret_cast<uint4*>(sQ + swz<D>(r, cc)) = v;
+    }
+    __syncthreads();
+  }
+
+  auto load_slice = [&](int sl, int stage) {
+    // 16 keys x D of K and V: 2 * 16 * CPR chunks over 32 lanes
+    const int key0 = sl * 16;
+    const int page = block_tables[static_cast<long long>(b) * bt_stride + key0 / page_size];
+    const long long base = ((static_cast<long long>(page) * KV + kvh) * page_size + key0 % page_size) * D;
+    const uint32_t kdst = ring_u + stage * 2 * L::kSliceBytes, vdst = kdst + L::kSliceBytes;
+#pragma unroll
+    for (int i = 0; i < 16 * CPR / 32; ++i) {
+      const int c = i * 32 + lane;
+      const int r = c / CPR, cc = c % CPR;
+      const bool valid = key0 + r < ctx;
+      const long long off = base + static_cast<long long>(valid ? r : 0) * D + cc * 8;
+      cp_async16(kdst + swz<D>(r, cc), k_cache + off, valid);
+      cp_async16(vdst + swz<D>(r, cc), v_cache + off, valid);
+    }
+  };
+  // ---- per-warp pipeline over its slices
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int first = s0 + warp;
+  const int n_mine = first < s1 ? (s1 - first + 3) / 4 : 0;
+#pragma unroll
+  for (int j = 0; j < L::kStages - 1; ++j) {
+    if (j < n_mine) load_slice(first + 4 * j, j);
+    cp_async_commit();
+  }
+  for (int j = 0; j < n_mine; ++j) {
+    const int stage = j % L::kStages;
+    if (j + L::kStages - 1 < n_mine) load_slice(first + 4 * (j + L::kStages - 1), (j + L::kStages - 1) % L::kStages);
+    cp_async_commit();
+    cp_async_wait<L::kStages - 1>();
+    __syncwarp();
+    const int key0 = (first + 4 * j) * 16;
+    const uint32_t kbase = ring_u + stage * 2 * L::kSliceBytes, vbase = kbase + L::kSliceBytes;
+    // S (16 heads x 16 keys) = Q K^T
+    float sc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(kbase + swz<D>((lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+      if constexpr (D <= 128) {
+        mma_bf16_16816(sc[0], qa[ks], b0, b1);
+        mma_bf16_16816(sc[1], qa[ks], b2, b3);
+      } else {
+        uint32_t a[4];
+        ldmatrix_x4(smem_u32(sQ) + swz<D>((lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)), a[0], a[1], a[2], a[3]);
+        mma_bf16_16816(sc[0], a, b0, b1);
+        mma_bf16_16816(sc[1], a, b2, b3);
+      }
+    }
+    // scale, softcap, mask (keys outside [first_key, ctx)), online softmax per head row
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + nt * 8 + 2 * t4 + (e & 1);
+        float v = softcap_apply(sc[nt][e] * scale, softcap);
+        v = (key < ctx && key >= first_key) ? v : -INFINITY;
+        sc[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float alpha[2], m_new[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      m_new[r] = fmaxf(m_run[r], mx[r]);
+      alpha[r] = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - m_new[r]);
+      m_run[r] = m_new[r];
+    }
+    float rs[2] = {0.f, 0.f};
+    uint32_t pa[4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      float pr[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mm = m_new[e >> 1];
+        pr[e] = (sc[nt][e] == -INFINITY || mm == -INFINITY) ? 0.f : __expf(sc[nt][e] - mm);
+        rs[e >> 1] += pr[e];
+      }
+      pa[nt * 2 + 0] = pack_bf162(pr[0], pr[1]);
+      pa[nt * 2 + 1] = pack_bf162(pr[2], pr[3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+      l_run[r] = l_run[r] * alpha[r] + rs[r];
+    }
+    const bool rescale = alpha[0] != 1.f || alpha[1] != 1.f;
+    if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= alpha[0];
+        o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1];
+        o[i][3] *= alpha[1];
+      }
+    }
+    // O (16 heads x D) += P V
+#pragma unroll
+    for (int dt = 0; dt < D / 8; dt += 2) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(vbase + swz<D>((lane & 7) + ((lane >> 3) & 1) * 8, dt + (lane >> 4)), b0, b1, b2, b3);
+      mma_bf16_16816(o[dt], pa, b0, b1);
+      mma_bf16_16816(o[dt + 1], pa, b2, b3);
+    }
+    __syncwarp();  // the stage is refilled by this warp's next load_slice
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its ring: the merge area aliases the rings
+
+  // ---- merge the four warps: each stores its rows < G as [row][D + 2] = O (unnormalised), m, l
+  float* mg = reinterpret_cast<float*>(msm);
+  {
+    float* mine = mg + static_cast<size_t>(warp) * 16 * (D + 2);
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      const int d = dt * 8 + 2 * t4;
+      if (g < G) *reinterpret_cast<float2*>(mine + g * (D + 2) + d) = make_float2(o[dt][0], o[dt][1]);
+      if (g + 8 < G) *reinterpret_cast<float2*>(mine + (g + 8) * (D + 2) + d) = make_float2(o[dt][2], o[dt][3]);
+    }
+    if (t4 == 0) {
+      if (g < G) {
+        mine[g * (D + 2) + D] = m_run[0];
+        mine[g * (D + 2) + D + 1] = l_run[0];
+      }
+      if (g + 8 < G) {
+        mine[(g + 8) * (D + 2) + D] = m_run[1];
+        mine[(g + 8) * (D + 2) + D + 1] = l_run[1];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * (D / 2); idx += 128) {
+    const int r = idx / (D / 2), d = (idx % (D / 2)) * 2;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, mg[(w * 16 + r) * (D + 2) + D]);
+    float n0 = 0.f, n1 = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* row = mg + (w * 16 + r) * (D + 2);
+      const float wt = (row[D] == -INFINITY) ? 0.f : __expf(row[D] - m);
+      n0 += wt * row[d];
+      n1 += wt * row[d + 1];
+      den += wt * row[D + 1];
+    }
+    const int h = kvh * G + r;
+    if (splits == 1) {
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      *reinterpret_cast<uint32_t*>(out + (static_cast<long long>(b) * H + h) * D + d) = pack_bf162(n0 * inv, n1 * inv);
+    } else {
+      const long long base = (static_cast<long long>(b) * H + h) * splits + sp;
+      *reinterpret_cast<float2*>(part_o + base * D + d) = make_float2(n0, n1);
+      if (d == 0) {
+        part_ml[base * 2] = m;
+        part_ml[base * 2 + 1] = den;
+      }
+    }
+  }
+}
+
+template <int D>
+static int launch_decode_mma_t(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
+                               const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int page, float scale,
+                               float cap, int window, int splits, cudaStream_t st) {
+  using L = DecodeMma<D>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(decode_attn_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    attr_done = true;
+  }
+  dim3 grid(B, KV, splits);
+  decode_attn_mma_kernel<D><<<grid, 128, L::kBytes, st>>>(static_cast<const __nv_bfloat16*>(q), q_stride,
+                                                          static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt,
+                                                          bt_stride, ctx, static_cast<__nv_bfloat16*>(out), po, pml, H, KV, page, scale, cap,
+                                                          window, splits);
+  if (splits > 1) {
+    dim3 g2(B, H);
+    decode_merge_kernel<<<g2, D, 0, st>>>(po, pml, static_cast<__nv_bfloat16*>(out), H, D, splits);
+  }
+  return 0;
+}
+
+// impl: 0 = tensor-core kernel when it applies (group <= 16, page_size % 16 == 0), 1 = CUDA-core kernel
+int launch_decode_attention_impl(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
+                                 const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int D, int page, float scale,
+                                 float cap, int window, int splits, int impl, cudaStream_t st) {
+  if (B == 0) return 0;
+  const int G = H / KV;
+  if (impl == 0 && G <= 16 && page % 16 == 0 && (q_stride % 2) == 0) {
+    switch (D) {
+      case 64: return launch_decode_mma_t<64>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, B, H, KV, page, scale, cap, window, splits, st);
+      case 128: return launch_decode_mma_t<128>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, B, H, KV, page, scale, cap, window, splits, st);
+      case 256: return launch_decode_mma_t<256>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, B, H, KV, page, scale, cap, window, splits, st);
+      default: return 1;
+    }
+  }
+  return launch_decode_attention(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, B, H, KV, D, page, scale, cap, window, splits, st);
+}
+
 // grid (num_q_tiles, H), 128 threads; tile i covers query rows [tile_q0[i], tile_q0[i] + 64) of sequence tile_seq[i]
 template <int D>
 __global__ void __launch_bounds__(128) prefill_attn_kernel(

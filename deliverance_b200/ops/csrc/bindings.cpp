@@ -364,7 +364,7 @@ void rope_kv(Tensor& qkv, const Tensor& positions, c10::optional<Tensor> slots, 
 // ---- attention ------------------------------------------------------------------------------------------------------
 // q: view [B, H*D] bf16 with arbitrary row stride (the q part of the fused qkv activation)
 Tensor decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables, const Tensor& ctx_lens,
-                        int64_t H, double scale, double softcap, int64_t window, int64_t splits) {
+                        int64_t H, double scale, double softcap, int64_t window, int64_t splits, int64_t impl) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 2 && q.stride(1) == 1, "q must be bf16 [B, H*D]");
   check_bf16(k_cache, "k_cache");
   check_bf16(v_cache, "v_cache");
@@ -387,10 +387,10 @@ Tensor decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_
     pop = po.data_ptr<float>();
     pmlp = pml.data_ptr<float>();
   }
-  int rc = dlv::launch_decode_attention(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(),
-                                        static_cast<int>(block_tables.stride(0)), ctx_lens.data_ptr<int>(), out.data_ptr(), pop, pmlp, B,
-                                        static_cast<int>(H), KV, D, page, static_cast<float>(scale), static_cast<float>(softcap),
-                                        static_cast<int>(window), static_cast<int>(splits), cur_stream());
+  int rc = dlv::launch_decode_attention_impl(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(),
+                                             static_cast<int>(block_tables.stride(0)), ctx_lens.data_ptr<int>(), out.data_ptr(), pop, pmlp, B,
+                                             static_cast<int>(H), KV, D, page, static_cast<float>(scale), static_cast<float>(softcap),
+                                             static_cast<int>(window), static_cast<int>(splits), static_cast<int>(impl), cur_stream());
   TORCH_CHECK(rc == 0, "decode attention: unsupported head_dim / group size (code ", rc, ")");
   check_last_error("decode_attention");
   return out;
@@ -622,7 +622,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding", &embedding, py::arg("table"), py::arg("ids"), py::arg("scale") = 1.0, py::arg("pos_table") = py::none(),
         py::arg("pos") = py::none(), py::arg("type_table") = py::none(), py::arg("types") = py::none());
   m.def("rope_kv", &rope_kv);
-  m.def("decode_attention", &decode_attention);
+  m.def("decode_attention", &decode_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("block_tables"), py::arg("ctx_lens"),
+        py::arg("H"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("window") = 0, py::arg("splits") = 1, py::arg("impl") = 0);
   m.def("prefill_attention", &prefill_attention);
   m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("logits_post", &logits_post, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);

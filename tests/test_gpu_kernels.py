@@ -134,11 +134,15 @@ def _paged_setup(ctx_lens, KV, D, page=32, seed=0):
     return kc, vc, bt
 
 
-@pytest.mark.parametrize("D,H,KV", [(128, 32, 8), (64, 32, 4), (256, 16, 8), (128, 8, 8), (128, 14, 2)])
+@pytest.mark.parametrize("impl", [0, 1])
+@pytest.mark.parametrize("D,H,KV", [(128, 32, 8), (64, 32, 4), (256, 16, 8), (128, 8, 8), (128, 14, 2), (64, 32, 2)])
 @pytest.mark.parametrize("splits", [1, 4])
 @pytest.mark.parametrize("softcap,window", [(0.0, 0), (50.0, 0), (0.0, 48)])
-def test_decode_attention(D, H, KV, splits, softcap, window):
-    ctx = [1, 31, 32, 33, 100, 257]
+def test_decode_attention(D, H, KV, splits, softcap, window, impl):
+    """impl 0 = tensor-core kernel (GQA group as MMA rows), impl 1 = CUDA-core kernel; both against the fp32 reference."""
+    if impl == 1 and H // KV > 8:
+        pytest.skip("the CUDA-core kernel covers groups of up to 8 heads")
+    ctx = [1, 31, 32, 33, 100, 257, 700]
     kc, vc, bt = _paged_setup(ctx, KV, D)
     B = len(ctx)
     q = (torch.randn(B, H * D) * 0.5).to(torch.bfloat16)
@@ -146,7 +150,7 @@ def test_decode_attention(D, H, KV, splits, softcap, window):
     cl = torch.tensor(ctx, dtype=torch.int32)
     o_ref = ref.paged_attention(q.float().reshape(B, H, D), kc.float(), vc.float(), bt, torch.arange(B), torch.ones(B, dtype=torch.long),
                                 cl, scale, softcap, window, True).reshape(B, H * D)
-    o = ops.decode_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cl.to(DEV), H, scale, softcap, window, splits)
+    o = ops.decode_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cl.to(DEV), H, scale, softcap, window, splits, impl)
     assert _rel(o.cpu(), o_ref) < 1e-2
 
 
