@@ -48,6 +48,7 @@ class Request:
     t_done: float = 0.0
     limit: int = 0  # absolute position limit
     cancelled: bool = False
+    pending: int = 0  # tokens launched on the device but not yet read by the host (lookahead decode)
     error: Optional[str] = None
     state_snapshots: dict = field(default_factory=dict)
 
@@ -76,6 +77,7 @@ class EngineConfig:
     num_pages: Optional[int] = None  # default: sized from free device memory
     kv_memory_fraction: float = 0.85
     cuda_graphs: bool = True
+    lookahead: bool = True  # overlap the host bookkeeping of step N with the device work of step N + 1 (greedy graph decode)
     kv: KvCacheSettings = field(default_factory=KvCacheSettings)
     max_state_slots: int = 0
 
@@ -111,6 +113,10 @@ class Engine:
                         "graph_replays": 0, "kernel_launches": 0}
         self.use_graphs = bool(self.config.cuda_graphs and self.device.type == "cuda")
         self.hybrid = mamba_shapes is not None
+        # one-step lookahead of greedy graph decode: the step in flight whose sampled tokens the host has not read yet
+        self._inflight: Optional[dict] = None
+        # ("force" runs the same schedule without CUDA graphs: the host-side logic is then testable on a CPU)
+        self.lookahead = bool(self.config.lookahead and (self.use_graphs or self.config.lookahead == "force"))
         if self.device.type == "cuda":
             e = ops.require_ext()
             e.init_scratch(self.device.index if self.device.index is not None else torch.cuda.current_device())
@@ -157,7 +163,7 @@ class Engine:
             self._finish(r, reason)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._inflight is not None)
 
     # ------------------------------------------------------------------------------------------------ scheduling
     def _admit(self, r: Request) -> bool:
@@ -196,20 +202,30 @@ class Engine:
             r.state_slot = -1
 
     def step(self) -> list[Request]:
-        """Run one engine step; returns the requests that finished in it."""
+        """Run one engine step; returns the requests that finished in it. With lookahead decode the tokens of a decode step are
+        read (and its finished requests reported) by the next call, while the device already runs the following step."""
         self.metrics["steps"] += 1
+        finished: list[Request] = []
         for r in [x for x in self.running if x.cancelled]:
-            self._finish(r, FinishReason.CANCELLED)
+            if r.pending == 0:
+                self._finish(r, FinishReason.CANCELLED)
+                finished.append(r)
+        if self.waiting and self._inflight is not None and len(self.running) < self.config.max_seqs:
+            finished += self._drain()  # admissions and prefill work on settled request state
         while self.waiting and self._admit(self.waiting[0]):
             self.waiting.pop(0)
         prefill = [r for r in self.running if r.computed < len(r.prompt)]
         if prefill:
-            return self._prefill_step(prefill)
+            finished += self._drain()
+            prefill = [r for r in prefill if r.state != FINISHED]
+            return finished + (self._prefill_step(prefill) if prefill else [])
         if self.running:
-            return self._decode_step(list(self.running))
+            return finished + self._decode_step(list(self.running))
+        if self._inflight is not None:
+            return finished + self._drain()
         if self.waiting:
             raise MemoryError("waiting requests cannot be admitted: KV cache too small for the prompt")
-        return []
+        return finished
 
     # ------------------------------------------------------------------------------------------------ prefill
     def _prefill_step(self, reqs: list[Request]) -> list[Request]:
@@ -253,14 +269,24 @@ class Engine:
     def _decode_inputs(self, reqs: list[Request]):
         seqs = []
         for r in reqs:
-            pos = r.total_len - 1  # position of the token being fed (the last sampled one)
+            pos = r.total_len - 1 + r.pending  # position of the token being fed (the last sampled one)
             self.kv.ensure_pages(r.pages, pos + 1)
-            seqs.append({"tokens": [r.output[-1]], "start": pos, "pages": r.pages, "state_slot": max(r.state_slot, 0)})
+            seqs.append({"tokens": [r.output[-1] if r.output else 0], "start": pos, "pages": r.pages, "state_slot": max(r.state_slot, 0)})
         return seqs
 
+    def _plain_greedy(self, reqs: list[Request]) -> bool:
+        return all(r.guide is None and r.sampling.greedy and not r.params.logprobs for r in reqs)
+
     def _decode_step(self, reqs: list[Request]) -> list[Request]:
+        B = len(reqs)
+        if self.lookahead and B <= _BUCKETS[-1] and self._plain_greedy(reqs):
+            return self._lookahead_decode(reqs)
+        finished = self._drain()
+        reqs = [r for r in reqs if r.state != FINISHED]
+        if not reqs:
+            return finished
+        B = len(reqs)
         seqs = self._decode_inputs(reqs)
-        B = len(seqs)
         self.metrics["decode_steps"] += 1
         self.metrics["decode_tokens"] += B
         if self.use_graphs and B <= _BUCKETS[-1]:
@@ -269,7 +295,76 @@ class Engine:
             batch = make_batch(seqs, self.page_size, self.device)
             batch.decode_splits = self._splits(B)
             logits = self.model.forward(batch, self.kv)
-        return self._sample_and_advance(reqs, logits)
+        return finished + self._sample_and_advance(reqs, logits)
+
+    def _lookahead_decode(self, reqs: list[Request]) -> list[Request]:
+        """Launch the decode step of ``reqs`` with the previous step's tokens still on the device, then settle the previous step
+        on the host while this one runs. A request that turns out to have finished in the previous step has one surplus token
+        computed, which is dropped; its pages are released only after this launch, so nothing reads them late."""
+        prev = self._inflight
+        B = len(reqs)
+        dev_tokens = None
+        if prev is not None:
+            where = {id(r): i for i, r in enumerate(prev["reqs"])}
+            if any(r.pending and id(r) not in where for r in reqs) or any(not r.pending for r in reqs):
+                # the batch gained a member that is not part of the step in flight: settle first
+                finished = self._drain()
+                reqs = [r for r in reqs if r.state != FINISHED]
+                return finished + (self._decode_step(reqs) if reqs else [])
+            rows = [where[id(r)] for r in reqs]
+            dev_tokens = prev["tokens"]
+            if rows != list(range(len(prev["reqs"]))):
+                dev_tokens = dev_tokens.index_select(0, torch.tensor(rows, device=dev_tokens.device))
+        seqs = self._decode_inputs(reqs)
+        self.metrics["decode_steps"] += 1
+        self.metrics["decode_tokens"] += B
+        if self.use_graphs:
+            logits = self._graph_decode(seqs, dev_tokens)[:B]
+        else:
+            if dev_tokens is not None:
+                for sq, t in zip(seqs, dev_tokens.tolist()):
+                    sq["tokens"] = [int(t)]
+            batch = make_batch(seqs, self.page_size, self.device)
+            batch.decode_splits = self._splits(B)
+            logits = self.model.forward(batch, self.kv)
+        idx, _ = ops.argmax(logits)
+        ev = None
+        if self.device.type == "cuda":
+            slot = self.metrics["decode_steps"] & 1
+            if not hasattr(self, "_tok_host"):
+                self._tok_host = [torch.zeros(_BUCKETS[-1], dtype=torch.int64).pin_memory() for _ in range(2)]
+            host = self._tok_host[slot]
+            host[:B].copy_(idx, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        else:
+            host = idx.clone()
+        for r in reqs:
+            r.pending = 1
+        self._inflight = {"reqs": list(reqs), "tokens": idx, "host": host, "event": ev}
+        return self._settle(prev) if prev is not None else []
+
+    def _settle(self, step: dict) -> list[Request]:
+        """Read the sampled tokens of a launched step and run the per-request bookkeeping."""
+        if step["event"] is not None:
+            step["event"].synchronize()
+        tokens = step["host"][: len(step["reqs"])].tolist()
+        live, toks = [], []
+        for r, t in zip(step["reqs"], tokens):
+            if r.state != FINISHED:
+                r.pending = 0
+                live.append(r)
+                toks.append(t)
+        finished = self._advance(live, toks, [None] * len(live))
+        if self._inflight is not None and self._inflight is not step:
+            for r in live:  # still part of the step that is running now
+                if r.state != FINISHED and any(r is x for x in self._inflight["reqs"]):
+                    r.pending = 1
+        return finished
+
+    def _drain(self) -> list[Request]:
+        step, self._inflight = self._inflight, None
+        return self._settle(step) if step is not None else []
 
     def _splits(self, B: int) -> int:
         """Split-KV factor of decode attention: the smallest one that fills the resident CTA slots (two CTAs per SM) evenly."""
@@ -283,7 +378,7 @@ class Engine:
                 best, best_eff = s, eff
         return best
 
-    def _graph_decode(self, seqs: list[dict]) -> torch.Tensor:
+    def _graph_decode(self, seqs: list[dict], dev_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         B = len(seqs)
         bucket = next(b for b in _BUCKETS if b >= B)
         g = self._graphs.get(bucket)
@@ -317,6 +412,8 @@ class Engine:
             bt[n:, :1] = 0
         b: ForwardBatch = g["batch"]
         b.token_ids.copy_(h["tok"], non_blocking=True)
+        if dev_tokens is not None:  # lookahead: the previous step's samples never left the device
+            b.token_ids[:n].copy_(dev_tokens[:n])
         b.positions.copy_(h["pos"], non_blocking=True)
         b.slots.copy_(h["slots"], non_blocking=True)
         b.ctx_len.copy_(h["ctx"], non_blocking=True)
@@ -391,6 +488,9 @@ class Engine:
             if mask is not None or cfg.final_softcap > 0 or inv_scale != 1.0:
                 logits = ops.logits_post(logits if not self.use_graphs else logits.clone(), mask, cfg.final_softcap, inv_scale)
             tokens, lps = self.sampler.sample(logits, [r.sampling for r in reqs])
+        return self._advance(reqs, tokens, lps)
+
+    def _advance(self, reqs: list[Request], tokens: list, lps: list) -> list[Request]:
         now = time.perf_counter()
         finished = []
         for r, tok, lp in zip(reqs, tokens, lps):

@@ -165,3 +165,50 @@ def test_cancel_and_callback_error(tiny):
     r2 = eng.add_request([4, 5, 6], GeneratorParameters(max_tokens=50), on_token=boom)
     eng.run([r2])
     assert r2.finish_reason == FinishReason.ERROR and eng.kv.allocator.available() > 0
+
+
+def test_lookahead_decode_matches_synchronous(tmp_path):
+    """One-step lookahead (tokens of step N read while step N + 1 runs) must produce the same tokens, stop reasons and
+    callback order per request as the synchronous schedule, with staggered arrivals, different lengths and a cancellation."""
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.ckpt.loader import WeightLoader
+    from deliverance_b200.config import load_config
+    from deliverance_b200.engine.engine import Engine, EngineConfig
+    from deliverance_b200.models.transformer import DecoderModel
+    from deliverance_b200.params import GeneratorParameters
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "qwen3", seed=11, std=0.08)
+    cfg = load_config(d)
+    model = DecoderModel(cfg, "cpu").load(WeightLoader(d))
+    prompts = [[3, 5, 7, 9, 11], [2, 4, 6], [8, 1, 8, 1, 8, 1, 8], [13, 17]]
+    lens = [9, 4, 12, 6]
+
+    def run(lookahead):
+        eng = Engine(model, EngineConfig(num_pages=64, max_batch_tokens=8, lookahead=lookahead), eos_ids=(-1,))
+        seen = {}
+        reqs = []
+        for i, (p, n) in enumerate(zip(prompts[:3], lens[:3])):
+            reqs.append(eng.add_request(p, GeneratorParameters(max_tokens=n, temperature=0.0), on_token=lambda t, r, i=i: seen.setdefault(i, []).append(t)))
+        steps = 0
+        late = None
+        while eng.has_work():
+            eng.step()
+            steps += 1
+            if steps == 4:  # a request that arrives while decode steps are in flight
+                late = eng.add_request(prompts[3], GeneratorParameters(max_tokens=lens[3], temperature=0.0))
+                reqs.append(late)
+            if steps == 6:
+                eng.abort(reqs[2])
+        assert eng._inflight is None
+        return [r.output for r in reqs], [r.finish_reason for r in reqs], seen, eng.kv.allocator.available()
+
+    out_sync, why_sync, seen_sync, free_sync = run(False)
+    out_la, why_la, seen_la, free_la = run("force")
+    assert out_la[0] == out_sync[0] and out_la[1] == out_sync[1] and out_la[3] == out_sync[3]
+    assert why_la[:2] == why_sync[:2] and why_la[3] == why_sync[3]
+    # the cancelled request stops within one step of the synchronous schedule and its tokens are a prefix-consistent run
+    n = min(len(out_la[2]), len(out_sync[2]))
+    assert out_la[2][:n] == out_sync[2][:n] and abs(len(out_la[2]) - len(out_sync[2])) <= 2
+    assert seen_la[0] == out_la[0] and seen_la[1] == out_la[1]
+    assert free_la == free_sync  # every page came back
