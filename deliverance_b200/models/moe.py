@@ -27,7 +27,9 @@ def moe_forward(model, i: int, lw, x: torch.Tensor) -> torch.Tensor:
     renorm = True if cfg.model_type == "mixtral" else (cfg.norm_topk_prob if cfg.router_mode == "softmax_topk" else False)
     e0, ne = lw.expert0, lw.n_local_experts or E
     if x.device.type == "cuda":
-        y = _moe_cuda(model, lw, x, logits, E, k, cfg.router_mode, renorm, cfg.hidden_act, e0, ne)
+        y, reduced = _moe_cuda(model, lw, x, logits, E, k, cfg.router_mode, renorm, cfg.hidden_act, e0, ne)
+        if reduced:
+            return y
     else:
         w, idx = ref.moe_route(logits, k, cfg.router_mode, renorm)
         local = (idx >= e0) & (idx < e0 + ne)
@@ -62,5 +64,10 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
     gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
     hmid = ops.act_mul(gu, act)
     ys = down_w.run(hmid, items, bn, max(1, min(8, down_w.K // 1024)) if small else 1)
+    fused = getattr(model.tp, "fused", None)
+    if ep and fused is not None:
+        y = fused.moe_combine_all_reduce(ys, pos, w, T, k, offsets, e0, ne)  # combine + sum over ranks in one kernel
+        if y is not None:
+            return y, True
     ops._count()
-    return e.moe_combine(ys, pos, w, T, k, *rng)
+    return e.moe_combine(ys, pos, w, T, k, *rng), False

@@ -520,6 +520,40 @@ Tensor moe_combine(const Tensor& ys, const Tensor& pos, const Tensor& w, int64_t
   return out;
 }
 
+// Expert-parallel combine fused with the all-reduce over peer memory; returns false (nothing launched) outside the fused path.
+bool moe_combine_allreduce(const Tensor& ys, const Tensor& pos, const Tensor& w, int64_t T, int64_t k, const Tensor& offsets, int64_t e0,
+                           int64_t ne, const TpComm& comm, Tensor& out) {
+  check_bf16(ys, "ys");
+  check_cuda(pos, "pos");
+  check_cuda(w, "w");
+  check_cuda(offsets, "offsets");
+  const int H = static_cast<int>(ys.size(1));
+  TORCH_CHECK(pos.scalar_type() == at::kInt && w.scalar_type() == at::kFloat && offsets.scalar_type() == at::kInt && pos.numel() == T * k &&
+                  w.numel() == T * k && ys.size(0) == T * k && e0 + ne < offsets.numel(), "bad combine arguments");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == T && out.size(1) == H && out.is_contiguous() &&
+                  ys.is_contiguous(), "bad out");
+  if (!dlv::comm_rows_supported(comm.args(), static_cast<int>(T), H)) return false;
+  c10::cuda::CUDAGuard guard(ys.device());
+  DeviceScratch& s = scratch_for(ys.device().index());
+  dlv::launch_moe_combine_allreduce(ys.data_ptr(), pos.data_ptr<int>(), w.data_ptr<float>(), static_cast<int>(T), static_cast<int>(k), H,
+                                    offsets.data_ptr<int>(), static_cast<int>(e0), static_cast<int>(ne), out.data_ptr(), comm.args(),
+                                    s.status.data_ptr<int>(), cur_stream());
+  check_last_error("moe_combine_allreduce");
+  return true;
+}
+// One-shot all-reduce of a small bf16 tensor [rows <= 128, H] over peer memory; false when the shape is outside the fused path.
+bool oneshot_allreduce(const Tensor& x, const TpComm& comm, Tensor& out) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.sizes() == x.sizes() && out.is_contiguous(), "bad all-reduce arguments");
+  const int rows = static_cast<int>(x.size(0)), H = static_cast<int>(x.size(1));
+  if (!dlv::comm_rows_supported(comm.args(), rows, H)) return false;
+  c10::cuda::CUDAGuard guard(x.device());
+  DeviceScratch& s = scratch_for(x.device().index());
+  dlv::launch_oneshot_allreduce(x.data_ptr(), rows, H, out.data_ptr(), comm.args(), s.status.data_ptr<int>(), cur_stream());
+  check_last_error("oneshot_allreduce");
+  return true;
+}
+
 // ---- Mamba2 -----------------------------------------------------------------------------------------------------------
 // meta: int32 tensors prepared on the host (row_seq [T], chunk_* [n_chunks], seq_chunk0 / seq_nchunks [S])
 Tensor mamba2_forward(const Tensor& zx, const Tensor& conv_w, c10::optional<Tensor> conv_b, const Tensor& dt_bias, const Tensor& A_log,
@@ -632,6 +666,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_gather", &moe_gather, py::arg("x"), py::arg("perm"), py::arg("k"), py::arg("offsets") = py::none(), py::arg("e0") = 0, py::arg("ne") = 0);
   m.def("moe_combine", &moe_combine, py::arg("ys"), py::arg("pos"), py::arg("w"), py::arg("T"), py::arg("k"), py::arg("offsets") = py::none(),
         py::arg("e0") = 0, py::arg("ne") = 0);
+  m.def("moe_combine_allreduce", &moe_combine_allreduce);
+  m.def("oneshot_allreduce", &oneshot_allreduce);
   m.def("mamba2_forward", &mamba2_forward);
   m.def("q4_quantize", &q4_quantize);
   m.def("q4_dequantize", &q4_dequantize, py::arg("packed"), py::arg("scales"), py::arg("to_bf16") = false);

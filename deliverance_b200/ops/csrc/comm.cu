@@ -1,0 +1,205 @@
+// Fused compute + collective kernels over NVLink peer memory that are not GEMM epilogues.
+//
+//   moe_combine_allreduce: expert parallelism with replicated tokens. Every rank holds the outputs of ITS experts for the
+//     (token, slot) pairs routed to them. One CTA per token forms the weighted sum over the local slots (fp32), stores it as
+//     bf16 into the receive slab of EVERY rank with plain peer stores, publishes it with one release-add per rank, waits
+//     (bounded) until all ranks have published the same token to it, and adds the partial sums in rank order: the top-k
+//     combine and the all-reduce over the expert-parallel group are one kernel, no intermediate [T, H] tensor and no NCCL call.
+//   oneshot_allreduce: the same exchange for an existing bf16 tensor (small decode-size tensors that no GEMM produces).
+//
+// Protocol (shared with the GEMM all-reduce epilogue in gemm_tc.cuh, so launches of both kinds can interleave): receive slabs
+// are double-buffered on the parity of a per-rank launch counter; flags are cumulative per (source rank, CTA index) and the
+// expected value is kept per CTA index, so CUDA-graph replays need no reset; the last CTA of a grid advances the launch
+// counter. Every rank must launch the same sequence of fused kernels with the same grids. All CTAs of a launch are resident at
+// once (grid <= 148, small CTAs), otherwise waiting CTAs could keep a peer's publishers from being scheduled.
+// Plain peer loads / stores only: no multimem, no TMA.
+//
+// The reference combines expert outputs on the coordinator after a gRPC round trip per expert group
+// (core/.../model/MixtureOfExpertsBlock.java:78-112; distributed/.../tensorparallel/TensorParallelCoordinator.java).
+#include "common.cuh"
+#include "gemm_api.h"
+
+namespace dlv {
+
+struct CommParams {
+  int size, rank, ncta_max;
+  long long slab;
+  unsigned long long recv[8];
+  unsigned long long flags[8];
+  unsigned int* rounds;
+  unsigned int* call;
+  int* status;
+};
+
+// Publish this CTA's region to every rank and wait until every rank has published the same region to this rank.
+// Call with all threads of the CTA; returns a CTA-uniform flag (false: a wait ran out, the status word is set).
+__device__ __forceinline__ bool exchange_barrier(const CommParams& p, unsigned cta_id, int* s_flag) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < p.size; ++r) {
+      const int dst = (p.rank + r) % p.size;
+      red_release_sys_add(reinterpret_cast<uint32_t*>(p.flags[dst]) + static_cast<size_t>(p.rank) * p.ncta_max + cta_id, 1u);
+    }
+    const unsigned round = p.rounds[cta_id];
+    bool all = true;
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flags[p.rank]);
+    for (int src = 0; src < p.size && all; ++src) all = flag_wait_ge(mine + static_cast<size_t>(src) * p.ncta_max + cta_id, round + 1u, p.status);
+    p.rounds[cta_id] = round + 1u;
+    *s_flag = all ? 1 : 0;
+  }
+  __syncthreads();
+  return *s_flag != 0;
+}
+
+__device__ __forceinline__ void finish_launch(const CommParams& p, unsigned call) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(p.call + 1, 1u) == gridDim.x - 1u) {
+      p.call[1] = 0u;
+      __threadfence();
+      p.call[0] = call + 1u;
+    }
+  }
+}
+
+// grid = T tokens (<= ncta_max, all resident), 128 threads. ys: expert outputs in expert-grouped row order [T * k, H].
+__global__ void __launch_bounds__(128) moe_combine_allreduce_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ pos,
+                                                                    const float* __restrict__ w, int k, int H,
+                                                                    const int* __restrict__ offsets, int e0, int ne,
+                                                                    __nv_bfloat16* __restrict__ out, const CommParams p) {
+  __shared__ int s_flag;
+  const int t = blockIdx.x;
+  const unsigned cta_id = blockIdx.x;
+  const unsigned call = *reinterpret_cast<volatile unsigned*>(p.call);
+  const long long par_off = static_cast<long long>(call & 1u) * p.size * p.slab;
+  const int lo = offsets[e0], hi = offsets[e0 + ne];
+  // phase A: weighted sum over the slots whose expert lives here -> every rank's slab [parity][my rank][t, :]
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int prow = pos[static_cast<size_t>(t) * k + j];
+      if (prow < lo || prow >= hi) continue;
+      const float wt = w[static_cast<size_t>(t) * k + j];
+      const uint4 v = reinterpret_cast<const uint4*>(ys + static_cast<size_t>(prow) * H)[i];
+      const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf162(vu[e]);
+        acc[2 * e] += wt * f.x;
+        acc[2 * e + 1] += wt * f.y;
+      }
+    }
+    uint4 o;
+    uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ou[e] = pack_bf162(acc[2 * e], acc[2 * e + 1]);
+    const long long off = par_off + static_cast<long long>(p.rank) * p.slab + static_cast<long long>(t) * H + i * 8;
+    for (int r = 0; r < p.size; ++r)
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.recv[(p.rank + r) % p.size]) + off) = o;
+  }
+  const bool ok = exchange_barrier(p, cta_id, &s_flag);
+  // phase B: add the partial sums of all ranks in rank order (identical result on every rank)
+  if (ok) {
+    const __nv_bfloat16* rbase = reinterpret_cast<const __nv_bfloat16*>(p.recv[p.rank]) + par_off + static_cast<long long>(t) * H;
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int src = 0; src < p.size; ++src) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(rbase + static_cast<long long>(src) * p.slab) + i);
+        const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf162(vu[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+      uint4 o;
+      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ou[e] = pack_bf162(acc[2 * e], acc[2 * e + 1]);
+      reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[i] = o;
+    }
+  }
+  finish_launch(p, call);
+}
+
+// grid = rows (<= ncta_max, all resident), 128 threads: x [rows, H] bf16 -> out = sum over ranks
+__global__ void __launch_bounds__(128) oneshot_allreduce_kernel(const __nv_bfloat16* __restrict__ x, int H, __nv_bfloat16* __restrict__ out,
+                                                                const CommParams p) {
+  __shared__ int s_flag;
+  const int t = blockIdx.x;
+  const unsigned call = *reinterpret_cast<volatile unsigned*>(p.call);
+  const long long par_off = static_cast<long long>(call & 1u) * p.size * p.slab;
+  const long long off = par_off + static_cast<long long>(p.rank) * p.slab + static_cast<long long>(t) * H;
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    const uint4 v = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H)[i];
+    for (int r = 0; r < p.size; ++r)
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.recv[(p.rank + r) % p.size]) + off)[i] = v;
+  }
+  const bool ok = exchange_barrier(p, blockIdx.x, &s_flag);
+  if (ok) {
+    const __nv_bfloat16* rbase = reinterpret_cast<const __nv_bfloat16*>(p.recv[p.rank]) + par_off + static_cast<long long>(t) * H;
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int src = 0; src < p.size; ++src) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(rbase + static_cast<long long>(src) * p.slab) + i);
+        const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf162(vu[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+      uint4 o;
+      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ou[e] = pack_bf162(acc[2 * e], acc[2 * e + 1]);
+      reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[i] = o;
+    }
+  }
+  finish_launch(p, call);
+}
+
+static CommParams make_params(const GemmTpArgs* tp, int* status) {
+  CommParams p = {};
+  p.size = tp->size;
+  p.rank = tp->rank;
+  p.ncta_max = tp->ncta_max;
+  p.slab = tp->slab;
+  for (int r = 0; r < 8; ++r) {
+    p.recv[r] = tp->recv[r];
+    p.flags[r] = tp->flags[r];
+  }
+  p.rounds = tp->rounds;
+  p.call = tp->call;
+  p.status = status;
+  return p;
+}
+
+bool comm_rows_supported(const GemmTpArgs* tp, int rows, int H) {
+  return tp != nullptr && tp->size > 1 && tp->size <= 8 && rows > 0 && rows <= 128 && rows <= tp->ncta_max && H % 8 == 0 &&
+         static_cast<long long>(rows) * H <= tp->slab;
+}
+
+void launch_moe_combine_allreduce(const void* ys, const int* pos, const float* w, int T, int k, int H, const int* offsets, int e0, int ne,
+                                  void* out, const GemmTpArgs* tp, int* status, cudaStream_t st) {
+  if (T == 0) return;
+  moe_combine_allreduce_kernel<<<T, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(ys), pos, w, k, H, offsets, e0, ne,
+                                                  static_cast<__nv_bfloat16*>(out), make_params(tp, status));
+}
+
+void launch_oneshot_allreduce(const void* x, int rows, int H, void* out, const GemmTpArgs* tp, int* status, cudaStream_t st) {
+  if (rows == 0) return;
+  oneshot_allreduce_kernel<<<rows, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), H, static_cast<__nv_bfloat16*>(out),
+                                                 make_params(tp, status));
+}
+
+}  // namespace dlv

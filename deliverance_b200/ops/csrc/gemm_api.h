@@ -88,6 +88,12 @@ void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, i
                         int ne, cudaStream_t st);
 void launch_moe_items(const int* offsets, int e0, int ne, int bn, int max_items, int* items, cudaStream_t st);
 
+// comm.cu: fused compute + collective kernels over peer memory (same protocol as the GEMM all-reduce epilogue)
+bool comm_rows_supported(const GemmTpArgs* tp, int rows, int H);
+void launch_moe_combine_allreduce(const void* ys, const int* pos, const float* w, int T, int k, int H, const int* offsets, int e0, int ne,
+                                  void* out, const GemmTpArgs* tp, int* status, cudaStream_t st);
+void launch_oneshot_allreduce(const void* x, int rows, int H, void* out, const GemmTpArgs* tp, int* status, cudaStream_t st);
+
 // mamba.cu
 int launch_mamba2(const void* zx, int ld, int T, int num_seqs, int I, int conv_dim, int K, int H, int d_head, int G, int S,
                   const float* conv_w, const float* conv_b, const float* dt_bias, const float* A_log, const float* D, const float* norm_w,

@@ -221,6 +221,8 @@ class TensorParallelContext:
     def all_reduce(self, key: str, t: torch.Tensor) -> torch.Tensor:
         if not self.enabled:
             return t
+        if self.fused is not None and t.is_cuda:
+            return self.fused.all_reduce(t, key)  # one-shot peer-memory kernel for decode-size tensors, NCCL otherwise
         return self.collectives.all_reduce_sum(key, t)
 
 

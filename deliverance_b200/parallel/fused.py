@@ -65,6 +65,28 @@ class FusedTensorParallel:
         return self.tp.collectives.all_reduce_sum(key, y)
 
 
+    def all_reduce(self, x: torch.Tensor, key: str) -> torch.Tensor:
+        """Sum a small bf16 ``[rows, H]`` tensor over the ranks with the one-shot peer-memory kernel, NCCL otherwise."""
+        if x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous():
+            out = torch.empty_like(x)
+            if ops.require_ext().oneshot_allreduce(x, self.comm, out):
+                ops._count()
+                self.stats["fused"] += 1
+                return out
+        self.stats["fallback"] += 1
+        return self.tp.collectives.all_reduce_sum(key, x)
+
+    def moe_combine_all_reduce(self, ys, pos, w, T: int, k: int, offsets, e0: int, ne: int):
+        """Top-k weighted combine of the local experts' rows fused with the sum over the expert-parallel ranks. Returns ``None``
+        when the batch is outside the fused path (the caller then combines locally and all-reduces)."""
+        out = torch.empty(T, ys.shape[1], dtype=torch.bfloat16, device=ys.device)
+        if ops.require_ext().moe_combine_allreduce(ys, pos, w, T, k, offsets, e0, ne, self.comm, out):
+            ops._count()
+            self.stats["fused"] += 1
+            return out
+        return None
+
+
 def _no_bias(w):
     import copy
 

@@ -129,6 +129,64 @@ def main() -> int:
     report(check="tp_model_tokens", sequences=len(prompts), equal_nccl=agree_nccl, equal_fused=agree_fused, first_token_equal=first_tok, ok=good,
            fused_calls=fused.stats["fused"], fallback_calls=fused.stats["fallback"])
 
+    # ---------------------------------------------------------------- (2b) one-shot all-reduce and fused MoE combine
+    e = ops.require_ext()
+    g = torch.Generator().manual_seed(77)
+    for rows, Hd in ((1, 2048), (64, 4096), (128, 2560)):
+        full = (torch.randn(world, rows, Hd, generator=g) * 0.5).to(torch.bfloat16)
+        mine = full[rank].contiguous().to(dev)
+        want = full.float().sum(0).to(dev)
+        outs = [fused.all_reduce(mine, "ar") for _ in range(3)]
+        torch.cuda.synchronize()
+        ops.check_status(local)
+        err = max(((o.float() - want).norm() / want.norm()).item() for o in outs)
+        good = err < 1e-2 and all(torch.equal(outs[0], o) for o in outs[1:])
+        ok_all &= good
+        report(check="oneshot_all_reduce", rows=rows, H=Hd, rel_err=err, ok=good)
+    for (T, E, k, Hd) in ((64, 8, 2, 4096), (32, 128, 8, 2048), (5, 8 * world, 2, 1024)):
+        if E % world:
+            continue
+        ne, e0 = E // world, rank * (E // world)
+        logits = torch.randn(T, E, generator=g)
+        w_, idx, counts, offsets, perm, pos = e.moe_route(logits.to(dev), k, 0, True)
+        ys_full = (torch.randn(T * k, Hd, generator=g) * 0.5).to(torch.bfloat16)  # every rank draws the same rows ...
+        ys = ys_full.to(dev)
+        lo, hi = int(offsets[e0].item()), int(offsets[e0 + ne].item())
+        junk = torch.full_like(ys, float("nan"))
+        junk[lo:hi] = ys[lo:hi]  # ... but only holds those of its own experts
+        got = fused.moe_combine_all_reduce(junk, pos, w_, T, k, offsets, e0, ne)
+        torch.cuda.synchronize()
+        ops.check_status(local)
+        want = (ys_full.float()[pos.cpu().long()].reshape(T, k, Hd) * w_.cpu().unsqueeze(-1)).sum(1).to(dev)
+        err = ((got.float() - want).norm() / want.norm()).item() if got is not None else float("nan")
+        good = got is not None and err < 2e-2
+        ok_all &= good
+        report(check="moe_combine_all_reduce", T=T, E=E, k=k, H=Hd, rel_err=err, ok=good)
+
+    # ---------------------------------------------------------------- (2c) expert-parallel MoE model vs single GPU
+    mshape = dict(model_type="qwen3_moe", vocab_size=4096, hidden_size=1024, intermediate_size=2048, num_hidden_layers=2,
+                  num_attention_heads=16, num_key_value_heads=8, head_dim=128, max_position_embeddings=1024, rms_norm_eps=1e-6,
+                  rope_theta=1e6, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True,
+                  decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False)
+    mcfg = parse_config(dict(mshape))
+    mres = {}
+    for name, ctx in (("single", TensorParallelContext()), ("ep_fused", tp)):
+        model = DecoderModel(mcfg, dev, torch.bfloat16, ctx).load(SyntheticLoader(mshape, 5, True, dev, std=0.05))
+        ec = EngineConfig(num_pages=256, cuda_graphs=True)
+        ec.kv.enabled = False
+        eng = Engine(model, ec, eos_ids=(-1,))
+        rs = eng.generate_batch(prompts, GeneratorParameters(max_tokens=8))
+        mres[name] = [r.token_ids for r in rs]
+        local_experts = [lw.n_local_experts for lw in model.layers if lw.router is not None]
+        torch.cuda.synchronize()
+        ops.check_status(local)
+        dist.barrier()
+    first_tok = all(a[0] == b[0] for a, b in zip(mres["single"], mres["ep_fused"]))
+    equal = sum(a == b for a, b in zip(mres["single"], mres["ep_fused"]))
+    ok_all &= first_tok
+    report(check="ep_moe_model_tokens", local_experts=local_experts[0], equal=equal, first_token_equal=first_tok, ok=first_tok,
+           fused_calls=fused.stats["fused"], fallback_calls=fused.stats["fallback"])
+
     # ---------------------------------------------------------------- (3) timing
     if a.bench:
         N, Kfull = 2560, 9728 // (32 * world) * 32 * world
