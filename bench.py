@@ -297,7 +297,9 @@ def main() -> int:
             "vs_baseline": value / REFERENCE_DECODE_TOK_S, "dtype": "bf16 activations x JQ4 (4-bit) weights" if args.quant == "jq4" else "bf16",
             "data": "synthetic (uniform random prompts, random-init N(0,0.02) weights quantised to JQ4)",
             "config": {"model": f"{args.shape}-shape {args.quant}", "global_batch": B, "seq_len": P, "decode_tokens_timed": args.steps,
-                       "parallelism": f"tp{args.gpus}", "l2": "per-step weight stream (>2 GB/rank) exceeds the 126 MB L2; no flush needed",
+                       "parallelism": (f"tp{args.gpus}" if cfg.num_experts == 0 or args.gpus == 1 or cfg.num_experts % args.gpus else
+                                       f"tp{args.gpus} attention + ep{args.gpus} experts"),
+                       "l2": "per-step weight stream (>2 GB/rank) exceeds the 126 MB L2; no flush needed",
                        "comm": ("fused-p2p" if tp.fused is not None else "nccl") if world > 1 else "none",
                        "baseline_note": "reference number is single-request CPU decode (it has no request batching)"},
             "clocks": clocks,

@@ -87,7 +87,7 @@ class DecoderModel:
         if self.device.type == "cuda" and cfg.num_heads and cfg.head_dim not in (64, 128, 256):
             raise ValueError(f"head_dim {cfg.head_dim} is not supported by the CUDA attention kernels (64, 128, 256)")
         self.n_heads = cfg.num_heads // tp.size
-        self.n_kv = cfg.num_kv_heads // tp.size
+        self.n_kv = max(1, cfg.num_kv_heads // tp.size)  # with more ranks than KV heads, size / kv_heads ranks replicate one head
         self.layers: list[LayerWeights] = []
         self.embed: Optional[torch.Tensor] = None
         self.final_norm: Optional[torch.Tensor] = None
@@ -128,10 +128,14 @@ class DecoderModel:
             if lw.kind == "mamba":
                 lw.mamba = self._load_mamba(loader, p + "mamba.")
             else:
-                parts = [get(p + f"self_attn.{n}_proj.weight", row()) for n in ("q", "k", "v")]
+                kv_row = row()
+                if tp.enabled and cfg.num_kv_heads % tp.size != 0:
+                    kv_row = ShardSpec("row", tp.rank // (tp.size // cfg.num_kv_heads), cfg.num_kv_heads)
+                shard_of = {"q": row(), "k": kv_row, "v": kv_row}
+                parts = [get(p + f"self_attn.{n}_proj.weight", shard_of[n]) for n in ("q", "k", "v")]
                 bias = None
                 if cfg.qkv_bias and loader.has(p + "self_attn.q_proj.bias"):
-                    bias = torch.cat([loader.load(p + f"self_attn.{n}_proj.bias", row()).float().reshape(-1) for n in ("q", "k", "v")])
+                    bias = torch.cat([loader.load(p + f"self_attn.{n}_proj.bias", shard_of[n]).float().reshape(-1) for n in ("q", "k", "v")])
                 lw.qkv = self._lin(_cat_weights(parts), bias)
                 if cfg.qk_norm:
                     lw.q_norm = vec(p + "self_attn.q_norm.weight")

@@ -51,10 +51,12 @@ class TensorParallelPlanner:
             return False
         if size == 1:
             return True
-        dims = [cfg.num_heads, cfg.num_kv_heads, cfg.q_size, cfg.kv_size, cfg.hidden_size]
+        dims = [cfg.num_heads, cfg.q_size, cfg.hidden_size]
         if cfg.intermediate_size:
             dims.append(cfg.intermediate_size)
-        return all(d % size == 0 for d in dims)
+        # KV heads either split evenly or, with more ranks than KV heads, are replicated: size / kv_heads ranks share one head
+        kv_ok = cfg.num_kv_heads % size == 0 or size % cfg.num_kv_heads == 0
+        return kv_ok and all(d % size == 0 for d in dims)
 
     @staticmethod
     def validate(cfg: ModelConfig, size: int) -> None:
@@ -80,7 +82,12 @@ class TensorParallelPlanner:
             per = n // size
             return ShardRange(rank * per, (rank + 1) * per)
 
-        return TPPlan(rank, size, rng(cfg.num_heads), rng(cfg.num_kv_heads), rng(max(cfg.intermediate_size, size)), rng(cfg.hidden_size))
+        if cfg.num_kv_heads % size == 0:
+            kv = rng(cfg.num_kv_heads)
+        else:
+            head = rank // (size // cfg.num_kv_heads)
+            kv = ShardRange(head, head + 1)
+        return TPPlan(rank, size, rng(cfg.num_heads), kv, rng(max(cfg.intermediate_size, size)), rng(cfg.hidden_size))
 
 
 class Collectives:

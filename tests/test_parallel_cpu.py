@@ -26,12 +26,15 @@ PROMPT = list(range(5, 45))
 def test_planner():
     cfg = parse_config(tiny_config("llama", num_attention_heads=8, num_key_value_heads=4, hidden_size=128, intermediate_size=256))
     assert TensorParallelPlanner.compatible(cfg, 1) and TensorParallelPlanner.compatible(cfg, 2) and TensorParallelPlanner.compatible(cfg, 4)
-    assert not TensorParallelPlanner.compatible(cfg, 8) and not TensorParallelPlanner.compatible(cfg, 3)
-    assert TensorParallelPlanner.choose_size(cfg, 8) == 4 and TensorParallelPlanner.choose_size(cfg, 3) == 2
+    assert TensorParallelPlanner.compatible(cfg, 8) and not TensorParallelPlanner.compatible(cfg, 3)  # 8 ranks: KV heads replicated x2
+    assert not TensorParallelPlanner.compatible(cfg, 16)
+    assert TensorParallelPlanner.choose_size(cfg, 8) == 8 and TensorParallelPlanner.choose_size(cfg, 3) == 2
+    p8 = TensorParallelPlanner.plan(cfg, 5, 8)
+    assert (p8.heads.begin, p8.heads.end) == (5, 6) and (p8.kv_heads.begin, p8.kv_heads.end) == (2, 3)
     p = TensorParallelPlanner.plan(cfg, 1, 4)
     assert (p.heads.begin, p.heads.end) == (2, 4) and (p.kv_heads.begin, p.kv_heads.end) == (1, 2) and p.hidden.size == 32
     with pytest.raises(ValueError):
-        TensorParallelPlanner.plan(cfg, 0, 8)
+        TensorParallelPlanner.plan(cfg, 0, 16)
     assert not TensorParallelContext().enabled and TensorParallelContext(1, 2).enabled and TensorParallelContext(0, 2).is_coordinator
 
 
@@ -82,6 +85,23 @@ def test_expert_parallel_thread_ranks_match_single(tmp_path, family):
     m = DecoderModel(cfg, "cpu", tp=TensorParallelContext(1, 2, InProcessCollectives(group, 1))).load(WeightLoader(d))
     sparse = [lw for lw in m.layers if lw.router is not None]
     assert sparse and all(lw.expert0 == cfg.num_experts // 2 and len(lw.experts_gate_up) == cfg.num_experts // 2 for lw in sparse)
+
+
+def test_kv_head_replication_four_ranks(tmp_path):
+    """More ranks than KV heads: two ranks share each KV head; tokens must match the single-rank run."""
+    d = str(tmp_path / "rep")
+    write_tiny_model(d, "qwen3", seed=6, std=0.05, hidden_size=128, intermediate_size=256, num_attention_heads=8, num_key_value_heads=2,
+                     head_dim=32)
+    cfg = load_config(d)
+    single = [None]
+    _run_rank(d, cfg, TensorParallelContext(), single, 0)
+    group = InProcessGroup(4, timeout=60)
+    out = [None] * 4
+    ts = [threading.Thread(target=_run_rank, args=(d, cfg, TensorParallelContext(r, 4, InProcessCollectives(group, r)), out, r)) for r in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not isinstance(out[0], Exception), out[0]
+    assert out[0] == out[1] == out[2] == out[3] == single[0]
 
 
 def test_in_process_group_reports_missing_rank():
