@@ -10,6 +10,7 @@ quantize, activation-multiply, gather-rows-add (embedding), paged decode attenti
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -34,7 +35,14 @@ def ext():
     if not _ext_checked:
         _ext = load_extension()
         _ext_checked = True
+        if _ext is not None and os.environ.get("DLV_GEMM_PDL", "1") == "0":
+            _ext.gemm_pdl(False)
     return _ext
+
+
+def set_gemm_pdl(on: bool) -> None:
+    """Programmatic dependent launch of the GEMM kernels (their prologue and weight prefetch overlap the previous kernel's tail)."""
+    require_ext().gemm_pdl(bool(on))
 
 
 def require_ext():

@@ -647,6 +647,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("take_status", &take_status);
   m.def("init_scratch", &init_scratch);
   m.def("gemm_trace", &gemm_trace);
+  m.def("gemm_pdl", [](bool on) { dlv::gemm_set_pdl(on); });
   m.def("num_sms", &dlv::gemm_num_sms);
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);

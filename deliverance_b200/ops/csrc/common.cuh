@@ -129,6 +129,14 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   return ok != 0;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the stream is
+// still running, once every CTA of the predecessor has called pdl_trigger() (or exited). It must call pdl_wait() before it
+// reads anything the predecessor wrote and before it writes global memory; the wait returns when the predecessor grid has
+// completed and its writes are visible. Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- proxies / fences -----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

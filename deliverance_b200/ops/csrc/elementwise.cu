@@ -15,6 +15,7 @@ namespace dlv {
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* residual,
                                                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                       int H, float eps, float offset, float res_mult) {
+  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
   extern __shared__ float row[];  // H floats
   __shared__ float red[32];
   const size_t base = static_cast<size_t>(blockIdx.x) * H;
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 __global__ void __launch_bounds__(256) layernorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                         const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, int H,
                                                         float eps) {
+  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
   extern __shared__ float row[];
   __shared__ float red[32];
   const size_t base = static_cast<size_t>(blockIdx.x) * H;
@@ -107,6 +109,7 @@ __device__ __forceinline__ float act_apply(float g, int act) {
 // in: [T, 2*I] (gate | up), out: [T, I]; I % 8 == 0
 __global__ void __launch_bounds__(256) act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int I,
                                                       int act, long long total_vec) {
+  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total_vec) return;
   const int per_row = I / 8;
@@ -130,6 +133,7 @@ __global__ void __launch_bounds__(256) act_mul_kernel(const __nv_bfloat16* __res
 // unary activation in place-capable form (gpt2 / bert MLP without an up projection)
 __global__ void __launch_bounds__(256) act_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int act,
                                                   long long n) {
+  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) out[i] = f2bf(act_apply(bf2f(in[i]), act));
 }
@@ -140,6 +144,7 @@ __global__ void __launch_bounds__(128) embedding_kernel(const __nv_bfloat16* __r
                                                         const __nv_bfloat16* __restrict__ pos_table, const int* __restrict__ pos,
                                                         const __nv_bfloat16* __restrict__ type_table, const int* __restrict__ types,
                                                         __nv_bfloat16* __restrict__ out, int H, int vocab, float scale) {
+  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;  // host validates ids; never read out of the table
@@ -195,6 +200,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(__nv_bfloat16* __restrict_
                                                       const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ k_cache,
                                                       __nv_bfloat16* __restrict__ v_cache, int T, int H, int KV, int block_size,
                                                       int rot_half, float eps, float norm_offset, int max_pos) {
+  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int heads = H + 2 * KV;

@@ -83,6 +83,8 @@ void gemm_weight_init(GemmWeightDesc* w) {
   }
 }
 
+bool g_gemm_pdl = true;  // programmatic dependent launch of the GEMM kernels (ops.set_gemm_pdl / DLV_GEMM_PDL=0 turn it off)
+void gemm_set_pdl(bool on) { g_gemm_pdl = on; }
 unsigned long long* g_gemm_trace = nullptr;
 void gemm_set_trace(unsigned long long* p) { g_gemm_trace = p; }
 
@@ -211,15 +213,23 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = L::kBytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int na = 0;
   if (cluster) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = p.splits;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = p.splits;
+    ++na;
   }
+  if (g_gemm_pdl) {
+    // programmatic dependent launch: prologue + weight streaming overlap the tail of the kernel in front (see pdl_wait)
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<Q4, BN>, w->map_w, map_x, p);
   if (e != cudaSuccess) throw std::runtime_error(std::string("gemm launch: ") + cudaGetErrorString(e));
 }
@@ -297,15 +307,22 @@ static void run_grouped(const GemmWeightDesc* w, const void* x, int rows, int ld
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = L::kBytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int na = 0;
   if (splits > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = splits;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = splits;
+    ++na;
   }
+  if (g_gemm_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<Q4, BN>, w->map_w, map_x, p);
   if (e != cudaSuccess) throw std::runtime_error(std::string("grouped gemm launch: ") + cudaGetErrorString(e));
 }

@@ -168,6 +168,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   const int n0 = n_tile * kGemmBM;
   int m0 = m_tile * BN, m_lim = p.M, w_tile = n_tile, w_row0 = n0;
   if (p.grp_items != nullptr) {
+    pdl_wait();  // the work list is written by the kernels in front of this one
     const int4 it = p.grp_items[blockIdx.y];
     if (it.x < 0) return;  // uniform over the cluster (its CTAs differ in blockIdx.z only); nothing is set up yet
     m0 = it.y;
@@ -264,6 +265,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   } else if (warp == 2 || warp == 20) {
     // ---------------- activation producers ----------------
     if (lane == 0) {
+      // Launched with programmatic stream serialization, this kernel may run its prologue and stream weights while the kernel
+      // that produces the activations is still finishing; nothing that kernel wrote is read before this point.
+      pdl_wait();
       const int first_i = warp == 2 ? 0 : 1;
       int last_issued = -1, n_issued = 0;
       for (int i = first_i; i < nkb; i += 2) {
@@ -397,6 +401,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         }
       }
     }
+    pdl_wait();  // global memory is written (and the peer-memory bookkeeping read) only after the predecessor grid is complete
     // ---- accumulator -> fp32 tile [col][row] in shared memory (the rings are idle once the MMAs retired) ----
     if (ok) ok = mbar_wait(smem_u32(bar_acc), 0, abort_flag, p.status);
     // All 512 threads reach this barrier; afterwards the abort flag gives a CTA-uniform decision (it is only ever

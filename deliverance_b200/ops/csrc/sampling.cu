@@ -18,6 +18,7 @@ __device__ __forceinline__ bool mask_allows(const uint32_t* mask_row, int i) {
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int ld, int V,
                                                       const uint32_t* __restrict__ mask, int mask_ld, float softcap,
                                                       float inv_scale, long long* __restrict__ out_idx, float* __restrict__ out_val) {
+  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
   __shared__ float sv[32];
   __shared__ int si[32];
   const int b = blockIdx.x;
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 
 __global__ void __launch_bounds__(256) logits_post_kernel(float* __restrict__ logits, int ld, int V, const uint32_t* __restrict__ mask,
                                                           int mask_ld, float softcap, float inv_scale) {
+  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
   const int b = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= V) return;
