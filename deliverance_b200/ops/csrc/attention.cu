@@ -37,7 +37,8 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(
     float* __restrict__ part_o,               // [num_seqs, H, splits, D]
     float* __restrict__ part_ml,              // [num_seqs, H, splits, 2]
     int H, int KV, int page_size, float scale, float softcap, int window, int splits) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   constexpr int PARTS0 = D * GP / 64;
   constexpr int PARTS = PARTS0 < 8 ? 8 : (PARTS0 > 32 ? 32 : PARTS0);  // threads that share one key
   constexpr int EPT = D / PARTS;                                       // query elements per thread and head
@@ -242,7 +243,8 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(
 // grid (num_seqs, H), D threads
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int H, int D, int splits) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const long long base = (static_cast<long long>(b) * H + h) * splits;
   float m = -INFINITY;
@@ -282,7 +284,7 @@ static int launch_decode_t(const void* q, long long q_stride, const void* kc, co
                                                       scale, cap, window, splits);
   if (splits > 1) {
     dim3 g2(B, H);
-    decode_merge_kernel<<<g2, D, 0, st>>>(po, pml, static_cast<__nv_bfloat16*>(out), H, D, splits);
+    launch_pdl(decode_merge_kernel, dim3(g2), dim3(D), 0, st, po, pml, static_cast<__nv_bfloat16*>(out), H, D, splits);
   }
   return 0;
 }
@@ -365,7 +367,8 @@ __global__ void __launch_bounds__(128, (D <= 128 ? 2 : 1)) decode_attn_mma_kerne
     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int bt_stride,
     const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int H, int KV, int page_size, float scale, float softcap, int window, int splits) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   using L = DecodeMma<D>;
   constexpr int CPR = D / 8;  // 16-byte chunks per row
   extern __shared__ __align__(128) uint8_t msm[];
@@ -586,13 +589,13 @@ static int launch_decode_mma_t(const void* q, long long q_stride, const void* kc
     attr_done = true;
   }
   dim3 grid(B, KV, splits);
-  decode_attn_mma_kernel<D><<<grid, 128, L::kBytes, st>>>(static_cast<const __nv_bfloat16*>(q), q_stride,
+  launch_pdl(decode_attn_mma_kernel<D>, dim3(grid), dim3(128), L::kBytes, st, static_cast<const __nv_bfloat16*>(q), q_stride,
                                                           static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt,
                                                           bt_stride, ctx, static_cast<__nv_bfloat16*>(out), po, pml, H, KV, page, scale, cap,
                                                           window, splits);
   if (splits > 1) {
     dim3 g2(B, H);
-    decode_merge_kernel<<<g2, D, 0, st>>>(po, pml, static_cast<__nv_bfloat16*>(out), H, D, splits);
+    launch_pdl(decode_merge_kernel, dim3(g2), dim3(D), 0, st, po, pml, static_cast<__nv_bfloat16*>(out), H, D, splits);
   }
   return 0;
 }
@@ -622,7 +625,8 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(
     const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ ctx_lens,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, __nv_bfloat16* __restrict__ out,  // [T, H, D]
     int H, int KV, int page_size, float scale, float softcap, int window, int causal) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   constexpr int BM = 64, BN = 64, CPR = D / 8;
   extern __shared__ __align__(128) uint8_t psm[];
   uint8_t* sQ = psm;                       // BM * D * 2

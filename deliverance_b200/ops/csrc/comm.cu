@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(128) moe_combine_allreduce_kernel(const __nv_b
                                                                     const float* __restrict__ w, int k, int H,
                                                                     const int* __restrict__ offsets, int e0, int ne,
                                                                     __nv_bfloat16* __restrict__ out, const CommParams p) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   __shared__ int s_flag;
   const int t = blockIdx.x;
   const unsigned cta_id = blockIdx.x;
@@ -132,7 +133,8 @@ __global__ void __launch_bounds__(128) moe_combine_allreduce_kernel(const __nv_b
 // grid = rows (<= ncta_max, all resident), 128 threads: x [rows, H] bf16 -> out = sum over ranks
 __global__ void __launch_bounds__(128) oneshot_allreduce_kernel(const __nv_bfloat16* __restrict__ x, int H, __nv_bfloat16* __restrict__ out,
                                                                 const CommParams p) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   __shared__ int s_flag;
   const int t = blockIdx.x;
   const unsigned call = *reinterpret_cast<volatile unsigned*>(p.call);

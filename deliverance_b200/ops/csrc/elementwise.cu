@@ -15,7 +15,8 @@ namespace dlv {
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* residual,
                                                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                       int H, float eps, float offset, float res_mult) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   extern __shared__ float row[];  // H floats
   __shared__ float red[32];
   const size_t base = static_cast<size_t>(blockIdx.x) * H;
@@ -72,7 +73,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 __global__ void __launch_bounds__(256) layernorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                         const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, int H,
                                                         float eps) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   extern __shared__ float row[];
   __shared__ float red[32];
   const size_t base = static_cast<size_t>(blockIdx.x) * H;
@@ -109,7 +111,8 @@ __device__ __forceinline__ float act_apply(float g, int act) {
 // in: [T, 2*I] (gate | up), out: [T, I]; I % 8 == 0
 __global__ void __launch_bounds__(256) act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int I,
                                                       int act, long long total_vec) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total_vec) return;
   const int per_row = I / 8;
@@ -133,7 +136,8 @@ __global__ void __launch_bounds__(256) act_mul_kernel(const __nv_bfloat16* __res
 // unary activation in place-capable form (gpt2 / bert MLP without an up projection)
 __global__ void __launch_bounds__(256) act_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int act,
                                                   long long n) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) out[i] = f2bf(act_apply(bf2f(in[i]), act));
 }
@@ -144,7 +148,8 @@ __global__ void __launch_bounds__(128) embedding_kernel(const __nv_bfloat16* __r
                                                         const __nv_bfloat16* __restrict__ pos_table, const int* __restrict__ pos,
                                                         const __nv_bfloat16* __restrict__ type_table, const int* __restrict__ types,
                                                         __nv_bfloat16* __restrict__ out, int H, int vocab, float scale) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;  // host validates ids; never read out of the table
@@ -200,7 +205,8 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(__nv_bfloat16* __restrict_
                                                       const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ k_cache,
                                                       __nv_bfloat16* __restrict__ v_cache, int T, int H, int KV, int block_size,
                                                       int rot_half, float eps, float norm_offset, int max_pos) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int heads = H + 2 * KV;
@@ -286,7 +292,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(__nv_bfloat16* __restrict_
 void launch_rmsnorm(const void* x, void* residual, const void* w, void* y, int T, int H, float eps, float offset,
                     float res_mult, cudaStream_t st) {
   if (T == 0) return;
-  rmsnorm_kernel<<<T, 256, H * sizeof(float), st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
+  launch_pdl(rmsnorm_kernel, dim3(T), dim3(256), H * sizeof(float), st, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
                                                     static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), H, eps,
                                                     offset, res_mult);
 }
@@ -298,7 +304,7 @@ void launch_layernorm(const void* x, const void* w, const void* b, void* y, int 
 void launch_act_mul(const void* in, void* out, long long T, int I, int act, cudaStream_t st) {
   const long long total = T * (I / 8);
   if (total == 0) return;
-  act_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in),
+  launch_pdl(act_mul_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(in),
                                                                              static_cast<__nv_bfloat16*>(out), I, act, total);
 }
 void launch_act(const void* in, void* out, long long n, int act, cudaStream_t st) {
@@ -309,7 +315,7 @@ void launch_act(const void* in, void* out, long long n, int act, cudaStream_t st
 void launch_embedding(const void* table, const int* ids, const void* pos_table, const int* pos, const void* type_table,
                       const int* types, void* out, int T, int H, int vocab, float scale, cudaStream_t st) {
   if (T == 0) return;
-  embedding_kernel<<<T, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(table), ids, static_cast<const __nv_bfloat16*>(pos_table), pos,
+  launch_pdl(embedding_kernel, dim3(T), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(table), ids, static_cast<const __nv_bfloat16*>(pos_table), pos,
                                       static_cast<const __nv_bfloat16*>(type_table), types, static_cast<__nv_bfloat16*>(out), H, vocab,
                                       scale);
 }
@@ -320,7 +326,7 @@ int launch_rope_kv(void* qkv, const int* positions, const long long* slots, cons
   const long long warps = static_cast<long long>(T) * (H + 2 * KV);
   const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
 #define DLV_ROPE(DD)                                                                                                         \
-  rope_kv_kernel<DD><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(qkv), positions, slots,                                \
+  launch_pdl(rope_kv_kernel<DD>, dim3(grid), dim3(256), 0, st, static_cast<__nv_bfloat16*>(qkv), positions, slots,                                \
                                            static_cast<const __nv_bfloat16*>(qn), static_cast<const __nv_bfloat16*>(kn), cos_t, \
                                            sin_t, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), T, \
                                            H, KV, block_size, rot_half, eps, norm_offset, max_pos)

@@ -83,7 +83,8 @@ void gemm_weight_init(GemmWeightDesc* w) {
   }
 }
 
-bool g_gemm_pdl = true;  // programmatic dependent launch of the GEMM kernels (ops.set_gemm_pdl / DLV_GEMM_PDL=0 turn it off)
+bool g_pdl_enabled = true;
+bool& g_gemm_pdl = g_pdl_enabled;  // programmatic dependent launch of the GEMM kernels (ops.set_gemm_pdl / DLV_GEMM_PDL=0 turn it off)
 void gemm_set_pdl(bool on) { g_gemm_pdl = on; }
 unsigned long long* g_gemm_trace = nullptr;
 void gemm_set_trace(unsigned long long* p) { g_gemm_trace = p; }

@@ -210,6 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
   }
+  pdl_trigger();  // kernels behind this one may be scheduled as soon as every CTA of this grid has started
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
   tc_fence_before();
   __syncthreads();

@@ -21,7 +21,8 @@ __global__ void __launch_bounds__(256) mamba_conv_kernel(const __nv_bfloat16* __
                                                          const float* __restrict__ conv_state, const long long* __restrict__ slots,
                                                          const int* __restrict__ row_seq, const int* __restrict__ q_start,
                                                          const int* __restrict__ positions, float* __restrict__ out, int T) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(T) * conv_dim) return;
   const int row = static_cast<int>(idx / conv_dim), c = static_cast<int>(idx % conv_dim);
@@ -45,7 +46,8 @@ __global__ void __launch_bounds__(256) mamba_conv_state_kernel(const __nv_bfloat
                                                                float* __restrict__ conv_state, const long long* __restrict__ slots,
                                                                const int* __restrict__ q_start, const int* __restrict__ q_len,
                                                                const int* __restrict__ positions, int S) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(S) * conv_dim) return;
   const int s = static_cast<int>(idx / conv_dim), c = static_cast<int>(idx % conv_dim);
@@ -72,7 +74,8 @@ __global__ void mamba_scan_kernel(const __nv_bfloat16* __restrict__ zx, int ld, 
                                   const int* __restrict__ chunk_row0, const int* __restrict__ chunk_len, const int* __restrict__ chunk_first,
                                   const int* __restrict__ chunk_last, const int* __restrict__ positions, float* __restrict__ chunk_state,
                                   float* __restrict__ chunk_decay, float* __restrict__ y, int H, int d_head, int G, int S, int parts, int mode) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   extern __shared__ float sh[];  // B [S] | C [S]
   float* sB = sh;
   float* sC = sh + S;
@@ -143,7 +146,8 @@ __global__ void __launch_bounds__(256) mamba_carry_kernel(float* __restrict__ ch
                                                           const int* __restrict__ seq_chunk0, const int* __restrict__ seq_nchunks,
                                                           const int* __restrict__ q_start, const int* __restrict__ positions, int H,
                                                           int per_head) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const int seq = blockIdx.x, h = blockIdx.y;
   const int c0 = seq_chunk0[seq], nc = seq_nchunks[seq];
   const bool fresh = positions[q_start[seq]] == 0;
@@ -162,7 +166,8 @@ __global__ void __launch_bounds__(256) mamba_carry_kernel(float* __restrict__ ch
 // gated RMSNorm over the whole intermediate: one CTA per row, y fp32 -> out bf16
 __global__ void __launch_bounds__(256) mamba_norm_kernel(const float* __restrict__ y, const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
                                                          int I, float eps) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   __shared__ float red[32];
   const size_t base = static_cast<size_t>(blockIdx.x) * I;
   float ss = 0.f;

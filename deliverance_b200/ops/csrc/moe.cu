@@ -16,7 +16,8 @@ constexpr int kMaxTopK = 16;
 // one warp per token; E <= 1024
 __global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int mode, int renorm,
                                                        float* __restrict__ w_out, int* __restrict__ idx_out, int* __restrict__ counts) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -85,7 +86,8 @@ __global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__
 // pos[t * k + j] = row of that pair in the grouped order; perm[row] = t * k + j.
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, const int* __restrict__ counts, int T, int E, int k,
                                                         int* __restrict__ offsets, int* __restrict__ perm, int* __restrict__ pos) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   extern __shared__ int sh[];  // E + 1 offsets
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -113,7 +115,8 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
 
 __global__ void __launch_bounds__(128) moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ perm, int k, int H,
                                                          __nv_bfloat16* __restrict__ xs, const int* __restrict__ offsets, int e0, int ne) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const int row = blockIdx.x;
   if (offsets != nullptr && (row < offsets[e0] || row >= offsets[e0 + ne])) return;  // another rank's expert
   const int t = perm[row] / k;
@@ -125,7 +128,8 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const __nv_bfloat16* __
 __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ pos,
                                                           const float* __restrict__ w, int k, int H, __nv_bfloat16* __restrict__ out,
                                                           const int* __restrict__ offsets, int e0, int ne) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const int t = blockIdx.x;
   const int lo = offsets != nullptr ? offsets[e0] : 0, hi = offsets != nullptr ? offsets[e0 + ne] : 0x7fffffff;
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
@@ -178,7 +182,8 @@ void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, i
 // rows, in expert order; the rest of the `max_items` slots get expert = -1. Single CTA (at most a few hundred items).
 __global__ void __launch_bounds__(256) moe_items_kernel(const int* __restrict__ offsets, int e0, int ne, int bn, int max_items,
                                                         int4* __restrict__ items) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   __shared__ int first[1025];
   if (threadIdx.x == 0) {
     int acc = 0;

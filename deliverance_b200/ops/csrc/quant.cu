@@ -18,7 +18,8 @@ __device__ __forceinline__ float load_as_float<__half>(const __half* p, long lon
 template <typename T>
 __global__ void __launch_bounds__(256) q4_quantize_kernel(const T* __restrict__ w, long long n_blocks, uint8_t* __restrict__ packed,
                                                           float* __restrict__ scales) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const long long blk = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (blk >= n_blocks) return;
   float v[32];
@@ -68,7 +69,8 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { re
 template <typename T>
 __global__ void __launch_bounds__(256) q4_dequantize_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scales,
                                                             long long n_blocks, T* __restrict__ out) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const long long blk = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (blk >= n_blocks) return;
   const uint4 w = reinterpret_cast<const uint4*>(packed)[blk];

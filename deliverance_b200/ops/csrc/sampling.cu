@@ -18,7 +18,8 @@ __device__ __forceinline__ bool mask_allows(const uint32_t* mask_row, int i) {
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int ld, int V,
                                                       const uint32_t* __restrict__ mask, int mask_ld, float softcap,
                                                       float inv_scale, long long* __restrict__ out_idx, float* __restrict__ out_val) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   __shared__ float sv[32];
   __shared__ int si[32];
   const int b = blockIdx.x;
@@ -72,7 +73,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 
 __global__ void __launch_bounds__(256) logits_post_kernel(float* __restrict__ logits, int ld, int V, const uint32_t* __restrict__ mask,
                                                           int mask_ld, float softcap, float inv_scale) {
-  pdl_trigger();  // lets a dependent GEMM start its prologue and weight prefetch under this kernel's tail
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
   const int b = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= V) return;
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(256) logits_post_kernel(float* __restrict__ lo
 void launch_argmax(const float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
                    long long* out_idx, float* out_val, cudaStream_t st) {
   if (B == 0) return;
-  argmax_kernel<<<B, 1024, 0, st>>>(logits, ld, V, mask, mask_ld, softcap, inv_scale, out_idx, out_val);
+  launch_pdl(argmax_kernel, dim3(B), dim3(1024), 0, st, logits, ld, V, mask, mask_ld, softcap, inv_scale, out_idx, out_val);
 }
 void launch_logits_post(float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
                         cudaStream_t st) {
