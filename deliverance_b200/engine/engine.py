@@ -212,8 +212,12 @@ class Engine:
                 finished.append(r)
         if self.waiting and self._inflight is not None and len(self.running) < self.config.max_seqs:
             finished += self._drain()  # admissions and prefill work on settled request state
-        while self.waiting and self._admit(self.waiting[0]):
-            self.waiting.pop(0)
+        # Admit only while this step's prefill budget has room: a request admitted later looks the prefix cache up later and
+        # finds what the requests in front of it have stored by then (concurrent arrivals that share a prefix).
+        backlog = sum(len(r.prompt) - r.computed for r in self.running if r.computed < len(r.prompt))
+        while self.waiting and backlog < self.config.max_batch_tokens and self._admit(self.waiting[0]):
+            r = self.waiting.pop(0)
+            backlog += len(r.prompt) - r.computed
         prefill = [r for r in self.running if r.computed < len(r.prompt)]
         if prefill:
             finished += self._drain()
