@@ -128,6 +128,90 @@ class MixtralToolCallParser(ToolCallParser):
     """Placeholder like the reference's stub: Mixtral replies are never parsed into calls."""
 
 
+class Gemma4ToolCallParser(ToolCallParser):
+    """``<|tool_call>call:NAME{args}<tool_call|>`` regions. ``args`` is either JSON or the template's relaxed form with bare
+    keys and ``<|"|>`` as the string quote (reference: core/.../toolcallparser/Gemma4ToolCallParser.java and its test vectors
+    in Gemma4ToolCallParserTest.java). Ids count from 101; a closed region ends the turn."""
+
+    OPEN, CLOSE, QUOTE = "<|tool_call>", "<tool_call|>", '<|"|>'
+    FIRST_ID = 101
+
+    def extract(self, text: str) -> list[ToolCall]:
+        calls: list[ToolCall] = []
+        pos = 0
+        while True:
+            a = text.find(self.OPEN, pos)
+            if a < 0:
+                break
+            b = text.find(self.CLOSE, a)
+            body = text[a + len(self.OPEN) : b if b >= 0 else len(text)].strip()
+            pos = (b + len(self.CLOSE)) if b >= 0 else len(text)
+            if not body.startswith("call:"):
+                continue
+            brace = body.find("{")
+            if brace < 0:
+                continue
+            name = body[5:brace].strip()
+            raw = _match_braces(body, brace)
+            if not name or raw is None:
+                continue
+            try:
+                args = json.loads(self._to_json(raw))
+            except ValueError:
+                continue
+            if isinstance(args, dict):
+                calls.append(ToolCall(str(self.FIRST_ID + len(calls)), name, args))
+        return calls
+
+    def _to_json(self, raw: str) -> str:
+        """Relaxed argument syntax -> JSON: ``<|"|>`` becomes a quote, bare object keys get quoted (outside strings only)."""
+        out, i, in_str = [], 0, False
+        while i < len(raw):
+            if raw.startswith(self.QUOTE, i):
+                out.append('"')
+                in_str = not in_str
+                i += len(self.QUOTE)
+                continue
+            c = raw[i]
+            if in_str:
+                if c == '"':  # a literal quote inside a <|"|>-delimited string
+                    out.append('\\"')
+                elif c == "\\" and i + 1 < len(raw):
+                    out.append(raw[i : i + 2])
+                    i += 1
+                else:
+                    out.append(c)
+                i += 1
+                continue
+            if c == '"':  # ordinary JSON string: copy verbatim
+                j = i + 1
+                while j < len(raw) and raw[j] != '"':
+                    j += 2 if raw[j] == "\\" else 1
+                out.append(raw[i : j + 1])
+                i = j + 1
+                continue
+            if c.isalpha() or c == "_":
+                j = i
+                while j < len(raw) and (raw[j].isalnum() or raw[j] in "_.-"):
+                    j += 1
+                word = raw[i:j]
+                k = j
+                while k < len(raw) and raw[k].isspace():
+                    k += 1
+                if k < len(raw) and raw[k] == ":" and word not in ("true", "false", "null"):
+                    out.append(json.dumps(word))
+                else:
+                    out.append(word)
+                i = j
+                continue
+            out.append(c)
+            i += 1
+        return "".join(out)
+
+    def should_end_turn(self, text_with_special: str) -> bool:
+        return self.CLOSE in text_with_special
+
+
 def parser_for_model(name: str) -> ToolCallParser:
     n = (name or "").lower()
     base = n.split("/")[-1]
@@ -137,6 +221,8 @@ def parser_for_model(name: str) -> ToolCallParser:
         return LlamaToolCallParser()
     if base.startswith("mixtral"):
         return MixtralToolCallParser()
+    if base.startswith(("gemma-4", "gemma4")):
+        return Gemma4ToolCallParser()
     return DefaultToolCallParser()
 
 

@@ -364,6 +364,40 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         app.add_api_route(path, embeddings, methods=["POST"])
     for path in ("/models", "/v1/models"):
         app.add_api_route(path, models, methods=["GET"])
+    async def metrics():
+        """Prometheus text exposition of the engine and runner counters (the reference reports through Dropwizard metrics:
+        core/.../model/InferenceProfiler.java:24-161; ttft / tokens-per-second timers in GenerationEngine.java:128-175)."""
+        from fastapi.responses import PlainTextResponse
+
+        lines = []
+
+        def emit(name, kind, help_text, samples):
+            lines.append(f"# HELP {name} {help_text}")
+            lines.append(f"# TYPE {name} {kind}")
+            for labels, v in samples:
+                lab = ",".join(f'{k}="{val}"' for k, val in labels.items())
+                lines.append(f"{name}{{{lab}}} {v}")
+
+        eng_keys = (("steps", "engine steps"), ("prefill_steps", "prefill steps"), ("decode_steps", "decode steps"),
+                    ("prefill_tokens", "prompt tokens computed"), ("decode_tokens", "tokens generated by decode steps"),
+                    ("graph_replays", "CUDA graph replays"), ("kernel_launches", "kernels of the extension launched"))
+        for key, text in eng_keys:
+            emit(f"deliverance_engine_{key}_total", "counter", text,
+                 [({"model": n}, r.clm.engine.metrics.get(key, 0)) for n, r in registry.generation.items()])
+        for key in ("submitted", "finished", "errors", "cancelled"):
+            emit(f"deliverance_requests_{key}_total", "counter", f"requests {key}", [({"model": n}, r.stats.get(key, 0)) for n, r in registry.generation.items()])
+        emit("deliverance_requests_running", "gauge", "sequences in the running batch",
+             [({"model": n}, len(r.clm.engine.running)) for n, r in registry.generation.items()])
+        emit("deliverance_requests_waiting", "gauge", "requests waiting for admission",
+             [({"model": n}, len(r.clm.engine.waiting)) for n, r in registry.generation.items()])
+        emit("deliverance_kv_pages_free", "gauge", "free KV cache pages",
+             [({"model": n}, r.clm.engine.kv.allocator.available()) for n, r in registry.generation.items()])
+        for key in ("lookup", "hits", "misses", "evict", "stored", "hit_tokens"):
+            emit(f"deliverance_prefix_cache_{key}_total", "counter", f"prefix cache {key}",
+                 [({"model": n}, r.clm.engine.kv.prefix.metrics.get(key, 0)) for n, r in registry.generation.items()])
+        return PlainTextResponse("\n".join(lines) + "\n", media_type="text/plain; version=0.0.4")
+
+    app.add_api_route("/metrics", metrics, methods=["GET"])
     app.add_api_route("/tp/status", tp_status, methods=["GET"])
     app.add_api_route("/ui", ui, methods=["GET"])
     return app

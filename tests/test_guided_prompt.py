@@ -127,3 +127,23 @@ def test_incremental_detokenizer_utf8():
     pieces = [d.push(i) for i in ids + [2]]
     assert pieces == ["", "é", "!", ""] and d.text == "é!"
     assert tk.decode(tk.encode("héllo")) == "héllo"
+
+
+def test_gemma4_tool_call_parser_vectors():
+    """Golden vectors of the reference's Gemma4ToolCallParserTest (JSON arguments, the template's relaxed syntax, nesting)."""
+    from deliverance_b200.prompt.parsers import Gemma4ToolCallParser, parser_for_model
+
+    p = Gemma4ToolCallParser()
+    c = p.extract('<|channel>thought\nNeed weather data<channel|><|tool_call>call:get_weather{"location":"Albany, NY","unit":"celsius"}<tool_call|>')
+    assert len(c) == 1 and c[0].id == "101" and c[0].name == "get_weather" and c[0].arguments == {"location": "Albany, NY", "unit": "celsius"}
+    c = p.extract('<|channel>thought\nx<channel|><|tool_call>call:get_current_temperature{detail_level:0,location:<|"|>Paris, France<|"|>,'
+                  'unit:<|"|>celsius<|"|>}<tool_call|><|tool_response>')
+    assert c[0].name == "get_current_temperature" and c[0].arguments == {"detail_level": 0, "location": "Paris, France", "unit": "celsius"}
+    c = p.extract('<|tool_call>call:foo{bool_value:true,list_value:[<|"|>foo<|"|>,<|"|>bar<|"|>],null_value:null,number_value:1,'
+                  'string_value:<|"|>foo<|"|>,struct_value:{foo:<|"|>bar<|"|>}}<tool_call|>')
+    assert c[0].arguments == {"bool_value": True, "list_value": ["foo", "bar"], "null_value": None, "number_value": 1, "string_value": "foo",
+                              "struct_value": {"foo": "bar"}}
+    c = p.extract('<|tool_call>call:flight_searcher.get_weather{"location":"Albany, NY"}<tool_call|><|tool_call>call:b{x:2}<tool_call|>')
+    assert [x.name for x in c] == ["flight_searcher.get_weather", "b"] and c[1].id == "102"
+    assert p.should_end_turn("abc<tool_call|>") and not p.should_end_turn("abc")
+    assert isinstance(parser_for_model("google/gemma-4-12b-it"), Gemma4ToolCallParser)

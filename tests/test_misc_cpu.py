@@ -172,3 +172,46 @@ def test_lora_hot_swap_equals_merge(tmp_path):
     assert t_hot == t_merged and t_hot != t_base
     with pytest.raises(KeyError):
         base.activate_lora("nope")
+
+
+def test_sketches_facade_and_metrics_endpoint(tmp_path):
+    import dataclasses
+    from typing import Literal
+
+    from fastapi.testclient import TestClient
+
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.server.app import ModelRegistry, create_app
+    from deliverance_b200.server.runner import EngineRunner
+    from deliverance_b200.sketches import Sketches, schema_of
+
+    d = str(tmp_path / "tiny")
+    write_tiny_model(d, "llama", seed=3, std=0.05)
+    clm = AutoModelForCausalLM.from_pretrained(d, device="cpu")
+    sk = Sketches(clm, max_tokens=160)
+    assert sk.choice("pick:", ["alpha", "beta"]) in ("alpha", "beta")
+    import re
+
+    assert re.fullmatch(r"[0-9]{3}-[a-c]{2}", sk.regex("code:", r"[0-9]{3}-[a-c]{2}"))
+
+    @dataclasses.dataclass
+    class Pet:
+        kind: Literal["cat", "dog"]
+        legs: Literal[2, 4]
+
+    assert schema_of(Pet)["properties"]["kind"] == {"enum": ["cat", "dog"]}
+    pet = sk.typed("a pet:", Pet)
+    assert pet.kind in ("cat", "dog") and isinstance(pet.legs, int)
+
+    reg = ModelRegistry()
+    runner = EngineRunner(clm)
+    reg.generation["tiny"] = runner
+    try:
+        c = TestClient(create_app(reg))
+        c.post("/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3})
+        m = c.get("/metrics")
+        assert m.status_code == 200 and 'deliverance_requests_finished_total{model="tiny"} 1' in m.text
+        assert "deliverance_engine_decode_tokens_total" in m.text and "deliverance_kv_pages_free" in m.text
+    finally:
+        runner.close()
