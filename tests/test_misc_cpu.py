@@ -215,3 +215,35 @@ def test_sketches_facade_and_metrics_endpoint(tmp_path):
         assert "deliverance_engine_decode_tokens_total" in m.text and "deliverance_kv_pages_free" in m.text
     finally:
         runner.close()
+
+
+def test_nanocode_agent_loop_with_scripted_model(tmp_path):
+    """The agent executes tool calls, feeds results back, asks for approval before changes and stays inside the workspace."""
+    from deliverance_b200.agents.nanocode import Agent, ToolExecutor
+
+    (tmp_path / "a.txt").write_text("hello world\nsecond line\n")
+    asked = []
+    ex = ToolExecutor(str(tmp_path), lambda kind, info: (asked.append(kind), kind != "run")[1])
+
+    def call(name, **args):
+        return {"id": f"c{len(script)}", "type": "function", "function": {"name": name, "arguments": json.dumps(args)}}
+
+    script = []
+    script.append({"content": "", "tool_calls": [call("grep", pattern="hello"), call("read", path="a.txt", start=2, end=2)]})
+    script.append({"content": "", "tool_calls": [call("edit", path="a.txt", old="hello", new="goodbye"), call("run", command="rm -rf /"),
+                                                 call("read", path="../../etc/passwd"), call("write", path="sub/b.txt", content="x")]})
+    script.append({"content": "done", "tool_calls": []})
+    seen = []
+
+    def chat(messages, **kw):
+        seen.append([m["role"] for m in messages])
+        assert kw["tools"]
+        return {"choices": [{"message": script[len(seen) - 1]}]}
+
+    agent = Agent(chat, ex, on_text=lambda t: None)
+    assert agent.ask("change the greeting") == "done"
+    tool_msgs = [m["content"] for m in agent.messages if m["role"] == "tool"]
+    assert tool_msgs[0].startswith("a.txt:1:hello world") and tool_msgs[1] == "2\tsecond line\n"
+    assert tool_msgs[2] == "edited a.txt" and tool_msgs[3] == "denied by the user" and "outside the workspace" in tool_msgs[4]
+    assert (tmp_path / "a.txt").read_text().startswith("goodbye world") and (tmp_path / "sub" / "b.txt").read_text() == "x"
+    assert asked == ["edit", "run", "write"] and seen[-1][-1] == "tool"
