@@ -389,6 +389,10 @@ class GroupedLinearWeight:
 def moe_token_tile(rows: int, local_experts: int) -> int:
     """Token tile (UMMA N) of the grouped GEMM for ``rows`` routed rows spread over ``local_experts`` experts."""
     avg = rows / max(1, local_experts)
+    if avg <= 3:
+        return 4  # CUDA-core grouped GEMV (<= 4 rows per work item)
+    if avg <= 6:
+        return 8
     for bn in (16, 32, 64, 128):
         if avg <= bn * 0.75:
             return bn

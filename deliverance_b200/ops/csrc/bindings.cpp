@@ -157,6 +157,12 @@ class GemmWeight {
     c10::cuda::CUDAGuard guard(xs.device());
     Tensor out = out_opt.has_value() ? out_opt.value() : torch::empty({xs.size(0), n_per_expert}, xs.options());
     TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == xs.size(0) && out.size(1) == n_per_expert && out.stride(1) == 1, "bad out");
+    if (bn <= 8) {  // decode-size groups: CUDA-core GEMV, one warp per weight row and work item
+      dlv::gemv_grouped_run(&desc_, static_cast<int>(n_per_expert), xs.data_ptr(), static_cast<int>(xs.stride(0)), out.data_ptr(),
+                            static_cast<int>(out.stride(0)), items.data_ptr<int>(), static_cast<int>(items.size(0)), static_cast<int>(bn), cur_stream());
+      check_last_error("grouped gemv launch");
+      return out;
+    }
     DeviceScratch& s = scratch_for(xs.device().index());
     dlv::gemm_tc_run_grouped(&desc_, static_cast<int>(n_per_expert), xs.data_ptr(), static_cast<int>(xs.size(0)), static_cast<int>(xs.stride(0)),
                              out.data_ptr(), static_cast<int>(out.stride(0)), items.data_ptr<int>(), static_cast<int>(items.size(0)),
@@ -480,7 +486,7 @@ std::vector<Tensor> moe_route(const Tensor& logits, int64_t k, int64_t mode, boo
 }
 Tensor moe_items(const Tensor& offsets, int64_t e0, int64_t ne, int64_t bn, int64_t max_items) {
   check_cuda(offsets, "offsets");
-  TORCH_CHECK(offsets.scalar_type() == at::kInt && e0 >= 0 && ne >= 1 && ne <= 1024 && e0 + ne < offsets.numel() + 0 && bn >= 16 && max_items >= 1, "bad work-list arguments");
+  TORCH_CHECK(offsets.scalar_type() == at::kInt && e0 >= 0 && ne >= 1 && ne <= 1024 && e0 + ne < offsets.numel() + 0 && bn >= 1 && max_items >= 1, "bad work-list arguments");
   c10::cuda::CUDAGuard guard(offsets.device());
   Tensor items = torch::empty({max_items, 4}, offsets.options());
   dlv::launch_moe_items(offsets.data_ptr<int>(), static_cast<int>(e0), static_cast<int>(ne), static_cast<int>(bn), static_cast<int>(max_items), items.data_ptr<int>(), cur_stream());

@@ -441,6 +441,119 @@ __global__ void __launch_bounds__(128) gemv_simt_kernel(const void* __restrict__
   }
 }
 
+// ------------------------------------------------------------------------------------------------ grouped CUDA-core GEMV
+// Fine-grained mixture-of-experts decode: dozens of experts with one to eight rows each. The tensor-core kernel pays ~5 us
+// of fixed cost per CTA on every (expert, tile) pair; here one warp owns one weight row of one work item and multiplies it
+// with the item's (up to MT) token rows, so a work item costs a few hundred instructions and the kernel is bound by the
+// weight stream. grid (ceil(N / 4), max_items), 4 warps; items as built by launch_moe_items with bn == MT.
+template <int MT, bool Q4>
+__global__ void __launch_bounds__(128) gemv_grouped_kernel(const void* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
+                                                           __nv_bfloat16* __restrict__ out, int ldo, int N, int K,
+                                                           const int4* __restrict__ items) {
+  pdl_wait();
+  pdl_trigger();
+  const int4 it = items[blockIdx.y];
+  if (it.x < 0) return;
+  const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (n >= N) return;
+  const int r0 = it.y;
+  const int cnt = min(MT, it.z - it.y);
+  float acc[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+  if (Q4) {
+    const int kb_total = (K + 127) / 128;
+    const int n_tiles = (N + 127) / 128;
+    const int r = n & 127;
+    const uint8_t* tile_row = static_cast<const uint8_t*>(wdata) + (static_cast<size_t>(it.x) * n_tiles + (n >> 7)) * kb_total * kQ4StageBytes;
+    for (int blk = lane; blk < K / 32; blk += 32) {
+      const uint8_t* stage = tile_row + static_cast<size_t>(blk >> 2) * kQ4StageBytes;
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(stage + r * 64 + (((blk & 3) ^ ((r >> 1) & 3)) << 4)));
+      const float sc = __ldg(reinterpret_cast<const float*>(stage + 8192 + r * 16 + (blk & 3) * 4));
+      const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+      float wf[32];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const uint32_t byte = (words[i] >> (8 * b)) & 0xFFu;
+          wf[4 * i + b] = static_cast<float>(static_cast<int>(byte & 0xFu) - 8) * sc;
+          wf[16 + 4 * i + b] = static_cast<float>(static_cast<int>(byte >> 4) - 8) * sc;
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m < cnt) {
+          const __nv_bfloat16* xr = x + static_cast<size_t>(r0 + m) * ldx + blk * 32;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xr + c * 8);
+            const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack_bf162(xu[e]);
+              acc[m] += f.x * wf[c * 8 + 2 * e] + f.y * wf[c * 8 + 2 * e + 1];
+            }
+          }
+        }
+      }
+    }
+  } else {
+    const __nv_bfloat16* wrow = static_cast<const __nv_bfloat16*>(wdata) + (static_cast<size_t>(it.x) * N + n) * K;
+    for (int k0 = lane * 8; k0 < K; k0 += 256) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + k0));
+      const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+      float wf[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf162(wu[e]);
+        wf[2 * e] = f.x;
+        wf[2 * e + 1] = f.y;
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m < cnt) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r0 + m) * ldx + k0);
+          const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf162(xu[e]);
+            acc[m] += f.x * wf[2 * e] + f.y * wf[2 * e + 1];
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] = warp_sum(acc[m]);
+  if (lane == 0) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+      if (m < cnt) out[static_cast<size_t>(r0 + m) * ldo + n] = f2bf(acc[m]);
+  }
+}
+
+void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,
+                      int max_items, int mt, cudaStream_t st) {
+  if (max_items <= 0) return;
+  if (ldx % 8 != 0 || w->K % 8 != 0) throw std::runtime_error("grouped gemv needs 16-byte aligned rows");
+  if (max_items > 65535) throw std::runtime_error("grouped gemv: work list too long");
+  const dim3 grid((n_per_expert + 3) / 4, max_items);
+  const int4* it = reinterpret_cast<const int4*>(items);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+#define DLV_GG(MTV)                                                                                                                 \
+  if (w->is_q4) launch_pdl(gemv_grouped_kernel<MTV, true>, grid, dim3(128), 0, st, w->data, xp, ldx, op, ldo, n_per_expert, w->K, it); \
+  else launch_pdl(gemv_grouped_kernel<MTV, false>, grid, dim3(128), 0, st, w->data, xp, ldx, op, ldo, n_per_expert, w->K, it)
+  switch (mt) {
+    case 4: DLV_GG(4); break;
+    case 8: DLV_GG(8); break;
+    default: throw std::runtime_error("grouped gemv: rows per item must be 4 or 8");
+  }
+#undef DLV_GG
+}
+
 void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
                    cudaStream_t st) {
   const unsigned grid = (w->N + 3) / 4;

@@ -43,6 +43,9 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
 // 128-row tiles), `items` is the device work list of launch_moe_items built with the same token tile `bn`.
 void gemm_tc_run_grouped(const GemmWeightDesc* w, int n_per_expert, const void* x, int rows, int ldx, void* out, int ldo,
                          const int* items, int max_items, int bn, int splits, int* status, cudaStream_t st);
+// CUDA-core variant for decode-size groups (at most `mt` = 4 or 8 rows per work item; items built with bn == mt)
+void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,
+                      int max_items, int mt, cudaStream_t st);
 // true when the fused all-reduce epilogue can take this problem (one wave of CTAs, rows and columns inside the slab)
 bool gemm_tp_supported(const GemmWeightDesc* w, int M, const GemmTpArgs* tp);
 void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,

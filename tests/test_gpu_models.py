@@ -65,7 +65,7 @@ def test_grouped_gemm_matches_per_expert(T, E, k, N, K, e0, ne, q4):
     x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
     xs = e.moe_gather(x.cuda(), perm, k, offsets, e0, ne)
     off = offsets.cpu().tolist()
-    for bn, splits in ((ops.moe_token_tile(T * k * ne // E, ne), 1), (16, 2), (64, 4)):
+    for bn, splits in ((ops.moe_token_tile(T * k * ne // E, ne), 1), (16, 2), (64, 4), (4, 1), (8, 1)):  # 4 / 8: CUDA-core grouped GEMV
         max_items = (T * k + bn - 1) // bn + ne
         items = e.moe_items(offsets, e0, ne, bn, max_items)
         it = items.cpu()
