@@ -209,8 +209,26 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
   p.x3d = w->K % 64 == 0 ? 1 : 0;
   if (p.x3d) encode_map_kchunks(&map_x, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN);
   else encode_map_2d(&map_x, 0, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, BN, 64, 128);
+  // Tail split: a single-split grid that is a few tiles larger than the SM count would run a full second wave for those few
+  // tiles. They are cut into up to 8 k-ranges each (reduced through the workspace), so the second wave is a short one.
+  int grid_x = p.n_tiles;
+  if ((tp == nullptr || tp->size <= 1) && splits == 1 && p.m_tiles == 1 && force_splits == 0 && ws != nullptr && counters != nullptr &&
+      p.kb_total >= 8) {
+    const int cap = gemm_num_sms();
+    const int rem = p.n_tiles % cap;
+    if (p.n_tiles > cap && rem > 0 && rem * 8 <= cap) {
+      const int kb_per = (p.kb_total + 7) / 8;
+      const int s_eff = (p.kb_total + kb_per - 1) / kb_per;
+      if (s_eff > 1 && static_cast<size_t>(rem) * s_eff * BN * kGemmBM <= ws_floats && rem <= n_counters) {
+        p.tail_tile0 = p.n_tiles - rem;
+        p.tail_splits = s_eff;
+        p.tail_kb_per_split = kb_per;
+        grid_x = p.tail_tile0 + rem * s_eff;
+      }
+    }
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.n_tiles, p.m_tiles, p.splits);
+  cfg.gridDim = dim3(grid_x, p.m_tiles, p.splits);
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = L::kBytes;
   cfg.stream = st;

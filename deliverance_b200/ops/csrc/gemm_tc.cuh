@@ -73,6 +73,9 @@ struct GemmParams {
   // item = {expert, first row, end row, 0}; expert < 0 marks an unused slot (the CTA returns at once). The weights of all
   // local experts are stacked (JQ4: n_tiles tile rows per expert, dense: N rows per expert); N / n_tiles are per expert.
   const int4* grp_items;
+  // ---- tail split: CTAs with blockIdx.x >= tail_tile0 share the last tiles `tail_splits` ways (workspace reduction), so that a
+  // grid a few tiles larger than the SM count ends with a short second wave instead of a full one (host: splits == 1) ----
+  int tail_tile0, tail_splits, tail_kb_per_split;
   int x3d, w3d;  // the activation / dense weight map is the 3-D chunked form: one copy per stage instead of two
 };
 
@@ -164,7 +167,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
 #define DLV_CTA_STAMP(j) do { if (p.trace != nullptr && cta_lin < 2048u) p.trace[16 + 4 * cta_lin + (j)] = globaltimer_ns(); } while (0)
   if (threadIdx.x == 0) DLV_CTA_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
+  int n_tile = blockIdx.x, split = blockIdx.z;
+  const int m_tile = blockIdx.y;
+  int splits = p.splits, kb_per_split = p.kb_per_split, ws_tile = m_tile * p.n_tiles + blockIdx.x;
+  if (p.tail_splits > 1 && static_cast<int>(blockIdx.x) >= p.tail_tile0) {
+    const int j = static_cast<int>(blockIdx.x) - p.tail_tile0;
+    n_tile = p.tail_tile0 + j / p.tail_splits;
+    split = j % p.tail_splits;
+    splits = p.tail_splits;
+    kb_per_split = p.tail_kb_per_split;
+    ws_tile = j / p.tail_splits;
+  }
   const int n0 = n_tile * kGemmBM;
   int m0 = m_tile * BN, m_lim = p.M, w_tile = n_tile, w_row0 = n0;
   if (p.grp_items != nullptr) {
@@ -176,8 +189,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     w_tile = it.x * p.n_tiles + n_tile;
     w_row0 = it.x * p.N + n0;
   }
-  const int kb_begin = split * p.kb_per_split;
-  const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);
+  const int kb_begin = split * kb_per_split;
+  const int kb_end = min(p.kb_total, kb_begin + kb_per_split);
   const int nkb = max(0, kb_end - kb_begin);
   constexpr uint32_t TMEM_COLS = Q4 ? kGemmTmemCols : (L::kAccCols < 32 ? 32 : L::kAccCols);
   // Every CTA walks its k-blocks from a different starting point: CTAs that run at the same time would otherwise all ask
@@ -438,11 +451,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         }
       }
     }
-    if (p.splits == 1 || !p.cluster_reduce) asm volatile("bar.sync 1, 512;" ::: "memory");
+    if (splits == 1 || !p.cluster_reduce) asm volatile("bar.sync 1, 512;" ::: "memory");
   }
   if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(5);
   // ---------------- reduce over the split-K cluster (distributed shared memory) and store ----------------
-  const bool clustered = p.splits > 1 && p.cluster_reduce;
+  const bool clustered = splits > 1 && p.cluster_reduce;
   if (clustered) cluster_sync_all();  // every CTA of the cluster has its partial tile in shared memory (or is aborting)
   if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(6);
   if (warp >= kGemmEpiWarp0 && warp < kGemmEpiWarp0 + 16 && *abort_flag == 0) {
@@ -451,25 +464,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     const int n = n0 + row4;
     const float* stage = reinterpret_cast<const float*>(smem);
     const uint32_t stage_addr = smem_u32(smem);
-    if (p.splits > 1 && !p.cluster_reduce) {
+    if (splits > 1 && !p.cluster_reduce) {
       // fallback: partial tiles through the global workspace, the last CTA to arrive reduces in split order
-      const int tile_id = m_tile * p.n_tiles + n_tile;
-      float* part = p.ws + (static_cast<size_t>(tile_id) * p.splits + split) * (BN * kGemmBM);
+      const int tile_id = ws_tile;
+      float* part = p.ws + (static_cast<size_t>(tile_id) * splits + split) * (BN * kGemmBM);
       for (int col = csel; col < BN; col += 16)
         *reinterpret_cast<float4*>(part + col * kGemmBM + row4) = *reinterpret_cast<const float4*>(stage + col * kGemmBM + row4);
       __threadfence();
       asm volatile("bar.sync 1, 512;" ::: "memory");
       if (t == 0) {
         const int old = atomicAdd(&p.counters[tile_id], 1);
-        *s_last = (old == p.splits - 1) ? 1 : 0;
+        *s_last = (old == splits - 1) ? 1 : 0;
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");
       if (*s_last) __threadfence();
     }
-    const bool do_store = p.splits == 1 || p.cluster_reduce || *s_last;
+    const bool do_store = splits == 1 || p.cluster_reduce || *s_last;
     const bool fused_tp = p.tp_size > 1;
     const uint32_t me = clustered ? cluster_ctarank() : 0u;
-    const int stride = clustered ? p.splits : 1;
+    const int stride = clustered ? splits : 1;
     const bool vec_ok = (n + 3 < p.N) && ((p.ldo & 3) == 0);
     // reduced (over split-K) accumulator of column `col`, rows row4 .. row4+3
     auto column_acc = [&](int col) -> float4 {
@@ -477,14 +490,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       if (clustered) {
         acc = make_float4(0.f, 0.f, 0.f, 0.f);
         const uint32_t a = stage_addr + static_cast<uint32_t>((col * kGemmBM + row4) * 4);
-        for (int sp = 0; sp < p.splits; ++sp) {
+        for (int sp = 0; sp < splits; ++sp) {
           const float4 v = ld_dsmem_f32x4(a, static_cast<uint32_t>(sp));
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-      } else if (p.splits > 1) {
+      } else if (splits > 1) {
         acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float* base = p.ws + static_cast<size_t>(m_tile * p.n_tiles + n_tile) * p.splits * (BN * kGemmBM);
-        for (int sp = 0; sp < p.splits; ++sp) {
+        const float* base = p.ws + static_cast<size_t>(ws_tile) * splits * (BN * kGemmBM);
+        for (int sp = 0; sp < splits; ++sp) {
           const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (static_cast<size_t>(sp) * BN + col) * kGemmBM + row4));
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
@@ -529,7 +542,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         acc.x += bias.x; acc.y += bias.y; acc.z += bias.z; acc.w += bias.w;
         store_out(m, acc);
       }
-      if (p.splits > 1 && !p.cluster_reduce && t == 0) p.counters[m_tile * p.n_tiles + n_tile] = 0;
+      if (splits > 1 && !p.cluster_reduce && t == 0) p.counters[ws_tile] = 0;
     }
     if (fused_tp) {
       // ---- GEMM + one-shot all-reduce over peer memory (host guarantees: N % 4 == 0, cluster or single split) ----

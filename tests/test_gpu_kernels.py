@@ -41,6 +41,7 @@ def test_gemv_simt(M, q4):
     (1, 256, 512, 1), (8, 256, 1024, 1), (16, 384, 2560, 0), (17, 128, 256, 1), (64, 512, 2048, 0), (64, 2560, 9728, 0),
     (100, 640, 1216, 1), (128, 256, 4096, 2), (300, 384, 1024, 1), (5, 200, 2560, 4), (33, 1000, 608, 0),
     (64, 256, 4096, 8), (48, 384, 4096, -4), (16, 128, 9728, -16), (7, 256, 2048, 3), (600, 256, 512, 0),
+    (64, 19456, 1024, 0), (8, 19712, 1280, 0),  # a few tiles more than SMs: the tail tiles are split over k
 ])
 @pytest.mark.parametrize("q4", [True, False])
 def test_gemm_tcgen05(M, N, K, splits, q4):
