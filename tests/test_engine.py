@@ -212,3 +212,32 @@ def test_lookahead_decode_matches_synchronous(tmp_path):
     assert out_la[2][:n] == out_sync[2][:n] and abs(len(out_la[2]) - len(out_sync[2])) <= 2
     assert seen_la[0] == out_la[0] and seen_la[1] == out_la[1]
     assert free_la == free_sync  # every page came back
+
+
+def test_concurrent_arrivals_share_prefix_through_cache(tmp_path):
+    """Requests that arrive together and share a prefix: admission is gated by the prefill budget, so the later ones find the
+    prefix that the first ones stored, and outputs equal the uncached run."""
+    from deliverance_b200.ckpt.loader import WeightLoader
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.config import load_config
+    from deliverance_b200.engine.engine import Engine, EngineConfig
+    from deliverance_b200.models.transformer import DecoderModel
+    from deliverance_b200.params import GeneratorParameters
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=12, std=0.08)
+    model = DecoderModel(load_config(d), "cpu").load(WeightLoader(d))
+    prefix = [(7 * i + 3) % 250 + 1 for i in range(96)]
+    prompts = [prefix + [10 + i, 20 + i, 30 + i] for i in range(6)]
+
+    def run(cache_on, budget):
+        ec = EngineConfig(num_pages=128, max_batch_tokens=budget, max_seqs=8)
+        ec.kv.enabled = cache_on
+        eng = Engine(model, ec, eos_ids=(-1,))
+        rs = eng.generate_batch(prompts, GeneratorParameters(max_tokens=5, temperature=0.0))
+        return [r.token_ids for r in rs], dict(eng.kv.prefix.metrics), eng.metrics["prefill_tokens"]
+
+    base, _, tokens_nocache = run(False, 100)
+    got, m, tokens_cached = run(True, 100)
+    assert got == base
+    assert m["hits"] >= 4 and tokens_cached < tokens_nocache * 0.6
