@@ -105,6 +105,33 @@ class Sampler:
 
     def __init__(self, decode_token=None):
         self.decode_token = decode_token or (lambda i: str(i))
+        self.stats = {"kernel_rows": 0, "fallback_rows": 0}
+
+    def _sample_cuda(self, logits: torch.Tensor, rest: list) -> list[int]:
+        """Rows through the histogram-select kernel (csrc/sampling.cu); rows it declines (a histogram bin too crowded, a pick in
+        the far tail) go through the sorting path."""
+        dev = logits.device
+        sub = logits.index_select(0, torch.tensor([r[0] for r in rest], device=dev)) if len(rest) != logits.shape[0] else logits
+        temps = torch.tensor([r[1] for r in rest], dtype=torch.float32)
+        args = (
+            (1.0 / temps).to(dev),
+            torch.tensor([r[2] for r in rest], dtype=torch.int64, device=dev),
+            torch.tensor([r[3] for r in rest], dtype=torch.float32, device=dev),
+            torch.tensor([r[4] for r in rest], dtype=torch.uint8, device=dev),
+            torch.tensor([r[5] for r in rest], dtype=torch.float32, device=dev),
+        )
+        tok, ok = ops.require_ext().sample_rows(sub.contiguous() if sub.stride(1) != 1 else sub, *args)
+        ops._count()
+        tok_l, ok_l = tok.tolist(), ok.tolist()
+        bad = [i for i, o in enumerate(ok_l) if not o]
+        self.stats["kernel_rows"] += len(rest) - len(bad)
+        self.stats["fallback_rows"] += len(bad)
+        if bad:
+            bi = torch.tensor(bad, device=dev)
+            fb = sample_top_k_top_p_batch(sub.index_select(0, bi), temps[bad].to(dev), args[1][bi], args[2][bi], args[3][bi].bool(), args[4][bi]).tolist()
+            for i, t in zip(bad, fb):
+                tok_l[i] = t
+        return tok_l
 
     def sample(self, logits: torch.Tensor, states: list[SamplingState]) -> tuple[list[int], list[Optional[TokenLogProb]]]:
         B, V = logits.shape
@@ -126,6 +153,11 @@ class Sampler:
                 out[i] = pick if pick is not None else int(amax[i])
                 continue
             rest.append((i, T, candidate_limit(top_k, V), top_p if top_p is not None else 0.0, utp is not None, s.rng.random()))
+        if rest and logits.device.type == "cuda":
+            toks = self._sample_cuda(logits, rest)
+            for r, t in zip(rest, toks):
+                out[r[0]] = int(t)
+            rest = []
         if rest:
             rows = torch.tensor([r[0] for r in rest], device=logits.device)
             dev = logits.device

@@ -451,6 +451,27 @@ std::vector<Tensor> argmax(const Tensor& logits, c10::optional<Tensor> mask, dou
   check_last_error("argmax");
   return {idx, val};
 }
+// Top-k / top-p / uniform-top-p sampling of every row with one kernel launch (histogram select, no vocabulary sort).
+// Returns (token ids int64 [B], handled int32 [B]); rows with handled == 0 need the sorting fallback.
+std::vector<Tensor> sample_rows(const Tensor& logits, const Tensor& inv_temp, const Tensor& limits, const Tensor& top_p, const Tensor& uniform,
+                                const Tensor& us) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
+  const int B = static_cast<int>(logits.size(0)), V = static_cast<int>(logits.size(1));
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&inv_temp, &limits, &top_p, &uniform, &us}) {
+    check_cuda(*t, "sampling parameter");
+    TORCH_CHECK(t->numel() == B && t->is_contiguous(), "one sampling parameter per row");
+  }
+  TORCH_CHECK(inv_temp.scalar_type() == at::kFloat && top_p.scalar_type() == at::kFloat && us.scalar_type() == at::kFloat &&
+                  limits.scalar_type() == at::kLong && uniform.scalar_type() == at::kByte, "sampling parameter dtypes");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor tok = torch::zeros({B}, logits.options().dtype(at::kLong));
+  Tensor ok = torch::zeros({B}, logits.options().dtype(at::kInt));
+  dlv::launch_sample(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, inv_temp.data_ptr<float>(),
+                     reinterpret_cast<const long long*>(limits.data_ptr<int64_t>()), top_p.data_ptr<float>(), uniform.data_ptr<uint8_t>(),
+                     us.data_ptr<float>(), reinterpret_cast<long long*>(tok.data_ptr<int64_t>()), ok.data_ptr<int>(), cur_stream());
+  check_last_error("sample_rows");
+  return {tok, ok};
+}
 void logits_post(Tensor& logits, c10::optional<Tensor> mask, double softcap, double inv_scale) {
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
   const int B = static_cast<int>(logits.size(0)), V = static_cast<int>(logits.size(1));
@@ -667,6 +688,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("H"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("window") = 0, py::arg("splits") = 1, py::arg("impl") = 0);
   m.def("prefill_attention", &prefill_attention);
   m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
+  m.def("sample_rows", &sample_rows);
   m.def("logits_post", &logits_post, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("moe_route", &moe_route);
   m.def("moe_items", &moe_items);

@@ -81,6 +81,9 @@ void launch_argmax(const float* logits, int ld, int B, int V, const uint32_t* ma
 void launch_logits_post(float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
                         cudaStream_t st);
 
+void launch_sample(const float* logits, int ld, int B, int V, const float* inv_temp, const long long* limits, const float* top_p,
+                   const unsigned char* uniform, const float* us, long long* out_tok, int* out_ok, cudaStream_t st);
+
 // moe.cu
 void launch_moe_route(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
                       int* perm, int* pos, cudaStream_t st);

@@ -83,6 +83,319 @@ __global__ void __launch_bounds__(256) logits_post_kernel(float* __restrict__ lo
   row[i] = mask_allows(mrow, i) ? post_logit(row[i], softcap, inv_scale) : -INFINITY;
 }
 
+// =====================================================================================================================
+// Top-k / top-p / uniform-top-p sampling without sorting the vocabulary
+// =====================================================================================================================
+// Semantics (core/.../model/AbstractGeneratorSampler.java:100-323 as restated in engine/sampler.py): order the tokens by
+// s = logit / T descending (ties: lower id first); keep the first L (top-k); softmax over the kept set; the nucleus is the
+// shortest prefix whose mass reaches top_p; then either a uniform pick inside the nucleus or the inverse-CDF walk with one
+// uniform u. Only three positions of that order matter (the L-th element, the nucleus end, the picked element), so the row
+// is never sorted: one pass builds a 2048-bin histogram (count, weight) over a linear map of [min, max] (clamped to the top
+// 40 nats), prefix sums locate the bin of each position, and only that bin's elements are gathered and sorted in shared
+// memory. Weights are exp(s - max) in 40-bit fixed point and summed with integer atomics: the result does not depend on the
+// order of the additions, so every tensor-parallel rank draws the same token. A bin with more than 4096 elements (or a
+// position inside the clamped tail) makes the row report "not handled" and the caller falls back to the sorting path.
+constexpr int kSampBins = 2048;
+constexpr int kSampCand = 4096;
+constexpr float kSampRange = 40.f;
+constexpr double kSampOne = 1099511627776.0;  // 2^40
+
+struct SampShared {
+  unsigned int cnt[kSampBins];
+  unsigned long long wsum[kSampBins];
+  float ckey[kSampCand];
+  int cidx[kSampCand];
+  unsigned long long cw[kSampCand];
+  float red_f[32];
+  float red_g[32];
+  unsigned int ncand;
+  int bin_sel;
+  unsigned int rank_sel;         // count-based: elements of the bin before the position
+  unsigned long long w_before;   // weight-based: weight in front of the bin
+  int result, fail;
+};
+
+__device__ __forceinline__ unsigned long long samp_weight(float s, float mx) {
+  if (s == -INFINITY) return 0ull;
+  return static_cast<unsigned long long>(exp(static_cast<double>(s) - static_cast<double>(mx)) * kSampOne + 0.5);
+}
+__device__ __forceinline__ int samp_bin(float s, float mx, float scale) {
+  if (s == -INFINITY) return kSampBins - 1;
+  const float d = (mx - s) * scale;
+  return d >= static_cast<float>(kSampBins - 1) ? kSampBins - 1 : static_cast<int>(d);
+}
+// (a sorts before b) in the sampling order: larger key first, then lower index
+__device__ __forceinline__ bool samp_before(float ka, int ia, float kb, int ib) { return ka > kb || (ka == kb && ia < ib); }
+
+// Gather the elements of bin `b` into shared memory and sort them in sampling order. Returns false on overflow.
+__device__ bool samp_collect_sort(SampShared& sh, const float* __restrict__ row, int V, float inv_t, float mx, float scale, int b) {
+  __syncthreads();
+  if (threadIdx.x == 0) sh.ncand = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float s = row[i] * inv_t;
+    if (samp_bin(s, mx, scale) == b) {
+      const unsigned int slot = atomicAdd(&sh.ncand, 1u);
+      if (slot < kSampCand) {
+        sh.ckey[slot] = s;
+        sh.cidx[slot] = i;
+      }
+    }
+  }
+  __syncthreads();
+  const unsigned int n = sh.ncand;
+  if (n > kSampCand) return false;
+  unsigned int np2 = 1;
+  while (np2 < n) np2 <<= 1;
+  for (unsigned int i = n + threadIdx.x; i < np2; i += blockDim.x) {
+    sh.ckey[i] = -INFINITY;
+    sh.cidx[i] = 0x7fffffff;  // padding sorts last
+  }
+  __syncthreads();
+  for (unsigned int k = 2; k <= np2; k <<= 1) {
+    for (unsigned int j = k >> 1; j > 0; j >>= 1) {
+      for (unsigned int i = threadIdx.x; i < np2; i += blockDim.x) {
+        const unsigned int l = i ^ j;
+        if (l > i) {
+          const bool up = (i & k) == 0;
+          const float ka = sh.ckey[i], kb = sh.ckey[l];
+          const int ia = sh.cidx[i], ib = sh.cidx[l];
+          const bool swap = up ? samp_before(kb, ib, ka, ia) : samp_before(ka, ia, kb, ib);
+          if (swap) {
+            sh.ckey[i] = kb;
+            sh.cidx[i] = ib;
+            sh.ckey[l] = ka;
+            sh.cidx[l] = ia;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (unsigned int i = threadIdx.x; i < n; i += blockDim.x) sh.cw[i] = samp_weight(sh.ckey[i], mx);
+  __syncthreads();
+  return true;
+}
+
+// one CTA (1024 threads) per row. out_ok[b] = 0: the row needs the sorting fallback (out_tok[b] is then undefined).
+__global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ inv_temp,
+                                                      const long long* __restrict__ limits, const float* __restrict__ top_p,
+                                                      const unsigned char* __restrict__ uniform, const float* __restrict__ us,
+                                                      long long* __restrict__ out_tok, int* __restrict__ out_ok) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ __align__(16) unsigned char samp_raw[];
+  SampShared& sh = *reinterpret_cast<SampShared*>(samp_raw);
+  const int b = blockIdx.x;
+  const float* row = logits + static_cast<size_t>(b) * ld;
+  const float inv_t = inv_temp[b];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // ---- pass 1: max and smallest finite value of s
+  float mx = -INFINITY, mn = INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float s = row[i] * inv_t;
+    if (s != -INFINITY) {
+      mx = fmaxf(mx, s);
+      mn = fminf(mn, s);
+    }
+  }
+  mx = warp_max(mx);
+  mn = -warp_max(-mn);
+  if (lane == 0) {
+    sh.red_f[warp] = mx;
+    sh.red_g[warp] = mn;
+  }
+  for (int i = threadIdx.x; i < kSampBins; i += blockDim.x) {
+    sh.cnt[i] = 0u;
+    sh.wsum[i] = 0ull;
+  }
+  if (threadIdx.x == 0) {
+    sh.fail = 0;
+    sh.result = 0;
+  }
+  __syncthreads();
+  mx = -INFINITY;
+  mn = INFINITY;
+  for (int w = 0; w < 32; ++w) {
+    mx = fmaxf(mx, sh.red_f[w]);
+    mn = fminf(mn, sh.red_g[w]);
+  }
+  if (mx == -INFINITY) {  // every token masked out
+    if (threadIdx.x == 0) out_ok[b] = 0;
+    return;
+  }
+  const float range = fminf(kSampRange, fmaxf(mx - mn, 1e-6f));
+  const float scale = static_cast<float>(kSampBins - 1) / range;
+  // ---- pass 2: histogram of counts and fixed-point weights
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float s = row[i] * inv_t;
+    const int bin = samp_bin(s, mx, scale);
+    atomicAdd(&sh.cnt[bin], 1u);
+    const unsigned long long w = samp_weight(s, mx);
+    if (w) atomicAdd(&sh.wsum[bin], w);
+  }
+  __syncthreads();
+  // ---- inclusive prefix sums over the bins (warp 0: 64 consecutive bins per lane)
+  if (warp == 0) {
+    constexpr int PER = kSampBins / 32;
+    unsigned int c = 0;
+    unsigned long long w = 0;
+    for (int j = 0; j < PER; ++j) {
+      c += sh.cnt[lane * PER + j];
+      w += sh.wsum[lane * PER + j];
+    }
+    unsigned int ci = c;
+    unsigned long long wi = w;
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned int oc = __shfl_up_sync(0xffffffffu, ci, o);
+      const unsigned long long ow = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) {
+        ci += oc;
+        wi += ow;
+      }
+    }
+    unsigned int cb = ci - c;
+    unsigned long long wb = wi - w;
+    for (int j = 0; j < PER; ++j) {
+      cb += sh.cnt[lane * PER + j];
+      wb += sh.wsum[lane * PER + j];
+      sh.cnt[lane * PER + j] = cb;
+      sh.wsum[lane * PER + j] = wb;
+    }
+  }
+  __syncthreads();
+  auto cum_c = [&](int bin) -> unsigned int { return bin < 0 ? 0u : sh.cnt[bin]; };
+  auto cum_w = [&](int bin) -> unsigned long long { return bin < 0 ? 0ull : sh.wsum[bin]; };
+  const long long Lraw = limits[b];
+  const unsigned int L = static_cast<unsigned int>(Lraw < 1 ? 1 : (Lraw > V ? V : Lraw));
+  // ---- (a) top-k: bin and in-bin count of the L-th element, mass of the kept set
+  int bL = kSampBins;            // bin that holds the L-th element (kSampBins: everything is kept)
+  unsigned int rL = 0;           // kept elements of that bin
+  unsigned long long total = cum_w(kSampBins - 1);
+  if (L < static_cast<unsigned int>(V)) {
+    int lo = 0, hi = kSampBins - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (sh.cnt[mid] >= L) hi = mid; else lo = mid + 1;
+    }
+    bL = lo;
+    rL = L - cum_c(bL - 1);
+    if (bL == kSampBins - 1 || !samp_collect_sort(sh, row, V, inv_t, mx, scale, bL)) {
+      if (threadIdx.x == 0) out_ok[b] = 0;
+      return;
+    }
+    if (threadIdx.x == 0) {
+      unsigned long long acc = cum_w(bL - 1);
+      for (unsigned int j = 0; j < rL; ++j) acc += sh.cw[j];
+      sh.w_before = acc;
+    }
+    __syncthreads();
+    total = sh.w_before;
+    __syncthreads();
+  }
+  // ---- (b) nucleus end
+  const float tp = top_p[b];
+  unsigned int n = L;                 // candidates the pick may come from
+  unsigned long long nuc_total = total;
+  int b_end = bL;                      // bin that holds the last candidate (kSampBins: none, all bins complete)
+  unsigned int r_end = rL;             // candidates of that bin
+  if (tp > 0.f) {
+    const unsigned long long target = static_cast<unsigned long long>(static_cast<double>(tp) * static_cast<double>(total));
+    int lo = 0, hi = bL < kSampBins ? bL : kSampBins - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      const unsigned long long kw = (mid < bL) ? sh.wsum[mid] : total;
+      if (kw >= target) hi = mid; else lo = mid + 1;
+    }
+    const int bp = lo;
+    if (bp == kSampBins - 1 || !samp_collect_sort(sh, row, V, inv_t, mx, scale, bp)) {
+      if (threadIdx.x == 0) out_ok[b] = 0;
+      return;
+    }
+    if (threadIdx.x == 0) {
+      const unsigned int lim = (bp == bL) ? rL : sh.ncand;
+      unsigned long long acc = cum_w(bp - 1);
+      unsigned int r = lim;
+      for (unsigned int j = 0; j < lim; ++j) {
+        acc += sh.cw[j];
+        if (acc >= target) {
+          r = j + 1;
+          break;
+        }
+      }
+      sh.rank_sel = r;
+      sh.w_before = acc;
+    }
+    __syncthreads();
+    b_end = bp;
+    r_end = sh.rank_sel;
+    n = cum_c(bp - 1) + r_end;
+    nuc_total = sh.w_before;
+    __syncthreads();
+  }
+  // ---- (c) the pick
+  const float u = us[b];
+  int bq;
+  if (uniform[b]) {
+    long long pos = static_cast<long long>(u * static_cast<float>(n));
+    if (pos > static_cast<long long>(n) - 1) pos = static_cast<long long>(n) - 1;
+    if (pos < 0) pos = 0;
+    int lo = 0, hi = kSampBins - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (sh.cnt[mid] > static_cast<unsigned int>(pos)) hi = mid; else lo = mid + 1;
+    }
+    bq = lo;
+    if (bq == kSampBins - 1 || !samp_collect_sort(sh, row, V, inv_t, mx, scale, bq)) {
+      if (threadIdx.x == 0) out_ok[b] = 0;
+      return;
+    }
+    if (threadIdx.x == 0) sh.result = sh.cidx[static_cast<unsigned int>(pos) - cum_c(bq - 1)];
+  } else {
+    const unsigned long long t2 = static_cast<unsigned long long>(static_cast<double>(u) * static_cast<double>(nuc_total));
+    int lo = 0, hi = b_end < kSampBins ? b_end : kSampBins - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      const unsigned long long kw = (mid < b_end) ? sh.wsum[mid] : nuc_total;
+      if (kw >= t2) hi = mid; else lo = mid + 1;
+    }
+    bq = lo;
+    if (bq == kSampBins - 1 || !samp_collect_sort(sh, row, V, inv_t, mx, scale, bq)) {
+      if (threadIdx.x == 0) out_ok[b] = 0;
+      return;
+    }
+    if (threadIdx.x == 0) {
+      const unsigned int lim = (bq == b_end) ? r_end : sh.ncand;
+      unsigned long long acc = cum_w(bq - 1);
+      int tok = sh.cidx[lim > 0 ? lim - 1 : 0];
+      for (unsigned int j = 0; j < lim; ++j) {
+        acc += sh.cw[j];
+        if (acc >= t2) {
+          tok = sh.cidx[j];
+          break;
+        }
+      }
+      sh.result = tok;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    out_tok[b] = sh.result;
+    out_ok[b] = 1;
+  }
+}
+
+void launch_sample(const float* logits, int ld, int B, int V, const float* inv_temp, const long long* limits, const float* top_p,
+                   const unsigned char* uniform, const float* us, long long* out_tok, int* out_ok, cudaStream_t st) {
+  if (B == 0) return;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(SampShared)));
+    attr_done = true;
+  }
+  launch_pdl(sample_kernel, dim3(B), dim3(1024), sizeof(SampShared), st, logits, ld, V, inv_temp, limits, top_p, uniform, us, out_tok, out_ok);
+}
+
 void launch_argmax(const float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
                    long long* out_idx, float* out_val, cudaStream_t st) {
   if (B == 0) return;
