@@ -243,7 +243,7 @@ def main() -> int:
         ev0.record()
         for _ in range(args.steps):
             gr["graph"].replay()
-            ops.argmax(gr["logits"])
+            eng._greedy(gr["logits"])
         ev1.record()
         sync_all()
         dev_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
@@ -281,7 +281,7 @@ def main() -> int:
                 ev0.record()
                 for _ in range(args.steps):
                     gr["graph"].replay()
-                    ops.argmax(gr["logits"])
+                    eng._greedy(gr["logits"])
                 ev1.record()
                 sync_all()
                 ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps

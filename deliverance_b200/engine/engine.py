@@ -331,7 +331,7 @@ class Engine:
             batch = make_batch(seqs, self.page_size, self.device)
             batch.decode_splits = self._splits(B)
             logits = self.model.forward(batch, self.kv)
-        idx, _ = ops.argmax(logits)
+        idx = self._greedy(logits)
         ev = None
         if self.device.type == "cuda":
             slot = self.metrics["decode_steps"] & 1
@@ -485,14 +485,22 @@ class Engine:
         inv_scale = 1.0 / cfg.logits_scaling if cfg.logits_scaling not in (0.0, 1.0) else 1.0
         all_greedy_plain = mask is None and all(r.sampling.greedy and not r.params.logprobs for r in reqs)
         if all_greedy_plain:
-            idx, _ = ops.argmax(logits)  # softcap and positive scaling keep the argmax
-            tokens = idx.tolist()
+            tokens = self._greedy(logits).tolist()  # softcap and positive scaling keep the argmax
             lps = [None] * len(reqs)
         else:
+            logits = self._full(logits)
             if mask is not None or cfg.final_softcap > 0 or inv_scale != 1.0:
                 logits = ops.logits_post(logits if not self.use_graphs else logits.clone(), mask, cfg.final_softcap, inv_scale)
             tokens, lps = self.sampler.sample(logits, [r.sampling for r in reqs])
         return self._advance(reqs, tokens, lps)
+
+    def _greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        fn = getattr(self.model, "greedy_tokens", None)
+        return fn(logits) if fn is not None else ops.argmax(logits)[0]
+
+    def _full(self, logits: torch.Tensor) -> torch.Tensor:
+        fn = getattr(self.model, "full_logits", None)
+        return fn(logits) if fn is not None else logits
 
     def _advance(self, reqs: list[Request], tokens: list, lps: list) -> list[Request]:
         now = time.perf_counter()

@@ -19,7 +19,7 @@ from typing import Callable, Optional
 import torch
 
 from .. import ops
-from ..ckpt.loader import ShardSpec, WeightLoader
+from ..ckpt.loader import ShardSpec, WeightLoader, shard_dense, shard_q4
 from ..ckpt.safetensors_io import Q4Tensor
 from ..config import ModelConfig
 from ..ops import LinearWeight, ref
@@ -96,6 +96,8 @@ class DecoderModel:
         self.layer_hook: Optional[Callable[[int, str, torch.Tensor], None]] = None  # debug / trace hook
         self.profiler = None
         self.active_lora: Optional[str] = None
+        self.shard_head = True  # split the output head over the vocabulary under tensor parallelism
+        self.vocab_shard: Optional[tuple] = None
         self._moe_impl = None
 
     # ------------------------------------------------------------------------------------------------ loading
@@ -155,13 +157,26 @@ class DecoderModel:
             head = loader.load("lm_head.weight")
         else:
             head = emb
+        # Under tensor parallelism each rank holds a contiguous slice of the vocabulary rows of the head: it projects 1 / size of
+        # the logits, greedy decoding exchanges one (value, index) pair per row, sampling gathers the slices.
+        self.vocab_shard = None
+        if tp.enabled and self.shard_head and cfg.vocab_size % tp.size == 0:
+            vs = cfg.vocab_size // tp.size
+            self.vocab_shard = (tp.rank * vs, (tp.rank + 1) * vs)
+            spec = ShardSpec("row", tp.rank, tp.size)
+            tied_dense = head is emb and not isinstance(head, Q4Tensor)
+            head = shard_q4(head, spec) if isinstance(head, Q4Tensor) else shard_dense(head, spec)
+        else:
+            tied_dense = head is emb and not isinstance(head, Q4Tensor)
         if head_quant and head_quant.upper() == "Q4" and not isinstance(head, Q4Tensor):
             from ..ckpt.jq4 import q4_quantize
 
             hp, hs = q4_quantize(head.float())
             head = Q4Tensor(hp, hs, tuple(head.shape))
-        if isinstance(head, Q4Tensor) or head is not emb or self.device.type != "cuda":
+        if isinstance(head, Q4Tensor) or not tied_dense or self.device.type != "cuda":
             self.lm_head = self._lin(head)
+        elif self.vocab_shard is not None:
+            self.lm_head = LinearWeight(self.embed[self.vocab_shard[0] : self.vocab_shard[1]])  # a row slice of the embedding table
         else:
             self.lm_head = LinearWeight(self.embed)  # share storage with the embedding table
         if cfg.use_rope:
@@ -382,9 +397,26 @@ class DecoderModel:
         return x
 
     def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
-        """Full-vocabulary fp32 logits (before logit scaling / softcap, which the sampler applies)."""
+        """fp32 logits (before logit scaling / softcap, which the sampler applies): the full vocabulary, or this rank's slice
+        of it when the head is sharded (``vocab_shard``; see :meth:`greedy_tokens` / :meth:`full_logits`)."""
         with self._stage("sampler.output_projection"):
             return ops.linear(hidden_rows, self.lm_head, out_f32=True)
+
+    def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        """First-maximum argmax over the whole vocabulary from (possibly sharded) logits; int64 ``[B]`` on the logits' device."""
+        idx, val = ops.argmax(logits)
+        if self.vocab_shard is None:
+            return idx
+        pair = torch.stack([val.float(), idx.float()], dim=1).contiguous()  # vocabulary slices are < 2^24 wide: exact in fp32
+        parts = torch.stack(self.tp.collectives.all_gather(pair), dim=0)  # [size, B, 2]
+        best = torch.argmax(parts[:, :, 0], dim=0)  # first maximum = lowest rank = lowest global index on ties
+        local = parts[best, torch.arange(parts.shape[1], device=parts.device), 1].to(torch.int64)
+        return local + best.to(torch.int64) * (self.vocab_shard[1] - self.vocab_shard[0])
+
+    def full_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        if self.vocab_shard is None:
+            return logits
+        return torch.cat(self.tp.collectives.all_gather(logits.contiguous()), dim=1)
 
     def forward(self, batch: ForwardBatch, kv, all_rows: bool = False) -> torch.Tensor:
         h = self.forward_hidden(batch, kv)

@@ -104,6 +104,38 @@ def test_kv_head_replication_four_ranks(tmp_path):
     assert out[0] == out[1] == out[2] == out[3] == single[0]
 
 
+def test_vocab_sharded_head_matches_full_head(tmp_path):
+    """Each rank projects its slice of the vocabulary; greedy tokens, sampled tokens and guided tokens equal the unsharded run."""
+    d = str(tmp_path / "vs")
+    write_tiny_model(d, "llama", seed=8, std=0.05, hidden_size=128, intermediate_size=256)
+    cfg = load_config(d)
+    params = [GeneratorParameters(max_tokens=6, temperature=0.0), GeneratorParameters(max_tokens=6, temperature=0.9, top_p=0.8, seed=5),
+              GeneratorParameters(max_tokens=6, temperature=0.0, guided_regex="[0-9]{3}")]
+
+    def run(ctx, out, idx):
+        try:
+            m = DecoderModel(cfg, "cpu", tp=ctx).load(WeightLoader(d))
+            from deliverance_b200.api import CausalLanguageModel
+            from deliverance_b200.tokenizer.auto import AutoTokenizer
+
+            clm = CausalLanguageModel(m, Engine(m, EngineConfig(num_pages=64)), AutoTokenizer.from_pretrained(d), "t")
+            out[idx] = ([clm.generate(PROMPT, p).token_ids for p in params], m.vocab_shard)
+        except Exception as e:  # noqa: BLE001
+            out[idx] = e
+
+    single = [None]
+    run(TensorParallelContext(), single, 0)
+    group = InProcessGroup(2, timeout=60)
+    out = [None, None]
+    ts = [threading.Thread(target=run, args=(TensorParallelContext(r, 2, InProcessCollectives(group, r)), out, r)) for r in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not isinstance(out[0], Exception), out[0]
+    assert not isinstance(out[1], Exception), out[1]
+    assert single[0][1] is None and out[0][1] == (0, cfg.vocab_size // 2) and out[1][1] == (cfg.vocab_size // 2, cfg.vocab_size)
+    assert out[0][0] == out[1][0] == single[0][0]
+
+
 def test_in_process_group_reports_missing_rank():
     g = InProcessGroup(2, timeout=0.3)
     c = InProcessCollectives(g, 0)
