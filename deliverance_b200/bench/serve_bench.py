@@ -155,6 +155,8 @@ def main() -> int:
     model = DecoderModel(cfg, dev, torch.bfloat16, tp).load(SyntheticLoader(shape, 0, a.quant == "jq4", dev, dtype=torch.bfloat16))
     per_seq = (a.prefix + a.unique + a.gen + 256 + 31) // 32
     ec = EngineConfig(max_batch_tokens=8192, max_seqs=a.streams, num_pages=a.streams * per_seq + 64)
+    ec.kv.max_prefix_tokens = max(4096, a.prefix + a.unique)  # the reference's default caches at most 512 prompt tokens
+    ec.kv.policy = "FIXED_BLOCKS"
     eng = Engine(model, ec, eos_ids=(-1,))
     d = tempfile.mkdtemp(prefix="dlv_serve_")
     with open(os.path.join(d, "config.json"), "w") as f:

@@ -103,6 +103,8 @@ class PrefixCache:
         self.alloc = allocator
         self.entries: "OrderedDict[bytes, PrefixEntry]" = OrderedDict()
         self.metrics = {"lookup": 0, "hits": 0, "misses": 0, "evict": 0, "stored": 0, "hit_tokens": 0}
+        self.disk = None  # optional second tier (kv.disk.DiskPrefixStore), attached by PagedKVCache.attach_disk
+        self.kv = None
 
     @staticmethod
     def key(salt: str, tokens: list[int]) -> bytes:
@@ -126,6 +128,15 @@ class PrefixCache:
                 self.entries.move_to_end(k)
                 best = e
                 break
+        if best is None and self.disk is not None:
+            for L in sorted(self.settings.checkpoint_lengths(len(tokens)), reverse=True):
+                k = self.key(salt, tokens[:L])
+                if self.disk.has(k):
+                    got = self.disk.load(self.kv, k)
+                    if got is not None:
+                        best = PrefixEntry(got[0], got[1], None)
+                        self.entries[k] = best  # the entry owns the references taken by load()
+                        break
         if best is None:
             self.metrics["misses"] += 1
             return None
@@ -161,7 +172,9 @@ class PrefixCache:
     def evict_one(self) -> bool:
         if not self.entries:
             return False
-        _, e = self.entries.popitem(last=False)
+        k, e = self.entries.popitem(last=False)
+        if self.disk is not None and e.state is None and not self.disk.has(k):
+            self.disk.save(self.kv, k, e.pages, e.length)  # spill before the pages go back to the allocator
         for p in e.pages:
             self.alloc.release(p)
         self.metrics["evict"] += 1
@@ -198,6 +211,7 @@ class PagedKVCache:
                 self.v.append(torch.zeros(shape, dtype=dtype, device=self.device))
         self.allocator = PageAllocator(num_pages)
         self.prefix = PrefixCache(self.settings, self.allocator)
+        self.prefix.kv = self
         # recurrent state (hybrid models): per layer conv_state [slots, convDim, K-1] and ssm_state [slots, H, d_head, S]
         self.conv_state: dict[int, torch.Tensor] = {}
         self.ssm_state: dict[int, torch.Tensor] = {}
@@ -255,6 +269,13 @@ class PagedKVCache:
             self.conv_state[i][slot].copy_(t)
         for i, t in snap["ssm"].items():
             self.ssm_state[i][slot].copy_(t)
+
+    def attach_disk(self, directory: str, compression: str = "LZ4", bits: int = 4, max_bytes: int = 8 << 30):
+        """Spill evicted prefixes to ``directory`` and pull them back on later hits (attention-only models)."""
+        from .disk import DiskPrefixStore
+
+        self.prefix.disk = DiskPrefixStore(directory, compression, bits, max_bytes)
+        return self.prefix.disk
 
     def gather_rows(self, layer: int, pages: list[int], n_tokens: int):
         """Dense ``[KV, n_tokens, D]`` copies of K and V (tests, snapshots, debugging)."""

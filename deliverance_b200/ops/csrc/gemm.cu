@@ -463,7 +463,9 @@ __global__ void __launch_bounds__(128) gemv_simt_kernel(const void* __restrict__
 // Fine-grained mixture-of-experts decode: dozens of experts with one to eight rows each. The tensor-core kernel pays ~5 us
 // of fixed cost per CTA on every (expert, tile) pair; here one warp owns one weight row of one work item and multiplies it
 // with the item's (up to MT) token rows, so a work item costs a few hundred instructions and the kernel is bound by the
-// weight stream. grid (ceil(N / 4), max_items), 4 warps; items as built by launch_moe_items with bn == MT.
+// weight stream. grid (ceil(N / 32), max_items), 4 warps x 8 weight rows each (a CTA per weight row would spend more time
+// being launched than working); items as built by launch_moe_items with bn == MT.
+constexpr int kGemvRowsPerWarp = 8;
 template <int MT, bool Q4>
 __global__ void __launch_bounds__(128) gemv_grouped_kernel(const void* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
                                                            __nv_bfloat16* __restrict__ out, int ldo, int N, int K,
@@ -472,11 +474,12 @@ __global__ void __launch_bounds__(128) gemv_grouped_kernel(const void* __restric
   pdl_trigger();
   const int4 it = items[blockIdx.y];
   if (it.x < 0) return;
-  const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (n >= N) return;
   const int r0 = it.y;
   const int cnt = min(MT, it.z - it.y);
+  for (int rw = 0; rw < kGemvRowsPerWarp; ++rw) {
+  const int n = (blockIdx.x * 4 + (threadIdx.x >> 5)) * kGemvRowsPerWarp + rw;
+  if (n >= N) return;
   float acc[MT];
 #pragma unroll
   for (int m = 0; m < MT; ++m) acc[m] = 0.f;
@@ -550,6 +553,7 @@ __global__ void __launch_bounds__(128) gemv_grouped_kernel(const void* __restric
     for (int m = 0; m < MT; ++m)
       if (m < cnt) out[static_cast<size_t>(r0 + m) * ldo + n] = f2bf(acc[m]);
   }
+  }
 }
 
 void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,
@@ -557,7 +561,7 @@ void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, 
   if (max_items <= 0) return;
   if (ldx % 8 != 0 || w->K % 8 != 0) throw std::runtime_error("grouped gemv needs 16-byte aligned rows");
   if (max_items > 65535) throw std::runtime_error("grouped gemv: work list too long");
-  const dim3 grid((n_per_expert + 3) / 4, max_items);
+  const dim3 grid((n_per_expert + 4 * kGemvRowsPerWarp - 1) / (4 * kGemvRowsPerWarp), max_items);
   const int4* it = reinterpret_cast<const int4*>(items);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);

@@ -241,3 +241,33 @@ def test_concurrent_arrivals_share_prefix_through_cache(tmp_path):
     got, m, tokens_cached = run(True, 100)
     assert got == base
     assert m["hits"] >= 4 and tokens_cached < tokens_nocache * 0.6
+
+
+def test_disk_tier_restores_evicted_prefix(tmp_path):
+    """A prefix evicted from memory is written to disk, found again by a later request and gives the same tokens."""
+    from deliverance_b200.ckpt.loader import WeightLoader
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.config import load_config
+    from deliverance_b200.engine.engine import Engine, EngineConfig
+    from deliverance_b200.models.transformer import DecoderModel
+    from deliverance_b200.params import GeneratorParameters
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=14, std=0.08)
+    model = DecoderModel(load_config(d), "cpu").load(WeightLoader(d))
+    a = [(5 * i + 1) % 250 + 1 for i in range(70)]
+    b = [(11 * i + 7) % 250 + 1 for i in range(70)]
+    p = GeneratorParameters(max_tokens=4, temperature=0.0)
+    ec = EngineConfig(num_pages=64)
+    ec.kv.max_entries = 2  # tiny in-memory tier: the next prompt's entries push the previous ones out
+    ec.kv.policy = "ANCHORS"
+    eng = Engine(model, ec, eos_ids=(-1,))
+    disk = eng.kv.attach_disk(str(tmp_path / "kvdisk"), compression="LZ4")
+    first = eng.generate(a, p).token_ids
+    eng.generate(b, p)
+    assert disk.metrics["disk_writes"] >= 1 and eng.kv.prefix.metrics["evict"] >= 1
+    computed_before = eng.metrics["prefill_tokens"]
+    again = eng.generate(a, p).token_ids
+    assert again == first
+    assert disk.metrics["disk_hits"] >= 1
+    assert eng.metrics["prefill_tokens"] - computed_before < len(a)  # part of the prompt came back from disk
