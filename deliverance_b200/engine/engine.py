@@ -275,7 +275,8 @@ class Engine:
         for r in reqs:
             pos = r.total_len - 1 + r.pending  # position of the token being fed (the last sampled one)
             self.kv.ensure_pages(r.pages, pos + 1)
-            seqs.append({"tokens": [r.output[-1] if r.output else 0], "start": pos, "pages": r.pages, "state_slot": max(r.state_slot, 0)})
+            seqs.append({"tokens": [r.output[-1] if r.output else 0], "start": pos, "pages": r.pages, "state_slot": max(r.state_slot, 0),
+                         "rid": r.rid})
         return seqs
 
     def _plain_greedy(self, reqs: list[Request]) -> bool:
@@ -399,13 +400,20 @@ class Engine:
         h["ctx"][:n] = torch.tensor([p + 1 for p in starts], dtype=torch.int32)
         width = max(len(s["pages"]) for s in seqs)
         bt = h["bt"]
+        owners = g.setdefault("bt_owners", [None] * bucket)
         for i, s in enumerate(seqs):
             pg = s["pages"]
+            key = (s.get("rid"), len(pg))  # a request's page list only grows: same owner and length = same row
+            if key[0] is not None and owners[i] == key:
+                continue
+            owners[i] = key
             row = s.get("bt_row")
             if row is not None:
                 bt[i, : len(pg)] = row[: len(pg)]
             else:
                 bt[i, : len(pg)] = torch.tensor(pg, dtype=torch.int32)
+        for i in range(n, bucket):
+            owners[i] = None
         if self.hybrid:
             h["st"][:n] = torch.tensor([s["state_slot"] for s in seqs], dtype=torch.int64)
         if n < bucket:
@@ -477,11 +485,23 @@ class Engine:
         mask = None
         if any(r.guide is not None for r in reqs):
             words = (cfg.vocab_size + 31) // 32
-            m = torch.full((len(reqs), words), -1, dtype=torch.int32)
-            for i, r in enumerate(reqs):
-                if r.guide is not None:
-                    m[i] = r.guide.allowed_mask()
-            mask = m.to(logits.device, non_blocking=True)
+            dev = logits.device
+            if dev.type == "cuda":
+                # masks live on the device per automaton state (uploaded once); the step only gathers rows
+                mask = torch.full((len(reqs), words), -1, dtype=torch.int32, device=dev)
+                idx, rows = [], []
+                for i, r in enumerate(reqs):
+                    if r.guide is not None:
+                        on = getattr(r.guide, "allowed_mask_on", None)
+                        rows.append(on(dev) if on is not None else r.guide.allowed_mask().to(dev))
+                        idx.append(i)
+                mask[torch.tensor(idx, device=dev)] = torch.stack(rows)
+            else:
+                m = torch.full((len(reqs), words), -1, dtype=torch.int32)
+                for i, r in enumerate(reqs):
+                    if r.guide is not None:
+                        m[i] = r.guide.allowed_mask()
+                mask = m
         inv_scale = 1.0 / cfg.logits_scaling if cfg.logits_scaling not in (0.0, 1.0) else 1.0
         all_greedy_plain = mask is None and all(r.sampling.greedy and not r.params.logprobs for r in reqs)
         if all_greedy_plain:

@@ -172,6 +172,16 @@ class LazyIndex:
             self._masks[state] = m
         return m
 
+    def mask_on(self, state: int, device) -> torch.Tensor:
+        """The allow-bitmask of ``state`` as a tensor on ``device`` (uploaded once per state and kept)."""
+        cache = self.__dict__.setdefault("_dev_masks", {})
+        key = (state, str(device))
+        m = cache.get(key)
+        if m is None:
+            m = self.mask(state).to(device)
+            cache[key] = m
+        return m
+
     def next_state(self, state: int, token: int) -> Optional[int]:
         return self.transitions(state).get(token)
 
@@ -229,6 +239,9 @@ class IndexGuide(Guide):
 
     def allowed_mask(self) -> torch.Tensor:
         return self.index.mask(self.state)
+
+    def allowed_mask_on(self, device) -> torch.Tensor:
+        return self.index.mask_on(self.state, device)
 
     def accept(self, token: int) -> None:
         if token in self.index.vocab.eos_ids:
