@@ -46,28 +46,34 @@ def moe_forward(model, i: int, lw, x: torch.Tensor) -> torch.Tensor:
 
 def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
     e = ops.require_ext()
+    st = model._stage
     T, H = x.shape
     rows = T * k
-    # weights [T, k] fp32, expert ids [T, k], counts [E], offsets [E + 1], perm: grouped row -> (token * k + slot), pos: inverse
-    w, idx, counts, offsets, perm, pos = e.moe_route(logits.contiguous(), k, 0 if mode == "softmax_topk" else 1, bool(renorm))
-    ops._count(2)
     ep = ne != E
-    rng = (offsets, e0, ne) if ep else (None, 0, 0)
-    xs = e.moe_gather(x, perm, k, *rng)  # [T * k, H] rows grouped by expert (only the local experts' rows are filled)
-    bn = ops.moe_token_tile(rows if not ep else max(1, rows * ne // E), ne)
-    max_items = min((rows + bn - 1) // bn + ne, rows) if rows >= ne else rows
-    max_items = max(1, max_items)
-    items = e.moe_items(offsets, e0, ne, bn, max_items)
-    ops._count(2)
+    with st("moe.route"):
+        # weights [T, k] fp32, expert ids [T, k], counts [E], offsets [E + 1], perm: grouped row -> (token * k + slot), pos: inverse
+        w, idx, counts, offsets, perm, pos = e.moe_route(logits.contiguous(), k, 0 if mode == "softmax_topk" else 1, bool(renorm))
+        ops._count(2)
+        rng = (offsets, e0, ne) if ep else (None, 0, 0)
+        xs = e.moe_gather(x, perm, k, *rng)  # [T * k, H] rows grouped by expert (only the local experts' rows are filled)
+        bn = ops.moe_token_tile(rows if not ep else max(1, rows * ne // E), ne)
+        max_items = min((rows + bn - 1) // bn + ne, rows) if rows >= ne else rows
+        max_items = max(1, max_items)
+        items = e.moe_items(offsets, e0, ne, bn, max_items)
+        ops._count(2)
     gu_w, down_w = lw.experts_gate_up_grouped, lw.experts_down_grouped
     small = bn <= 64  # decode-sized groups: split K so that more CTAs stream weights
-    gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
-    hmid = ops.act_mul(gu, act)
-    ys = down_w.run(hmid, items, bn, max(1, min(8, down_w.K // 1024)) if small else 1)
-    fused = getattr(model.tp, "fused", None)
-    if ep and fused is not None:
-        y = fused.moe_combine_all_reduce(ys, pos, w, T, k, offsets, e0, ne)  # combine + sum over ranks in one kernel
-        if y is not None:
-            return y, True
-    ops._count()
-    return e.moe_combine(ys, pos, w, T, k, *rng), False
+    with st("moe.gate_up"):
+        gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
+    with st("moe.activation_multiply"):
+        hmid = ops.act_mul(gu, act)
+    with st("moe.down"):
+        ys = down_w.run(hmid, items, bn, max(1, min(8, down_w.K // 1024)) if small else 1)
+    with st("moe.combine"):
+        fused = getattr(model.tp, "fused", None)
+        if ep and fused is not None:
+            y = fused.moe_combine_all_reduce(ys, pos, w, T, k, offsets, e0, ne)  # combine + sum over ranks in one kernel
+            if y is not None:
+                return y, True
+        ops._count()
+        return e.moe_combine(ys, pos, w, T, k, *rng), False
