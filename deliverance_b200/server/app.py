@@ -38,6 +38,12 @@ class ServerSettings:
     heartbeat_s: float = 1.0
     request_timeout_s: float = 600.0
     pre_generate: Optional[Callable[[dict, GeneratorParameters], Optional[str]]] = None  # may rewrite or reject (return error text)
+    # Under load every streamed token costs the interpreter an event-loop wake-up, a JSON chunk and a socket write, and with
+    # a hundred streams that work competes with the engine thread. Above `coalesce_above` concurrent requests a stream sends
+    # one chunk per `coalesce_tokens` tokens (or every `coalesce_ms`); the first token always goes out at once.
+    coalesce_above: int = 16
+    coalesce_tokens: int = 4
+    coalesce_ms: float = 50.0
 
     @property
     def reasoning_key(self) -> str:
@@ -195,10 +201,27 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         loop = asyncio.get_running_loop()
         q: asyncio.Queue = asyncio.Queue()
 
+        pending: list = []  # pieces not yet handed to the event loop (touched by the engine thread only)
+        sent = {"first": True, "at": time.monotonic()}
+
+        def flush():
+            if pending:
+                text = "".join(pending)
+                pending.clear()
+                sent["at"] = time.monotonic()
+                loop.call_soon_threadsafe(q.put_nowait, ("tok", text))
+
         def on_event(tok, piece, text_sp, ms):
-            loop.call_soon_threadsafe(q.put_nowait, ("tok", piece))
+            if piece:
+                pending.append(piece)
+            busy = len(runner.active) > settings.coalesce_above
+            if sent["first"] or not busy or len(pending) >= settings.coalesce_tokens or (time.monotonic() - sent["at"]) * 1e3 >= settings.coalesce_ms:
+                if pending:
+                    sent["first"] = False
+                flush()
 
         def on_done(sub):
+            flush()
             loop.call_soon_threadsafe(q.put_nowait, ("done", sub))
 
         sub = runner.submit(prompt, params, on_event, on_done, session)
