@@ -30,7 +30,8 @@ import time
 def _schema(rng: random.Random) -> dict:
     props = {}
     for i in range(8):
-        props[f"f{i}_{rng.randrange(1000)}"] = {"type": "string", "maxLength": 12} if rng.random() < 0.5 else {"type": "integer"}
+        # bounded value sets: a random-init model would otherwise emit digits until max_tokens and never close the object
+        props[f"f{i}_{rng.randrange(1000)}"] = {"type": "string", "maxLength": 6} if rng.random() < 0.5 else {"enum": [rng.randrange(100) for _ in range(3)]}
     return {"type": "object", "properties": props, "required": list(props), "additionalProperties": False}
 
 
