@@ -225,6 +225,36 @@ def main() -> int:
             roof = max(hbm_us, nvl_us)
             report(check="bench_linear_all_reduce", world=world, M=M, N=N, K_per_rank=Ks, fused_us=res["fused"], gemm_nccl_us=res["gemm+nccl"],
                    roofline_us=roof, fused_frac_of_roofline=roof / res["fused"], speedup_vs_nccl=res["gemm+nccl"] / res["fused"])
+        # fused MoE combine + all-reduce against the local combine followed by the NCCL all-reduce
+        for (T, E, k, Hd) in ((64, 8 * world if world > 8 else 8 if 8 % world == 0 else world, 2, 4096), (32, 128 if 128 % world == 0 else 16 * world, 8, 2048)):
+            ne, e0 = E // world, rank * (E // world)
+            g2 = torch.Generator().manual_seed(9)
+            w_, idx, counts, offsets, perm, pos = e.moe_route(torch.randn(T, E, generator=g2).to(dev), k, 0, True)
+            ys = (torch.randn(T * k, Hd, generator=g2) * 0.5).to(torch.bfloat16).to(dev)
+            res = {}
+            for mode in ("fused", "combine+nccl"):
+                def run():
+                    if mode == "fused":
+                        return fused.moe_combine_all_reduce(ys, pos, w_, T, k, offsets, e0, ne)
+                    y = e.moe_combine(ys, pos, w_, T, k, offsets, e0, ne)
+                    dist.all_reduce(y)
+                    return y
+                for _ in range(10):
+                    run()
+                torch.cuda.synchronize()
+                dist.barrier()
+                e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0_.record()
+                for _ in range(50):
+                    run()
+                e1_.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0_.elapsed_time(e1_) * 1e3 / 50], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                res[mode] = t.item()
+            nvl_us = (world - 1) * T * Hd * 2 / 770e3  # bytes this GPU sends at the measured peer-copy rate
+            report(check="bench_moe_combine_all_reduce", world=world, T=T, E=E, k=k, H=Hd, fused_us=res["fused"], combine_nccl_us=res["combine+nccl"],
+                   nvlink_roofline_us=nvl_us, speedup_vs_nccl=res["combine+nccl"] / res["fused"])
     dist.barrier()
     dist.destroy_process_group()
     return 0 if ok_all else 1
