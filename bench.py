@@ -30,7 +30,7 @@ REFERENCE_DECODE_TOK_S = 12.06
 
 
 def reference_arm(args) -> int:
-    why = ("reference is a Java 25 + Maven multi-module project: `pip install /root/reference` fails (no setup.py / "
+    why = ("reference is a Java 25 + Maven multi-module project: `pip install` of its source tree fails (no setup.py / "
            "pyproject.toml) and neither a JDK nor Maven nor its online dependencies exist on this box")
     print(json.dumps({"impl": "reference", "unavailable": why, "n_gpus": args.gpus}))
     return 0

@@ -1,6 +1,6 @@
 """Random-weight checkpoints with the real tensor names and shape formulas of every supported family.
 
-Used by the tests (tiny shapes) and by the benchmarks (full BASELINE shapes, random-init N(0, 0.02)), mirroring the
+Used by the tests (tiny shapes) and by the benchmarks (full benchmark shapes, random-init N(0, 0.02)), mirroring the
 reference's "HF-ported" test suites that write a synthetic model directory and load it through the normal loader
 (core/src/test/.../model/qwen3/Qwen3HfTextModelPortedTest.java:86-93).
 """
