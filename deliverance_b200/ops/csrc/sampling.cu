@@ -71,6 +71,83 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
   }
 }
 
+// Two-stage argmax for large vocabularies and few rows: one CTA per row reads 600 KB alone (64 CTAs on 148 SMs, ~0.5 TB/s);
+// here kArgmaxSeg CTAs share a row and a second small kernel keeps the first maximum. The partial results live in a static
+// device buffer (rows <= kArgmaxRows): launches on different streams of one device must not overlap.
+constexpr int kArgmaxSeg = 8;
+constexpr int kArgmaxRows = 1024;
+static __device__ float g_argmax_val[kArgmaxRows * kArgmaxSeg];
+static __device__ int g_argmax_idx[kArgmaxRows * kArgmaxSeg];
+
+__global__ void __launch_bounds__(512) argmax_part_kernel(const float* __restrict__ logits, int ld, int V, const uint32_t* __restrict__ mask,
+                                                          int mask_ld) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float sv[16];
+  __shared__ int si[16];
+  const int b = blockIdx.x, seg = blockIdx.y;
+  const int per = (((V + kArgmaxSeg - 1) / kArgmaxSeg) + 3) & ~3;
+  const int lo = seg * per, hi = min(V, lo + per);
+  const float* row = logits + static_cast<size_t>(b) * ld;
+  const uint32_t* mrow = mask ? mask + static_cast<size_t>(b) * mask_ld : nullptr;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    if (!mask_allows(mrow, i)) continue;
+    const float v = row[i];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) {
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+        best = sv[w];
+        bi = si[w];
+      }
+    }
+    g_argmax_val[b * kArgmaxSeg + seg] = best;
+    g_argmax_idx[b * kArgmaxSeg + seg] = bi;
+  }
+}
+
+__global__ void __launch_bounds__(32) argmax_final_kernel(const float* __restrict__ logits, int ld, float softcap, float inv_scale,
+                                                          long long* __restrict__ out_idx, float* __restrict__ out_val) {
+  pdl_wait();
+  pdl_trigger();
+  const int b = blockIdx.x;
+  if (threadIdx.x != 0) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int s = 0; s < kArgmaxSeg; ++s) {
+    const float v = g_argmax_val[b * kArgmaxSeg + s];
+    const int i = g_argmax_idx[b * kArgmaxSeg + s];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+  if (bi == 0x7fffffff) bi = 0;  // every token masked or all logits -inf / NaN
+  out_idx[b] = bi;
+  if (out_val) out_val[b] = post_logit(logits[static_cast<size_t>(b) * ld + bi], softcap, inv_scale);
+}
+
 __global__ void __launch_bounds__(256) logits_post_kernel(float* __restrict__ logits, int ld, int V, const uint32_t* __restrict__ mask,
                                                           int mask_ld, float softcap, float inv_scale) {
   pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
@@ -399,6 +476,11 @@ void launch_sample(const float* logits, int ld, int B, int V, const float* inv_t
 void launch_argmax(const float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
                    long long* out_idx, float* out_val, cudaStream_t st) {
   if (B == 0) return;
+  if (V >= 32768 && B <= kArgmaxRows && B * 2 <= 296) {  // few long rows: split each row over several CTAs
+    launch_pdl(argmax_part_kernel, dim3(B, kArgmaxSeg), dim3(512), 0, st, logits, ld, V, mask, mask_ld);
+    launch_pdl(argmax_final_kernel, dim3(B), dim3(32), 0, st, logits, ld, softcap, inv_scale, out_idx, out_val);
+    return;
+  }
   launch_pdl(argmax_kernel, dim3(B), dim3(1024), 0, st, logits, ld, V, mask, mask_ld, softcap, inv_scale, out_idx, out_val);
 }
 void launch_logits_post(float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,

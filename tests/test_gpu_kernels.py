@@ -187,6 +187,11 @@ def test_argmax_and_logits_post():
         mask[b, t // 32] = 1 << (t % 32) if t % 32 != 31 else -(1 << 31)
     idx2, _ = ops.argmax(logits, mask)
     assert idx2.tolist() == allowed
+    # 64 rows (two-stage path: several CTAs per row) and a short vocabulary (one CTA per row), values included
+    for BB, VV in ((64, 151936), (130, 151936), (7, 1000)):
+        lg = torch.randn(BB, VV, device=DEV)
+        i3, v3 = ops.argmax(lg)
+        assert torch.equal(i3, torch.argmax(lg, dim=-1)) and torch.allclose(v3, lg.max(dim=-1).values)
     l2 = logits.clone()
     ops.logits_post(l2, mask, 30.0, 0.5)
     exp = torch.tanh(logits * 0.5 / 30.0) * 30.0
