@@ -2,17 +2,63 @@
 
 The reference keeps evicted / cold KV pages in a disk backend that is a cache, not durable state (core/DiskKvBackend.md:6-12;
 core/.../tensor/KvBufferCache.java ``kvbuffercache.disk.*`` counters). Here an evicted prefix entry (attention layers only)
-is snapshotted with :func:`kv.turboquant.snapshot_pages` (``NONE`` | ``LZ4`` | ``MSE_TURBOQUANT``) into one file named after
-the prefix key; a lookup that misses in memory probes the directory for the policy's checkpoint lengths, allocates pages,
+is snapshotted with :func:`kv.turboquant.snapshot_pages` (``NONE`` | ``LZ4`` | ``MSE_TURBOQUANT``) into one safetensors file
+(arrays plus a JSON header, nothing executable) named after the prefix key; a lookup that misses in memory probes the directory for the policy's checkpoint lengths, allocates pages,
 restores the rows and re-registers the entry. Files are evicted oldest-first beyond ``max_bytes``.
 """
 from __future__ import annotations
 
+import json
 import os
-import pickle
 from typing import Optional
 
-from .turboquant import restore_pages, snapshot_pages
+import torch
+
+from ..ckpt.safetensors_io import SafeTensorFile, write_safetensors
+from .turboquant import Encoded, MseTurboQuantCodec, restore_pages, snapshot_pages
+
+
+def _pack(snap: dict) -> tuple[dict, dict]:
+    """Snapshot -> (tensors, metadata) for a safetensors file: nothing executable is stored, only arrays and a JSON header."""
+    tensors, layers = {}, {}
+    comp = snap["compression"]
+    for i, (a, b) in snap["layers"].items():
+        for tag, v in (("k", a), ("v", b)):
+            name = f"l{i}.{tag}"
+            if comp == "MSE_TURBOQUANT":
+                tensors[name + ".codes"], tensors[name + ".norms"] = v.codes, v.norms
+                layers[name] = {"shape": list(v.shape), "bits": v.bits}
+            elif comp == "LZ4":
+                raw, shape, dtype = v
+                tensors[name] = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+                layers[name] = {"shape": list(shape), "dtype": str(dtype).replace("torch.", "")}
+            else:
+                tensors[name] = v.contiguous()
+    codec = snap.get("codec")
+    meta = {"compression": comp, "n_tokens": str(snap["n_tokens"]), "layers": json.dumps(layers), "layer_ids": json.dumps(sorted(snap["layers"])),
+            "codec": json.dumps({"dim": codec.dim, "bits": codec.bits} if codec is not None else None)}
+    return tensors, meta
+
+
+def _unpack(f: SafeTensorFile) -> dict:
+    meta = f.metadata
+    comp = meta["compression"]
+    info = json.loads(meta["layers"])
+    codec_cfg = json.loads(meta["codec"])
+    snap = {"compression": comp, "n_tokens": int(meta["n_tokens"]), "layers": {},
+            "codec": MseTurboQuantCodec(codec_cfg["dim"], codec_cfg["bits"]) if codec_cfg else None}
+    for i in json.loads(meta["layer_ids"]):
+        pair = []
+        for tag in ("k", "v"):
+            name = f"l{i}.{tag}"
+            if comp == "MSE_TURBOQUANT":
+                pair.append(Encoded(f.tensor(name + ".codes").clone(), f.tensor(name + ".norms").clone(), tuple(info[name]["shape"]), info[name]["bits"]))
+            elif comp == "LZ4":
+                pair.append((f.tensor(name).numpy().tobytes(), tuple(info[name]["shape"]), getattr(torch, info[name]["dtype"])))
+            else:
+                pair.append(f.tensor(name).clone())
+        snap["layers"][i] = tuple(pair)
+    return snap
 
 
 class DiskPrefixStore:
@@ -33,8 +79,8 @@ class DiskPrefixStore:
     def save(self, kv, key: bytes, pages: list[int], length: int) -> None:
         snap = snapshot_pages(kv, pages, length, self.compression, self.bits)
         tmp = self._path(key) + ".tmp"
-        with open(tmp, "wb") as f:
-            pickle.dump(snap, f, protocol=pickle.HIGHEST_PROTOCOL)
+        tensors, meta = _pack(snap)
+        write_safetensors(tmp, tensors, meta)
         os.replace(tmp, self._path(key))
         self.metrics["disk_writes"] += 1
         self._trim()
@@ -43,9 +89,8 @@ class DiskPrefixStore:
         """Allocate pages and restore the prefix; returns (pages, length) holding one reference each, or None."""
         path = self._path(key)
         try:
-            with open(path, "rb") as f:
-                snap = pickle.load(f)
-        except (OSError, pickle.UnpicklingError, EOFError):
+            snap = _unpack(SafeTensorFile(path))
+        except (OSError, ValueError, KeyError):
             self.metrics["disk_misses"] += 1
             return None
         n_pages = (snap["n_tokens"] + kv.page_size - 1) // kv.page_size

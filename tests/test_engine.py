@@ -271,3 +271,23 @@ def test_disk_tier_restores_evicted_prefix(tmp_path):
     assert again == first
     assert disk.metrics["disk_hits"] >= 1
     assert eng.metrics["prefill_tokens"] - computed_before < len(a)  # part of the prompt came back from disk
+
+
+@pytest.mark.parametrize("compression", ["NONE", "MSE_TURBOQUANT"])
+def test_disk_store_formats_roundtrip(tmp_path, compression):
+    from deliverance_b200.kv.disk import DiskPrefixStore
+    from deliverance_b200.kv.paged import PagedKVCache
+
+    layout = {"layers": 2, "kv_heads": 2, "head_dim": 64, "layer_kinds": ["attention", "attention"]}
+    kv = PagedKVCache(layout, 16, "cpu", torch.float32)
+    g = torch.Generator().manual_seed(2)
+    for t in kv.k + kv.v:
+        t.copy_(torch.randn(t.shape, generator=g))
+    store = DiskPrefixStore(str(tmp_path / "d"), compression=compression, bits=4)
+    store.save(kv, b"\\x01" * 20, [3, 7], 40)
+    before = kv.gather_rows(1, [3, 7], 40)
+    pages, n = store.load(kv, b"\\x01" * 20)
+    after = kv.gather_rows(1, pages, n)
+    tol = 0.0 if compression == "NONE" else 0.2
+    assert n == 40 and ((after[0] - before[0]).norm() / before[0].norm()).item() <= tol + 1e-7
+    assert store.load(kv, b"\\x02" * 20) is None and store.metrics["disk_misses"] == 1
