@@ -36,17 +36,22 @@ struct CommParams {
 __device__ __forceinline__ bool exchange_barrier(const CommParams& p, unsigned cta_id, int* s_flag) {
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int r = 0; r < p.size; ++r) {
-      const int dst = (p.rank + r) % p.size;
-      red_release_sys_add(reinterpret_cast<uint32_t*>(p.flags[dst]) + static_cast<size_t>(p.rank) * p.ncta_max + cta_id, 1u);
-    }
+  if (threadIdx.x < 32) {
+    // one lane per peer: release-adds and flag waits of all peers proceed side by side
+    const int lane = threadIdx.x;
     const unsigned round = p.rounds[cta_id];
-    bool all = true;
-    const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flags[p.rank]);
-    for (int src = 0; src < p.size && all; ++src) all = flag_wait_ge(mine + static_cast<size_t>(src) * p.ncta_max + cta_id, round + 1u, p.status);
-    p.rounds[cta_id] = round + 1u;
-    *s_flag = all ? 1 : 0;
+    bool ok_lane = true;
+    if (lane < p.size) {
+      const int dst = (p.rank + lane) % p.size;
+      red_release_sys_add(reinterpret_cast<uint32_t*>(p.flags[dst]) + static_cast<size_t>(p.rank) * p.ncta_max + cta_id, 1u);
+      const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flags[p.rank]);
+      ok_lane = flag_wait_ge(mine + static_cast<size_t>(lane) * p.ncta_max + cta_id, round + 1u, p.status);
+    }
+    const bool all = __all_sync(0xffffffffu, ok_lane);
+    if (lane == 0) {
+      p.rounds[cta_id] = round + 1u;
+      *s_flag = all ? 1 : 0;
+    }
   }
   __syncthreads();
   return *s_flag != 0;

@@ -565,19 +565,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       }
       __threadfence_system();
       asm volatile("bar.sync 1, 512;" ::: "memory");
-      if (t == 0) {
-        for (int r = 0; r < p.tp_size; ++r) {
-          const int dst = (p.tp_rank + r) % p.tp_size;
-          red_release_sys_add(reinterpret_cast<uint32_t*>(p.tp_flags[dst]) + static_cast<size_t>(p.tp_rank) * p.tp_ncta_max + cta_id, 1u);
-        }
-        // phase B gate: every rank has published this CTA's region for this call
+      if (t < 32) {
+        // One lane per peer: the release-adds (each carries a system-scope fence) and the flag waits of the tp_size peers run
+        // side by side; issued by a single thread they cost tp_size serial fence round trips (measured: 8 ranks, +20 us).
         const unsigned round = p.tp_rounds[cta_id];
-        bool all = true;
-        const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.tp_flags[p.tp_rank]);
-        for (int src = 0; src < p.tp_size && all; ++src)
-          all = flag_wait_ge(mine + static_cast<size_t>(src) * p.tp_ncta_max + cta_id, round + 1u, p.status);
-        p.tp_rounds[cta_id] = round + 1u;
-        *s_last = all ? 1 : 0;
+        bool ok_lane = true;
+        if (t < p.tp_size) {
+          const int dst = (p.tp_rank + t) % p.tp_size;
+          red_release_sys_add(reinterpret_cast<uint32_t*>(p.tp_flags[dst]) + static_cast<size_t>(p.tp_rank) * p.tp_ncta_max + cta_id, 1u);
+          // phase B gate: rank `t` has published this CTA's region for this call
+          const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.tp_flags[p.tp_rank]);
+          ok_lane = flag_wait_ge(mine + static_cast<size_t>(t) * p.tp_ncta_max + cta_id, round + 1u, p.status);
+        }
+        const bool all = __all_sync(0xffffffffu, ok_lane);
+        if (t == 0) {
+          p.tp_rounds[cta_id] = round + 1u;
+          *s_last = all ? 1 : 0;
+        }
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");
       if (*s_last && n + 3 < p.N) {
