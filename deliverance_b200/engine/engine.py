@@ -284,7 +284,9 @@ class Engine:
 
     def _decode_step(self, reqs: list[Request]) -> list[Request]:
         B = len(reqs)
-        if self.lookahead and B <= _BUCKETS[-1] and self._plain_greedy(reqs):
+        # (a request one token short of its context limit is settled synchronously: the surplus token of a lookahead step would
+        # need a position and a page beyond the limit)
+        if self.lookahead and B <= _BUCKETS[-1] and self._plain_greedy(reqs) and all(r.total_len + r.pending + 1 < r.limit for r in reqs):
             return self._lookahead_decode(reqs)
         finished = self._drain()
         reqs = [r for r in reqs if r.state != FINISHED]
