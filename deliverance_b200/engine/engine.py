@@ -77,6 +77,7 @@ class EngineConfig:
     num_pages: Optional[int] = None  # default: sized from free device memory
     kv_memory_fraction: float = 0.85
     cuda_graphs: bool = True
+    device_timeout_s: float = 120.0  # watchdog of the lookahead path: a step that does not finish in this time raises
     lookahead: bool = True  # overlap the host bookkeeping of step N with the device work of step N + 1 (greedy graph decode)
     kv: KvCacheSettings = field(default_factory=KvCacheSettings)
     max_state_slots: int = 0
@@ -354,7 +355,7 @@ class Engine:
     def _settle(self, step: dict) -> list[Request]:
         """Read the sampled tokens of a launched step and run the per-request bookkeeping."""
         if step["event"] is not None:
-            step["event"].synchronize()
+            self._wait_event(step["event"])
         tokens = step["host"][: len(step["reqs"])].tolist()
         live, toks = [], []
         for r, t in zip(step["reqs"], tokens):
@@ -368,6 +369,19 @@ class Engine:
                 if r.state != FINISHED and any(r is x for x in self._inflight["reqs"]):
                     r.pending = 1
         return finished
+
+    def _wait_event(self, ev) -> None:
+        """Host-side watchdog: wait for a recorded event, but give up after ``device_timeout_s`` so that a device that stopped
+        answering fails the requests in flight (the runner isolates the fault) instead of blocking the serving thread forever."""
+        if ev.query():
+            return
+        t0 = time.perf_counter()
+        pause = 20e-6
+        while not ev.query():
+            if time.perf_counter() - t0 > self.config.device_timeout_s:
+                raise RuntimeError(f"device did not finish a decode step within {self.config.device_timeout_s:.0f} s")
+            time.sleep(pause)
+            pause = min(pause * 1.5, 1e-3)
 
     def _drain(self) -> list[Request]:
         step, self._inflight = self._inflight, None

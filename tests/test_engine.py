@@ -291,3 +291,22 @@ def test_disk_store_formats_roundtrip(tmp_path, compression):
     tol = 0.0 if compression == "NONE" else 0.2
     assert n == 40 and ((after[0] - before[0]).norm() / before[0].norm()).item() <= tol + 1e-7
     assert store.load(kv, b"\\x02" * 20) is None and store.metrics["disk_misses"] == 1
+
+
+def test_device_watchdog_raises_on_stuck_event():
+    """The lookahead path polls its completion event with a deadline; an event that never completes raises instead of blocking."""
+    from deliverance_b200.engine.engine import Engine, EngineConfig
+
+    class Stuck:
+        def query(self):
+            return False
+
+    class Done:
+        def query(self):
+            return True
+
+    eng = Engine.__new__(Engine)
+    eng.config = EngineConfig(device_timeout_s=0.05)
+    Engine._wait_event(eng, Done())
+    with pytest.raises(RuntimeError, match="did not finish"):
+        Engine._wait_event(eng, Stuck())
