@@ -381,7 +381,7 @@ class Engine:
             if time.perf_counter() - t0 > self.config.device_timeout_s:
                 raise RuntimeError(f"device did not finish a decode step within {self.config.device_timeout_s:.0f} s")
             time.sleep(pause)
-            pause = min(pause * 1.5, 1e-3)
+            pause = min(pause * 1.5, 2e-4)
 
     def _drain(self) -> list[Request]:
         step, self._inflight = self._inflight, None
