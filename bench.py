@@ -87,6 +87,30 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
+def _shutdown(dist, eng) -> None:
+    """Leave cleanly, and leave in any case: settle the step in flight, drop the captured graphs (they hold NCCL work when the
+    all-reduce runs through NCCL), then tear the process group down under a timer. A communicator teardown that blocks (seen
+    once with NCCL collectives captured in CUDA graphs) must not keep eight GPUs busy after the result line is printed."""
+    import threading
+
+    import torch
+
+    threading.Timer(45.0, lambda: os._exit(0)).start() if dist is not None else None
+    try:
+        if eng is not None:
+            eng._drain()
+            torch.cuda.synchronize()
+            eng._graphs.clear()
+        if dist is not None:
+            torch.cuda.synchronize()
+            dist.barrier()
+            dist.destroy_process_group()
+    finally:
+        if dist is not None:
+            sys.stdout.flush()
+            os._exit(0)  # also ends the timer thread
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -171,9 +195,7 @@ def main() -> int:
                               "config": {"model": f"{args.shape}-shape bf16", "global_batch": args.batch, "seq_len": args.prompt_len,
                                          "parallelism": f"tp{args.gpus}", "kernels": "cuBLAS + torch SDPA + NCCL, decode step in a CUDA graph"},
                               "clocks": clocks, "extras": {"prefill_tok_s": r["prefill_tok_s"], "prefill_ms": r["prefill_ms"]}}))
-        if dist is not None:
-            dist.barrier()
-            dist.destroy_process_group()
+        _shutdown(dist, None)
         return 0
 
     ops.require_ext()
@@ -308,10 +330,8 @@ def main() -> int:
             "gpu_launches": int(launches_per_step * args.steps),
             "extras": extras,
         }
-        print(json.dumps(out))
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+        print(json.dumps(out), flush=True)
+    _shutdown(dist, eng)
     return 0
 
 
