@@ -31,7 +31,8 @@ from .models.transformer import DecoderModel
 from .parallel.context import SINGLE, TensorParallelContext
 from .params import FinishReason, GeneratorParameters, Response
 from .prompt.chat import PromptBuilder, PromptContext
-from .prompt.parsers import ReasoningTextSplitter, StopStringDetector, ToolCallParser, parser_for_model, split_reasoning
+from .prompt.parsers import (ReasoningTextSplitter, StopStringDetector, ToolCallParser, parser_for_model, prompt_ends_inside_reasoning,
+                             split_reasoning)
 from .tokenizer.auto import AutoTokenizer, IncrementalDetokenizer
 
 
@@ -137,6 +138,7 @@ class CausalLanguageModel:
             prompt = prompt.prompt
         ids = self.encode_prompt(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
         gen = Generation(self, params, on_event, session or str(uuid.uuid4()), has_tools)
+        gen.starts_in_reasoning = isinstance(prompt, str) and prompt_ends_inside_reasoning(prompt)
         guide = self.guides.create(params)
         stopper = StopStringDetector(gen.detok_special, params.stop_words, params.include_stop_str_in_output,
                                      self.tool_parser if has_tools else None)
@@ -169,6 +171,7 @@ class Generation:
         self.on_event = on_event
         self.session = session
         self.has_tools = has_tools
+        self.starts_in_reasoning = False  # the prompt ended inside <think> (set by submit)
         self.detok_plain = IncrementalDetokenizer(clm.tokenizer, skip_special=True)
         self.detok_special = IncrementalDetokenizer(clm.tokenizer, skip_special=False)
         self.request: Optional[Request] = None
@@ -195,7 +198,7 @@ class Generation:
                     text = text[: i + (len(s) if self.params.include_stop_str_in_output else 0)]
                     break
         r.text_with_special_tokens = text_sp
-        content, reasoning = split_reasoning(text)
+        content, reasoning = split_reasoning(text, self.starts_in_reasoning)
         r.reasoning = reasoning
         r.text = content
         if self.has_tools:

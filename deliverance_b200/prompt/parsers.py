@@ -279,8 +279,16 @@ class ReasoningTextSplitter:
         return seg, ""
 
 
-def split_reasoning(text: str) -> tuple[str, Optional[str]]:
-    s = ReasoningTextSplitter()
+def prompt_ends_inside_reasoning(prompt: str) -> bool:
+    """True when the rendered prompt already opened ``<think>`` and did not close it (thinking templates end the generation
+    prompt with ``<think>\n``): the generated text then starts in the reasoning channel
+    (reference: core/.../model/ReasoningTextSplitter.java ``promptEndsInsideReasoning``)."""
+    a = prompt.rfind(ReasoningTextSplitter.OPEN)
+    return a >= 0 and prompt.find(ReasoningTextSplitter.CLOSE, a) < 0
+
+
+def split_reasoning(text: str, start_in_reasoning: bool = False) -> tuple[str, Optional[str]]:
+    s = ReasoningTextSplitter(start_in_reasoning)
     s.accept(text)
     s.flush()
     return s.content.lstrip("\n") if s.reasoning else s.content, (s.reasoning.strip() or None)

@@ -25,7 +25,7 @@ from typing import Any, Callable, Optional
 from fastapi import Request  # module level: handler annotations are resolved from the module namespace
 
 from ..params import FinishReason, GeneratorParameters, Response
-from ..prompt.parsers import ReasoningTextSplitter
+from ..prompt.parsers import ReasoningTextSplitter, prompt_ends_inside_reasoning
 from .runner import EngineRunner
 
 
@@ -225,7 +225,8 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
             loop.call_soon_threadsafe(q.put_nowait, ("done", sub))
 
         sub = runner.submit(prompt, params, on_event, on_done, session)
-        splitter = ReasoningTextSplitter()
+        text = getattr(prompt, "prompt", prompt)
+        splitter = ReasoningTextSplitter(isinstance(text, str) and prompt_ends_inside_reasoning(text))
 
         async def gen():
             try:

@@ -147,3 +147,22 @@ def test_gemma4_tool_call_parser_vectors():
     assert [x.name for x in c] == ["flight_searcher.get_weather", "b"] and c[1].id == "102"
     assert p.should_end_turn("abc<tool_call|>") and not p.should_end_turn("abc")
     assert isinstance(parser_for_model("google/gemma-4-12b-it"), Gemma4ToolCallParser)
+
+
+def test_reasoning_splitter_reference_vectors():
+    """core/.../model/ReasoningTextSplitterTest.java: split tags across pieces, prompts that end inside <think>."""
+    from deliverance_b200.prompt.parsers import ReasoningTextSplitter, prompt_ends_inside_reasoning, split_reasoning
+
+    s = ReasoningTextSplitter()
+    assert s.accept("<think>") == ("", "")
+    assert s.accept("reason</") == ("", "reason")
+    assert s.accept("think") == ("", "")
+    assert s.accept(">answer") == ("answer", "")
+    s = ReasoningTextSplitter(True)
+    assert s.accept("I'll inspect files.") == ("", "I'll inspect files.")
+    assert s.accept("</") == ("", "")
+    assert s.accept("think>ArchiveController.java") == ("ArchiveController.java", "")
+    assert prompt_ends_inside_reasoning("<|start_of_role|>assistant<|end_of_role|><think>\n")
+    assert not prompt_ends_inside_reasoning("<|start_of_role|>assistant<|end_of_role|>")
+    assert not prompt_ends_inside_reasoning("<think>x</think>\nassistant:")
+    assert split_reasoning("plan the answer</think>\nfinal", True) == ("final", "plan the answer")
