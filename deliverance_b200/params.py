@@ -57,6 +57,13 @@ class GeneratorParameters:
             raise ValueError("top_k cannot be combined with xtc")
         if self.uniform_top_p is not None and self.top_p is None:
             raise ValueError("uniform_top_p requires top_p")
+        # value ranges of AbstractGeneratorSampler.sampleTopKTopP (core/.../model/AbstractGeneratorSampler.java:267-279)
+        if self.top_p is not None and not 0.0 < self.top_p <= 1.0:
+            raise ValueError("top_p must be in (0, 1]")
+        if self.uniform_top_p is not None and not 0.0 < self.uniform_top_p <= 1.0:
+            raise ValueError("uniform_top_p must be in (0, 1]")
+        if self.top_k is not None and self.top_k <= 0:
+            raise ValueError("top_k must be > 0")
 
 
 @dataclass

@@ -310,3 +310,23 @@ def test_device_watchdog_raises_on_stuck_event():
     Engine._wait_event(eng, Done())
     with pytest.raises(RuntimeError, match="did not finish"):
         Engine._wait_event(eng, Stuck())
+
+
+def test_sampler_reference_vectors():
+    """core/src/test/.../TopKSamplerTest.java: candidate counts, combined top-k + top-p, uniform pick inside the nucleus, ranges."""
+    from deliverance_b200.engine.sampler import candidate_limit, sample_top_k_top_p_batch
+    from deliverance_b200.params import GeneratorParameters
+
+    assert candidate_limit(64.0, 262_144) == 64 and candidate_limit(0.10, 100) == 90
+    logits = torch.tensor([[5.0, 4.0, 3.0, 2.0, 1.0]])
+
+    def pick(u, uniform):
+        return int(sample_top_k_top_p_batch(logits, torch.tensor([1.0]), torch.tensor([2]), torch.tensor([0.95]), torch.tensor([uniform]),
+                                            torch.tensor([u]))[0])
+
+    assert pick(0.99, False) == 1 and pick(0.60, False) == 0 and pick(0.60, True) == 1
+    for bad in (dict(uniform_top_p=0.0, top_p=0.9), dict(uniform_top_p=1.01, top_p=0.9), dict(uniform_top_p=1.0), dict(top_p=0.0), dict(top_k=0)):
+        with pytest.raises(ValueError):
+            GeneratorParameters(temperature=1.0, **bad).validate()
+    with pytest.raises(ValueError):
+        GeneratorParameters(temperature=0.0, top_p=0.9, uniform_top_p=1.0).validate()
