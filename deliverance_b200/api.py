@@ -56,12 +56,47 @@ class AutoModelConfig:
     kv_pages: Optional[int] = None
     profile_stages: bool = False
 
+    kv_checkpoints: int = 4
+    kv_compression: str = "NONE"
+    kv_turboquant_bits: int = 4
+    ignored: tuple = ()  # reference keys that have no meaning on this runtime (kept for diagnostics)
+
+    # reference key -> field (core/.../model/AutoModelConfig.java:24-37,66-75); benchmark configs under benchmarks/configs/*.json load unchanged
+    _REF_KEYS = {"outputHeadQuantization": "output_head_quantization", "maxBatchSize": "max_batch_size"}
+    _REF_KV_KEYS = {"maxEntries": "kv_max_entries", "blockSize": "kv_block_size", "maxPrefixTokensPerPrompt": "kv_max_prefix_tokens",
+                    "prefixCheckpointPolicy": "kv_policy", "prefixCompression": "kv_compression", "prefixTurboQuantBits": "kv_turboquant_bits",
+                    "maxPrefixCheckpointsPerPrompt": "kv_checkpoints", "contextRowsPerPageTarget": "kv_block_size"}
+    # CPU-runtime knobs of the reference: working dtypes (activations are bf16 here), WebGPU offload switches, the tensor runtime
+    _REF_IGNORED = ("workingMemoryType", "workingQuantType", "gpuPrefill", "gpuDecode", "gpuDecodeAttention", "packedPrefill", "download",
+                    "tensorRuntimeMode", "tensorPlanTrace")
+
     @staticmethod
     def from_json(path_or_text: str) -> "AutoModelConfig":
+        """Accepts this package's snake_case keys and the reference's JSON layout (camelCase, nested ``kvBufferCache`` and
+        ``quantizeOnDemand`` objects)."""
         text = open(path_or_text).read() if os.path.exists(path_or_text) else path_or_text
         d = json.loads(text)
-        known = {f for f in AutoModelConfig.__dataclass_fields__}
-        return AutoModelConfig(**{k: v for k, v in d.items() if k in known})
+        known = {f for f in AutoModelConfig.__dataclass_fields__} - {"ignored"}
+        out = {k: v for k, v in d.items() if k in known}
+        ignored = [k for k in d if k in AutoModelConfig._REF_IGNORED]
+        for k, f in AutoModelConfig._REF_KEYS.items():
+            if k in d:
+                out[f] = d[k]
+        kvb = d.get("kvBufferCache") or {}
+        for k, f in AutoModelConfig._REF_KV_KEYS.items():
+            if k in kvb and kvb[k] is not None:
+                out[f] = kvb[k]
+        if "prefixCheckpointAnchors" in kvb:
+            ignored.append("kvBufferCache.prefixCheckpointAnchors")
+        if d.get("quantizeOnDemand"):
+            out["quantize_on_demand"] = True
+        unknown = [k for k in d if k not in known and k not in AutoModelConfig._REF_KEYS and k not in AutoModelConfig._REF_IGNORED
+                   and k not in ("kvBufferCache", "quantizeOnDemand")]
+        if unknown:
+            raise ValueError(f"unknown configuration keys: {', '.join(sorted(unknown))}")
+        cfg = AutoModelConfig(**out)
+        cfg.ignored = tuple(ignored)
+        return cfg
 
 
 def _device(name: str) -> torch.device:
@@ -267,7 +302,8 @@ class AutoModelForCausalLM:
             self.conf.model = conf.model or model
             self.model_dir = self.conf.model
             self.kv = KvCacheSettings(block_size=conf.kv_block_size, max_prefix_tokens=conf.kv_max_prefix_tokens,
-                                      max_entries=conf.kv_max_entries, policy=conf.kv_policy)
+                                      max_entries=conf.kv_max_entries, policy=conf.kv_policy, checkpoints=conf.kv_checkpoints,
+                                      compression=conf.kv_compression, enabled=conf.kv_max_entries > 0 and conf.kv_max_prefix_tokens > 0)
             return self
 
         def with_name(self, name: str):

@@ -247,3 +247,22 @@ def test_nanocode_agent_loop_with_scripted_model(tmp_path):
     assert tool_msgs[2] == "edited a.txt" and tool_msgs[3] == "denied by the user" and "outside the workspace" in tool_msgs[4]
     assert (tmp_path / "a.txt").read_text().startswith("goodbye world") and (tmp_path / "sub" / "b.txt").read_text() == "x"
     assert asked == ["edit", "run", "write"] and seen[-1][-1] == "tool"
+
+
+def test_auto_model_config_accepts_reference_json(tmp_path):
+    """The reference's benchmark configs (benchmarks/configs/*.json) load unchanged; CPU-runtime knobs are recorded as ignored."""
+    from deliverance_b200.api import AutoModelConfig, AutoModelForCausalLM
+
+    c = AutoModelConfig.from_json(json.dumps({
+        "outputHeadQuantization": "Q4", "maxBatchSize": 512, "workingMemoryType": "F32", "workingQuantType": "I8", "gpuPrefill": True,
+        "kvBufferCache": {"maxEntries": 10000, "blockSize": 32, "maxPrefixTokensPerPrompt": 8192, "prefixCheckpointPolicy": "START_AND_END",
+                          "prefixCompression": "MSE_TURBOQUANT", "prefixTurboQuantBits": 4, "maxPrefixCheckpointsPerPrompt": 4,
+                          "contextRowsPerPageTarget": 32}}))
+    assert c.output_head_quantization == "Q4" and c.max_batch_size == 512 and c.kv_max_prefix_tokens == 8192 and c.kv_policy == "START_AND_END"
+    assert c.kv_compression == "MSE_TURBOQUANT" and c.kv_turboquant_bits == 4 and set(c.ignored) == {"workingMemoryType", "workingQuantType", "gpuPrefill"}
+    off = AutoModelConfig.from_json('{"gpuPrefill": true, "kvBufferCache": {"maxEntries": 0, "maxPrefixTokensPerPrompt": 0}}')
+    b = AutoModelForCausalLM.new_builder("x").with_config(off)
+    assert not b.kv.enabled
+    assert AutoModelConfig.from_json('{"max_seqs": 4, "kv_policy": "ANCHORS"}').kv_policy == "ANCHORS"
+    with pytest.raises(ValueError):
+        AutoModelConfig.from_json('{"noSuchKnob": 1}')
