@@ -85,12 +85,40 @@ def map_chat_request(body: dict, runner: EngineRunner):
             b.add_user(content)
         elif role == "assistant":
             b.add_assistant(content, m.get("tool_calls"))
-        elif role == "tool":
+        elif role == "developer":  # newer name of the system role
+            b.add_system(content)
+        elif role in ("tool", "function"):  # "function": result message of the legacy functions API
             b.add_tool_result(m.get("tool_call_id"), content, m.get("name"))
         else:
             raise ValueError(f"unsupported message role '{role}'")
-    b.add_tools(body.get("tools"))
+    b.add_tools(select_tools(body))
     return b.build(), map_params(body)
+
+
+def select_tools(body: dict):
+    """The tool list the template sees: ``tools`` (or the legacy ``functions`` list wrapped into tool entries), filtered by
+    ``tool_choice`` / legacy ``function_call``: "none" hides the tools, a named function keeps only that one, "auto" / "required"
+    keep all. The reference's request schema carries these fields (web/deliverance_specification.yaml,
+    CreateChatCompletionRequest) without acting on them; they are honoured here so OpenAI clients behave as they expect."""
+    tools = body.get("tools")
+    if not tools and body.get("functions"):
+        tools = [{"type": "function", "function": f} for f in body["functions"] if isinstance(f, dict)]
+    if not tools:
+        return None
+    choice = body.get("tool_choice")
+    if choice is None:
+        choice = body.get("function_call")
+    if choice == "none":
+        return None
+    name = None
+    if isinstance(choice, dict):
+        name = (choice.get("function") or {}).get("name") or choice.get("name")
+    if name:
+        picked = [t for t in tools if (t.get("function") or t).get("name") == name]
+        if not picked:
+            raise ValueError(f"tool_choice names unknown function '{name}'")
+        return picked
+    return tools
 
 
 def map_params(body: dict) -> GeneratorParameters:
@@ -116,6 +144,11 @@ def map_params(body: dict) -> GeneratorParameters:
     p.top_logprobs = int(body.get("top_logprobs") or 0)
     p.guided_regex = body.get("guided_regex")
     p.guided_json = body.get("guided_json")
+    rf = body.get("response_format")
+    if isinstance(rf, dict) and p.guided_json is None and p.guided_regex is None:
+        if rf.get("type") == "json_schema":
+            js = rf.get("json_schema") or {}
+            p.guided_json = js.get("schema", js)
     p.guided_choice = body.get("guided_choice")
     p.cache_salt = str(body.get("cache_salt") or "")
     p.validate()
@@ -278,6 +311,7 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         session = request.headers.get("x-deliverance-session") or str(uuid.uuid4())
         cid, created, model = "chatcmpl-" + uuid.uuid4().hex, int(time.time()), body.get("model") or runner.clm.name
         if body.get("stream"):
+            include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
             first = {"sent": False}
 
             def make_chunk(delta: dict, finish: Optional[str]):
@@ -297,6 +331,8 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
                 last = make_chunk({}, _finish(r))
                 last["usage"] = _usage(r)
                 out.append(last)
+                if include_usage:  # OpenAI stream_options.include_usage: one more chunk with no choices, usage only
+                    out.append({"id": cid, "object": "chat.completion.chunk", "created": created, "model": model, "choices": [], "usage": _usage(r)})
                 return out
 
             return await _stream(request, runner, prompt, params, session, make_chunk, final_chunks, prompt.has_tools)
@@ -331,13 +367,17 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         session = request.headers.get("x-deliverance-session") or str(uuid.uuid4())
         cid, created, model = "cmpl-" + str(uuid.uuid4()), int(time.time()), body.get("model") or runner.clm.name
         if body.get("stream"):
+            include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
             def make_chunk(delta: dict, finish):
                 return {"id": cid, "object": "text_completion", "created": created, "model": model,
                         "choices": [{"index": 0, "text": delta.get("content") or delta.get(settings.reasoning_key) or "", "finish_reason": finish}]}
 
             def final_chunks(r: Response):
-                return [{"id": cid, "object": "text_completion", "created": created, "model": model,
-                         "choices": [{"index": 0, "text": "", "finish_reason": _finish(r)}], "usage": _usage(r)}]
+                out = [{"id": cid, "object": "text_completion", "created": created, "model": model,
+                        "choices": [{"index": 0, "text": "", "finish_reason": _finish(r)}], "usage": _usage(r)}]
+                if include_usage:
+                    out.append({"id": cid, "object": "text_completion", "created": created, "model": model, "choices": [], "usage": _usage(r)})
+                return out
 
             return await _stream(request, runner, prompt, params, session, make_chunk, final_chunks, False)
         try:

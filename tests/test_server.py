@@ -114,3 +114,38 @@ def test_pre_generate_hook_and_reasoning_field(registry):
     r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "user": "bad"})
     assert r.status_code == 400 and r.json()["error"]["message"] == "blocked"
     assert ServerSettings(reasoning_field="vllm").reasoning_key == "reasoning" and ServerSettings().reasoning_key == "reasoning_content"
+
+
+def test_openai_compat_fields(registry):
+    """Request fields of the reference's schema that OpenAI clients send: stream_options, tool_choice, legacy functions /
+    function_call, the "function" and "developer" roles, response_format json_schema."""
+    from deliverance_b200.server.app import select_tools
+
+    tools = [{"type": "function", "function": {"name": "a", "parameters": {}}}, {"type": "function", "function": {"name": "b", "parameters": {}}}]
+    assert select_tools({"tools": tools}) == tools and select_tools({"tools": tools, "tool_choice": "auto"}) == tools
+    assert select_tools({"tools": tools, "tool_choice": "none"}) is None and select_tools({}) is None
+    assert select_tools({"tools": tools, "tool_choice": {"type": "function", "function": {"name": "b"}}}) == tools[1:]
+    legacy = select_tools({"functions": [{"name": "f", "parameters": {}}], "function_call": {"name": "f"}})
+    assert legacy == [{"type": "function", "function": {"name": "f", "parameters": {}}}]
+    with pytest.raises(ValueError):
+        select_tools({"tools": tools, "tool_choice": {"type": "function", "function": {"name": "zz"}}})
+
+    c = TestClient(create_app(registry))
+    r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "hello"}], "max_tokens": 4, "stream": True,
+                                          "stream_options": {"include_usage": True}})
+    chunks = [json.loads(e) for e in _sse(r)[:-1]]
+    assert chunks[-1]["choices"] == [] and chunks[-1]["usage"]["completion_tokens"] == 4
+    assert chunks[-2]["choices"][0]["finish_reason"] == "length"
+    r = c.post("/v1/completions", json={"prompt": "abc", "max_tokens": 3, "stream": True, "stream_options": {"include_usage": True}})
+    chunks = [json.loads(e) for e in _sse(r)[:-1]]
+    assert chunks[-1]["choices"] == [] and chunks[-1]["usage"]["completion_tokens"] == 3
+    r = c.post("/chat/completions", json={"messages": [{"role": "developer", "content": "be brief"}, {"role": "user", "content": "q"},
+                                                       {"role": "assistant", "content": "calling"}, {"role": "function", "name": "f", "content": "42"}],
+                                          "max_tokens": 3, "tool_choice": "none", "tools": tools})
+    assert r.status_code == 200, r.text
+    r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "max_tokens": 30,
+                                          "response_format": {"type": "json_schema", "json_schema": {"name": "x", "schema": {
+                                              "type": "object", "properties": {"ok": {"type": "boolean"}}}}}})
+    assert json.loads(r.json()["choices"][0]["message"]["content"]) in ({"ok": True}, {"ok": False})
+    r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "tools": tools, "tool_choice": {"function": {"name": "zz"}}})
+    assert r.status_code == 400
