@@ -31,8 +31,8 @@ from .models.transformer import DecoderModel
 from .parallel.context import SINGLE, TensorParallelContext
 from .params import FinishReason, GeneratorParameters, Response
 from .prompt.chat import PromptBuilder, PromptContext
-from .prompt.parsers import (ReasoningTextSplitter, StopStringDetector, ToolCallParser, parser_for_model, prompt_ends_inside_reasoning,
-                             split_reasoning)
+from .prompt.parsers import (Gemma4ToolCallParser, ReasoningTextSplitter, StopStringDetector, ToolCallParser, parse_gemma4_response,
+                             parser_for_model, prompt_ends_inside_reasoning, split_reasoning)
 from .tokenizer.auto import AutoTokenizer, IncrementalDetokenizer
 
 
@@ -233,7 +233,10 @@ class Generation:
                     text = text[: i + (len(s) if self.params.include_stop_str_in_output else 0)]
                     break
         r.text_with_special_tokens = text_sp
-        content, reasoning = split_reasoning(text, self.starts_in_reasoning)
+        if isinstance(self.clm.tool_parser, Gemma4ToolCallParser):  # gemma-4 marks its thought channel with special tokens
+            content, reasoning = parse_gemma4_response(text_sp, text)
+        else:
+            content, reasoning = split_reasoning(text, self.starts_in_reasoning)
         r.reasoning = reasoning
         r.text = content
         if self.has_tools:

@@ -18,7 +18,7 @@ from .tiny import build_tensors  # noqa: F401  (small models reuse the tiny buil
 
 
 def _shapes(cfg: dict) -> dict[str, tuple]:
-    """name -> shape for decoder families (llama, mistral, qwen2, qwen3, gemma2, mixtral, qwen3_moe)."""
+    """name -> shape for decoder families (llama, mistral, qwen2, qwen3, gemma2, gemma3, mixtral, qwen3_moe)."""
     mt = cfg["model_type"]
     h, L, V = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["vocab_size"]
     nh, nkv = cfg["num_attention_heads"], cfg.get("num_key_value_heads") or cfg["num_attention_heads"]
@@ -37,10 +37,10 @@ def _shapes(cfg: dict) -> dict[str, tuple]:
         s[p + "self_attn.o_proj.weight"] = (h, nh * hd)
         if mt == "qwen2":
             s[p + "self_attn.q_proj.bias"], s[p + "self_attn.k_proj.bias"], s[p + "self_attn.v_proj.bias"] = (nh * hd,), (nkv * hd,), (nkv * hd,)
-        if mt in ("qwen3", "qwen3_moe"):
+        if mt in ("qwen3", "qwen3_moe", "gemma3_text"):
             s[p + "self_attn.q_norm.weight"] = (hd,)
             s[p + "self_attn.k_norm.weight"] = (hd,)
-        if mt == "gemma2":
+        if mt in ("gemma2", "gemma3_text"):
             s[p + "pre_feedforward_layernorm.weight"] = (h,)
             s[p + "post_feedforward_layernorm.weight"] = (h,)
         if mt == "mixtral":
@@ -90,7 +90,7 @@ class SyntheticLoader:
         shape = self.shapes[name]
         g = torch.Generator(device=self.device).manual_seed((self.seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFF)
         if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
-            base = 0.0 if self.cfg["model_type"] == "gemma2" else 1.0
+            base = 0.0 if self.cfg["model_type"] in ("gemma2", "gemma3_text") else 1.0
             return (base + torch.randn(shape, generator=g, device=self.device) * 0.02).to(self.dtype)
         if name.endswith(".gate.weight"):  # routers: wider spread so that top-k choices are well separated
             return (torch.randn(shape, generator=g, device=self.device) * 0.5).to(self.dtype)
@@ -134,5 +134,10 @@ GEMMA2_9B = dict(model_type="gemma2", vocab_size=256000, hidden_size=3584, inter
                  rope_theta=10000.0, attn_logit_softcapping=50.0, final_logit_softcapping=30.0, sliding_window=4096,
                  query_pre_attn_scalar=256, hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True, bos_token_id=2,
                  eos_token_id=1)
+GEMMA3_4B = dict(model_type="gemma3_text", vocab_size=262208, hidden_size=2560, intermediate_size=10240, num_hidden_layers=34,
+                 num_attention_heads=8, num_key_value_heads=4, head_dim=256, max_position_embeddings=131072, rms_norm_eps=1e-6,
+                 rope_theta=1e6, rope_local_base_freq=10000.0, rope_scaling={"factor": 8.0, "rope_type": "linear"}, sliding_window=1024,
+                 sliding_window_pattern=6, query_pre_attn_scalar=256, hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True,
+                 bos_token_id=2, eos_token_id=1)
 SHAPES = {"qwen3-4b": QWEN3_4B, "tinyllama": TINYLLAMA, "mixtral-8x7b": MIXTRAL_8X7B, "qwen3-30b-a3b": QWEN3_30B_A3B,
-          "gemma2-9b": GEMMA2_9B}
+          "gemma2-9b": GEMMA2_9B, "gemma3-4b": GEMMA3_4B}

@@ -35,6 +35,12 @@ def tiny_config(model_type: str, **over) -> dict:
     if model_type == "gemma2":
         base.update(head_dim=64, attn_logit_softcapping=50.0, final_logit_softcapping=30.0, hidden_activation="gelu_pytorch_tanh",
                     sliding_window=64, query_pre_attn_scalar=64, tie_word_embeddings=True)
+    if model_type == "gemma3_text":
+        base.update(head_dim=64, hidden_activation="gelu_pytorch_tanh", sliding_window=8, query_pre_attn_scalar=64, tie_word_embeddings=True,
+                    num_hidden_layers=3, layer_types=["sliding_attention", "sliding_attention", "full_attention"], rms_norm_eps=1e-6,
+                    rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                                     "full_attention": {"rope_type": "default", "rope_theta": 1000000.0}})
+        base.pop("rope_theta")
     if model_type == "gpt2":
         base = dict(model_type="gpt2", vocab_size=256, n_embd=64, n_head=4, n_layer=2, n_ctx=256, n_positions=256,
                     layer_norm_epsilon=1e-5, bos_token_id=1, eos_token_id=2, activation_function="gelu_new")
@@ -100,7 +106,7 @@ def build_tensors(cfg: dict, seed: int = 0, dtype=torch.float32, std: float = 0.
     t["model.embed_tokens.weight"] = R(V, h)
     for i in range(L):
         p = f"model.layers.{i}."
-        t[p + "input_layernorm.weight"] = ones(h) if mt != "gemma2" else R(h)
+        t[p + "input_layernorm.weight"] = ones(h) if mt not in ("gemma2", "gemma3_text") else R(h)
         is_mamba = mt == "granitemoehybrid" and cfg["layer_types"][i] == "mamba"
         if is_mamba:
             H, G, S, dh, K = cfg["mamba_n_heads"], cfg["mamba_n_groups"], cfg["mamba_d_state"], cfg["mamba_d_head"], cfg["mamba_d_conv"]
@@ -126,8 +132,11 @@ def build_tensors(cfg: dict, seed: int = 0, dtype=torch.float32, std: float = 0.
             if mt in ("qwen3", "qwen3_moe"):
                 t[p + "self_attn.q_norm.weight"] = ones(hd)
                 t[p + "self_attn.k_norm.weight"] = ones(hd)
-        t[p + "post_attention_layernorm.weight"] = ones(h) if mt != "gemma2" else R(h)
-        if mt == "gemma2":
+            if mt == "gemma3_text":  # stored as w - 1
+                t[p + "self_attn.q_norm.weight"] = R(hd)
+                t[p + "self_attn.k_norm.weight"] = R(hd)
+        t[p + "post_attention_layernorm.weight"] = ones(h) if mt not in ("gemma2", "gemma3_text") else R(h)
+        if mt in ("gemma2", "gemma3_text"):
             t[p + "pre_feedforward_layernorm.weight"] = R(h)
             t[p + "post_feedforward_layernorm.weight"] = R(h)
         if mt == "mixtral":
@@ -153,7 +162,7 @@ def build_tensors(cfg: dict, seed: int = 0, dtype=torch.float32, std: float = 0.
                 t[p + "block_sparse_moe.output_linear.weight"] = R(E, h, I)
         else:
             t[p + "mlp.gate_proj.weight"], t[p + "mlp.up_proj.weight"], t[p + "mlp.down_proj.weight"] = R(I, h), R(I, h), R(h, I)
-    t["model.norm.weight"] = ones(h) if mt != "gemma2" else R(h)
+    t["model.norm.weight"] = ones(h) if mt not in ("gemma2", "gemma3_text") else R(h)
     if not cfg.get("tie_word_embeddings", False):
         t["lm_head.weight"] = R(V, h)
     return t

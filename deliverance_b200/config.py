@@ -18,8 +18,13 @@ from dataclasses import dataclass, field
 from typing import Any, Optional
 
 SUPPORTED_MODEL_TYPES = (
-    "llama", "mistral", "mixtral", "gemma2", "qwen2", "qwen3", "qwen3_moe", "gpt2", "granitemoehybrid", "bert",
+    "llama", "mistral", "mixtral", "gemma2", "gemma3_text", "gemma3", "qwen2", "qwen3", "qwen3_moe", "gpt2", "granitemoehybrid", "bert",
 )
+
+# transformers' Gemma3TextConfig defaults: hub configs of the multimodal checkpoints leave most text fields out
+_GEMMA3_TEXT_DEFAULTS = dict(vocab_size=262208, hidden_size=2304, intermediate_size=9216, num_hidden_layers=26, num_attention_heads=8,
+                             num_key_value_heads=4, head_dim=256, max_position_embeddings=131072, rms_norm_eps=1e-6,
+                             query_pre_attn_scalar=256, sliding_window=4096, bos_token_id=2, eos_token_id=1, pad_token_id=0)
 
 
 @dataclass
@@ -36,6 +41,7 @@ class ModelConfig:
     norm_eps: float = 1e-5
     rope_theta: float = 10000.0
     rope_factor: float = 1.0
+    rope_local_theta: float = 0.0  # gemma3: base of the sliding-window layers' rotary table (0 = same table for every layer)
     hidden_act: str = "silu"
     tie_word_embeddings: bool = False
     bos_token_id: Optional[int] = None
@@ -141,6 +147,14 @@ def parse_config(d: dict) -> ModelConfig:
     mt = d.get("model_type")
     if mt not in SUPPORTED_MODEL_TYPES:
         raise ValueError(f"unsupported model_type '{mt}' (supported: {', '.join(SUPPORTED_MODEL_TYPES)})")
+    if mt in ("gemma3", "gemma3_text"):
+        # the multimodal wrapper nests the language model's fields; only the text tower is served
+        outer, d = d, dict(_GEMMA3_TEXT_DEFAULTS)
+        d.update({k: v for k, v in (outer.get("text_config") or outer).items() if v is not None or k.endswith("softcapping")})
+        for k in ("eos_token_id", "bos_token_id"):
+            if outer.get(k) is not None:
+                d[k] = outer[k]
+        d["model_type"] = mt = "gemma3_text"
     if mt == "gpt2":
         h = d["n_embd"]
         nh = d["n_head"]
@@ -216,6 +230,39 @@ def parse_config(d: dict) -> ModelConfig:
                 cfg.layer_types = tuple("sliding" if "sliding" in t else "attention" for t in lt)
             else:  # HF gemma2: even layers slide, odd layers are global
                 cfg.layer_types = tuple("sliding" if i % 2 == 0 else "attention" for i in range(nl))
+    elif mt == "gemma3_text":
+        # gemma2 block layout (four norms with 1 + w, scaled embeddings, tied head) plus per-head q/k RMSNorm, no attention
+        # softcap, five sliding-window layers per global layer, and a separate rotary base for the sliding layers
+        # (reference: core/.../model/gemma3/Gemma3Model.java:90-140, Gemma3Config.java; semantics of transformers' Gemma3TextModel)
+        import torch
+
+        cfg.hidden_act = d.get("hidden_activation") or d.get("hidden_act") or "gelu_pytorch_tanh"
+        cfg.attn_softcap = float(d.get("attn_logit_softcapping") or 0.0)
+        cfg.final_softcap = float(d.get("final_logit_softcapping") or 0.0)
+        cfg.norm_weight_offset = 1.0
+        cfg.post_norms = True
+        cfg.qk_norm = True
+        cfg.tie_word_embeddings = bool(d.get("tie_word_embeddings", True))
+        cfg.embedding_multiplier = float(torch.tensor(math.sqrt(h), dtype=torch.float32).to(torch.bfloat16).float())
+        cfg.attn_scale = 1.0 / math.sqrt(float(d.get("query_pre_attn_scalar") or cfg.head_dim))
+        cfg.sliding_window = int(d.get("sliding_window") or 0)
+        lt = d.get("layer_types")
+        if lt:
+            cfg.layer_types = tuple("sliding" if "sliding" in t else "attention" for t in lt)
+        else:
+            pat = int(d.get("sliding_window_pattern") or d.get("_sliding_window_pattern") or 6)
+            cfg.layer_types = tuple("attention" if (i + 1) % pat == 0 else "sliding" for i in range(nl))
+        if cfg.sliding_window <= 0:
+            cfg.layer_types = tuple("attention" for _ in range(nl))
+        rp = d.get("rope_parameters") or {}
+        if "full_attention" in rp:  # per-layer-type rotary parameters (newer configs)
+            full, loc = rp["full_attention"], rp.get("sliding_attention") or {}
+            cfg.rope_theta = float(full.get("rope_theta", 1e6))
+            cfg.rope_factor = float(full.get("factor", 1.0)) if full.get("rope_type", "default") == "linear" else 1.0
+            cfg.rope_local_theta = float(loc.get("rope_theta", 10000.0))
+        else:
+            cfg.rope_theta = float(d.get("rope_theta") or 1e6)
+            cfg.rope_local_theta = float(d.get("rope_local_base_freq") or 10000.0)
     elif mt == "granitemoehybrid":
         cfg.embedding_multiplier = float(d.get("embedding_multiplier", 1.0))
         cfg.residual_multiplier = float(d.get("residual_multiplier", 1.0))

@@ -1,4 +1,4 @@
-"""Decoder-only model graph shared by llama, mistral, qwen2, qwen3, gemma2, mixtral, qwen3_moe and granitemoehybrid.
+"""Decoder-only model graph shared by llama, mistral, qwen2, qwen3, gemma2, gemma3, mixtral, qwen3_moe and granitemoehybrid.
 
 One graph, configured by :class:`~deliverance_b200.config.ModelConfig` flags, over the ragged-batch op surface in
 :mod:`deliverance_b200.ops`. Per layer (reference: core/.../generator/TransformerBlock.java:161-200):
@@ -93,6 +93,7 @@ class DecoderModel:
         self.final_norm: Optional[torch.Tensor] = None
         self.lm_head: Optional[LinearWeight] = None
         self.cos = self.sin = None
+        self.cos_local = self.sin_local = None  # rotary tables of sliding-window layers when their base differs (gemma3)
         self.layer_hook: Optional[Callable[[int, str, torch.Tensor], None]] = None  # debug / trace hook
         self.profiler = None
         self.active_lora: Optional[str] = None
@@ -120,6 +121,12 @@ class DecoderModel:
             t = loader.load(name)
             return self._dev(t.reshape(-1) if not isinstance(t, Q4Tensor) else t.dequantize().reshape(-1))
 
+        if not loader.has(prefix + "embed_tokens.weight"):
+            # text tower of a multimodal checkpoint (gemma3): the language model's tensors carry a wrapper prefix
+            for alt in ("language_model.model.", "model.language_model."):
+                if loader.has(alt + "embed_tokens.weight"):
+                    prefix = alt
+                    break
         emb = loader.load(prefix + "embed_tokens.weight")
         emb_dense = emb.dequantize(torch.float32) if isinstance(emb, Q4Tensor) else emb
         self.embed = self._dev(emb_dense)
@@ -182,6 +189,9 @@ class DecoderModel:
         if cfg.use_rope:
             cos, sin = ref.rope_tables(cfg.head_dim, cfg.max_position_embeddings, cfg.rope_theta, cfg.rope_factor)
             self.cos, self.sin = cos.to(self.device), sin.to(self.device)
+            if cfg.rope_local_theta > 0:
+                cos, sin = ref.rope_tables(cfg.head_dim, cfg.max_position_embeddings, cfg.rope_local_theta, 1.0)
+                self.cos_local, self.sin_local = cos.to(self.device), sin.to(self.device)
         return self
 
     def _load_ff(self, loader, lw, i, p, get, row, col):
@@ -309,8 +319,10 @@ class DecoderModel:
             if lw.lora:
                 qkv = self._lora(lw, "qkv", x, qkv)
         k_cache, v_cache = kv.layer(i)
+        local_rope = lw.kind == "sliding" and self.cos_local is not None
+        cos, sin = (self.cos_local, self.sin_local) if local_rope else (self.cos, self.sin)
         with self._stage("causalselfattention.rope"):
-            q = ops.rope_kv(qkv, batch.positions, batch.slots, lw.q_norm, lw.k_norm, self.cos, self.sin, k_cache, v_cache,
+            q = ops.rope_kv(qkv, batch.positions, batch.slots, lw.q_norm, lw.k_norm, cos, sin, k_cache, v_cache,
                             self.n_heads, self.n_kv, cfg.head_dim, cfg.norm_eps, cfg.norm_weight_offset)
         window = cfg.window(i)
         with self._stage("causalselfattention.score_value"):

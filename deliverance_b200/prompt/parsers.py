@@ -279,6 +279,35 @@ class ReasoningTextSplitter:
         return seg, ""
 
 
+class Gemma4ChannelSplitter(ReasoningTextSplitter):
+    """Streaming splitter for gemma-4 channel markers: ``<|channel>thought\n ... <channel|>`` is the reasoning channel."""
+
+    OPEN, CLOSE = "<|channel>thought\n", "<channel|>"
+
+
+_GEMMA4_MARKERS = ("<|channel>", "<channel|>", "<|turn>", "<turn|>", "<|think|>")
+
+
+def parse_gemma4_response(text_with_special: str, fallback: str = "") -> tuple[str, Optional[str]]:
+    """(content, reasoning) of a complete gemma-4 reply: the first closed thought channel is the reasoning, what is left
+    with the channel / turn markers removed is the content; without a closed thought channel the cleaned fallback text is the
+    content (reference: core/.../model/gemma4/Gemma4ResponseParser.java:10-52 and Gemma4ResponseParserTest.java)."""
+
+    def clean(t: str) -> str:
+        for m in _GEMMA4_MARKERS:
+            t = t.replace(m, "")
+        return t.strip()
+
+    start_tag, end_tag = Gemma4ChannelSplitter.OPEN, Gemma4ChannelSplitter.CLOSE
+    a = text_with_special.find(start_tag) if text_with_special else -1
+    b = text_with_special.find(end_tag, a + len(start_tag)) if a >= 0 else -1
+    if b < 0:
+        return clean(fallback or ""), None
+    reasoning = text_with_special[a + len(start_tag) : b].strip()
+    content = clean(text_with_special[:a] + text_with_special[b + len(end_tag) :]) or clean(fallback or "")
+    return content, (reasoning or None)
+
+
 def prompt_ends_inside_reasoning(prompt: str) -> bool:
     """True when the rendered prompt already opened ``<think>`` and did not close it (thinking templates end the generation
     prompt with ``<think>\n``): the generated text then starts in the reasoning channel

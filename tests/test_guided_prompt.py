@@ -166,3 +166,21 @@ def test_reasoning_splitter_reference_vectors():
     assert not prompt_ends_inside_reasoning("<|start_of_role|>assistant<|end_of_role|>")
     assert not prompt_ends_inside_reasoning("<think>x</think>\nassistant:")
     assert split_reasoning("plan the answer</think>\nfinal", True) == ("final", "plan the answer")
+
+
+def test_gemma4_response_channels_reference_vectors():
+    """Vectors of the reference's Gemma4ResponseParserTest plus the streaming splitter over the same markers."""
+    from deliverance_b200.prompt.parsers import Gemma4ChannelSplitter, parse_gemma4_response
+
+    assert parse_gemma4_response("<|channel>thought\nfirst reason second reason<channel|>Final answer",
+                                 "thought\nfirst reason second reasonFinal answer") == ("Final answer", "first reason second reason")
+    assert parse_gemma4_response("<|channel>thought\n<channel|>Final answer", "thought\nFinal answer") == ("Final answer", None)
+    assert parse_gemma4_response("", "<|turn>plain<turn|>") == ("plain", None)
+    assert parse_gemma4_response("<|channel>thought\nnever closed", "fallback text") == ("fallback text", None)
+    sp = Gemma4ChannelSplitter()
+    c = r = ""
+    for piece in ["<|chan", "nel>thou", "ght\nwhy ", "not<chan", "nel|>Answer"]:
+        dc, dr = sp.accept(piece)
+        c, r = c + dc, r + dr
+    dc, dr = sp.flush()
+    assert (c + dc, r + dr) == ("Answer", "why not")

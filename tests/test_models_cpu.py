@@ -21,7 +21,7 @@ def _ours(d, chunk=16, head_quant=None):
     return m, Engine(m, EngineConfig(num_pages=64, max_batch_tokens=chunk))
 
 
-@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma2", "mixtral", "qwen3_moe", "gpt2", "granitemoehybrid"])
+@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma2", "gemma3_text", "mixtral", "qwen3_moe", "gpt2", "granitemoehybrid"])
 def test_greedy_tokens_match_hf(tmp_path, family):
     d = str(tmp_path / family)
     write_tiny_model(d, family, seed=1, std=0.05)
@@ -33,7 +33,7 @@ def test_greedy_tokens_match_hf(tmp_path, family):
     assert r.token_ids == out[0, len(PROMPT):].tolist()
 
 
-@pytest.mark.parametrize("family", ["llama", "gemma2", "granitemoehybrid"])
+@pytest.mark.parametrize("family", ["llama", "gemma2", "gemma3_text", "granitemoehybrid"])
 def test_prefill_logits_match_hf(tmp_path, family):
     d = str(tmp_path / family)
     write_tiny_model(d, family, seed=2, std=0.05)
@@ -81,3 +81,31 @@ def test_layer_trace_hook(tmp_path):
     m.layer_hook = lambda layer, stage, t: seen.append((layer, stage, tuple(t.shape)))
     eng.generate(PROMPT[:5], GeneratorParameters(max_tokens=1))
     assert (-1, "embed", (5, 64)) in seen and (1, "out", (5, 64)) in seen
+
+
+def test_gemma3_multimodal_wrapper_config_and_prefix(tmp_path):
+    """A gemma3 checkpoint in the multimodal layout (nested text_config with most fields left to defaults, wrapper tensor prefix,
+    old-style rope_local_base_freq / sliding_window_pattern) loads as its text tower."""
+    import json
+
+    from deliverance_b200.ckpt.safetensors_io import write_safetensors
+    from deliverance_b200.ckpt.tiny import build_tensors, tiny_config
+    from deliverance_b200.config import parse_config
+
+    full = parse_config({"model_type": "gemma3", "text_config": {"hidden_size": 2560, "intermediate_size": 10240, "num_hidden_layers": 34,
+                                                                   "rope_scaling": {"factor": 8.0, "rope_type": "linear"}, "sliding_window": 1024},
+                         "eos_token_id": [1, 106]})
+    assert (full.num_heads, full.num_kv_heads, full.head_dim, full.vocab_size) == (8, 4, 256, 262208)
+    assert full.rope_theta == 1e6 and full.rope_local_theta == 10000.0 and full.rope_factor == 8.0 and full.eos_token_ids == (1, 106)
+    assert [full.layer_type(i) for i in range(6)] == ["sliding"] * 5 + ["attention"] and full.window(0) == 1024 and full.window(5) == 0
+    text = tiny_config("gemma3_text")
+    d = tmp_path / "mm"
+    d.mkdir()
+    tensors = {("language_model." + k): v for k, v in build_tensors(text, 1, std=0.05).items()}
+    write_safetensors(str(d / "model.safetensors"), tensors)
+    (d / "config.json").write_text(json.dumps({"model_type": "gemma3", "text_config": {k: v for k, v in text.items() if k != "model_type"}}))
+    plain = tmp_path / "plain"
+    write_tiny_model(str(plain), "gemma3_text", seed=1, std=0.05)
+    a = _ours(str(d))[1].generate(PROMPT, GeneratorParameters(max_tokens=4)).token_ids
+    b = _ours(str(plain))[1].generate(PROMPT, GeneratorParameters(max_tokens=4)).token_ids
+    assert a == b
