@@ -17,6 +17,7 @@ import base64
 import hashlib
 import hmac
 import json
+import os
 import time
 import uuid
 from dataclasses import dataclass, field
@@ -414,6 +415,13 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
 
     async def tp_status():
         st = dict(registry.tp_status())
+        sf = os.environ.get("DLV_CLUSTER_STATUS_FILE")  # written by the rank supervisor (parallel/cluster.py --status-file)
+        if sf and os.path.exists(sf):
+            try:
+                with open(sf) as f:
+                    st["cluster"] = json.load(f)
+            except (OSError, ValueError):
+                pass
         st["runners"] = {n: dict(r.stats, engine=dict(r.clm.engine.metrics), prefix_cache=dict(r.clm.engine.kv.prefix.metrics)) for n, r in registry.generation.items()}
         return JSONResponse(st)
 

@@ -21,6 +21,7 @@ from typing import Optional
 
 from ..api import CausalLanguageModel
 from ..parallel.context import Collectives
+from ..parallel.cluster import beat
 from ..prompt.chat import PromptContext
 from .runner import EngineRunner, Submission
 
@@ -42,6 +43,7 @@ class LockstepRunner(EngineRunner):
         eng = self.clm.engine
         last_sent = 0.0
         while True:
+            beat()  # liveness for the rank supervisor (parallel/cluster.py); no-op when not supervised
             stop = self._stop.is_set()
             fresh: list[Submission] = []
             try:
@@ -129,6 +131,7 @@ def follower_loop(clm: CausalLanguageModel, control: Collectives, max_idle: Opti
     steps = 0
     last = time.monotonic()
     while True:
+        beat()
         cmd = control.broadcast_object(None, 0)
         if cmd is None:
             raise RuntimeError("control group delivered no command (coordinator gone?)")

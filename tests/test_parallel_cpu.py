@@ -280,3 +280,62 @@ def test_lockstep_serving_thread_ranks(tmp_path):
     assert len(rc.token_ids) < 200 and runner.stats["cancelled"] == 1
     assert not err and not ft.is_alive()
     assert got == want and steps[0] >= 6
+
+
+_CLUSTER_CHILD = r"""
+import os, sys, time
+import torch, torch.distributed as dist
+from deliverance_b200.parallel.cluster import beat
+mode, out = sys.argv[1], sys.argv[2]
+rank, gen = int(os.environ["RANK"]), int(os.environ["DLV_RESTART_COUNT"])
+beat(0.0)
+dist.init_process_group("gloo")
+t = torch.tensor([float(rank + 1)])
+dist.all_reduce(t)
+if gen == 0 and rank == 1:
+    if mode == "exit":      # a rank dies between steps, with no collective in flight
+        os._exit(3)
+    if mode == "hang":      # a rank stops publishing liveness (host-side stall), the others keep beating
+        time.sleep(60)
+for _ in range(20 if gen == 0 else 2):
+    beat(0.0)
+    time.sleep(0.05)
+open(os.path.join(out, f"done_gen{gen}_rank{rank}"), "w").write(str(t.item()))
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.parametrize("mode", ["exit", "hang", "ok"])
+def test_local_cluster_restarts_group_on_failure(tmp_path, mode):
+    """Supervisor of one-process-per-GPU groups: a rank that exits, or that goes silent, makes the supervisor stop the other
+    ranks (by pid) and start the whole group again on a fresh rendezvous port; a healthy group just finishes."""
+    import json
+    import sys
+
+    from deliverance_b200.parallel.cluster import LocalCluster
+
+    script = tmp_path / "child.py"
+    script.write_text(_CLUSTER_CHILD)
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.environ.get("PYTHONPATH", "")]))
+    status = tmp_path / "status.json"
+    c = LocalCluster([sys.executable, str(script), mode, str(tmp_path)], nproc=2, max_restarts=2, hang_timeout=1.5 if mode == "hang" else 0.0,
+                     grace=2.0, env=env, status_file=str(status), start_timeout=60.0)
+    assert c.run() == 0
+    st = json.loads(status.read_text())
+    assert st["state"] == "finished"
+    if mode == "ok":
+        assert st["restarts"] == 0 and (tmp_path / "done_gen0_rank1").read_text() == "3.0"
+    else:
+        assert st["restarts"] == 1 and st["generation"] == 2
+        assert ("exited with code 3" if mode == "exit" else "silent for") in st["last_failure"]
+        assert (tmp_path / "done_gen1_rank0").read_text() == "3.0" and (tmp_path / "done_gen1_rank1").read_text() == "3.0"
+        assert not (tmp_path / "done_gen0_rank1").exists()
+
+
+def test_local_cluster_gives_up_after_max_restarts(tmp_path):
+    import sys
+
+    from deliverance_b200.parallel.cluster import LocalCluster
+
+    c = LocalCluster([sys.executable, "-c", "import sys; sys.exit(7)"], nproc=2, max_restarts=1, grace=1.0)
+    assert c.run() == 1 and c.status.state == "failed" and c.status.restarts == 1 and len(c.status.failures) == 2
