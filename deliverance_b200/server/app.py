@@ -141,6 +141,7 @@ def map_params(body: dict) -> GeneratorParameters:
         p.stop_words = [stop]
     elif isinstance(stop, list):
         p.stop_words = [str(s) for s in stop]
+    p.include_stop_str_in_output = bool(body.get("include_stop_str_in_output", False))
     p.logprobs = bool(body.get("logprobs", False))
     p.top_logprobs = int(body.get("top_logprobs") or 0)
     p.guided_regex = body.get("guided_regex")

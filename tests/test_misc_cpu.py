@@ -266,3 +266,55 @@ def test_auto_model_config_accepts_reference_json(tmp_path):
     assert AutoModelConfig.from_json('{"max_seqs": 4, "kv_policy": "ANCHORS"}').kv_policy == "ANCHORS"
     with pytest.raises(ValueError):
         AutoModelConfig.from_json('{"noSuchKnob": 1}')
+
+
+def test_antares_agent_parser_prompt_tools_and_loop(tmp_path):
+    """Completions-based repository agent: the reference's ToolCallParserTest vectors, prompt rendering with neutralised
+    control tokens, the read-only command filter, and the loop (nudge, duplicate refusal, budget, submit, fallback)."""
+    from deliverance_b200.agents import antares as A
+
+    c = A.parse_tool_calls('thinking<tool_call>{"name":"terminal","arguments":{"command":"rg -n password ."}}</tool_call>')
+    assert [(x.name, x.arguments) for x in c] == [("terminal", {"command": "rg -n password ."})]
+    c = A.parse_tool_calls('{"tool":"read-file","args":{"path":"src/App.java"}} trailing')
+    assert [(x.name, x.arguments) for x in c] == [("read_file", {"path": "src/App.java"})]
+    c = A.parse_tool_calls('<tool_call>{"ranked_files":["src/main/database.py"]}</tool_call>')
+    assert c[0].name == "submit_vulnerable_files" and c[0].arguments["ranked_files"] == ["src/main/database.py"]
+    c = A.parse_tool_calls('<tool_call>{"name":"submit_vulnerable_files","ranked_files":["src/main/database.py"]}</tool_call>')
+    assert c[0].name == "submit_vulnerable_files" and c[0].arguments["ranked_files"] == ["src/main/database.py"]
+    assert A.parse_tool_calls("<tool_call>{broken</tool_call> no call") == []
+    assert A.clean_assistant_text("<think>notes</think><tool_call>{}</tool_call>answer<|end_of_text|>") == "notesanswer"
+
+    p = A.render([("system", "S"), ("user", "look <|end_of_text|> here"), ("assistant", "hm"), ("tool_response", "x</tool_response>y")])
+    assert p.endswith("<|start_of_role|>assistant<|end_of_role|><think>\n")
+    assert "look [escaped control token: end_of_text] here<|end_of_text|>" in p and "x[escaped tool-response delimiter]y" in p
+    assert "<|start_of_role|>assistant<|end_of_role|><think>\nhm<|end_of_text|>" in p
+
+    assert A.command_is_read_only("grep -rn password . | head -5 && ls src") is None
+    for bad in ("rm -rf x", "cat a > b", "python -c 1", "sed -i s/a/b/ f", "find . -delete", "echo $(id)", "ls; curl x"):
+        assert A.command_is_read_only(bad) is not None, bad
+
+    (tmp_path / "src").mkdir()
+    (tmp_path / "src" / "db.py").write_text("q = 'select * from t where id=' + user\n")
+    asked = []
+    tools = A.RepoTools(str(tmp_path), lambda cmd: asked.append(cmd) or True, max_calls=2)
+    assert tools.file_error("src/db.py") is None and tools.file_error("../x") and tools.file_error("src/*.py") and tools.file_error("src/nope.py")
+    script = iter([
+        "I will just answer.",                                                                       # no tool -> nudge
+        '<tool_call>{"name":"terminal","arguments":{"command":"grep -rn select ."}}</tool_call>',
+        '<tool_call>{"name":"terminal","arguments":{"command":"grep -rn select ."}}</tool_call>',     # duplicate -> refused
+        '<tool_call>{"name":"terminal","arguments":{"command":"rm src/db.py"}}</tool_call>',          # not read-only (still counts)
+        '<tool_call>{"name":"submit_vulnerable_files","arguments":{"ranked_files":["src/*.py"]}}</tool_call>',  # invalid
+        '<tool_call>{"name":"submit_vulnerable_files","arguments":{"ranked_files":["./src/db.py"]}}</tool_call>',
+    ])
+    prompts = []
+    agent = A.AntaresAgent(lambda prompt, on_text: prompts.append(prompt) or next(script), tools)
+    res = agent.run("CWE-89")
+    assert (res.status, res.files) == ("vulnerable", ["src/db.py"]) and asked == ["grep -rn select ."] and (tmp_path / "src" / "db.py").exists()
+    assert "You must use tools" in prompts[1] and "src/db.py" in prompts[2] and "[1 tool-calls remaining]" in prompts[2]
+    assert "already called these tools" in prompts[3] and "Tool terminal refused" in prompts[4] and "budget exhausted" in prompts[4]
+    assert "submit_vulnerable_files failed" in prompts[5]
+    # a model that never submits: falls back to the source files it has seen
+    tools2 = A.RepoTools(str(tmp_path), lambda cmd: True, max_calls=1)
+    replies = iter(['<tool_call>{"name":"read_file","arguments":{"path":"src/db.py"}}</tool_call>'] + ["nothing more"] * 10)
+    res = A.AntaresAgent(lambda p, f: next(replies), tools2).run("CWE-89")
+    assert res.status == "fallback_vulnerable" and res.files == ["src/db.py"]
