@@ -318,3 +318,49 @@ def test_antares_agent_parser_prompt_tools_and_loop(tmp_path):
     replies = iter(['<tool_call>{"name":"read_file","arguments":{"path":"src/db.py"}}</tool_call>'] + ["nothing more"] * 10)
     res = A.AntaresAgent(lambda p, f: next(replies), tools2).run("CWE-89")
     assert res.status == "fallback_vulnerable" and res.files == ["src/db.py"]
+
+
+def test_smoke_benchmarks_thinking_and_lora(tmp_path):
+    """The thinking smoke benchmark's answer extraction and pass predicates, its JSONL rows on a tiny model, and the LoRA
+    benchmark's base / lora-adapted rows (merge at load and hot swap generate the same adapted tokens)."""
+    import io
+
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.bench import smoke_benchmarks as sb
+    from deliverance_b200.ckpt.lora import lora_names
+    from deliverance_b200.ckpt.safetensors_io import write_safetensors
+    from deliverance_b200.ckpt.tiny import tiny_config, write_tiny_model
+
+    assert sb.final_answer("<think>maybe 10 cents</think>work...\nFinal: `0.05` dollars") == "0.05 dollars"
+    bat = next(c for c in sb.CASES if c.id == "bat-ball")
+    assert bat.check("0.05 dollars") and not bat.check("0.10") and not bat.check("it is 0.05, not 0.10")
+    assert next(c for c in sb.CASES if c.id == "missing-dollar").check("no, nothing is missing")
+    d = str(tmp_path / "base")
+    write_tiny_model(d, "llama", seed=5, std=0.08, max_position_embeddings=1024)
+    clm = AutoModelForCausalLM.from_pretrained(d, device="cpu")
+    buf = io.StringIO()
+    s = sb.run_thinking(clm, buf, max_tokens=4, cases=sb.CASES[:1] + sb.CASES[-1:])
+    rows = [json.loads(l) for l in buf.getvalue().splitlines()]
+    assert s["cases"] == 2 and s["max_token_warnings"] == 2 and [r["case_id"] for r in rows] == ["square-area", "follow-up"]
+    assert rows[1]["generated_tokens"] == 8 and set(rows[0]) == {"timestamp", "case_id", "pass", "finish_reason", "generated_tokens", "time_ms",
+                                                                 "time_to_first_token_ms", "response"}
+    cfg = tiny_config("llama")
+    g = torch.Generator().manual_seed(9)
+    tensors = {}
+    for i in range(cfg["num_hidden_layers"]):
+        a, b = lora_names(f"model.layers.{i}.self_attn.q_proj.weight")
+        tensors[a], tensors[b] = torch.randn(4, 64, generator=g) * 0.3, torch.randn(64, 4, generator=g) * 0.3
+    ad = str(tmp_path / "adapter")
+    os.makedirs(ad)
+    write_safetensors(os.path.join(ad, "adapter_model.safetensors"), tensors)
+    with open(os.path.join(ad, "adapter_config.json"), "w") as f:
+        json.dump({"r": 4, "lora_alpha": 8, "target_modules": ["q_proj"]}, f)
+    out = {}
+    for mode in ("merge", "hotswap"):
+        buf = io.StringIO()
+        out[mode] = sb.run_lora(d, ad, buf, mode=mode, max_tokens=6, device="cpu", prompts=sb.LORA_PROMPTS[:2])
+        lines = buf.getvalue().splitlines()
+        assert lines[0].split(",") == sb.LORA_COLUMNS and len(lines) == 5
+        assert [r["variant"] for r in out[mode]] == ["base", "base", "lora-adapted", "lora-adapted"]
+    assert [r["token_ids"] for r in out["merge"]] == [r["token_ids"] for r in out["hotswap"]]
+    assert out["merge"][0]["token_ids"] != out["merge"][2]["token_ids"]
