@@ -364,3 +364,56 @@ def test_smoke_benchmarks_thinking_and_lora(tmp_path):
         assert [r["variant"] for r in out[mode]] == ["base", "base", "lora-adapted", "lora-adapted"]
     assert [r["token_ids"] for r in out["merge"]] == [r["token_ids"] for r in out["hotswap"]]
     assert out["merge"][0]["token_ids"] != out["merge"][2]["token_ids"]
+
+
+def test_vibrant_codegen_transformers_and_rag(tmp_path):
+    """Spec-driven generation: replies are split into source files (java: package folders, imports repeated per type; python:
+    file markers), existing files are kept unless the spec allows overwriting; retrieval chat over a toy embedding."""
+    import io
+
+    from deliverance_b200.agents import vibrant as V
+
+    reply = ("Sure!\n```java\npackage com.acme.shapes;\nimport java.util.List;\n\npublic interface Shape {\n  double area();\n}\n\n"
+             "public class Square implements Shape {\n  double s;\n  public double area() { return s * s; }\n}\n```\nDone.")
+    spec_file = tmp_path / "vibes.json"
+    spec_file.write_text(json.dumps({"vibeSpecs": [
+        {"id": "shapes", "systemMessage": ["You write Java."], "userMessage": "Make shapes.", "generateTo": "gen",
+         "messageTransformer": "io.teknek.deliverance.vibrant.JavaResponseTransformer"},
+        {"id": "off", "userMessage": ["x"], "enabled": False},
+        {"id": "tool", "userMessage": ["py"], "generateTo": "pygen", "messageTransformer": "python", "overwrite": True}]}))
+    specs = V.load_specs(str(spec_file))
+    assert specs[0].transformer == "java" and specs[0].user_messages == ["Make shapes."] and not specs[1].enabled
+    seen = []
+
+    def chat(messages):
+        seen.append(messages)
+        return reply if "Java" in messages[0]["content"] else "```python\n# file: a.py\nx = 1\n# file: pkg/b.py\ny = 2\n```"
+
+    out = V.run_specs(chat, specs, str(tmp_path), log=lambda s: None)
+    sq = (tmp_path / "gen" / "com" / "acme" / "shapes" / "Square.java").read_text()
+    assert sq.startswith("package com.acme.shapes;\nimport java.util.List;\npublic class Square implements Shape {") and sq.rstrip().endswith("}")
+    assert (tmp_path / "gen" / "com" / "acme" / "shapes" / "Shape.java").exists() and len(out["shapes"]) == 2 and "off" not in out
+    assert (tmp_path / "pygen" / "a.py").read_text() == "x = 1\n" and (tmp_path / "pygen" / "pkg" / "b.py").read_text() == "y = 2\n"
+    assert seen[0][0] == {"role": "system", "content": "You write Java."}
+    with pytest.raises(FileExistsError):  # overwrite is off for the java spec
+        V.run_specs(chat, specs[:1], str(tmp_path), log=lambda s: None)
+    V.run_specs(chat, specs[2:], str(tmp_path), log=lambda s: None)  # overwrite allowed
+    with pytest.raises(ValueError):
+        V.transform_python("```python\n# file: ../evil.py\nx\n```", str(tmp_path), specs[2])
+    assert V.fenced_region("no fences", "java") == "no fences"
+
+    chunks = V.split_text("para one\n\n" + "x" * 900 + "\n\npara three " * 30, 400, 50)
+    assert all(len(c) <= 400 for c in chunks) and len(chunks) > 3
+    words = ["mojo", "tensor", "socket"]
+    embed = lambda texts: torch.tensor([[float(t.lower().count(w)) + 0.01 for w in words] for t in texts])  # noqa: E731
+    store = V.VectorStore(embed)
+    (tmp_path / "src").mkdir()
+    (tmp_path / "src" / "a.py").write_text("class Plugin(Mojo):\n    '''a mojo mojo'''\n")
+    (tmp_path / "src" / "b.py").write_text("def reduce(tensor):\n    return tensor.sum()\n")
+    buf = io.StringIO()
+    asked = []
+    rag = V.RagChat(lambda m: asked.append(m[0]["content"]) or "answer", store, buf)
+    assert rag.line(f"index {tmp_path / 'src'}") and "2 chunks" in buf.getvalue()
+    assert rag.line("embedding which classes extend Mojo") and store.search("mojo", 1)[0][1]["path"].endswith("a.py")
+    assert rag.line("template What extends Mojo?") and "class Plugin(Mojo)" in asked[0] and asked[0].endswith("Question: What extends Mojo?")
+    assert rag.line("hello") and asked[1] == "hello" and not rag.line("undeliver")
