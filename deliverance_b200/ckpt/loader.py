@@ -111,6 +111,13 @@ class WeightLoader:
             q = Q4Tensor(packed, scales, info.shape)
             return shard_q4(q, shard) if shard and shard.size > 1 else q
         t = fh.tensor(name)
+        if info.dtype == "I8" and self.has(name + ".qb"):
+            # block-32 int8 weights with a scale sidecar (the reference's optional Q8 weight format): served dense
+            from .jq4 import q8_dequantize
+
+            qb = name + ".qb"
+            scales = self._files[self._where[qb]].tensor(qb).reshape(*info.shape[:-1], info.shape[-1] // BLOCK)
+            t = q8_dequantize(t, scales.float(), torch.bfloat16)
         return shard_dense(t, shard) if shard and shard.size > 1 else t
 
     def load_dense(self, name: str, dtype: torch.dtype = torch.float32, shard: Optional[ShardSpec] = None) -> torch.Tensor:

@@ -30,7 +30,7 @@ def main() -> int:
     from .runner import EngineRunner
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    tp = control = None
+    tp = control = placement = None
     if world > 1:  # one process per GPU: NCCL for tensors, a gloo side group for the control commands
         import torch
         import torch.distributed as dist
@@ -42,9 +42,20 @@ def main() -> int:
         cuda = torch.cuda.is_available() and a.device != "cpu"
         if cuda:
             torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+            if os.environ.get("DLV_AFFINITY", "off") != "off":  # opt-in: pin this rank to the cores of its GPU's NUMA node
+                from ..utils.affinity import place_local_rank
+
+                placement = place_local_rank(int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("LOCAL_WORLD_SIZE", world)))
         dist.init_process_group("nccl" if cuda else "gloo")
         control = TorchCollectives(dist.new_group(backend="gloo"))
         tp = TensorParallelContext(dist.get_rank(), world, TorchCollectives())
+        if cuda and os.environ.get("DLV_FUSED_TP", "1") != "0":
+            try:  # tensor-parallel sums inside the GEMM epilogue over NVLink peer memory; NCCL all-reduce otherwise
+                from ..parallel.fused import FusedTensorParallel
+
+                tp.fused = FusedTensorParallel.create(tp, torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+            except Exception as e:  # noqa: BLE001
+                print(f"[server] fused tensor parallelism unavailable, using NCCL all-reduce: {e}", flush=True)
     reg = ModelRegistry()
     for d in a.model:
         b = AutoModelForCausalLM.new_builder(d).with_device(a.device).with_output_head_quantization(a.output_head_quantization)
@@ -63,6 +74,10 @@ def main() -> int:
 
             follower_loop(clm, control)
             return 0
+    if tp is not None:
+        backend = "nccl + fused peer-memory epilogues" if getattr(tp, "fused", None) is not None else ("nccl" if cuda else "gloo")
+        reg.tp_status = lambda: {"enabled": True, "size": world, "rank": 0, "backend": backend, "membership": "static",
+                                 "placement": None if placement is None else placement.to_json()}
     for d in a.embedding_model:
         reg.embedding[os.path.basename(os.path.normpath(d))] = AutoModelForEmbeddings.from_pretrained(d, a.device)
     settings = ServerSettings(reasoning_field=a.reasoning_field, basic_user=a.basic_user, basic_password=a.basic_password, jwt_secret=a.jwt_secret)

@@ -426,6 +426,34 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         st["runners"] = {n: dict(r.stats, engine=dict(r.clm.engine.metrics), prefix_cache=dict(r.clm.engine.kv.prefix.metrics)) for n, r in registry.generation.items()}
         return JSONResponse(st)
 
+    async def tp_endpoints():
+        """The ranks of the tensor-parallel group. Ranks are processes of one node that talk over NCCL / peer memory, not HTTP
+        services, so an entry names the rank and its device instead of a URL (reference: /tp/endpoints lists rank-server URLs,
+        web/.../TensorParallelDiagnosticsController.java:22-40)."""
+        st = registry.tp_status()
+        n = int(st.get("size", 1))
+        return JSONResponse({"size": n, "endpoints": [{"rank": r, "device": f"cuda:{r}" if st.get("enabled") else "local",
+                                                       "role": "coordinator+rank" if r == 0 else "rank"} for r in range(n)]})
+
+    async def tp_gossip():
+        """Membership view. The group is fixed at launch (RANK / WORLD_SIZE), so the view is the static member list plus the
+        supervisor's restart history when one is running."""
+        st = dict(registry.tp_status())
+        out = {"membership": "static", "leader": 0, "members": list(range(int(st.get("size", 1))))}
+        sf = os.environ.get("DLV_CLUSTER_STATUS_FILE")
+        if sf and os.path.exists(sf):
+            try:
+                with open(sf) as f:
+                    out["supervisor"] = json.load(f)
+            except (OSError, ValueError):
+                pass
+        return JSONResponse(out)
+
+    async def tp_assign(request: Request):
+        q = request.query_params
+        return error(409, f"rank assignment is static: ranks are fixed at launch (requested nodeId={q.get('nodeId')} rank={q.get('rank')}); "
+                          "restart the group with a different --nproc to change it")
+
     async def ui():
         return HTMLResponse(_UI)
 
@@ -472,6 +500,9 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
 
     app.add_api_route("/metrics", metrics, methods=["GET"])
     app.add_api_route("/tp/status", tp_status, methods=["GET"])
+    app.add_api_route("/tp/endpoints", tp_endpoints, methods=["GET"])
+    app.add_api_route("/tp/gossip", tp_gossip, methods=["GET"])
+    app.add_api_route("/tp/assign", tp_assign, methods=["POST"])
     app.add_api_route("/ui", ui, methods=["GET"])
     return app
 

@@ -56,6 +56,19 @@ def test_q8_roundtrip():
     assert (q8_dequantize(q, s) - x).abs().max() < x.abs().max() / 100
 
 
+def test_loader_dequantises_i8_block_weights(tmp_path):
+    """An ``I8`` entry with a ``.qb`` scale sidecar (block-32 int8 weights) loads as a dense tensor; a plain int8 tensor stays."""
+    from deliverance_b200.ckpt.loader import WeightLoader
+
+    x = torch.randn(4, 64)
+    q, s = q8_quantize(x)
+    write_safetensors(str(tmp_path / "model.safetensors"), {"w.weight": q, "w.weight.qb": s, "plain": torch.arange(4, dtype=torch.int8)})
+    ld = WeightLoader(str(tmp_path))
+    w = ld.load("w.weight")
+    assert w.dtype == torch.bfloat16 and (w.float() - x).abs().max() < x.abs().max() / 50
+    assert ld.load("plain").dtype == torch.int8 and "w.weight.qb" not in ld.names()
+
+
 def test_safetensors_roundtrip_with_q4(tmp_path):
     w = torch.randn(4, 64)
     p, s = q4_quantize(w)

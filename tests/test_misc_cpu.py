@@ -417,3 +417,38 @@ def test_vibrant_codegen_transformers_and_rag(tmp_path):
     assert rag.line("embedding which classes extend Mojo") and store.search("mojo", 1)[0][1]["path"].endswith("a.py")
     assert rag.line("template What extends Mojo?") and "class Plugin(Mojo)" in asked[0] and asked[0].endswith("Question: What extends Mojo?")
     assert rag.line("hello") and asked[1] == "hello" and not rag.line("undeliver")
+
+
+def test_rank_affinity_from_fake_sysfs(tmp_path):
+    """NUMA placement of rank processes, driven by a fake sysfs tree: PCI id normalisation, node lookup, core shares of ranks
+    that share a node, analyze / off modes, and machines that report no node."""
+    from deliverance_b200.utils import affinity as A
+
+    assert A.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert A.normalise_pci_bus_id("00000000:1B:00.0") == "0000:1b:00.0" and A.normalise_pci_bus_id("1b:00.0") == "0000:1b:00.0"
+    root = tmp_path / "sys"
+    for bus, node in (("0000:1b:00.0", 0), ("0000:43:00.0", 0), ("0000:9b:00.0", 1), ("0000:c3:00.0", -1)):
+        d = root / "bus" / "pci" / "devices" / bus
+        d.mkdir(parents=True)
+        (d / "numa_node").write_text(f"{node}\n")
+    for node, cl in ((0, "0-7"), (1, "8-15")):
+        d = root / "devices" / "system" / "node" / f"node{node}"
+        d.mkdir(parents=True)
+        (d / "cpulist").write_text(cl + "\n")
+    (root / "devices" / "system" / "cpu" / "cpu9" / "node1").mkdir(parents=True)
+    assert A.numa_node_of_cpu(9, str(root)) == 1 and A.numa_node_of_cpu(3, str(root)) == -1
+    calls = []
+    bus = ["00000000:1B:00.0", "00000000:43:00.0", "00000000:9B:00.0", "00000000:C3:00.0"]
+    kw = dict(sysfs_root=str(root), bus_ids=bus, setaffinity=lambda pid, cpus: calls.append(sorted(cpus)), allowed=set(range(16)))
+    p0 = A.place_local_rank(0, 4, "enforce", **kw)
+    p1 = A.place_local_rank(1, 4, "enforce", **kw)
+    p2 = A.place_local_rank(2, 4, "enforce", **kw)
+    assert (p0.numa_node, p0.cpus, p0.applied) == (0, [0, 1, 2, 3], True) and p1.cpus == [4, 5, 6, 7] and p2.cpus == list(range(8, 16))
+    assert calls == [[0, 1, 2, 3], [4, 5, 6, 7], list(range(8, 16))]
+    p3 = A.place_local_rank(3, 4, "enforce", **kw)
+    assert not p3.applied and "no NUMA node" in p3.note and len(calls) == 3
+    pa = A.place_local_rank(2, 4, "analyze", **kw)
+    assert pa.cpus and not pa.applied and len(calls) == 3 and A.place_rank(0, bus[0], "off").note == "off"
+    restricted = A.place_rank(2, bus[2], "enforce", str(root), setaffinity=lambda *a: None, allowed={0, 1})
+    assert not restricted.applied and "no usable cores" in restricted.note
+    assert p0.to_json()["cpus"] == 4

@@ -49,6 +49,8 @@ def test_chat_blocking_and_models(registry):
     m = c.get("/models").json()["data"]
     assert {x["id"] for x in m} == {"tiny-llama", "tiny-bert"}
     assert c.get("/tp/status").json()["enabled"] is False
+    assert c.get("/tp/endpoints").json() == {"size": 1, "endpoints": [{"rank": 0, "device": "local", "role": "coordinator+rank"}]}
+    assert c.get("/tp/gossip").json()["membership"] == "static" and c.post("/tp/assign?nodeId=n1&rank=1").status_code == 409
 
 
 def test_chat_streaming_sse(registry):
