@@ -10,7 +10,9 @@ import os
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", action="append", required=True, help="model directory (repeatable)")
+    ap.add_argument("--model", action="append", default=[], help="model directory (repeatable)")
+    ap.add_argument("--config", help=".properties (or .json) file in the reference's key layout: models, KV cache, auth, port")
+    ap.add_argument("--models-root", default=os.environ.get("DELIVERANCE_HOME", "~/.deliverance"), help="where --config model names are looked up")
     ap.add_argument("--embedding-model", action="append", default=[])
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8080)
@@ -22,6 +24,28 @@ def main() -> int:
     ap.add_argument("--jwt-secret", default=os.environ.get("DELIVERANCE_JWT_SECRET"))
     ap.add_argument("--max-seqs", type=int, default=128)
     a = ap.parse_args()
+    conf = None
+    head_quant, lora, kv = {}, {}, None
+    if a.config:
+        from .config import load_server_config
+
+        conf = load_server_config(a.config)
+        kv = conf.kv_settings() if conf.kv else None
+        for e in conf.models:
+            d = e.resolve_dir(a.models_root)
+            if e.inference_type == "GENERATION":
+                a.model.append(d)
+                head_quant[d], lora[d] = e.output_head_quantization, e.lora_adapter
+            else:
+                a.embedding_model.append(d)
+        a.port = conf.port or a.port
+        a.reasoning_field = conf.reasoning_field or a.reasoning_field
+        a.basic_user, a.basic_password = conf.basic_user or a.basic_user, conf.basic_password or a.basic_password
+        a.jwt_secret = conf.jwt_secret or a.jwt_secret
+        if conf.ignored:
+            print(f"[server] config keys without an equivalent here: {', '.join(sorted(conf.ignored))}", flush=True)
+    if not a.model and not a.embedding_model:
+        ap.error("--model or --config with at least one model is required")
     import uvicorn
 
     from ..api import AutoModelForCausalLM
@@ -58,7 +82,11 @@ def main() -> int:
                 print(f"[server] fused tensor parallelism unavailable, using NCCL all-reduce: {e}", flush=True)
     reg = ModelRegistry()
     for d in a.model:
-        b = AutoModelForCausalLM.new_builder(d).with_device(a.device).with_output_head_quantization(a.output_head_quantization)
+        b = AutoModelForCausalLM.new_builder(d).with_device(a.device).with_output_head_quantization(head_quant.get(d) or a.output_head_quantization)
+        if kv is not None:
+            b.with_kv_cache_settings(kv)
+        if lora.get(d):
+            b.with_lora_adapter(lora[d])
         b.conf.max_seqs = a.max_seqs
         if tp is not None:
             b.with_tensor_parallel_context(tp)

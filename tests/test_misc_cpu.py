@@ -452,3 +452,54 @@ def test_rank_affinity_from_fake_sysfs(tmp_path):
     restricted = A.place_rank(2, bus[2], "enforce", str(root), setaffinity=lambda *a: None, allowed={0, 1})
     assert not restricted.applied and "no usable cores" in restricted.note
     assert p0.to_json()["cpus"] == 4
+
+
+def test_server_properties_config(tmp_path):
+    """The reference's .properties layout: indexed model entries (both key spellings), KV prefix settings, ${ENV:default}
+    placeholders, ignored runtime-specific keys; the same keys as nested JSON."""
+    from deliverance_b200.server.config import load_server_config, parse_properties
+
+    p = tmp_path / "srv.properties"
+    p.write_text("""# comment
+server.port=${TP_WEB_PORT:8081}
+deliverance.tensor.operations.type=simd
+deliverance-model.configs[0].model-owner=edwardcapriolo
+deliverance-model.configs[0].model-name=${TP_MODEL:Qwen3-4B-JQ4}
+deliverance-model.configs[0].inference-type=GENERATION
+deliverance-model.configs[0].output-head-quantization=Q4
+deliverance-model.configs[0].tensor-parallel.enabled=true
+deliverance-model.configs[0].tensor-parallel.size=${TP_SIZE:4}
+deliverance-model.configs[0].tensor-parallel.seeds[0]=coordinator=udp://127.0.0.1:42606
+deliverance-model.configs[1].modelName=all-MiniLM-L6-v2
+deliverance-model.configs[1].modelOwner=sentence-transformers
+deliverance-model.configs[1].inferenceType=EMBEDDING
+deliverance.kv.prefix.max-tokens=8192
+deliverance.kv.prefix.checkpoint-policy=start_and_end
+deliverance.kv.prefix.max-checkpoints=12
+deliverance.kv.prefix.compression=MSE_TURBOQUANT
+deliverance.kv.prefix.turboquant.bits=4
+deliverance.kv.context-rows-per-page-target=32
+deliverance.openai.reasoning-field=vllm
+deliverance.basic.auth.user=bob
+""")
+    c = load_server_config(str(p), env={"TP_SIZE": "8"})
+    assert c.port == 8081 and len(c.models) == 2 and c.reasoning_field == "vllm" and c.basic_user == "bob"
+    m0, m1 = c.models
+    assert (m0.owner, m0.name, m0.output_head_quantization, m0.tp_enabled, m0.tp_size) == ("edwardcapriolo", "Qwen3-4B-JQ4", "Q4", True, 8)
+    assert (m1.owner, m1.name, m1.inference_type) == ("sentence-transformers", "all-MiniLM-L6-v2", "EMBEDDING")
+    kv = c.kv_settings()
+    assert (kv.max_prefix_tokens, kv.policy, kv.checkpoints, kv.compression, kv.block_size) == (8192, "START_AND_END", 12, "MSE_TURBOQUANT", 32)
+    assert c.kv_turboquant_bits == 4 and "deliverance.tensor.operations.type" in c.ignored and any("seeds" in k for k in c.ignored)
+    (tmp_path / "root" / "edwardcapriolo_Qwen3-4B-JQ4").mkdir(parents=True)
+    assert m0.resolve_dir(str(tmp_path / "root")).endswith("edwardcapriolo_Qwen3-4B-JQ4")
+    assert m1.resolve_dir(str(tmp_path / "root")).endswith("sentence-transformers_all-MiniLM-L6-v2")
+    assert parse_properties("a = 1\\\n  2\nb: x\n! note\n") == {"a": "12", "b": "x"}
+    j = tmp_path / "srv.json"
+    j.write_text(json.dumps({"server": {"port": 9000}, "deliverance-model": {"configs": [{"model-dir": "/m/x", "inferenceType": "generation"}]},
+                             "deliverance": {"kv": {"prefix": {"max-tokens": 1024}}}}))
+    cj = load_server_config(str(j))
+    assert cj.port == 9000 and cj.models[0].model_dir == "/m/x" and cj.models[0].inference_type == "GENERATION" and cj.kv == {"max_prefix_tokens": 1024}
+    bad = tmp_path / "bad.properties"
+    bad.write_text("deliverance-model.configs[0].inference-type=NOPE\ndeliverance-model.configs[0].model-name=x\n")
+    with pytest.raises(ValueError):
+        load_server_config(str(bad))
