@@ -503,3 +503,54 @@ deliverance.basic.auth.user=bob
     bad.write_text("deliverance-model.configs[0].inference-type=NOPE\ndeliverance-model.configs[0].model-name=x\n")
     with pytest.raises(ValueError):
         load_server_config(str(bad))
+
+
+def test_chat_model_adapters(tmp_path):
+    """One ChatModel interface over HTTP and over an in-process model: option merging, the tool-execution loop (fake
+    transport), guided options and streaming on a tiny embedded model."""
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.integrations import ChatOptions, EmbeddedChatModel, HttpChatModel, ToolCallback
+
+    add = ToolCallback("add", "adds two numbers", {"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "integer"}}}, lambda a, b: a + b)
+    base = ChatOptions(temperature=0.2, max_tokens=16, tools=[add], extra={"cache_salt": "s"})
+    m = base.merged(ChatOptions(temperature=0.0, guided_regex="[0-9]+", extra={"ntokens": 64}))
+    assert (m.temperature, m.max_tokens, m.guided_regex, [t.name for t in m.tools]) == (0.0, 16, "[0-9]+", ["add"])
+    f = m.request_fields()
+    assert f["tools"][0]["function"]["name"] == "add" and f["cache_salt"] == "s" and f["ntokens"] == 64 and "top_p" not in f
+
+    class FakeClient:
+        def __init__(self):
+            self.calls = []
+
+        def chat(self, messages, **params):
+            self.calls.append((messages, params))
+            if len(self.calls) == 1:
+                return {"choices": [{"message": {"role": "assistant", "content": "", "tool_calls": [
+                    {"id": "call_101", "type": "function", "function": {"name": "add", "arguments": "{\"a\": 2, \"b\": 40}"}}]}, "finish_reason": "tool_calls"}]}
+            return {"choices": [{"message": {"role": "assistant", "content": "It is 42.", "reasoning_content": "tool said 42"}, "finish_reason": "stop"}],
+                    "usage": {"completion_tokens": 4}}
+
+        def stream_chat(self, messages, **params):
+            yield "content", "hi"
+            yield "finish", "stop"
+
+    fc = FakeClient()
+    hm = HttpChatModel(client=fc, defaults=base)
+    r = hm.call([{"role": "user", "content": "2+40?"}])
+    assert (r.content, r.reasoning, r.finish_reason, r.usage) == ("It is 42.", "tool said 42", "stop", {"completion_tokens": 4})
+    assert fc.calls[1][0][-1] == {"role": "tool", "tool_call_id": "call_101", "name": "add", "content": "42"} and fc.calls[1][0][-2]["tool_calls"]
+    assert r.messages[-1] == {"role": "assistant", "content": "It is 42."} and list(hm.stream([{"role": "user", "content": "x"}])) == [("content", "hi"), ("finish", "stop")]
+    fc2 = FakeClient()
+    r2 = HttpChatModel(client=fc2).call([{"role": "user", "content": "q"}])  # no callback for "add": the call is handed to the caller
+    assert r2.tool_calls and r2.finish_reason == "tool_calls" and len(fc2.calls) == 1
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=5, std=0.08, max_position_embeddings=1024)
+    em = EmbeddedChatModel(AutoModelForCausalLM.from_pretrained(d, device="cpu"), ChatOptions(max_tokens=8, temperature=0.0))
+    r = em.call([{"role": "system", "content": "s"}, {"role": "user", "content": "number?"}], ChatOptions(guided_regex="[0-9]{3}"))
+    assert __import__("re").fullmatch("[0-9]{3}", r.content) and r.usage["completion_tokens"] >= 3
+    ev = list(em.stream([{"role": "user", "content": "hello"}], ChatOptions(max_tokens=5)))
+    assert ev[-1] == ("finish", "length") and sum(1 for k, _ in ev if k == "content") >= 1
+    with pytest.raises(ValueError):
+        em.call([{"role": "user", "content": "x"}], ChatOptions(extra={"nope": 1}))
