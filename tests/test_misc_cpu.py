@@ -554,3 +554,23 @@ def test_chat_model_adapters(tmp_path):
     assert ev[-1] == ("finish", "length") and sum(1 for k, _ in ev if k == "content") >= 1
     with pytest.raises(ValueError):
         em.call([{"role": "user", "content": "x"}], ChatOptions(extra={"nope": 1}))
+
+
+def test_tokenizer_benchmark_and_upload_plan(tmp_path, capsys):
+    from deliverance_b200.ckpt import upload
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.tokenizer import benchmark as tb
+    from deliverance_b200.tokenizer.auto import AutoTokenizer
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=1)
+    r = tb.run(AutoTokenizer.from_pretrained(d), tb.DEFAULT_TEXT, warmup=1, iterations=3)
+    assert r["incremental_equals_decode"] and r["tokens"] > 0 and len(r["ids_sha256"]) == 64 and r["tokens_s"] > 0
+    assert tb.ids_sha256([1, 2, -1]) == __import__("hashlib").sha256(bytes([0, 0, 0, 1, 0, 0, 0, 2, 255, 255, 255, 255])).hexdigest()
+    assert [p for p, _ in upload.plan(d)] == ["config.json", "model.safetensors"]
+    assert upload.main(["me/tiny", d, "--dry-run"]) == 0 and "2 files" in capsys.readouterr().out
+    open(os.path.join(d, "deliverance-quantization.json"), "w").write("{}")
+    with pytest.raises(RuntimeError):
+        upload.plan(d)
+    open(os.path.join(d, ".finished"), "w").close()
+    assert "deliverance-quantization.json" in [p for p, _ in upload.plan(d)] and ".finished" not in [p for p, _ in upload.plan(d)]
