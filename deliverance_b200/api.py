@@ -57,6 +57,7 @@ class AutoModelConfig:
     profile_stages: bool = False
 
     kv_checkpoints: int = 4
+    kv_anchors: tuple = (32, 64, 128)
     kv_compression: str = "NONE"
     kv_turboquant_bits: int = 4
     ignored: tuple = ()  # reference keys that have no meaning on this runtime (kept for diagnostics)
@@ -86,8 +87,8 @@ class AutoModelConfig:
         for k, f in AutoModelConfig._REF_KV_KEYS.items():
             if k in kvb and kvb[k] is not None:
                 out[f] = kvb[k]
-        if "prefixCheckpointAnchors" in kvb:
-            ignored.append("kvBufferCache.prefixCheckpointAnchors")
+        if kvb.get("prefixCheckpointAnchors"):
+            out["kv_anchors"] = tuple(int(a) for a in kvb["prefixCheckpointAnchors"])
         if d.get("quantizeOnDemand"):
             out["quantize_on_demand"] = True
         unknown = [k for k in d if k not in known and k not in AutoModelConfig._REF_KEYS and k not in AutoModelConfig._REF_IGNORED
@@ -305,7 +306,7 @@ class AutoModelForCausalLM:
             self.conf.model = conf.model or model
             self.model_dir = self.conf.model
             self.kv = KvCacheSettings(block_size=conf.kv_block_size, max_prefix_tokens=conf.kv_max_prefix_tokens,
-                                      max_entries=conf.kv_max_entries, policy=conf.kv_policy, checkpoints=conf.kv_checkpoints,
+                                      max_entries=conf.kv_max_entries, policy=conf.kv_policy, checkpoints=conf.kv_checkpoints, anchors=tuple(conf.kv_anchors),
                                       compression=conf.kv_compression, enabled=conf.kv_max_entries > 0 and conf.kv_max_prefix_tokens > 0)
             return self
 

@@ -34,28 +34,40 @@ class KvCacheSettings:
     block_size: int = PAGE_SIZE
     max_prefix_tokens: int = 512
     max_entries: int = 10_000
-    policy: str = "START_AND_END"  # FIXED_BLOCKS | START_AND_END | ANCHORS
-    checkpoints: int = 4
+    policy: str = "START_AND_END"  # FIXED_BLOCKS | START_AND_END | ANCHORS_AND_LARGEST
+    checkpoints: int = 4  # most checkpoints kept per prompt (START_AND_END, ANCHORS_AND_LARGEST)
+    anchors: tuple = (32, 64, 128)
     enabled: bool = True
     compression: str = "NONE"  # NONE | LZ4 | MSE_TURBOQUANT (host snapshots only, see kv.snapshot)
 
     def checkpoint_lengths(self, n_tokens: int) -> list[int]:
+        """Prefix lengths (multiples of the block size, at most ``max_prefix_tokens``) at which a prompt of ``n_tokens`` is
+        checkpointed (reference: core/.../tensor/KvBufferCache.java:457-507 and the vectors of KvBufferCachePrefixTest.java):
+        FIXED_BLOCKS = every block; START_AND_END = the first ceil(checkpoints / 2) blocks and the last floor(checkpoints / 2)
+        block ends; ANCHORS_AND_LARGEST = the anchors that fit (at most checkpoints - 1 of them) plus the largest aligned length."""
         b = self.block_size
         L = (min(n_tokens, self.max_prefix_tokens) // b) * b
-        if L <= 0:
+        if L < b:
             return []
         if self.policy == "FIXED_BLOCKS":
             return list(range(b, L + 1, b))
+        m = max(1, self.checkpoints)
         if self.policy == "START_AND_END":
-            c = {b, 2 * b, L - b, L}
-            return sorted(x for x in c if 0 < x <= L)
-        if self.policy == "ANCHORS":
-            c = {L}
-            for a in (32, 64, 128):
+            n_start = (m + 1) // 2
+            n_end = m - n_start
+            picked = set(range(b, min(L, n_start * b) + 1, b))
+            picked.update(x for x in range(L - (n_end - 1) * b, L + 1, b) if x >= b)
+            return sorted(picked)
+        if self.policy in ("ANCHORS_AND_LARGEST", "ANCHORS"):
+            picked: list = []
+            for a in self.anchors:
                 a = (a // b) * b
-                if 0 < a <= L:
-                    c.add(a)
-            return sorted(c)
+                if b <= a <= L and a not in picked:
+                    picked.append(a)
+                if len(picked) >= max(0, m - 1):
+                    break
+            out = sorted(set(picked) | {L})
+            return sorted(set(out[: m - 1] + [L])) if len(out) > m else out
         raise ValueError(f"unknown checkpoint policy {self.policy}")
 
 

@@ -12,7 +12,7 @@ tp_local/coordinator.properties; both ``model-name`` and ``modelName`` spellings
     deliverance-model.configs[i].lora-adapter             adapter directory merged at load (extension)
     deliverance-model.configs[i].tensor-parallel.enabled | size
     deliverance.kv.prefix.max-tokens | checkpoint-policy | max-checkpoints | compression | turboquant.bits | enabled | max-entries
-    deliverance.kv.context-rows-per-page-target
+    deliverance.kv.context-rows-per-page-target | deliverance.kv.disk-dir
     deliverance.openai.reasoning-field                    openai | vllm
     deliverance.basic.auth.user | deliverance.basic.auth.password | deliverance.jwt.secret
 
@@ -100,6 +100,7 @@ class ServerConfig:
     models: list = field(default_factory=list)
     kv: dict = field(default_factory=dict)  # KvCacheSettings field -> value
     kv_turboquant_bits: Optional[int] = None
+    kv_disk_dir: Optional[str] = None  # evicted prefixes spill to files under this directory
     reasoning_field: Optional[str] = None
     basic_user: Optional[str] = None
     basic_password: Optional[str] = None
@@ -153,6 +154,8 @@ def load_server_config(path: str, env: Optional[dict] = None) -> ServerConfig:
             cfg.kv[name] = conv(v)
         elif key == "deliverance.kv.prefix.turboquant.bits":
             cfg.kv_turboquant_bits = int(v)
+        elif key == "deliverance.kv.disk-dir":
+            cfg.kv_disk_dir = v or None
         elif key == "server.port":
             cfg.port = int(v)
         elif key == "deliverance.openai.reasoning-field":

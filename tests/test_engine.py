@@ -330,3 +330,23 @@ def test_sampler_reference_vectors():
             GeneratorParameters(temperature=1.0, **bad).validate()
     with pytest.raises(ValueError):
         GeneratorParameters(temperature=0.0, top_p=0.9, uniform_top_p=1.0).validate()
+
+
+def test_checkpoint_policies_reference_vectors():
+    """The checkpoint lengths of the reference's KvBufferCachePrefixTest for all three policies."""
+    from deliverance_b200.kv.paged import KvCacheSettings as S
+
+    big = 10**6
+    fb = S(block_size=4, policy="FIXED_BLOCKS", max_prefix_tokens=big)
+    assert [fb.checkpoint_lengths(n) for n in (3, 4, 15)] == [[], [4], [4, 8, 12]]
+    al = S(block_size=4, policy="ANCHORS_AND_LARGEST", max_prefix_tokens=1000, checkpoints=4, anchors=(4, 8, 12))
+    assert al.checkpoint_lengths(35) == [4, 8, 12, 32]
+    assert [al.checkpoint_lengths(n) for n in (3, 4, 15)] == [[], [4], [4, 8, 12]]
+    assert S(block_size=4, policy="ANCHORS_AND_LARGEST", max_prefix_tokens=big, checkpoints=3, anchors=(4, 8, 12, 16)).checkpoint_lengths(35) == [4, 8, 32]
+    assert S(block_size=32, policy="ANCHORS_AND_LARGEST", max_prefix_tokens=512, checkpoints=4).checkpoint_lengths(5000) == [32, 64, 128, 512]
+    assert S(block_size=4, policy="ANCHORS_AND_LARGEST", max_prefix_tokens=16, anchors=(4, 8)).checkpoint_lengths(16) == [4, 8, 16]
+    se = S(block_size=4, max_prefix_tokens=big, checkpoints=6)
+    assert se.policy == "START_AND_END" and se.checkpoint_lengths(35) == [4, 8, 12, 24, 28, 32]
+    assert [se.checkpoint_lengths(n) for n in (3, 4, 15)] == [[], [4], [4, 8, 12]]
+    assert S(block_size=32, max_prefix_tokens=512, checkpoints=4).checkpoint_lengths(5000) == [32, 64, 480, 512]
+    assert S(block_size=32, max_prefix_tokens=512, checkpoints=4).checkpoint_lengths(100) == [32, 64, 96]
