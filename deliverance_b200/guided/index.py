@@ -92,7 +92,10 @@ class RegexDFA:
 
         if len(pattern) > settings.max_regex_length:
             raise ValueError(f"regex longer than {settings.max_regex_length} characters")
-        fsm = interegular.parse_pattern(pattern).to_fsm().reduce()
+        try:
+            fsm = interegular.parse_pattern(pattern).to_fsm().reduce()
+        except Exception as e:  # noqa: BLE001 - the parser's own exception types carry no message
+            raise ValueError(f"cannot compile guided regex {pattern[:80]!r}: {type(e).__name__} {e}".rstrip()) from e
         self.initial = fsm.initial
         self.finals = frozenset(fsm.finals)
         self.map = fsm.map

@@ -73,13 +73,17 @@ def map_chat_request(body: dict, runner: EngineRunner):
     msgs = body.get("messages")
     if not isinstance(msgs, list) or not msgs:
         raise ValueError("'messages' must be a non-empty list")
+    if body.get("chat_template_kwargs") is not None and not isinstance(body["chat_template_kwargs"], dict):
+        raise ValueError("'chat_template_kwargs' must be an object")
     b = clm.prompt_builder().with_template(body.get("chat_template")).with_kwargs(body.get("chat_template_kwargs"))
     for m in msgs:
+        if not isinstance(m, dict):
+            raise ValueError("every entry of 'messages' must be an object with 'role' and 'content'")
         role = m.get("role")
         content = m.get("content")
         if isinstance(content, list):  # text parts
             content = "".join(p.get("text", "") for p in content if isinstance(p, dict) and p.get("type", "text") == "text")
-        content = content or ""
+        content = "" if content is None else content if isinstance(content, str) else json.dumps(content)
         if role == "system":
             b.add_system(content)
         elif role == "user":
@@ -102,6 +106,8 @@ def select_tools(body: dict):
     keep all. The reference's request schema carries these fields (web/deliverance_specification.yaml,
     CreateChatCompletionRequest) without acting on them; they are honoured here so OpenAI clients behave as they expect."""
     tools = body.get("tools")
+    if tools is not None and (not isinstance(tools, list) or not all(isinstance(t, dict) for t in tools)):
+        raise ValueError("'tools' must be a list of tool objects")
     if not tools and body.get("functions"):
         tools = [{"type": "function", "function": f} for f in body["functions"] if isinstance(f, dict)]
     if not tools:
@@ -130,8 +136,12 @@ def map_params(body: dict) -> GeneratorParameters:
                      ("xtc_probability", "xtc_probability")):
         if body.get(src) is not None:
             setattr(p, dst, float(body[src]))
+    if body.get("n") not in (None, 1):
+        raise ValueError("only n = 1 is supported")
     if body.get("max_tokens") is not None:
         p.max_tokens = int(body["max_tokens"])
+        if p.max_tokens <= 0:
+            raise ValueError("max_tokens must be > 0")
     if body.get("ntokens") is not None:
         p.ntokens = int(body["ntokens"])
     if body.get("seed") is not None:
@@ -144,7 +154,11 @@ def map_params(body: dict) -> GeneratorParameters:
     p.include_stop_str_in_output = bool(body.get("include_stop_str_in_output", False))
     p.logprobs = bool(body.get("logprobs", False))
     p.top_logprobs = int(body.get("top_logprobs") or 0)
+    if not 0 <= p.top_logprobs <= 20:
+        raise ValueError("top_logprobs must be between 0 and 20")
     p.guided_regex = body.get("guided_regex")
+    if p.guided_regex is not None and not isinstance(p.guided_regex, str):
+        raise ValueError("'guided_regex' must be a string")
     p.guided_json = body.get("guided_json")
     rf = body.get("response_format")
     if isinstance(rf, dict) and p.guided_json is None and p.guided_regex is None:
@@ -309,7 +323,9 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
                 if msg:
                     return error(400, msg)
         except (ValueError, KeyError, TypeError) as e:
-            return error(400, str(e.args[0]) if e.args else str(e))
+            return error(400, (str(e.args[0]) if e.args and str(e.args[0]) else "") or f"invalid request ({type(e).__name__})")
+        except Exception as e:  # noqa: BLE001 - e.g. a chat template that does not compile or render
+            return error(400, f"could not prepare the request: {type(e).__name__}: {e}")
         session = request.headers.get("x-deliverance-session") or str(uuid.uuid4())
         cid, created, model = "chatcmpl-" + uuid.uuid4().hex, int(time.time()), body.get("model") or runner.clm.name
         if body.get("stream"):

@@ -151,3 +151,18 @@ def test_openai_compat_fields(registry):
     assert json.loads(r.json()["choices"][0]["message"]["content"]) in ({"ok": True}, {"ok": False})
     r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "tools": tools, "tool_choice": {"function": {"name": "zz"}}})
     assert r.status_code == 400
+
+
+def test_malformed_requests_are_400(registry):
+    """Bad field types and values are the client's fault: a 400 with a message, never a 500."""
+    c = TestClient(create_app(registry), raise_server_exceptions=False)
+    u = [{"role": "user", "content": "hi"}]
+    for body in ({"messages": u, "max_tokens": 0}, {"messages": u, "max_tokens": "many"}, {"messages": ["hi"]}, {"messages": u, "n": 3},
+                 {"messages": u, "tools": "x"}, {"messages": u, "tools": [1]}, {"messages": u, "top_logprobs": 99, "logprobs": True},
+                 {"messages": u, "guided_regex": "([a-z"}, {"messages": u, "guided_regex": 5}, {"messages": u, "chat_template": "{% for %}"},
+                 {"messages": u, "chat_template_kwargs": "x"}, {"messages": u, "temperature": "hot"}, {"messages": u, "seed": "abc"}):
+        r = c.post("/chat/completions", json=dict(body, **({} if "max_tokens" in body else {"max_tokens": 2})))
+        assert r.status_code == 400 and r.json()["error"]["message"], (body, r.status_code, r.text)
+    assert c.post("/chat/completions", content="{not json", headers={"Content-Type": "application/json"}).status_code == 400
+    r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": None}, {"role": "user", "content": 5}], "max_tokens": 2})
+    assert r.status_code == 200
