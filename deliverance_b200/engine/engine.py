@@ -51,6 +51,13 @@ class Request:
     pending: int = 0  # tokens launched on the device but not yet read by the host (lookahead decode)
     error: Optional[str] = None
     state_snapshots: dict = field(default_factory=dict)
+    fill: Optional[list] = None  # tokens whose KV must be cached before decoding: the prompt, or after a preemption prompt + output[:-1]
+    resumed: bool = False  # re-admitted after a preemption: the prefill only rebuilds the cache, nothing is sampled from it
+    preemptions: int = 0
+
+    def __post_init__(self):
+        if self.fill is None:
+            self.fill = self.prompt
 
     @property
     def total_len(self) -> int:
@@ -171,22 +178,23 @@ class Engine:
         """Prefix lookup + page reservation for a waiting request."""
         if len(self.running) >= self.config.max_seqs:
             return False
-        need_pages = (len(r.prompt) + 1 + self.page_size - 1) // self.page_size
-        if not self.kv.can_allocate(need_pages):
+        need_pages = (len(r.fill) + 1 + self.page_size - 1) // self.page_size
+        # one page of headroom per running sequence: a request admitted into a nearly full pool would be preempted at once
+        if not self.kv.can_allocate(need_pages + len(self.running)):
             return False
         if self.hybrid:
             if not self.kv.free_slots:
                 return False
             r.state_slot = self.kv.alloc_state_slot()
-        hit = self.kv.prefix.lookup(r.salt, r.prompt)
+        hit = self.kv.prefix.lookup(r.salt, r.fill)
         if hit is not None:
             r.pages = hit.pages
             r.prefix_hit = hit.length
             r.computed = hit.length
             if self.hybrid and hit.state is not None:
                 self.kv.restore_state(r.state_slot, hit.state)
-            if r.computed >= len(r.prompt):
-                r.computed = len(r.prompt) - 1  # full hit: replay the last prompt token to get logits
+            if r.computed >= len(r.fill):
+                r.computed = len(r.fill) - 1  # full hit: replay the last prompt token to get logits
         r.state = RUNNING
         self.running.append(r)
         return True
@@ -202,6 +210,58 @@ class Engine:
             self.kv.free_state_slot(r.state_slot)
             r.state_slot = -1
 
+    # ------------------------------------------------------------------------------------------------ memory pressure
+    def _preempt(self, v: Request) -> None:
+        """Take a running request out of the batch and give its pages back; it re-enters at the head of the waiting queue and
+        rebuilds its cache by prefilling prompt + generated tokens (recompute; its own prompt is usually a prefix-cache hit).
+        Sampling state, guide, stop detector and the tokens produced so far stay with the request, so its output is unchanged."""
+        self.running.remove(v)
+        self.kv.release_pages(v.pages)
+        if v.state_slot >= 0:
+            self.kv.free_state_slot(v.state_slot)
+            v.state_slot = -1
+        v.state, v.computed, v.state_snapshots = WAITING, 0, {}
+        v.resumed = bool(v.output)
+        v.fill = v.prompt + v.output[:-1] if v.output else v.prompt
+        v.preemptions += 1
+        self.metrics["preemptions"] = self.metrics.get("preemptions", 0) + 1
+        self.waiting.insert(0, v)
+
+    def _new_pages(self, r: Request, n_tokens: int) -> int:
+        return max(0, (n_tokens + self.page_size - 1) // self.page_size - len(r.pages))
+
+    def _reserve(self, r: Request, n_tokens: int) -> bool:
+        """Pages for the first ``n_tokens`` positions of ``r``. Under pressure, requests admitted after ``r`` are preempted
+        (youngest first); False when ``r`` has to wait for older requests to finish instead."""
+        need = self._new_pages(r, n_tokens)
+        while need > 0 and not self.kv.can_allocate(need):
+            younger = self.running[self.running.index(r) + 1 :]
+            victims = [v for v in younger if v.pending == 0]
+            if not victims:
+                if self.running[0] is r and not younger:
+                    raise MemoryError("KV cache is too small for this sequence")
+                return False
+            self._preempt(victims[-1])
+        self.kv.ensure_pages(r.pages, n_tokens)
+        return True
+
+    def _make_room_for_decode(self, reqs: list[Request]) -> tuple:
+        """Before a decode step: every sequence needs room for one more position (two with a token in flight). When the
+        pool cannot supply that, the step in flight is settled and the youngest sequences are preempted until it can."""
+        need = sum(self._new_pages(r, r.total_len + r.pending) for r in reqs)
+        if need == 0 or self.kv.can_allocate(need):
+            return reqs, []
+        finished = self._drain()
+        reqs = [r for r in reqs if r.state == RUNNING]
+        while reqs and not self.kv.can_allocate(sum(self._new_pages(r, r.total_len) for r in reqs)):
+            v = self.running[-1]  # youngest first; that may be a request whose prefill is waiting for pages
+            if v is reqs[0]:
+                raise MemoryError("KV cache is too small for this sequence")
+            self._preempt(v)
+            if v in reqs:
+                reqs.remove(v)
+        return reqs, finished
+
     def step(self) -> list[Request]:
         """Run one engine step; returns the requests that finished in it. With lookahead decode the tokens of a decode step are
         read (and its finished requests reported) by the next call, while the device already runs the following step."""
@@ -215,17 +275,21 @@ class Engine:
             finished += self._drain()  # admissions and prefill work on settled request state
         # Admit only while this step's prefill budget has room: a request admitted later looks the prefix cache up later and
         # finds what the requests in front of it have stored by then (concurrent arrivals that share a prefix).
-        backlog = sum(len(r.prompt) - r.computed for r in self.running if r.computed < len(r.prompt))
+        backlog = sum(len(r.fill) - r.computed for r in self.running if r.computed < len(r.fill))
         while self.waiting and backlog < self.config.max_batch_tokens and self._admit(self.waiting[0]):
             r = self.waiting.pop(0)
-            backlog += len(r.prompt) - r.computed
-        prefill = [r for r in self.running if r.computed < len(r.prompt)]
+            backlog += len(r.fill) - r.computed
+        prefill = [r for r in self.running if r.computed < len(r.fill)]
         if prefill:
             finished += self._drain()
             prefill = [r for r in prefill if r.state != FINISHED]
-            return finished + (self._prefill_step(prefill) if prefill else [])
-        if self.running:
-            return finished + self._decode_step(list(self.running))
+            out = self._prefill_step(prefill) if prefill else []
+            if out is not None:
+                return finished + out
+            # every prefill of this step waits for pages that older, decoding requests hold: let those make progress
+        ready = [r for r in self.running if r.computed >= len(r.fill)]
+        if ready:
+            return finished + self._decode_step(ready)
         if self._inflight is not None:
             return finished + self._drain()
         if self.waiting:
@@ -233,24 +297,27 @@ class Engine:
         return finished
 
     # ------------------------------------------------------------------------------------------------ prefill
-    def _prefill_step(self, reqs: list[Request]) -> list[Request]:
+    def _prefill_step(self, reqs: list[Request]) -> Optional[list]:
         budget = self.config.max_batch_tokens
         seqs, chosen = [], []
         for r in reqs:
             if budget <= 0:
                 break
-            n = min(len(r.prompt) - r.computed, budget)
+            n = min(len(r.fill) - r.computed, budget)
             if self.hybrid:
                 # recurrent state can only be snapshotted at chunk ends: stop chunks at the prefix-cache checkpoints
-                for L in self.kv.settings.checkpoint_lengths(len(r.prompt)):
+                for L in self.kv.settings.checkpoint_lengths(len(r.fill)):
                     if r.computed < L < r.computed + n:
                         n = L - r.computed
                         break
-            self.kv.ensure_pages(r.pages, r.computed + n)
-            seqs.append({"tokens": r.prompt[r.computed : r.computed + n], "start": r.computed, "pages": r.pages,
+            if r.state != RUNNING or not self._reserve(r, r.computed + n):
+                continue  # preempted by an older request of this step, or waiting for older requests to release pages
+            seqs.append({"tokens": r.fill[r.computed : r.computed + n], "start": r.computed, "pages": r.pages,
                          "state_slot": max(r.state_slot, 0)})
             chosen.append((r, n))
             budget -= n
+        if not seqs:
+            return None
         batch = make_batch(seqs, self.page_size, self.device)
         logits = self.model.forward(batch, self.kv)
         self.metrics["prefill_steps"] += 1
@@ -258,10 +325,13 @@ class Engine:
         done_rows, done_reqs = [], []
         for i, (r, n) in enumerate(chosen):
             r.computed += n
-            if self.hybrid and r.computed in self.kv.settings.checkpoint_lengths(len(r.prompt)):
+            if self.hybrid and r.computed in self.kv.settings.checkpoint_lengths(len(r.fill)):
                 r.state_snapshots[r.computed] = self.kv.snapshot_state(r.state_slot)
-            if r.computed >= len(r.prompt):
-                self.kv.prefix.store(r.salt, r.prompt, r.pages, r.state_snapshots if self.hybrid else None)
+            if r.computed >= len(r.fill):
+                self.kv.prefix.store(r.salt, r.fill, r.pages, r.state_snapshots if self.hybrid else None)
+                if r.resumed:  # cache rebuilt after a preemption: the next token was sampled before, decoding just continues
+                    r.resumed = False
+                    continue
                 done_rows.append(i)
                 done_reqs.append(r)
         finished = []
@@ -277,13 +347,16 @@ class Engine:
             pos = r.total_len - 1 + r.pending  # position of the token being fed (the last sampled one)
             self.kv.ensure_pages(r.pages, pos + 1)
             seqs.append({"tokens": [r.output[-1] if r.output else 0], "start": pos, "pages": r.pages, "state_slot": max(r.state_slot, 0),
-                         "rid": r.rid})
+                         "rid": (r.rid, r.preemptions)})
         return seqs
 
     def _plain_greedy(self, reqs: list[Request]) -> bool:
         return all(r.guide is None and r.sampling.greedy and not r.params.logprobs for r in reqs)
 
     def _decode_step(self, reqs: list[Request]) -> list[Request]:
+        reqs, early = self._make_room_for_decode(reqs)
+        if early or not reqs:
+            return early + (self._decode_step(reqs) if reqs else [])
         B = len(reqs)
         # (a request one token short of its context limit is settled synchronously: the surplus token of a lookahead step would
         # need a position and a page beyond the limit)
@@ -419,7 +492,7 @@ class Engine:
         owners = g.setdefault("bt_owners", [None] * bucket)
         for i, s in enumerate(seqs):
             pg = s["pages"]
-            key = (s.get("rid"), len(pg))  # a request's page list only grows: same owner and length = same row
+            key = (s.get("rid"), len(pg))  # between preemptions a request's page list only grows: same owner and length = same row
             if key[0] is not None and owners[i] == key:
                 continue
             owners[i] = key

@@ -258,8 +258,18 @@ class PagedKVCache:
         pages.clear()
 
     def can_allocate(self, n_pages: int) -> bool:
-        cached = sum(len(e.pages) for e in self.prefix.entries.values())
-        return self.allocator.available() + cached >= n_pages
+        """True when ``n_pages`` can be had from the free list plus what evicting prefix-cache entries would really free:
+        a cached page comes back only if nothing but cache entries holds it (entries of several checkpoint lengths share
+        pages, and running sequences that hit the cache hold references too)."""
+        free = self.allocator.available()
+        if free >= n_pages:
+            return True
+        held: dict = {}
+        for e in self.prefix.entries.values():
+            for p in e.pages:
+                held[p] = held.get(p, 0) + 1
+        ref = self.allocator.ref
+        return free + sum(1 for p, c in held.items() if ref[p] == c) >= n_pages
 
     def alloc_state_slot(self) -> int:
         if not self.free_slots:

@@ -350,3 +350,44 @@ def test_checkpoint_policies_reference_vectors():
     assert [se.checkpoint_lengths(n) for n in (3, 4, 15)] == [[], [4], [4, 8, 12]]
     assert S(block_size=32, max_prefix_tokens=512, checkpoints=4).checkpoint_lengths(5000) == [32, 64, 480, 512]
     assert S(block_size=32, max_prefix_tokens=512, checkpoints=4).checkpoint_lengths(100) == [32, 64, 96]
+
+
+@pytest.mark.parametrize("family,lookahead", [("qwen3", False), ("qwen3", "force"), ("granitemoehybrid", False)])
+def test_memory_pressure_preempts_and_recomputes(tmp_path, family, lookahead):
+    """Random arrivals into a page pool far too small for all of them: younger sequences are preempted (pages released,
+    cache rebuilt by recompute when they are re-admitted) and every request still produces exactly the tokens of an isolated
+    run, greedy and seeded sampling alike; all pages come back at the end."""
+    d = str(tmp_path / "m")
+    write_tiny_model(d, family, seed=11, std=0.08)
+    model = DecoderModel(load_config(d), "cpu").load(WeightLoader(d))
+    rng = random.Random(5)
+    shared = [rng.randrange(3, 250) for _ in range(70)]
+    jobs = []
+    for i in range(10):
+        p = (shared[: rng.choice([32, 64, 70])] if rng.random() < 0.6 else []) + [rng.randrange(3, 250) for _ in range(rng.randrange(1, 40))]
+        params = GeneratorParameters(max_tokens=rng.randrange(20, 110), temperature=0.0 if i % 3 else 0.8, top_p=None if i % 3 else 0.9, seed=i)
+        jobs.append((p, params, rng.randrange(0, 6)))
+
+    def fresh(params):
+        return GeneratorParameters(max_tokens=params.max_tokens, temperature=params.temperature, top_p=params.top_p, seed=params.seed)
+
+    singles = [Engine(model, EngineConfig(num_pages=64, max_batch_tokens=64, lookahead=False), eos_ids=(-1,)).generate(p, fresh(q)).token_ids
+               for p, q, _ in jobs]
+    eng = Engine(model, EngineConfig(num_pages=9, max_batch_tokens=48, max_seqs=6, lookahead=lookahead, max_state_slots=8,
+                                     kv=KvCacheSettings(max_prefix_tokens=4096, policy="FIXED_BLOCKS")), eos_ids=(-1,))
+    reqs = [None] * len(jobs)
+    step = 0
+    while step < 3000 and (eng.has_work() or any(r is None for r in reqs)):
+        for i, (p, q, at) in enumerate(jobs):
+            if at == step:
+                reqs[i] = eng.add_request(p, fresh(q))
+        if eng.has_work():
+            eng.step()
+        step += 1
+    assert [r.output for r in reqs] == singles
+    assert eng.metrics.get("preemptions", 0) > 0 and sum(r.preemptions for r in reqs) == eng.metrics["preemptions"]
+    eng.kv.prefix.clear()
+    assert eng.kv.allocator.available() == eng.kv.num_pages - 1 and not eng.running and not eng.waiting
+    with pytest.raises(MemoryError):  # a single sequence that cannot fit is an error, not a hang
+        small = Engine(model, EngineConfig(num_pages=3, max_batch_tokens=48, lookahead=False), eos_ids=(-1,))
+        small.generate(shared[:40], GeneratorParameters(max_tokens=60))
