@@ -10,6 +10,7 @@ stop order max_tokens -> guided-choice complete -> stop strings -> tool-parser e
 """
 from __future__ import annotations
 
+import logging
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Optional
@@ -21,6 +22,8 @@ from ..kv.paged import KvCacheSettings, PagedKVCache, compose_salt
 from ..models.batch import ForwardBatch, make_batch
 from ..params import FinishReason, GeneratorParameters, Response, TokenLogProb
 from .sampler import Sampler, SamplingState
+
+_log = logging.getLogger("deliverance_b200.engine")
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
@@ -54,6 +57,7 @@ class Request:
     fill: Optional[list] = None  # tokens whose KV must be cached before decoding: the prompt, or after a preemption prompt + output[:-1]
     resumed: bool = False  # re-admitted after a preemption: the prefill only rebuilds the cache, nothing is sampled from it
     preemptions: int = 0
+    t_progress: float = 0.0
 
     def __post_init__(self):
         if self.fill is None:
@@ -323,8 +327,15 @@ class Engine:
         self.metrics["prefill_steps"] += 1
         self.metrics["prefill_tokens"] += batch.num_tokens
         done_rows, done_reqs = [], []
+        now = time.perf_counter()
         for i, (r, n) in enumerate(chosen):
             r.computed += n
+            if r.computed < len(r.fill) and now - max(r.t_progress, r.t_submit) >= 3.0:
+                # long prompts: a progress line every 3 s (the reference logs prefill progress the same way, AbstractModel.java:1126-1148)
+                r.t_progress = now
+                rate = (r.computed - r.prefix_hit) / max(now - r.t_submit, 1e-9)
+                _log.info("prefill progress request=%d tokens=%d/%d rate=%.0f tok/s eta=%.1f s", r.rid, r.computed, len(r.fill), rate,
+                          (len(r.fill) - r.computed) / max(rate, 1e-9))
             if self.hybrid and r.computed in self.kv.settings.checkpoint_lengths(len(r.fill)):
                 r.state_snapshots[r.computed] = self.kv.snapshot_state(r.state_slot)
             if r.computed >= len(r.fill):

@@ -6,6 +6,7 @@ Same stage names and report format as the reference's ``InferenceProfiler`` (cor
 CUDA events on the current stream and resolved at ``summary()`` (one synchronize), so the timers do not serialise the
 stream. Path counters (``sampler.output_weight_Q4`` ...) record which kernel variant ran. Enabled with
 ``DELIVERANCE_PROFILE_STAGES=1`` or ``--profile-stages``; eager mode only (a captured CUDA graph replays without Python).
+With ``DELIVERANCE_NVTX=1`` every stage also opens an NVTX range of the same name, so a timeline profiler shows the stages.
 """
 from __future__ import annotations
 
@@ -26,6 +27,7 @@ class InferenceProfiler:
         self._totals: dict[str, float] = defaultdict(float)  # ms
         self._counts: dict[str, int] = defaultdict(int)
         self.counters: dict[str, int] = defaultdict(int)
+        self.nvtx = self.cuda and bool(os.environ.get("DELIVERANCE_NVTX"))
 
     @staticmethod
     def from_env(device=None) -> "InferenceProfiler | None":
@@ -38,11 +40,15 @@ class InferenceProfiler:
             return
         if self.cuda:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if self.nvtx:
+                torch.cuda.nvtx.range_push(name)
             a.record()
             try:
                 yield
             finally:
                 b.record()
+                if self.nvtx:
+                    torch.cuda.nvtx.range_pop()
                 self._pending[name].append((a, b))
         else:
             t0 = time.perf_counter()
