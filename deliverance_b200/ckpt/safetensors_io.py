@@ -73,6 +73,16 @@ class Q4Tensor:
         return Q4Tensor(self.packed.to(device), self.scales.to(device), self.shape)
 
 
+def _view(raw, dtype) -> torch.Tensor:
+    """Zero-copy tensor over a read-only mapping. Loaded weights are never written in place (every consumer converts or copies
+    them to the device), so torch's warning about non-writable buffers is silenced here."""
+    import warnings
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", UserWarning)
+        return torch.frombuffer(raw, dtype=dtype)
+
+
 class SafeTensorFile:
     """One mapped ``.safetensors`` file."""
 
@@ -112,7 +122,7 @@ class SafeTensorFile:
                 numel *= s
             if len(raw) != numel // 2:
                 raise ValueError(f"{name}: Q4 payload has {len(raw)} bytes, expected {numel // 2}")
-            t = torch.frombuffer(raw, dtype=torch.uint8) if len(raw) else torch.empty(0, dtype=torch.uint8)
+            t = _view(raw, torch.uint8) if len(raw) else torch.empty(0, dtype=torch.uint8)
             return t.reshape(*info.shape[:-1], info.shape[-1] // 2)
         dt, size = _DTYPES[info.dtype]
         numel = 1
@@ -122,7 +132,7 @@ class SafeTensorFile:
             raise ValueError(f"{name}: payload has {len(raw)} bytes, expected {numel * size}")
         if numel == 0:
             return torch.empty(info.shape, dtype=dt)
-        return torch.frombuffer(raw, dtype=dt).reshape(info.shape)
+        return _view(raw, dt).reshape(info.shape)
 
     def close(self) -> None:
         try:
