@@ -85,7 +85,8 @@ class LocalCluster:
         self.grace, self.poll = grace, poll
         self.env = dict(env if env is not None else os.environ)
         self.status_file = status_file
-        self.start_timeout = start_timeout or hang_timeout  # a rank must publish its first heartbeat within this many seconds
+        # a rank must publish its first heartbeat within this many seconds; loading a model takes far longer than a step
+        self.start_timeout = start_timeout or (max(10 * hang_timeout, 600.0) if hang_timeout > 0 else 0.0)
         self.status = ClusterStatus()
         self.procs: list[subprocess.Popen] = []
         self.hb_dir = tempfile.mkdtemp(prefix="dlv_hb_")
