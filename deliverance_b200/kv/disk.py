@@ -62,11 +62,12 @@ def _unpack(f: SafeTensorFile) -> dict:
 
 
 class DiskPrefixStore:
-    def __init__(self, directory: str, compression: str = "LZ4", bits: int = 4, max_bytes: int = 8 << 30):
+    def __init__(self, directory: str, compression: str = "LZ4", bits: int = 4, max_bytes: int = 8 << 30, max_age_s: float = 0.0):
         self.dir = directory
         self.compression = compression
         self.bits = bits
         self.max_bytes = max_bytes
+        self.max_age_s = max_age_s  # files not read or written for this long are swept (0: keep until the byte limit evicts them)
         os.makedirs(directory, exist_ok=True)
         self.metrics = {"disk_writes": 0, "disk_hits": 0, "disk_misses": 0, "disk_evict": 0, "disk_bytes": 0}
 
@@ -103,7 +104,28 @@ class DiskPrefixStore:
         self.metrics["disk_hits"] += 1
         return pages, snap["n_tokens"]
 
+    def sweep(self, now: Optional[float] = None) -> int:
+        """Age sweeper: removes files whose last use (a hit refreshes the time stamp) is older than ``max_age_s``, and stale
+        temporaries of writers that died. Runs on every write; callers may also run it periodically. Returns the number removed
+        (the reference sweeps its disk pages by age in a background task, core/.../tensor/KvBufferCache.java:609-722)."""
+        import time
+
+        now = time.time() if now is None else now
+        removed = 0
+        for f in os.listdir(self.dir):
+            p = os.path.join(self.dir, f)
+            try:
+                age = now - os.path.getmtime(p)
+                if (f.endswith(".kv") and self.max_age_s > 0 and age > self.max_age_s) or (f.endswith(".tmp") and age > 600):
+                    os.remove(p)
+                    removed += 1
+            except OSError:
+                pass  # another process removed it first
+        self.metrics["disk_evict"] += removed
+        return removed
+
     def _trim(self) -> None:
+        self.sweep()
         files = [(os.path.getmtime(os.path.join(self.dir, f)), os.path.getsize(os.path.join(self.dir, f)), os.path.join(self.dir, f))
                  for f in os.listdir(self.dir) if f.endswith(".kv")]
         total = sum(s for _, s, _ in files)

@@ -292,11 +292,11 @@ class PagedKVCache:
         for i, t in snap["ssm"].items():
             self.ssm_state[i][slot].copy_(t)
 
-    def attach_disk(self, directory: str, compression: str = "LZ4", bits: int = 4, max_bytes: int = 8 << 30):
+    def attach_disk(self, directory: str, compression: str = "LZ4", bits: int = 4, max_bytes: int = 8 << 30, max_age_s: float = 0.0):
         """Spill evicted prefixes to ``directory`` and pull them back on later hits (attention-only models)."""
         from .disk import DiskPrefixStore
 
-        self.prefix.disk = DiskPrefixStore(directory, compression, bits, max_bytes)
+        self.prefix.disk = DiskPrefixStore(directory, compression, bits, max_bytes, max_age_s)
         return self.prefix.disk
 
     def gather_rows(self, layer: int, pages: list[int], n_tokens: int):

@@ -391,3 +391,34 @@ def test_memory_pressure_preempts_and_recomputes(tmp_path, family, lookahead):
     with pytest.raises(MemoryError):  # a single sequence that cannot fit is an error, not a hang
         small = Engine(model, EngineConfig(num_pages=3, max_batch_tokens=48, lookahead=False), eos_ids=(-1,))
         small.generate(shared[:40], GeneratorParameters(max_tokens=60))
+
+
+def test_disk_store_age_sweeper_and_byte_limit(tmp_path):
+    import os
+    import time
+
+    from deliverance_b200.kv.disk import DiskPrefixStore
+    from deliverance_b200.kv.paged import PagedKVCache
+
+    layout = {"layers": 2, "kv_heads": 2, "head_dim": 64, "layer_kinds": ["attention", "attention"]}
+    kv = PagedKVCache(layout, 16, "cpu", torch.float32)
+    store = DiskPrefixStore(str(tmp_path / "d"), compression="NONE", max_age_s=100.0)
+    keys = [bytes([i]) * 20 for i in range(3)]
+    for k in keys:
+        store.save(kv, k, [1, 2], 40)
+    old = time.time() - 1000
+    os.utime(store._path(keys[0]), (old, old))
+    open(os.path.join(store.dir, "dead.kv.tmp"), "w").close()
+    os.utime(os.path.join(store.dir, "dead.kv.tmp"), (old, old))
+    assert store.sweep() == 2 and not store.has(keys[0]) and store.has(keys[1]) and not os.path.exists(os.path.join(store.dir, "dead.kv.tmp"))
+    for k in keys[1:]:
+        os.utime(store._path(k), (time.time() - 90, time.time() - 90))
+    assert store.load(kv, keys[1]) is not None  # a hit refreshes the time stamp
+    assert store.sweep(time.time() + 50) == 1 and store.has(keys[1]) and not store.has(keys[2])
+    one = os.path.getsize(store._path(keys[1]))
+    small = DiskPrefixStore(str(tmp_path / "e"), compression="NONE", max_bytes=int(one * 2.5))
+    for i, k in enumerate(keys + [b"\x09" * 20]):
+        small.save(kv, k, [1, 2], 40)
+        os.utime(small._path(k), (time.time() - 100 + i, time.time() - 100 + i))
+    small._trim()
+    assert [small.has(k) for k in keys + [b"\x09" * 20]] == [False, False, True, True] and small.metrics["disk_bytes"] == 2 * one
