@@ -119,16 +119,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
-// Warp-wide wait: one lane polls, the others sleep at the warp barrier. Hundreds of threads polling mbarriers keep the
-// shared-memory pipe busy and slow down every arrival and wait of the CTA; a pipeline stage then costs several hundred
-// nanoseconds even when no work is attached to it. All lanes of the (converged) warp must call this.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status) ? 1 : 0;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  return ok != 0;
-}
-
 // ---- programmatic dependent launch ------------------------------------------------------------------------------------
 // A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the stream is
 // still running, once every CTA of the predecessor has called pdl_trigger() (or exited). It must call pdl_wait() before it

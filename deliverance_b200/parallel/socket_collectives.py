@@ -14,7 +14,6 @@ import socket
 import struct
 import threading
 import time
-from typing import Optional
 
 import torch
 
