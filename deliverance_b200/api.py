@@ -111,6 +111,10 @@ def build_model(cfg: ModelConfig, device, dtype, tp: TensorParallelContext):
         return Gpt2Model(cfg, device, dtype, tp)
     if cfg.model_type == "bert":
         return BertModel(cfg, device, dtype)
+    if cfg.model_type == "gemma4_text":
+        from .models.gemma4 import Gemma4Model
+
+        return Gemma4Model(cfg, device, dtype, tp)
     return DecoderModel(cfg, device, dtype, tp)
 
 

@@ -18,7 +18,7 @@ from dataclasses import dataclass, field
 from typing import Any, Optional
 
 SUPPORTED_MODEL_TYPES = (
-    "llama", "mistral", "mixtral", "gemma2", "gemma3_text", "gemma3", "qwen2", "qwen3", "qwen3_moe", "gpt2", "granitemoehybrid", "bert",
+    "llama", "mistral", "mixtral", "gemma2", "gemma3_text", "gemma3", "gemma4_text", "gemma4", "qwen2", "qwen3", "qwen3_moe", "gpt2", "granitemoehybrid", "bert",
 )
 
 # transformers' Gemma3TextConfig defaults: hub configs of the multimodal checkpoints leave most text fields out
@@ -88,6 +88,7 @@ class ModelConfig:
     label2id: dict = field(default_factory=dict)
     id2label: dict = field(default_factory=dict)
     raw: dict = field(default_factory=dict, repr=False)
+    extra: dict = field(default_factory=dict, repr=False)  # family-specific structure (gemma4: per-layer head shapes, shared KV, ...)
 
     # ---- derived -------------------------------------------------------------------------------------------------
     @property
@@ -125,6 +126,68 @@ class ModelConfig:
         return self.mamba_intermediate + 2 * self.mamba_n_groups * self.mamba_d_state
 
 
+# transformers' Gemma4TextConfig defaults (hub configs nest the text fields and leave defaults out)
+_GEMMA4_TEXT_DEFAULTS = dict(vocab_size=262144, hidden_size=2304, intermediate_size=9216, num_hidden_layers=30, num_attention_heads=8,
+                             num_key_value_heads=4, head_dim=256, global_head_dim=512, max_position_embeddings=131072, rms_norm_eps=1e-6,
+                             sliding_window=512, vocab_size_per_layer_input=262144, hidden_size_per_layer_input=256, bos_token_id=2,
+                             eos_token_id=1, pad_token_id=0, hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)
+
+
+def _parse_gemma4(outer: dict) -> ModelConfig:
+    """gemma4 text tower (reference: core/.../model/gemma4/Gemma4Config.java:35-180; semantics of transformers' Gemma4TextModel):
+    sliding layers use ``head_dim`` and ``num_key_value_heads``; full-attention layers use ``global_head_dim`` and, with
+    ``attention_k_eq_v``, ``num_global_key_value_heads`` with values taken from the keys; the last ``num_kv_shared_layers``
+    layers reuse the cache of the last earlier layer of their type; the last layer is always a full-attention layer."""
+    d = dict(_GEMMA4_TEXT_DEFAULTS)
+    d.update({k: v for k, v in (outer.get("text_config") or outer).items() if v is not None})
+    for k in ("eos_token_id", "bos_token_id"):
+        if outer.get(k) is not None:
+            d[k] = outer[k]
+    nl, hd = int(d["num_hidden_layers"]), int(d["head_dim"])
+    lt = list(d.get("layer_types") or ["full_attention" if (i + 1) % 6 == 0 else "sliding_attention" for i in range(nl)])
+    if lt and lt[-1] != "full_attention":
+        lt[-1] = "full_attention"
+    ghd = int(d.get("global_head_dim") or hd)
+    k_eq_v = bool(d.get("attention_k_eq_v"))
+    nkv = int(d.get("num_key_value_heads") or d["num_attention_heads"])
+    gkv = int(d.get("num_global_key_value_heads") or nkv) if k_eq_v else nkv
+    shared_n = int(d.get("num_kv_shared_layers") or 0)
+    first_shared = nl - shared_n
+    shared_from = []
+    for i in range(nl):
+        if shared_n > 0 and i >= first_shared > 0:
+            prev = [j for j in range(first_shared) if lt[j] == lt[i]]
+            shared_from.append(prev[-1])
+        else:
+            shared_from.append(-1)
+    rp = d.get("rope_parameters") or {}
+    full = rp.get("full_attention") or {"rope_type": "proportional", "partial_rotary_factor": 0.25, "rope_theta": 1e6}
+    loc = rp.get("sliding_attention") or {"rope_type": "default", "rope_theta": 10000.0}
+    cfg = ModelConfig(
+        model_type="gemma4_text", vocab_size=int(d["vocab_size"]), hidden_size=int(d["hidden_size"]), num_layers=nl,
+        num_heads=int(d["num_attention_heads"]), num_kv_heads=nkv, head_dim=hd, intermediate_size=int(d["intermediate_size"]),
+        max_position_embeddings=int(d["max_position_embeddings"]), norm_eps=float(d["rms_norm_eps"]), rope_theta=float(full.get("rope_theta", 1e6)),
+        rope_factor=float(full.get("factor", 1.0)), rope_local_theta=float(loc.get("rope_theta", 10000.0)),
+        hidden_act=d.get("hidden_activation") or "gelu_pytorch_tanh", tie_word_embeddings=bool(d.get("tie_word_embeddings", True)),
+        bos_token_id=d.get("bos_token_id"), eos_token_ids=_eos(d.get("eos_token_id")), pad_token_id=d.get("pad_token_id"), qk_norm=True,
+        attn_scale=1.0, final_softcap=float(d.get("final_logit_softcapping") or 0.0), sliding_window=int(d.get("sliding_window") or 0),
+        layer_types=tuple("sliding" if "sliding" in t else "attention" for t in lt), embedding_multiplier=math.sqrt(float(d["hidden_size"])),
+        num_experts=int(d.get("num_experts") or 0) if d.get("enable_moe_block") else 0, experts_per_token=int(d.get("top_k_experts") or 0),
+        moe_intermediate_size=int(d.get("moe_intermediate_size") or d.get("expert_intermediate_size") or 0), raw=d,
+    )
+    cfg.extra = {
+        "head_dims": [hd if t == "sliding" else ghd for t in cfg.layer_types],
+        "kv_heads": [nkv if t == "sliding" else gkv for t in cfg.layer_types],
+        "k_eq_v": [k_eq_v and t != "sliding" for t in cfg.layer_types],
+        "shared_from": shared_from,
+        "double_wide": [bool(d.get("use_double_wide_mlp")) and s >= 0 for s in shared_from],
+        "rope_partial": float(full.get("partial_rotary_factor", 1.0)) if full.get("rope_type") == "proportional" else 1.0,
+        "ple_hidden": int(d.get("hidden_size_per_layer_input") or 0), "ple_vocab": int(d.get("vocab_size_per_layer_input") or 0),
+        "bidirectional": d.get("use_bidirectional_attention") == "all",
+    }
+    return cfg
+
+
 def _eos(v: Any) -> tuple[int, ...]:
     if v is None:
         return ()
@@ -147,6 +210,8 @@ def parse_config(d: dict) -> ModelConfig:
     mt = d.get("model_type")
     if mt not in SUPPORTED_MODEL_TYPES:
         raise ValueError(f"unsupported model_type '{mt}' (supported: {', '.join(SUPPORTED_MODEL_TYPES)})")
+    if mt in ("gemma4", "gemma4_text"):
+        return _parse_gemma4(d)
     if mt in ("gemma3", "gemma3_text"):
         # the multimodal wrapper nests the language model's fields; only the text tower is served
         outer, d = d, dict(_GEMMA3_TEXT_DEFAULTS)

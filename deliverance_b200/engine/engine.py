@@ -123,7 +123,8 @@ class Engine:
         self._graphs: dict[int, dict] = {}
         self.metrics = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "prefill_tokens": 0, "decode_tokens": 0,
                         "graph_replays": 0, "kernel_launches": 0}
-        self.use_graphs = bool(self.config.cuda_graphs and self.device.type == "cuda")
+        # (a family that runs on the PyTorch operator set reads lengths on the host inside its forward: not capturable)
+        self.use_graphs = bool(self.config.cuda_graphs and self.device.type == "cuda" and getattr(model, "supports_cuda_graphs", True))
         self.hybrid = mamba_shapes is not None
         # one-step lookahead of greedy graph decode: the step in flight whose sampled tokens the host has not read yet
         self._inflight: Optional[dict] = None

@@ -213,12 +213,19 @@ class PagedKVCache:
         kinds = layout["layer_kinds"]
         self.k: list[Optional[torch.Tensor]] = []
         self.v: list[Optional[torch.Tensor]] = []
-        shape = (num_pages, layout["kv_heads"], self.page_size, layout["head_dim"])
-        for kind in kinds:
+        # optional per-layer shapes and cache sharing (gemma4: wide global heads, late layers reuse an earlier layer's cache)
+        heads = layout.get("kv_heads_per_layer") or [layout["kv_heads"]] * len(kinds)
+        dims = layout.get("head_dim_per_layer") or [layout["head_dim"]] * len(kinds)
+        shared = layout.get("shared_from") or [-1] * len(kinds)
+        for i, kind in enumerate(kinds):
             if kind == "mamba":
                 self.k.append(None)
                 self.v.append(None)
+            elif shared[i] >= 0:
+                self.k.append(self.k[shared[i]])
+                self.v.append(self.v[shared[i]])
             else:
+                shape = (num_pages, heads[i], self.page_size, dims[i])
                 self.k.append(torch.zeros(shape, dtype=dtype, device=self.device))
                 self.v.append(torch.zeros(shape, dtype=dtype, device=self.device))
         self.allocator = PageAllocator(num_pages)
@@ -239,8 +246,12 @@ class PagedKVCache:
 
     @staticmethod
     def bytes_per_page(layout: dict, page_size: int, dtype) -> int:
-        n_attn = sum(1 for k in layout["layer_kinds"] if k != "mamba")
-        return 2 * n_attn * layout["kv_heads"] * page_size * layout["head_dim"] * torch.empty((), dtype=dtype).element_size()
+        kinds = layout["layer_kinds"]
+        heads = layout.get("kv_heads_per_layer") or [layout["kv_heads"]] * len(kinds)
+        dims = layout.get("head_dim_per_layer") or [layout["head_dim"]] * len(kinds)
+        shared = layout.get("shared_from") or [-1] * len(kinds)
+        rows = sum(heads[i] * dims[i] for i, k in enumerate(kinds) if k != "mamba" and shared[i] < 0)
+        return 2 * rows * page_size * torch.empty((), dtype=dtype).element_size()
 
     # -- per-sequence page management ---------------------------------------------------------------------------
     def ensure_pages(self, pages: list[int], n_tokens: int) -> None:
@@ -302,8 +313,9 @@ class PagedKVCache:
     def gather_rows(self, layer: int, pages: list[int], n_tokens: int):
         """Dense ``[KV, n_tokens, D]`` copies of K and V (tests, snapshots, debugging)."""
         idx = torch.tensor(pages[: (n_tokens + self.page_size - 1) // self.page_size], device=self.device, dtype=torch.long)
-        k = self.k[layer][idx].permute(1, 0, 2, 3).reshape(self.layout["kv_heads"], -1, self.layout["head_dim"])[:, :n_tokens]
-        v = self.v[layer][idx].permute(1, 0, 2, 3).reshape(self.layout["kv_heads"], -1, self.layout["head_dim"])[:, :n_tokens]
+        kh, hd = self.k[layer].shape[1], self.k[layer].shape[3]
+        k = self.k[layer][idx].permute(1, 0, 2, 3).reshape(kh, -1, hd)[:, :n_tokens]
+        v = self.v[layer][idx].permute(1, 0, 2, 3).reshape(kh, -1, hd)[:, :n_tokens]
         return k, v
 
 

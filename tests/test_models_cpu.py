@@ -109,3 +109,56 @@ def test_gemma3_multimodal_wrapper_config_and_prefix(tmp_path):
     a = _ours(str(d))[1].generate(PROMPT, GeneratorParameters(max_tokens=4)).token_ids
     b = _ours(str(plain))[1].generate(PROMPT, GeneratorParameters(max_tokens=4)).token_ids
     assert a == b
+
+
+@pytest.mark.parametrize("variant", ["base", "shared_kv", "k_eq_v", "moe", "no_ple_softcap"])
+def test_gemma4_matches_hf(tmp_path, variant):
+    """gemma4 text tower against transformers on random tiny checkpoints written by transformers itself (its own tensor
+    names): per-layer head shapes, proportional rotary embedding, per-layer inputs, shared KV layers with double-wide MLPs,
+    V = K global layers, the MoE block, final softcap."""
+    import json
+
+    from deliverance_b200.api import build_model
+    from deliverance_b200.config import parse_config
+
+    over = {"base": {}, "shared_kv": dict(num_kv_shared_layers=3, use_double_wide_mlp=True),
+            "k_eq_v": dict(attention_k_eq_v=True, num_global_key_value_heads=1),
+            "moe": dict(enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32),
+            "no_ple_softcap": dict(hidden_size_per_layer_input=0, final_logit_softcapping=30.0)}[variant]
+    kw = dict(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=6, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=32, global_head_dim=64, sliding_window=8, max_position_embeddings=256, vocab_size_per_layer_input=256,
+              hidden_size_per_layer_input=16, layer_types=["sliding_attention", "sliding_attention", "full_attention"] * 2)
+    kw.update(over)
+    torch.manual_seed(0)
+    hf = transformers.Gemma4ForCausalLM(transformers.Gemma4TextConfig(**kw)).eval().float()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.08)
+            else:
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+        for n, b in hf.named_buffers():
+            if n.endswith("layer_scalar"):
+                b.fill_(0.9)
+    d = str(tmp_path / "g4")
+    hf.save_pretrained(d, safe_serialization=True)
+    cfg = load_config(d)
+    assert cfg.model_type == "gemma4_text" and cfg.extra["head_dims"] == [32, 32, 64] * 2
+    m = build_model(cfg, "cpu", None, __import__("deliverance_b200.parallel.context", fromlist=["SINGLE"]).SINGLE).load(WeightLoader(d))
+    eng = Engine(m, EngineConfig(num_pages=64, max_batch_tokens=16))
+    got = eng.generate(PROMPT, GeneratorParameters(max_tokens=6)).token_ids
+    with torch.no_grad():
+        want = hf.generate(torch.tensor([PROMPT]), max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(PROMPT):].tolist()
+        ref_logits = hf(torch.tensor([PROMPT])).logits[0]
+    assert got == want
+    from deliverance_b200.models.batch import make_batch
+
+    kv = Engine(m, EngineConfig(num_pages=64, max_batch_tokens=4096)).kv
+    lg = m.forward(make_batch([{"tokens": PROMPT, "start": 0, "pages": [1, 2], "state_slot": 0}], 32, "cpu"), kv, all_rows=True)
+    if cfg.final_softcap:
+        lg = torch.tanh(lg / cfg.final_softcap) * cfg.final_softcap
+    assert torch.allclose(lg, ref_logits, atol=3e-4, rtol=1e-3)
+    if variant == "shared_kv":
+        assert kv.k[3] is kv.k[0] or kv.k[3] is kv.k[1] and kv.k[5] is kv.k[2] and m.layers[4].w["gate_proj"].shape[0] == 256
+        nested = parse_config({"model_type": "gemma4", "text_config": json.load(open(d + "/config.json")), "eos_token_id": [1, 106]})
+        assert nested.extra["shared_from"] == cfg.extra["shared_from"] == [-1, -1, -1, 1, 1, 2] and nested.eos_token_ids == (1, 106)
