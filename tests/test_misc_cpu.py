@@ -574,3 +574,26 @@ def test_tokenizer_benchmark_and_upload_plan(tmp_path, capsys):
         upload.plan(d)
     open(os.path.join(d, ".finished"), "w").close()
     assert "deliverance-quantization.json" in [p for p, _ in upload.plan(d)] and ".finished" not in [p for p, _ in upload.plan(d)]
+
+
+def test_model_support_facade(tmp_path):
+    from deliverance_b200 import model_support as ms
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+
+    d, b = str(tmp_path / "llama"), str(tmp_path / "bert")
+    write_tiny_model(d, "llama", seed=1)
+    write_tiny_model(b, "bert", seed=2)
+    assert ms.detect_model(d) == "llama" and ms.detect_model(os.path.join(b, "config.json")) == "bert"
+    t = ms.InferenceType
+    assert t.parse("generation") is t.FULL_GENERATION and t.parse("FULL_EMBEDDING").is_pooling and not t.FORWARD_PASS.is_output
+    assert t.FULL_CLASSIFICATION.is_classify and t.OUTPUT_TO_TOKEN.is_output and not t.OUTPUT_TO_TOKEN.is_input
+    clm = ms.load_model(d, device="cpu")
+    assert clm.generate([3, 4, 5], None).generated_tokens > 0
+    emb = ms.load_model(b, t.FULL_EMBEDDING, device="cpu")
+    assert len(emb.embed("hello world")) == 64
+    assert len(ms.load_model(d, t.FULL_EMBEDDING, device="cpu").embed("decoder as embedder")) == 64
+    ms.add_model("llama", lambda model_dir, it, device, **kw: ("custom", it))
+    try:
+        assert ms.load_model(d, t.FORWARD_PASS) == ("custom", t.FORWARD_PASS)
+    finally:
+        ms._REGISTRY.clear()
