@@ -10,6 +10,7 @@ reasoning, finish reason, token counts, timings, tool calls) and its stop order.
 from __future__ import annotations
 
 import json
+import logging
 import os
 import uuid
 from dataclasses import dataclass, field
@@ -34,6 +35,9 @@ from .prompt.chat import PromptBuilder, PromptContext
 from .prompt.parsers import (Gemma4ToolCallParser, ReasoningTextSplitter, StopStringDetector, ToolCallParser, parse_gemma4_response,
                              parser_for_model, prompt_ends_inside_reasoning, split_reasoning)
 from .tokenizer.auto import AutoTokenizer, IncrementalDetokenizer
+
+
+_log = logging.getLogger("deliverance_b200.generation")
 
 
 @dataclass
@@ -238,6 +242,12 @@ class Generation:
                     text = text[: i + (len(s) if self.params.include_stop_str_in_output else 0)]
                     break
         r.text_with_special_tokens = text_sp
+        if _log.isEnabledFor(logging.INFO):
+            # per-request lines in the reference's wording (core/.../model/GenerationEngine.java:131-132, 259-266)
+            n, dt = r.generated_tokens, max(r.total_ms - r.ttft_ms, 1e-6)
+            _log.info("time_to_first_token=%.1f ms prefix_length=%d", r.ttft_ms, r.prefix_hit_tokens)
+            _log.info("generation_complete prompt_tokens=%d generated_tokens=%d total_ms=%.1f tokens_per_second=%.2f decode_tokens_per_second=%.2f finish=%s",
+                      r.prompt_tokens, n, r.total_ms, n / max(r.total_ms, 1e-6) * 1e3, max(n - 1, 0) / dt * 1e3, r.finish_reason.name)
         if isinstance(self.clm.tool_parser, Gemma4ToolCallParser):  # gemma-4 marks its thought channel with special tokens
             content, reasoning = parse_gemma4_response(text_sp, text)
         else:

@@ -497,7 +497,8 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
 
         eng_keys = (("steps", "engine steps"), ("prefill_steps", "prefill steps"), ("decode_steps", "decode steps"),
                     ("prefill_tokens", "prompt tokens computed"), ("decode_tokens", "tokens generated by decode steps"),
-                    ("graph_replays", "CUDA graph replays"), ("kernel_launches", "kernels of the extension launched"))
+                    ("graph_replays", "CUDA graph replays"), ("kernel_launches", "kernels of the extension launched"),
+                    ("preemptions", "sequences preempted under KV memory pressure"))
         for key, text in eng_keys:
             emit(f"deliverance_engine_{key}_total", "counter", text,
                  [({"model": n}, r.clm.engine.metrics.get(key, 0)) for n, r in registry.generation.items()])
