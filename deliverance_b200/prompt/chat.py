@@ -147,16 +147,57 @@ class PromptBuilder:
         self.kwargs.update(kwargs or {})
         return self
 
+    def continue_final_message(self, on: bool = True) -> "PromptBuilder":
+        """Render so that the model continues the last message instead of starting a new turn (a prefilled assistant reply):
+        no generation prompt, and the rendered text is cut right after the last message's content."""
+        self._continue_final = on
+        return self
+
+    def _select_template(self) -> Optional[str]:
+        """A tokenizer may carry several named templates (a dict, or a list of ``{"name", "template"}``): ``tool_use`` is taken
+        when tools are present and it exists, otherwise ``default``; a ``template_name`` kwarg picks one by name."""
+        t = self.template
+        if isinstance(t, list):
+            t = {e["name"]: e["template"] for e in t if isinstance(e, dict) and "name" in e and "template" in e}
+        if isinstance(t, dict):
+            name = self.kwargs.get("template_name")
+            if name is not None:
+                if name not in t:
+                    raise ValueError(f"chat template '{name}' not found (available: {', '.join(sorted(t))})")
+                return t[name]
+            if self.tools and "tool_use" in t:
+                return t["tool_use"]
+            if "default" in t:
+                return t["default"]
+            raise ValueError(f"no default chat template among: {', '.join(sorted(t))}")
+        return t
+
     def build(self) -> PromptContext:
         if not self.messages:
             raise ValueError("a prompt needs at least one message")
-        if self.template:
-            variables = {"messages": self.messages, "add_generation_prompt": self.add_generation_prompt,
-                         "bos_token": self.bos_token, "eos_token": self.eos_token}
+        cont = getattr(self, "_continue_final", False)
+        gen = self.add_generation_prompt and not cont
+        template = self._select_template()
+        if template:
+            variables = {"messages": self.messages, "add_generation_prompt": gen, "bos_token": self.bos_token, "eos_token": self.eos_token}
             if self.tools:
                 variables["tools"] = self.tools
-            variables.update(self.kwargs)
-            text = _jinja_env().from_string(self.template).render(**variables)
+            variables.update({k: v for k, v in self.kwargs.items() if k != "template_name"})
+            text = _jinja_env().from_string(template).render(**variables)
         else:
-            text = render_chatml(self.messages, self.tools, self.add_generation_prompt, self.kwargs.get("enable_thinking"))
+            text = render_chatml(self.messages, self.tools, gen, self.kwargs.get("enable_thinking"))
+        if cont:
+            final = self.messages[-1].get("content") or ""
+            if isinstance(final, list):  # text parts: the last text part is what gets continued
+                final = next((p.get("text", "") for p in reversed(final) if isinstance(p, dict) and p.get("type", "text") == "text"), "")
+            final = final.strip()
+            i = text.rfind(final) if final else -1
+            if i < 0:
+                raise ValueError("continue_final_message: the final message does not appear in the rendered chat (does the template "
+                                 "rewrite message contents?)")
+            # keep the message's own trailing whitespace when the template kept it, drop what the template adds after it
+            end = i + len(final)
+            raw = self.messages[-1].get("content") if isinstance(self.messages[-1].get("content"), str) else final
+            tail = raw[len(raw.rstrip()):]
+            text = text[:end] + (tail if text[end:end + len(tail)] == tail else "")
         return PromptContext(text, bool(self.tools))

@@ -97,6 +97,10 @@ def map_chat_request(body: dict, runner: EngineRunner):
         else:
             raise ValueError(f"unsupported message role '{role}'")
     b.add_tools(select_tools(body))
+    if body.get("add_generation_prompt") is False:
+        b.add_generation_prompt = False
+    if body.get("continue_final_message"):  # the model continues the last (assistant) message instead of opening a new turn
+        b.continue_final_message()
     return b.build(), map_params(body)
 
 

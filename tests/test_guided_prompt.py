@@ -184,3 +184,32 @@ def test_gemma4_response_channels_reference_vectors():
         c, r = c + dc, r + dr
     dc, dr = sp.flush()
     assert (c + dc, r + dr) == ("Answer", "why not")
+
+
+def test_hf_common_chat_template_behaviours():
+    """The chat-template tests of transformers' common tokenizer suite that the reference ports (dummy template, raise_exception)
+    and the ones it lists as unsupported there: loop controls, strftime_now, named template selection, continue_final_message."""
+    import datetime
+
+    dummy = "{% for message in messages %}{{message['role'] + message['content']}}{% endfor %}"
+    p = PromptBuilder(dummy).add_system("system message").add_user("user message").add_assistant("assistant message").build().prompt
+    assert p == "systemsystem messageuseruser messageassistantassistant message"
+    with pytest.raises(Exception):
+        PromptBuilder("{{ raise_exception('bad role') }}").add_user("hi").build()
+    loop = "{%- for message in messages %}{%- if message.role == 'user' %}{{ message.content }}{%- break %}{%- endif %}{%- endfor %}"
+    assert PromptBuilder(loop).add_system("s").add_user("first").add_user("second").build().prompt == "first"
+    assert PromptBuilder("{{ strftime_now('%Y-%m-%d') }}").add_user("x").build().prompt == datetime.date.today().strftime("%Y-%m-%d")
+    named = {"default": "D:{{ messages[0].content }}", "tool_use": "T:{{ messages[0].content }}", "rag": "R:{{ messages[0].content }}"}
+    assert PromptBuilder(named).add_user("q").build().prompt == "D:q"
+    assert PromptBuilder(named).add_user("q").add_tools([{"type": "function", "function": {"name": "f"}}]).build().prompt == "T:q"
+    assert PromptBuilder([{"name": k, "template": v} for k, v in named.items()]).add_user("q").with_kwargs({"template_name": "rag"}).build().prompt == "R:q"
+    with pytest.raises(ValueError):
+        PromptBuilder(named).add_user("q").with_kwargs({"template_name": "nope"}).build()
+    tpl = "{% for m in messages %}<|{{ m.role }}|>{{ m.content }}<|end|>\n{% endfor %}{% if add_generation_prompt %}<|assistant|>{% endif %}"
+    b = PromptBuilder(tpl).add_user("hi").add_assistant('{"name": "')
+    assert b.build().prompt.endswith('<|assistant|>{"name": "<|end|>\n<|assistant|>')
+    assert b.continue_final_message().build().prompt == '<|user|>hi<|end|>\n<|assistant|>{"name": "'
+    # an earlier message with the same text is not the cut point
+    c = PromptBuilder(tpl).add_user("hi!").add_assistant("hi!").add_user("again").add_assistant("hi!").continue_final_message().build().prompt
+    assert c == "<|user|>hi!<|end|>\n<|assistant|>hi!<|end|>\n<|user|>again<|end|>\n<|assistant|>hi!"
+    assert PromptBuilder().add_user("q").add_assistant("The answer is").continue_final_message().build().prompt.endswith("<|im_start|>assistant\nThe answer is")

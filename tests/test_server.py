@@ -151,6 +151,12 @@ def test_openai_compat_fields(registry):
     assert json.loads(r.json()["choices"][0]["message"]["content"]) in ({"ok": True}, {"ok": False})
     r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "tools": tools, "tool_choice": {"function": {"name": "zz"}}})
     assert r.status_code == 400
+    from deliverance_b200.server.app import map_chat_request
+
+    runner = next(iter(registry.generation.values()))
+    body = {"messages": [{"role": "user", "content": "q"}, {"role": "assistant", "content": "The answer"}], "continue_final_message": True}
+    assert map_chat_request(body, runner)[0].prompt.endswith("The answer")
+    assert not map_chat_request({"messages": body["messages"][:1], "add_generation_prompt": False}, runner)[0].prompt.endswith("assistant\n")
 
 
 def test_malformed_requests_are_400(registry):
