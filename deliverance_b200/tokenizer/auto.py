@@ -116,6 +116,106 @@ class ByteTokenizer:
         return "".join(parts)
 
 
+class SentencePieceBackend:
+    """``tokenizer.model`` (SentencePiece) behind the backend interface of the ``tokenizers`` runtime."""
+
+    def __init__(self, path: str):
+        import sentencepiece as spm
+
+        self.sp = spm.SentencePieceProcessor(model_file=path)
+
+    def token_to_id(self, t):
+        i = self.sp.piece_to_id(t)
+        return i if self.sp.id_to_piece(i) == t else None
+
+    def id_to_token(self, i):
+        return self.sp.id_to_piece(int(i)) if 0 <= int(i) < self.sp.get_piece_size() else None
+
+    def get_vocab_size(self, with_added_tokens=True):
+        return self.sp.get_piece_size()
+
+    def encode(self, text, add_special_tokens=False):
+        ids = self.sp.encode(text)
+        if add_special_tokens and self.sp.bos_id() >= 0:
+            ids = [self.sp.bos_id()] + ids
+
+        class _E:
+            pass
+
+        e = _E()
+        e.ids = ids
+        return e
+
+    def decode(self, ids, skip_special_tokens=False):
+        ids = [int(i) for i in ids]
+        if skip_special_tokens:
+            ids = [i for i in ids if not self.sp.is_control(i)]
+            return self.sp.decode(ids)
+        out, run = [], []
+        for i in ids:  # control pieces (<s>, </s>) are dropped by the library's decode: spell them out
+            if self.sp.is_control(i):
+                out.append(self.sp.decode(run))
+                out.append(self.sp.id_to_piece(i))
+                run = []
+            else:
+                run.append(i)
+        out.append(self.sp.decode(run))
+        return "".join(out)
+
+
+def _legacy_backend(model_dir: str, config: dict):
+    """Tokenizer files older than ``tokenizer.json``: SentencePiece ``tokenizer.model`` (llama / mistral / gemma families),
+    ``vocab.json`` + ``merges.txt`` (byte-level BPE: gpt2, qwen2), ``vocab.txt`` (BERT WordPiece). Returns (backend, specials)
+    or None (reference families: grace/.../AutoTokenizer.java:49-69, 218-230)."""
+    p = lambda n: os.path.join(model_dir, n)  # noqa: E731
+    if os.path.exists(p("tokenizer.model")):
+        tk = SentencePieceBackend(p("tokenizer.model"))
+        special = {tk.sp.id_to_piece(i): i for i in range(tk.sp.get_piece_size()) if tk.sp.is_control(i)}
+        if tk.sp.bos_id() >= 0:
+            config.setdefault("bos_token", tk.sp.id_to_piece(tk.sp.bos_id()))
+        if tk.sp.eos_id() >= 0:
+            config.setdefault("eos_token", tk.sp.id_to_piece(tk.sp.eos_id()))
+        return tk, special
+    if os.path.exists(p("vocab.json")) and os.path.exists(p("merges.txt")):
+        from tokenizers import Tokenizer, decoders, models, pre_tokenizers
+
+        tk = Tokenizer(models.BPE.from_file(p("vocab.json"), p("merges.txt")))
+        tk.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=bool(config.get("add_prefix_space", False)))
+        tk.decoder = decoders.ByteLevel()
+        special = {}
+        for name in ("bos_token", "eos_token", "unk_token", "pad_token"):
+            t = _tok_str(config.get(name)) or ("<|endoftext|>" if name != "pad_token" else None)
+            if t and tk.token_to_id(t) is not None:
+                special[t] = tk.token_to_id(t)
+                config.setdefault(name, t)
+        if special:
+            from tokenizers import AddedToken
+
+            tk.add_special_tokens([AddedToken(t, special=True) for t in special])
+        return tk, special
+    if os.path.exists(p("vocab.txt")):
+        from tokenizers import Tokenizer, decoders, models, normalizers, pre_tokenizers, processors
+
+        with open(p("vocab.txt"), encoding="utf-8") as f:
+            vocab = {line.rstrip("\n"): i for i, line in enumerate(f)}
+        unk = _tok_str(config.get("unk_token")) or "[UNK]"
+        tk = Tokenizer(models.WordPiece(vocab, unk_token=unk))
+        tk.normalizer = normalizers.BertNormalizer(lowercase=bool(config.get("do_lower_case", True)))
+        tk.pre_tokenizer = pre_tokenizers.BertPreTokenizer()
+        tk.decoder = decoders.WordPiece()
+        cls, sep = _tok_str(config.get("cls_token")) or "[CLS]", _tok_str(config.get("sep_token")) or "[SEP]"
+        if cls in vocab and sep in vocab:
+            tk.post_processor = processors.TemplateProcessing(single=f"{cls} $A {sep}", pair=f"{cls} $A {sep} $B:1 {sep}:1",
+                                                              special_tokens=[(cls, vocab[cls]), (sep, vocab[sep])])
+        special = {t: vocab[t] for t in (cls, sep, unk, "[PAD]", "[MASK]") if t in vocab}
+        from tokenizers import AddedToken
+
+        tk.add_special_tokens([AddedToken(t, special=True) for t in special])
+        config.setdefault("pad_token", "[PAD]")
+        return tk, special
+    return None
+
+
 class AutoTokenizer:
     @staticmethod
     def from_pretrained(model_dir: str) -> PreTrainedTokenizer:
@@ -135,6 +235,8 @@ class AutoTokenizer:
             for a in raw.get("added_tokens", []):
                 if a.get("special"):
                     special[a["content"]] = a["id"]
+        elif (legacy := _legacy_backend(model_dir, config)) is not None:
+            tk, special = legacy
         else:
             vocab = 260
             mc = os.path.join(model_dir, "config.json")

@@ -597,3 +597,49 @@ def test_model_support_facade(tmp_path):
         assert ms.load_model(d, t.FORWARD_PASS) == ("custom", t.FORWARD_PASS)
     finally:
         ms._REGISTRY.clear()
+
+
+def test_legacy_tokenizer_file_layouts(tmp_path):
+    """Tokenizer directories without tokenizer.json: SentencePiece model, GPT-2 style vocab.json + merges.txt, BERT vocab.txt;
+    each must agree with the transformers tokenizer of the same files."""
+    import sentencepiece as spm
+
+    from deliverance_b200.tokenizer.auto import AutoTokenizer, IncrementalDetokenizer
+
+    text = "Hello world, hello tokenizers! The quick brown fox."
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("\n".join([text, "the quick brown fox jumps over the lazy dog", "hello hello world world tokenizers are quick"] * 20))
+    sp_dir = tmp_path / "sp"
+    sp_dir.mkdir()
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(sp_dir / "tokenizer"), vocab_size=60, model_type="bpe",
+                                   bos_id=1, eos_id=2, unk_id=0, minloglevel=2)
+    tok = AutoTokenizer.from_pretrained(str(sp_dir))
+    ref = spm.SentencePieceProcessor(model_file=str(sp_dir / "tokenizer.model"))
+    ids = tok.encode(text)
+    assert ids == ref.encode(text) and tok.decode(ids) == ref.decode(ids) and (tok.bos_token, tok.eos_token) == ("<s>", "</s>")
+    assert tok.bos_token_id == 1 and tok.is_special(2) and tok.decode([1] + ids[:3] + [2]).startswith("<s>") and tok.encode(text, add_special_tokens=True)[0] == 1
+    det = IncrementalDetokenizer(tok, skip_special=True)
+    assert "".join(det.push(i) for i in ids) == tok.decode(ids, skip_special_tokens=True)
+
+    bpe_dir = tmp_path / "bpe"
+    bpe_dir.mkdir()
+    from tokenizers import ByteLevelBPETokenizer
+
+    t = ByteLevelBPETokenizer()
+    t.train([str(corpus)], vocab_size=300, min_frequency=1, special_tokens=["<|endoftext|>"])
+    t.save_model(str(bpe_dir))
+    tok = AutoTokenizer.from_pretrained(str(bpe_dir))
+    hf = ByteLevelBPETokenizer(str(bpe_dir / "vocab.json"), str(bpe_dir / "merges.txt"))
+    ids = tok.encode(text + " Ünïcödé")
+    assert ids == hf.encode(text + " Ünïcödé").ids and tok.decode(ids) == text + " Ünïcödé" and tok.eos_token == "<|endoftext|>" and tok.is_special(tok.eos_token_id)
+
+    wp_dir = tmp_path / "wp"
+    wp_dir.mkdir()
+    words = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]", "hello", "world", "the", "quick", "brown", "fox", "token", "##izer", "##s", ",", "!", "."]
+    (wp_dir / "vocab.txt").write_text("\n".join(words) + "\n")
+    tok = AutoTokenizer.from_pretrained(str(wp_dir))
+    from tokenizers import BertWordPieceTokenizer
+
+    hf = BertWordPieceTokenizer(str(wp_dir / "vocab.txt"))
+    assert tok.encode(text, add_special_tokens=True) == hf.encode(text).ids and tok.encode(text) == hf.encode(text, add_special_tokens=False).ids
+    assert tok.decode(tok.encode("hello tokenizers")) == "hello tokenizers" and tok.pad_token == "[PAD]"
