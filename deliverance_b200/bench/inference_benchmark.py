@@ -39,7 +39,9 @@ COLUMNS = ["engine", "model", "case_id", "category", "turn", "prompt_chars", "pr
 
 
 def load_suite(path):
-    """MT-Bench style JSONL: one object per line with ``question_id``, ``category`` and ``turns`` (list of user messages)."""
+    """MT-Bench style JSONL: one object per line with ``question_id``, ``category`` and ``turns`` (list of user messages);
+    a line may carry ``guided_choice`` / ``guided_regex`` / ``guided_json`` (the reference's guided support suite), applied to
+    every turn of the case."""
     import json
 
     suite = []
@@ -47,7 +49,8 @@ def load_suite(path):
         for line in f:
             if line.strip():
                 q = json.loads(line)
-                suite.append((str(q.get("question_id", len(suite))), q.get("category", ""), list(q["turns"])))
+                guided = {k: q[k] for k in ("guided_choice", "guided_regex", "guided_json") if q.get(k) is not None}
+                suite.append((str(q.get("question_id", len(suite))), q.get("category", ""), list(q["turns"]), guided))
     return suite
 
 
@@ -133,7 +136,9 @@ def main() -> int:
                 record(f"synthetic-{i}", "synthetic", 1, 0, r, (time.perf_counter() - t0) * 1e3)
             continue
         suite = load_suite(a.questions) if a.questions else DEFAULT_SUITE
-        for case_id, category, turns in suite:
+        for case in suite:
+            case_id, category, turns = case[:3]
+            guided = case[3] if len(case) > 3 else {}
             messages = []
             for ti, user in enumerate(turns, 1):
                 messages.append({"role": "user", "content": user})
@@ -142,7 +147,7 @@ def main() -> int:
                     pb = pb.add_user(m["content"]) if m["role"] == "user" else pb.add_assistant(m["content"])
                 ctx = pb.build()
                 t0 = time.perf_counter()
-                r = clm.generate(ctx, GeneratorParameters(max_tokens=a.max_tokens, temperature=a.temperature))
+                r = clm.generate(ctx, GeneratorParameters(max_tokens=a.max_tokens, temperature=a.temperature, **guided))
                 total = (time.perf_counter() - t0) * 1e3
                 record(case_id, category, ti, len(ctx.prompt), r, total,
                        {"messages": list(messages), "rendered_prompt": ctx.prompt, "response_text": r.text,

@@ -643,3 +643,73 @@ def test_legacy_tokenizer_file_layouts(tmp_path):
     hf = BertWordPieceTokenizer(str(wp_dir / "vocab.txt"))
     assert tok.encode(text, add_special_tokens=True) == hf.encode(text).ids and tok.encode(text) == hf.encode(text, add_special_tokens=False).ids
     assert tok.decode(tok.encode("hello tokenizers")) == "hello tokenizers" and tok.pad_token == "[PAD]"
+
+
+GUIDED_SUITE = [
+    {"question_id": "guided-choice-nfl", "category": "guided_choice", "turns": ["Choose the better New York NFL football team."], "guided_choice": ["Giants", "Jets"]},
+    {"question_id": "guided-regex-ticket", "category": "guided_regex", "turns": ["Create a support ticket identifier."], "guided_regex": "TICKET-[0-9]{4}"},
+    {"question_id": "guided-regex-routing", "category": "guided_regex", "turns": ["Route a pet insurance request."], "guided_regex": "(cats|dogs|birds|fish)"},
+    {"question_id": "guided-json-person", "category": "guided_json", "turns": ["Alice is 42 years old and lives in Paris."],
+     "guided_json": {"type": "object", "properties": {"name": {"const": "Alice"}, "age": {"type": "integer"}, "city": {"const": "Paris"}},
+                     "required": ["name", "age", "city"], "additionalProperties": False}},
+    {"question_id": "guided-json-polymorphic-pet", "category": "guided_json", "turns": ["A vaccinated seven year old dog named Rex."],
+     "guided_json": {"oneOf": [
+         {"type": "object", "properties": {"kind": {"const": "cat"}, "name": {"const": "Misty"}, "lives_left": {"type": "integer"}}},
+         {"type": "object", "properties": {"kind": {"const": "dog"}, "name": {"const": "Rex"}, "vaccinated": {"type": "boolean"}, "age": {"type": "integer"}}}]}},
+    {"question_id": "guided-json-incident-report", "category": "guided_json", "turns": ["API latency was high in us-east."],
+     "guided_json": {"type": "object", "properties": {
+         "service": {"const": "api"}, "region": {"const": "us-east"}, "severity": {"enum": ["low", "medium", "high"]}, "impacted_users": {"type": "integer"},
+         "mitigated": {"type": "boolean"}, "actions": {"type": "array", "items": {"enum": ["rollback", "scale_up", "restart", "notify"]}, "maxItems": 3}}}},
+]
+
+
+def test_guided_support_suite_through_the_benchmark(tmp_path):
+    """The six cases of the reference's guided support suite (choice, two regexes, three JSON schemas incl. oneOf and an enum
+    array), run through the single-request benchmark CLI on a tiny random model: every response must satisfy its constraint."""
+    import csv
+    import re
+    import sys
+
+    from deliverance_b200.bench import inference_benchmark as ib
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=3, std=0.08, max_position_embeddings=1024)
+    q = tmp_path / "suite.jsonl"
+    q.write_text("\n".join(json.dumps(c) for c in GUIDED_SUITE) + "\n")
+    assert [c[3] for c in ib.load_suite(str(q))][1] == {"guided_regex": "TICKET-[0-9]{4}"}
+    out, jl = tmp_path / "out.csv", tmp_path / "out.jsonl"
+    argv = sys.argv
+    sys.argv = ["x", "--model", d, "--questions", str(q), "--max-tokens", "120", "--out", str(out), "--jsonl-output", str(jl), "--device", "cpu"]
+    try:
+        assert ib.main() == 0
+    finally:
+        sys.argv = argv
+    rows = list(csv.DictReader(open(out)))
+    texts = {json.loads(l)["case_id"]: json.loads(l)["response_text"] for l in open(jl)}
+    assert [r["case_id"] for r in rows] == [c["question_id"] for c in GUIDED_SUITE]
+    assert texts["guided-choice-nfl"] in ("Giants", "Jets") and re.fullmatch("TICKET-[0-9]{4}", texts["guided-regex-ticket"])
+    assert texts["guided-regex-routing"] in ("cats", "dogs", "birds", "fish")
+    from deliverance_b200.guided.index import RegexDFA
+    from deliverance_b200.guided.json_schema import schema_to_regex
+
+    finish = {r["case_id"]: r["finish_reason"] for r in rows}
+    for case in GUIDED_SUITE[3:]:
+        # a random model may write digits of an unbounded integer until max_tokens: then the text must still be a prefix the
+        # schema's automaton accepts so far; a finished reply must parse and match
+        cid, text = case["question_id"], texts[case["question_id"]]
+        dfa = RegexDFA(schema_to_regex(case["guided_json"]))
+        state, live = dfa.initial, dfa.live_states()
+        for ch in text:
+            state = dfa.step(state, ch)
+            assert state is not None and state in live, (cid, text)
+        if finish[cid] != "length":
+            assert state in dfa.finals, (cid, text)
+            obj = json.loads(text)
+            if cid == "guided-json-person":
+                assert list(obj) == ["name", "age", "city"] and obj["name"] == "Alice" and isinstance(obj["age"], int)
+            elif cid == "guided-json-polymorphic-pet":
+                assert (obj["kind"], obj["name"]) in (("cat", "Misty"), ("dog", "Rex"))
+            else:
+                assert obj["severity"] in ("low", "medium", "high") and set(obj["actions"]) <= {"rollback", "scale_up", "restart", "notify"}
+    assert texts["guided-json-person"].startswith('{"name":"Alice","age":')
