@@ -328,6 +328,51 @@ class AutoModelForCausalLM:
             self.name = name
             return self
 
+        def with_tensor_parallel_collectives(self, collectives):
+            """Collectives of an already configured rank / size (reference: withTensorParallelCollectives)."""
+            self.tp = TensorParallelContext(self.tp.rank, self.tp.size, collectives)
+            return self
+
+        def with_download(self, on: bool = True, home: Optional[str] = None):
+            """Treat the model argument as ``owner/name`` and fetch it into the local model cache when it is not there yet
+            (reference: withDownload + ModelFetcher; needs network access, a directory that exists is used as it is)."""
+            self._download, self._download_home = on, home
+            return self
+
+        def _accept(self, key: str, value):
+            """Builder switches of the reference's CPU / WebGPU runtime that select code paths this runtime does not have
+            (there is one CUDA path): accepted so that ported code keeps working, recorded for diagnostics."""
+            self.conf.ignored = tuple(self.conf.ignored) + (f"{key}={value}",)
+            return self
+
+        def with_working_quant_type(self, dtype):  # activations stay bf16; int8 block activations are a CPU-kernel input format
+            return self._accept("workingQuantType", dtype)
+
+        def with_tensor_provider(self, provider):
+            return self._accept("tensorProvider", getattr(provider, "__name__", provider))
+
+        def with_parallel_settings(self, settings):  # gossip membership: ranks are fixed at launch on one node
+            return self._accept("parallelSettings", settings)
+
+        def with_gpu_prefill(self, on: bool = True):
+            return self._accept("gpuPrefill", on)
+
+        def with_gpu_decode(self, on: bool = True):
+            return self._accept("gpuDecode", on)
+
+        def with_gpu_decode_attention(self, on: bool = True):
+            return self._accept("gpuDecodeAttention", on)
+
+        def with_packed_prefill(self, on: bool = True):
+            return self._accept("packedPrefill", on)
+
+        def with_tensor_runtime_mode(self, mode):
+            return self._accept("tensorRuntimeMode", mode)
+
+        def with_tensor_plan_trace(self, on: bool = True):
+            """The reference prints its tensor plan per generation; the counterpart here is the stage profiler's report."""
+            return self.with_profile_stages(on) if on else self
+
         def with_layer_debug_hook(self, hook):
             self.layer_hook = hook
             return self
@@ -340,6 +385,11 @@ class AutoModelForCausalLM:
             """Weights + model graph only (no engine, no tokenizer)."""
             conf = self.conf
             model_dir = self.model_dir
+            if getattr(self, "_download", False) and not os.path.isdir(model_dir):
+                from .ckpt.fetch import ModelFetcher
+
+                kw = {"home": self._download_home} if self._download_home else {}
+                model_dir = ModelFetcher.from_id(model_dir, **kw).maybe_download()
             if conf.quantize_on_demand:
                 cache_root = os.path.expanduser(os.environ.get("DELIVERANCE_HOME", "~/.deliverance"))
                 target = os.path.join(cache_root, os.path.basename(os.path.normpath(model_dir)) + "-JQ4")

@@ -713,3 +713,25 @@ def test_guided_support_suite_through_the_benchmark(tmp_path):
             else:
                 assert obj["severity"] in ("low", "medium", "high") and set(obj["actions"]) <= {"rollback", "scale_up", "restart", "notify"}
     assert texts["guided-json-person"].startswith('{"name":"Alice","age":')
+
+
+def test_builder_reference_methods_and_download_cache(tmp_path):
+    """Builder methods of the reference that have no separate code path here are accepted and recorded; with_download resolves
+    ``owner/name`` through the local model cache (a finished cache directory needs no network)."""
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.params import GeneratorParameters
+
+    home = tmp_path / "home"
+    d = home / "acme_tiny-llama"
+    write_tiny_model(str(d), "llama", seed=1)
+    (d / ".finished").write_text("")
+    b = (AutoModelForCausalLM.new_builder("acme/tiny-llama").with_device("cpu").with_download(True, str(home)).with_working_quant_type("I8")
+         .with_gpu_prefill(True).with_gpu_decode(False).with_gpu_decode_attention(True).with_packed_prefill(True).with_tensor_runtime_mode("ENFORCE")
+         .with_tensor_provider("simd").with_parallel_settings(None).with_tensor_plan_trace(False))
+    clm = b.build()
+    assert clm.name == "acme_tiny-llama" and clm.generate([3, 4, 5], GeneratorParameters(max_tokens=2)).generated_tokens == 2
+    assert "workingQuantType=I8" in b.conf.ignored and "gpuDecode=False" in b.conf.ignored and len(b.conf.ignored) == 8
+    assert AutoModelForCausalLM.new_builder(str(d)).with_tensor_plan_trace(True).conf.profile_stages
+    with pytest.raises(ValueError):
+        AutoModelForCausalLM.new_builder("no-slash").with_download().with_device("cpu").build()
