@@ -117,6 +117,27 @@ class PrefixCache:
         self.metrics = {"lookup": 0, "hits": 0, "misses": 0, "evict": 0, "stored": 0, "hit_tokens": 0}
         self.disk = None  # optional second tier (kv.disk.DiskPrefixStore), attached by PagedKVCache.attach_disk
         self.kv = None
+        self.held: dict = {}  # page -> number of cache entries that hold a reference to it
+
+    def _count(self, pages: list, d: int) -> None:
+        held = self.held
+        for p in pages:
+            n = held.get(p, 0) + d
+            if n > 0:
+                held[p] = n
+            else:
+                held.pop(p, None)
+
+    def reclaimable(self, want: int) -> int:
+        """How many pages (counted up to ``want``) evicting cache entries would really free: pages that nothing but cache
+        entries hold (entries of several checkpoint lengths share pages; running sequences that hit the cache hold them too)."""
+        ref, n = self.alloc.ref, 0
+        for p, c in self.held.items():
+            if ref[p] == c:
+                n += 1
+                if n >= want:
+                    break
+        return n
 
     @staticmethod
     def key(salt: str, tokens: list[int]) -> bytes:
@@ -148,6 +169,7 @@ class PrefixCache:
                     if got is not None:
                         best = PrefixEntry(got[0], got[1], None)
                         self.entries[k] = best  # the entry owns the references taken by load()
+                        self._count(best.pages, +1)
                         break
         if best is None:
             self.metrics["misses"] += 1
@@ -175,6 +197,7 @@ class PrefixCache:
             for p in chain:
                 self.alloc.retain(p)
             self.entries[k] = PrefixEntry(list(chain), L, None if state_at is None else state_at[L])
+            self._count(chain, +1)
             added += 1
             self.metrics["stored"] += 1
         while len(self.entries) > self.settings.max_entries:
@@ -187,6 +210,7 @@ class PrefixCache:
         k, e = self.entries.popitem(last=False)
         if self.disk is not None and e.state is None and not self.disk.has(k):
             self.disk.save(self.kv, k, e.pages, e.length)  # spill before the pages go back to the allocator
+        self._count(e.pages, -1)
         for p in e.pages:
             self.alloc.release(p)
         self.metrics["evict"] += 1
@@ -273,14 +297,7 @@ class PagedKVCache:
         a cached page comes back only if nothing but cache entries holds it (entries of several checkpoint lengths share
         pages, and running sequences that hit the cache hold references too)."""
         free = self.allocator.available()
-        if free >= n_pages:
-            return True
-        held: dict = {}
-        for e in self.prefix.entries.values():
-            for p in e.pages:
-                held[p] = held.get(p, 0) + 1
-        ref = self.allocator.ref
-        return free + sum(1 for p, c in held.items() if ref[p] == c) >= n_pages
+        return free >= n_pages or free + self.prefix.reclaimable(n_pages - free) >= n_pages
 
     def alloc_state_slot(self) -> int:
         if not self.free_slots:

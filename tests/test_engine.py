@@ -422,3 +422,27 @@ def test_disk_store_age_sweeper_and_byte_limit(tmp_path):
         os.utime(small._path(k), (time.time() - 100 + i, time.time() - 100 + i))
     small._trim()
     assert [small.has(k) for k in keys + [b"\x09" * 20]] == [False, False, True, True] and small.metrics["disk_bytes"] == 2 * one
+
+
+def test_reclaimable_pages_are_counted_exactly():
+    """Entries of several checkpoint lengths share pages and running sequences hold cached pages too: only pages held by
+    nothing but cache entries count as reclaimable, and the incremental bookkeeping survives stores, hits and evictions."""
+    from deliverance_b200.kv.paged import PagedKVCache
+
+    layout = {"layers": 1, "kv_heads": 1, "head_dim": 64, "layer_kinds": ["attention"]}
+    kv = PagedKVCache(layout, 9, "cpu", torch.float32, KvCacheSettings(block_size=32, policy="FIXED_BLOCKS", max_prefix_tokens=4096))
+    toks = list(range(3, 3 + 96))
+    pages: list = []
+    kv.ensure_pages(pages, 96)  # 3 pages; 5 stay free
+    kv.prefix.store("", toks, pages)  # entries at 32, 64, 96 share the chain
+    assert kv.prefix.held == {pages[0]: 3, pages[1]: 2, pages[2]: 1} and kv.prefix.reclaimable(99) == 0  # the sequence still holds them
+    assert kv.can_allocate(5) and not kv.can_allocate(6)
+    kv.release_pages(list(pages))
+    assert kv.prefix.reclaimable(99) == 3 and kv.prefix.reclaimable(2) == 2 and kv.can_allocate(8) and not kv.can_allocate(9)
+    hit = kv.prefix.lookup("", toks[:64] + [7, 7])  # a new sequence takes two of the cached pages
+    assert hit.length == 64 and kv.prefix.reclaimable(99) == 1 and kv.can_allocate(6) and not kv.can_allocate(7)
+    kv.release_pages(list(hit.pages))
+    kv.prefix.evict_one()  # the 32-token entry (least recently used)
+    assert kv.prefix.held == {pages[0]: 2, pages[1]: 2, pages[2]: 1} and kv.prefix.reclaimable(99) == 3
+    kv.prefix.clear()
+    assert kv.prefix.held == {} and kv.allocator.available() == 8
