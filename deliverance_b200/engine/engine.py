@@ -121,6 +121,7 @@ class Engine:
         self.running: list[Request] = []
         self._next_id = 0
         self._graphs: dict[int, dict] = {}
+        self._failed: list[Request] = []  # requests failed inside a step (reported by step())
         self.metrics = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "prefill_tokens": 0, "decode_tokens": 0,
                         "graph_replays": 0, "kernel_launches": 0}
         # (a family that runs on the PyTorch operator set reads lengths on the host inside its forward: not capturable)
@@ -232,6 +233,28 @@ class Engine:
         self.metrics["preemptions"] = self.metrics.get("preemptions", 0) + 1
         self.waiting.insert(0, v)
 
+    def _fail_oom(self, r: Request) -> None:
+        """The oldest sequence cannot grow although nothing is left to preempt: the pool is too small for it. Only this
+        request fails; :meth:`step` reports it with the other finished requests."""
+        r.error = (f"KV cache is too small for this sequence ({r.total_len} tokens, {self.kv.num_pages - 1} pages of "
+                   f"{self.page_size} tokens)")
+        self._finish(r, FinishReason.ERROR)
+        self._failed.append(r)
+
+    def reset(self) -> None:
+        """Drop every request and give all their pages and state slots back (after a fault in a step: the requests are failed
+        by the caller, the engine must come back empty and leak nothing). Cached prefixes stay."""
+        self._inflight = None
+        for r in list(self.running) + list(self.waiting):
+            r.pending = 0
+            if r.state != FINISHED:
+                if r in self.waiting:
+                    self.waiting.remove(r)
+                self._finish(r, FinishReason.ERROR)
+        self.running.clear()
+        self.waiting.clear()
+        self._failed.clear()
+
     def _new_pages(self, r: Request, n_tokens: int) -> int:
         return max(0, (n_tokens + self.page_size - 1) // self.page_size - len(r.pages))
 
@@ -244,7 +267,7 @@ class Engine:
             victims = [v for v in younger if v.pending == 0]
             if not victims:
                 if self.running[0] is r and not younger:
-                    raise MemoryError("KV cache is too small for this sequence")
+                    self._fail_oom(r)
                 return False
             self._preempt(victims[-1])
         self.kv.ensure_pages(r.pages, n_tokens)
@@ -261,13 +284,22 @@ class Engine:
         while reqs and not self.kv.can_allocate(sum(self._new_pages(r, r.total_len) for r in reqs)):
             v = self.running[-1]  # youngest first; that may be a request whose prefill is waiting for pages
             if v is reqs[0]:
-                raise MemoryError("KV cache is too small for this sequence")
+                self._fail_oom(v)
+                reqs.remove(v)
+                continue
             self._preempt(v)
             if v in reqs:
                 reqs.remove(v)
         return reqs, finished
 
     def step(self) -> list[Request]:
+        out = self._step()
+        if self._failed:
+            out = out + [r for r in self._failed if r not in out]
+            self._failed.clear()
+        return out
+
+    def _step(self) -> list[Request]:
         """Run one engine step; returns the requests that finished in it. With lookahead decode the tokens of a decode step are
         read (and its finished requests reported) by the next call, while the device already runs the following step."""
         self.metrics["steps"] += 1
@@ -672,6 +704,8 @@ class Engine:
         self.run([r])
         if self.device.type == "cuda":
             ops.check_status(self.device.index)
+        if r.finish_reason == FinishReason.ERROR and r.error and r.error.startswith("KV cache is too small"):
+            raise MemoryError(r.error)
         return r.response()
 
     def generate_batch(self, prompts: list[list[int]], params: Optional[GeneratorParameters] = None) -> list[Response]:

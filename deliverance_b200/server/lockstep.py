@@ -26,8 +26,8 @@ from ..prompt.chat import PromptContext
 from .runner import EngineRunner, Submission
 
 
-def _command(new=(), cancel=(), stop=False) -> dict:
-    return {"new": list(new), "cancel": list(cancel), "stop": bool(stop)}
+def _command(new=(), cancel=(), stop=False, reset=False) -> dict:
+    return {"new": list(new), "cancel": list(cancel), "stop": bool(stop), "reset": bool(reset)}
 
 
 class LockstepRunner(EngineRunner):
@@ -70,7 +70,7 @@ class LockstepRunner(EngineRunner):
             fresh = admitted
             cancel = [s.session for s in self.active if s.cancelled and s.session not in self._announced_cancel
                       and s.generation.request.state != "finished"]
-            busy = eng.has_work() or new or cancel or stop
+            busy = eng.has_work() or new or cancel or stop or getattr(self, "_reset_followers", False)
             if not busy and time.monotonic() - last_sent < self.heartbeat:
                 for s in list(self.active):
                     if s.generation.request.state == "finished":
@@ -78,7 +78,8 @@ class LockstepRunner(EngineRunner):
                 time.sleep(self.idle_sleep)
                 continue
             try:
-                self.control.broadcast_object(_command(new, cancel, stop), 0)
+                self.control.broadcast_object(_command(new, cancel, stop, getattr(self, "_reset_followers", False)), 0)
+                self._reset_followers = False
                 last_sent = time.monotonic()
             except Exception as e:  # noqa: BLE001 - a follower is gone: fail what is in flight
                 for s in fresh + list(self.active):
@@ -103,8 +104,12 @@ class LockstepRunner(EngineRunner):
                 except Exception as e:  # noqa: BLE001
                     for s in list(self.active):
                         self._finish(s, e)
-                    eng.running.clear()
-                    eng.waiting.clear()
+                    try:
+                        eng.reset()
+                    except Exception:  # noqa: BLE001
+                        eng.running.clear()
+                        eng.waiting.clear()
+                    self._reset_followers = True  # the other ranks drop their copies of the failed requests with the next command
                     continue
             for s in list(self.active):
                 if s.generation.request.state == "finished":
@@ -139,6 +144,9 @@ def follower_loop(clm: CausalLanguageModel, control: Collectives, max_idle: Opti
             last = time.monotonic()
         elif max_idle is not None and time.monotonic() - last > max_idle:
             raise TimeoutError("no work from the coordinator")
+        if cmd.get("reset"):  # rank 0 failed a step and dropped every request: drop them here too, before the new ones
+            eng.reset()
+            live.clear()
         if cmd["stop"]:
             return steps
         for ids, params, has_tools, session in cmd["new"]:

@@ -62,8 +62,13 @@ class EngineRunner:
             s.error = error
             self.stats["errors"] += 1
         else:
-            s.response = s.generation.finish()
-            self.stats["finished"] += 1
+            req = s.generation.request
+            if req.finish_reason is not None and req.finish_reason.name == "ERROR" and req.error:
+                s.error = RuntimeError(req.error)  # failed inside the engine (KV pool too small for it, failing callback)
+                self.stats["errors"] += 1
+            else:
+                s.response = s.generation.finish()
+                self.stats["finished"] += 1
         if s in self.active:
             self.active.remove(s)
         s.done.set()
@@ -104,13 +109,12 @@ class EngineRunner:
                 eng.step()
             except Exception as e:  # noqa: BLE001 - an engine fault fails the in-flight requests, not the server
                 for s in list(self.active):
-                    try:
-                        eng.abort(s.generation.request)
-                    except Exception:  # noqa: BLE001
-                        pass
                     self._finish(s, e)
-                eng.running.clear()
-                eng.waiting.clear()
+                try:
+                    eng.reset()  # every request is dropped and its pages and state slots go back to the pool
+                except Exception:  # noqa: BLE001 - bookkeeping damaged by the fault: start from empty queues at least
+                    eng.running.clear()
+                    eng.waiting.clear()
                 continue
             for s in list(self.active):
                 if s.generation.request.state == "finished":

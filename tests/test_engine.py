@@ -446,3 +446,27 @@ def test_reclaimable_pages_are_counted_exactly():
     assert kv.prefix.held == {pages[0]: 2, pages[1]: 2, pages[2]: 1} and kv.prefix.reclaimable(99) == 3
     kv.prefix.clear()
     assert kv.prefix.held == {} and kv.allocator.available() == 8
+
+
+def test_oom_fails_one_request_and_reset_returns_every_page(tiny):
+    """A sequence the pool cannot hold fails alone (the others finish); Engine.reset() after a fault returns all pages."""
+    eng = _engine(tiny, pages=5, chunk=64, lookahead=False)
+    eng.eos_ids = frozenset((-1,))
+    small = eng.add_request([5, 6, 7], GeneratorParameters(max_tokens=4))
+    big = eng.add_request(list(range(3, 120)), GeneratorParameters(max_tokens=100))  # 117 + 100 tokens > 4 pages of 32
+    done = []
+    while eng.has_work():
+        done += eng.step()
+    assert small.finish_reason == FinishReason.MAX_TOKENS and len(small.output) == 4
+    assert big.finish_reason == FinishReason.ERROR and big.error.startswith("KV cache is too small") and big in done
+    eng.kv.prefix.clear()
+    assert eng.kv.allocator.available() == 4
+    a = eng.add_request([5, 6, 7, 8], GeneratorParameters(max_tokens=50))
+    b = eng.add_request([9, 10], GeneratorParameters(max_tokens=50))
+    for _ in range(3):
+        eng.step()
+    assert eng.kv.allocator.available() < 4
+    eng.reset()
+    eng.kv.prefix.clear()
+    assert eng.kv.allocator.available() == 4 and not eng.has_work() and a.finish_reason == FinishReason.ERROR and b.state == "finished"
+    assert eng.generate([5, 6, 7], GeneratorParameters(max_tokens=3)).generated_tokens == 3  # usable afterwards

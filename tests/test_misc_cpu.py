@@ -735,3 +735,56 @@ def test_builder_reference_methods_and_download_cache(tmp_path):
     assert AutoModelForCausalLM.new_builder(str(d)).with_tensor_plan_trace(True).conf.profile_stages
     with pytest.raises(ValueError):
         AutoModelForCausalLM.new_builder("no-slash").with_download().with_device("cpu").build()
+
+
+def test_runner_isolates_engine_faults_and_oom(tmp_path):
+    """A fault inside an engine step fails the requests in flight, returns their KV pages and leaves the server usable;
+    a request that cannot fit into the KV pool fails alone with a message."""
+    import threading
+
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.params import GeneratorParameters
+    from deliverance_b200.server.runner import EngineRunner
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=3, std=0.05, max_position_embeddings=1024)
+    b = AutoModelForCausalLM.new_builder(d).with_device("cpu")
+    b.conf.kv_pages = 8
+    clm = b.build()
+    clm.eos_ids, clm.engine.eos_ids = set(), frozenset((-1,))
+    clm.engine.kv.settings.enabled = False
+    runner = EngineRunner(clm)
+    try:
+        real_forward, boom = clm.model.forward, {"n": 0}
+
+        def flaky(*a, **kw):
+            boom["n"] += 1
+            if boom["n"] == 3:
+                raise RuntimeError("injected fault")
+            return real_forward(*a, **kw)
+
+        clm.model.forward = flaky
+        errs = []
+
+        def call(i):
+            try:
+                runner.generate(f"prompt {i}", GeneratorParameters(max_tokens=20), None, f"s{i}", 60)
+            except Exception as e:  # noqa: BLE001
+                errs.append(str(e))
+
+        ths = [threading.Thread(target=call, args=(i,)) for i in range(3)]
+        for t in ths:
+            t.start()
+        for t in ths:
+            t.join(60)
+        assert errs and all("injected fault" in e for e in errs)
+        assert clm.engine.kv.allocator.available() == 7 and not clm.engine.has_work()
+        assert runner.generate("after the fault", GeneratorParameters(max_tokens=3), None, "ok", 60).generated_tokens == 3
+        with pytest.raises(Exception) as ei:  # 7 pages of 32 tokens cannot hold 300 tokens
+            runner.generate("x" * 150, GeneratorParameters(max_tokens=200), None, "big", 60)
+        assert "KV cache is too small" in str(ei.value)
+        assert runner.generate("still fine", GeneratorParameters(max_tokens=3), None, "ok2", 60).generated_tokens == 3
+        assert clm.engine.kv.allocator.available() == 7
+    finally:
+        runner.close()
