@@ -6,6 +6,13 @@ PORT="${PORT:-8080}"
 TP_SIZE="${TP_SIZE:-1}"
 EXTRA="${SERVER_ARGS:-}"
 if [ "$TP_SIZE" -gt 1 ]; then
+  # the rank supervisor starts one process per GPU and restarts the whole group when a rank dies or stops reporting
+  # (SUPERVISE=0 falls back to a plain torchrun launch)
+  if [ "${SUPERVISE:-1}" = "1" ]; then
+    exec python -m deliverance_b200.parallel.cluster --nproc "$TP_SIZE" --no-exit-ok --max-restarts "${MAX_RESTARTS:-5}" \
+         --hang-timeout "${HANG_TIMEOUT:-120}" --start-timeout "${START_TIMEOUT:-1800}" --status-file /tmp/deliverance-cluster.json -- \
+         python -m deliverance_b200.server --model "$MODEL" --host 0.0.0.0 --port "$PORT" $EXTRA
+  fi
   exec python -m torch.distributed.run --nnodes=1 --nproc-per-node "$TP_SIZE" --master-addr 127.0.0.1 --master-port 29500 \
        -m deliverance_b200.server --model "$MODEL" --host 0.0.0.0 --port "$PORT" $EXTRA
 fi

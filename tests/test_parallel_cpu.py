@@ -339,3 +339,55 @@ def test_local_cluster_gives_up_after_max_restarts(tmp_path):
 
     c = LocalCluster([sys.executable, "-c", "import sys; sys.exit(7)"], nproc=2, max_restarts=1, grace=1.0)
     assert c.run() == 1 and c.status.state == "failed" and c.status.restarts == 1 and len(c.status.failures) == 2
+
+
+def test_supervised_tensor_parallel_server_recovers_from_a_dead_rank(tmp_path):
+    """Two-rank lockstep serving (gloo, CPU) under the rank supervisor: a chat request is served, rank 1 is killed between
+    requests (its exact pid, host side), the supervisor restarts the group and the same endpoint serves again."""
+    import json
+    import signal
+    import socket
+    import time
+    import urllib.request
+
+    d = str(tmp_path / "tiny")
+    write_tiny_model(d, "llama", seed=3, std=0.05)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    status = str(tmp_path / "status.json")
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.environ.get("PYTHONPATH", "")]))
+    sup = subprocess.Popen([sys.executable, "-m", "deliverance_b200.parallel.cluster", "--nproc", "2", "--no-exit-ok", "--hang-timeout", "30",
+                            "--start-timeout", "180", "--status-file", status, "--",
+                            sys.executable, "-m", "deliverance_b200.server", "--model", d, "--device", "cpu", "--port", str(port)], env=env)
+
+    def chat():
+        body = json.dumps({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4}).encode()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/chat/completions", body, {"Content-Type": "application/json"})
+        return json.loads(urllib.request.urlopen(req, timeout=30).read())
+
+    def wait_up(limit=150):
+        t0 = time.time()
+        while time.time() - t0 < limit:
+            try:
+                return chat()
+            except Exception:  # noqa: BLE001 - not listening yet
+                time.sleep(0.5)
+        raise AssertionError("server did not come up")
+
+    try:
+        first = wait_up()
+        st = json.load(open(status))
+        assert first["usage"]["completion_tokens"] == 4 and st["state"] == "running" and len(st["pids"]) == 2
+        tp = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/tp/status", timeout=10).read())
+        assert tp["enabled"] and tp["size"] == 2 and tp["cluster"]["generation"] == 1
+        os.kill(st["pids"][1], signal.SIGKILL)
+        time.sleep(2.0)
+        again = wait_up()
+        st = json.load(open(status))
+        assert again["choices"][0]["message"]["content"] == first["choices"][0]["message"]["content"]
+        assert st["restarts"] == 1 and "exited with code -9" in st["last_failure"] and st["state"] == "running"
+    finally:
+        sup.send_signal(signal.SIGTERM)
+        assert sup.wait(60) == 0
