@@ -474,6 +474,12 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         return error(409, f"rank assignment is static: ranks are fixed at launch (requested nodeId={q.get('nodeId')} rank={q.get('rank')}); "
                           "restart the group with a different --nproc to change it")
 
+    async def health():
+        """Liveness / readiness probe (never behind authentication): 200 while every engine runner thread is alive."""
+        dead = [n for n, r in registry.generation.items() if getattr(r, "thread", None) is not None and not r.thread.is_alive()]
+        body = {"status": "ok" if not dead else "degraded", "models": len(registry.generation) + len(registry.embedding), "dead_runners": dead}
+        return JSONResponse(body, status_code=200 if not dead else 503)
+
     async def ui():
         return HTMLResponse(_UI)
 
@@ -525,6 +531,8 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
     app.add_api_route("/tp/gossip", tp_gossip, methods=["GET"])
     app.add_api_route("/tp/assign", tp_assign, methods=["POST"])
     app.add_api_route("/ui", ui, methods=["GET"])
+    for path in ("/health", "/healthz"):
+        app.add_api_route(path, health, methods=["GET"])
     return app
 
 

@@ -49,6 +49,7 @@ def test_chat_blocking_and_models(registry):
     m = c.get("/models").json()["data"]
     assert {x["id"] for x in m} == {"tiny-llama", "tiny-bert"}
     assert c.get("/tp/status").json()["enabled"] is False
+    assert c.get("/health").json() == {"status": "ok", "models": 2, "dead_runners": []} and c.get("/healthz").status_code == 200
     assert c.get("/tp/endpoints").json() == {"size": 1, "endpoints": [{"rank": 0, "device": "local", "role": "coordinator+rank"}]}
     assert c.get("/tp/gossip").json()["membership"] == "static" and c.post("/tp/assign?nodeId=n1&rank=1").status_code == 409
 
