@@ -330,6 +330,13 @@ def main() -> int:
             "gpu_launches": int(launches_per_step * args.steps),
             "extras": extras,
         }
+        try:  # fraction of the measured roofline (copy bandwidth / cuBLAS rate of this pool) for the timed decode step
+            from deliverance_b200.bench.roofline import report
+
+            rf = report(cfg, B, P + args.warmup + args.steps // 2, args.quant, world, dev_ms)
+            out["roofline"] = {k: rf[k] for k in ("target_ms", "bound", "fraction", "hbm_ms", "tensor_ms", "nvlink_ms", "denominators")}
+        except Exception as e:  # noqa: BLE001 - reporting only
+            out["roofline"] = {"error": repr(e)}
         print(json.dumps(out), flush=True)
     _shutdown(dist, eng)
     return 0

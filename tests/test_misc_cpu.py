@@ -788,3 +788,28 @@ def test_runner_isolates_engine_faults_and_oom(tmp_path):
         assert clm.engine.kv.allocator.available() == 7
     finally:
         runner.close()
+
+
+def test_roofline_calculator(tmp_path):
+    from deliverance_b200.bench import roofline as rf
+    from deliverance_b200.ckpt.synthetic import SHAPES
+    from deliverance_b200.config import parse_config
+
+    cfg = parse_config(dict(SHAPES["qwen3-4b"]))
+    c = rf.decode_step_cost(cfg, 64, 2048, "jq4", 1)
+    # 36 layers x (2560 x 6144 + 4096 x 2560 + 3 x 2560 x 9728) weights + the 151936 x 2560 head, 0.625 bytes per element
+    elems = 36 * (2560 * 6144 + 4096 * 2560 + 3 * 2560 * 9728) + 151936 * 2560
+    assert abs(c.weight_bytes - elems * 0.625) < 1 and abs(c.kv_bytes - 64 * 36 * 2049 * 2 * 8 * 128 * 2) < 1 and c.nvlink_bytes == 0
+    p = tmp_path / "peaks.json"
+    p.write_text(json.dumps({"hbm_gbs": 6000.0, "bf16_tflops": 1500.0, "bf16_tflops_sustained": 1400.0}))
+    r = rf.report(cfg, 64, 2048, "jq4", 1, 6.0, str(p))
+    assert r["bound"] == "hbm" and r["denominators"] == "of measured" and abs(r["target_ms"] - (c.hbm_bytes / 6e12 * 1e3)) < 1e-9
+    assert abs(r["fraction"] - r["target_ms"] / 6.0) < 1e-12
+    assert rf.load_peaks(str(tmp_path / "missing.json"))[1] == "fallback"
+    c8 = rf.decode_step_cost(cfg, 64, 2048, "jq4", 8)
+    assert abs(c8.weight_bytes - c.weight_bytes / 8) < 1 and c8.nvlink_bytes == 2 * 36 * 64 * 2560 * 2 * 7 and abs(c8.kv_bytes - c.kv_bytes / 8) < 1
+    moe = parse_config(dict(SHAPES["mixtral-8x7b"]))
+    m1, m64 = rf.decode_step_cost(moe, 1, 1024, "bf16", 1), rf.decode_step_cost(moe, 64, 1024, "bf16", 1)
+    assert m1.weight_bytes < m64.weight_bytes  # one token touches two of the eight experts per layer
+    g = parse_config(dict(SHAPES["gemma2-9b"]))
+    assert rf.decode_step_cost(g, 1, 8000, "bf16", 1).kv_bytes < 42 * 8001 * 2 * 8 * 256 * 2  # sliding layers read at most the window
