@@ -173,3 +173,38 @@ def test_malformed_requests_are_400(registry):
     assert c.post("/chat/completions", content="{not json", headers={"Content-Type": "application/json"}).status_code == 400
     r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": None}, {"role": "user", "content": 5}], "max_tokens": 2})
     assert r.status_code == 200
+
+
+def test_streaming_tool_calls_never_leak_markup(tmp_path):
+    """Behaviours of the reference's ChatCompletionStreamingToolCallTest on the real stack: the model is forced (guided regex)
+    to emit a reasoning block and two raw <tool_call> regions; with tools in the request no markup reaches the stream, the
+    calls arrive as ONE structured tool_calls delta after generation, reasoning goes to its own field, finish_reason is
+    tool_calls; the blocking reply carries the same calls."""
+    from deliverance_b200.guided.json_schema import escape_literal
+
+    d = str(tmp_path / "qwen-tiny")
+    write_tiny_model(d, "llama", seed=3, std=0.05, max_position_embeddings=2048)
+    clm = AutoModelForCausalLM.from_pretrained(d, device="cpu")
+    reg = ModelRegistry()
+    reg.generation[clm.name] = EngineRunner(clm)
+    try:
+        c = TestClient(create_app(reg))
+        call = '<tool_call>{"name":"grep","arguments":{"path":"/tmp/ed","pattern":"cat","limit":10}}</tool_call>'
+        body = {"messages": [{"role": "user", "content": "grep the file"}], "max_tokens": 400, "guided_regex": escape_literal("<think>checking</think>\n" + call + call),
+                "tools": [{"type": "function", "function": {"name": "grep", "parameters": {"type": "object"}}}]}
+        r = c.post("/chat/completions", json=dict(body, stream=True))
+        assert "<tool_call>" not in r.text and "</tool_call>" not in r.text
+        chunks = [json.loads(e) for e in _sse(r)[:-1]]
+        deltas = [ch["choices"][0]["delta"] for ch in chunks if ch["choices"]]
+        tool_deltas = [x for x in deltas if x.get("tool_calls")]
+        assert len(tool_deltas) == 1 and [t["function"]["name"] for t in tool_deltas[0]["tool_calls"]] == ["grep", "grep"]
+        assert json.loads(tool_deltas[0]["tool_calls"][0]["function"]["arguments"]) == {"path": "/tmp/ed", "pattern": "cat", "limit": 10}
+        assert [t["id"] for t in tool_deltas[0]["tool_calls"]] == ["101", "102"] and [t["index"] for t in tool_deltas[0]["tool_calls"]] == [0, 1]
+        assert "".join(x.get("reasoning_content") or "" for x in deltas) == "checking" and "".join(x.get("content") or "" for x in deltas) == ""
+        assert chunks[-1]["choices"][0]["finish_reason"] == "tool_calls"
+        msg = c.post("/chat/completions", json=body).json()["choices"][0]
+        assert msg["finish_reason"] == "tool_calls" and len(msg["message"]["tool_calls"]) == 2 and msg["message"]["reasoning_content"] == "checking"
+        assert msg["message"]["content"] == ""
+    finally:
+        for r_ in reg.generation.values():
+            r_.close()
