@@ -108,6 +108,12 @@ class Engine:
         self.sampler = Sampler(decode_token)
         layout = model.kv_layout()
         pages = self.config.num_pages or self._auto_pages(layout)
+        tp = getattr(model, "tp", None)
+        if self.config.num_pages is None and tp is not None and tp.enabled and tp.collectives is not None:
+            # ranks size their pools from their own free memory; admission and preemption must decide alike on every rank
+            # (a rank with a smaller pool would run a different batch and the collectives would no longer match): take the minimum
+            mine = torch.tensor([float(pages)], dtype=torch.float32, device=self.device)
+            pages = int(min(float(t.item()) for t in tp.collectives.all_gather(mine)))
         mamba_shapes = None
         slots = self.config.max_state_slots
         if any(k == "mamba" for k in layout["layer_kinds"]):
