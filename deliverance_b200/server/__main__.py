@@ -91,7 +91,10 @@ def main() -> int:
         if tp is not None:
             b.with_tensor_parallel_context(tp)
         clm = b.build()
-        if conf is not None and conf.kv_disk_dir:
+        if conf is not None and conf.kv_disk_dir and tp is not None:
+            # every rank would have to find the same prefixes on disk (a rank that misses a file would run a different batch)
+            print("[server] deliverance.kv.disk-dir is ignored under tensor parallelism", flush=True)
+        elif conf is not None and conf.kv_disk_dir:
             clm.engine.kv.attach_disk(os.path.join(os.path.expanduser(conf.kv_disk_dir), clm.name),
                                       "MSE_TURBOQUANT" if conf.kv.get("compression") == "MSE_TURBOQUANT" else "LZ4", conf.kv_turboquant_bits or 4)
         if tp is None:
