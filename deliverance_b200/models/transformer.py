@@ -13,6 +13,8 @@ everything else replicated (DefaultTransformerWeightPolicyResolver.java:10-26).
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import Callable, Optional
 
@@ -61,6 +63,7 @@ class LayerWeights:
     # mamba2
     mamba: Optional[dict] = None
     lora: dict = field(default_factory=dict)  # projection name -> LoraSlot
+    fused_act: bool = False  # gate_up holds interleaved rows and the GEMM epilogue applies the gated activation
 
 
 def _cat_weights(parts: list) -> "torch.Tensor | Q4Tensor":
@@ -98,6 +101,8 @@ class DecoderModel:
         self.profiler = None
         self.active_lora: Optional[str] = None
         self.shard_head = True  # split the output head over the vocabulary under tensor parallelism
+        # opt-in (DLV_FUSED_ACT=1): act(gate) * up inside the gate|up GEMM epilogue instead of a separate kernel
+        self.fused_act = os.environ.get("DLV_FUSED_ACT", "0") == "1"
         self.vocab_shard: Optional[tuple] = None
         self._moe_impl = None
 
@@ -227,7 +232,12 @@ class DecoderModel:
                     lw.experts_down.append(self._lin(_slice_expert(wout, e)))
         else:
             parts = [get(p + "mlp.gate_proj.weight", row()), get(p + "mlp.up_proj.weight", row())]
-            lw.gate_up = self._lin(_cat_weights(parts))
+            if self.fused_act and parts[0].shape[0] % 64 == 0 and ops.fused_act_kind(cfg.hidden_act):
+                # gate and up rows interleaved per 64 outputs: the GEMM epilogue applies act(gate) * up (ops.linear_act)
+                lw.gate_up = self._lin(ops.interleave_gate_up(parts[0], parts[1]))
+                lw.fused_act = True
+            else:
+                lw.gate_up = self._lin(_cat_weights(parts))
             lw.down = self._lin(get(p + "mlp.down_proj.weight", col))
         if lw.experts_gate_up and self.device.type == "cuda":
             lw.experts_gate_up_grouped = ops.GroupedLinearWeight(lw.experts_gate_up)
@@ -265,6 +275,8 @@ class DecoderModel:
             groups = {"qkv": [p + f"self_attn.{n}_proj.weight" for n in ("q", "k", "v")], "o": [p + "self_attn.o_proj.weight"],
                       "gate_up": [p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"], "down": [p + "mlp.down_proj.weight"]}
             for slot, names in groups.items():
+                if slot == "gate_up" and lw.fused_act and any(adapter.has(n) for n in names):
+                    raise ValueError("run-time LoRA on gate_proj / up_proj is not available with the fused activation epilogue (DLV_FUSED_ACT)")
                 w = getattr(lw, slot)
                 if w is None or not any(adapter.has(n) for n in names):
                     continue
@@ -359,12 +371,16 @@ class DecoderModel:
             if lw.router is not None:
                 y = y + self.moe(i, lw, x)
             return y
-        with self._stage("mlpblock.gate_up_projection"):
-            gu = ops.linear(x, lw.gate_up)
-            if lw.lora:
-                gu = self._lora(lw, "gate_up", x, gu)
-        with self._stage("mlpblock.activation_multiply"):
-            h = ops.act_mul(gu, cfg.hidden_act)
+        if lw.fused_act:
+            with self._stage("mlpblock.gate_up_projection"):
+                h = ops.linear_act(x, lw.gate_up, cfg.hidden_act)
+        else:
+            with self._stage("mlpblock.gate_up_projection"):
+                gu = ops.linear(x, lw.gate_up)
+                if lw.lora:
+                    gu = self._lora(lw, "gate_up", x, gu)
+            with self._stage("mlpblock.activation_multiply"):
+                h = ops.act_mul(gu, cfg.hidden_act)
         with self._stage("mlpblock.down_projection"):
             d = self._row_parallel(h, lw.down, f"layer.{i}.mlp.down_proj")
             if lw.lora:

@@ -203,6 +203,51 @@ def linear(x: torch.Tensor, w: LinearWeight, out_f32: bool = False, impl: int = 
     return y.float() if out_f32 else y
 
 
+_ACT_KINDS = {"silu": 1, "swish": 1, "gelu_pytorch_tanh": 2, "gelu_new": 2, "gelu_tanh": 2, "gelu_fast": 2}
+
+
+def fused_act_kind(act: str) -> int:
+    """Code of an activation the GEMM epilogue can apply (0: none)."""
+    return _ACT_KINDS.get((act or "silu").lower(), 0)
+
+
+def interleave_gate_up(gate, up, block: int = 64):
+    """Row order for :func:`linear_act`: blocks of ``block`` gate rows, each followed by the up rows of the same outputs, so that
+    one 128-row weight tile of the GEMM holds both halves of 64 outputs. Works on dense tensors and on JQ4 tensors (rows of the
+    packed nibbles and of the scales move together)."""
+    from ..ckpt.safetensors_io import Q4Tensor
+
+    def mix(a, b):
+        n = a.shape[0]
+        if n % block != 0 or b.shape != a.shape:
+            raise ValueError(f"gate / up rows ({n}) must be equal and a multiple of {block}")
+        return torch.stack([a.reshape(n // block, block, -1), b.reshape(n // block, block, -1)], dim=1).reshape(2 * n, -1).contiguous()
+
+    if isinstance(gate, Q4Tensor) and isinstance(up, Q4Tensor):
+        packed, scales = mix(gate.packed, up.packed), mix(gate.scales, up.scales)
+        return Q4Tensor(packed, scales, (packed.shape[0], packed.shape[1] * 2))
+    if isinstance(gate, Q4Tensor) or isinstance(up, Q4Tensor):
+        gate = gate.dequantize(torch.float32) if isinstance(gate, Q4Tensor) else gate
+        up = up.dequantize(torch.float32) if isinstance(up, Q4Tensor) else up
+    return mix(gate, up.to(gate.dtype))
+
+
+def linear_act(x: torch.Tensor, w: LinearWeight, act: str, block: int = 64) -> torch.Tensor:
+    """``act(x @ Wg^T) * (x @ Wu^T)`` in one GEMM whose epilogue applies the gated activation; ``w`` holds the gate and up rows in
+    the order of :func:`interleave_gate_up`. Returns ``[T, N / 2]``."""
+    if _cuda(x):
+        kind = fused_act_kind(act)
+        if kind == 0:
+            raise ValueError(f"activation '{act}' is not available in the GEMM epilogue")
+        _count()
+        return w.handle().run_act(x, kind)
+    y = ref.linear_q4(x, w.packed, w.scales, None) if w.q4 else ref.linear_dense(x, w.w, None)
+    T, n2 = y.shape
+    y = y.reshape(T, n2 // (2 * block), 2, block)
+    g, u = y[:, :, 0, :].reshape(T, n2 // 2), y[:, :, 1, :].reshape(T, n2 // 2)
+    return (ref.act_fn(act)(g.float()) * u.float()).to(x.dtype)
+
+
 # ---------------------------------------------------------------------------------------------------------- norms etc.
 def rmsnorm(x, w, eps, offset=0.0):
     if _cuda(x):

@@ -146,6 +146,23 @@ class GemmWeight {
     check_last_error("gemm launch");
     return out;
   }
+  // Gate | up projection with act(gate) * up in the epilogue. `this` holds the gate and up rows interleaved per 128-row tile (64 gate
+  // rows followed by the 64 up rows of the same outputs); returns [M, N / 2]. act: 1 = SiLU, 2 = tanh-approximated GELU.
+  Tensor run_act(const Tensor& x, int64_t act) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(1) == desc_.K && x.stride(1) == 1, "x must be bf16 [M, K]");
+    TORCH_CHECK(x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x rows must be 16-byte aligned");
+    TORCH_CHECK(desc_.N % 128 == 0, "gate|up rows must be a multiple of 128");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int M = static_cast<int>(x.size(0));
+    Tensor out = torch::empty({M, desc_.N / 2}, x.options());
+    if (M == 0) return out;
+    DeviceScratch& s = scratch_for(x.device().index());
+    dlv::gemm_tc_run_act(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), out.data_ptr(), static_cast<int>(out.stride(0)), static_cast<int>(act),
+                         s.ws.data_ptr<float>(), static_cast<size_t>(s.ws.numel()), s.counters.data_ptr<int>(),
+                         static_cast<int>(s.counters.numel()), s.status.data_ptr<int>(), cur_stream());
+    check_last_error("gemm (fused activation) launch");
+    return out;
+  }
   // Grouped (MoE) GEMM: `this` stacks the local experts' weights (n_per_expert rows each; JQ4: whole 128-row tiles per expert),
   // xs holds rows sorted by expert, `items` comes from moe_items with the same token tile.
   Tensor run_grouped(const Tensor& xs, const Tensor& items, int64_t n_per_expert, int64_t bn, int64_t splits, c10::optional<Tensor> out_opt) {
@@ -666,6 +683,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("run", &GemmWeight::run, py::arg("x"), py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("out_f32") = false,
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
+      .def("run_act", &GemmWeight::run_act, py::arg("x"), py::arg("act"))
       .def("run_grouped", &GemmWeight::run_grouped, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits") = 1,
            py::arg("out") = py::none())
       .def_property_readonly("N", &GemmWeight::n)

@@ -77,6 +77,9 @@ struct GemmParams {
   // grid a few tiles larger than the SM count ends with a short second wave instead of a full one (host: splits == 1) ----
   int tail_tile0, tail_splits, tail_kb_per_split;
   int x3d, w3d;  // the activation / dense weight map is the 3-D chunked form: one copy per stage instead of two
+  // ---- gated activation in the epilogue (kernel template ACT): the weight rows of a tile are 64 gate rows followed by the 64 up
+  // rows of the same outputs (interleaved at load time); out[m, 64 * tile + r] = act(gate) * up, ldo counts N / 2 columns ----
+  int act_kind;  // 1: SiLU, 2: tanh-approximated GELU
 };
 
 template <bool Q4, int BN>
@@ -137,7 +140,7 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t c
   return v;
 }
 
-template <bool Q4, int BN>
+template <bool Q4, int BN, bool ACT = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K] (unused for JQ4, which streams p.wq)
                const __grid_constant__ CUtensorMap map_x,   // bf16 [M, K]
@@ -533,7 +536,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       bias.z = n + 2 < p.N ? p.bias[n + 2] : 0.f;
       bias.w = n + 3 < p.N ? p.bias[n + 3] : 0.f;
     }
-    if (do_store && !fused_tp) {
+    if constexpr (ACT) {
+      // ---- gated activation: rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same 64 outputs ----
+      // (host guarantees: no bias, no tensor-parallel fusion, N a multiple of 128, p.ldo = pitch of the [M, N / 2] output)
+      if (do_store) {
+        auto acc_at = [&](int col, int r4) -> float4 {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (clustered) {
+            const uint32_t a = stage_addr + static_cast<uint32_t>((col * kGemmBM + r4) * 4);
+            for (int sp = 0; sp < splits; ++sp) {
+              const float4 v = ld_dsmem_f32x4(a, static_cast<uint32_t>(sp));
+              acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+          } else if (splits > 1) {
+            const float* base = p.ws + static_cast<size_t>(ws_tile) * splits * (BN * kGemmBM);
+            for (int sp = 0; sp < splits; ++sp) {
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (static_cast<size_t>(sp) * BN + col) * kGemmBM + r4));
+              acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+          } else {
+            acc = *reinterpret_cast<const float4*>(stage + col * kGemmBM + r4);
+          }
+          return acc;
+        };
+        auto act1 = [&](float g) -> float {
+          if (p.act_kind == 2) {
+            const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+            return 0.5f * g * (1.f + tanhf(u));
+          }
+          return g / (1.f + __expf(-g));
+        };
+        if (row4 < 64) {
+          const int half_n = p.N >> 1;
+          const int no = (n_tile << 6) + row4;  // output column of weight row row4 of this tile (per expert in grouped mode)
+          for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
+            const int m = m0 + col;
+            if (m >= m_lim) break;
+            const float4 g = acc_at(col, row4), u = acc_at(col, row4 + 64);
+            const float vals[4] = {act1(g.x) * u.x, act1(g.y) * u.y, act1(g.z) * u.z, act1(g.w) * u.w};
+            const size_t o = static_cast<size_t>(m) * p.ldo + no;
+            if (no + 3 < half_n && (p.ldo & 3) == 0 && !p.out_f32) {
+              uint2 pk;
+              pk.x = pack_bf162(vals[0], vals[1]);
+              pk.y = pack_bf162(vals[2], vals[3]);
+              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
+            } else {
+              for (int e = 0; e < 4; ++e) {
+                if (no + e < half_n) {
+                  if (p.out_f32) reinterpret_cast<float*>(p.out)[o + e] = vals[e];
+                  else reinterpret_cast<__nv_bfloat16*>(p.out)[o + e] = f2bf(vals[e]);
+                }
+              }
+            }
+          }
+        }
+        if (splits > 1 && !p.cluster_reduce && t == 0) p.counters[ws_tile] = 0;
+      }
+    } else if (do_store && !fused_tp) {
       // column c of the tile is finished by cluster rank c % splits; the 16 column slots of this CTA take turns
       for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
         const int m = m0 + col;
@@ -544,7 +603,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       }
       if (splits > 1 && !p.cluster_reduce && t == 0) p.counters[ws_tile] = 0;
     }
-    if (fused_tp) {
+    if (!ACT && fused_tp) {
       // ---- GEMM + one-shot all-reduce over peer memory (host guarantees: N % 4 == 0, cluster or single split) ----
       const unsigned cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
       const unsigned call = *reinterpret_cast<volatile unsigned*>(p.tp_call);

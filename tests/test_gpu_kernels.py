@@ -249,3 +249,30 @@ def test_sample_rows_kernel_matches_sorting_sampler(V, peaked):
         assert logits[i, tok[i]] != float("-inf")
         kth = torch.topk(logits[i], int(limits[i])).values[-1]
         assert logits[i, tok[i]] >= kth
+
+
+@pytest.mark.skipif(__import__("os").environ.get("DLV_TEST_FUSED_ACT") != "1",
+                    reason="epilogue activation of the gate|up GEMM: opt-in until it has been timed and checked on a B200 (DLV_TEST_FUSED_ACT=1)")
+@pytest.mark.parametrize("M,I,K,q4,act", [(1, 256, 256, True, "silu"), (7, 512, 1024, True, "silu"), (64, 9728, 2560, True, "silu"),
+                                           (64, 1216, 2560, True, "silu"), (33, 512, 768, False, "gelu_pytorch_tanh"),
+                                           (200, 1024, 512, False, "silu"), (64, 19456, 2560, True, "silu")])
+def test_gemm_epilogue_gated_activation(M, I, K, q4, act):
+    """linear_act (rows interleaved per 64 outputs, act(gate) * up in the epilogue) against act_mul(linear) in fp32."""
+    g = torch.Generator().manual_seed(I + K)
+    wg, wu = torch.randn(I, K, generator=g) * 0.05, torch.randn(I, K, generator=g) * 0.05
+    if q4:
+        pg, sg = q4_quantize(wg)
+        pu, su = q4_quantize(wu)
+        wg, wu = q4_dequantize(pg, sg), q4_dequantize(pu, su)
+        mixed = ops.interleave_gate_up(Q4Tensor(pg, sg, (I, K)), Q4Tensor(pu, su, (I, K)))
+    else:
+        wg, wu = wg.to(torch.bfloat16).float(), wu.to(torch.bfloat16).float()
+        mixed = ops.interleave_gate_up(wg.to(torch.bfloat16), wu.to(torch.bfloat16))
+    lw = LinearWeight(mixed).to(DEV, torch.bfloat16)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    y = ops.linear_act(x.to(DEV), lw, act)
+    torch.cuda.synchronize()
+    ops.check_status()
+    yr = ref.act_fn(act)(x.float() @ wg.t()) * (x.float() @ wu.t())
+    assert y.shape == (M, I) and _rel(y.cpu(), yr) < 2e-2, _rel(y.cpu(), yr)
+    assert torch.equal(y, ops.linear_act(x.to(DEV), lw, act))

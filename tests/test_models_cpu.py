@@ -162,3 +162,29 @@ def test_gemma4_matches_hf(tmp_path, variant):
         assert kv.k[3] is kv.k[0] or kv.k[3] is kv.k[1] and kv.k[5] is kv.k[2] and m.layers[4].w["gate_proj"].shape[0] == 256
         nested = parse_config({"model_type": "gemma4", "text_config": json.load(open(d + "/config.json")), "eos_token_id": [1, 106]})
         assert nested.extra["shared_from"] == cfg.extra["shared_from"] == [-1, -1, -1, 1, 1, 2] and nested.eos_token_ids == (1, 106)
+
+
+@pytest.mark.parametrize("family,quantize", [("llama", False), ("gemma2", False), ("qwen3", True)])
+def test_fused_activation_layout_matches_separate_kernels(tmp_path, family, quantize, monkeypatch):
+    """Opt-in gate|up layout for the GEMM epilogue activation (rows interleaved per 64 outputs): on the oracle path the model
+    must produce the same logits as with the concatenated layout and the separate activation kernel."""
+    from deliverance_b200 import ops
+    from deliverance_b200.models.batch import make_batch
+
+    d = str(tmp_path / family)
+    write_tiny_model(d, family, seed=6, std=0.05, quantize=quantize)
+    plain, eng = _ours(d, chunk=4096)
+    monkeypatch.setenv("DLV_FUSED_ACT", "1")
+    fused, eng2 = _ours(d, chunk=4096)
+    assert all(lw.fused_act for lw in fused.layers) and not any(lw.fused_act for lw in plain.layers)
+    assert fused.layers[0].gate_up.q4 == quantize
+    batch = make_batch([{"tokens": PROMPT, "start": 0, "pages": [1, 2], "state_slot": 0}], 32, "cpu")
+    a = plain.forward(batch, eng.kv, all_rows=True)
+    b = fused.forward(batch, eng2.kv, all_rows=True)
+    assert torch.allclose(a, b, atol=1e-5, rtol=1e-5)
+    g, u = torch.arange(128.0).reshape(128, 1).repeat(1, 4), -torch.arange(128.0).reshape(128, 1).repeat(1, 4)
+    mixed = ops.interleave_gate_up(g, u)
+    assert mixed[:64, 0].tolist() == list(range(64)) and mixed[64:128, 0].tolist() == [-float(i) for i in range(64)] and mixed[128, 0] == 64
+    assert ops.fused_act_kind("silu") == 1 and ops.fused_act_kind("gelu_pytorch_tanh") == 2 and ops.fused_act_kind("relu") == 0
+    with pytest.raises(ValueError):
+        ops.interleave_gate_up(torch.zeros(100, 4), torch.zeros(100, 4))
