@@ -34,7 +34,7 @@ from .params import FinishReason, GeneratorParameters, Response
 from .prompt.chat import PromptBuilder, PromptContext
 from .prompt.parsers import (Gemma4ToolCallParser, ReasoningTextSplitter, StopStringDetector, ToolCallParser, parse_gemma4_response,
                              parser_for_model, prompt_ends_inside_reasoning, split_reasoning)
-from .tokenizer.auto import AutoTokenizer, IncrementalDetokenizer
+from .tokenizer.auto import AutoTokenizer, IncrementalDetokenizer, SpecialTextView
 
 
 _log = logging.getLogger("deliverance_b200.generation")
@@ -217,7 +217,7 @@ class Generation:
         self.has_tools = has_tools
         self.starts_in_reasoning = False  # the prompt ended inside <think> (set by submit)
         self.detok_plain = IncrementalDetokenizer(clm.tokenizer, skip_special=True)
-        self.detok_special = IncrementalDetokenizer(clm.tokenizer, skip_special=False)
+        self.detok_special = SpecialTextView(clm.tokenizer, self.detok_plain)
         self.request: Optional[Request] = None
         self.stopper: Optional[StopStringDetector] = None
 

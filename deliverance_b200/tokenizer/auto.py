@@ -281,3 +281,29 @@ class IncrementalDetokenizer:
         self.read = len(self.ids)
         self.text += delta
         return delta
+
+
+class SpecialTextView:
+    """Text of a generation WITH special tokens, kept next to the plain incremental detokeniser. Until the first special token
+    appears both texts are the same string, so nothing is decoded twice; the first special token starts a second incremental
+    detokeniser by replaying the ids seen so far (once)."""
+
+    def __init__(self, tokenizer: PreTrainedTokenizer, plain: IncrementalDetokenizer):
+        self.tk = tokenizer
+        self.plain = plain
+        self.own: Optional[IncrementalDetokenizer] = None
+
+    def push(self, token_id: int) -> None:
+        """Call BEFORE pushing the same token into the plain detokeniser."""
+        if self.own is not None:
+            self.own.push(token_id)
+        elif self.tk.is_special(token_id):
+            self.own = IncrementalDetokenizer(self.tk, skip_special=False)
+            for t in self.plain.ids:
+                self.own.push(t)
+            self.own.push(token_id)
+
+    @property
+    def text(self) -> str:
+        return self.plain.text if self.own is None else self.own.text
+

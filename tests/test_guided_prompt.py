@@ -213,3 +213,30 @@ def test_hf_common_chat_template_behaviours():
     c = PromptBuilder(tpl).add_user("hi!").add_assistant("hi!").add_user("again").add_assistant("hi!").continue_final_message().build().prompt
     assert c == "<|user|>hi!<|end|>\n<|assistant|>hi!<|end|>\n<|user|>again<|end|>\n<|assistant|>hi!"
     assert PromptBuilder().add_user("q").add_assistant("The answer is").continue_final_message().build().prompt.endswith("<|im_start|>assistant\nThe answer is")
+
+
+def test_special_text_view_equals_a_second_detokenizer(tmp_path):
+    """The text-with-special-tokens view must equal a full second incremental detokeniser at every step, before and after the
+    first special token, including multi-byte characters split over tokens."""
+    import random
+
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.tokenizer.auto import AutoTokenizer, IncrementalDetokenizer, SpecialTextView
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=1)
+    tok = AutoTokenizer.from_pretrained(d)  # byte-level fallback: ids 1 / 2 are <s> / </s>
+    rng = random.Random(3)
+    text_ids = tok.encode("héllo wörld 你好 🙂 plain ascii tail")
+    for specials_at in ([], [5], [0, 9, 10], [len(text_ids) - 1]):
+        ids = list(text_ids)
+        for p in specials_at:
+            ids.insert(p, rng.choice([1, 2]))
+        plain, ref = IncrementalDetokenizer(tok, skip_special=True), IncrementalDetokenizer(tok, skip_special=False)
+        view = SpecialTextView(tok, plain)
+        for t in ids:
+            view.push(t)
+            plain.push(t)
+            ref.push(t)
+            assert view.text == ref.text
+        assert (view.own is None) == (not specials_at) and plain.text == "héllo wörld 你好 🙂 plain ascii tail"
