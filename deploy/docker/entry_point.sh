@@ -1,7 +1,11 @@
 #!/bin/sh
 # MODEL (directory under /models or absolute path) and optional TP_SIZE (GPUs of this node) select what is served.
 set -e
-MODEL="${MODEL:?set MODEL to a model directory}"
+CONFIG="${CONFIG:-}"   # optional .properties file (models, KV cache, auth); replaces MODEL
+if [ -n "$CONFIG" ]; then
+  exec python -m deliverance_b200.server --config "$CONFIG" --models-root "${MODELS_ROOT:-/models}" --host 0.0.0.0 ${SERVER_ARGS:-}
+fi
+MODEL="${MODEL:?set MODEL to a model directory (or CONFIG to a .properties file)}"
 PORT="${PORT:-8080}"
 TP_SIZE="${TP_SIZE:-1}"
 EXTRA="${SERVER_ARGS:-}"
