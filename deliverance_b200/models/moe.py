@@ -38,6 +38,7 @@ def moe_forward(model, i: int, lw, x: torch.Tensor) -> torch.Tensor:
             lambda e, rows: ops.linear(rows, lw.experts_gate_up[e]),
             lambda e, h: ops.linear(h, lw.experts_down[e]),
             ne, cfg.hidden_act,
+            (lambda e, rows: ops.linear_act(rows, lw.experts_gate_up[e], cfg.hidden_act)) if lw.fused_act_experts else None,
         )
     if ne != E:
         y = model.tp.all_reduce(f"layer.{i}.moe.combine", y)
@@ -63,10 +64,16 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
         ops._count(2)
     gu_w, down_w = lw.experts_gate_up_grouped, lw.experts_down_grouped
     small = bn <= 64  # decode-sized groups: split K so that more CTAs stream weights
-    with st("moe.gate_up"):
-        gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
-    with st("moe.activation_multiply"):
-        hmid = ops.act_mul(gu, act)
+    if lw.fused_act_experts and bn >= 16:
+        with st("moe.gate_up"):  # act(gate) * up in the grouped GEMM's epilogue (interleaved expert rows)
+            hmid = gu_w.run_act(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1, act)
+    else:
+        if lw.fused_act_experts:
+            raise RuntimeError("interleaved expert weights need the tensor-core grouped GEMM (token tile >= 16)")
+        with st("moe.gate_up"):
+            gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
+        with st("moe.activation_multiply"):
+            hmid = ops.act_mul(gu, act)
     with st("moe.down"):
         ys = down_w.run(hmid, items, bn, max(1, min(8, down_w.K // 1024)) if small else 1)
     with st("moe.combine"):

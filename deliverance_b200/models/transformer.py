@@ -64,6 +64,7 @@ class LayerWeights:
     mamba: Optional[dict] = None
     lora: dict = field(default_factory=dict)  # projection name -> LoraSlot
     fused_act: bool = False  # gate_up holds interleaved rows and the GEMM epilogue applies the gated activation
+    fused_act_experts: bool = False  # the same for the routed experts' gate|up weights
 
 
 def _cat_weights(parts: list) -> "torch.Tensor | Q4Tensor":
@@ -212,13 +213,13 @@ class DecoderModel:
             lw.router = self._lin(loader.load(p + "block_sparse_moe.gate.weight"))
             for e in range(e0, e0 + ne):
                 ep_ = p + f"block_sparse_moe.experts.{e}."
-                lw.experts_gate_up.append(self._lin(_cat_weights([get(ep_ + "w1.weight"), get(ep_ + "w3.weight")])))
+                lw.experts_gate_up.append(self._lin(self._gate_up_rows(lw, get(ep_ + "w1.weight"), get(ep_ + "w3.weight"))))
                 lw.experts_down.append(self._lin(get(ep_ + "w2.weight")))
         elif mt == "qwen3_moe" and cfg.is_sparse_layer(i):
             lw.router = self._lin(loader.load(p + "mlp.gate.weight"))
             for e in range(e0, e0 + ne):
                 ep_ = p + f"mlp.experts.{e}."
-                lw.experts_gate_up.append(self._lin(_cat_weights([get(ep_ + "gate_proj.weight"), get(ep_ + "up_proj.weight")])))
+                lw.experts_gate_up.append(self._lin(self._gate_up_rows(lw, get(ep_ + "gate_proj.weight"), get(ep_ + "up_proj.weight"))))
                 lw.experts_down.append(self._lin(get(ep_ + "down_proj.weight")))
         elif mt == "granitemoehybrid":
             lw.shared_gate_up = self._lin(get(p + "shared_mlp.input_linear.weight"))
@@ -243,6 +244,15 @@ class DecoderModel:
             lw.experts_gate_up_grouped = ops.GroupedLinearWeight(lw.experts_gate_up)
             lw.experts_down_grouped = ops.GroupedLinearWeight(lw.experts_down)
             lw.experts_gate_up, lw.experts_down = [], []
+
+    def _gate_up_rows(self, lw, gate, up):
+        """Rows of one expert's gate|up projection: concatenated, or (opt-in) interleaved per 64 outputs for the GEMM epilogue
+        activation; the layer remembers which (all experts of a layer share the choice)."""
+        # (ranks that hold very many experts may route decode batches to the CUDA-core grouped GEMV, which has no such epilogue)
+        if self.fused_act and gate.shape[0] % 64 == 0 and ops.fused_act_kind(self.cfg.hidden_act) and (lw.n_local_experts or 0) < 96:
+            lw.fused_act_experts = True
+            return ops.interleave_gate_up(gate, up)
+        return _cat_weights([gate, up])
 
     def _load_mamba(self, loader, p) -> dict:
         f32 = lambda n: self._dev(loader.load_dense(p + n), torch.float32)  # noqa: E731

@@ -430,6 +430,12 @@ class GroupedLinearWeight:
         _count()
         return self.handle.run_grouped(xs, items, self.N, bn, splits, out)
 
+    def run_act(self, xs: torch.Tensor, items: torch.Tensor, bn: int, splits: int, act: str) -> torch.Tensor:
+        """Grouped gate|up projection with ``act(gate) * up`` in the epilogue; the experts' rows must be in the order of
+        :func:`interleave_gate_up`. Returns ``[rows, N / 2]``."""
+        _count()
+        return self.handle.run_grouped_act(xs, items, self.N, bn, splits, fused_act_kind(act))
+
 
 def moe_token_tile(rows: int, local_experts: int) -> int:
     """Token tile (UMMA N) of the grouped GEMM for ``rows`` routed rows spread over ``local_experts`` experts."""

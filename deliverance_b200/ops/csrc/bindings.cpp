@@ -187,6 +187,22 @@ class GemmWeight {
     check_last_error("grouped gemm launch");
     return out;
   }
+  // Grouped gate | up projection with act(gate) * up in the epilogue (every expert's rows interleaved per tile); [rows, n / 2].
+  Tensor run_grouped_act(const Tensor& xs, const Tensor& items, int64_t n_per_expert, int64_t bn, int64_t splits, int64_t act) {
+    TORCH_CHECK(xs.is_cuda() && xs.scalar_type() == at::kBFloat16 && xs.dim() == 2 && xs.size(1) == desc_.K && xs.stride(1) == 1, "xs must be bf16 [rows, K]");
+    TORCH_CHECK(xs.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(xs.data_ptr()) & 15) == 0, "xs rows must be 16-byte aligned");
+    TORCH_CHECK(items.is_cuda() && items.scalar_type() == at::kInt && items.dim() == 2 && items.size(1) == 4 && items.is_contiguous(), "items must be int32 [n, 4]");
+    TORCH_CHECK(n_per_expert > 0 && n_per_expert % 128 == 0 && desc_.N % n_per_expert == 0, "gate|up rows per expert must be a multiple of 128");
+    TORCH_CHECK(bn >= 16, "the fused activation needs the tensor-core tiles (token tile >= 16)");
+    c10::cuda::CUDAGuard guard(xs.device());
+    Tensor out = torch::empty({xs.size(0), n_per_expert / 2}, xs.options());
+    DeviceScratch& s = scratch_for(xs.device().index());
+    dlv::gemm_tc_run_grouped_act(&desc_, static_cast<int>(n_per_expert), xs.data_ptr(), static_cast<int>(xs.size(0)), static_cast<int>(xs.stride(0)),
+                                 out.data_ptr(), static_cast<int>(out.stride(0)), items.data_ptr<int>(), static_cast<int>(items.size(0)),
+                                 static_cast<int>(bn), static_cast<int>(splits), static_cast<int>(act), s.status.data_ptr<int>(), cur_stream());
+    check_last_error("grouped gemm (fused activation) launch");
+    return out;
+  }
   // Row-parallel projection fused with the tensor-parallel sum: every rank calls this with its K-shard; `out` holds the
   // all-reduced result on every rank. Returns false (nothing launched) when the shape is outside the fused path.
   bool run_tp(const Tensor& x, Tensor& out, const TpComm& comm, c10::optional<Tensor> bias) {
@@ -684,6 +700,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
       .def("run_act", &GemmWeight::run_act, py::arg("x"), py::arg("act"))
+      .def("run_grouped_act", &GemmWeight::run_grouped_act, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits"),
+           py::arg("act"))
       .def("run_grouped", &GemmWeight::run_grouped, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits") = 1,
            py::arg("out") = py::none())
       .def_property_readonly("N", &GemmWeight::n)

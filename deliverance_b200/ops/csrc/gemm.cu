@@ -409,6 +409,42 @@ void gemm_tc_run_grouped(const GemmWeightDesc* w, int n_per_expert, const void* 
 #undef DLV_LAUNCH
 }
 
+// Grouped gate | up projection with the gated activation in the epilogue: every expert's rows are interleaved per 128-row tile
+// (64 gate rows, then the 64 up rows of the same outputs); out is [rows, n_per_expert / 2].
+void gemm_tc_run_grouped_act(const GemmWeightDesc* w, int n_per_expert, const void* x, int rows, int ldx, void* out, int ldo,
+                             const int* items, int max_items, int bn, int splits, int act, int* status, cudaStream_t st) {
+  if (rows <= 0 || max_items <= 0) return;
+  if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
+  if (max_items > 65535) throw std::runtime_error("grouped gemm: work list too long");
+  if (n_per_expert % kGemmBM != 0) throw std::runtime_error("fused activation: gate|up rows per expert must be a multiple of 128");
+  if (act != 1 && act != 2) throw std::runtime_error("fused activation: unknown activation");
+  GemmParams p = {};
+  p.M = rows;
+  p.N = n_per_expert;
+  p.K = w->K;
+  p.kb_total = (w->K + kGemmBK - 1) / kGemmBK;
+  p.n_tiles = n_per_expert / kGemmBM;
+  p.m_tiles = max_items;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_f32 = 0;
+  p.status = status;
+  p.grp_items = reinterpret_cast<const int4*>(items);
+  p.act_kind = act;
+#define DLV_LAUNCH(BNV)                                                                    \
+  if (w->is_q4) run_grouped<true, BNV, true>(w, x, rows, ldx, p, max_items, splits, st);   \
+  else run_grouped<false, BNV, true>(w, x, rows, ldx, p, max_items, splits, st)
+  switch (bn) {
+    case 16: DLV_LAUNCH(16); break;
+    case 32: DLV_LAUNCH(32); break;
+    case 64: DLV_LAUNCH(64); break;
+    case 128: DLV_LAUNCH(128); break;
+    case 256: DLV_LAUNCH(256); break;
+    default: throw std::runtime_error("grouped gemm: token tile must be 16, 32, 64, 128 or 256");
+  }
+#undef DLV_LAUNCH
+}
+
 // ------------------------------------------------------------------------------------------------ CUDA-core GEMV
 // One warp per weight row, MT tokens. fp32 accumulation; JQ4 blocks are expanded in registers.
 template <int MT, bool Q4>

@@ -41,6 +41,8 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
                  const GemmTpArgs* tp = nullptr);
 // Grouped (mixture-of-experts) GEMM over rows sorted by expert; `w` stacks the local experts (JQ4: each expert padded to whole
 // 128-row tiles), `items` is the device work list of launch_moe_items built with the same token tile `bn`.
+void gemm_tc_run_grouped_act(const GemmWeightDesc* w, int n_per_expert, const void* x, int rows, int ldx, void* out, int ldo,
+                             const int* items, int max_items, int bn, int splits, int act, int* status, cudaStream_t st);
 // gate | up projection with act(gate) * up computed in the epilogue (weights interleaved per tile; see gemm.cu)
 void gemm_tc_run_act(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, int act, float* ws, size_t ws_floats,
                      int* counters, int n_counters, int* status, cudaStream_t st);

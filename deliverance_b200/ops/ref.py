@@ -185,15 +185,16 @@ def moe_route(router_logits: torch.Tensor, k: int, mode: str, renorm: bool):
     return w, idx
 
 
-def moe_experts(x, weights, idx, gate_up_fn, down_fn, num_experts, act):
-    """Group tokens by expert, run gate|up -> act*mul -> down per expert, scatter-add with the route weight."""
+def moe_experts(x, weights, idx, gate_up_fn, down_fn, num_experts, act, gated_fn=None):
+    """Group tokens by expert, run gate|up -> act*mul -> down per expert, scatter-add with the route weight. ``gated_fn(e, rows)``
+    replaces gate|up + act*mul when the expert weights are stored in the interleaved layout of the fused epilogue."""
     T, Hd = x.shape
     out = torch.zeros(T, Hd, dtype=torch.float32, device=x.device)
     for e in range(num_experts):
         tok, slot = torch.nonzero(idx == e, as_tuple=True)
         if tok.numel() == 0:
             continue
-        h = act_mul(gate_up_fn(e, x[tok]), act)
+        h = gated_fn(e, x[tok]) if gated_fn is not None else act_mul(gate_up_fn(e, x[tok]), act)
         y = down_fn(e, h).float()
         out.index_add_(0, tok, y * weights[tok, slot].unsqueeze(1))
     return out.to(x.dtype)

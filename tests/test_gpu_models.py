@@ -135,3 +135,27 @@ def test_generate_gpu_graphs_vs_eager(tmp_path, family):
         res.append([r.token_ids for r in rs])
         ops.check_status(0)
     assert res[0] == res[1]
+
+
+@pytest.mark.skipif(__import__("os").environ.get("DLV_TEST_FUSED_ACT") != "1",
+                    reason="epilogue activation: opt-in until checked on a B200 (DLV_TEST_FUSED_ACT=1)")
+@pytest.mark.parametrize("family", ["qwen3", "gemma2", "mixtral", "qwen3_moe"])
+def test_fused_activation_models_gpu(tmp_path, family, monkeypatch):
+    """Models loaded with the interleaved gate|up layout (activation in the GEMM epilogue) against the default layout."""
+    d = str(tmp_path / family)
+    over = dict(hidden_size=128) if family in ("qwen3", "qwen3_moe", "gemma2") else dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2)
+    write_tiny_model(d, family, seed=9, std=0.05, quantize=family in ("qwen3", "qwen3_moe"), **over)
+    cfg = load_config(d)
+    plain = DecoderModel(cfg, "cuda:0").load(WeightLoader(d))
+    monkeypatch.setenv("DLV_FUSED_ACT", "1")
+    fused = DecoderModel(cfg, "cuda:0").load(WeightLoader(d))
+    assert any(lw.fused_act or lw.fused_act_experts for lw in fused.layers)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, 250, (n,), generator=g).tolist() for n in (70, 33, 5)]
+    outs = []
+    for m in (plain, fused):
+        eng = Engine(m, EngineConfig(num_pages=128, max_batch_tokens=96))
+        outs.append([r.token_ids for r in eng.generate_batch(prompts, GeneratorParameters(max_tokens=8))])
+        ops.check_status(0)
+    agree = sum(a == b for x, y in zip(*outs) for a, b in zip(x, y)) / sum(len(x) for x in outs[0])
+    assert agree > 0.9, (agree, outs)

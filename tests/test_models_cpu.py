@@ -164,7 +164,7 @@ def test_gemma4_matches_hf(tmp_path, variant):
         assert nested.extra["shared_from"] == cfg.extra["shared_from"] == [-1, -1, -1, 1, 1, 2] and nested.eos_token_ids == (1, 106)
 
 
-@pytest.mark.parametrize("family,quantize", [("llama", False), ("gemma2", False), ("qwen3", True)])
+@pytest.mark.parametrize("family,quantize", [("llama", False), ("gemma2", False), ("qwen3", True), ("mixtral", False), ("qwen3_moe", True)])
 def test_fused_activation_layout_matches_separate_kernels(tmp_path, family, quantize, monkeypatch):
     """Opt-in gate|up layout for the GEMM epilogue activation (rows interleaved per 64 outputs): on the oracle path the model
     must produce the same logits as with the concatenated layout and the separate activation kernel."""
@@ -176,8 +176,9 @@ def test_fused_activation_layout_matches_separate_kernels(tmp_path, family, quan
     plain, eng = _ours(d, chunk=4096)
     monkeypatch.setenv("DLV_FUSED_ACT", "1")
     fused, eng2 = _ours(d, chunk=4096)
-    assert all(lw.fused_act for lw in fused.layers) and not any(lw.fused_act for lw in plain.layers)
-    assert fused.layers[0].gate_up.q4 == quantize
+    moe = family in ("mixtral", "qwen3_moe")
+    assert all(lw.fused_act_experts if moe else lw.fused_act for lw in fused.layers) and not any(lw.fused_act or lw.fused_act_experts for lw in plain.layers)
+    assert (fused.layers[0].experts_gate_up[0] if moe else fused.layers[0].gate_up).q4 == quantize
     batch = make_batch([{"tokens": PROMPT, "start": 0, "pages": [1, 2], "state_slot": 0}], 32, "cpu")
     a = plain.forward(batch, eng.kv, all_rows=True)
     b = fused.forward(batch, eng2.kv, all_rows=True)
