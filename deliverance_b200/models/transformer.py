@@ -104,6 +104,8 @@ class DecoderModel:
         self.shard_head = True  # split the output head over the vocabulary under tensor parallelism
         # opt-in (DLV_FUSED_ACT=1): act(gate) * up inside the gate|up GEMM epilogue instead of a separate kernel
         self.fused_act = os.environ.get("DLV_FUSED_ACT", "0") == "1"
+        # opt-in (DLV_FUSED_ROPE=1, head_dim 128): q/k norm + rotary embedding + KV write inside the q|k|v GEMM epilogue
+        self.fused_rope = os.environ.get("DLV_FUSED_ROPE", "0") == "1" and cfg.head_dim == 128 and cfg.use_rope
         self.vocab_shard: Optional[tuple] = None
         self._moe_impl = None
 
@@ -336,16 +338,22 @@ class DecoderModel:
 
     def attention(self, i: int, lw: LayerWeights, x: torch.Tensor, batch: ForwardBatch, kv) -> torch.Tensor:
         cfg = self.cfg
-        with self._stage("causalselfattention.qkv_projection"):
-            qkv = ops.linear(x, lw.qkv)
-            if lw.lora:
-                qkv = self._lora(lw, "qkv", x, qkv)
         k_cache, v_cache = kv.layer(i)
         local_rope = lw.kind == "sliding" and self.cos_local is not None
         cos, sin = (self.cos_local, self.sin_local) if local_rope else (self.cos, self.sin)
-        with self._stage("causalselfattention.rope"):
-            q = ops.rope_kv(qkv, batch.positions, batch.slots, lw.q_norm, lw.k_norm, cos, sin, k_cache, v_cache,
-                            self.n_heads, self.n_kv, cfg.head_dim, cfg.norm_eps, cfg.norm_weight_offset)
+        if self.fused_rope and "qkv" not in lw.lora:
+            # opt-in: norm + rotary + cache write in the projection's epilogue (one launch instead of two, q is written once)
+            with self._stage("causalselfattention.qkv_projection"):
+                q = ops.linear_rope_kv(x, lw.qkv, batch.positions, batch.slots, lw.q_norm, lw.k_norm, cos, sin, k_cache, v_cache,
+                                       self.n_heads, self.n_kv, cfg.head_dim, cfg.norm_eps, cfg.norm_weight_offset)
+        else:
+            with self._stage("causalselfattention.qkv_projection"):
+                qkv = ops.linear(x, lw.qkv)
+                if lw.lora:
+                    qkv = self._lora(lw, "qkv", x, qkv)
+            with self._stage("causalselfattention.rope"):
+                q = ops.rope_kv(qkv, batch.positions, batch.slots, lw.q_norm, lw.k_norm, cos, sin, k_cache, v_cache,
+                                self.n_heads, self.n_kv, cfg.head_dim, cfg.norm_eps, cfg.norm_weight_offset)
         window = cfg.window(i)
         with self._stage("causalselfattention.score_value"):
             if batch.is_decode:

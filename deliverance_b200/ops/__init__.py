@@ -310,6 +310,18 @@ def rope_kv(qkv, positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cach
     return q.reshape(qkv.shape[0], H * D)
 
 
+def linear_rope_kv(x, w: LinearWeight, positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset=0.0):
+    """q|k|v projection + per-head q/k RMSNorm + RoPE + paged cache write as ONE kernel on CUDA (the GEMM epilogue does the head
+    work: a 128-row weight tile is one head, so ``D`` must be 128); the oracle path composes the separate operators. Returns q
+    ``[T, H*D]``."""
+    if _cuda(x):
+        if D != 128:
+            raise ValueError("the fused q/k/v epilogue needs head_dim 128")
+        _count()
+        return w.handle().run_qkv(x, positions.to(torch.int32), slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, eps, norm_offset, w.bias)
+    return rope_kv(linear(x, w), positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset)
+
+
 def decode_splits(num_seqs: int, kv_heads: int, max_ctx: int, sms: int = 148) -> int:
     """Split-KV factor: enough CTAs for two waves, at least four 32-key tiles per split."""
     ctas = max(1, num_seqs * kv_heads)

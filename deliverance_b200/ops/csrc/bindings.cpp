@@ -187,6 +187,65 @@ class GemmWeight {
     check_last_error("grouped gemm launch");
     return out;
   }
+  // q | k | v projection with per-head RMSNorm, rotary embedding and the paged KV write in the epilogue (head_dim 128). Returns the
+  // query heads [M, H * 128]; K and V go straight into the cache rows `slots`.
+  Tensor run_qkv(const Tensor& x, const Tensor& positions, const Tensor& slots, c10::optional<Tensor> q_norm_w, c10::optional<Tensor> k_norm_w,
+                 c10::optional<Tensor> cos_t, c10::optional<Tensor> sin_t, Tensor& k_cache, Tensor& v_cache, int64_t H, int64_t KV, double eps,
+                 double norm_offset, c10::optional<Tensor> bias) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(1) == desc_.K && x.stride(1) == 1, "x must be bf16 [M, K]");
+    TORCH_CHECK(x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x rows must be 16-byte aligned");
+    TORCH_CHECK(desc_.N == (H + 2 * KV) * 128, "weight rows must be (H + 2 KV) * 128 (head_dim 128)");
+    const int M = static_cast<int>(x.size(0));
+    TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == at::kInt && positions.numel() == M, "positions must be int32 [M]");
+    TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kLong && slots.numel() == M, "slots must be int64 [M]");
+    check_bf16(k_cache, "k_cache");
+    check_bf16(v_cache, "v_cache");
+    TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(1) == KV && k_cache.size(3) == 128 && k_cache.is_contiguous(), "cache must be contiguous [pages, KV, page, 128]");
+    TORCH_CHECK(v_cache.sizes() == k_cache.sizes() && v_cache.is_contiguous(), "k/v cache shape mismatch");
+    dlv::GemmQkvArgs a = {};
+    a.positions = positions.data_ptr<int>();
+    a.slots = reinterpret_cast<const long long*>(slots.data_ptr<int64_t>());
+    if (q_norm_w.has_value()) {
+      check_bf16(q_norm_w.value(), "q_norm");
+      check_bf16(k_norm_w.value(), "k_norm");
+      TORCH_CHECK(q_norm_w.value().numel() == 128 && k_norm_w.value().numel() == 128, "q/k norm weights must have 128 entries");
+      a.q_norm_w = q_norm_w.value().data_ptr();
+      a.k_norm_w = k_norm_w.value().data_ptr();
+    }
+    a.max_pos = 1;
+    if (cos_t.has_value()) {
+      check_cuda(cos_t.value(), "cos");
+      check_cuda(sin_t.value(), "sin");
+      TORCH_CHECK(cos_t.value().scalar_type() == at::kFloat && cos_t.value().dim() == 2 && cos_t.value().is_contiguous() &&
+                  sin_t.value().sizes() == cos_t.value().sizes() && sin_t.value().is_contiguous(), "cos/sin must be contiguous fp32 [max_pos, rot/2]");
+      a.cos_t = cos_t.value().data_ptr<float>();
+      a.sin_t = sin_t.value().data_ptr<float>();
+      a.rot_half = static_cast<int>(cos_t.value().size(1));
+      a.max_pos = static_cast<int>(cos_t.value().size(0));
+      TORCH_CHECK(a.rot_half <= 64, "rotary dimension exceeds head_dim");
+    }
+    a.k_cache = k_cache.data_ptr();
+    a.v_cache = v_cache.data_ptr();
+    a.heads = static_cast<int>(H);
+    a.kv_heads = static_cast<int>(KV);
+    a.block_size = static_cast<int>(k_cache.size(2));
+    a.eps = static_cast<float>(eps);
+    a.norm_offset = static_cast<float>(norm_offset);
+    const float* bptr = nullptr;
+    if (bias.has_value()) {
+      TORCH_CHECK(bias.value().is_cuda() && bias.value().scalar_type() == at::kFloat && bias.value().numel() == desc_.N && bias.value().is_contiguous(), "bias must be fp32 [N]");
+      bptr = bias.value().data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor q = torch::empty({M, H * 128}, x.options());
+    if (M == 0) return q;
+    DeviceScratch& s = scratch_for(x.device().index());
+    dlv::gemm_tc_run_qkv(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), q.data_ptr(), static_cast<int>(q.stride(0)), bptr, &a,
+                         s.ws.data_ptr<float>(), static_cast<size_t>(s.ws.numel()), s.counters.data_ptr<int>(),
+                         static_cast<int>(s.counters.numel()), s.status.data_ptr<int>(), cur_stream());
+    check_last_error("gemm (fused q/k/v epilogue) launch");
+    return q;
+  }
   // Grouped gate | up projection with act(gate) * up in the epilogue (every expert's rows interleaved per tile); [rows, n / 2].
   Tensor run_grouped_act(const Tensor& xs, const Tensor& items, int64_t n_per_expert, int64_t bn, int64_t splits, int64_t act) {
     TORCH_CHECK(xs.is_cuda() && xs.scalar_type() == at::kBFloat16 && xs.dim() == 2 && xs.size(1) == desc_.K && xs.stride(1) == 1, "xs must be bf16 [rows, K]");
@@ -700,6 +759,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
       .def("run_act", &GemmWeight::run_act, py::arg("x"), py::arg("act"))
+      .def("run_qkv", &GemmWeight::run_qkv)
       .def("run_grouped_act", &GemmWeight::run_grouped_act, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits"),
            py::arg("act"))
       .def("run_grouped", &GemmWeight::run_grouped, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits") = 1,

@@ -102,13 +102,13 @@ int gemm_num_sms() {
 }
 
 // Number of clusters of `size` CTAs of this kernel that can be resident at once (0 when such a cluster cannot be scheduled).
-template <bool Q4, int BN, bool ACT = false>
+template <bool Q4, int BN, int EPI = 0>
 static int cluster_capacity(int size) {
   using L = GemmSmem<Q4, BN>;
   static int cap[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<Q4, BN, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<Q4, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     attr_done = true;
   }
@@ -129,7 +129,7 @@ static int cluster_capacity(int size) {
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       int n = 0;
-      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<Q4, BN, ACT>, &cfg);
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<Q4, BN, EPI>, &cfg);
       (void)cudaGetLastError();
       cap[size] = (e == cudaSuccess && n > 0) ? n : 0;
     }
@@ -137,7 +137,7 @@ static int cluster_capacity(int size) {
   return cap[size];
 }
 
-template <bool Q4, int BN, bool ACT = false>
+template <bool Q4, int BN, int EPI = 0>
 static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmParams p, float* ws, size_t ws_floats, int* counters,
                    int n_counters, int force_splits, cudaStream_t st, const GemmTpArgs* tp) {
   using L = GemmSmem<Q4, BN>;
@@ -154,7 +154,7 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
     double best = 1e30;
     for (int s = 1; s <= 8; ++s) {
       if (s > 1 && p.kb_total / s < 2) break;
-      const int cap = cluster_capacity<Q4, BN, ACT>(s);
+      const int cap = cluster_capacity<Q4, BN, EPI>(s);
       if (cap <= 0) continue;
       if (tp != nullptr && tp->size > 1 && (tiles > cap || tiles * s > tp->ncta_max)) continue;  // fused all-reduce: one wave
       const int waves = (tiles + cap - 1) / cap;
@@ -171,7 +171,7 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
   if (splits < 1) splits = 1;
   p.kb_per_split = (p.kb_total + splits - 1) / splits;
   splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
-  bool cluster = splits > 1 && !no_cluster && splits <= 8 && cluster_capacity<Q4, BN, ACT>(splits) > 0;
+  bool cluster = splits > 1 && !no_cluster && splits <= 8 && cluster_capacity<Q4, BN, EPI>(splits) > 0;
   if (splits > 1 && !cluster) {
     const size_t need = static_cast<size_t>(tiles) * splits * BN * kGemmBM;
     if (ws == nullptr || counters == nullptr || need > ws_floats || tiles > n_counters) {
@@ -179,14 +179,14 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
       p.kb_per_split = p.kb_total;
     }
   }
-  (void)cluster_capacity<Q4, BN, ACT>(1);  // sets the shared-memory attribute
+  (void)cluster_capacity<Q4, BN, EPI>(1);  // sets the shared-memory attribute
   if (tp != nullptr && tp->size > 1) {
     // fused all-reduce: partial tiles must come from a single split or a cluster, and the grid must be resident at once
     if (splits > 1 && !cluster) {
       splits = 1;
       p.kb_per_split = p.kb_total;
     }
-    const int cap = cluster_capacity<Q4, BN, ACT>(splits > 1 ? splits : 1);
+    const int cap = cluster_capacity<Q4, BN, EPI>(splits > 1 ? splits : 1);
     if (tiles > cap || tiles * splits > tp->ncta_max) throw std::runtime_error("fused tensor-parallel GEMM: grid does not fit in one wave");
     p.tp_size = tp->size;
     p.tp_rank = tp->rank;
@@ -249,7 +249,7 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<Q4, BN, ACT>, w->map_w, map_x, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<Q4, BN, EPI>, w->map_w, map_x, p);
   if (e != cudaSuccess) throw std::runtime_error(std::string("gemm launch: ") + cudaGetErrorString(e));
 }
 
@@ -321,8 +321,8 @@ void gemm_tc_run_act(const GemmWeightDesc* w, const void* x, int M, int ldx, voi
   p.status = status;
   p.act_kind = act;
 #define DLV_LAUNCH(BNV)                                                                                           \
-  if (w->is_q4) run_tc<true, BNV, true>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, 0, st, nullptr);     \
-  else run_tc<false, BNV, true>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, 0, st, nullptr)
+  if (w->is_q4) run_tc<true, BNV, 1>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, 0, st, nullptr);     \
+  else run_tc<false, BNV, 1>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, 0, st, nullptr)
   switch (BN) {
     case 16: DLV_LAUNCH(16); break;
     case 32: DLV_LAUNCH(32); break;
@@ -336,15 +336,15 @@ void gemm_tc_run_act(const GemmWeightDesc* w, const void* x, int M, int ldx, voi
 // ------------------------------------------------------------------------------------------------ grouped (MoE) GEMM
 // out[r, :] = xs[r, :] @ W[expert(r)]^T for rows grouped by expert. `items` is the device work list built by
 // launch_moe_items with the same token tile `bn`; `max_items` bounds it (unused slots return at once).
-template <bool Q4, int BN, bool ACT = false>
+template <bool Q4, int BN, int EPI = 0>
 static void run_grouped(const GemmWeightDesc* w, const void* x, int rows, int ldx, GemmParams p, int max_items, int splits, cudaStream_t st) {
   using L = GemmSmem<Q4, BN>;
   if (splits > p.kb_total / 2) splits = p.kb_total / 2;
   if (splits < 1) splits = 1;
-  while (splits > 1 && cluster_capacity<Q4, BN, ACT>(splits) <= 0) --splits;
+  while (splits > 1 && cluster_capacity<Q4, BN, EPI>(splits) <= 0) --splits;
   p.kb_per_split = (p.kb_total + splits - 1) / splits;
   splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
-  (void)cluster_capacity<Q4, BN, ACT>(1);  // sets the shared-memory attribute
+  (void)cluster_capacity<Q4, BN, EPI>(1);  // sets the shared-memory attribute
   p.splits = splits;
   p.cluster_reduce = splits > 1 ? 1 : 0;
   p.wq = w->is_q4 ? static_cast<const uint8_t*>(w->data) : nullptr;
@@ -374,7 +374,7 @@ static void run_grouped(const GemmWeightDesc* w, const void* x, int rows, int ld
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<Q4, BN, ACT>, w->map_w, map_x, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<Q4, BN, EPI>, w->map_w, map_x, p);
   if (e != cudaSuccess) throw std::runtime_error(std::string("grouped gemm launch: ") + cudaGetErrorString(e));
 }
 
@@ -409,6 +409,53 @@ void gemm_tc_run_grouped(const GemmWeightDesc* w, int n_per_expert, const void* 
 #undef DLV_LAUNCH
 }
 
+// q | k | v projection whose epilogue applies the per-head RMSNorm (optional), the rotary embedding (optional) and writes K / V
+// straight into the paged cache; only the query heads go to `q_out` [M, H * 128]. head_dim must be 128 (one weight tile = one head).
+void gemm_tc_run_qkv(const GemmWeightDesc* w, const void* x, int M, int ldx, void* q_out, int ldo, const float* bias, const GemmQkvArgs* a,
+                     float* ws, size_t ws_floats, int* counters, int n_counters, int* status, cudaStream_t st) {
+  if (M <= 0) return;
+  if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
+  if (w->N != (a->heads + 2 * a->kv_heads) * kGemmBM) throw std::runtime_error("fused q/k/v epilogue: weight rows must be (H + 2 KV) * 128");
+  if (ldo % 4 != 0) throw std::runtime_error("fused q/k/v epilogue: query row pitch must be a multiple of 4");
+  const int BN = pick_bn(M);
+  GemmParams p = {};
+  p.M = M;
+  p.N = w->N;
+  p.K = w->K;
+  p.kb_total = (w->K + kGemmBK - 1) / kGemmBK;
+  p.out = q_out;
+  p.ldo = ldo;
+  p.out_f32 = 0;
+  p.bias = bias;
+  p.status = status;
+  p.qk_positions = a->positions;
+  p.qk_slots = a->slots;
+  p.q_norm_w = static_cast<const __nv_bfloat16*>(a->q_norm_w);
+  p.k_norm_w = static_cast<const __nv_bfloat16*>(a->k_norm_w);
+  p.qk_cos = a->cos_t;
+  p.qk_sin = a->sin_t;
+  p.k_cache = static_cast<__nv_bfloat16*>(a->k_cache);
+  p.v_cache = static_cast<__nv_bfloat16*>(a->v_cache);
+  p.qk_heads = a->heads;
+  p.qk_kv_heads = a->kv_heads;
+  p.qk_block_size = a->block_size;
+  p.qk_rot_half = a->rot_half;
+  p.qk_max_pos = a->max_pos;
+  p.qk_eps = a->eps;
+  p.qk_norm_offset = a->norm_offset;
+#define DLV_LAUNCH(BNV)                                                                                        \
+  if (w->is_q4) run_tc<true, BNV, 2>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, 0, st, nullptr);     \
+  else run_tc<false, BNV, 2>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, 0, st, nullptr)
+  switch (BN) {
+    case 16: DLV_LAUNCH(16); break;
+    case 32: DLV_LAUNCH(32); break;
+    case 64: DLV_LAUNCH(64); break;
+    case 128: DLV_LAUNCH(128); break;
+    default: DLV_LAUNCH(256); break;
+  }
+#undef DLV_LAUNCH
+}
+
 // Grouped gate | up projection with the gated activation in the epilogue: every expert's rows are interleaved per 128-row tile
 // (64 gate rows, then the 64 up rows of the same outputs); out is [rows, n_per_expert / 2].
 void gemm_tc_run_grouped_act(const GemmWeightDesc* w, int n_per_expert, const void* x, int rows, int ldx, void* out, int ldo,
@@ -432,8 +479,8 @@ void gemm_tc_run_grouped_act(const GemmWeightDesc* w, int n_per_expert, const vo
   p.grp_items = reinterpret_cast<const int4*>(items);
   p.act_kind = act;
 #define DLV_LAUNCH(BNV)                                                                    \
-  if (w->is_q4) run_grouped<true, BNV, true>(w, x, rows, ldx, p, max_items, splits, st);   \
-  else run_grouped<false, BNV, true>(w, x, rows, ldx, p, max_items, splits, st)
+  if (w->is_q4) run_grouped<true, BNV, 1>(w, x, rows, ldx, p, max_items, splits, st);   \
+  else run_grouped<false, BNV, 1>(w, x, rows, ldx, p, max_items, splits, st)
   switch (bn) {
     case 16: DLV_LAUNCH(16); break;
     case 32: DLV_LAUNCH(32); break;

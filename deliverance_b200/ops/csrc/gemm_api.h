@@ -41,6 +41,21 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
                  const GemmTpArgs* tp = nullptr);
 // Grouped (mixture-of-experts) GEMM over rows sorted by expert; `w` stacks the local experts (JQ4: each expert padded to whole
 // 128-row tiles), `items` is the device work list of launch_moe_items built with the same token tile `bn`.
+// arguments of the q | k | v epilogue (per-head RMSNorm, rotary embedding, paged KV write); see gemm_tc_run_qkv
+struct GemmQkvArgs {
+  const int* positions;        // [M]
+  const long long* slots;      // [M] flat cache rows, < 0: skip the cache write
+  const void* q_norm_w;        // bf16 [128] or nullptr
+  const void* k_norm_w;
+  const float* cos_t;          // [max_pos, rot_half] or nullptr
+  const float* sin_t;
+  void* k_cache;               // bf16 [blocks, KV, block_size, 128]
+  void* v_cache;
+  int heads, kv_heads, block_size, rot_half, max_pos;
+  float eps, norm_offset;
+};
+void gemm_tc_run_qkv(const GemmWeightDesc* w, const void* x, int M, int ldx, void* q_out, int ldo, const float* bias, const GemmQkvArgs* a,
+                     float* ws, size_t ws_floats, int* counters, int n_counters, int* status, cudaStream_t st);
 void gemm_tc_run_grouped_act(const GemmWeightDesc* w, int n_per_expert, const void* x, int rows, int ldx, void* out, int ldo,
                              const int* items, int max_items, int bn, int splits, int act, int* status, cudaStream_t st);
 // gate | up projection with act(gate) * up computed in the epilogue (weights interleaved per tile; see gemm.cu)

@@ -80,6 +80,19 @@ struct GemmParams {
   // ---- gated activation in the epilogue (kernel template ACT): the weight rows of a tile are 64 gate rows followed by the 64 up
   // rows of the same outputs (interleaved at load time); out[m, 64 * tile + r] = act(gate) * up, ldo counts N / 2 columns ----
   int act_kind;  // 1: SiLU, 2: tanh-approximated GELU
+  // ---- q | k | v projection with per-head RMSNorm, rotary embedding and the paged KV write in the epilogue (kernel template
+  // EPI = 2; head_dim must be 128 so that one weight tile is one head): tiles 0 .. H-1 are query heads (written to out [M, H * 128]),
+  // the next KV tiles key heads (normalised, rotated, written to k_cache), the last KV tiles value heads (copied to v_cache) ----
+  const int* qk_positions;         // [M]
+  const long long* qk_slots;       // [M] flat cache row (block * block_size + offset), < 0: no cache write
+  const __nv_bfloat16* q_norm_w;   // [128] or nullptr
+  const __nv_bfloat16* k_norm_w;   // [128] or nullptr
+  const float* qk_cos;             // [max_pos, rot_half] or nullptr (no rotation)
+  const float* qk_sin;
+  __nv_bfloat16* k_cache;          // [blocks, KV, block_size, 128]
+  __nv_bfloat16* v_cache;
+  int qk_heads, qk_kv_heads, qk_block_size, qk_rot_half, qk_max_pos;
+  float qk_eps, qk_norm_offset;
 };
 
 template <bool Q4, int BN>
@@ -140,12 +153,14 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t c
   return v;
 }
 
-template <bool Q4, int BN, bool ACT = false>
+// EPI selects the epilogue: 0 = plain store (+ bias, + fused tensor-parallel sum), 1 = gated activation, 2 = q/k norm + rotary + KV write
+template <bool Q4, int BN, int EPI = 0>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K] (unused for JQ4, which streams p.wq)
                const __grid_constant__ CUtensorMap map_x,   // bf16 [M, K]
                const GemmParams p) {
   using L = GemmSmem<Q4, BN>;
+  constexpr bool ACT = EPI == 1, QKV = EPI == 2;
   constexpr int NW = L::kNW > 0 ? L::kNW : 1, NX = L::kNX, NR = L::kNR > 0 ? L::kNR : 1, NA = L::kNA, NI = L::kNI;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -536,7 +551,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       bias.z = n + 2 < p.N ? p.bias[n + 2] : 0.f;
       bias.w = n + 3 < p.N ? p.bias[n + 3] : 0.f;
     }
-    if constexpr (ACT) {
+    if constexpr (QKV) {
+      // ---- q | k | v heads: this tile is one head of 128 dims; a warp (32 lanes x 4 dims) holds a whole head of one token ----
+      // (host guarantees: head_dim 128, no tensor-parallel fusion; the column loop is warp-uniform, so the shuffles below are safe)
+      if (do_store) {
+        const int lane_e = t & 31;
+        const int head = n_tile;
+        const bool is_q = head < p.qk_heads, is_k = !is_q && head < p.qk_heads + p.qk_kv_heads;
+        const int kvh = is_q ? 0 : (is_k ? head - p.qk_heads : head - p.qk_heads - p.qk_kv_heads);
+        const __nv_bfloat16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+        float nwv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (nw != nullptr) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) nwv[e] = bf2f(nw[row4 + e]) + p.qk_norm_offset;
+        }
+        const bool rotate = (is_q || is_k) && p.qk_cos != nullptr;
+        const int dpair = row4 & 63;  // index of this thread's first dim inside its half
+        for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
+          const int m = m0 + col;
+          if (m >= m_lim) break;
+          const float4 a4 = column_acc(col);
+          float v[4] = {a4.x + bias.x, a4.y + bias.y, a4.z + bias.z, a4.w + bias.w};
+          if (nw != nullptr) {
+            float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float inv = rsqrtf(ss * (1.f / 128.f) + p.qk_eps);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = bf2f(f2bf(v[e] * inv * nwv[e]));  // rounded like a separate norm kernel would
+          }
+          if (rotate) {
+            int pos = p.qk_positions[m];
+            pos = pos < 0 ? 0 : (pos >= p.qk_max_pos ? p.qk_max_pos - 1 : pos);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);  // dim d +- 64 lives 16 lanes away
+              const int d = dpair + e;
+              if (d < p.qk_rot_half) {
+                const float c = p.qk_cos[static_cast<size_t>(pos) * p.qk_rot_half + d], sn = p.qk_sin[static_cast<size_t>(pos) * p.qk_rot_half + d];
+                v[e] = lane_e < 16 ? v[e] * c - other * sn : v[e] * c + other * sn;
+              }
+            }
+          }
+          uint2 pk;
+          pk.x = pack_bf162(v[0], v[1]);
+          pk.y = pack_bf162(v[2], v[3]);
+          if (is_q) {
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(m) * p.ldo + (head << 7) + row4) = pk;
+          } else {
+            const long long slot = p.qk_slots != nullptr ? p.qk_slots[m] : -1;
+            if (slot >= 0) {
+              const long long blk = slot / p.qk_block_size, off = slot % p.qk_block_size;
+              __nv_bfloat16* cache = is_k ? p.k_cache : p.v_cache;
+              *reinterpret_cast<uint2*>(cache + ((blk * p.qk_kv_heads + kvh) * p.qk_block_size + off) * 128 + row4) = pk;
+            }
+          }
+        }
+        if (splits > 1 && !p.cluster_reduce && t == 0) p.counters[ws_tile] = 0;
+      }
+    } else if constexpr (ACT) {
       // ---- gated activation: rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same 64 outputs ----
       // (host guarantees: no bias, no tensor-parallel fusion, N a multiple of 128, p.ldo = pitch of the [M, N / 2] output)
       if (do_store) {
@@ -603,7 +676,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       }
       if (splits > 1 && !p.cluster_reduce && t == 0) p.counters[ws_tile] = 0;
     }
-    if (!ACT && fused_tp) {
+    if (EPI == 0 && fused_tp) {
       // ---- GEMM + one-shot all-reduce over peer memory (host guarantees: N % 4 == 0, cluster or single split) ----
       const unsigned cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
       const unsigned call = *reinterpret_cast<volatile unsigned*>(p.tp_call);

@@ -276,3 +276,37 @@ def test_gemm_epilogue_gated_activation(M, I, K, q4, act):
     yr = ref.act_fn(act)(x.float() @ wg.t()) * (x.float() @ wu.t())
     assert y.shape == (M, I) and _rel(y.cpu(), yr) < 2e-2, _rel(y.cpu(), yr)
     assert torch.equal(y, ops.linear_act(x.to(DEV), lw, act))
+
+
+@pytest.mark.skipif(__import__("os").environ.get("DLV_TEST_FUSED_ROPE") != "1",
+                    reason="q|k|v epilogue (norm + rotary + KV write): opt-in until checked on a B200 (DLV_TEST_FUSED_ROPE=1)")
+@pytest.mark.parametrize("M,H,KV,K,q4,qk_norm,rot_half,bias", [(1, 4, 2, 256, True, True, 64, False), (7, 32, 8, 2560, True, True, 64, False),
+                                                                (64, 32, 8, 2560, True, True, 64, False), (64, 4, 1, 2560, True, False, 64, True),
+                                                                (200, 8, 2, 512, False, True, 32, True), (33, 4, 4, 4096, False, False, 64, False)])
+def test_gemm_epilogue_rope_kv(M, H, KV, K, q4, qk_norm, rot_half, bias):
+    """linear_rope_kv against the two separate kernels (projection, then rope_kv) on the same inputs: query heads and the
+    written cache rows must agree up to the bf16 rounding of the intermediate tensor."""
+    D, page = 128, 32
+    g = torch.Generator().manual_seed(M + H)
+    N = (H + 2 * KV) * D
+    qt, wd = _q4_weight(N, K, seed=N + K)
+    lw = (LinearWeight(qt) if q4 else LinearWeight(wd.to(torch.bfloat16))).to(DEV, torch.bfloat16)
+    lw.bias = torch.randn(N, generator=g).to(DEV) * 0.1 if bias else None
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    pos = torch.randint(0, 500, (M,), generator=g).to(torch.int32).to(DEV)
+    n_pages = (M + page - 1) // page + 2
+    perm = torch.randperm(n_pages * page, generator=g)[:M].to(torch.int64).to(DEV)
+    cos, sin = ref.rope_tables(D, 512, 10000.0, 1.0, rot_dim=2 * rot_half)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    qn = (1 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(DEV) if qk_norm else None
+    kn = (1 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(DEV) if qk_norm else None
+    caches = [torch.zeros(n_pages, KV, page, D, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    q_ref = ops.rope_kv(ops.linear(x, lw), pos, perm, qn, kn, cos, sin, caches[0], caches[1], H, KV, D, 1e-6, 0.0).clone()
+    q = ops.linear_rope_kv(x, lw, pos, perm, qn, kn, cos, sin, caches[2], caches[3], H, KV, D, 1e-6, 0.0)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert q.shape == (M, H * D) and _rel(q.float().cpu(), q_ref.float().cpu()) < 2e-2
+    assert _rel(caches[2].float().cpu(), caches[0].float().cpu()) < 2e-2 and _rel(caches[3].float().cpu(), caches[1].float().cpu()) < 2e-2
+    untouched = torch.ones(n_pages * page, dtype=torch.bool)
+    untouched[perm.cpu()] = False
+    assert caches[2].permute(0, 2, 1, 3).reshape(n_pages * page, -1)[untouched].abs().sum() == 0  # no stray cache rows

@@ -189,3 +189,22 @@ def test_fused_activation_layout_matches_separate_kernels(tmp_path, family, quan
     assert ops.fused_act_kind("silu") == 1 and ops.fused_act_kind("gelu_pytorch_tanh") == 2 and ops.fused_act_kind("relu") == 0
     with pytest.raises(ValueError):
         ops.interleave_gate_up(torch.zeros(100, 4), torch.zeros(100, 4))
+
+
+def test_fused_rope_path_composes_the_same_operators(tmp_path, monkeypatch):
+    """Opt-in q|k|v epilogue path: on the oracle path it must reproduce the default path exactly (same cache contents, same logits)."""
+    from deliverance_b200.models.batch import make_batch
+
+    d = str(tmp_path / "q")
+    write_tiny_model(d, "qwen3", seed=8, std=0.05, head_dim=128, hidden_size=128)
+    plain, eng = _ours(d, chunk=4096)
+    monkeypatch.setenv("DLV_FUSED_ROPE", "1")
+    fused, eng2 = _ours(d, chunk=4096)
+    assert fused.fused_rope and not plain.fused_rope
+    batch = make_batch([{"tokens": PROMPT, "start": 0, "pages": [1, 2], "state_slot": 0}], 32, "cpu")
+    a, b = plain.forward(batch, eng.kv, all_rows=True), fused.forward(batch, eng2.kv, all_rows=True)
+    assert torch.equal(a, b) and torch.equal(eng.kv.k[1], eng2.kv.k[1]) and torch.equal(eng.kv.v[0], eng2.kv.v[0])
+    monkeypatch.setenv("DLV_FUSED_ROPE", "1")
+    d64 = str(tmp_path / "l")
+    write_tiny_model(d64, "llama", seed=8)
+    assert not _ours(d64)[0].fused_rope  # head_dim 16: not eligible
