@@ -30,6 +30,10 @@
 // warps 2 + 20 = activation TMA producers, warps 3..18 = JQ4 dequant (one 32-element block per thread and stage) and epilogue
 // (tcgen05.ld -> fp32 tile in shared memory -> reduce over the cluster -> 8/16-byte global stores).
 //
+// Epilogue variants (template EPI): 0 = store (+ bias, + the tensor-parallel sum above); 1 = gated activation for gate|up weights whose
+// rows are interleaved per 64 outputs (act(gate) * up, half as many output columns); 2 = q|k|v heads of dimension 128: per-head
+// RMSNorm, rotary embedding and the paged KV-cache write happen on the staged tile, only the query heads are written to `out`.
+//
 // This replaces the reference's CPU kernels gemm_q8_q4 / gemm_bf16_q4 / gemm_bf16
 // (native/src/main/c/simd/vector_simd.c:339-633,1186-1411,1414-1668) and the WGSL gemm_q4 / gemm_i8q4_v5 shaders.
 #pragma once
