@@ -299,6 +299,27 @@ class PagedKVCache:
         free = self.allocator.available()
         return free >= n_pages or free + self.prefix.reclaimable(n_pages - free) >= n_pages
 
+    def audit(self, sequences) -> None:
+        """Consistency check for tests and debugging: every page's reference count must equal the number of sequences that list
+        it plus the number of prefix-cache entries that hold it; free pages have count 0 and are listed once; page 0 (scratch)
+        is never handed out. ``sequences``: iterables of page ids (the running requests' page lists). Raises AssertionError."""
+        want = [0] * self.num_pages
+        for pages in sequences:
+            for p in pages:
+                want[p] += 1
+        per_entry: dict = {}
+        for e in self.prefix.entries.values():
+            for p in e.pages:
+                want[p] += 1
+                per_entry[p] = per_entry.get(p, 0) + 1
+        assert per_entry == self.prefix.held, "prefix-cache holder counts out of date"
+        free = self.allocator.free
+        assert len(set(free)) == len(free) and 0 not in free, "free list has duplicates or the scratch page"
+        for p in range(1, self.num_pages):
+            assert self.allocator.ref[p] == want[p], f"page {p}: reference count {self.allocator.ref[p]}, holders {want[p]}"
+            assert (want[p] == 0) == (p in free) or want[p] > 0, f"page {p}: free-list membership does not match its count"
+        assert sum(1 for p in range(1, self.num_pages) if want[p] == 0) == len(free), "free page count mismatch"
+
     def alloc_state_slot(self) -> int:
         if not self.free_slots:
             raise MemoryError("no free recurrent-state slot")

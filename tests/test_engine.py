@@ -383,6 +383,7 @@ def test_memory_pressure_preempts_and_recomputes(tmp_path, family, lookahead):
                 reqs[i] = eng.add_request(p, fresh(q))
         if eng.has_work():
             eng.step()
+            eng.kv.audit([r.pages for r in eng.running])  # reference counts, holder counts and the free list stay consistent
         step += 1
     assert [r.output for r in reqs] == singles
     assert eng.metrics.get("preemptions", 0) > 0 and sum(r.preemptions for r in reqs) == eng.metrics["preemptions"]
@@ -470,3 +471,54 @@ def test_oom_fails_one_request_and_reset_returns_every_page(tiny):
     eng.kv.prefix.clear()
     assert eng.kv.allocator.available() == 4 and not eng.has_work() and a.finish_reason == FinishReason.ERROR and b.state == "finished"
     assert eng.generate([5, 6, 7], GeneratorParameters(max_tokens=3)).generated_tokens == 3  # usable afterwards
+
+
+def test_prefix_cache_random_operations_keep_reference_counts_consistent():
+    """Property test (hypothesis): arbitrary interleavings of sequence creation (with prefix hits), growth, caching, release and
+    eviction never break the page accounting, and everything comes back at the end."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    from deliverance_b200.kv.paged import PagedKVCache
+
+    layout = {"layers": 1, "kv_heads": 1, "head_dim": 64, "layer_kinds": ["attention"]}
+    ops_strategy = st.lists(st.tuples(st.sampled_from(["new", "grow", "store", "release", "evict"]), st.integers(0, 7), st.integers(1, 90)), max_size=60)
+
+    @settings(max_examples=60, deadline=None)
+    @given(ops_strategy, st.sampled_from(["FIXED_BLOCKS", "START_AND_END", "ANCHORS_AND_LARGEST"]))
+    def run(script, policy):
+        kv = PagedKVCache(layout, 24, "cpu", torch.float32, KvCacheSettings(block_size=32, policy=policy, max_prefix_tokens=4096, max_entries=6))
+        seqs: dict = {}
+        for op, key, n in script:
+            if op == "new" and key not in seqs:
+                toks = [3 + (key % 3)] * 40 + [10 + key] * n  # three families of shared 40-token heads
+                hit = kv.prefix.lookup("", toks)
+                pages = list(hit.pages) if hit is not None else []
+                try:
+                    kv.ensure_pages(pages, len(toks))
+                except MemoryError:
+                    kv.release_pages(pages)
+                    continue
+                seqs[key] = (toks, pages)
+            elif op == "grow" and key in seqs:
+                toks, pages = seqs[key]
+                toks.extend([20 + key] * n)
+                try:
+                    kv.ensure_pages(pages, len(toks))
+                except MemoryError:
+                    del toks[-n:]
+            elif op == "store" and key in seqs:
+                kv.prefix.store("", seqs[key][0], seqs[key][1])
+            elif op == "release" and key in seqs:
+                kv.release_pages(seqs.pop(key)[1])
+            elif op == "evict":
+                kv.prefix.evict_one()
+            kv.audit([p for _, p in seqs.values()])
+            assert kv.can_allocate(kv.allocator.available()) and not kv.can_allocate(kv.num_pages)
+        for _, pages in seqs.values():
+            kv.release_pages(pages)
+        kv.prefix.clear()
+        kv.audit([])
+        assert kv.allocator.available() == kv.num_pages - 1
+
+    run()
