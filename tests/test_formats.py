@@ -180,3 +180,47 @@ def test_lora_names_merge_and_delta(tmp_path):
     Ar, Bs = ad.resolved(n)
     y = apply_lora_delta(x, x @ base.t(), Ar, Bs)
     assert torch.allclose(y, x @ merged.t(), atol=1e-5)
+
+
+def test_jq4_properties_hypothesis():
+    """Property tests: the quantiser never errs by more than one step of its block, nibble 0 sits on the block's largest
+    magnitude, tile packing for the tensor-core GEMM is lossless for ragged shapes, and row interleaving commutes with packing."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    from deliverance_b200 import ops
+    from deliverance_b200.ckpt.jq4 import q4_dequantize
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.integers(1, 5), st.integers(1, 6), st.integers(0, 2**31 - 1), st.floats(1e-3, 50.0))
+    def quant(rows, blocks, seed, spread):
+        g = torch.Generator().manual_seed(seed)
+        w = torch.randn(rows, blocks * 32, generator=g) * spread
+        p, s = q4_quantize(w)
+        err = (q4_dequantize(p, s) - w).abs().reshape(rows, blocks, 32)
+        step = s.abs().reshape(rows, blocks, 1)
+        assert bool((err <= step * 1.0 + 1e-5 * spread).all())  # half a step from rounding, up to one where nibble 15 clamps
+        blk = w.reshape(rows, blocks, 32)
+        amax = blk.abs().argmax(dim=2, keepdim=True)
+        deq = q4_dequantize(p, s).reshape(rows, blocks, 32)
+        assert torch.allclose(deq.gather(2, amax), blk.gather(2, amax), rtol=1e-5, atol=1e-6 * spread)  # the extreme is exact (nibble 0 = -8)
+
+    @settings(max_examples=25, deadline=None)
+    @given(st.integers(1, 300), st.integers(1, 9), st.integers(0, 2**31 - 1))
+    def tiles(n, kblocks, seed):
+        g = torch.Generator().manual_seed(seed)
+        k = kblocks * 32
+        packed = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)
+        scales = torch.randn(n, k // 32, generator=g)
+        t = ops.prepack_q4(packed, scales)
+        assert t.shape == ((n + 127) // 128, (k + 127) // 128, 10240)
+        p2, s2 = ops.unpack_q4(t, n, k)
+        assert torch.equal(p2, packed) and torch.equal(s2, scales)
+
+    quant()
+    tiles()
+    g = torch.Generator().manual_seed(1)
+    pg, sg = q4_quantize(torch.randn(128, 64, generator=g))
+    pu, su = q4_quantize(torch.randn(128, 64, generator=g))
+    mixed = ops.interleave_gate_up(Q4Tensor(pg, sg, (128, 64)), Q4Tensor(pu, su, (128, 64)))
+    assert torch.equal(mixed.packed[64:128], pu[:64]) and torch.equal(mixed.scales[128:192], sg[64:128]) and mixed.shape == (256, 64)
