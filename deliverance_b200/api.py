@@ -32,7 +32,7 @@ from .models.transformer import DecoderModel
 from .parallel.context import SINGLE, TensorParallelContext
 from .params import FinishReason, GeneratorParameters, Response
 from .prompt.chat import PromptBuilder, PromptContext
-from .prompt.parsers import (Gemma4ToolCallParser, ReasoningTextSplitter, StopStringDetector, ToolCallParser, parse_gemma4_response,
+from .prompt.parsers import (Gemma4ToolCallParser, StopStringDetector, ToolCallParser, parse_gemma4_response,
                              parser_for_model, prompt_ends_inside_reasoning, split_reasoning)
 from .tokenizer.auto import AutoTokenizer, IncrementalDetokenizer, SpecialTextView
 
