@@ -298,9 +298,17 @@ def embedding(table, ids, scale=1.0, pos_table=None, pos=None, type_table=None, 
     return out.to(dtype or table.dtype)
 
 
+def _check_full_rotary(cos, D: int) -> None:
+    """The kernels rotate the pairs (d, d + D/2); a table that covers only part of the head (partial rotary embedding, where the
+    pairs lie inside the rotated sub-range) would silently mean something else, so it is refused. No supported family needs it."""
+    if cos is not None and cos.shape[1] * 2 != D:
+        raise NotImplementedError(f"rotary table covers {cos.shape[1] * 2} of {D} head dims: partial rotary embedding is not supported by the CUDA kernels")
+
+
 def rope_kv(qkv, positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset=0.0):
     """Per-head q/k RMSNorm (optional) + RoPE (optional) + paged cache write. Returns q ``[T, H*D]`` (a view on CUDA)."""
     if _cuda(qkv):
+        _check_full_rotary(cos, D)
         _count()
         require_ext().rope_kv(qkv, positions.to(torch.int32), slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps,
                               norm_offset)
@@ -317,6 +325,7 @@ def linear_rope_kv(x, w: LinearWeight, positions, slots, q_norm_w, k_norm_w, cos
     if _cuda(x):
         if D != 128:
             raise ValueError("the fused q/k/v epilogue needs head_dim 128")
+        _check_full_rotary(cos, D)
         _count()
         return w.handle().run_qkv(x, positions.to(torch.int32), slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, eps, norm_offset, w.bias)
     return rope_kv(linear(x, w), positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset)
