@@ -60,6 +60,7 @@ class AutoModelConfig:
     kv_pages: Optional[int] = None
     profile_stages: bool = False
 
+    decode_interleave: int = 0  # EngineConfig.decode_interleave
     kv_checkpoints: int = 4
     kv_anchors: tuple = (32, 64, 128)
     kv_compression: str = "NONE"
@@ -421,7 +422,7 @@ class AutoModelForCausalLM:
             conf = self.conf
             econf = EngineConfig(max_batch_tokens=conf.max_batch_size, max_seqs=conf.max_seqs, num_pages=conf.kv_pages,
                                  cuda_graphs=conf.cuda_graphs and not (conf.profile_stages or bool(os.environ.get("DELIVERANCE_PROFILE_STAGES"))),
-                                 kv=self.kv)
+                                 kv=self.kv, decode_interleave=conf.decode_interleave)
             engine = Engine(model, econf)
             tok = AutoTokenizer.from_pretrained(model_dir)
             return CausalLanguageModel(model, engine, tok, self.name or os.path.basename(os.path.normpath(model_dir)), self.sketches)

@@ -90,6 +90,9 @@ class EngineConfig:
     cuda_graphs: bool = True
     device_timeout_s: float = 120.0  # watchdog of the lookahead path: a step that does not finish in this time raises
     lookahead: bool = True  # overlap the host bookkeeping of step N with the device work of step N + 1 (greedy graph decode)
+    # 0: prefill work always goes first (best time to first token, running sequences wait while prompts are computed);
+    # k > 0: after k consecutive prefill steps one decode step runs for the sequences that are ready (bounded inter-token latency)
+    decode_interleave: int = 0
     kv: KvCacheSettings = field(default_factory=KvCacheSettings)
     max_state_slots: int = 0
 
@@ -128,6 +131,7 @@ class Engine:
         self._next_id = 0
         self._graphs: dict[int, dict] = {}
         self._failed: list[Request] = []  # requests failed inside a step (reported by step())
+        self._prefill_streak = 0
         self.metrics = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "prefill_tokens": 0, "decode_tokens": 0,
                         "graph_replays": 0, "kernel_launches": 0}
         # (a family that runs on the PyTorch operator set reads lengths on the host inside its forward: not capturable)
@@ -323,6 +327,10 @@ class Engine:
             r = self.waiting.pop(0)
             backlog += len(r.fill) - r.computed
         prefill = [r for r in self.running if r.computed < len(r.fill)]
+        k = self.config.decode_interleave
+        if prefill and k > 0 and self._prefill_streak >= k and any(r.computed >= len(r.fill) for r in self.running):
+            prefill = []  # the running sequences get a decode step before the next prompt chunk
+        self._prefill_streak = self._prefill_streak + 1 if prefill else 0
         if prefill:
             finished += self._drain()
             prefill = [r for r in prefill if r.state != FINISHED]

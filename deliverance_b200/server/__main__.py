@@ -23,6 +23,8 @@ def main() -> int:
     ap.add_argument("--basic-password", default=os.environ.get("DELIVERANCE_BASIC_PASSWORD"))
     ap.add_argument("--jwt-secret", default=os.environ.get("DELIVERANCE_JWT_SECRET"))
     ap.add_argument("--max-seqs", type=int, default=128)
+    ap.add_argument("--decode-interleave", type=int, default=0,
+                    help="after this many consecutive prompt-chunk steps run one decode step for the running sequences (0: prompts first)")
     a = ap.parse_args()
     conf = None
     head_quant, lora, kv = {}, {}, None
@@ -88,6 +90,7 @@ def main() -> int:
         if lora.get(d):
             b.with_lora_adapter(lora[d])
         b.conf.max_seqs = a.max_seqs
+        b.conf.decode_interleave = a.decode_interleave
         if tp is not None:
             b.with_tensor_parallel_context(tp)
         clm = b.build()

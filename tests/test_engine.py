@@ -522,3 +522,26 @@ def test_prefix_cache_random_operations_keep_reference_counts_consistent():
         assert kv.allocator.available() == kv.num_pages - 1
 
     run()
+
+
+def test_decode_interleave_bounds_the_wait_of_running_sequences(tiny):
+    """With decode_interleave = 1 a running sequence gets a token between the prompt chunks of later arrivals; with the default
+    it waits until the whole prompt backlog is computed. Outputs are the same either way."""
+    def run(k):
+        eng = _engine(tiny, pages=64, chunk=16, lookahead=False, decode_interleave=k)
+        eng.eos_ids = frozenset((-1,))
+        first = eng.add_request([5, 6, 7], GeneratorParameters(max_tokens=12))
+        while not first.output:
+            eng.step()
+        late = eng.add_request(list(range(3, 99)), GeneratorParameters(max_tokens=3))  # 96 tokens = 6 chunks of 16
+        trace = []
+        while eng.has_work():
+            before = len(first.output)
+            eng.step()
+            trace.append("d" if len(first.output) > before else "p")
+        return first.output, late.output, "".join(trace)
+
+    a_first, a_late, a_trace = run(0)
+    b_first, b_late, b_trace = run(1)
+    assert a_first == b_first and a_late == b_late
+    assert a_trace.startswith("pppppp") and "pp" not in b_trace and b_trace.count("p") == 6
