@@ -119,6 +119,8 @@ class LockstepRunner(EngineRunner):
     def close(self) -> None:
         self._stop.set()
         self.thread.join(timeout=10)
+        if not self.thread.is_alive():
+            self._drain_on_stop()
 
 
 class PromptIds(list):

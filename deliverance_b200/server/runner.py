@@ -120,6 +120,25 @@ class EngineRunner:
                 if s.generation.request.state == "finished":
                     self._finish(s)
 
+    def _drain_on_stop(self) -> None:
+        """The loop has ended: nobody will step the engine again, so callers still waiting are answered with an error instead of
+        running into their time-outs, and the engine gives its pages back."""
+        pending = list(self.active)
+        try:
+            while True:
+                pending.append(self.inbox.get_nowait())
+        except queue.Empty:
+            pass
+        for s in pending:
+            if not s.done.is_set():
+                self._finish(s, RuntimeError("server is shutting down"))
+        try:
+            self.clm.engine.reset()
+        except Exception:  # noqa: BLE001
+            pass
+
     def close(self) -> None:
         self._stop.set()
         self.thread.join(timeout=5)
+        if not self.thread.is_alive():
+            self._drain_on_stop()

@@ -813,3 +813,34 @@ def test_roofline_calculator(tmp_path):
     assert m1.weight_bytes < m64.weight_bytes  # one token touches two of the eight experts per layer
     g = parse_config(dict(SHAPES["gemma2-9b"]))
     assert rf.decode_step_cost(g, 1, 8000, "bf16", 1).kv_bytes < 42 * 8001 * 2 * 8 * 256 * 2  # sliding layers read at most the window
+
+
+def test_runner_close_answers_waiting_callers(tmp_path):
+    import threading
+    import time
+
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+    from deliverance_b200.params import GeneratorParameters
+    from deliverance_b200.server.runner import EngineRunner
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=3, std=0.05, max_position_embeddings=4096)
+    clm = AutoModelForCausalLM.from_pretrained(d, device="cpu")
+    clm.eos_ids, clm.engine.eos_ids = set(), frozenset((-1,))
+    runner = EngineRunner(clm)
+    out = {}
+
+    def call():
+        try:
+            out["r"] = runner.generate("long running request", GeneratorParameters(max_tokens=3000), None, "s", 120)
+        except Exception as e:  # noqa: BLE001
+            out["e"] = str(e)
+
+    t = threading.Thread(target=call)
+    t.start()
+    while not clm.engine.running:
+        time.sleep(0.01)
+    runner.close()
+    t.join(20)
+    assert not t.is_alive() and "shutting down" in out.get("e", "") and not clm.engine.has_work()
