@@ -23,6 +23,7 @@ def main() -> int:
     ap.add_argument("--basic-password", default=os.environ.get("DELIVERANCE_BASIC_PASSWORD"))
     ap.add_argument("--jwt-secret", default=os.environ.get("DELIVERANCE_JWT_SECRET"))
     ap.add_argument("--max-seqs", type=int, default=128)
+    ap.add_argument("--max-queue", type=int, default=0, help="refuse new requests with 429 while this many are in flight (0: no limit)")
     ap.add_argument("--decode-interleave", type=int, default=0,
                     help="after this many consecutive prompt-chunk steps run one decode step for the running sequences (0: prompts first)")
     a = ap.parse_args()
@@ -117,7 +118,8 @@ def main() -> int:
                                  "placement": None if placement is None else placement.to_json()}
     for d in a.embedding_model:
         reg.embedding[os.path.basename(os.path.normpath(d))] = AutoModelForEmbeddings.from_pretrained(d, a.device)
-    settings = ServerSettings(reasoning_field=a.reasoning_field, basic_user=a.basic_user, basic_password=a.basic_password, jwt_secret=a.jwt_secret)
+    settings = ServerSettings(reasoning_field=a.reasoning_field, basic_user=a.basic_user, basic_password=a.basic_password, jwt_secret=a.jwt_secret,
+                              max_queue=a.max_queue)
     try:
         uvicorn.run(create_app(reg, settings), host=a.host, port=a.port, log_level="info")
     finally:

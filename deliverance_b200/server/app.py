@@ -42,6 +42,9 @@ class ServerSettings:
     # Under load every streamed token costs the interpreter an event-loop wake-up, a JSON chunk and a socket write, and with
     # a hundred streams that work competes with the engine thread. Above `coalesce_above` concurrent requests a stream sends
     # one chunk per `coalesce_tokens` tokens (or every `coalesce_ms`); the first token always goes out at once.
+    # Back-pressure: with more than this many requests in the server (running, waiting for admission or not yet picked up by the
+    # engine thread) a new one is refused with 429 and a Retry-After header instead of queueing without bound (0: no limit).
+    max_queue: int = 0
     coalesce_above: int = 16
     coalesce_tokens: int = 4
     coalesce_ms: float = 50.0
@@ -317,10 +320,19 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
 
         return StreamingResponse(gen(), media_type="text/event-stream", headers={"X-Deliverance-Session": session, "Cache-Control": "no-cache"})
 
+    def overloaded(runner):
+        if settings.max_queue > 0 and len(runner.active) + runner.inbox.qsize() >= settings.max_queue:
+            return JSONResponse(status_code=429, headers={"Retry-After": "1"},
+                                content={"error": {"message": f"server is at capacity ({settings.max_queue} requests in flight)", "type": "rate_limit_error"}})
+        return None
+
     async def chat(request: Request):
         try:
             body = await _body(request)
             runner = registry.find(body.get("model"))
+            busy = overloaded(runner)
+            if busy is not None:
+                return busy
             prompt, params = map_chat_request(body, runner)
             if settings.pre_generate is not None:
                 msg = settings.pre_generate(body, params)
@@ -378,6 +390,9 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         try:
             body = await _body(request)
             runner = registry.find(body.get("model"))
+            busy = overloaded(runner)
+            if busy is not None:
+                return busy
             prompt = body.get("prompt")
             if isinstance(prompt, list) and prompt and isinstance(prompt[0], str):
                 prompt = prompt[0]

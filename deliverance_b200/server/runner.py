@@ -79,6 +79,18 @@ class EngineRunner:
                 pass
 
     def _loop(self) -> None:
+        while not self._stop.is_set():
+            try:
+                self._serve()
+            except Exception as e:  # noqa: BLE001 - a bug in the bookkeeping must not leave callers waiting for a dead thread
+                for s in list(self.active):
+                    self._finish(s, e)
+                try:
+                    self.clm.engine.reset()
+                except Exception:  # noqa: BLE001
+                    pass
+
+    def _serve(self) -> None:
         eng = self.clm.engine
         while not self._stop.is_set():
             try:

@@ -208,3 +208,15 @@ def test_streaming_tool_calls_never_leak_markup(tmp_path):
     finally:
         for r_ in reg.generation.values():
             r_.close()
+
+
+def test_backpressure_429(registry, monkeypatch):
+    runner = next(iter(registry.generation.values()))
+    c = TestClient(create_app(registry, ServerSettings(max_queue=2)))
+    assert c.post("/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "max_tokens": 2}).status_code == 200
+    monkeypatch.setattr(runner.inbox, "qsize", lambda: 2)  # two requests waiting to be picked up
+    r = c.post("/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "max_tokens": 2})
+    assert r.status_code == 429 and r.headers["retry-after"] == "1" and r.json()["error"]["type"] == "rate_limit_error"
+    assert c.post("/v1/completions", json={"prompt": "x", "max_tokens": 2}).status_code == 429
+    monkeypatch.undo()
+    assert c.post("/v1/completions", json={"prompt": "x", "max_tokens": 2}).status_code == 200
