@@ -1,7 +1,7 @@
 #!/bin/sh
 # MODEL (directory under /models or absolute path) and optional TP_SIZE (GPUs of this node) select what is served.
 set -e
-CONFIG="${CONFIG:-}"   # optional .properties file (models, KV cache, auth); replaces MODEL
+CONFIG="${CONFIG:-}"   # optional .properties / .json configuration (models, KV cache, auth; see example-config.json); replaces MODEL
 if [ -n "$CONFIG" ]; then
   exec python -m deliverance_b200.server --config "$CONFIG" --models-root "${MODELS_ROOT:-/models}" --host 0.0.0.0 ${SERVER_ARGS:-}
 fi
