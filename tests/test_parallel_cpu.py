@@ -297,7 +297,7 @@ if gen == 0 and rank == 1:
         os._exit(3)
     if mode == "hang":      # a rank stops publishing liveness (host-side stall), the others keep beating
         time.sleep(60)
-for _ in range(20 if gen == 0 else 2):
+for _ in range((160 if mode == "hang" else 20) if gen == 0 else 2):
     beat(0.0)
     time.sleep(0.05)
 open(os.path.join(out, f"done_gen{gen}_rank{rank}"), "w").write(str(t.item()))
@@ -318,7 +318,7 @@ def test_local_cluster_restarts_group_on_failure(tmp_path, mode):
     script.write_text(_CLUSTER_CHILD)
     env = dict(os.environ, PYTHONPATH=os.pathsep.join([os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.environ.get("PYTHONPATH", "")]))
     status = tmp_path / "status.json"
-    c = LocalCluster([sys.executable, str(script), mode, str(tmp_path)], nproc=2, max_restarts=2, hang_timeout=1.5 if mode == "hang" else 0.0,
+    c = LocalCluster([sys.executable, str(script), mode, str(tmp_path)], nproc=2, max_restarts=2, hang_timeout=5.0 if mode == "hang" else 0.0,
                      grace=2.0, env=env, status_file=str(status), start_timeout=60.0)
     assert c.run() == 0
     st = json.loads(status.read_text())
