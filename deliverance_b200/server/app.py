@@ -498,14 +498,16 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
     async def ui():
         return HTMLResponse(_UI)
 
+    from .spec import route_docs  # request / response schemas for GET /openapi.json
+
     for path in ("/chat/completions", "/v1/chat/completions"):
-        app.add_api_route(path, chat, methods=["POST"])
+        app.add_api_route(path, chat, methods=["POST"], **route_docs("chat"))
     for path in ("/v1/completions", "/completions"):
-        app.add_api_route(path, completions, methods=["POST"])
+        app.add_api_route(path, completions, methods=["POST"], **route_docs("completions"))
     for path in ("/embeddings", "/v1/embeddings"):
-        app.add_api_route(path, embeddings, methods=["POST"])
+        app.add_api_route(path, embeddings, methods=["POST"], **route_docs("embeddings"))
     for path in ("/models", "/v1/models"):
-        app.add_api_route(path, models, methods=["GET"])
+        app.add_api_route(path, models, methods=["GET"], **route_docs("models"))
     async def metrics():
         """Prometheus text exposition of the engine and runner counters (the reference reports through Dropwizard metrics:
         core/.../model/InferenceProfiler.java:24-161; ttft / tokens-per-second timers in GenerationEngine.java:128-175)."""

@@ -220,3 +220,25 @@ def test_backpressure_429(registry, monkeypatch):
     assert c.post("/v1/completions", json={"prompt": "x", "max_tokens": 2}).status_code == 429
     monkeypatch.undo()
     assert c.post("/v1/completions", json={"prompt": "x", "max_tokens": 2}).status_code == 200
+
+
+def test_openapi_document_describes_the_api(registry):
+    """GET /openapi.json carries request and response schemas of the endpoints (clients can be generated from it), and the
+    request schema accepts what the server accepts."""
+    c = TestClient(create_app(registry))
+    doc = c.get("/openapi.json").json()
+    chat = doc["paths"]["/chat/completions"]["post"]
+    req = chat["requestBody"]["content"]["application/json"]["schema"]
+    assert {"messages", "tools", "guided_json", "guided_regex", "uniform_top_p", "xtc_threshold", "chat_template_kwargs", "stream_options"} <= set(req["properties"])
+    assert "text/event-stream" in chat["responses"]["200"]["content"] and "429" in chat["responses"] and req["required"] == ["messages"]
+    assert doc["paths"]["/v1/completions"]["post"]["requestBody"]["content"]["application/json"]["schema"]["required"] == ["prompt"]
+    assert "embedding" in json.dumps(doc["paths"]["/embeddings"]["post"]["responses"]["200"])
+    jsonschema = pytest.importorskip("jsonschema")
+    body = {"messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]}], "max_tokens": 4, "stop": ["x"], "top_logprobs": 2,
+            "tools": [{"type": "function", "function": {"name": "f", "parameters": {"type": "object"}}}], "tool_choice": "auto"}
+    jsonschema.validate(body, req)
+    r = c.post("/chat/completions", json={k: v for k, v in body.items() if k not in ("tools", "tool_choice")})  # (the tiny model's context is 256 bytes)
+    assert r.status_code == 200
+    jsonschema.validate(r.json(), chat["responses"]["200"]["content"]["application/json"]["schema"])
+    with pytest.raises(jsonschema.ValidationError):
+        jsonschema.validate({"messages": [], "max_tokens": 0}, req)
