@@ -242,3 +242,47 @@ def test_openapi_document_describes_the_api(registry):
     jsonschema.validate(r.json(), chat["responses"]["200"]["content"]["application/json"]["schema"])
     with pytest.raises(jsonschema.ValidationError):
         jsonschema.validate({"messages": [], "max_tokens": 0}, req)
+
+
+def test_interrogation_game_setup_and_loop(registry):
+    """The game's guided_regex name step runs through the real server; the long JSON steps and the suspect are scripted."""
+    import re
+
+    from deliverance_b200.agents import interrogation_game as g
+
+    c = TestClient(create_app(registry))
+    replies = iter(["I was at home.", "Fine, I took it. " + g.MARKER])
+    seen = []
+
+    def chat(messages, **fields):
+        seen.append(fields)
+        if "guided_regex" in fields:
+            r = c.post("/chat/completions", json={"messages": messages, **fields})
+            assert r.status_code == 200, r.text
+            return r.json()["choices"][0]["message"]["content"]
+        schema = fields.get("guided_json")
+        if schema and "places" in schema["properties"]:
+            return json.dumps({"places": [f"_place {i}" for i in range(10)]})
+        if schema and "items" in schema["properties"]:
+            return json.dumps({"items": [f"item {i}" for i in range(10)]})
+        if schema:
+            return json.dumps({"case_title": "The Missing Ledger", "setting": "a bakery", "clues": ["a", "b", "c"],
+                               "hidden": {"what_happened": "w", "motive": "m", "method": "h", "mistake": "k"}})
+        return next(replies)
+
+    lines = iter(["/case", "", "/reveal", "where were you?", "you left flour on the ledger"])
+    out = []
+    game = g.Game(chat, lambda: next(lines, None), out.append, seed=5)
+    assert game.play() == "confessed"
+    name = game.case["suspect"]
+    assert re.fullmatch(g.SUSPECT_NAME_REGEX, name), name
+    assert seen[0]["uniform_top_p"] == 1.0 and seen[1]["temperature"] == 1.2
+    text = "\n".join(out)
+    assert "selected: place" in text and "HIDDEN TRUTH\nwhat happened: w" in text and text.count("CASE: The Missing Ledger") == 2
+    assert g.MARKER not in text and "DEAD TO RIGHTS" in text
+    msgs = [{"role": "x"}] * 40
+    g.trim_conversation(msgs)
+    assert len(msgs) == g.CASE_CONTEXT_MESSAGES + g.RECENT_MESSAGES
+    quit_game = g.Game(chat, lambda: "/quit", out.append)
+    quit_game.case = game.case
+    assert quit_game.play() == "closed"
