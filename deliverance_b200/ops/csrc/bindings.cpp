@@ -88,6 +88,54 @@ class TpComm {
   Tensor rounds_, call_;
 };
 
+// ---- peer-memory state for GEMM -> reduce-scatter -> all-gather (prefill-size batches) -----------------------------------
+class TpScatter {
+ public:
+  // recv / gather / flag pointers: device addresses of every rank's areas as mapped in this process; capacities in bf16 elements
+  TpScatter(int64_t rank, int64_t size, std::vector<int64_t> recv_ptrs, std::vector<int64_t> gather_ptrs, std::vector<int64_t> flag_ptrs,
+            int64_t recv_elems, int64_t gather_elems) {
+    TORCH_CHECK(size >= 2 && size <= 8 && rank >= 0 && rank < size, "tensor-parallel size must be 2..8");
+    TORCH_CHECK(static_cast<int64_t>(recv_ptrs.size()) == size && static_cast<int64_t>(gather_ptrs.size()) == size &&
+                    static_cast<int64_t>(flag_ptrs.size()) == size, "one pointer per rank");
+    args_.size = static_cast<int>(size);
+    args_.rank = static_cast<int>(rank);
+    args_.recv_elems = recv_elems;
+    args_.gather_elems = gather_elems;
+    for (int r = 0; r < 8; ++r) {
+      args_.recv[r] = r < size ? static_cast<unsigned long long>(recv_ptrs[r]) : 0ull;
+      args_.gather[r] = r < size ? static_cast<unsigned long long>(gather_ptrs[r]) : 0ull;
+      args_.flags[r] = r < size ? static_cast<unsigned long long>(flag_ptrs[r]) : 0ull;
+      TORCH_CHECK(r >= size || ((args_.recv[r] & 15) == 0 && (args_.gather[r] & 15) == 0 && (args_.flags[r] & 3) == 0 && args_.recv[r] != 0 &&
+                                args_.gather[r] != 0 && args_.flags[r] != 0), "bad peer pointer");
+      group_cum_[r] = 0;
+    }
+  }
+  const dlv::GemmScatterArgs* args() const { return &args_; }
+  // Advances the cumulative counters by one launch of this shape (every rank runs the same launches in the same order).
+  void advance(const dlv::GemmScatterPlan& plan) {
+    tile_cum_ += static_cast<unsigned>(plan.tiles[args_.rank]);
+    for (int r = 0; r < args_.size; ++r) group_cum_[r] += static_cast<unsigned>(plan.groups[r]);
+  }
+  unsigned tile_target() const { return tile_cum_; }
+  const unsigned* group_targets() const { return group_cum_; }
+
+ private:
+  dlv::GemmScatterArgs args_;
+  unsigned tile_cum_ = 0;
+  unsigned group_cum_[8];
+};
+
+// rows_per_rank, then rows / tiles / groups per rank: the cut of a launch of M rows and N columns over `size` ranks
+std::vector<int64_t> scatter_plan(int64_t M, int64_t N, int64_t size) {
+  TORCH_CHECK(size >= 1 && size <= 8 && M >= 0 && N > 0, "bad plan arguments");
+  const dlv::GemmScatterPlan plan = dlv::gemm_scatter_plan(static_cast<int>(M), static_cast<int>(N), static_cast<int>(size));
+  std::vector<int64_t> v{plan.rows_per_rank};
+  for (int r = 0; r < size; ++r) v.push_back(plan.rows[r]);
+  for (int r = 0; r < size; ++r) v.push_back(plan.tiles[r]);
+  for (int r = 0; r < size; ++r) v.push_back(plan.groups[r]);
+  return v;
+}
+
 // ---- GEMM weight handle -------------------------------------------------------------------------------------------
 class GemmWeight {
  public:
@@ -281,6 +329,31 @@ class GemmWeight {
                      s.ws.data_ptr<float>(), static_cast<size_t>(s.ws.numel()), s.counters.data_ptr<int>(),
                      static_cast<int>(s.counters.numel()), s.status.data_ptr<int>(), 0, cur_stream(), comm.args());
     check_last_error("fused tp gemm launch");
+    return true;
+  }
+  // Row-parallel projection for prefill-size batches: GEMM whose epilogue scatters partial tiles to the ranks that own the token
+  // rows, reduction of the owned rows, gather of the others. `out` holds the summed result on every rank. Returns false
+  // (nothing launched) when the shape is outside this path. Not for CUDA-graph capture (expected counts are launch arguments).
+  bool run_scatter(const Tensor& x, Tensor& out, TpScatter& comm, c10::optional<Tensor> bias) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(1) == desc_.K && x.stride(1) == 1, "x must be bf16 [M, K]");
+    TORCH_CHECK(x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x rows must be 16-byte aligned");
+    const int M = static_cast<int>(x.size(0));
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == M && out.size(1) == desc_.N && out.is_contiguous() &&
+                    (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "bad out");
+    if (!dlv::gemm_scatter_supported(&desc_, M, comm.args())) return false;
+    const float* bptr = nullptr;
+    if (bias.has_value()) {
+      TORCH_CHECK(bias.value().is_cuda() && bias.value().scalar_type() == at::kFloat && bias.value().numel() == desc_.N, "bias must be fp32 [N]");
+      bptr = bias.value().data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    DeviceScratch& s = scratch_for(x.device().index());
+    const dlv::GemmScatterPlan plan = dlv::gemm_scatter_plan(M, desc_.N, comm.args()->size);
+    comm.advance(plan);
+    dlv::gemm_tc_run_scatter(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), comm.args(), s.status.data_ptr<int>(), cur_stream());
+    dlv::launch_scatter_reduce(comm.args(), &plan, M, desc_.N, bptr, out.data_ptr(), comm.tile_target(), s.status.data_ptr<int>(), cur_stream());
+    dlv::launch_scatter_finish(comm.args(), &plan, M, desc_.N, out.data_ptr(), comm.group_targets(), s.status.data_ptr<int>(), cur_stream());
+    check_last_error("gemm reduce-scatter launch");
     return true;
   }
   int64_t n() const { return desc_.N; }
@@ -753,11 +826,15 @@ Tensor q4_dequantize(const Tensor& packed, const Tensor& scales, bool to_bf16) {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<TpComm, std::shared_ptr<TpComm>>(m, "TpComm")
       .def(py::init<int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t, Tensor, Tensor>());
+  py::class_<TpScatter, std::shared_ptr<TpScatter>>(m, "TpScatter")
+      .def(py::init<int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t>());
+  m.def("scatter_plan", &scatter_plan);
   py::class_<GemmWeight, std::shared_ptr<GemmWeight>>(m, "GemmWeight")
       .def(py::init<Tensor, bool, int64_t, int64_t>(), py::arg("w"), py::arg("is_q4"), py::arg("N"), py::arg("K"))
       .def("run", &GemmWeight::run, py::arg("x"), py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("out_f32") = false,
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
+      .def("run_scatter", &GemmWeight::run_scatter, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
       .def("run_act", &GemmWeight::run_act, py::arg("x"), py::arg("act"))
       .def("run_qkv", &GemmWeight::run_qkv)
       .def("run_grouped_act", &GemmWeight::run_grouped_act, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits"),

@@ -211,4 +211,128 @@ void launch_oneshot_allreduce(const void* x, int rows, int H, void* out, const G
                                                  make_params(tp, status));
 }
 
+// ------------------------------------------------------------------------------------------------ reduce-scatter + all-gather
+// Second and third step of the prefill-size tensor-parallel projection (the first is the GEMM with epilogue EPI = 3, which has
+// stored every rank's partial sums of MY token rows into my receive area [size sources][rows_per_rank][N]).
+//   scatter_reduce_kernel: waits (bounded) until every source has published all its tiles for my rows, sums the slabs in rank
+//     order (+ bias), writes the rows to `out` and, with plain peer stores, into the gather area of every other rank, then
+//     publishes one count per CTA and peer.
+//   scatter_finish_kernel: one CTA per row group of the OTHER ranks: waits (bounded) for that source's groups, copies the rows
+//     from my gather area into `out`.
+// Who waits for whom: a reduce CTA waits only for GEMM kernels (which never wait), a finish CTA only for reduce kernels, and on
+// one GPU the three run in stream order, so no launch needs to be resident at once. Buffers are single: a rank's next GEMM comes
+// after its finish kernel, i.e. after every peer has pushed its reduced rows and therefore has read its receive area; a peer's
+// next reduce waits for this rank's next GEMM, which comes after this rank's finish kernel has drained the gather area.
+// Counters are cumulative; the host passes the expected totals, so these launches are not captured in CUDA graphs.
+struct ScatterParams {
+  int size, rank, rows_per_rank, M, N;
+  unsigned long long recv, gather[8], flags[8];
+  unsigned int targets[8];
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) scatter_reduce_kernel(const ScatterParams p, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out) {
+  __shared__ int s_ok;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    bool ok_lane = true;
+    if (lane < p.size) ok_lane = flag_wait_ge(reinterpret_cast<const uint32_t*>(p.flags[p.rank]) + lane, p.targets[0], p.status);
+    const bool all = __all_sync(0xffffffffu, ok_lane);
+    if (lane == 0) s_ok = all ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_ok == 0) return;
+  const int first = p.rank * p.rows_per_rank;
+  const int end = min(p.M, first + p.rows_per_rank);
+  const int row0 = first + blockIdx.x * kScatterGroupRows;
+  const int vec = p.N / 8;
+  const __nv_bfloat16* slabs = reinterpret_cast<const __nv_bfloat16*>(p.recv);
+  for (int idx = threadIdx.x; idx < kScatterGroupRows * vec; idx += blockDim.x) {
+    const int r = idx / vec, i = idx - r * vec;
+    const int m = row0 + r;
+    if (m >= end) break;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = bias != nullptr ? bias[i * 8 + e] : 0.f;
+    for (int src = 0; src < p.size; ++src) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slabs + (static_cast<long long>(src) * p.rows_per_rank + (m - first)) * p.N) + i);
+      const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf162(vu[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    uint4 o;
+    uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ou[e] = pack_bf162(acc[2 * e], acc[2 * e + 1]);
+    const long long off = static_cast<long long>(m) * p.N;
+    reinterpret_cast<uint4*>(out + off)[i] = o;
+    for (int d = 1; d < p.size; ++d)
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.gather[(p.rank + d) % p.size]) + off)[i] = o;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x >= 1 && threadIdx.x < p.size)
+    red_release_sys_add(reinterpret_cast<uint32_t*>(p.flags[(p.rank + threadIdx.x) % p.size]) + 8 + p.rank, 1u);
+}
+
+__global__ void __launch_bounds__(256) scatter_finish_kernel(const ScatterParams p, int groups_per_rank, __nv_bfloat16* __restrict__ out) {
+  __shared__ int s_ok;
+  const int src = blockIdx.x / groups_per_rank, g = blockIdx.x - src * groups_per_rank;
+  if (src == p.rank || src >= p.size) return;
+  const int first = src * p.rows_per_rank;
+  const int end = min(p.M, first + p.rows_per_rank);
+  const int row0 = first + g * kScatterGroupRows;
+  if (row0 >= end) return;
+  if (threadIdx.x == 0)
+    s_ok = flag_wait_ge(reinterpret_cast<const uint32_t*>(p.flags[p.rank]) + 8 + src, p.targets[src], p.status) ? 1 : 0;
+  __syncthreads();
+  if (s_ok == 0) return;
+  const int vec = p.N / 8;
+  const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(p.gather[p.rank]);
+  for (int idx = threadIdx.x; idx < kScatterGroupRows * vec; idx += blockDim.x) {
+    const int r = idx / vec, i = idx - r * vec;
+    const int m = row0 + r;
+    if (m >= end) break;
+    const long long off = static_cast<long long>(m) * p.N;
+    reinterpret_cast<uint4*>(out + off)[i] = __ldcg(reinterpret_cast<const uint4*>(mine + off) + i);
+  }
+}
+
+static ScatterParams make_scatter_params(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, int* status) {
+  ScatterParams p = {};
+  p.size = a->size;
+  p.rank = a->rank;
+  p.rows_per_rank = plan->rows_per_rank;
+  p.M = M;
+  p.N = N;
+  p.recv = a->recv[a->rank];
+  for (int r = 0; r < 8; ++r) {
+    p.gather[r] = a->gather[r];
+    p.flags[r] = a->flags[r];
+  }
+  p.status = status;
+  return p;
+}
+
+void launch_scatter_reduce(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, const float* bias, void* out,
+                           unsigned gemm_target, int* status, cudaStream_t st) {
+  const int groups = plan->groups[a->rank];
+  if (groups == 0) return;
+  ScatterParams p = make_scatter_params(a, plan, M, N, status);
+  p.targets[0] = gemm_target;
+  scatter_reduce_kernel<<<groups, 256, 0, st>>>(p, bias, static_cast<__nv_bfloat16*>(out));
+}
+
+void launch_scatter_finish(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, void* out, const unsigned* group_targets,
+                           int* status, cudaStream_t st) {
+  const int groups_per_rank = plan->rows_per_rank / kScatterGroupRows;
+  ScatterParams p = make_scatter_params(a, plan, M, N, status);
+  for (int r = 0; r < 8; ++r) p.targets[r] = group_targets[r];
+  scatter_finish_kernel<<<groups_per_rank * a->size, 256, 0, st>>>(p, groups_per_rank, static_cast<__nv_bfloat16*>(out));
+}
+
 }  // namespace dlv

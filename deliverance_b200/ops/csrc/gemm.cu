@@ -333,6 +333,59 @@ void gemm_tc_run_act(const GemmWeightDesc* w, const void* x, int M, int ldx, voi
 #undef DLV_LAUNCH
 }
 
+// ------------------------------------------------------------------------------------------------ GEMM -> reduce-scatter
+// Prefill-size row-parallel projections under tensor parallelism. Token rows are cut into one contiguous range per rank (a
+// multiple of 8 rows). The GEMM (EPI = 3) stores each partial tile into the receive area of the rank that owns its
+// rows while the other tiles are still being computed, and never waits, so the grid may be many waves. comm.cu then sums the
+// partial slabs of the owned rows and hands the reduced rows to every rank.
+GemmScatterPlan gemm_scatter_plan(int M, int N, int size) {
+  GemmScatterPlan plan = {};
+  const int per = (M + size - 1) / size;
+  plan.rows_per_rank = ((per + kScatterGroupRows - 1) / kScatterGroupRows) * kScatterGroupRows;
+  const int n_tiles = (N + kGemmBM - 1) / kGemmBM;
+  for (int r = 0; r < 8; ++r) {
+    int rows = r < size ? M - r * plan.rows_per_rank : 0;
+    rows = rows < 0 ? 0 : (rows > plan.rows_per_rank ? plan.rows_per_rank : rows);
+    plan.rows[r] = rows;
+    // 256-token tiles of the GEMM that contain at least one of this rank's rows
+    const int lo = r * plan.rows_per_rank;
+    plan.tiles[r] = rows > 0 ? n_tiles * ((lo + rows - 1) / 256 - lo / 256 + 1) : 0;
+    plan.groups[r] = (rows + kScatterGroupRows - 1) / kScatterGroupRows;
+  }
+  return plan;
+}
+
+bool gemm_scatter_supported(const GemmWeightDesc* w, int M, const GemmScatterArgs* a) {
+  if (a == nullptr || a->size <= 1 || a->size > 8) return false;
+  if (w->N % 8 != 0 || M < 256 * a->size) return false;  // smaller batches: the one-shot epilogue or the library all-reduce
+  const GemmScatterPlan plan = gemm_scatter_plan(M, w->N, a->size);
+  return static_cast<long long>(a->size) * plan.rows_per_rank * w->N <= a->recv_elems &&
+         static_cast<long long>(M) * w->N <= a->gather_elems;
+}
+
+void gemm_tc_run_scatter(const GemmWeightDesc* w, const void* x, int M, int ldx, const GemmScatterArgs* a, int* status, cudaStream_t st) {
+  if (!gemm_scatter_supported(w, M, a)) throw std::runtime_error("GEMM -> reduce-scatter: shape outside the fused path");
+  if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
+  GemmParams p = {};
+  p.M = M;
+  p.N = w->N;
+  p.K = w->K;
+  p.kb_total = (w->K + kGemmBK - 1) / kGemmBK;
+  p.out = nullptr;
+  p.ldo = w->N;
+  p.status = status;
+  p.tp_size = a->size;
+  p.tp_rank = a->rank;
+  p.tp_rows = gemm_scatter_plan(M, w->N, a->size).rows_per_rank;
+  for (int r = 0; r < 8; ++r) {
+    p.tp_recv[r] = a->recv[r];
+    p.tp_flags[r] = a->flags[r];
+  }
+  // one split per tile (force_splits = 1): the owner counts exactly n_tiles * its m-tiles publications per source and launch
+  if (w->is_q4) run_tc<true, 256, 3>(w, x, M, ldx, p, nullptr, 0, nullptr, 0, 1, st, nullptr);
+  else run_tc<false, 256, 3>(w, x, M, ldx, p, nullptr, 0, nullptr, 0, 1, st, nullptr);
+}
+
 // ------------------------------------------------------------------------------------------------ grouped (MoE) GEMM
 // out[r, :] = xs[r, :] @ W[expert(r)]^T for rows grouped by expert. `items` is the device work list built by
 // launch_moe_items with the same token tile `bn`; `max_items` bounds it (unused slots return at once).

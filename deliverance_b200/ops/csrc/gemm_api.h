@@ -32,6 +32,26 @@ struct GemmTpArgs {
   unsigned int* call = nullptr;    // local [2]
 };
 
+// Peer-memory state of the GEMM -> reduce-scatter -> all-gather path for prefill-size batches (see gemm_tc_run_scatter).
+struct GemmScatterArgs {
+  int size = 1, rank = 0;
+  long long recv_elems = 0;      // capacity of a receive area in bf16 elements: size * rows_per_rank * N must fit
+  long long gather_elems = 0;    // capacity of a gather area: M * N must fit
+  unsigned long long recv[8];    // every rank's receive area, bf16 [size sources][rows_per_rank][N] for the launch at hand
+  unsigned long long gather[8];  // every rank's gather area, bf16 [M][N]: rows arrive reduced from their owners
+  unsigned long long flags[8];   // every rank's u32 [16], cumulative: [src] partial tiles from src, [8 + src] reduced row groups from src
+};
+// How a launch of M token rows is cut over the ranks: rank r owns rows [r * rows_per_rank, min(M, (r + 1) * rows_per_rank)).
+struct GemmScatterPlan {
+  int rows_per_rank;  // a multiple of kScatterGroupRows
+  int rows[8];        // rows owned per rank (0 for ranks beyond the end)
+  int tiles[8];       // GEMM CTAs that publish to rank r, per source rank
+  int groups[8];      // reduce CTAs of rank r (kScatterGroupRows rows each)
+};
+constexpr int kScatterGroupRows = 8;
+GemmScatterPlan gemm_scatter_plan(int M, int N, int size);
+bool gemm_scatter_supported(const GemmWeightDesc* w, int M, const GemmScatterArgs* a);
+
 void gemm_weight_init(GemmWeightDesc* w);
 int gemm_num_sms();
 void gemm_set_pdl(bool on);  // programmatic dependent launch of the GEMM kernels (on by default)
@@ -66,6 +86,9 @@ void gemm_tc_run_grouped(const GemmWeightDesc* w, int n_per_expert, const void* 
 // CUDA-core variant for decode-size groups (at most `mt` = 4 or 8 rows per work item; items built with bn == mt)
 void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,
                       int max_items, int mt, cudaStream_t st);
+// Row-parallel projection whose partial tiles go straight to the rank that owns their token rows (epilogue EPI = 3, no waiting
+// inside the GEMM). Follow it with launch_scatter_reduce and launch_scatter_finish on the same stream.
+void gemm_tc_run_scatter(const GemmWeightDesc* w, const void* x, int M, int ldx, const GemmScatterArgs* a, int* status, cudaStream_t st);
 // true when the fused all-reduce epilogue can take this problem (one wave of CTAs, rows and columns inside the slab)
 bool gemm_tp_supported(const GemmWeightDesc* w, int M, const GemmTpArgs* tp);
 void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
@@ -120,6 +143,14 @@ bool comm_rows_supported(const GemmTpArgs* tp, int rows, int H);
 void launch_moe_combine_allreduce(const void* ys, const int* pos, const float* w, int T, int k, int H, const int* offsets, int e0, int ne,
                                   void* out, const GemmTpArgs* tp, int* status, cudaStream_t st);
 void launch_oneshot_allreduce(const void* x, int rows, int H, void* out, const GemmTpArgs* tp, int* status, cudaStream_t st);
+
+// Sum the size partial slabs of this rank's rows (+ bias), write them to out and to every peer's gather area, publish.
+// gemm_target: cumulative number of partial tiles every source must have published to this rank.
+void launch_scatter_reduce(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, const float* bias, void* out,
+                           unsigned gemm_target, int* status, cudaStream_t st);
+// Wait for the other ranks' reduced rows and copy them from the gather area into out. group_targets[src]: cumulative row groups.
+void launch_scatter_finish(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, void* out, const unsigned* group_targets,
+                           int* status, cudaStream_t st);
 
 // mamba.cu
 int launch_mamba2(const void* zx, int ld, int T, int num_seqs, int I, int conv_dim, int K, int H, int d_head, int G, int S,

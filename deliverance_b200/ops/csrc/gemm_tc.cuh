@@ -32,7 +32,9 @@
 //
 // Epilogue variants (template EPI): 0 = store (+ bias, + the tensor-parallel sum above); 1 = gated activation for gate|up weights whose
 // rows are interleaved per 64 outputs (act(gate) * up, half as many output columns); 2 = q|k|v heads of dimension 128: per-head
-// RMSNorm, rotary embedding and the paged KV-cache write happen on the staged tile, only the query heads are written to `out`.
+// RMSNorm, rotary embedding and the paged KV-cache write happen on the staged tile, only the query heads are written to `out`;
+// 3 = reduce-scatter over the tensor-parallel ranks: the partial tile is stored into the receive area of the rank that owns its
+// token rows and published with one release-add; no CTA waits, the reduction is a separate kernel (comm.cu).
 //
 // This replaces the reference's CPU kernels gemm_q8_q4 / gemm_bf16_q4 / gemm_bf16
 // (native/src/main/c/simd/vector_simd.c:339-633,1186-1411,1414-1668) and the WGSL gemm_q4 / gemm_i8q4_v5 shaders.
@@ -97,6 +99,10 @@ struct GemmParams {
   __nv_bfloat16* v_cache;
   int qk_heads, qk_kv_heads, qk_block_size, qk_rot_half, qk_max_pos;
   float qk_eps, qk_norm_offset;
+  // ---- GEMM -> reduce-scatter (kernel template EPI = 3, prefill-size batches): token rows [r * tp_rows, (r + 1) * tp_rows) belong to
+  // rank r. The partial tile goes row by row as bf16 to the owner's receive area tp_recv[owner] = [tp_size sources][tp_rows][N]
+  // (plain peer stores) and one release-add per CTA and owner on tp_flags[owner][tp_rank] publishes it. Nothing waits in this kernel, so the grid may be any number of waves; comm.cu reduces and gathers. ----
+  int tp_rows;
 };
 
 template <bool Q4, int BN>
@@ -164,7 +170,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
                const __grid_constant__ CUtensorMap map_x,   // bf16 [M, K]
                const GemmParams p) {
   using L = GemmSmem<Q4, BN>;
-  constexpr bool ACT = EPI == 1, QKV = EPI == 2;
+  constexpr bool ACT = EPI == 1, QKV = EPI == 2, SCAT = EPI == 3;
   constexpr int NW = L::kNW > 0 ? L::kNW : 1, NX = L::kNX, NR = L::kNR > 0 ? L::kNR : 1, NA = L::kNA, NI = L::kNI;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -669,6 +675,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         }
         if (splits > 1 && !p.cluster_reduce && t == 0) p.counters[ws_tile] = 0;
       }
+    } else if constexpr (SCAT) {
+      // ---- GEMM -> reduce-scatter (host guarantees: N % 4 == 0, one split or a cluster, tp_size > 1) ----
+      // row m belongs to rank m / tp_rows and is row (m - owner * tp_rows) of source slab tp_rank in the owner's receive area
+      if (n + 3 < p.N) {
+        for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {
+          const int m = m0 + col;
+          if (m >= m_lim) break;
+          const float4 acc = column_acc(col);
+          uint2 pk;
+          pk.x = pack_bf162(acc.x, acc.y);
+          pk.y = pack_bf162(acc.z, acc.w);
+          const int owner = m / p.tp_rows;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.tp_recv[owner]) +
+                               (static_cast<long long>(p.tp_rank) * p.tp_rows + (m - owner * p.tp_rows)) * static_cast<long long>(p.N);
+          *reinterpret_cast<uint2*>(dst + n) = pk;
+        }
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      // every CTA of the tile (all splits of a cluster) counts once at every rank that owns some of the tile's rows: an owner
+      // expects n_tiles * (m-tiles that overlap its rows) * splits publications per source and launch
+      const int o_lo = m0 / p.tp_rows, o_hi = (min(m0 + BN, m_lim) - 1) / p.tp_rows;
+      if (t <= o_hi - o_lo) red_release_sys_add(reinterpret_cast<uint32_t*>(p.tp_flags[o_lo + t]) + p.tp_rank, 1u);
     } else if (do_store && !fused_tp) {
       // column c of the tile is finished by cluster rank c % splits; the 16 column slots of this CTA take turns
       for (int col = static_cast<int>(me) + stride * csel; col < BN; col += stride * 16) {

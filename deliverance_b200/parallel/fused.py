@@ -5,8 +5,15 @@ handles exchanged between the ranks of one node, every rank's buffer mapped into
 slabs and the flag matrix used by the GEMM kernel's all-reduce epilogue (csrc/gemm_tc.cuh). ``linear_all_reduce`` replaces
 the reference's ``allReduceSum`` round trip through a central HTTP/TCP server after ``o_proj`` and ``down_proj``
 (core/.../generator/CausalSelfAttention.java:403-405,448-452; core/.../model/tensorparallel/TensorParallelMlp.java:169-171)
-with peer stores issued from inside the GEMM epilogue; shapes outside the fused path (prefill-size batches, grids larger
-than one wave) fall back to the GEMM followed by the NCCL all-reduce.
+with peer stores issued from inside the GEMM epilogue; shapes outside the fused path (grids larger than one wave) fall back
+to the GEMM followed by the NCCL all-reduce.
+
+Prefill-size batches (at least 256 rows per rank) have a second path, off unless ``DLV_TP_SCATTER=1``: GEMM -> reduce-scatter
+-> all-gather. The GEMM epilogue stores each partial tile into the receive area of the rank that owns those token rows while
+the other tiles are still being computed and never waits; a reduce kernel sums the owned rows and pushes them to every
+rank's gather area; a last kernel waits for the peers' rows and copies them into the output (``ScatterState``,
+csrc/gemm_tc.cuh epilogue 3, csrc/comm.cu). Each rank sends and receives ``2 (n - 1) / n`` of the output over NVLink, the
+first half under the GEMM.
 
 Plain peer loads/stores only: no NVLS multimem and no TMA multicast, so a rank that leaves between steps cannot fault the
 others through a multicast binding.
@@ -19,6 +26,34 @@ from .. import ops
 from .context import TensorParallelContext
 
 NCTA_MAX = 1024
+
+
+def scatter_enabled() -> bool:
+    import os
+
+    return os.environ.get("DLV_TP_SCATTER", "0") == "1"
+
+
+class ScatterState:
+    """Symmetric receive / gather areas and counters of the GEMM -> reduce-scatter -> all-gather path."""
+
+    def __init__(self, tp: TensorParallelContext, device, max_rows: int, max_cols: int):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        pad_rows = max_rows + 8 * tp.size  # rows per rank are rounded up to 8
+        self.recv_elems = pad_rows * max_cols
+        self.gather_elems = max_rows * max_cols
+        recv_bytes, gather_bytes = self.recv_elems * 2, self.gather_elems * 2
+        self.buf = symm.empty(recv_bytes + gather_bytes + 64, dtype=torch.uint8, device=device)
+        self.buf[recv_bytes + gather_bytes:].zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm.rendezvous(self.buf, dist.group.WORLD)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.comm = ops.require_ext().TpScatter(tp.rank, tp.size, ptrs, [p + recv_bytes for p in ptrs],
+                                                [p + recv_bytes + gather_bytes for p in ptrs], self.recv_elems, self.gather_elems)
+        dist.barrier()
+        torch.cuda.synchronize(device)
 
 
 class FusedTensorParallel:
@@ -44,7 +79,12 @@ class FusedTensorParallel:
         self.comm = e.TpComm(tp.rank, tp.size, ptrs, [p + recv_bytes for p in ptrs], self.slab, NCTA_MAX, self.rounds, self.call)
         dist.barrier()
         torch.cuda.synchronize(self.device)
-        self.stats = {"fused": 0, "fallback": 0}
+        self.stats = {"fused": 0, "fallback": 0, "scatter": 0}
+        self.scatter = None
+        if scatter_enabled():
+            import os
+
+            self.scatter = ScatterState(tp, self.device, int(os.environ.get("DLV_TP_SCATTER_ROWS", "4096")), max_cols)
 
     @staticmethod
     def create(tp: TensorParallelContext, device) -> "FusedTensorParallel":
@@ -60,6 +100,11 @@ class FusedTensorParallel:
             ops._count()
             self.stats["fused"] += 1
             return out
+        if self.scatter is not None and x.shape[0] >= 256 * self.tp.size and not torch.cuda.is_current_stream_capturing():
+            if w.handle().run_scatter(x, out, self.scatter.comm, bias):
+                ops._count(3)
+                self.stats["scatter"] += 1
+                return out
         self.stats["fallback"] += 1
         y = ops.linear(x, w) if self.tp.rank == 0 or w.bias is None else ops.linear(x, _no_bias(w))
         return self.tp.collectives.all_reduce_sum(key, y)

@@ -95,6 +95,25 @@ def main() -> int:
     ok_all &= good
     report(check="fused_in_cuda_graph", ok=good, fused_calls=fused.stats["fused"], fallback_calls=fused.stats["fallback"])
 
+    # prefill-size batches: GEMM -> reduce-scatter -> all-gather (only when DLV_TP_SCATTER=1 built the state)
+    if fused.scatter is not None:
+        for M in (256 * world, 256 * world + 9, 2048 + 256 * world):
+            g = torch.Generator().manual_seed(7 + M)
+            xs = (torch.randn(M, lw.K, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+            part = (xs.float().cpu() @ wref.t()).to(dev)
+            dist.all_reduce(part)
+            before = fused.stats["scatter"]
+            ys = [fused.linear_all_reduce(xs, lw, "s") for _ in range(3)]
+            torch.cuda.synchronize()
+            ops.check_status(local)
+            err = max(((y.float() - part).norm() / part.norm()).item() for y in ys)
+            gathered = [torch.empty_like(ys[0]) for _ in range(world)]
+            dist.all_gather(gathered, ys[0])
+            good = err < 2e-2 and all(torch.equal(ys[0], y) for y in ys[1:]) and all(torch.equal(gathered[0], t) for t in gathered) \
+                and fused.stats["scatter"] == before + 3
+            ok_all &= good
+            report(check="gemm_reduce_scatter_gather", M=M, N=lw.N, K_per_rank=lw.K, rel_err=err, ok=good)
+
     # ---------------------------------------------------------------- (2) tensor-parallel model vs single GPU
     from deliverance_b200.ckpt.synthetic import SyntheticLoader
     from deliverance_b200.config import parse_config
@@ -225,6 +244,44 @@ def main() -> int:
             roof = max(hbm_us, nvl_us)
             report(check="bench_linear_all_reduce", world=world, M=M, N=N, K_per_rank=Ks, fused_us=res["fused"], gemm_nccl_us=res["gemm+nccl"],
                    roofline_us=roof, fused_frac_of_roofline=roof / res["fused"], speedup_vs_nccl=res["gemm+nccl"] / res["fused"])
+        # prefill-size: GEMM -> reduce-scatter -> all-gather against GEMM + NCCL all-reduce (needs DLV_TP_SCATTER=1)
+        if fused.scatter is not None:
+            Np, Kp = 4096, 14336 // (32 * world) * 32
+            wp = [LinearWeight((torch.randn(Np, Kp, device=dev) * 0.02).to(torch.bfloat16)).to(dev, torch.bfloat16) for _ in range(4)]
+            for M in (2048, 4096):
+                if M < 256 * world:
+                    continue
+                x = (torch.randn(M, Kp, device=dev) * 0.5).to(torch.bfloat16)
+                res = {}
+                for mode in ("scatter", "gemm+nccl"):
+                    def run(i):
+                        if mode == "scatter":
+                            return fused.linear_all_reduce(x, wp[i % 4], "p")
+                        y = ops.linear(x, wp[i % 4])
+                        dist.all_reduce(y)
+                        return y
+                    for i in range(4):
+                        run(i)
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for i in range(16):
+                        run(i)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / 16], device=dev)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    res[mode] = t.item()
+                ops.check_status(local)
+                # roofline: slower of the GEMM at the measured cuBLAS bf16 rate and the bytes a GPU must send (partials to the owners,
+                # reduced rows to everyone: 2 (n - 1) / n of the output) at 770 GB/s
+                flop_us = 2.0 * M * Np * Kp / 1.59e9
+                nvl_us = 2.0 * (world - 1) / world * M * Np * 2 / 770e3
+                roof = max(flop_us, nvl_us)
+                report(check="bench_gemm_reduce_scatter_gather", world=world, M=M, N=Np, K_per_rank=Kp, scatter_us=res["scatter"],
+                       gemm_nccl_us=res["gemm+nccl"], roofline_us=roof, frac_of_roofline=roof / res["scatter"],
+                       speedup_vs_nccl=res["gemm+nccl"] / res["scatter"])
         # fused MoE combine + all-reduce against the local combine followed by the NCCL all-reduce
         for (T, E, k, Hd) in ((64, 8 * world if world > 8 else 8 if 8 % world == 0 else world, 2, 4096), (32, 128 if 128 % world == 0 else 16 * world, 8, 2048)):
             ne, e0 = E // world, rank * (E // world)

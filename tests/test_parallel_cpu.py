@@ -391,3 +391,29 @@ def test_supervised_tensor_parallel_server_recovers_from_a_dead_rank(tmp_path):
     finally:
         sup.send_signal(signal.SIGTERM)
         assert sup.wait(60) == 0
+
+
+def test_scatter_plan_counts_match_the_epilogue_rule():
+    """Host-side expectations of the GEMM -> reduce-scatter path: the rows are cut without gaps, and the number of publications an
+    owner waits for equals what the GEMM epilogue's rule (one count per CTA and per owner that has rows in the CTA's 256-token
+    tile) produces."""
+    from deliverance_b200 import ops
+
+    e = ops.ext()
+    if e is None or not hasattr(e, "scatter_plan"):
+        pytest.skip("extension not built")
+    for size in (2, 4, 8):
+        for M in (256 * size, 256 * size + 9, 2048, 2049, 4096, 8191):
+            for N in (1024, 4096 + 128):
+                v = e.scatter_plan(M, N, size)
+                rpr, rows, tiles, groups = v[0], v[1:1 + size], v[1 + size:1 + 2 * size], v[1 + 2 * size:1 + 3 * size]
+                assert rpr % 8 == 0 and sum(rows) == M and all(0 <= r <= rpr for r in rows)
+                assert all(rows[i] == rpr for i in range(size - 1) if rows[i + 1] > 0)
+                n_tiles = -(-N // 128)
+                published = [0] * size
+                for m0 in range(0, M, 256):
+                    o_lo, o_hi = m0 // rpr, (min(m0 + 256, M) - 1) // rpr
+                    for o in range(o_lo, o_hi + 1):
+                        published[o] += n_tiles
+                assert published == list(tiles), (size, M, N)
+                assert list(groups) == [-(-r // 8) for r in rows]

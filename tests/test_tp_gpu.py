@@ -21,3 +21,16 @@ def test_two_rank_selftest():
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert lines and all(l["ok"] for l in lines if "ok" in l)
     assert any(l["check"] == "fused_in_cuda_graph" for l in lines)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.skipif(os.environ.get("DLV_TEST_TP_SCATTER") != "1", reason="GEMM -> reduce-scatter path is opt-in (DLV_TEST_TP_SCATTER=1)")
+def test_two_rank_gemm_reduce_scatter():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, DLV_TP_SCATTER="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29519", "-m", "deliverance_b200.parallel.selftest"]
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    scat = [l for l in lines if l.get("check") == "gemm_reduce_scatter_gather"]
+    assert len(scat) == 3 and all(l["ok"] for l in scat)
