@@ -87,6 +87,16 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
+def _approx_weight_gb(shape: dict, quant: str) -> float:
+    """Stored weight bytes of one full replica (matrices + embedding / output head), in GB."""
+    from deliverance_b200.bench.roofline import _weight_elems
+    from deliverance_b200.config import parse_config
+
+    stored, _, router, head = _weight_elems(parse_config(dict(shape)), 1)
+    bpe = 0.5625 if quant == "jq4" else 2.0
+    return (stored * bpe + router * 2.0 + head * (2.0 + bpe)) / 1e9
+
+
 def _shutdown(dist, eng) -> None:
     """Leave cleanly, and leave in any case: settle the step in flight, drop the captured graphs (they hold NCCL work when the
     all-reduce runs through NCCL), then tear the process group down under a timer. A communicator teardown that blocks (seen
@@ -124,6 +134,9 @@ def main() -> int:
     ap.add_argument("--no-extras", action="store_true", help="skip the batch-1 / batch-8 decode phases")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "dp", "tp"],
+                    help="N > 1: dp = one engine replica per GPU, --batch sequences each (weak scaling); tp = one engine over N GPUs "
+                         "(tensor parallel, --batch sequences in total, strong scaling); auto = dp when the weights fit one GPU with room to spare")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -150,10 +163,17 @@ def main() -> int:
 
     tp = TensorParallelContext()
     dist = None
+    mode = args.parallelism
+    if mode == "auto":
+        # a replica per GPU serves more tokens per second than sharding a model that fits: shard only when the weights need it
+        weight_gb = _approx_weight_gb(SHAPES[args.shape], args.quant)
+        mode = "dp" if weight_gb < 0.25 * 180 and args.impl == "own" else "tp"
+    replicas = world if (world > 1 and mode == "dp") else 1
     if world > 1:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
+    if world > 1 and mode == "tp":
         tp = TensorParallelContext(rank, world, TorchCollectives())
         if args.impl == "own" and args.comm in ("auto", "fused"):
             try:
@@ -213,7 +233,7 @@ def main() -> int:
     torch.cuda.synchronize()
     build_s = time.time() - t0
 
-    g = torch.Generator().manual_seed(1234)
+    g = torch.Generator().manual_seed(1234 + (rank if replicas > 1 else 0))  # replicas serve different prompts
     prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g)
     pinned = prompts.to(torch.int32).pin_memory()
 
@@ -308,32 +328,39 @@ def main() -> int:
                 sync_all()
                 ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
                 extras[f"decode_tok_s_b{nb}"] = nb / (ms / 1e3)
+        if replicas > 1:
+            extras["scope"] = "per replica (one GPU)"
         if "decode_tok_s_b1" in extras:
             extras["vs_baseline_b1"] = extras["decode_tok_s_b1"] / REFERENCE_DECODE_TOK_S
 
-    value = B / (dev_ms / 1e3)
+    value = replicas * B / (dev_ms / 1e3)  # replicas: every rank decodes its own B sequences; dev_ms is the slowest rank's step
+    if replicas > 1:
+        par = f"dp{world} (one engine replica per GPU; --parallelism tp shards one engine instead)"
+    elif cfg.num_experts == 0 or args.gpus == 1 or cfg.num_experts % args.gpus:
+        par = f"tp{args.gpus}"
+    else:
+        par = f"tp{args.gpus} attention + ep{args.gpus} experts"
     if rank == 0:
         out = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak" if replicas > 1 else "strong",
             "vs_baseline": value / REFERENCE_DECODE_TOK_S, "dtype": "bf16 activations x JQ4 (4-bit) weights" if args.quant == "jq4" else "bf16",
             "data": "synthetic (uniform random prompts, random-init N(0,0.02) weights quantised to JQ4)",
-            "config": {"model": f"{args.shape}-shape {args.quant}", "global_batch": B, "seq_len": P, "decode_tokens_timed": args.steps,
-                       "parallelism": (f"tp{args.gpus}" if cfg.num_experts == 0 or args.gpus == 1 or cfg.num_experts % args.gpus else
-                                       f"tp{args.gpus} attention + ep{args.gpus} experts"),
+            "config": {"model": f"{args.shape}-shape {args.quant}", "global_batch": B * replicas, "seq_len": P, "decode_tokens_timed": args.steps,
+                       "parallelism": par,
                        "l2": "per-step weight stream (>2 GB/rank) exceeds the 126 MB L2; no flush needed",
-                       "comm": ("fused-p2p" if tp.fused is not None else "nccl") if world > 1 else "none",
+                       "comm": ("fused-p2p" if tp.fused is not None else "nccl") if tp.enabled else "none",
                        "baseline_note": "reference number is single-request CPU decode (it has no request batching)"},
             "clocks": clocks,
-            "e2e": {"value": B / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(h2d_per_step),
-                    "d2h_bytes_per_step": int(d2h_per_step)},
-            "gpu_launches": int(launches_per_step * args.steps),
+            "e2e": {"value": replicas * B / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(h2d_per_step) * replicas, "d2h_bytes_per_step": int(d2h_per_step) * replicas},
+            "gpu_launches": int(launches_per_step * args.steps) * replicas,
             "extras": extras,
         }
         try:  # fraction of the measured roofline (copy bandwidth / cuBLAS rate of this pool) for the timed decode step
             from deliverance_b200.bench.roofline import report
 
-            rf = report(cfg, B, P + args.warmup + args.steps // 2, args.quant, world, dev_ms)
+            rf = report(cfg, B, P + args.warmup + args.steps // 2, args.quant, world if tp.enabled else 1, dev_ms)
             out["roofline"] = {k: rf[k] for k in ("target_ms", "bound", "fraction", "hbm_ms", "tensor_ms", "nvlink_ms", "denominators")}
         except Exception as e:  # noqa: BLE001 - reporting only
             out["roofline"] = {"error": repr(e)}
