@@ -335,7 +335,7 @@ def main() -> int:
 
     value = replicas * B / (dev_ms / 1e3)  # replicas: every rank decodes its own B sequences; dev_ms is the slowest rank's step
     if replicas > 1:
-        par = f"dp{world} (one engine replica per GPU; --parallelism tp shards one engine instead)"
+        par = f"dp{world}"  # one engine replica per GPU; --parallelism tp shards one engine over the GPUs instead
     elif cfg.num_experts == 0 or args.gpus == 1 or cfg.num_experts % args.gpus:
         par = f"tp{args.gpus}"
     else:
