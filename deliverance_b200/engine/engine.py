@@ -264,6 +264,11 @@ class Engine:
         self.running.clear()
         self.waiting.clear()
         self._failed.clear()
+        fused = getattr(getattr(self.model, "tp", None), "fused", None)
+        if fused is not None and getattr(fused, "scatter", None) is not None:
+            # its counters are cumulative across launches and ranks; after a failed step they may disagree, so prefill-size
+            # projections go back to the GEMM + library all-reduce until the process group is rebuilt
+            fused.scatter = None
 
     def _new_pages(self, r: Request, n_tokens: int) -> int:
         return max(0, (n_tokens + self.page_size - 1) // self.page_size - len(r.pages))
