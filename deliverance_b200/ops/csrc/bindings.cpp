@@ -108,6 +108,7 @@ class TpScatter {
       TORCH_CHECK(r >= size || ((args_.recv[r] & 15) == 0 && (args_.gather[r] & 15) == 0 && (args_.flags[r] & 3) == 0 && args_.recv[r] != 0 &&
                                 args_.gather[r] != 0 && args_.flags[r] != 0), "bad peer pointer");
       group_cum_[r] = 0;
+      gather_cum_[r] = 0;
     }
   }
   const dlv::GemmScatterArgs* args() const { return &args_; }
@@ -118,11 +119,17 @@ class TpScatter {
   }
   unsigned tile_target() const { return tile_cum_; }
   const unsigned* group_targets() const { return group_cum_; }
+  // the same for one all-gather -> GEMM launch (its counters are separate from the reduce-scatter ones)
+  void advance_gather(const dlv::GemmScatterPlan& plan) {
+    for (int r = 0; r < args_.size; ++r) gather_cum_[r] += static_cast<unsigned>(plan.groups[r]);
+  }
+  const unsigned* gather_targets() const { return gather_cum_; }
 
  private:
   dlv::GemmScatterArgs args_;
   unsigned tile_cum_ = 0;
   unsigned group_cum_[8];
+  unsigned gather_cum_[8];
 };
 
 // rows_per_rank, then rows / tiles / groups per rank: the cut of a launch of M rows and N columns over `size` ranks
@@ -354,6 +361,33 @@ class GemmWeight {
     dlv::launch_scatter_reduce(comm.args(), &plan, M, desc_.N, bptr, out.data_ptr(), comm.tile_target(), s.status.data_ptr<int>(), cur_stream());
     dlv::launch_scatter_finish(comm.args(), &plan, M, desc_.N, out.data_ptr(), comm.group_targets(), s.status.data_ptr<int>(), cur_stream());
     check_last_error("gemm reduce-scatter launch");
+    return true;
+  }
+  // Column-parallel projection of activations whose rows are sharded over the ranks: `x_own` holds this rank's rows (the cut of
+  // scatter_plan(M, ., size)); they are pushed to every rank's gather area and the GEMM's activation producers wait per token
+  // tile for the owners. `out` = all_gather(x) @ W^T, [M, N]. Between two calls the ranks must have been ordered by another
+  // collective (the gather area is a single buffer). Returns false (nothing launched) outside this path.
+  bool run_gathered(const Tensor& x_own, int64_t M, Tensor& out, TpScatter& comm, c10::optional<Tensor> bias) {
+    TORCH_CHECK(x_own.is_cuda() && x_own.scalar_type() == at::kBFloat16 && x_own.dim() == 2 && x_own.size(1) == desc_.K && x_own.is_contiguous(),
+                "x_own must be contiguous bf16 [rows, K]");
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(x_own.data_ptr()) & 15) == 0, "x_own must be 16-byte aligned");
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == M && out.size(1) == desc_.N && out.stride(1) == 1, "bad out");
+    if (!dlv::gemm_gathered_supported(&desc_, static_cast<int>(M), comm.args())) return false;
+    const dlv::GemmScatterPlan plan = dlv::gemm_scatter_plan(static_cast<int>(M), desc_.N, comm.args()->size);
+    TORCH_CHECK(x_own.size(0) == plan.rows[comm.args()->rank], "x_own must hold exactly the rows this rank owns");
+    const float* bptr = nullptr;
+    if (bias.has_value()) {
+      TORCH_CHECK(bias.value().is_cuda() && bias.value().scalar_type() == at::kFloat && bias.value().numel() == desc_.N, "bias must be fp32 [N]");
+      bptr = bias.value().data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x_own.device());
+    DeviceScratch& s = scratch_for(x_own.device().index());
+    comm.advance_gather(plan);
+    dlv::launch_gather_push(comm.args(), &plan, x_own.data_ptr(), static_cast<int>(M), desc_.K, s.status.data_ptr<int>(), cur_stream());
+    dlv::gemm_tc_run_gathered(&desc_, static_cast<int>(M), comm.args(), comm.gather_targets(), out.data_ptr(), static_cast<int>(out.stride(0)), bptr,
+                              s.ws.data_ptr<float>(), static_cast<size_t>(s.ws.numel()), s.counters.data_ptr<int>(),
+                              static_cast<int>(s.counters.numel()), s.status.data_ptr<int>(), cur_stream());
+    check_last_error("all-gather gemm launch");
     return true;
   }
   int64_t n() const { return desc_.N; }
@@ -835,6 +869,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
       .def("run_scatter", &GemmWeight::run_scatter, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
+      .def("run_gathered", &GemmWeight::run_gathered, py::arg("x_own"), py::arg("M"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
       .def("run_act", &GemmWeight::run_act, py::arg("x"), py::arg("act"))
       .def("run_qkv", &GemmWeight::run_qkv)
       .def("run_grouped_act", &GemmWeight::run_grouped_act, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits"),

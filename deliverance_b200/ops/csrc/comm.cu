@@ -302,6 +302,28 @@ __global__ void __launch_bounds__(256) scatter_finish_kernel(const ScatterParams
   }
 }
 
+// all-gather by push: this rank's rows of x [rows, K] go into every rank's gather area (own included) at their global row
+// offset; one release-add per CTA and rank on flags[dst][16 + my rank]. The consumer is the GEMM with the gather prologue.
+__global__ void __launch_bounds__(256) gather_push_kernel(const ScatterParams p, const __nv_bfloat16* __restrict__ x_own) {
+  const int first = p.rank * p.rows_per_rank;
+  const int end = min(p.M, first + p.rows_per_rank);
+  const int row0 = first + blockIdx.x * kScatterGroupRows;
+  const int vec = p.N / 8;  // N holds the row length K here
+  for (int idx = threadIdx.x; idx < kScatterGroupRows * vec; idx += blockDim.x) {
+    const int r = idx / vec, i = idx - r * vec;
+    const int m = row0 + r;
+    if (m >= end) break;
+    const uint4 v = reinterpret_cast<const uint4*>(x_own + static_cast<long long>(m - first) * p.N)[i];
+    const long long off = static_cast<long long>(m) * p.N;
+    for (int d = 0; d < p.size; ++d)
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.gather[(p.rank + d) % p.size]) + off)[i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.size)
+    red_release_sys_add(reinterpret_cast<uint32_t*>(p.flags[(p.rank + threadIdx.x) % p.size]) + 16 + p.rank, 1u);
+}
+
 static ScatterParams make_scatter_params(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, int* status) {
   ScatterParams p = {};
   p.size = a->size;
@@ -333,6 +355,13 @@ void launch_scatter_finish(const GemmScatterArgs* a, const GemmScatterPlan* plan
   ScatterParams p = make_scatter_params(a, plan, M, N, status);
   for (int r = 0; r < 8; ++r) p.targets[r] = group_targets[r];
   scatter_finish_kernel<<<groups_per_rank * a->size, 256, 0, st>>>(p, groups_per_rank, static_cast<__nv_bfloat16*>(out));
+}
+
+void launch_gather_push(const GemmScatterArgs* a, const GemmScatterPlan* plan, const void* x_own, int M, int K, int* status, cudaStream_t st) {
+  const int groups = plan->groups[a->rank];
+  if (groups == 0) return;
+  ScatterParams p = make_scatter_params(a, plan, M, K, status);
+  gather_push_kernel<<<groups, 256, 0, st>>>(p, static_cast<const __nv_bfloat16*>(x_own));
 }
 
 }  // namespace dlv

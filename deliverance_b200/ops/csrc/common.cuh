@@ -147,6 +147,9 @@ inline cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem,
 
 // ---- proxies / fences -----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Orders what this thread has observed through ordinary loads (e.g. an acquired flag) before bulk copies it issues afterwards:
+// global memory that another GPU wrote and published with a flag is read by TMA only after this fence.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

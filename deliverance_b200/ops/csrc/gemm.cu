@@ -386,6 +386,38 @@ void gemm_tc_run_scatter(const GemmWeightDesc* w, const void* x, int M, int ldx,
   else run_tc<false, 256, 3>(w, x, M, ldx, p, nullptr, 0, nullptr, 0, 1, st, nullptr);
 }
 
+// ------------------------------------------------------------------------------------------------ all-gather -> GEMM
+// Column-parallel projections whose input rows live sharded over the ranks (sequence parallel). The rows are staged once in
+// this GPU's gather area (pushed by their owners over NVLink) and read from there by TMA: a remote tile crosses the link once,
+// however many weight tiles use it. The wait for a token tile's owners sits in the activation producers (EPI = 4), so weights
+// stream and tiles whose rows have arrived run while other rows are still in flight.
+bool gemm_gathered_supported(const GemmWeightDesc* w, int M, const GemmScatterArgs* a) {
+  if (a == nullptr || a->size <= 1 || a->size > 8) return false;
+  if (w->K % 8 != 0 || M < 256 * a->size) return false;
+  return static_cast<long long>(M) * w->K <= a->gather_elems;
+}
+
+void gemm_tc_run_gathered(const GemmWeightDesc* w, int M, const GemmScatterArgs* a, const unsigned* group_targets, void* out, int ldo,
+                          const float* bias, float* ws, size_t ws_floats, int* counters, int n_counters, int* status, cudaStream_t st) {
+  if (!gemm_gathered_supported(w, M, a)) throw std::runtime_error("all-gather -> GEMM: shape outside the fused path");
+  GemmParams p = {};
+  p.M = M;
+  p.N = w->N;
+  p.K = w->K;
+  p.kb_total = (w->K + kGemmBK - 1) / kGemmBK;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_f32 = 0;
+  p.bias = bias;
+  p.status = status;
+  p.ag_rows = gemm_scatter_plan(M, w->N, a->size).rows_per_rank;
+  p.ag_flags = reinterpret_cast<const uint32_t*>(a->flags[a->rank]) + 16;
+  for (int r = 0; r < 8; ++r) p.ag_targets[r] = group_targets[r];
+  const void* x = reinterpret_cast<const void*>(a->gather[a->rank]);  // [M][K] bf16, this GPU's own memory
+  if (w->is_q4) run_tc<true, 256, 4>(w, x, M, w->K, p, ws, ws_floats, counters, n_counters, 0, st, nullptr);
+  else run_tc<false, 256, 4>(w, x, M, w->K, p, ws, ws_floats, counters, n_counters, 0, st, nullptr);
+}
+
 // ------------------------------------------------------------------------------------------------ grouped (MoE) GEMM
 // out[r, :] = xs[r, :] @ W[expert(r)]^T for rows grouped by expert. `items` is the device work list built by
 // launch_moe_items with the same token tile `bn`; `max_items` bounds it (unused slots return at once).

@@ -39,7 +39,8 @@ struct GemmScatterArgs {
   long long gather_elems = 0;    // capacity of a gather area: M * N must fit
   unsigned long long recv[8];    // every rank's receive area, bf16 [size sources][rows_per_rank][N] for the launch at hand
   unsigned long long gather[8];  // every rank's gather area, bf16 [M][N]: rows arrive reduced from their owners
-  unsigned long long flags[8];   // every rank's u32 [16], cumulative: [src] partial tiles from src, [8 + src] reduced row groups from src
+  unsigned long long flags[8];   // every rank's u32 [24], cumulative: [src] partial tiles from src, [8 + src] reduced row groups from
+                                 // src, [16 + src] row groups src pushed for an all-gather -> GEMM
 };
 // How a launch of M token rows is cut over the ranks: rank r owns rows [r * rows_per_rank, min(M, (r + 1) * rows_per_rank)).
 struct GemmScatterPlan {
@@ -89,6 +90,13 @@ void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, 
 // Row-parallel projection whose partial tiles go straight to the rank that owns their token rows (epilogue EPI = 3, no waiting
 // inside the GEMM). Follow it with launch_scatter_reduce and launch_scatter_finish on the same stream.
 void gemm_tc_run_scatter(const GemmWeightDesc* w, const void* x, int M, int ldx, const GemmScatterArgs* a, int* status, cudaStream_t st);
+// all-gather -> GEMM: every rank holds the rows it owns (the cut of gemm_scatter_plan) of the activations [M, K]. launch_gather_push
+// copies them into every rank's gather area and publishes one count per CTA; gemm_tc_run_gathered multiplies the local gather
+// area by `w`, its activation producers wait per token tile for the owners' counts (group_targets[src], cumulative).
+bool gemm_gathered_supported(const GemmWeightDesc* w, int M, const GemmScatterArgs* a);
+void launch_gather_push(const GemmScatterArgs* a, const GemmScatterPlan* plan, const void* x_own, int M, int K, int* status, cudaStream_t st);
+void gemm_tc_run_gathered(const GemmWeightDesc* w, int M, const GemmScatterArgs* a, const unsigned* group_targets, void* out, int ldo,
+                          const float* bias, float* ws, size_t ws_floats, int* counters, int n_counters, int* status, cudaStream_t st);
 // true when the fused all-reduce epilogue can take this problem (one wave of CTAs, rows and columns inside the slab)
 bool gemm_tp_supported(const GemmWeightDesc* w, int M, const GemmTpArgs* tp);
 void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,

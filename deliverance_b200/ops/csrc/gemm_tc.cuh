@@ -34,7 +34,9 @@
 // rows are interleaved per 64 outputs (act(gate) * up, half as many output columns); 2 = q|k|v heads of dimension 128: per-head
 // RMSNorm, rotary embedding and the paged KV-cache write happen on the staged tile, only the query heads are written to `out`;
 // 3 = reduce-scatter over the tensor-parallel ranks: the partial tile is stored into the receive area of the rank that owns its
-// token rows and published with one release-add; no CTA waits, the reduction is a separate kernel (comm.cu).
+// token rows and published with one release-add; no CTA waits, the reduction is a separate kernel (comm.cu); 4 = store as in 0, but
+// the activation producers first wait until the ranks that own the tile's token rows have pushed them into the local gather area
+// (all-gather -> GEMM: the weight stream and the other tiles run under the transfer).
 //
 // This replaces the reference's CPU kernels gemm_q8_q4 / gemm_bf16_q4 / gemm_bf16
 // (native/src/main/c/simd/vector_simd.c:339-633,1186-1411,1414-1668) and the WGSL gemm_q4 / gemm_i8q4_v5 shaders.
@@ -103,6 +105,12 @@ struct GemmParams {
   // rank r. The partial tile goes row by row as bf16 to the owner's receive area tp_recv[owner] = [tp_size sources][tp_rows][N]
   // (plain peer stores) and one release-add per CTA and owner on tp_flags[owner][tp_rank] publishes it. Nothing waits in this kernel, so the grid may be any number of waves; comm.cu reduces and gathers. ----
   int tp_rows;
+  // ---- all-gather -> GEMM (kernel template EPI = 4): the activation map covers this rank's gather area [M][K], into which every
+  // rank pushes the rows it owns (rows [r * ag_rows, (r + 1) * ag_rows) come from rank r) and then adds to ag_flags[r] (local,
+  // cumulative). The activation producers wait (bounded) until the owners of their token tile have reached ag_targets[] ----
+  const uint32_t* ag_flags;
+  unsigned int ag_targets[8];
+  int ag_rows;
 };
 
 template <bool Q4, int BN>
@@ -310,9 +318,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       // Launched with programmatic stream serialization, this kernel may run its prologue and stream weights while the kernel
       // that produces the activations is still finishing; nothing that kernel wrote is read before this point.
       pdl_wait();
+      bool ag_ok = true;
+      if constexpr (EPI == 4) {
+        // all-gather prologue: the rows of this token tile arrive from their owners by peer stores; weights stream meanwhile
+        const int o_lo = m0 / p.ag_rows, o_hi = (min(m0 + BN, m_lim) - 1) / p.ag_rows;
+        for (int o = o_lo; o <= o_hi; ++o) {
+          if (!flag_wait_ge(p.ag_flags + o, p.ag_targets[o], p.status)) {
+            *abort_flag = 1;  // nothing is copied; the other roles leave through their own bounded waits
+            ag_ok = false;
+            break;
+          }
+        }
+        fence_proxy_async_all();
+      }
       const int first_i = warp == 2 ? 0 : 1;
       int last_issued = -1, n_issued = 0;
-      for (int i = first_i; i < nkb; i += 2) {
+      for (int i = first_i; i < nkb && ag_ok; i += 2) {
         const int s = i % NX;
         const uint32_t ph = (i / NX) & 1;
         if (!mbar_wait(smem_u32(&bar_x_empty[s]), ph ^ 1, abort_flag, p.status)) break;

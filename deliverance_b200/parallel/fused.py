@@ -45,7 +45,7 @@ class ScatterState:
         self.recv_elems = pad_rows * max_cols
         self.gather_elems = max_rows * max_cols
         recv_bytes, gather_bytes = self.recv_elems * 2, self.gather_elems * 2
-        self.buf = symm.empty(recv_bytes + gather_bytes + 64, dtype=torch.uint8, device=device)
+        self.buf = symm.empty(recv_bytes + gather_bytes + 128, dtype=torch.uint8, device=device)  # 24 u32 counters, padded
         self.buf[recv_bytes + gather_bytes:].zero_()
         torch.cuda.synchronize(device)
         self.handle = symm.rendezvous(self.buf, dist.group.WORLD)
@@ -110,6 +110,32 @@ class FusedTensorParallel:
         return self.tp.collectives.all_reduce_sum(key, y)
 
 
+    def own_rows(self, M: int) -> tuple:
+        """``(first, count)``: the token rows of an ``M``-row batch this rank owns in the scatter / gather paths."""
+        v = ops.require_ext().scatter_plan(M, 128, self.tp.size)
+        return self.tp.rank * v[0], v[1 + self.tp.rank]
+
+    def all_gather_linear(self, x_own: torch.Tensor, M: int, w, ordered: bool = False) -> torch.Tensor:
+        """``all_gather(x) @ W_shard^T`` for activations whose rows are sharded over the ranks (``x_own`` = the rows of
+        ``own_rows(M)``). The rows are pushed into every rank's gather area and the GEMM waits per token tile for their owners,
+        so weights stream and arrived tiles run under the transfer. ``ordered``: the caller guarantees that every rank has
+        finished the previous consumer of the gather area (a reduce-scatter in between does); otherwise a barrier is issued."""
+        out = torch.empty(M, w.N, dtype=torch.bfloat16, device=x_own.device)
+        if self.scatter is not None and not torch.cuda.is_current_stream_capturing():
+            if not ordered:
+                self.tp.collectives.all_reduce_sum("ag.order", torch.zeros(1, device=x_own.device))
+            if w.handle().run_gathered(x_own.contiguous(), M, out, self.scatter.comm, w.bias):
+                ops._count(2)
+                self.stats["gathered"] = self.stats.get("gathered", 0) + 1
+                return out
+        self.stats["fallback"] += 1
+        # ranks hold blocks of rows_per_rank rows, only the tail of the last non-empty block is padding
+        full = torch.cat(self.tp.collectives.all_gather(_pad_rows(x_own, self._rows_per_rank(M))), dim=0)[:M]
+        return ops.linear(full, w)
+
+    def _rows_per_rank(self, M: int) -> int:
+        return ops.require_ext().scatter_plan(M, 128, self.tp.size)[0]
+
     def all_reduce(self, x: torch.Tensor, key: str) -> torch.Tensor:
         """Sum a small bf16 ``[rows, H]`` tensor over the ranks with the one-shot peer-memory kernel, NCCL otherwise."""
         if x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous():
@@ -130,6 +156,12 @@ class FusedTensorParallel:
             self.stats["fused"] += 1
             return out
         return None
+
+
+def _pad_rows(x: torch.Tensor, rows: int) -> torch.Tensor:
+    if x.shape[0] == rows:
+        return x.contiguous()
+    return torch.cat([x, x.new_zeros(rows - x.shape[0], x.shape[1])], dim=0)
 
 
 def _no_bias(w):

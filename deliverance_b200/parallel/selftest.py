@@ -113,6 +113,20 @@ def main() -> int:
                 and fused.stats["scatter"] == before + 3
             ok_all &= good
             report(check="gemm_reduce_scatter_gather", M=M, N=lw.N, K_per_rank=lw.K, rel_err=err, ok=good)
+        # all-gather -> GEMM: every rank holds its rows of the activations, the weight (same on every rank here) multiplies all rows
+        for M in (256 * world, 256 * world + 9):
+            g = torch.Generator().manual_seed(11 + M)
+            xfull = (torch.randn(M, lw.K, generator=g) * 0.5).to(torch.bfloat16)
+            first, count = fused.own_rows(M)
+            x_own = xfull[first:first + count].contiguous().to(dev)
+            want = (xfull.float() @ wref.t()).to(dev)
+            ys = [fused.all_gather_linear(x_own, M, lw) for _ in range(3)]
+            torch.cuda.synchronize()
+            ops.check_status(local)
+            err = max(((y.float() - want).norm() / want.norm()).item() for y in ys)
+            good = err < 2e-2 and fused.stats.get("gathered", 0) >= 3
+            ok_all &= good
+            report(check="all_gather_gemm", M=M, N=lw.N, K=lw.K, rel_err=err, ok=good)
 
     # ---------------------------------------------------------------- (2) tensor-parallel model vs single GPU
     from deliverance_b200.ckpt.synthetic import SyntheticLoader

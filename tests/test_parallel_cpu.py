@@ -417,3 +417,41 @@ def test_scatter_plan_counts_match_the_epilogue_rule():
                         published[o] += n_tiles
                 assert published == list(tiles), (size, M, N)
                 assert list(groups) == [-(-r // 8) for r in rows]
+
+
+def test_all_gather_linear_fallback_reassembles_rows():
+    """Sharded-rows -> column-parallel projection without the peer-memory path: ranks pad their block to rows_per_rank, the
+    gathered blocks are cut back to M rows; the result equals the projection of the full activations."""
+    import torch
+
+    from deliverance_b200 import ops
+    from deliverance_b200.ops import LinearWeight
+    from deliverance_b200.parallel.fused import FusedTensorParallel
+
+    if ops.ext() is None or not hasattr(ops.ext(), "scatter_plan"):
+        pytest.skip("extension not built")
+    size, M, K, N = 2, 601, 64, 48
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(M, K, generator=g)
+    wt = torch.randn(N, K, generator=g) * 0.1
+    w = LinearWeight(wt)
+    plan = ops.ext().scatter_plan(M, 128, size)
+    rpr, rows = plan[0], plan[1:1 + size]
+    shards = [x[r * rpr:r * rpr + rows[r]] for r in range(size)]
+    assert sum(rows) == M
+    blocks = [torch.cat([s, s.new_zeros(rpr - s.shape[0], K)]) for s in shards]
+
+    class FakeCollectives:
+        def all_gather(self, t):
+            return blocks
+
+    class FakeTp:
+        def __init__(self, rank):
+            self.rank, self.size, self.collectives = rank, size, FakeCollectives()
+
+    for r in range(size):
+        f = object.__new__(FusedTensorParallel)
+        f.tp, f.scatter, f.stats = FakeTp(r), None, {"fused": 0, "fallback": 0, "scatter": 0}
+        assert f.own_rows(M) == (r * rpr, rows[r])
+        y = f.all_gather_linear(shards[r], M, w)
+        assert y.shape == (M, N) and torch.allclose(y.float(), x @ wt.t(), atol=1e-4)
