@@ -362,6 +362,10 @@ def main() -> int:
 
             rf = report(cfg, B, P + args.warmup + args.steps // 2, args.quant, world if tp.enabled else 1, dev_ms)
             out["roofline"] = {k: rf[k] for k in ("target_ms", "bound", "fraction", "hbm_ms", "tensor_ms", "nvlink_ms", "denominators")}
+            from deliverance_b200.bench.roofline import prefill_report
+
+            pf = prefill_report(cfg, B, P, args.quant, world if tp.enabled else 1, prefill_ms)
+            out["roofline"]["prefill"] = {k: pf[k] for k in ("target_ms", "bound", "fraction")}
         except Exception as e:  # noqa: BLE001 - reporting only
             out["roofline"] = {"error": repr(e)}
         print(json.dumps(out), flush=True)

@@ -95,6 +95,24 @@ def decode_step_cost(cfg, batch: int, ctx: int, quant: str = "jq4", tp: int = 1,
     return StepCost(weight_bytes, kv_bytes, flops, nv)
 
 
+def prefill_cost(cfg, batch: int, prompt: int, quant: str = "jq4", tp: int = 1) -> StepCost:
+    """Algorithmic cost of prefilling ``batch`` prompts of ``prompt`` tokens, per rank: every matrix multiplies every token
+    (the output head only the last token of each prompt), causal attention does half of the P x P score and value products.
+    Weights are counted once (they are re-read per chunk in practice; the phase is tensor-bound at these sizes)."""
+    stored, active, router, head = _weight_elems(cfg, tp)
+    bpe = 0.5 + 4.0 / 32.0 if quant == "jq4" else 2.0
+    tokens = batch * prompt
+    attn_layers = [i for i in range(cfg.num_layers) if cfg.layer_type(i) != "mamba"]
+    pairs = 0.0  # (query, key) pairs per sequence and layer
+    for i in attn_layers:
+        w = cfg.window(i)
+        pairs += prompt * (prompt + 1) / 2.0 if not w or w >= prompt else w * (prompt - w) + w * (w + 1) / 2.0
+    flops = 2.0 * tokens * (active + router) + 2.0 * batch * head + 4.0 * batch * pairs * (cfg.num_heads / tp) * cfg.head_dim
+    kv_bytes = tokens * len(attn_layers) * 2 * max(1.0, cfg.num_kv_heads / tp) * cfg.head_dim * 2.0  # written once
+    nv = 2 * len(attn_layers) * tokens * cfg.hidden_size * 2.0 * 2.0 * (tp - 1) / tp if tp > 1 else 0.0  # two-shot sums
+    return StepCost(stored * bpe + router * 2.0 + head * bpe, kv_bytes, flops, nv)
+
+
 def target_ms(cost: StepCost, peaks: dict, sustained: bool = True) -> dict:
     tf = peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"]
     t_hbm = cost.hbm_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
@@ -115,6 +133,16 @@ def report(cfg, batch: int, ctx: int, quant: str, tp: int, measured_ms: Optional
     return out
 
 
+def prefill_report(cfg, batch: int, prompt: int, quant: str, tp: int, measured_ms: Optional[float] = None, peaks_path: Optional[str] = None) -> dict:
+    peaks, source = load_peaks(peaks_path)
+    cost = prefill_cost(cfg, batch, prompt, quant, tp)
+    out = {"gflop": cost.flops / 1e9, "nvlink_mb": cost.nvlink_bytes / 1e6, **target_ms(cost, peaks), "denominators": f"of {source}"}
+    if measured_ms:
+        out["measured_ms"] = measured_ms
+        out["fraction"] = out["target_ms"] / measured_ms
+    return out
+
+
 def main() -> int:
     from deliverance_b200.ckpt.synthetic import SHAPES
     from deliverance_b200.config import parse_config
@@ -127,7 +155,11 @@ def main() -> int:
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--ms", type=float, default=None, help="measured milliseconds per step")
     ap.add_argument("--peaks", default=None)
+    ap.add_argument("--prefill", action="store_true", help="cost of prefilling --batch prompts of --ctx tokens instead of one decode step")
     a = ap.parse_args()
+    if a.prefill:
+        print(json.dumps(prefill_report(parse_config(dict(SHAPES[a.shape])), a.batch, a.ctx, a.quant, a.tp, a.ms, a.peaks), indent=1))
+        return 0
     print(json.dumps(report(parse_config(dict(SHAPES[a.shape])), a.batch, a.ctx, a.quant, a.tp, a.ms, a.peaks), indent=1))
     return 0
 

@@ -844,3 +844,19 @@ def test_runner_close_answers_waiting_callers(tmp_path):
     runner.close()
     t.join(20)
     assert not t.is_alive() and "shutting down" in out.get("e", "") and not clm.engine.has_work()
+
+
+def test_prefill_roofline_counts_every_matrix_and_half_the_attention():
+    from deliverance_b200.bench.roofline import prefill_cost, prefill_report
+    from deliverance_b200.ckpt.synthetic import SHAPES
+    from deliverance_b200.config import parse_config
+
+    cfg = parse_config(dict(SHAPES["qwen3-4b"]))
+    c1, c2 = prefill_cost(cfg, 1, 1024), prefill_cost(cfg, 2, 1024)
+    assert 1.99 < c2.flops / c1.flops < 2.01 and c1.nvlink_bytes == 0
+    long = prefill_cost(cfg, 1, 2048)
+    assert long.flops > 2 * c1.flops  # the attention term grows with the square of the prompt
+    tp8 = prefill_cost(cfg, 64, 2048, tp=8)
+    assert tp8.nvlink_bytes > 0 and abs(tp8.flops * 8 / prefill_cost(cfg, 64, 2048).flops - 1) < 0.02
+    r = prefill_report(cfg, 64, 2048, "jq4", 1, measured_ms=1562.0)
+    assert r["bound"] == "tensor" and 0.3 < r["fraction"] < 0.7
