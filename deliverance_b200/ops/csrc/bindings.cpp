@@ -356,8 +356,8 @@ class GemmWeight {
     c10::cuda::CUDAGuard guard(x.device());
     DeviceScratch& s = scratch_for(x.device().index());
     const dlv::GemmScatterPlan plan = dlv::gemm_scatter_plan(M, desc_.N, comm.args()->size);
-    comm.advance(plan);
     dlv::gemm_tc_run_scatter(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), comm.args(), s.status.data_ptr<int>(), cur_stream());
+    comm.advance(plan);  // only once the GEMM that publishes these counts is in the stream
     dlv::launch_scatter_reduce(comm.args(), &plan, M, desc_.N, bptr, out.data_ptr(), comm.tile_target(), s.status.data_ptr<int>(), cur_stream());
     dlv::launch_scatter_finish(comm.args(), &plan, M, desc_.N, out.data_ptr(), comm.group_targets(), s.status.data_ptr<int>(), cur_stream());
     check_last_error("gemm reduce-scatter launch");
@@ -382,8 +382,8 @@ class GemmWeight {
     }
     c10::cuda::CUDAGuard guard(x_own.device());
     DeviceScratch& s = scratch_for(x_own.device().index());
-    comm.advance_gather(plan);
     dlv::launch_gather_push(comm.args(), &plan, x_own.data_ptr(), static_cast<int>(M), desc_.K, s.status.data_ptr<int>(), cur_stream());
+    comm.advance_gather(plan);
     dlv::gemm_tc_run_gathered(&desc_, static_cast<int>(M), comm.args(), comm.gather_targets(), out.data_ptr(), static_cast<int>(out.stride(0)), bptr,
                               s.ws.data_ptr<float>(), static_cast<size_t>(s.ws.numel()), s.counters.data_ptr<int>(),
                               static_cast<int>(s.counters.numel()), s.status.data_ptr<int>(), cur_stream());
