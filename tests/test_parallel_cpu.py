@@ -455,3 +455,173 @@ def test_all_gather_linear_fallback_reassembles_rows():
         assert f.own_rows(M) == (r * rpr, rows[r])
         y = f.all_gather_linear(shards[r], M, w)
         assert y.shape == (M, N) and torch.allclose(y.float(), x @ wt.t(), atol=1e-4)
+
+
+def _simulate_scatter_protocol(size: int, launches: list, seed: int, capacity: int = 2, finish: bool = True, barrier: bool = True):
+    """Model of the peer-memory protocol behind GEMM -> reduce-scatter -> all-gather and all-gather -> GEMM (csrc/gemm_tc.cuh epilogue 3 /
+    prologue 4, csrc/comm.cu): ranks run their kernels in stream order, at most ``capacity`` CTAs of a kernel are resident, a
+    resident CTA whose flag wait is not satisfied keeps its slot, and a random scheduler interleaves everything. Buffers carry the
+    launch number that wrote them, so a read that sees another launch's data (a buffer reused too early) is caught."""
+    import random
+
+    rng = random.Random(seed)
+    G = 8  # rows per reduce / push CTA
+
+    def plan(M):
+        rpr = -(-(-(-M // size)) // G) * G
+        rows = [max(0, min(rpr, M - r * rpr)) for r in range(size)]
+        tiles = [0] * size
+        for m0 in range(0, M, 256):
+            for o in range(m0 // rpr, (min(m0 + 256, M) - 1) // rpr + 1):
+                tiles[o] += 1
+        return rpr, rows, tiles, [-(-r // G) for r in rows]
+
+    recv = [dict() for _ in range(size)]      # recv[owner][(src, local row)] = launch
+    gather = [dict() for _ in range(size)]    # gather[rank][row] = launch
+    fl_tile = [[0] * size for _ in range(size)]   # [owner][src]
+    fl_group = [[0] * size for _ in range(size)]  # [dst][src]   (reduce-scatter pushes)
+    fl_ag = [[0] * size for _ in range(size)]     # [dst][src]   (all-gather pushes)
+    arrived = [0] * size                          # barrier arrivals per rank (cumulative)
+    streams = [[] for _ in range(size)]
+    cum_tile, cum_group, cum_ag, barriers = [0] * size, [0] * size, [0] * size, 0
+
+    for li, (kind, M) in enumerate(launches):
+        rpr, rows, tiles, groups = plan(M)
+        if kind == "scatter":
+            for r in range(size):
+                cum_tile[r] += tiles[r]
+                cum_group[r] += groups[r]
+            t_tile, t_group = list(cum_tile), list(cum_group)
+            for me in range(size):
+                def gemm_cta(m0, me=me, rpr=rpr, M=M, li=li):
+                    def run():
+                        hi = min(m0 + 256, M)
+                        for m in range(m0, hi):
+                            recv[m // rpr][(me, m - (m // rpr) * rpr)] = li
+                        for o in range(m0 // rpr, (hi - 1) // rpr + 1):
+                            fl_tile[o][me] += 1
+                    return (lambda: True, run)
+                streams[me].append([gemm_cta(m0) for m0 in range(0, M, 256)])
+
+                def reduce_cta(gi, me=me, rpr=rpr, M=M, li=li, want=t_tile[me]):
+                    def ready():
+                        return all(fl_tile[me][s] >= want for s in range(size))
+
+                    def run():
+                        first = me * rpr
+                        for m in range(first + gi * G, min(M, first + rpr, first + (gi + 1) * G)):
+                            for s in range(size):
+                                assert recv[me][(s, m - first)] == li, ("receive area reused too early", li, me, s, m)
+                            for d in range(1, size):
+                                gather[(me + d) % size][m] = li
+                        for d in range(1, size):
+                            fl_group[(me + d) % size][me] += 1
+                    return (ready, run)
+                streams[me].append([reduce_cta(gi) for gi in range(groups[me])])
+
+                def finish_cta(src, gi, me=me, rpr=rpr, M=M, li=li, t_group=t_group):
+                    def ready():
+                        return fl_group[me][src] >= t_group[src]
+
+                    def run():
+                        first = src * rpr
+                        for m in range(first + gi * G, min(M, first + rpr, first + (gi + 1) * G)):
+                            assert gather[me][m] == li, ("gather area reused too early", li, me, src, m)
+                    return (ready, run)
+                if finish:
+                    streams[me].append([finish_cta(s, gi) for s in range(size) if s != me for gi in range(groups[s])])
+        else:  # all-gather -> GEMM, preceded by a barrier (ordered=False)
+            barriers += 1
+            for r in range(size):
+                cum_ag[r] += groups[r]
+            t_ag = list(cum_ag)
+            for me in range(size):
+                def barrier_cta(me=me, want=barriers):
+                    def run():
+                        arrived[me] += 0
+                    return (lambda: all(a >= want for a in arrived), run)
+
+                def arrive_cta(me=me):
+                    def run():
+                        arrived[me] += 1
+                    return (lambda: True, run)
+                if barrier:
+                    streams[me].append([arrive_cta()])
+                    streams[me].append([barrier_cta()])
+
+                def push_cta(gi, me=me, rpr=rpr, M=M, li=li):
+                    def run():
+                        first = me * rpr
+                        for m in range(first + gi * G, min(M, first + rpr, first + (gi + 1) * G)):
+                            for d in range(size):
+                                gather[(me + d) % size][m] = li
+                        for d in range(size):
+                            fl_ag[(me + d) % size][me] += 1
+                    return (lambda: True, run)
+                streams[me].append([push_cta(gi) for gi in range(groups[me])])
+
+                def ag_gemm_cta(m0, me=me, rpr=rpr, M=M, li=li, want=t_ag):
+                    hi = min(m0 + 256, M)
+                    owners = range(m0 // rpr, (hi - 1) // rpr + 1)
+
+                    def run():
+                        for m in range(m0, hi):
+                            assert gather[me][m] == li, ("gather area read before / after its launch", li, me, m)
+                    return (lambda: all(fl_ag[me][o] >= want[o] for o in owners), run)
+                streams[me].append([ag_gemm_cta(m0) for m0 in range(0, M, 256) for _ in range(2)])  # two weight tiles per token tile
+
+    # scheduler: per rank the current kernel with a queue of CTAs not yet resident and the resident ones
+    pos = [0] * size
+    pending = [list(s[0]) if s else [] for s in streams]
+    resident = [[] for _ in range(size)]
+    for r in range(size):
+        rng.shuffle(pending[r])
+    steps = 0
+    while any(pos[r] < len(streams[r]) for r in range(size)):
+        progressed = False
+        order = list(range(size))
+        rng.shuffle(order)
+        for r in order:
+            if pos[r] >= len(streams[r]):
+                continue
+            while pending[r] and len(resident[r]) < capacity:
+                resident[r].append(pending[r].pop())
+            runnable = [c for c in resident[r] if c[0]()]
+            if runnable and rng.random() < 0.7:
+                c = rng.choice(runnable)
+                c[1]()
+                resident[r].remove(c)
+                progressed = True
+            if not pending[r] and not resident[r]:
+                pos[r] += 1
+                if pos[r] < len(streams[r]):
+                    pending[r] = list(streams[r][pos[r]])
+                    rng.shuffle(pending[r])
+                progressed = True
+        steps += 1
+        if not progressed:
+            stuck = all(pos[r] >= len(streams[r]) or (not any(c[0]() for c in resident[r]) and (not pending[r] or len(resident[r]) >= capacity))
+                        for r in range(size))
+            assert not stuck, ("deadlock", pos, [len(x) for x in resident])
+        assert steps < 2_000_000
+    return steps
+
+
+@pytest.mark.parametrize("size", [2, 4, 8])
+def test_scatter_gather_protocol_has_no_deadlock_and_no_early_reuse(size):
+    launches = [("scatter", 256 * size), ("scatter", 256 * size + 9), ("gather", 256 * size + 9), ("scatter", 512 * size),
+                ("gather", 256 * size), ("gather", 300 * size), ("scatter", 256 * size)]
+    for seed in range(6):
+        _simulate_scatter_protocol(size, launches, seed, capacity=1 + seed % 3)
+    # the model is sharp enough to see the two orderings the design relies on: without the finish kernel a fast rank's next GEMM
+    # overwrites a receive area that is still being reduced; without the barrier two all-gathers in a row overwrite the gather area
+    def broken(seq, **kw):
+        for seed in range(40):
+            try:
+                _simulate_scatter_protocol(size, seq, seed, capacity=2, **kw)
+            except AssertionError as e:
+                return str(e)
+        return ""
+
+    assert "reused too early" in broken([("scatter", 512 * size)] * 6, finish=False)
+    assert "gather area" in broken([("gather", 512 * size)] * 6, barrier=False)
