@@ -113,9 +113,10 @@ class TpScatter {
   }
   const dlv::GemmScatterArgs* args() const { return &args_; }
   // Advances the cumulative counters by one launch of this shape (every rank runs the same launches in the same order).
-  void advance(const dlv::GemmScatterPlan& plan) {
+  void advance(const dlv::GemmScatterPlan& plan, bool gathered) {
     tile_cum_ += static_cast<unsigned>(plan.tiles[args_.rank]);
-    for (int r = 0; r < args_.size; ++r) group_cum_[r] += static_cast<unsigned>(plan.groups[r]);
+    if (gathered)
+      for (int r = 0; r < args_.size; ++r) group_cum_[r] += static_cast<unsigned>(plan.groups[r]);
   }
   unsigned tile_target() const { return tile_cum_; }
   const unsigned* group_targets() const { return group_cum_; }
@@ -341,13 +342,16 @@ class GemmWeight {
   // Row-parallel projection for prefill-size batches: GEMM whose epilogue scatters partial tiles to the ranks that own the token
   // rows, reduction of the owned rows, gather of the others. `out` holds the summed result on every rank. Returns false
   // (nothing launched) when the shape is outside this path. Not for CUDA-graph capture (expected counts are launch arguments).
-  bool run_scatter(const Tensor& x, Tensor& out, TpScatter& comm, c10::optional<Tensor> bias) {
+  // gather = false: plain reduce-scatter, `out` is [rows this rank owns, N]. The caller must then order the ranks before the next
+  // scatter launch (an all-gather -> GEMM on the same state does).
+  bool run_scatter(const Tensor& x, Tensor& out, TpScatter& comm, c10::optional<Tensor> bias, bool gather) {
     TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(1) == desc_.K && x.stride(1) == 1, "x must be bf16 [M, K]");
     TORCH_CHECK(x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x rows must be 16-byte aligned");
     const int M = static_cast<int>(x.size(0));
-    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == M && out.size(1) == desc_.N && out.is_contiguous() &&
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(1) == desc_.N && out.is_contiguous() &&
                     (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "bad out");
     if (!dlv::gemm_scatter_supported(&desc_, M, comm.args())) return false;
+    TORCH_CHECK(out.size(0) == (gather ? M : dlv::gemm_scatter_plan(M, desc_.N, comm.args()->size).rows[comm.args()->rank]), "out has the wrong number of rows");
     const float* bptr = nullptr;
     if (bias.has_value()) {
       TORCH_CHECK(bias.value().is_cuda() && bias.value().scalar_type() == at::kFloat && bias.value().numel() == desc_.N, "bias must be fp32 [N]");
@@ -357,9 +361,10 @@ class GemmWeight {
     DeviceScratch& s = scratch_for(x.device().index());
     const dlv::GemmScatterPlan plan = dlv::gemm_scatter_plan(M, desc_.N, comm.args()->size);
     dlv::gemm_tc_run_scatter(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), comm.args(), s.status.data_ptr<int>(), cur_stream());
-    comm.advance(plan);  // only once the GEMM that publishes these counts is in the stream
-    dlv::launch_scatter_reduce(comm.args(), &plan, M, desc_.N, bptr, out.data_ptr(), comm.tile_target(), s.status.data_ptr<int>(), cur_stream());
-    dlv::launch_scatter_finish(comm.args(), &plan, M, desc_.N, out.data_ptr(), comm.group_targets(), s.status.data_ptr<int>(), cur_stream());
+    comm.advance(plan, gather);  // only once the GEMM that publishes these counts is in the stream
+    dlv::launch_scatter_reduce(comm.args(), &plan, M, desc_.N, bptr, out.data_ptr(), comm.tile_target(), gather, s.status.data_ptr<int>(), cur_stream());
+    if (gather)
+      dlv::launch_scatter_finish(comm.args(), &plan, M, desc_.N, out.data_ptr(), comm.group_targets(), s.status.data_ptr<int>(), cur_stream());
     check_last_error("gemm reduce-scatter launch");
     return true;
   }
@@ -868,7 +873,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("run", &GemmWeight::run, py::arg("x"), py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("out_f32") = false,
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
-      .def("run_scatter", &GemmWeight::run_scatter, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
+      .def("run_scatter", &GemmWeight::run_scatter, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none(),
+           py::arg("gather") = true)
       .def("run_gathered", &GemmWeight::run_gathered, py::arg("x_own"), py::arg("M"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
       .def("run_act", &GemmWeight::run_act, py::arg("x"), py::arg("act"))
       .def("run_qkv", &GemmWeight::run_qkv)

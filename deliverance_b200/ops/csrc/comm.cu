@@ -231,7 +231,9 @@ struct ScatterParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(256) scatter_reduce_kernel(const ScatterParams p, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out) {
+// push = 0: plain reduce-scatter, `out` holds only this rank's rows [rows, N] (row 0 = first owned row) and nothing is sent on.
+__global__ void __launch_bounds__(256) scatter_reduce_kernel(const ScatterParams p, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                                             int push) {
   __shared__ int s_ok;
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
@@ -269,10 +271,15 @@ __global__ void __launch_bounds__(256) scatter_reduce_kernel(const ScatterParams
 #pragma unroll
     for (int e = 0; e < 4; ++e) ou[e] = pack_bf162(acc[2 * e], acc[2 * e + 1]);
     const long long off = static_cast<long long>(m) * p.N;
+    if (!push) {
+      reinterpret_cast<uint4*>(out + static_cast<long long>(m - first) * p.N)[i] = o;
+      continue;
+    }
     reinterpret_cast<uint4*>(out + off)[i] = o;
     for (int d = 1; d < p.size; ++d)
       reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.gather[(p.rank + d) % p.size]) + off)[i] = o;
   }
+  if (!push) return;
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x >= 1 && threadIdx.x < p.size)
@@ -341,12 +348,12 @@ static ScatterParams make_scatter_params(const GemmScatterArgs* a, const GemmSca
 }
 
 void launch_scatter_reduce(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, const float* bias, void* out,
-                           unsigned gemm_target, int* status, cudaStream_t st) {
+                           unsigned gemm_target, bool push, int* status, cudaStream_t st) {
   const int groups = plan->groups[a->rank];
   if (groups == 0) return;
   ScatterParams p = make_scatter_params(a, plan, M, N, status);
   p.targets[0] = gemm_target;
-  scatter_reduce_kernel<<<groups, 256, 0, st>>>(p, bias, static_cast<__nv_bfloat16*>(out));
+  scatter_reduce_kernel<<<groups, 256, 0, st>>>(p, bias, static_cast<__nv_bfloat16*>(out), push ? 1 : 0);
 }
 
 void launch_scatter_finish(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, void* out, const unsigned* group_targets,

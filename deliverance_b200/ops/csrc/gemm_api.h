@@ -152,10 +152,11 @@ void launch_moe_combine_allreduce(const void* ys, const int* pos, const float* w
                                   void* out, const GemmTpArgs* tp, int* status, cudaStream_t st);
 void launch_oneshot_allreduce(const void* x, int rows, int H, void* out, const GemmTpArgs* tp, int* status, cudaStream_t st);
 
-// Sum the size partial slabs of this rank's rows (+ bias), write them to out and to every peer's gather area, publish.
+// Sum the size partial slabs of this rank's rows (+ bias). push: write them to out [M, N] and to every peer's gather area and
+// publish (all-reduce, follow with launch_scatter_finish); !push: write them to out [own rows, N] only (reduce-scatter).
 // gemm_target: cumulative number of partial tiles every source must have published to this rank.
 void launch_scatter_reduce(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, const float* bias, void* out,
-                           unsigned gemm_target, int* status, cudaStream_t st);
+                           unsigned gemm_target, bool push, int* status, cudaStream_t st);
 // Wait for the other ranks' reduced rows and copy them from the gather area into out. group_targets[src]: cumulative row groups.
 void launch_scatter_finish(const GemmScatterArgs* a, const GemmScatterPlan* plan, int M, int N, void* out, const unsigned* group_targets,
                            int* status, cudaStream_t st);

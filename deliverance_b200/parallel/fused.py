@@ -110,6 +110,20 @@ class FusedTensorParallel:
         return self.tp.collectives.all_reduce_sum(key, y)
 
 
+    def linear_reduce_scatter(self, x: torch.Tensor, w, key: str) -> torch.Tensor:
+        """Rows ``own_rows(M)`` of ``sum over ranks (x @ W_shard^T)``: the GEMM epilogue sends every partial tile to the rank that
+        owns its token rows, the owner sums. Sequence-parallel building block: follow it with ``all_gather_linear(..., ordered=
+        True)`` (which also orders the ranks before the next scatter). Outside the peer-memory path: all-reduce, then slice."""
+        M = x.shape[0]
+        first, count = self.own_rows(M)
+        if self.scatter is not None and M >= 256 * self.tp.size and not torch.cuda.is_current_stream_capturing():
+            out = torch.empty(count, w.N, dtype=torch.bfloat16, device=x.device)
+            if w.handle().run_scatter(x, out, self.scatter.comm, w.bias, False):
+                ops._count(2)
+                self.stats["scatter"] += 1
+                return out
+        return self.linear_all_reduce(x, w, key)[first:first + count]
+
     def own_rows(self, M: int) -> tuple:
         """``(first, count)``: the token rows of an ``M``-row batch this rank owns in the scatter / gather paths."""
         v = ops.require_ext().scatter_plan(M, 128, self.tp.size)

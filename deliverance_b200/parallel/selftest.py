@@ -113,6 +113,27 @@ def main() -> int:
                 and fused.stats["scatter"] == before + 3
             ok_all &= good
             report(check="gemm_reduce_scatter_gather", M=M, N=lw.N, K_per_rank=lw.K, rel_err=err, ok=good)
+        # sequence-parallel chain: reduce-scatter (own rows only) -> all-gather -> GEMM, repeated without barriers in between
+        M = 256 * world + 40
+        g = torch.Generator().manual_seed(3)
+        xs = (torch.randn(M, lw.K, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+        part = (xs.float().cpu() @ wref.t()).to(dev)
+        dist.all_reduce(part)
+        first, count = fused.own_rows(M)
+        w_back = LinearWeight((torch.randn(lw.K, lw.N, generator=g) * 0.05).to(torch.bfloat16)).to(dev, torch.bfloat16)
+        good = True
+        dist.barrier()
+        for it in range(3):
+            own = fused.linear_reduce_scatter(xs, lw, "sp")
+            y = fused.all_gather_linear(own, M, w_back, ordered=True)
+            torch.cuda.synchronize()
+            ops.check_status(local)
+            want = ops.linear(part.to(torch.bfloat16), w_back)
+            e1 = ((own.float() - part[first:first + count]).norm() / part.norm()).item()
+            e2 = ((y.float() - want.float()).norm() / want.float().norm()).item()
+            good = good and own.shape[0] == count and e1 < 2e-2 and e2 < 3e-2
+        ok_all &= good
+        report(check="reduce_scatter_then_all_gather_gemm", M=M, rel_err_rows=e1, rel_err_chain=e2, ok=good)
         # all-gather -> GEMM: every rank holds its rows of the activations, the weight (same on every rank here) multiplies all rows
         for M in (256 * world, 256 * world + 9):
             g = torch.Generator().manual_seed(11 + M)

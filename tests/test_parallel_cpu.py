@@ -487,10 +487,11 @@ def _simulate_scatter_protocol(size: int, launches: list, seed: int, capacity: i
 
     for li, (kind, M) in enumerate(launches):
         rpr, rows, tiles, groups = plan(M)
-        if kind == "scatter":
+        if kind in ("scatter", "rs"):  # rs: plain reduce-scatter, the owner keeps its rows (no push, no finish kernel)
+            push = kind == "scatter"
             for r in range(size):
                 cum_tile[r] += tiles[r]
-                cum_group[r] += groups[r]
+                cum_group[r] += groups[r] if push else 0
             t_tile, t_group = list(cum_tile), list(cum_group)
             for me in range(size):
                 def gemm_cta(m0, me=me, rpr=rpr, M=M, li=li):
@@ -503,7 +504,7 @@ def _simulate_scatter_protocol(size: int, launches: list, seed: int, capacity: i
                     return (lambda: True, run)
                 streams[me].append([gemm_cta(m0) for m0 in range(0, M, 256)])
 
-                def reduce_cta(gi, me=me, rpr=rpr, M=M, li=li, want=t_tile[me]):
+                def reduce_cta(gi, me=me, rpr=rpr, M=M, li=li, want=t_tile[me], push=push):
                     def ready():
                         return all(fl_tile[me][s] >= want for s in range(size))
 
@@ -512,9 +513,9 @@ def _simulate_scatter_protocol(size: int, launches: list, seed: int, capacity: i
                         for m in range(first + gi * G, min(M, first + rpr, first + (gi + 1) * G)):
                             for s in range(size):
                                 assert recv[me][(s, m - first)] == li, ("receive area reused too early", li, me, s, m)
-                            for d in range(1, size):
+                            for d in range(1, size if push else 1):
                                 gather[(me + d) % size][m] = li
-                        for d in range(1, size):
+                        for d in range(1, size if push else 1):
                             fl_group[(me + d) % size][me] += 1
                     return (ready, run)
                 streams[me].append([reduce_cta(gi) for gi in range(groups[me])])
@@ -528,10 +529,11 @@ def _simulate_scatter_protocol(size: int, launches: list, seed: int, capacity: i
                         for m in range(first + gi * G, min(M, first + rpr, first + (gi + 1) * G)):
                             assert gather[me][m] == li, ("gather area reused too early", li, me, src, m)
                     return (ready, run)
-                if finish:
+                if finish and push:
                     streams[me].append([finish_cta(s, gi) for s in range(size) if s != me for gi in range(groups[s])])
-        else:  # all-gather -> GEMM, preceded by a barrier (ordered=False)
-            barriers += 1
+        else:  # all-gather -> GEMM, preceded by a barrier unless the caller vouches for the order ("gather_ordered")
+            with_barrier = barrier and kind == "gather"
+            barriers += 1 if with_barrier else 0
             for r in range(size):
                 cum_ag[r] += groups[r]
             t_ag = list(cum_ag)
@@ -545,7 +547,7 @@ def _simulate_scatter_protocol(size: int, launches: list, seed: int, capacity: i
                     def run():
                         arrived[me] += 1
                     return (lambda: True, run)
-                if barrier:
+                if with_barrier:
                     streams[me].append([arrive_cta()])
                     streams[me].append([barrier_cta()])
 
@@ -613,6 +615,10 @@ def test_scatter_gather_protocol_has_no_deadlock_and_no_early_reuse(size):
                 ("gather", 256 * size), ("gather", 300 * size), ("scatter", 256 * size)]
     for seed in range(6):
         _simulate_scatter_protocol(size, launches, seed, capacity=1 + seed % 3)
+    # sequence-parallel chain: reduce-scatter and all-gather -> GEMM alternate with no finish kernel and no barrier
+    chain = [("rs", 256 * size + 40), ("gather_ordered", 256 * size + 40)] * 4
+    for seed in range(6):
+        _simulate_scatter_protocol(size, chain, seed, capacity=1 + seed % 3)
     # the model is sharp enough to see the two orderings the design relies on: without the finish kernel a fast rank's next GEMM
     # overwrites a receive area that is still being reduced; without the barrier two all-gathers in a row overwrite the gather area
     def broken(seq, **kw):
@@ -625,3 +631,4 @@ def test_scatter_gather_protocol_has_no_deadlock_and_no_early_reuse(size):
 
     assert "reused too early" in broken([("scatter", 512 * size)] * 6, finish=False)
     assert "gather area" in broken([("gather", 512 * size)] * 6, barrier=False)
+    assert "reused too early" in broken([("rs", 512 * size)] * 6)  # plain reduce-scatters back to back need an ordering step between them

@@ -34,5 +34,6 @@ def test_two_rank_gemm_reduce_scatter():
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     scat = [l for l in lines if l.get("check") == "gemm_reduce_scatter_gather"]
     assert len(scat) == 3 and all(l["ok"] for l in scat)
+    assert any(l.get("check") == "reduce_scatter_then_all_gather_gemm" and l["ok"] for l in lines)
     gath = [l for l in lines if l.get("check") == "all_gather_gemm"]
     assert len(gath) == 2 and all(l["ok"] for l in gath)
