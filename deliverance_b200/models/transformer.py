@@ -108,6 +108,10 @@ class DecoderModel:
         self.fused_rope = os.environ.get("DLV_FUSED_ROPE", "0") == "1" and cfg.head_dim == 128 and cfg.use_rope
         self.vocab_shard: Optional[tuple] = None
         self._moe_impl = None
+        # opt-in (DLV_TP_SEQ_PARALLEL=1): sequence-parallel prefill under tensor parallelism for batches of at least this many rows
+        self.sp_min_rows: Optional[int] = 256 * tp.size if (tp.enabled and os.environ.get("DLV_TP_SEQ_PARALLEL", "0") == "1") else None
+        self._sp = None  # (M, rows per rank, first own row, own rows) while such a forward runs
+        self._sp_ordered = False
 
     # ------------------------------------------------------------------------------------------------ loading
     def _dev(self, t: torch.Tensor, dtype=None) -> torch.Tensor:
@@ -348,7 +352,7 @@ class DecoderModel:
                                        self.n_heads, self.n_kv, cfg.head_dim, cfg.norm_eps, cfg.norm_weight_offset)
         else:
             with self._stage("causalselfattention.qkv_projection"):
-                qkv = ops.linear(x, lw.qkv)
+                qkv = self._col_parallel(x, lw.qkv)
                 if lw.lora:
                     qkv = self._lora(lw, "qkv", x, qkv)
             with self._stage("causalselfattention.rope"):
@@ -368,8 +372,47 @@ class DecoderModel:
                 o = self._lora(lw, "o", a, o)
         return o
 
+    # ---- sequence parallelism for prefill-size batches under tensor parallelism (opt-in) ----
+    # Between a row-parallel and the next column-parallel projection every rank keeps only the token rows it owns: the sum over
+    # ranks becomes a reduce-scatter, residual add and norms run on 1 / size of the rows, and the column-parallel projection
+    # gathers its input (peer-memory kernels of parallel/fused.py on GPUs, plain collectives otherwise).
+    def _sp_plan(self, batch: ForwardBatch):
+        """``(M, rows_per_rank, first, count)`` when this forward runs sequence parallel, else ``None``."""
+        if not self.tp.enabled or batch.is_decode or self.sp_min_rows is None or type(self) is not DecoderModel:
+            return None
+        M = int(batch.token_ids.shape[0])
+        if M < self.sp_min_rows or self.fused_rope or self.cfg.model_type == "granitemoehybrid":
+            return None
+        if any(lw.kind == "mamba" or lw.router is not None or lw.lora or lw.fused_act for lw in self.layers):
+            return None
+        from ..parallel.fused import row_cut
+
+        rpr, first, count = row_cut(M, self.tp.size, self.tp.rank)
+        return M, rpr, first, count
+
+    def _gather_rows(self, x_own: torch.Tensor) -> torch.Tensor:
+        M, rpr, _, _ = self._sp
+        if x_own.shape[0] < rpr:
+            x_own = torch.cat([x_own, x_own.new_zeros(rpr - x_own.shape[0], x_own.shape[1])], dim=0)
+        return torch.cat(self.tp.collectives.all_gather(x_own.contiguous()), dim=0)[:M]
+
+    def _col_parallel(self, x: torch.Tensor, w: LinearWeight) -> torch.Tensor:
+        """Column-parallel projection; in a sequence-parallel forward ``x`` holds this rank's rows and the result all rows."""
+        if self._sp is None:
+            return ops.linear(x, w)
+        if self.tp.fused is not None and x.device.type == "cuda":
+            # the first gather of a forward orders the ranks itself; later ones follow a reduce-scatter, which does
+            ordered, self._sp_ordered = self._sp_ordered, True
+            return self.tp.fused.all_gather_linear(x, self._sp[0], w, ordered=ordered)
+        return ops.linear(self._gather_rows(x), w)
+
     def _row_parallel(self, x: torch.Tensor, w: LinearWeight, key: str) -> torch.Tensor:
-        """Row-parallel projection followed by the tensor-parallel sum."""
+        """Row-parallel projection followed by the tensor-parallel sum (sequence parallel: only this rank's rows of it)."""
+        if self._sp is not None:
+            _, _, first, count = self._sp
+            if self.tp.fused is not None and x.device.type == "cuda":
+                return self.tp.fused.linear_reduce_scatter(x, w, key)
+            return self.tp.all_reduce(key, ops.linear(x, w))[first:first + count].contiguous()
         if self.tp.enabled and self.tp.fused is not None and x.device.type == "cuda":
             return self.tp.fused.linear_all_reduce(x, w, key)
         y = ops.linear(x, w)
@@ -394,7 +437,7 @@ class DecoderModel:
                 h = ops.linear_act(x, lw.gate_up, cfg.hidden_act)
         else:
             with self._stage("mlpblock.gate_up_projection"):
-                gu = ops.linear(x, lw.gate_up)
+                gu = self._col_parallel(x, lw.gate_up)
                 if lw.lora:
                     gu = self._lora(lw, "gate_up", x, gu)
             with self._stage("mlpblock.activation_multiply"):
@@ -422,6 +465,19 @@ class DecoderModel:
         cfg = self.cfg
         residual = self.embed_tokens(batch)
         self._trace(-1, "embed", residual)
+        self._sp, self._sp_ordered = self._sp_plan(batch), False
+        if self._sp is not None:
+            residual = residual[self._sp[2]:self._sp[2] + self._sp[3]].contiguous()  # the residual stream stays row-sharded
+        try:
+            x = self._layers_forward(batch, kv, residual)
+            if self._sp is not None:
+                x = self._gather_rows(x)
+        finally:
+            self._sp = None
+        return x
+
+    def _layers_forward(self, batch: ForwardBatch, kv, residual: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
         eps, off, rm = cfg.norm_eps, cfg.norm_weight_offset, cfg.residual_multiplier
         x = ops.rmsnorm(residual, self.layers[0].input_norm, eps, off)
         for i, lw in enumerate(self.layers):

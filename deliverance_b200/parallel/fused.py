@@ -28,6 +28,14 @@ from .context import TensorParallelContext
 NCTA_MAX = 1024
 
 
+def row_cut(M: int, size: int, rank: int) -> tuple:
+    """``(rows_per_rank, first, count)``: rank ``rank`` owns token rows ``[first, first + count)`` of an ``M``-row batch; rows per rank
+    are ``ceil(M / size)`` rounded up to 8 (the same cut as the extension's ``scatter_plan``)."""
+    rpr = -(-(-(-M // size)) // 8) * 8
+    first = min(M, rank * rpr)
+    return rpr, first, max(0, min(rpr, M - rank * rpr))
+
+
 def scatter_enabled() -> bool:
     import os
 
@@ -126,8 +134,8 @@ class FusedTensorParallel:
 
     def own_rows(self, M: int) -> tuple:
         """``(first, count)``: the token rows of an ``M``-row batch this rank owns in the scatter / gather paths."""
-        v = ops.require_ext().scatter_plan(M, 128, self.tp.size)
-        return self.tp.rank * v[0], v[1 + self.tp.rank]
+        _, first, count = row_cut(M, self.tp.size, self.tp.rank)
+        return first, count
 
     def all_gather_linear(self, x_own: torch.Tensor, M: int, w, ordered: bool = False) -> torch.Tensor:
         """``all_gather(x) @ W_shard^T`` for activations whose rows are sharded over the ranks (``x_own`` = the rows of
@@ -148,7 +156,7 @@ class FusedTensorParallel:
         return ops.linear(full, w)
 
     def _rows_per_rank(self, M: int) -> int:
-        return ops.require_ext().scatter_plan(M, 128, self.tp.size)[0]
+        return row_cut(M, self.tp.size, self.tp.rank)[0]
 
     def all_reduce(self, x: torch.Tensor, key: str) -> torch.Tensor:
         """Sum a small bf16 ``[rows, H]`` tensor over the ranks with the one-shot peer-memory kernel, NCCL otherwise."""

@@ -632,3 +632,43 @@ def test_scatter_gather_protocol_has_no_deadlock_and_no_early_reuse(size):
     assert "reused too early" in broken([("scatter", 512 * size)] * 6, finish=False)
     assert "gather area" in broken([("gather", 512 * size)] * 6, barrier=False)
     assert "reused too early" in broken([("rs", 512 * size)] * 6)  # plain reduce-scatters back to back need an ordering step between them
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen3", "gemma2"])
+def test_sequence_parallel_prefill_matches_replicated(tmp_path, family):
+    """Opt-in sequence-parallel prefill (row-sharded residual stream between the projections) gives the same tokens as the
+    replicated tensor-parallel forward and as one rank; prompt lengths that do not divide by the ranks included."""
+    d = str(tmp_path / family)
+    over = dict(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=2)
+    if family != "llama":
+        over["head_dim"] = 32
+    write_tiny_model(d, family, seed=5, std=0.05, **over)
+    cfg = load_config(d)
+    prompt = [(7 * i + 3) % 200 + 5 for i in range(37)]
+
+    def run(ctx, out, idx, sp):
+        try:
+            m = DecoderModel(cfg, "cpu", tp=ctx).load(WeightLoader(d))
+            m.sp_min_rows = 2 if sp else None
+            seen = []
+            orig = m._sp_plan
+            m._sp_plan = lambda b: (seen.append(orig(b)), seen[-1])[1]
+            eng = Engine(m, EngineConfig(num_pages=32, max_batch_tokens=16))
+            out[idx] = (eng.generate(prompt, GeneratorParameters(max_tokens=6)).token_ids, sum(1 for x in seen if x is not None))
+        except Exception as e:  # noqa: BLE001
+            out[idx] = e
+
+    single = [None]
+    run(TensorParallelContext(), single, 0, False)
+    results = {}
+    for sp in (False, True):
+        group = InProcessGroup(2, timeout=60)
+        out = [None, None]
+        ts = [threading.Thread(target=run, args=(TensorParallelContext(r, 2, InProcessCollectives(group, r)), out, r, sp)) for r in range(2)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        assert not isinstance(out[0], Exception), out[0]
+        assert not isinstance(out[1], Exception), out[1]
+        results[sp] = out
+    assert results[True][0][0] == results[True][1][0] == results[False][0][0] == single[0][0]
+    assert results[True][0][1] >= 3 and results[False][0][1] == 0  # the 37-token prompt ran as 16 + 16 + 5 sequence-parallel chunks
