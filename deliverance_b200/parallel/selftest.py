@@ -183,6 +183,28 @@ def main() -> int:
     report(check="tp_model_tokens", sequences=len(prompts), equal_nccl=agree_nccl, equal_fused=agree_fused, first_token_equal=first_tok, ok=good,
            fused_calls=fused.stats["fused"], fallback_calls=fused.stats["fallback"])
 
+    # sequence-parallel prefill (DLV_TP_SEQ_PARALLEL=1): a prompt long enough for the row-sharded path against the same model on one GPU
+    n_long = 256 * world + 17
+    if os.environ.get("DLV_TP_SEQ_PARALLEL") == "1" and n_long + 8 <= shape["max_position_embeddings"]:
+        long_prompt = [torch.randint(0, 4096, (n_long,), generator=torch.Generator().manual_seed(99)).tolist()]
+        toks = {}
+        for name, ctx in (("single", TensorParallelContext()), ("tp_sp", tp)):
+            model = DecoderModel(cfg, dev, torch.bfloat16, ctx).load(SyntheticLoader(shape, 3, True, dev, std=0.05), head_quant="Q4")
+            used = []
+            plan = model._sp_plan
+            model._sp_plan = lambda b, plan=plan, used=used: (used.append(plan(b)), used[-1])[1]
+            ec = EngineConfig(num_pages=256, cuda_graphs=False)
+            ec.kv.enabled = False
+            rs = Engine(model, ec, eos_ids=(-1,)).generate_batch(long_prompt, GeneratorParameters(max_tokens=4))
+            toks[name] = (rs[0].token_ids, sum(1 for u in used if u is not None))
+            torch.cuda.synchronize()
+            ops.check_status(local)
+            dist.barrier()
+        good = toks["single"][0][0] == toks["tp_sp"][0][0] and toks["tp_sp"][1] >= 1
+        ok_all &= good
+        report(check="sequence_parallel_prefill_tokens", prompt=n_long, first_token_equal=good, sp_forwards=toks["tp_sp"][1],
+               equal_tokens=toks["single"][0] == toks["tp_sp"][0], ok=good)
+
     # ---------------------------------------------------------------- (2b) one-shot all-reduce and fused MoE combine
     e = ops.require_ext()
     g = torch.Generator().manual_seed(77)

@@ -26,7 +26,7 @@ def test_two_rank_selftest():
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.skipif(os.environ.get("DLV_TEST_TP_SCATTER") != "1", reason="GEMM -> reduce-scatter path is opt-in (DLV_TEST_TP_SCATTER=1)")
 def test_two_rank_gemm_reduce_scatter():
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, DLV_TP_SCATTER="1")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, DLV_TP_SCATTER="1", DLV_TP_SEQ_PARALLEL="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29519", "-m", "deliverance_b200.parallel.selftest"]
     p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
@@ -35,5 +35,6 @@ def test_two_rank_gemm_reduce_scatter():
     scat = [l for l in lines if l.get("check") == "gemm_reduce_scatter_gather"]
     assert len(scat) == 3 and all(l["ok"] for l in scat)
     assert any(l.get("check") == "reduce_scatter_then_all_gather_gemm" and l["ok"] for l in lines)
+    assert any(l.get("check") == "sequence_parallel_prefill_tokens" and l["ok"] for l in lines)
     gath = [l for l in lines if l.get("check") == "all_gather_gemm"]
     assert len(gath) == 2 and all(l["ok"] for l in gath)
