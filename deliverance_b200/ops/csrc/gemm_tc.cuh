@@ -113,6 +113,8 @@ struct GemmParams {
   int ag_rows;
 };
 
+static_assert(sizeof(GemmParams) + 2 * 128 <= 4096, "kernel parameters (two tensor maps + GemmParams) must fit the 4 KB parameter space");
+
 template <bool Q4, int BN>
 struct GemmSmem {
   static constexpr int kWTile = kGemmBM * 128;  // dense: one 64-wide bf16 sub-tile of W: 16 KB
