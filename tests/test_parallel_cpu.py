@@ -417,6 +417,10 @@ def test_scatter_plan_counts_match_the_epilogue_rule():
                         published[o] += n_tiles
                 assert published == list(tiles), (size, M, N)
                 assert list(groups) == [-(-r // 8) for r in rows]
+                from deliverance_b200.parallel.fused import row_cut
+
+                for r in range(size):  # the Python cut used by the model and the fallbacks is the extension's cut
+                    assert row_cut(M, size, r) == (rpr, min(M, r * rpr), rows[r])
 
 
 def test_all_gather_linear_fallback_reassembles_rows():
