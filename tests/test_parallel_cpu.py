@@ -638,8 +638,8 @@ def test_scatter_gather_protocol_has_no_deadlock_and_no_early_reuse(size):
     assert "reused too early" in broken([("rs", 512 * size)] * 6)  # plain reduce-scatters back to back need an ordering step between them
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "gemma2"])
-def test_sequence_parallel_prefill_matches_replicated(tmp_path, family):
+@pytest.mark.parametrize("family,ranks", [("llama", 2), ("qwen3", 2), ("gemma2", 2), ("llama", 4)])
+def test_sequence_parallel_prefill_matches_replicated(tmp_path, family, ranks):
     """Opt-in sequence-parallel prefill (row-sharded residual stream between the projections) gives the same tokens as the
     replicated tensor-parallel forward and as one rank; prompt lengths that do not divide by the ranks included."""
     d = str(tmp_path / family)
@@ -666,13 +666,13 @@ def test_sequence_parallel_prefill_matches_replicated(tmp_path, family):
     run(TensorParallelContext(), single, 0, False)
     results = {}
     for sp in (False, True):
-        group = InProcessGroup(2, timeout=60)
-        out = [None, None]
-        ts = [threading.Thread(target=run, args=(TensorParallelContext(r, 2, InProcessCollectives(group, r)), out, r, sp)) for r in range(2)]
+        group = InProcessGroup(ranks, timeout=60)
+        out = [None] * ranks
+        ts = [threading.Thread(target=run, args=(TensorParallelContext(r, ranks, InProcessCollectives(group, r)), out, r, sp)) for r in range(ranks)]
         [t.start() for t in ts]
         [t.join() for t in ts]
-        assert not isinstance(out[0], Exception), out[0]
-        assert not isinstance(out[1], Exception), out[1]
+        for o in out:
+            assert not isinstance(o, Exception), o
         results[sp] = out
-    assert results[True][0][0] == results[True][1][0] == results[False][0][0] == single[0][0]
+    assert all(o[0] == single[0][0] for o in results[True]) and results[False][0][0] == single[0][0]
     assert results[True][0][1] >= 3 and results[False][0][1] == 0  # the 37-token prompt ran as 16 + 16 + 5 sequence-parallel chunks
