@@ -1,5 +1,9 @@
 #!/usr/bin/env python
-"""Headline benchmark: Qwen3-4B-shaped dense decoder in JQ4, prefill of 2048 random tokens then decode, on N B200s (TP=N).
+"""Headline benchmark: Qwen3-4B-shaped dense decoder in JQ4, prefill of 2048 random tokens then decode, on N B200s.
+
+N > 1 (``--parallelism``): ``dp`` runs one engine replica per GPU with the full batch each (weak scaling; the default when the
+model fits one GPU with room to spare, which is how such a model is served for throughput), ``tp`` shards one engine over the
+GPUs with the fused tensor-parallel kernels (strong scaling: the same batch, lower latency per step).
 
 One "step" is one decode step of the whole batch (default 64 sequences, one new token each) after a real 2048-token
 prefill; ``value`` is decode tokens/s of the whole job (batch / step time, device-timed with CUDA events, max over ranks).
