@@ -92,7 +92,7 @@ class FusedTensorParallel:
         if scatter_enabled():
             import os
 
-            self.scatter = ScatterState(tp, self.device, int(os.environ.get("DLV_TP_SCATTER_ROWS", "4096")), max_cols)
+            self.scatter = ScatterState(tp, self.device, int(os.environ.get("DLV_TP_SCATTER_ROWS", "8192")), max_cols)
 
     @staticmethod
     def create(tp: TensorParallelContext, device) -> "FusedTensorParallel":
