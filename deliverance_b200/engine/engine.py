@@ -202,7 +202,10 @@ class Engine:
             if not self.kv.free_slots:
                 return False
             r.state_slot = self.kv.alloc_state_slot()
-        hit = self.kv.prefix.lookup(r.salt, r.fill)
+        # Recurrent (conv / SSM) state is not idempotent: a snapshot taken after L tokens may only be resumed at token L. A hit
+        # that covers the whole prompt would have to replay the last token on a state that already absorbed it, so hybrid
+        # models only take checkpoints strictly shorter than the prompt and prefill the remainder from the restored state.
+        hit = self.kv.prefix.lookup(r.salt, r.fill[:-1] if self.hybrid else r.fill)
         if hit is not None:
             r.pages = hit.pages
             r.prefix_hit = hit.length
@@ -542,8 +545,13 @@ class Engine:
         if g is None:
             g = self._capture(bucket)
         # stage inputs in pinned host buffers, one H2D copy per tensor
+        # Two staging sets used in turn: the H2D copies below are asynchronous, and with lookahead decode the host stages step
+        # N + 1 while the copies of step N may still be queued. A set is reused for step N + 2, which is staged only after the
+        # event recorded behind step N has been waited for, i.e. after its copies have been read.
         ps = self.page_size
-        h = g["host"]
+        slot = g["calls"] & 1
+        g["calls"] += 1
+        h = g["host"][slot]
         n = len(seqs)
         starts = [s["start"] for s in seqs]
         h["tok"][:n] = torch.tensor([s["tokens"][0] for s in seqs], dtype=torch.int32)
@@ -552,7 +560,7 @@ class Engine:
         h["ctx"][:n] = torch.tensor([p + 1 for p in starts], dtype=torch.int32)
         width = max(len(s["pages"]) for s in seqs)
         bt = h["bt"]
-        owners = g.setdefault("bt_owners", [None] * bucket)
+        owners = g["bt_owners"][slot]
         for i, s in enumerate(seqs):
             pg = s["pages"]
             key = (s.get("rid"), len(pg))  # between preemptions a request's page list only grows: same owner and length = same row
@@ -619,15 +627,16 @@ class Engine:
             logits = self.model.forward(batch, self.kv)
         launches = ops.LAUNCHES[0] - n0
         pin = dev.type == "cuda"
-        host = {
+        host = [{
             "tok": torch.zeros(bucket, dtype=torch.int32, pin_memory=pin),
             "pos": torch.zeros(bucket, dtype=torch.int32, pin_memory=pin),
             "slots": torch.zeros(bucket, dtype=torch.int64, pin_memory=pin),
             "ctx": torch.ones(bucket, dtype=torch.int32, pin_memory=pin),
             "bt": torch.zeros(bucket, self.max_pages_per_seq, dtype=torch.int32, pin_memory=pin),
             "st": torch.zeros(bucket, dtype=torch.int64, pin_memory=pin),
-        }
-        g = {"graph": graph, "batch": batch, "logits": logits, "host": host, "launches": launches}
+        } for _ in range(2)]
+        g = {"graph": graph, "batch": batch, "logits": logits, "host": host, "launches": launches, "calls": 0,
+             "bt_owners": [[None] * bucket, [None] * bucket]}
         self._graphs[bucket] = g
         return g
 

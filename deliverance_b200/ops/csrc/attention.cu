@@ -272,10 +272,9 @@ static int launch_decode_t(const void* q, long long q_stride, const void* kc, co
                            const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int page, float scale,
                            float cap, int window, int splits, cudaStream_t st) {
   const size_t smem = decode_smem_bytes<D, GP>();
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(decode_attn_kernel<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    attr_done = true;
   }
   dim3 grid(B, KV, splits);
   decode_attn_kernel<D, GP><<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), q_stride,
@@ -583,10 +582,9 @@ static int launch_decode_mma_t(const void* q, long long q_stride, const void* kc
                                const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int page, float scale,
                                float cap, int window, int splits, cudaStream_t st) {
   using L = DecodeMma<D>;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(decode_attn_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
-    attr_done = true;
   }
   dim3 grid(B, KV, splits);
   launch_pdl(decode_attn_mma_kernel<D>, dim3(grid), dim3(128), L::kBytes, st, static_cast<const __nv_bfloat16*>(q), q_stride,
@@ -787,10 +785,9 @@ static int launch_prefill_t(const void* q, long long q_stride, const void* kc, c
                             int num_tiles, void* out, int H, int KV, int page, float scale, float cap, int window, int causal,
                             cudaStream_t st) {
   const size_t smem = static_cast<size_t>(64 * D * 2) * 5;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(prefill_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    attr_done = true;
   }
   dim3 grid(num_tiles, H);
   prefill_attn_kernel<D><<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), q_stride, static_cast<const __nv_bfloat16*>(kc),

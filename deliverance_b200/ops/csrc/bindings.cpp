@@ -414,14 +414,6 @@ int64_t take_status(int64_t device) {
 void init_scratch(int64_t device) { scratch_for(static_cast<int>(device)); }
 // Debug: CTA (0,0,0) of every later GEMM launch stamps phase times (ns) into buf[0..15]; every CTA with linear index c < 2048
 // stamps start / first MMA / accumulator ready / end into buf[16 + 4c ..]. `buf` is int64 [8208] on the device; None stops it.
-void gemm_trace(c10::optional<Tensor> buf) {
-  if (!buf.has_value()) {
-    dlv::gemm_set_trace(nullptr);
-    return;
-  }
-  TORCH_CHECK(buf.value().is_cuda() && buf.value().scalar_type() == at::kLong && buf.value().numel() >= 8208, "trace buffer must be int64 [8208] on CUDA");
-  dlv::gemm_set_trace(reinterpret_cast<unsigned long long*>(buf.value().data_ptr<int64_t>()));
-}
 
 // ---- elementwise ----------------------------------------------------------------------------------------------------
 Tensor rmsnorm(const Tensor& x, const Tensor& w, double eps, double offset) {
@@ -887,7 +879,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("is_q4", &GemmWeight::is_q4);
   m.def("take_status", &take_status);
   m.def("init_scratch", &init_scratch);
-  m.def("gemm_trace", &gemm_trace);
   m.def("gemm_pdl", [](bool on) { dlv::gemm_set_pdl(on); });
   m.def("num_sms", &dlv::gemm_num_sms);
   m.def("rmsnorm", &rmsnorm);

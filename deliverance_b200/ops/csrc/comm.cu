@@ -14,8 +14,8 @@
 // once (grid <= 148, small CTAs), otherwise waiting CTAs could keep a peer's publishers from being scheduled.
 // Plain peer loads / stores only: no multimem, no TMA.
 //
-// The reference combines expert outputs on the coordinator after a gRPC round trip per expert group
-// (core/.../model/MixtureOfExpertsBlock.java:78-112; distributed/.../tensorparallel/TensorParallelCoordinator.java).
+// The reference keeps every expert on one host and combines their outputs locally, token by token (scale + accumulate,
+// core/.../model/MixtureOfExpertsBlock.java:78-112; Qwen3MoeFeedForward.java:175-183 scatterAdd); it has no expert parallelism.
 #include "common.cuh"
 #include "gemm_api.h"
 

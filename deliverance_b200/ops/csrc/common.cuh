@@ -145,6 +145,20 @@ inline cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem,
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// Per-kernel function attributes (dynamic shared-memory limit) belong to the device that was current when they were set, so
+// "already done" has to be remembered per device, not per process: a second GPU used by the same process needs its own call.
+struct PerDeviceOnce {
+  bool done[64] = {};
+  // true the first time this is called while the current device is current (always true for device ids outside the table)
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+};
+
 // ---- proxies / fences -----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // Orders what this thread has observed through ordinary loads (e.g. an acquired flag) before bulk copies it issues afterwards:

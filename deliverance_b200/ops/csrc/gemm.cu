@@ -86,8 +86,6 @@ void gemm_weight_init(GemmWeightDesc* w) {
 bool g_pdl_enabled = true;
 bool& g_gemm_pdl = g_pdl_enabled;  // programmatic dependent launch of the GEMM kernels (ops.set_gemm_pdl / DLV_GEMM_PDL=0 turn it off)
 void gemm_set_pdl(bool on) { g_gemm_pdl = on; }
-unsigned long long* g_gemm_trace = nullptr;
-void gemm_set_trace(unsigned long long* p) { g_gemm_trace = p; }
 
 
 int gemm_num_sms() {
@@ -106,11 +104,10 @@ template <bool Q4, int BN, int EPI = 0>
 static int cluster_capacity(int size) {
   using L = GemmSmem<Q4, BN>;
   static int cap[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDeviceOnce attr_once;  // the capacities below are shared: the GPUs of one process are the same model
+  if (attr_once.first()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<Q4, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-    attr_done = true;
   }
   if (size < 1 || size > 8) return 0;
   if (cap[size] < 0) {
@@ -287,7 +284,6 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
   p.out_f32 = out_f32 ? 1 : 0;
   p.bias = bias;
   p.status = status;
-  p.trace = g_gemm_trace;
 #define DLV_LAUNCH(BNV)                                                                              \
   if (w->is_q4) run_tc<true, BNV>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, force_splits, st, tp); \
   else run_tc<false, BNV>(w, x, M, ldx, p, ws, ws_floats, counters, n_counters, force_splits, st, tp)

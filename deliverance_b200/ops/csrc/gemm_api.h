@@ -56,7 +56,6 @@ bool gemm_scatter_supported(const GemmWeightDesc* w, int M, const GemmScatterArg
 void gemm_weight_init(GemmWeightDesc* w);
 int gemm_num_sms();
 void gemm_set_pdl(bool on);  // programmatic dependent launch of the GEMM kernels (on by default)
-void gemm_set_trace(unsigned long long* p);  // debug: device buffer of 16 u64 that CTA (0,0,0) stamps with globaltimer
 void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,
                  float* ws, size_t ws_floats, int* counters, int n_counters, int* status, int force_splits, cudaStream_t st,
                  const GemmTpArgs* tp = nullptr);

@@ -76,7 +76,6 @@ struct GemmParams {
   unsigned long long tp_flags[8];  // every rank's flag matrix (u32 [tp_size][tp_ncta_max], cumulative counters)
   unsigned int* tp_rounds;         // local: how many fused calls each CTA index has completed
   unsigned int* tp_call;           // local: [0] = number of fused launches completed, [1] = CTAs done in this launch
-  unsigned long long* trace;  // optional: 16 globaltimer stamps of CTA (0,0,0) (nullptr in production)
   // ---- grouped (mixture-of-experts) mode: blockIdx.y indexes a work list instead of a token tile ----
   // item = {expert, first row, end row, 0}; expert < 0 marks an unused slot (the CTA returns at once). The weights of all
   // local experts are stacked (JQ4: n_tiles tile rows per expert, dense: N rows per expert); N / n_tiles are per expert.
@@ -198,12 +197,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   int* s_last = const_cast<int*>(abort_flag) + 1;
   constexpr int NAS = Q4 ? NA : NW;  // depth of the A-operand ring
 
-  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#define DLV_STAMP(i) do { if (tracing) p.trace[i] = globaltimer_ns(); } while (0)
-  if (threadIdx.x == 0) DLV_STAMP(0);
-  const unsigned cta_lin = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-#define DLV_CTA_STAMP(j) do { if (p.trace != nullptr && cta_lin < 2048u) p.trace[16 + 4 * cta_lin + (j)] = globaltimer_ns(); } while (0)
-  if (threadIdx.x == 0) DLV_CTA_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int n_tile = blockIdx.x, split = blockIdx.z;
   const int m_tile = blockIdx.y;
@@ -267,7 +260,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) DLV_STAMP(1);
 
   // A single thread can only issue one bulk / tensor copy about every 0.3 us, whatever the size of the copy. So every stage
   // is ONE copy, and two warps per operand take alternate k-blocks (warps 0 + 19: weights, warps 2 + 20: activations).
@@ -382,7 +374,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         ok = ok && mbar_wait(smem_u32(&bar_x_full[sx]), (i / NX) & 1, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (i == 0 && lane == 0) { DLV_STAMP(2); DLV_CTA_STAMP(1); }
         tc_fence_after();
         if (lane == 0) {
           // descriptor start-address field counts 16-byte units: stage strides and the 32-byte k-step are added there
@@ -405,7 +396,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         __syncwarp();
       }
       if (lane == 0) {
-        if (issuer == 0) DLV_STAMP(3);
         umma_commit(smem_u32(bar_acc));  // one arrival per issuer
         if (!ok) {
           // outstanding MMAs must retire before TMEM is released
@@ -473,7 +463,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     // raised before the accumulator barrier can complete), so the named barriers below never miss a thread.
     asm volatile("bar.sync 1, 512;" ::: "memory");
     ok = (*abort_flag == 0);
-    if (t == 0) { DLV_STAMP(4); DLV_CTA_STAMP(2); }
     if (ok) {
       tc_fence_after();
       constexpr int GROUPS = BN >= 32 ? 4 : BN / 8;  // warps that share a quarter split the columns
@@ -504,11 +493,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     }
     if (splits == 1 || !p.cluster_reduce) asm volatile("bar.sync 1, 512;" ::: "memory");
   }
-  if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(5);
   // ---------------- reduce over the split-K cluster (distributed shared memory) and store ----------------
   const bool clustered = splits > 1 && p.cluster_reduce;
   if (clustered) cluster_sync_all();  // every CTA of the cluster has its partial tile in shared memory (or is aborting)
-  if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(6);
   if (warp >= kGemmEpiWarp0 && warp < kGemmEpiWarp0 + 16 && *abort_flag == 0) {
     const int t = threadIdx.x - kGemmEpiWarp0 * 32;
     const int row4 = (t & 31) * 4, csel = t >> 5;  // 4 consecutive weight rows, column slot 0..15
@@ -798,7 +785,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       }
     }
   }
-  if (threadIdx.x == kGemmEpiWarp0 * 32) DLV_STAMP(7);
   if (clustered) cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
   // ---------------- teardown ----------------
   tc_fence_before();
@@ -807,9 +793,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if (threadIdx.x == 0) { DLV_STAMP(8); DLV_CTA_STAMP(3); }
-#undef DLV_STAMP
-#undef DLV_CTA_STAMP
 }
 
 }  // namespace dlv

@@ -52,7 +52,11 @@ extern "C" int dlv_decode_attention_noalloc(const void* q, long long q_stride, c
   if (num_seqs < 0 || num_heads <= 0 || kv_heads <= 0 || num_heads % kv_heads != 0 || num_heads / kv_heads > 8) return DLV_NOALLOC_BAD_ARGUMENT;
   if (head_dim != 64 && head_dim != 128 && head_dim != 256) return DLV_NOALLOC_BAD_ARGUMENT;
   if (page_size <= 0 || page_size % 32 != 0 || bt_stride <= 0 || q_stride < static_cast<long long>(num_heads) * head_dim) return DLV_NOALLOC_BAD_ARGUMENT;
-  if ((reinterpret_cast<unsigned long long>(q) & 3ull) != 0 || (reinterpret_cast<unsigned long long>(out) & 3ull) != 0) return DLV_NOALLOC_BAD_ARGUMENT;
+  // the kernels read q and the caches with 16-byte vector loads (row t of q starts at q + t * q_stride elements) and write out
+  // with 4-byte stores: anything less aligned would fault on the device instead of being refused here
+  const unsigned long long align16 = reinterpret_cast<unsigned long long>(q) | reinterpret_cast<unsigned long long>(k_cache) |
+                                     reinterpret_cast<unsigned long long>(v_cache);
+  if ((align16 & 15ull) != 0 || q_stride % 8 != 0 || (reinterpret_cast<unsigned long long>(out) & 3ull) != 0) return DLV_NOALLOC_BAD_ARGUMENT;
   if (splits < 1 || splits > 64) return DLV_NOALLOC_BAD_ARGUMENT;
   if (num_seqs == 0) return DLV_NOALLOC_OK;
   float* part_o = nullptr;

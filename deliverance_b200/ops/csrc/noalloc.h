@@ -27,12 +27,14 @@ extern "C" {
 
 enum {
   DLV_NOALLOC_OK = 0,
-  DLV_NOALLOC_BAD_ARGUMENT = 1,   // null pointer, unsupported head_dim / group size, misaligned q, page size not a multiple of 32
+  DLV_NOALLOC_BAD_ARGUMENT = 1,   // null pointer, unsupported head_dim / group size, q / k_cache / v_cache not 16-byte aligned,
+                                  // q_stride not a multiple of 8 elements, out not 4-byte aligned, page size not a multiple of 32
   DLV_NOALLOC_TOO_LARGE = 2,      // the partial buffers would not fit in the built-in scratch
   DLV_NOALLOC_CUDA_ERROR = 3      // a CUDA runtime call failed; see dlv_noalloc_last_cuda_error()
 };
 
-// q: bf16 rows, row t at q + t * q_stride elements, heads contiguous [num_heads, head_dim].
+// q: bf16 rows, row t at q + t * q_stride elements, heads contiguous [num_heads, head_dim]; q must be 16-byte aligned and
+// q_stride a multiple of 8 elements (rows are read with 16-byte loads); k_cache / v_cache 16-byte aligned as well.
 // k_cache / v_cache: bf16 [pages, kv_heads, page_size, head_dim]. block_tables: int32 [num_seqs, bt_stride]. ctx_lens: int32.
 // out: bf16 [num_seqs, num_heads * head_dim]. splits >= 1 (1 uses no scratch at all).
 int dlv_decode_attention_noalloc(const void* q, long long q_stride, const void* k_cache, const void* v_cache, const int* block_tables,

@@ -1,7 +1,8 @@
 """Tensor-parallel serving in lockstep: rank 0 owns the HTTP front end, every rank owns one shard of the model.
 
-The reference keeps tensor-parallel workers in step by having the coordinator drive each of them over gRPC for every
-projection (distributed/.../tensorparallel/TensorParallelCoordinator.java; its workers never see a request). Here all
+The reference keeps tensor-parallel workers in step by having the coordinator call every rank's ``/forward`` or
+``/batchForward`` endpoint for each token (core/.../model/tensorparallel/TensorParallelGenerationGroup.java:216-235; its
+workers never see a request). Here all
 ranks run the same continuous-batching engine. What must be identical on every rank is the sequence of engine
 operations: which requests are admitted or cancelled before which step. Rank 0 therefore publishes one small command per
 loop iteration through a control group (gloo or thread ranks, never the NCCL stream): the token ids and parameters of new
@@ -56,18 +57,23 @@ class LockstepRunner(EngineRunner):
                         fresh.append(s)
             except queue.Empty:
                 pass
-            new, admitted = [], []
+            # A request is submitted to rank 0's engine BEFORE it is announced: only requests that the engine and the guide
+            # compiler accepted (prompt length, parameters, guided regex / schema, adapter id) reach the followers, so a malformed
+            # client request is answered with an error here and never costs a follower. No step runs between this point and the
+            # followers' own submit, so every rank still sees the same sequence of engine operations.
+            new = []
             for s in fresh:
                 try:
                     has_tools = isinstance(s.prompt, PromptContext) and s.prompt.has_tools
                     text = s.prompt.prompt if isinstance(s.prompt, PromptContext) else s.prompt
                     ids = self.clm.encode_prompt(text) if isinstance(text, str) else [int(t) for t in text]
                     s.session = s.session or f"s{self.stats['submitted']}-{id(s):x}"
-                    new.append((ids, copy.deepcopy(s.params), has_tools, s.session))
-                    admitted.append(s)
+                    announced = copy.deepcopy(s.params)
+                    s.generation = self.clm.submit(PromptIds(ids, has_tools), s.params, s.on_event, s.session)
+                    self.active.append(s)
+                    new.append((ids, announced, has_tools, s.session))
                 except Exception as e:  # noqa: BLE001 - bad request: report, keep serving
                     self._finish(s, e)
-            fresh = admitted
             cancel = [s.session for s in self.active if s.cancelled and s.session not in self._announced_cancel
                       and s.generation.request.state != "finished"]
             busy = eng.has_work() or new or cancel or stop or getattr(self, "_reset_followers", False)
@@ -82,17 +88,11 @@ class LockstepRunner(EngineRunner):
                 self._reset_followers = False
                 last_sent = time.monotonic()
             except Exception as e:  # noqa: BLE001 - a follower is gone: fail what is in flight
-                for s in fresh + list(self.active):
+                for s in list(self.active):
                     self._finish(s, RuntimeError(f"tensor-parallel control group failed: {e}"))
                 return
             if stop:
                 return
-            for s, (ids, params, has_tools, session) in zip(fresh, new):
-                try:
-                    s.generation = self.clm.submit(PromptIds(ids, has_tools), s.params, s.on_event, session)
-                    self.active.append(s)
-                except Exception as e:  # noqa: BLE001
-                    self._finish(s, e)
             for s in list(self.active):
                 if s.session in cancel:
                     self._announced_cancel.add(s.session)
@@ -152,7 +152,10 @@ def follower_loop(clm: CausalLanguageModel, control: Collectives, max_idle: Opti
         if cmd["stop"]:
             return steps
         for ids, params, has_tools, session in cmd["new"]:
-            live[session] = clm.submit(PromptIds(ids, has_tools), params, None, session)
+            try:
+                live[session] = clm.submit(PromptIds(ids, has_tools), params, None, session)
+            except Exception:  # noqa: BLE001 - rank 0 only announces what its own engine accepted; a rejection here must not end the rank
+                live.pop(session, None)
         for session in cmd["cancel"]:
             g = live.get(session)
             if g is not None and g.request.state != "finished":

@@ -545,3 +545,31 @@ def test_decode_interleave_bounds_the_wait_of_running_sequences(tiny):
     b_first, b_late, b_trace = run(1)
     assert a_first == b_first and a_late == b_late
     assert a_trace.startswith("pppppp") and "pp" not in b_trace and b_trace.count("p") == 6
+
+
+@pytest.mark.parametrize("family", ["granitemoehybrid", "llama"])
+def test_repeated_prompt_on_block_boundary_matches_uncached(tmp_path, family):
+    """A prompt whose length is a multiple of the block size, sent twice: the second run may reuse cached blocks but must produce
+    the tokens of an uncached run. Hybrid models must not resume a recurrent-state snapshot that already holds the last prompt
+    token (that token is replayed to get logits); they take a shorter checkpoint instead."""
+    d = str(tmp_path / "m")
+    write_tiny_model(d, family, seed=3, std=0.08)
+    model = DecoderModel(load_config(d), "cpu").load(WeightLoader(d))
+    rng = random.Random(9)
+    for n in (32, 64, 96, 70):
+        prompt = [rng.randrange(3, 250) for _ in range(n)]
+
+        def params():
+            return GeneratorParameters(max_tokens=12, temperature=1.0, top_p=0.95, seed=n)
+
+        want = Engine(model, EngineConfig(num_pages=64, max_batch_tokens=64, kv=KvCacheSettings(enabled=False)), eos_ids=(-1,)).generate(prompt, params())
+        eng = Engine(model, EngineConfig(num_pages=64, max_batch_tokens=64), eos_ids=(-1,))
+        first = eng.generate(prompt, params())
+        req = eng.add_request(prompt, params())
+        while eng.has_work():
+            eng.step()
+        assert first.token_ids == want.token_ids and req.output == want.token_ids, (family, n)
+        if n >= 64:
+            assert req.prefix_hit > 0, (family, n)
+        if family == "granitemoehybrid":
+            assert req.prefix_hit < n, (family, n)

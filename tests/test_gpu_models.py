@@ -151,11 +151,23 @@ def test_fused_activation_models_gpu(tmp_path, family, monkeypatch):
     fused = DecoderModel(cfg, "cuda:0").load(WeightLoader(d))
     assert any(lw.fused_act or lw.fused_act_experts for lw in fused.layers)
     g = torch.Generator().manual_seed(4)
-    prompts = [torch.randint(3, 250, (n,), generator=g).tolist() for n in (70, 33, 5)]
+    seqs = [torch.randint(3, 250, (n,), generator=g).tolist() for n in (70, 33, 5)]
     outs = []
     for m in (plain, fused):
-        eng = Engine(m, EngineConfig(num_pages=128, max_batch_tokens=96))
-        outs.append([r.token_ids for r in eng.generate_batch(prompts, GeneratorParameters(max_tokens=8))])
+        eng = Engine(m, EngineConfig(num_pages=128, cuda_graphs=False))
+        descr, nxt = [], 1
+        for i, t in enumerate(seqs):
+            n = (len(t) + 31) // 32
+            descr.append({"tokens": t, "start": 0, "pages": list(range(nxt, nxt + n)), "state_slot": i})
+            nxt += n
+        outs.append(m.forward(make_batch(descr, 32, m.device), eng.kv, all_rows=True).float().cpu())
         ops.check_status(0)
-    agree = sum(a == b for x, y in zip(*outs) for a, b in zip(x, y)) / sum(len(x) for x in outs[0])
-    assert agree > 0.9, (agree, outs)
+    # the epilogue applies the activation to fp32 accumulators, the two-kernel path to bf16-rounded ones: logits agree to bf16 noise
+    rel = ((outs[0] - outs[1]).norm() / outs[0].norm()).item()
+    assert rel < 2e-2, rel
+    assert (outs[0].argmax(-1) == outs[1].argmax(-1)).float().mean().item() > 0.9
+    # and the decode path (small token tiles, CUDA graphs) runs on the interleaved layout
+    eng = Engine(fused, EngineConfig(num_pages=128, max_batch_tokens=96))
+    rs = eng.generate_batch(seqs, GeneratorParameters(max_tokens=8))
+    ops.check_status(0)
+    assert all(r.generated_tokens == 8 for r in rs)

@@ -282,6 +282,54 @@ def test_lockstep_serving_thread_ranks(tmp_path):
     assert got == want and steps[0] >= 6
 
 
+def test_lockstep_bad_request_does_not_kill_followers(tmp_path):
+    """A request that the engine rejects (prompt over the context limit, a guided regex that does not compile) is answered with
+    an error on rank 0 and never announced; the follower keeps running and the next valid request gives the single-rank tokens."""
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.server.lockstep import LockstepRunner, follower_loop
+
+    d = str(tmp_path / "m")
+    write_tiny_model(d, "llama", seed=3, std=0.05, hidden_size=128, intermediate_size=256)
+    single = AutoModelForCausalLM.from_pretrained(d, device="cpu")
+    p = GeneratorParameters(max_tokens=6, temperature=0.0)
+    want = single.generate(PROMPT, p).token_ids
+    ctx = single.engine.cfg.max_position_embeddings
+    data, ctl = InProcessGroup(2, timeout=60.0), InProcessGroup(2, timeout=60.0)
+    clms = [None, None]
+
+    def build(rank):
+        clms[rank] = (AutoModelForCausalLM.new_builder(d).with_device("cpu")
+                      .with_tensor_parallel(rank, 2, InProcessCollectives(data, rank)).build())
+
+    ts = [threading.Thread(target=build, args=(r,)) for r in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    err = []
+
+    def follow():
+        try:
+            follower_loop(clms[1], InProcessCollectives(ctl, 1))
+        except Exception as e:  # noqa: BLE001
+            err.append(e)
+
+    ft = threading.Thread(target=follow, daemon=True)
+    ft.start()
+    runner = LockstepRunner(clms[0], InProcessCollectives(ctl, 0), heartbeat=0.05)
+    try:
+        too_long = runner.submit([5] * (ctx + 3), p)
+        with pytest.raises(ValueError):
+            too_long.wait(60)
+        bad_regex = runner.submit(PROMPT, GeneratorParameters(max_tokens=4, guided_regex="(unclosed"))
+        with pytest.raises(Exception):
+            bad_regex.wait(60)
+        assert ft.is_alive() and not err
+        got = runner.submit(PROMPT, p).wait(60).token_ids
+    finally:
+        runner.close()
+        ft.join(timeout=30)
+    assert got == want and not err and not ft.is_alive()
+
+
 _CLUSTER_CHILD = r"""
 import os, sys, time
 import torch, torch.distributed as dist

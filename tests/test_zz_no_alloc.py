@@ -72,5 +72,12 @@ def test_noalloc_decode_attention_matches_allocating_op():
     rc = lib.dlv_decode_attention_noalloc(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bt.stride(0), cl.data_ptr(),
                                           out.data_ptr(), B, H, KV, 96, page, scale, 0.0, 0, 2, stream)
     assert rc == 1  # unsupported head_dim
+    # pointers or strides that the kernels' 16-byte loads could not take are refused on the host (nothing is launched on them)
+    args = dict(q=q.data_ptr(), qs=q.stride(0), k=kc.data_ptr(), v=vc.data_ptr())
+    for bad in (dict(q=q.data_ptr() + 4), dict(qs=q.stride(0) + 4), dict(k=kc.data_ptr() + 8), dict(v=vc.data_ptr() + 2)):
+        a = dict(args, **bad)
+        rc = lib.dlv_decode_attention_noalloc(a["q"], a["qs"], a["k"], a["v"], bt.data_ptr(), bt.stride(0), cl.data_ptr(), sentinel.data_ptr(),
+                                              B, H, KV, D, page, scale, 0.0, 0, 2, stream)
+        assert rc == 1, bad
     torch.cuda.synchronize(dev)
     assert sentinel.float().abs().sum().item() == 0.0
