@@ -1,9 +1,9 @@
 #!/usr/bin/env python
 """Headline benchmark: Qwen3-4B-shaped dense decoder in JQ4, prefill of 2048 random tokens then decode, on N B200s.
 
-N > 1 (``--parallelism``): ``dp`` runs one engine replica per GPU with the full batch each (weak scaling; the default when the
-model fits one GPU with room to spare, which is how such a model is served for throughput), ``tp`` shards one engine over the
-GPUs with the fused tensor-parallel kernels (strong scaling: the same batch, lower latency per step).
+N > 1 (``--parallelism``): ``tp`` (the default) shards one engine over the GPUs with the fused tensor-parallel kernels (strong
+scaling: the same batch, lower latency per step); ``dp`` runs one engine replica per GPU with the full batch each (weak scaling,
+no communication), an explicit extra.
 
 One "step" is one decode step of the whole batch (default 64 sequences, one new token each) after a real 2048-token
 prefill; ``value`` is decode tokens/s of the whole job (batch / step time, device-timed with CUDA events, max over ranks).
@@ -115,16 +115,6 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def _approx_weight_gb(shape: dict, quant: str) -> float:
-    """Stored weight bytes of one full replica (matrices + embedding / output head), in GB."""
-    from deliverance_b200.bench.roofline import _weight_elems
-    from deliverance_b200.config import parse_config
-
-    stored, _, router, head = _weight_elems(parse_config(dict(shape)), 1)
-    bpe = 0.5625 if quant == "jq4" else 2.0
-    return (stored * bpe + router * 2.0 + head * (2.0 + bpe)) / 1e9
-
-
 def _shutdown(dist, eng) -> None:
     """Leave cleanly, and leave in any case: settle the step in flight, drop the captured graphs (they hold NCCL work when the
     all-reduce runs through NCCL), then tear the process group down under a timer. A communicator teardown that blocks (seen
@@ -152,7 +142,7 @@ def _shutdown(dist, eng) -> None:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="own", choices=["own", "reference", "torch"])
     ap.add_argument("--batch", type=int, default=64)
@@ -163,8 +153,8 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
     ap.add_argument("--parallelism", default="auto", choices=["auto", "dp", "tp"],
-                    help="N > 1: dp = one engine replica per GPU, --batch sequences each (weak scaling); tp = one engine over N GPUs "
-                         "(tensor parallel, --batch sequences in total, strong scaling); auto = dp when the weights fit one GPU with room to spare")
+                    help="N > 1: tp (default) = one engine over N GPUs (tensor parallel, --batch sequences in total, strong scaling); "
+                         "dp = one engine replica per GPU, --batch sequences each (weak scaling, no communication)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -193,9 +183,7 @@ def main() -> int:
     dist = None
     mode = args.parallelism
     if mode == "auto":
-        # a replica per GPU serves more tokens per second than sharding a model that fits: shard only when the weights need it
-        weight_gb = _approx_weight_gb(SHAPES[args.shape], args.quant)
-        mode = "dp" if weight_gb < 0.25 * 180 and args.impl == "own" else "tp"
+        mode = "tp"  # the benchmark configuration is tensor parallel at every N; replicas (dp) are an explicit extra
     replicas = world if (world > 1 and mode == "dp") else 1
     if world > 1:
         import torch.distributed as dist

@@ -82,6 +82,8 @@ class TpComm {
     args_.call = reinterpret_cast<unsigned int*>(call.data_ptr<int>());
   }
   const dlv::GemmTpArgs* args() const { return &args_; }
+  // Bound of the peer-flag waits of the comm.cu kernels launched with this state, in milliseconds at a nominal 2 GHz (0: default).
+  void set_wait_limit_ms(double ms) { args_.wait_limit_cycles = ms > 0 ? static_cast<long long>(ms * 2.0e6) : 0; }
 
  private:
   dlv::GemmTpArgs args_;
@@ -856,7 +858,8 @@ Tensor q4_dequantize(const Tensor& packed, const Tensor& scales, bool to_bf16) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<TpComm, std::shared_ptr<TpComm>>(m, "TpComm")
-      .def(py::init<int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t, Tensor, Tensor>());
+      .def(py::init<int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t, Tensor, Tensor>())
+      .def("set_wait_limit_ms", &TpComm::set_wait_limit_ms);
   py::class_<TpScatter, std::shared_ptr<TpScatter>>(m, "TpScatter")
       .def(py::init<int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t>());
   m.def("scatter_plan", &scatter_plan);

@@ -29,6 +29,7 @@ struct CommParams {
   unsigned int* rounds;
   unsigned int* call;
   int* status;
+  long long wait_limit;  // SM cycles a peer-flag wait may take before the kernel gives up and sets the status word
 };
 
 // Publish this CTA's region to every rank and wait until every rank has published the same region to this rank.
@@ -45,7 +46,7 @@ __device__ __forceinline__ bool exchange_barrier(const CommParams& p, unsigned c
       const int dst = (p.rank + lane) % p.size;
       red_release_sys_add(reinterpret_cast<uint32_t*>(p.flags[dst]) + static_cast<size_t>(p.rank) * p.ncta_max + cta_id, 1u);
       const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flags[p.rank]);
-      ok_lane = flag_wait_ge(mine + static_cast<size_t>(lane) * p.ncta_max + cta_id, round + 1u, p.status);
+      ok_lane = flag_wait_ge(mine + static_cast<size_t>(lane) * p.ncta_max + cta_id, round + 1u, p.status, p.wait_limit);
     }
     const bool all = __all_sync(0xffffffffu, ok_lane);
     if (lane == 0) {
@@ -190,6 +191,7 @@ static CommParams make_params(const GemmTpArgs* tp, int* status) {
   p.rounds = tp->rounds;
   p.call = tp->call;
   p.status = status;
+  p.wait_limit = tp->wait_limit_cycles > 0 ? tp->wait_limit_cycles : kWaitLimitCycles;
   return p;
 }
 

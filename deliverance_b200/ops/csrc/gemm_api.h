@@ -30,6 +30,7 @@ struct GemmTpArgs {
   unsigned long long flags[8];   // flag matrix of every rank
   unsigned int* rounds = nullptr;  // local [ncta_max]
   unsigned int* call = nullptr;    // local [2]
+  long long wait_limit_cycles = 0; // bound of every peer-flag wait in SM cycles (0: the default of about 2 s)
 };
 
 // Peer-memory state of the GEMM -> reduce-scatter -> all-gather path for prefill-size batches (see gemm_tc_run_scatter).

@@ -137,8 +137,6 @@ def test_generate_gpu_graphs_vs_eager(tmp_path, family):
     assert res[0] == res[1]
 
 
-@pytest.mark.skipif(__import__("os").environ.get("DLV_TEST_FUSED_ACT") != "1",
-                    reason="epilogue activation: opt-in until checked on a B200 (DLV_TEST_FUSED_ACT=1)")
 @pytest.mark.parametrize("family", ["qwen3", "gemma2", "mixtral", "qwen3_moe"])
 def test_fused_activation_models_gpu(tmp_path, family, monkeypatch):
     """Models loaded with the interleaved gate|up layout (activation in the GEMM epilogue) against the default layout."""

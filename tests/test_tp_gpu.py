@@ -24,7 +24,6 @@ def test_two_rank_selftest():
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.skipif(os.environ.get("DLV_TEST_TP_SCATTER") != "1", reason="GEMM -> reduce-scatter path is opt-in (DLV_TEST_TP_SCATTER=1)")
 def test_two_rank_gemm_reduce_scatter():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, DLV_TP_SCATTER="1", DLV_TP_SEQ_PARALLEL="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
