@@ -343,7 +343,10 @@ class DecoderModel:
 
         return apply_lora_delta(x, y, slot.a, slot.b_scaled)
 
-    def attention(self, i: int, lw: LayerWeights, x: torch.Tensor, batch: ForwardBatch, kv) -> torch.Tensor:
+    def attention(self, i: int, lw: LayerWeights, x: torch.Tensor, batch: ForwardBatch, kv, norm_after=None):
+        """Self-attention block output. With ``norm_after = (residual, post_w, norm_w)`` returns ``(y, fused)``: when ``fused`` the
+        tensor-parallel sum, the residual add and the norm that follow were done behind the output projection and ``y`` is already
+        ``rmsnorm(residual)``; otherwise ``y`` is the block output as without the argument."""
         cfg = self.cfg
         k_cache, v_cache = kv.layer(i)
         local_rope = lw.kind == "sliding" and self.cos_local is not None
@@ -371,10 +374,14 @@ class DecoderModel:
                 a = ops.prefill_attention(q, k_cache, v_cache, batch.block_tables, batch.q_start, batch.q_len, batch.ctx_len,
                                           self.n_heads, cfg.scale, cfg.attn_softcap, window, True, batch.tile_seq, batch.tile_q0)
         with self._stage("causalselfattention.output_projection"):
+            if norm_after is not None and not lw.lora:
+                x = self._row_parallel_norm(a, lw.o, norm_after)
+                if x is not None:
+                    return x, True
             o = self._row_parallel(a, lw.o, f"layer.{i}.self_attn.o_proj")
             if lw.lora:
                 o = self._lora(lw, "o", a, o)
-        return o
+        return (o, False) if norm_after is not None else o
 
     # ---- sequence parallelism for prefill-size batches under tensor parallelism (opt-in) ----
     # Between a row-parallel and the next column-parallel projection every rank keeps only the token rows it owns: the sum over
@@ -410,6 +417,17 @@ class DecoderModel:
             return self.tp.fused.all_gather_linear(x, self._sp[0], w, ordered=ordered)
         return ops.linear(self._gather_rows(x), w)
 
+    def _row_parallel_norm(self, x: torch.Tensor, w: LinearWeight, norm_after):
+        """Row-parallel projection + tensor-parallel sum + residual add + norm behind it, when the peer-memory path takes it
+        (decode-size batches on GPUs); ``None`` otherwise."""
+        if self._sp is not None or not self.tp.enabled or self.tp.fused is None or x.device.type != "cuda":
+            return None
+        fn = getattr(self.tp.fused, "linear_reduce_norm", None)
+        if fn is None:
+            return None
+        residual, post_w, norm_w = norm_after
+        return fn(x, w, residual, norm_w, post_w, self.cfg.norm_eps, self.cfg.norm_weight_offset, self.cfg.residual_multiplier)
+
     def _row_parallel(self, x: torch.Tensor, w: LinearWeight, key: str) -> torch.Tensor:
         """Row-parallel projection followed by the tensor-parallel sum (sequence parallel: only this rank's rows of it)."""
         if self._sp is not None:
@@ -425,17 +443,19 @@ class DecoderModel:
                 y = self.tp.all_reduce(key, y)
         return y
 
-    def feed_forward(self, i: int, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+    def feed_forward(self, i: int, lw: LayerWeights, x: torch.Tensor, norm_after=None):
+        """Feed-forward block output; ``norm_after`` as in :meth:`attention` (dense blocks only)."""
         cfg = self.cfg
         if lw.router is not None and cfg.model_type != "granitemoehybrid":
-            return self.moe(i, lw, x)
+            y = self.moe(i, lw, x)
+            return (y, False) if norm_after is not None else y
         if cfg.model_type == "granitemoehybrid":
             with self._stage("mlpblock.shared"):
                 h = ops.act_mul(ops.linear(x, lw.shared_gate_up), cfg.hidden_act)
                 y = ops.linear(h, lw.shared_down)
             if lw.router is not None:
                 y = y + self.moe(i, lw, x)
-            return y
+            return (y, False) if norm_after is not None else y
         if lw.fused_act:
             with self._stage("mlpblock.gate_up_projection"):
                 h = ops.linear_act(x, lw.gate_up, cfg.hidden_act)
@@ -447,10 +467,14 @@ class DecoderModel:
             with self._stage("mlpblock.activation_multiply"):
                 h = ops.act_mul(gu, cfg.hidden_act)
         with self._stage("mlpblock.down_projection"):
+            if norm_after is not None and not lw.lora:
+                x2 = self._row_parallel_norm(h, lw.down, norm_after)
+                if x2 is not None:
+                    return x2, True
             d = self._row_parallel(h, lw.down, f"layer.{i}.mlp.down_proj")
             if lw.lora:
                 d = self._lora(lw, "down", h, d)
-        return d
+        return (d, False) if norm_after is not None else d
 
     def moe(self, i: int, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         from .moe import moe_forward
@@ -485,20 +509,31 @@ class DecoderModel:
         eps, off, rm = cfg.norm_eps, cfg.norm_weight_offset, cfg.residual_multiplier
         x = ops.rmsnorm(residual, self.layers[0].input_norm, eps, off)
         for i, lw in enumerate(self.layers):
+            # Under fused tensor parallelism a decode-size row-parallel projection hands the sum over the ranks, the residual add and the
+            # norm behind it to one row-wise kernel (``fused`` below); every other case runs the steps one by one.
+            split = self.tp.enabled and self.tp.fused is not None and self.layer_hook is None and type(self) is DecoderModel
             if lw.kind == "mamba":
-                a = self.mamba(i, lw, x, batch, kv)
+                a, fused = self.mamba(i, lw, x, batch, kv), False
+            elif split:
+                a, fused = self.attention(i, lw, x, batch, kv, (residual, lw.post_attn_norm, lw.pre_ff_norm))
             else:
-                a = self.attention(i, lw, x, batch, kv)
-            if lw.post_attn_norm is not None:
-                a = ops.rmsnorm(a, lw.post_attn_norm, eps, off)
-            self._trace(i, "attn", a)
-            x = ops.add_rmsnorm(a, residual, lw.pre_ff_norm, eps, off, rm)
-            f = self.feed_forward(i, lw, x)
-            if lw.post_ff_norm is not None:
-                f = ops.rmsnorm(f, lw.post_ff_norm, eps, off)
-            self._trace(i, "ff", f)
+                a, fused = self.attention(i, lw, x, batch, kv), False
+            if fused:
+                x = a
+            else:
+                if lw.post_attn_norm is not None:
+                    a = ops.rmsnorm(a, lw.post_attn_norm, eps, off)
+                self._trace(i, "attn", a)
+                x = ops.add_rmsnorm(a, residual, lw.pre_ff_norm, eps, off, rm)
             nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
-            x = ops.add_rmsnorm(f, residual, nxt, eps, off, rm)
+            f, fused = self.feed_forward(i, lw, x, (residual, lw.post_ff_norm, nxt)) if split else (self.feed_forward(i, lw, x), False)
+            if fused:
+                x = f
+            else:
+                if lw.post_ff_norm is not None:
+                    f = ops.rmsnorm(f, lw.post_ff_norm, eps, off)
+                self._trace(i, "ff", f)
+                x = ops.add_rmsnorm(f, residual, nxt, eps, off, rm)
             self._trace(i, "out", residual)
         return x
 

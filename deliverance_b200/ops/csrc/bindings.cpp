@@ -7,6 +7,7 @@
 #include <memory>
 #include <unordered_map>
 
+#include "chain_api.h"
 #include "gemm_api.h"
 
 namespace {
@@ -84,6 +85,17 @@ class TpComm {
   const dlv::GemmTpArgs* args() const { return &args_; }
   // Bound of the peer-flag waits of the comm.cu kernels launched with this state, in milliseconds at a nominal 2 GHz (0: default).
   void set_wait_limit_ms(double ms) { args_.wait_limit_cycles = ms > 0 ? static_cast<long long>(ms * 2.0e6) : 0; }
+  // NVSwitch multicast address of the receive area (every rank's area bound to one multicast object), 0 = not available
+  void set_multicast(int64_t mc_recv) {
+    TORCH_CHECK((mc_recv & 15) == 0, "multicast address must be 16-byte aligned");
+    args_.mc_recv = static_cast<unsigned long long>(mc_recv);
+  }
+  bool has_multicast() const { return args_.mc_recv != 0; }
+  dlv::GemmTpArgs with_mode(int mode) const {
+    dlv::GemmTpArgs a = args_;
+    a.mode = mode;
+    return a;
+  }
 
  private:
   dlv::GemmTpArgs args_;
@@ -341,6 +353,24 @@ class GemmWeight {
     check_last_error("fused tp gemm launch");
     return true;
   }
+  // First half of the split form: the GEMM publishes its partial tiles (mode 1: into every rank's slab, mode 2: into its own slab for
+  // the multicast reduction) and does not wait. Returns the number of CTAs launched (0: shape outside the fused path, nothing
+  // launched); tp_reduce_norm must follow on the same stream with that number.
+  int64_t run_tp_push(const Tensor& x, const TpComm& comm, int64_t mode) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(1) == desc_.K && x.stride(1) == 1, "x must be bf16 [M, K]");
+    TORCH_CHECK(x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x rows must be 16-byte aligned");
+    TORCH_CHECK(mode == 1 || (mode == 2 && comm.has_multicast()), "mode must be 1 (peer stores) or 2 (multicast reduction, needs the multicast address)");
+    const int M = static_cast<int>(x.size(0));
+    if (M == 0 || desc_.N % 8 != 0 || !dlv::gemm_tp_supported(&desc_, M, comm.args())) return 0;
+    const dlv::GemmTpArgs a = comm.with_mode(static_cast<int>(mode));
+    c10::cuda::CUDAGuard guard(x.device());
+    DeviceScratch& s = scratch_for(x.device().index());
+    dlv::gemm_tc_run(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), nullptr, desc_.N, false, nullptr, s.ws.data_ptr<float>(),
+                     static_cast<size_t>(s.ws.numel()), s.counters.data_ptr<int>(), static_cast<int>(s.counters.numel()), s.status.data_ptr<int>(), 0,
+                     cur_stream(), &a);
+    check_last_error("tp gemm (publish only) launch");
+    return a.last_ctas;
+  }
   // Row-parallel projection for prefill-size batches: GEMM whose epilogue scatters partial tiles to the ranks that own the token
   // rows, reduction of the owned rows, gather of the others. `out` holds the summed result on every rank. Returns false
   // (nothing launched) when the shape is outside this path. Not for CUDA-graph capture (expected counts are launch arguments).
@@ -399,6 +429,8 @@ class GemmWeight {
   }
   int64_t n() const { return desc_.N; }
   int64_t k() const { return desc_.K; }
+  const dlv::GemmWeightDesc* desc() const { return &desc_; }
+  const Tensor& data() const { return w_; }
   bool is_q4() const { return desc_.is_q4; }
 
  private:
@@ -414,9 +446,6 @@ int64_t take_status(int64_t device) {
   return v;
 }
 void init_scratch(int64_t device) { scratch_for(static_cast<int>(device)); }
-// Debug: CTA (0,0,0) of every later GEMM launch stamps phase times (ns) into buf[0..15]; every CTA with linear index c < 2048
-// stamps start / first MMA / accumulator ready / end into buf[16 + 4c ..]. `buf` is int64 [8208] on the device; None stops it.
-
 // ---- elementwise ----------------------------------------------------------------------------------------------------
 Tensor rmsnorm(const Tensor& x, const Tensor& w, double eps, double offset) {
   check_bf16(x, "x");
@@ -766,6 +795,44 @@ bool moe_combine_allreduce(const Tensor& ys, const Tensor& pos, const Tensor& w,
   check_last_error("moe_combine_allreduce");
   return true;
 }
+// Second half of the split form (see GemmWeight::run_tp_push): sum over the ranks (+ bias), then kind 0: out = sum; kind 1:
+// residual += [RMSNorm(post_w)](sum) * res_mult (in place) and out = RMSNorm(residual, norm_w).
+void tp_reduce_norm(const TpComm& comm, int64_t mode, int64_t ctas, int64_t M, int64_t N, int64_t kind, c10::optional<Tensor> bias,
+                    c10::optional<Tensor> residual, c10::optional<Tensor> post_w, c10::optional<Tensor> norm_w, Tensor& out, double eps, double offset,
+                    double res_mult) {
+  TORCH_CHECK(ctas > 0 && M > 0 && M <= 128 && N % 8 == 0 && N <= 12288, "bad reduce shape");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.is_contiguous(), "bad out");
+  dlv::GemmTpArgs a = comm.with_mode(static_cast<int>(mode));
+  a.last_ctas = static_cast<int>(ctas);
+  const float* bptr = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias.value().is_cuda() && bias.value().scalar_type() == at::kFloat && bias.value().numel() == N && bias.value().is_contiguous(), "bias must be fp32 [N]");
+    bptr = bias.value().data_ptr<float>();
+  }
+  void* rp = nullptr;
+  const void* pw = nullptr;
+  const void* nw = nullptr;
+  if (kind == 1) {
+    TORCH_CHECK(residual.has_value() && norm_w.has_value(), "residual and norm weight are required");
+    check_bf16(residual.value(), "residual");
+    check_bf16(norm_w.value(), "norm_w");
+    TORCH_CHECK(residual.value().dim() == 2 && residual.value().size(0) == M && residual.value().size(1) == N && norm_w.value().numel() == N, "residual / norm shape");
+    rp = residual.value().data_ptr();
+    nw = norm_w.value().data_ptr();
+    if (post_w.has_value()) {
+      check_bf16(post_w.value(), "post_w");
+      TORCH_CHECK(post_w.value().numel() == N, "post norm shape");
+      pw = post_w.value().data_ptr();
+    }
+  } else {
+    TORCH_CHECK(kind == 0, "kind must be 0 or 1");
+  }
+  c10::cuda::CUDAGuard guard(out.device());
+  DeviceScratch& s = scratch_for(out.device().index());
+  dlv::launch_tp_reduce_norm(&a, static_cast<int>(M), static_cast<int>(N), static_cast<int>(kind), bptr, rp, pw, nw, out.data_ptr(), static_cast<float>(eps),
+                             static_cast<float>(offset), static_cast<float>(res_mult), s.status.data_ptr<int>(), cur_stream());
+  check_last_error("tp_reduce_norm");
+}
 // One-shot all-reduce of a small bf16 tensor [rows <= 128, H] over peer memory; false when the shape is outside the fused path.
 bool oneshot_allreduce(const Tensor& x, const TpComm& comm, Tensor& out) {
   check_bf16(x, "x");
@@ -778,6 +845,161 @@ bool oneshot_allreduce(const Tensor& x, const TpComm& comm, Tensor& out) {
   check_last_error("oneshot_allreduce");
   return true;
 }
+
+// ---- persistent decode chain ------------------------------------------------------------------------------------------
+// A chain is described once (weights, buffers, norm weights are fixed for a model's lifetime) and run once per decode step and
+// layer: `run(M, positions, slots)`. All buffers have kChainMaxRows rows; rows >= M are ignored.
+class DecodeChain {
+ public:
+  DecodeChain() {}
+  // kind: 0 store, 1 add + norm (unscaled, see chain_api.h), 2 act(gate) * up, 3 q|k|v (set_qkv must follow), 4 add.
+  // dep: x is the output of the projection added before this one. scale_src: index of the add + norm stage whose row factor applies.
+  void add_op(const GemmWeight& w, const Tensor& x, int64_t kind, bool dep, int64_t scale_src, c10::optional<Tensor> bias,
+              c10::optional<Tensor> residual, c10::optional<Tensor> norm_w, c10::optional<Tensor> out, double eps, double offset, double res_mult,
+              const std::string& act) {
+    TORCH_CHECK(static_cast<int>(ops_.size()) < dlv::kChainMaxOps, "a chain holds at most 4 projections");
+    TORCH_CHECK(!sync_.defined(), "the chain is sealed by its first run");
+    const dlv::GemmWeightDesc* d = w.desc();
+    TORCH_CHECK(d->is_q4, "the decode chain takes JQ4 weights");
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(1) == d->K && x.is_contiguous() && x.size(0) >= dlv::kChainMaxRows,
+                "chain input must be contiguous bf16 [>= 64, K]");
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0 && d->K % 64 == 0 && d->N % 8 == 0, "chain input alignment / shape");
+    TORCH_CHECK(kind >= 0 && kind <= 4, "unknown tile stage");
+    dlv::ChainOp o;
+    o.wq = d->data;
+    o.N = d->N;
+    o.K = d->K;
+    o.x = x.data_ptr();
+    o.x_rows = static_cast<int>(x.size(0));
+    o.dep = dep;
+    o.scale_src = static_cast<int>(scale_src);
+    c10::cuda::CUDAGuard guard(x.device());
+    auto fopt = torch::TensorOptions().device(x.device()).dtype(torch::kFloat32);
+    Tensor ws = torch::empty({static_cast<long>(dlv::chain_ws_floats(d->N, d->K, dlv::chain_ctas()))}, fopt);
+    o.ws = ws.data_ptr<float>();
+    keep_.push_back(ws);
+    o.kind = static_cast<int>(kind);
+    if (bias.has_value()) {
+      TORCH_CHECK(bias.value().is_cuda() && bias.value().scalar_type() == at::kFloat && bias.value().numel() == d->N && bias.value().is_contiguous() && d->N % 4 == 0, "bias must be fp32 [N]");
+      TORCH_CHECK(kind != 2, "the activation stage takes no bias");
+      o.bias = bias.value().data_ptr<float>();
+    }
+    if (kind == 1 || kind == 4) {
+      TORCH_CHECK(residual.has_value(), "the stage needs the residual rows");
+      check_bf16(residual.value(), "residual");
+      TORCH_CHECK(residual.value().dim() == 2 && residual.value().size(0) >= dlv::kChainMaxRows && residual.value().size(1) == d->N && d->N % 4 == 0, "residual shape");
+      o.residual = residual.value().data_ptr();
+    }
+    if (kind == 1) {
+      TORCH_CHECK(norm_w.has_value(), "add + norm needs the norm weight");
+      check_bf16(norm_w.value(), "norm_w");
+      TORCH_CHECK(norm_w.value().numel() == d->N, "norm weight shape");
+      o.norm_w = norm_w.value().data_ptr();
+      Tensor ssq = torch::zeros({static_cast<long>((d->N + 127) / 128) * 64}, fopt);
+      o.ssq = ssq.data_ptr<float>();
+      keep_.push_back(ssq);
+    }
+    if (kind != 4) {
+      TORCH_CHECK(out.has_value(), "the stage needs an output buffer");
+      check_bf16(out.value(), "out");
+      const int64_t out_cols = kind == 2 ? d->N / 2 : (kind == 3 ? -1 : d->N);
+      TORCH_CHECK(out.value().dim() == 2 && out.value().size(0) >= dlv::kChainMaxRows && (out_cols < 0 || out.value().size(1) == out_cols),
+                  "chain output must be bf16 [>= 64, cols]");
+      o.out = out.value().data_ptr();
+    }
+    o.eps = static_cast<float>(eps);
+    o.offset = static_cast<float>(offset);
+    o.res_mult = static_cast<float>(res_mult);
+    o.act = act_code(act);
+    ops_.push_back(o);
+    keep_.push_back(x);
+    keep_.push_back(w.data());
+    for (auto& t : {bias, residual, norm_w, out})
+      if (t.has_value()) keep_.push_back(t.value());
+  }
+  void set_qkv(c10::optional<Tensor> q_norm_w, c10::optional<Tensor> k_norm_w, c10::optional<Tensor> cos_t, c10::optional<Tensor> sin_t, Tensor& k_cache,
+               Tensor& v_cache, int64_t H, int64_t KV, double eps, double norm_offset) {
+    check_bf16(k_cache, "k_cache");
+    check_bf16(v_cache, "v_cache");
+    TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(1) == KV && k_cache.is_contiguous() && v_cache.sizes() == k_cache.sizes() && v_cache.is_contiguous(),
+                "cache must be contiguous [pages, KV, page, head_dim]");
+    const int D = static_cast<int>(k_cache.size(3));
+    TORCH_CHECK(D == 64 || D == 128, "head_dim must be 64 or 128");
+    qkv_ = {};
+    if (q_norm_w.has_value()) {
+      check_bf16(q_norm_w.value(), "q_norm");
+      check_bf16(k_norm_w.value(), "k_norm");
+      TORCH_CHECK(q_norm_w.value().numel() == D && k_norm_w.value().numel() == D, "q/k norm weights must have head_dim entries");
+      qkv_.q_norm_w = reinterpret_cast<const __nv_bfloat16*>(q_norm_w.value().data_ptr());
+      qkv_.k_norm_w = reinterpret_cast<const __nv_bfloat16*>(k_norm_w.value().data_ptr());
+      keep_.push_back(q_norm_w.value());
+      keep_.push_back(k_norm_w.value());
+    }
+    qkv_.max_pos = 1;
+    if (cos_t.has_value()) {
+      TORCH_CHECK(cos_t.value().is_cuda() && cos_t.value().scalar_type() == at::kFloat && cos_t.value().dim() == 2 && cos_t.value().is_contiguous() &&
+                  sin_t.value().sizes() == cos_t.value().sizes() && sin_t.value().is_contiguous() && sin_t.value().is_cuda(), "cos/sin must be contiguous fp32 [max_pos, rot/2]");
+      qkv_.cos_t = cos_t.value().data_ptr<float>();
+      qkv_.sin_t = sin_t.value().data_ptr<float>();
+      qkv_.rot_half = static_cast<int>(cos_t.value().size(1));
+      qkv_.max_pos = static_cast<int>(cos_t.value().size(0));
+      TORCH_CHECK(qkv_.rot_half == D / 2, "the chain applies full rotary embeddings only");
+      keep_.push_back(cos_t.value());
+      keep_.push_back(sin_t.value());
+    }
+    qkv_.k_cache = reinterpret_cast<__nv_bfloat16*>(k_cache.data_ptr());
+    qkv_.v_cache = reinterpret_cast<__nv_bfloat16*>(v_cache.data_ptr());
+    qkv_.heads = static_cast<int>(H);
+    qkv_.kv_heads = static_cast<int>(KV);
+    qkv_.head_dim = D;
+    qkv_.block_size = static_cast<int>(k_cache.size(2));
+    qkv_.eps = static_cast<float>(eps);
+    qkv_.norm_offset = static_cast<float>(norm_offset);
+    keep_.push_back(k_cache);
+    keep_.push_back(v_cache);
+    has_qkv_ = true;
+  }
+  void run(int64_t M, c10::optional<Tensor> positions, c10::optional<Tensor> slots) {
+    TORCH_CHECK(!ops_.empty() && M >= 0 && M <= dlv::kChainMaxRows, "chain: 0..64 rows");
+    if (M == 0) return;
+    const int dev = static_cast<const Tensor&>(keep_.front()).device().index();
+    c10::cuda::CUDAGuard guard(keep_.front().device());
+    if (!sync_.defined()) {
+      sync_words_ = dlv::chain_sync_words(ops_.data(), static_cast<int>(ops_.size()));
+      sync_ = torch::zeros({sync_words_}, torch::TensorOptions().device(keep_.front().device()).dtype(torch::kInt32));
+    }
+    bool needs_qkv = false;
+    for (auto& o : ops_) needs_qkv = needs_qkv || o.kind == dlv::kChainRowQkvRope;
+    dlv::ChainQkvArgs a = qkv_;
+    if (needs_qkv) {
+      TORCH_CHECK(has_qkv_ && positions.has_value(), "the q|k|v stage needs set_qkv and positions");
+      TORCH_CHECK(positions.value().is_cuda() && positions.value().scalar_type() == at::kInt && positions.value().numel() >= M, "positions must be int32 [M]");
+      a.positions = positions.value().data_ptr<int>();
+      a.slots = nullptr;
+      if (slots.has_value()) {
+        TORCH_CHECK(slots.value().is_cuda() && slots.value().scalar_type() == at::kLong && slots.value().numel() >= M, "slots must be int64 [M]");
+        a.slots = reinterpret_cast<const long long*>(slots.value().data_ptr<int64_t>());
+      }
+    }
+    DeviceScratch& s = scratch_for(dev);
+    dlv::chain_run(ops_.data(), static_cast<int>(ops_.size()), needs_qkv ? &a : nullptr, static_cast<int>(M),
+                   reinterpret_cast<unsigned*>(sync_.data_ptr<int>()), sync_words_, s.status.data_ptr<int>(), cur_stream());
+    check_last_error("decode chain launch");
+  }
+  // after a launch that ended with a status error the counters may be left non-zero: clear them before the next launch
+  void reset() {
+    if (sync_.defined()) sync_.zero_();
+  }
+  Tensor counters() const { return sync_; }
+
+ private:
+  std::vector<dlv::ChainOp> ops_;
+  dlv::ChainQkvArgs qkv_ = {};
+  bool has_qkv_ = false;
+  Tensor sync_;
+  int sync_words_ = 0;
+  std::vector<Tensor> keep_;
+};
 
 // ---- Mamba2 -----------------------------------------------------------------------------------------------------------
 // meta: int32 tensors prepared on the host (row_seq [T], chunk_* [n_chunks], seq_chunk0 / seq_nchunks [S])
@@ -859,7 +1081,18 @@ Tensor q4_dequantize(const Tensor& packed, const Tensor& scales, bool to_bf16) {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<TpComm, std::shared_ptr<TpComm>>(m, "TpComm")
       .def(py::init<int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t, Tensor, Tensor>())
-      .def("set_wait_limit_ms", &TpComm::set_wait_limit_ms);
+      .def("set_wait_limit_ms", &TpComm::set_wait_limit_ms)
+      .def("set_multicast", &TpComm::set_multicast)
+      .def("has_multicast", &TpComm::has_multicast);
+  py::class_<DecodeChain, std::shared_ptr<DecodeChain>>(m, "DecodeChain")
+      .def(py::init<>())
+      .def("add_op", &DecodeChain::add_op, py::arg("w"), py::arg("x"), py::arg("kind"), py::arg("dep") = false, py::arg("scale_src") = -1,
+           py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("norm_w") = py::none(), py::arg("out") = py::none(),
+           py::arg("eps") = 1e-6, py::arg("offset") = 0.0, py::arg("res_mult") = 1.0, py::arg("act") = "silu")
+      .def("set_qkv", &DecodeChain::set_qkv)
+      .def("run", &DecodeChain::run, py::arg("M"), py::arg("positions") = py::none(), py::arg("slots") = py::none())
+      .def("reset", &DecodeChain::reset)
+      .def("counters", &DecodeChain::counters);
   py::class_<TpScatter, std::shared_ptr<TpScatter>>(m, "TpScatter")
       .def(py::init<int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t>());
   m.def("scatter_plan", &scatter_plan);
@@ -868,6 +1101,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("run", &GemmWeight::run, py::arg("x"), py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("out_f32") = false,
            py::arg("impl") = 0, py::arg("force_splits") = 0)
       .def("run_tp", &GemmWeight::run_tp, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
+      .def("run_tp_push", &GemmWeight::run_tp_push, py::arg("x"), py::arg("comm"), py::arg("mode") = 1)
       .def("run_scatter", &GemmWeight::run_scatter, py::arg("x"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none(),
            py::arg("gather") = true)
       .def("run_gathered", &GemmWeight::run_gathered, py::arg("x_own"), py::arg("M"), py::arg("out"), py::arg("comm"), py::arg("bias") = py::none())
@@ -905,6 +1139,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("e0") = 0, py::arg("ne") = 0);
   m.def("moe_combine_allreduce", &moe_combine_allreduce);
   m.def("oneshot_allreduce", &oneshot_allreduce);
+  m.def("tp_reduce_norm", &tp_reduce_norm, py::arg("comm"), py::arg("mode"), py::arg("ctas"), py::arg("M"), py::arg("N"), py::arg("kind"),
+        py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("post_w") = py::none(), py::arg("norm_w") = py::none(), py::arg("out"),
+        py::arg("eps") = 1e-6, py::arg("offset") = 0.0, py::arg("res_mult") = 1.0);
   m.def("mamba2_forward", &mamba2_forward);
   m.def("q4_quantize", &q4_quantize);
   m.def("q4_dequantize", &q4_dequantize, py::arg("packed"), py::arg("scales"), py::arg("to_bf16") = false);

@@ -213,6 +213,143 @@ void launch_oneshot_allreduce(const void* x, int rows, int H, void* out, const G
                                                  make_params(tp, status));
 }
 
+// ------------------------------------------------------------------------------------------------ tensor-parallel sum + residual + norm
+// Second half of a row-parallel projection whose GEMM epilogue only published its partial tiles (GemmTpArgs::mode 1 or 2) and left:
+// one CTA per token row waits (bounded) until every rank's GEMM CTAs have published, sums the ranks' partial rows in rank order
+// (mode 1: from this rank's receive slabs; mode 2: one multimem.ld_reduce per 16 bytes through the NVSwitch multicast address, the
+// switch adds the eight ranks' values on the way), adds the bias, and then does what follows the projection in the layer:
+//   kind 0: out = sum                                  (a plain all-reduce)
+//   kind 1: [sum = RMSNorm(sum, post_w)] ; residual += sum * res_mult ; out = RMSNorm(residual, norm_w)
+// so the peer wait sits in a kernel of M small CTAs instead of in the GEMM's 148 large ones, the weight stream of the next GEMM
+// (launched with programmatic stream serialization) runs underneath it, and the separate add + norm launch disappears.
+// Replaces the all-reduce call sites core/.../generator/CausalSelfAttention.java:403-405,448-452 and
+// core/.../model/tensorparallel/TensorParallelMlp.java:169-171 together with the residual add and norm of TransformerBlock.java:161-200.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p, int N, int ncta, int mode, unsigned long long mc_recv, int kind,
+                                                             const float* __restrict__ bias, __nv_bfloat16* residual,
+                                                             const __nv_bfloat16* __restrict__ post_w, const __nv_bfloat16* __restrict__ norm_w,
+                                                             __nv_bfloat16* __restrict__ out, float eps, float offset, float res_mult) {
+  pdl_wait();     // the GEMM in front of this kernel has completed on this rank: its round counters and launch counter are final
+  pdl_trigger();
+  extern __shared__ float row[];  // N floats
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const int m = blockIdx.x;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  // every rank's GEMM CTAs have published this call (the GEMM left rounds[cta] at the value its peers' counters must reach)
+  const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flags[p.rank]);
+  for (int idx = threadIdx.x; idx < p.size * ncta; idx += blockDim.x) {
+    const int src = idx / ncta, cta = idx - src * ncta;
+    if (!flag_wait_ge(mine + static_cast<size_t>(src) * p.ncta_max + cta, p.rounds[cta], p.status, p.wait_limit)) s_ok = 0;
+  }
+  __syncthreads();
+  if (s_ok == 0) return;
+  const unsigned call = *reinterpret_cast<volatile unsigned*>(p.call) - 1u;  // the GEMM's last CTA has already advanced the counter
+  const long long par_off = static_cast<long long>(call & 1u) * p.size * p.slab;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < N; i += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    if (mode == 2) {
+      const uint4 v = multimem_ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(mc_recv) + par_off + static_cast<long long>(m) * N + i);
+      const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf162(vu[e]);
+        acc[2 * e] = f.x;
+        acc[2 * e + 1] = f.y;
+      }
+    } else {
+      const __nv_bfloat16* rbase = reinterpret_cast<const __nv_bfloat16*>(p.recv[p.rank]) + par_off + static_cast<long long>(m) * N + i;
+      for (int src = 0; src < p.size; ++src) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(rbase + static_cast<long long>(src) * p.slab));
+        const uint32_t* vu = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf162(vu[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float v = bf2f(f2bf(acc[e] + (bias != nullptr ? bias[i + e] : 0.f)));  // rounded like the output of the fused GEMM + all-reduce
+      row[i + e] = v;
+      ss += v * v;
+    }
+  }
+  if (kind == 0) {
+    __syncthreads();
+    for (int i = threadIdx.x * 8; i < N; i += blockDim.x * 8) {
+      uint4 o;
+      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ou[e] = pack_bf162(row[i + 2 * e], row[i + 2 * e + 1]);
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * N + i) = o;
+    }
+    return;
+  }
+  if (post_w != nullptr) {  // gemma2: norm on the block output before it joins the residual stream
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / N + eps);
+    for (int i = threadIdx.x * 8; i < N; i += blockDim.x * 8) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) row[i + e] = bf2f(f2bf(row[i + e] * inv * (bf2f(post_w[i + e]) + offset)));
+    }
+  }
+  ss = 0.f;
+  for (int i = threadIdx.x * 8; i < N; i += blockDim.x * 8) {
+    __nv_bfloat16* rp = residual + static_cast<size_t>(m) * N + i;
+    const uint4 rv = *reinterpret_cast<const uint4*>(rp);
+    const uint32_t* ru = reinterpret_cast<const uint32_t*>(&rv);
+    uint4 ov;
+    uint32_t* ou = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf162(ru[e]);
+      ou[e] = pack_bf162(f.x + row[i + 2 * e] * res_mult, f.y + row[i + 2 * e + 1] * res_mult);
+      const float2 back = unpack_bf162(ou[e]);  // the norm sees the stored (rounded) residual
+      row[i + 2 * e] = back.x;
+      row[i + 2 * e + 1] = back.y;
+      ss += back.x * back.x + back.y * back.y;
+    }
+    *reinterpret_cast<uint4*>(rp) = ov;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / N + eps);
+  for (int i = threadIdx.x * 8; i < N; i += blockDim.x * 8) {
+    const uint4 wv = *reinterpret_cast<const uint4*>(norm_w + i);
+    const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+    uint4 o;
+    uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf162(wu[e]);
+      ou[e] = pack_bf162(row[i + 2 * e] * inv * (f.x + offset), row[i + 2 * e + 1] * inv * (f.y + offset));
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * N + i) = o;
+  }
+}
+
+void launch_tp_reduce_norm(const GemmTpArgs* tp, int M, int N, int kind, const float* bias, void* residual, const void* post_w, const void* norm_w,
+                           void* out, float eps, float offset, float res_mult, int* status, cudaStream_t st) {
+  if (M == 0) return;
+  launch_pdl(tp_reduce_norm_kernel, dim3(M), dim3(256), static_cast<size_t>(N) * sizeof(float), st, make_params(tp, status), N, tp->last_ctas, tp->mode,
+             tp->mc_recv, kind, bias, static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(post_w),
+             static_cast<const __nv_bfloat16*>(norm_w), static_cast<__nv_bfloat16*>(out), eps, offset, res_mult);
+}
+
 // ------------------------------------------------------------------------------------------------ reduce-scatter + all-gather
 // Second and third step of the prefill-size tensor-parallel projection (the first is the GEMM with epilogue EPI = 3, which has
 // stored every rank's partial sums of MY token rows into my receive area [size sources][rows_per_rank][N]).

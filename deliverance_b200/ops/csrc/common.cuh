@@ -279,6 +279,9 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 // Wait until *p >= target. Returns false (and records kStatusFlagTimeout) when `limit_cycles` SM cycles pass first.
 __device__ __forceinline__ bool flag_wait_ge(const uint32_t* p, uint32_t target, int* status,
                                              long long limit_cycles = kWaitLimitCycles) {

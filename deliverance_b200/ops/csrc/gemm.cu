@@ -195,6 +195,8 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
     }
     p.tp_rounds = tp->rounds;
     p.tp_call = tp->call;
+    p.tp_mode = tp->mode;
+    tp->last_ctas = tiles * splits;
   }
   p.splits = splits;
   p.cluster_reduce = cluster ? 1 : 0;

@@ -31,6 +31,13 @@ struct GemmTpArgs {
   unsigned int* rounds = nullptr;  // local [ncta_max]
   unsigned int* call = nullptr;    // local [2]
   long long wait_limit_cycles = 0; // bound of every peer-flag wait in SM cycles (0: the default of about 2 s)
+  // What the row-parallel GEMM epilogue does with its partial tile: 0 = store it into every rank's slab, wait for the peers and
+  // reduce (GEMM + all-reduce in one kernel); 1 = store it into every rank's slab, publish and leave (launch_tp_reduce_norm waits,
+  // sums the ranks and applies the residual add and the norm that follow the projection); 2 = store it into this rank's own slab,
+  // publish and leave (the reduce kernel sums through the NVSwitch multicast address mc_recv with multimem.ld_reduce).
+  int mode = 0;
+  unsigned long long mc_recv = 0;  // multicast (NVLS) address of the receive area, 0 when not bound
+  mutable int last_ctas = 0;       // CTAs of the last fused launch (the reduce kernel waits for that many publications per rank)
 };
 
 // Peer-memory state of the GEMM -> reduce-scatter -> all-gather path for prefill-size batches (see gemm_tc_run_scatter).
@@ -151,6 +158,10 @@ bool comm_rows_supported(const GemmTpArgs* tp, int rows, int H);
 void launch_moe_combine_allreduce(const void* ys, const int* pos, const float* w, int T, int k, int H, const int* offsets, int e0, int ne,
                                   void* out, const GemmTpArgs* tp, int* status, cudaStream_t st);
 void launch_oneshot_allreduce(const void* x, int rows, int H, void* out, const GemmTpArgs* tp, int* status, cudaStream_t st);
+// Second half of a row-parallel projection launched with GemmTpArgs::mode 1 or 2 (see comm.cu): wait for the ranks, sum them, then
+// kind 0: out = sum; kind 1: residual += [RMSNorm(post_w)](sum) * res_mult, out = RMSNorm(residual, norm_w). N % 8 == 0, N <= 12288.
+void launch_tp_reduce_norm(const GemmTpArgs* tp, int M, int N, int kind, const float* bias, void* residual, const void* post_w, const void* norm_w,
+                           void* out, float eps, float offset, float res_mult, int* status, cudaStream_t st);
 
 // Sum the size partial slabs of this rank's rows (+ bias). push: write them to out [M, N] and to every peer's gather area and
 // publish (all-reduce, follow with launch_scatter_finish); !push: write them to out [own rows, N] only (reduce-scatter).

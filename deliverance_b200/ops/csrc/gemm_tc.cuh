@@ -76,6 +76,7 @@ struct GemmParams {
   unsigned long long tp_flags[8];  // every rank's flag matrix (u32 [tp_size][tp_ncta_max], cumulative counters)
   unsigned int* tp_rounds;         // local: how many fused calls each CTA index has completed
   unsigned int* tp_call;           // local: [0] = number of fused launches completed, [1] = CTAs done in this launch
+  int tp_mode;                     // 0: publish, wait and reduce here; 1: publish to every rank and leave; 2: publish to the own slab and leave
   // ---- grouped (mixture-of-experts) mode: blockIdx.y indexes a work list instead of a token tile ----
   // item = {expert, first row, end row, 0}; expert < 0 marks an unused slot (the CTA returns at once). The weights of all
   // local experts are stacked (JQ4: n_tiles tile rows per expert, dense: N rows per expert); N / n_tiles are per expert.
@@ -733,6 +734,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
           uint2 pk;
           pk.x = pack_bf162(acc.x, acc.y);
           pk.y = pack_bf162(acc.z, acc.w);
+          if (p.tp_mode == 2) {  // own slab, slot 0: the reduce kernel sums the ranks' slot 0 through the multicast address
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.tp_recv[p.tp_rank]) + par_off + static_cast<long long>(m) * p.N + n) = pk;
+            continue;
+          }
           const long long off = par_off + static_cast<long long>(p.tp_rank) * p.tp_slab + static_cast<long long>(m) * p.N + n;
           for (int r = 0; r < p.tp_size; ++r)
             *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.tp_recv[(p.tp_rank + r) % p.tp_size]) + off) = pk;
@@ -748,14 +753,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         if (t < p.tp_size) {
           const int dst = (p.tp_rank + t) % p.tp_size;
           red_release_sys_add(reinterpret_cast<uint32_t*>(p.tp_flags[dst]) + static_cast<size_t>(p.tp_rank) * p.tp_ncta_max + cta_id, 1u);
-          // phase B gate: rank `t` has published this CTA's region for this call
+          // phase B gate: rank `t` has published this CTA's region for this call (modes 1 / 2: the reduce kernel waits instead)
           const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.tp_flags[p.tp_rank]);
-          ok_lane = flag_wait_ge(mine + static_cast<size_t>(t) * p.tp_ncta_max + cta_id, round + 1u, p.status);
+          if (p.tp_mode == 0) ok_lane = flag_wait_ge(mine + static_cast<size_t>(t) * p.tp_ncta_max + cta_id, round + 1u, p.status);
         }
         const bool all = __all_sync(0xffffffffu, ok_lane);
         if (t == 0) {
           p.tp_rounds[cta_id] = round + 1u;
-          *s_last = all ? 1 : 0;
+          *s_last = (all && p.tp_mode == 0) ? 1 : 0;
         }
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");

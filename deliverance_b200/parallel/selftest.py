@@ -73,6 +73,33 @@ def main() -> int:
             good = err < 2e-2 and same and identical
             ok_all &= good
             report(check="fused_linear_all_reduce", N=N, K=Kfull, M=M, q4=q4, rel_err=err, repeatable=same, ranks_identical=identical, ok=good)
+            # split form: publish-only GEMM, then one row-wise kernel = wait + sum over ranks + residual add + RMSNorm
+            if M <= 64 and fused.reduce_mode != "epilogue":
+                res0 = (torch.randn(M, N, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+                nw = (1 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16).to(dev)
+                r_ref = res0.clone()
+                x_ref = ops.add_rmsnorm(ys[0], r_ref, nw, 1e-6, 0.0, 1.0)
+                outs = []
+                for _ in range(3):
+                    r = res0.clone()
+                    xn = fused.linear_reduce_norm(x, lw, r, nw, None, 1e-6, 0.0, 1.0)
+                    outs.append((xn, r))
+                torch.cuda.synchronize()
+                ops.check_status(local)
+                good = all(o[0] is not None for o in outs)
+                if good:
+                    e1 = ((outs[0][0].float() - x_ref.float()).norm() / x_ref.float().norm()).item()
+                    e2 = ((outs[0][1].float() - r_ref.float()).norm() / r_ref.float().norm()).item()
+                    same = all(torch.equal(outs[0][0], o[0]) and torch.equal(outs[0][1], o[1]) for o in outs[1:])
+                    gathered = [torch.empty_like(outs[0][0]) for _ in range(world)]
+                    dist.all_gather(gathered, outs[0][0])
+                    identical = all(torch.equal(gathered[0], t) for t in gathered)
+                    good = e1 < 1e-2 and e2 < 1e-2 and same and identical
+                    report(check="linear_reduce_norm", mode=fused.reduce_mode, N=N, K=Kfull, M=M, q4=q4, rel_err_x=e1, rel_err_residual=e2,
+                           repeatable=same, ranks_identical=identical, ok=good)
+                else:
+                    report(check="linear_reduce_norm", mode=fused.reduce_mode, N=N, K=Kfull, M=M, q4=q4, ok=False, reason="outside the fused path")
+                ok_all &= good
     # CUDA graph capture of two fused calls back to back (parity flips between them)
     x = (torch.randn(16, lw.K, device=dev) * 0.5).to(torch.bfloat16)
     ref = fused.linear_all_reduce(x, lw, "g").clone()
@@ -299,8 +326,39 @@ def main() -> int:
             hbm_us = N * Ks * 0.5625 / 6454.3e3
             nvl_us = (world - 1) * M * N * 2 / 770e3
             roof = max(hbm_us, nvl_us)
+            # the same projection followed by the residual add + norm of the layer: fused epilogue + norm kernel, split form, GEMM + NCCL + norm
+            resb = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+            nwb = torch.ones(N, dtype=torch.bfloat16, device=dev)
+            res2 = {}
+            for mode in ("epilogue+norm", "split", "gemm+nccl+norm"):
+                if mode == "split" and fused.reduce_mode == "epilogue":
+                    continue
+
+                def run2(i):
+                    if mode == "split":
+                        return fused.linear_reduce_norm(x, copies[i % 24], resb, nwb, None, 1e-6, 0.0, 0.0)
+                    if mode == "epilogue+norm":
+                        y = fused.linear_all_reduce(x, copies[i % 24], "b")
+                    else:
+                        y = ops.linear(x, copies[i % 24])
+                        dist.all_reduce(y)
+                    return ops.add_rmsnorm(y, resb, nwb, 1e-6, 0.0, 0.0)
+                for i in range(24):
+                    run2(i)
+                torch.cuda.synchronize()
+                dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(48):
+                    run2(i)
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) * 1e3 / 48], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                res2[mode] = t.item()
             report(check="bench_linear_all_reduce", world=world, M=M, N=N, K_per_rank=Ks, fused_us=res["fused"], gemm_nccl_us=res["gemm+nccl"],
-                   roofline_us=roof, fused_frac_of_roofline=roof / res["fused"], speedup_vs_nccl=res["gemm+nccl"] / res["fused"])
+                   roofline_us=roof, fused_frac_of_roofline=roof / res["fused"], speedup_vs_nccl=res["gemm+nccl"] / res["fused"],
+                   with_norm_us=res2, reduce_mode=fused.reduce_mode)
         # prefill-size: GEMM -> reduce-scatter -> all-gather against GEMM + NCCL all-reduce (needs DLV_TP_SCATTER=1)
         if fused.scatter is not None:
             Np, Kp = 4096, 14336 // (32 * world) * 32

@@ -342,3 +342,75 @@ def test_bounded_peer_wait_runs_out_and_context_survives():
     torch.cuda.synchronize()
     ops.check_status()
     assert _rel(y.float().cpu(), xx.float() @ wd.t()) < 2e-2
+
+
+@pytest.mark.parametrize("M,H,KV,D,hidden,inter,qk_norm,off,act", [
+    (1, 4, 2, 128, 512, 1024, True, 0.0, "silu"), (7, 4, 2, 128, 512, 1024, True, 0.0, "silu"),
+    (33, 8, 2, 64, 512, 768, False, 1.0, "gelu_pytorch_tanh"), (64, 16, 4, 64, 1024, 1536, False, 0.0, "silu"),
+    (64, 32, 8, 128, 2560, 9728, True, 0.0, "silu"), (8, 32, 8, 128, 2560, 9728, True, 0.0, "silu")])
+def test_decode_chain_matches_separate_kernels(M, H, KV, D, hidden, inter, qk_norm, off, act):
+    """One persistent launch (o_proj -> add + norm -> gate|up -> act * up -> down -> add + norm -> q|k|v -> norm / rotary / KV write)
+    against the same steps as separate kernels; every buffer the chain writes is compared, rows beyond M must stay untouched."""
+    e = ops.require_ext()
+    g = torch.Generator().manual_seed(M + hidden)
+    page, R = 32, 64
+    eps = 1e-6
+
+    def lin(N, K, seed, bias=False):
+        qt, _ = _q4_weight(N, K, seed=seed)
+        lw = LinearWeight(qt).to(DEV, torch.bfloat16)
+        lw.bias = (torch.randn(N, generator=g) * 0.1).to(DEV) if bias else None
+        return lw
+
+    w_o, w_gu, w_dn, w_qkv = lin(hidden, H * D, 1), lin(2 * inter, hidden, 2), lin(hidden, inter, 3), lin((H + 2 * KV) * D, hidden, 4, bias=not qk_norm)
+
+    def nw(n):
+        return (1 + 0.1 * torch.randn(n, generator=g)).to(torch.bfloat16).to(DEV)
+
+    n1, n2 = nw(hidden), nw(hidden)
+    qn, kn = (nw(D), nw(D)) if qk_norm else (None, None)
+    cos, sin = ref.rope_tables(D, 512, 10000.0, 1.0)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    attn = (torch.randn(R, H * D, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    res0 = (torch.randn(R, hidden, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    pos = torch.randint(0, 500, (M,), generator=g).to(torch.int32).to(DEV)
+    n_pages = 4
+    slots = torch.randperm(n_pages * page, generator=g)[:M].to(torch.int64).to(DEV)
+    caches = [torch.zeros(n_pages, KV, page, D, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    # ---- separate kernels ----
+    res_ref = res0[:M].clone()
+    x1 = ops.add_rmsnorm(ops.linear(attn[:M], w_o), res_ref, n1, eps, off, 1.0)
+    res_mid = res_ref.clone()
+    hh = ops.act_mul(ops.linear(x1, w_gu), act)
+    x2 = ops.add_rmsnorm(ops.linear(hh, w_dn), res_ref, n2, eps, off, 1.0)
+    q_ref = ops.rope_kv(ops.linear(x2, w_qkv), pos, slots, qn, kn, cos, sin, caches[0], caches[1], H, KV, D, eps, off).clone()
+    # ---- one launch ----
+    res = res0.clone()
+    bx1, bh, bx2, bq = (torch.full((R, n), 7.0, dtype=torch.bfloat16, device=DEV) for n in (hidden, inter, hidden, H * D))
+    poison = [torch.full((n,), float("nan"), device=DEV) for n in (1 << 22, 1 << 21, 1 << 20, 1 << 22)]
+    del poison  # the chain's workspaces come from the allocator's cache: a slot that is read but never written shows up as NaN
+    ch = e.DecodeChain()
+    ch.add_op(w_o.handle(), attn, 1, residual=res, norm_w=n1, out=bx1, eps=eps, offset=off)
+    ch.add_op(w_gu.handle(), bx1, 2, dep=True, scale_src=0, out=bh, act=act)
+    ch.add_op(w_dn.handle(), bh, 1, dep=True, residual=res, norm_w=n2, out=bx2, eps=eps, offset=off)
+    ch.add_op(w_qkv.handle(), bx2, 3, dep=True, scale_src=2, bias=w_qkv.bias, out=bq)
+    ch.set_qkv(qn, kn, cos, sin, caches[2], caches[3], H, KV, eps, off)
+    for rep in range(2):  # the second launch finds the counters the first one left (zero) and gives the same result
+        res.copy_(res0)
+        ch.run(M, pos, slots)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert ch.counters().abs().sum().item() == 0
+        # the norm stages hand on residual * weight; the row factor is applied behind the next projection
+        x1u = (res_mid.float() * (n1.float() + off)).to(torch.bfloat16)
+        x2u = (res_ref.float() * (n2.float() + off)).to(torch.bfloat16)
+        rels = {"x1": _rel(bx1[:M], x1u), "h": _rel(bh[:M], hh), "residual": _rel(res[:M], res_ref), "x2": _rel(bx2[:M], x2u),
+                "q": _rel(bq[:M], q_ref), "k_cache": _rel(caches[2], caches[0]), "v_cache": _rel(caches[3], caches[1])}
+        assert all(v < 2e-2 for v in rels.values()), rels
+        if M < R:
+            assert (bx1[M:] == 7.0).all() and (bh[M:] == 7.0).all() and (bq[M:] == 7.0).all() and torch.equal(res[M:], res0[M:])
+    first = bq[:M].clone()
+    res.copy_(res0)
+    ch.run(M, pos, slots)
+    torch.cuda.synchronize()
+    assert torch.equal(first, bq[:M])  # fixed summation order: bit-identical repeats
