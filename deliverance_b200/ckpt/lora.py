@@ -118,6 +118,14 @@ class MergingWeightLoader(WeightLoader):
 
 
 def apply_lora_delta(x: torch.Tensor, y: torch.Tensor, a: torch.Tensor, b_scaled: torch.Tensor) -> torch.Tensor:
-    """``y + (x @ A^T) @ (scale*B)^T`` — two skinny GEMMs and an add."""
+    """``y + (x @ A^T) @ (scale*B)^T``. On CUDA (bf16, rank <= 64) one kernel adds the delta into ``y`` in place
+    (csrc/aux.cu::lora_delta_kernel); elsewhere two skinny matrix products and an add."""
+    if (y.is_cuda and y.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and a.dtype == torch.bfloat16 and b_scaled.dtype == torch.bfloat16
+            and a.shape[0] <= 64 and x.dim() == 2 and y.dim() == 2 and x.stride(1) == 1 and y.stride(1) == 1 and x.shape[1] % 2 == 0 and x.stride(0) % 2 == 0):
+        from .. import ops
+
+        ops.require_ext().lora_delta(x, a.contiguous(), b_scaled.contiguous(), y)
+        ops._count()
+        return y
     t = x.to(a.dtype) @ a.t()
     return (y.to(a.dtype) + t @ b_scaled.t()).to(y.dtype)

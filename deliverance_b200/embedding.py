@@ -82,6 +82,11 @@ def recipe_from_model_root(model_dir: str) -> tuple[Optional[SentenceTransformer
     return mode, normalize
 
 
+_POOL_MODES = {PoolingType.AVG: 0, PoolingType.MAX: 1, PoolingType.SUM: 2, SentenceTransformersPooling.MEAN: 0, SentenceTransformersPooling.MAX: 1,
+               SentenceTransformersPooling.CLS: 3, SentenceTransformersPooling.LAST_TOKEN: 4, SentenceTransformersPooling.MEAN_SQRT_LEN: 5,
+               SentenceTransformersPooling.WEIGHTED_MEAN: 6}
+
+
 def pool_rows(h: torch.Tensor, pooling) -> torch.Tensor:
     if isinstance(pooling, SentenceTransformersPooling):
         return pooling.pool(h)
@@ -126,11 +131,19 @@ class EmbeddingModel:
     def embed_many(self, texts: list[str], pooling=PoolingType.AVG, normalize: Optional[bool] = None) -> torch.Tensor:
         toks = [self.encode_text(t) for t in texts]
         h, batch = self._hidden(toks)
-        hf = h.float()
         if pooling is PoolingType.MODEL:
             pooling = self.st_pooling or (SentenceTransformersPooling.CLS if isinstance(self.model, BertModel) else SentenceTransformersPooling.LAST_TOKEN)
             if normalize is None:
                 normalize = self.st_normalize
+        mode = _POOL_MODES.get(pooling)
+        if h.is_cuda and h.dtype == torch.bfloat16 and mode is not None:
+            # pooling and the L2 normalisation of every sequence in one kernel (csrc/aux.cu::pool_kernel)
+            from . import ops
+
+            lens = torch.tensor(list(batch.q_len_host), dtype=torch.int32, device=h.device)
+            ops._count()
+            return ops.require_ext().pool_rows(h.contiguous(), batch.q_start.to(torch.int32), lens, mode, bool(normalize))
+        hf = h.float()
         out = []
         for s, n in zip(batch.q_start.tolist(), batch.q_len_host):
             out.append(pool_rows(hf[s : s + n], pooling))
@@ -152,7 +165,11 @@ class ClassifierModel(EmbeddingModel):
         h, batch = self.model.encode([self.encode_text(text)])
         pooled = self.model.pooled_cls(h, batch)
         logits = ops.linear(pooled.contiguous(), self.model.classifier, out_f32=True)[0]
-        probs = torch.softmax(logits.float(), dim=-1).tolist()
+        if logits.is_cuda:
+            ops._count()
+            probs = ops.require_ext().softmax_rows(logits.float().unsqueeze(0).contiguous())[0].tolist()
+        else:
+            probs = torch.softmax(logits.float(), dim=-1).tolist()
         id2label = self.cfg.id2label or {v: k for k, v in self.cfg.label2id.items()}
         return {str(id2label.get(i, i)): p for i, p in enumerate(probs)}
 

@@ -140,19 +140,37 @@ class Sampler:
         amax = None
         if greedy_rows or any(s.params.xtc_threshold for s in states):
             amax, _ = ops.argmax(logits)
-        # XTC rows (rare): resolved one by one
+        # XTC rows: one kernel for all of them on CUDA (csrc/sampling.cu::xtc_kernel), row by row with torch statements on the CPU
         rest = []
+        xtc_rows = []
         for i, s in enumerate(states):
             if s.greedy:
                 continue
             top_k, top_p, utp, xtc, xtc_prob = s.effective()
             T = s.params.temperature
             if xtc is not None:
+                u = s.rng.random()
+                if logits.device.type == "cuda":
+                    xtc_rows.append((i, 1.0 if T == 0 else 1.0 / T, xtc, u <= xtc_prob, s.special_ids))
+                    continue
                 row = logits[i] if T == 0 else logits[i] / T
-                pick = xtc_pick(row, xtc, xtc_prob, s.rng.random(), s.special_ids)
+                pick = xtc_pick(row, xtc, xtc_prob, u, s.special_ids)
                 out[i] = pick if pick is not None else int(amax[i])
                 continue
             rest.append((i, T, candidate_limit(top_k, V), top_p if top_p is not None else 0.0, utp is not None, s.rng.random()))
+        if xtc_rows:
+            dev = logits.device
+            sub = logits.index_select(0, torch.tensor([r[0] for r in xtc_rows], device=dev))
+            special = sorted(set().union(*[r[4] for r in xtc_rows]))
+            picks = ops.require_ext().xtc_rows(
+                sub, torch.tensor([r[1] for r in xtc_rows], dtype=torch.float32, device=dev),
+                torch.tensor([r[2] for r in xtc_rows], dtype=torch.float32, device=dev),
+                torch.tensor([r[3] for r in xtc_rows], dtype=torch.uint8, device=dev),
+                torch.tensor(special or [-1], dtype=torch.int32, device=dev)).tolist()
+            ops._count()
+            am = amax.tolist()
+            for r, pk in zip(xtc_rows, picks):
+                out[r[0]] = int(pk) if pk >= 0 else int(am[r[0]])
         if rest and logits.device.type == "cuda":
             toks = self._sample_cuda(logits, rest)
             for r, t in zip(rest, toks):
@@ -177,7 +195,21 @@ class Sampler:
                 out[i] = int(am[i])
         lps: list[Optional[TokenLogProb]] = [None] * B
         want = [i for i, s in enumerate(states) if s.params.logprobs]
-        if want:
+        if want and logits.device.type == "cuda":
+            # one kernel: log-sum-exp, the chosen token's log-probability and the top-N per row (csrc/sampling.cu::logprob_kernel)
+            dev = logits.device
+            sub = logits.index_select(0, torch.tensor(want, device=dev)).float()
+            kmax = min(V, 64, max(states[i].params.top_logprobs for i in want))
+            clp, topi, topv = ops.require_ext().logprob_rows(sub, torch.tensor([out[i] for i in want], dtype=torch.int64, device=dev), kmax)
+            ops._count()
+            clp, topi, topv = clp.tolist(), topi.tolist(), topv.tolist()
+            for j, i in enumerate(want):
+                tl = TokenLogProb(out[i], self.decode_token(out[i]), float(clp[j]))
+                k = min(states[i].params.top_logprobs, kmax)
+                if k > 0:
+                    tl.top = [TokenLogProb(int(t), self.decode_token(int(t)), float(v)) for t, v in zip(topi[j][:k], topv[j][:k])]
+                lps[i] = tl
+        elif want:
             rows = torch.tensor(want, device=logits.device)
             sub = logits.index_select(0, rows).float()
             lse = torch.logsumexp(sub, dim=-1)

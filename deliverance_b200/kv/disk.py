@@ -28,7 +28,7 @@ def _pack(snap: dict) -> tuple[dict, dict]:
             if comp == "MSE_TURBOQUANT":
                 tensors[name + ".codes"], tensors[name + ".norms"] = v.codes, v.norms
                 layers[name] = {"shape": list(v.shape), "bits": v.bits}
-            elif comp == "LZ4":
+            elif comp in ("LZ4", "DEFLATE"):
                 raw, shape, dtype = v
                 tensors[name] = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
                 layers[name] = {"shape": list(shape), "dtype": str(dtype).replace("torch.", "")}
@@ -53,7 +53,7 @@ def _unpack(f: SafeTensorFile) -> dict:
             name = f"l{i}.{tag}"
             if comp == "MSE_TURBOQUANT":
                 pair.append(Encoded(f.tensor(name + ".codes").clone(), f.tensor(name + ".norms").clone(), tuple(info[name]["shape"]), info[name]["bits"]))
-            elif comp == "LZ4":
+            elif comp in ("LZ4", "DEFLATE"):
                 pair.append((f.tensor(name).numpy().tobytes(), tuple(info[name]["shape"]), getattr(torch, info[name]["dtype"])))
             else:
                 pair.append(f.tensor(name).clone())

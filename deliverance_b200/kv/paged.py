@@ -38,7 +38,7 @@ class KvCacheSettings:
     checkpoints: int = 4  # most checkpoints kept per prompt (START_AND_END, ANCHORS_AND_LARGEST)
     anchors: tuple = (32, 64, 128)
     enabled: bool = True
-    compression: str = "NONE"  # NONE | LZ4 | MSE_TURBOQUANT (host snapshots only, see kv.snapshot)
+    compression: str = "NONE"  # NONE | LZ4 | DEFLATE | MSE_TURBOQUANT (host snapshots only, see kv.turboquant)
 
     def checkpoint_lengths(self, n_tokens: int) -> list[int]:
         """Prefix lengths (multiples of the block size, at most ``max_prefix_tokens``) at which a prompt of ``n_tokens`` is

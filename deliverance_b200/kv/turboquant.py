@@ -16,6 +16,23 @@ from dataclasses import dataclass
 import torch
 
 
+def block_compress(raw: bytes, codec: str) -> bytes:
+    """``LZ4``: the LZ4 block format (the extension's host codec, csrc/lz4_block.cpp); ``DEFLATE``: zlib level 1."""
+    if codec == "DEFLATE":
+        return zlib.compress(raw, 1)
+    from ..ops import require_ext
+
+    return require_ext().lz4_compress(raw)
+
+
+def block_decompress(data: bytes, n_out: int, codec: str) -> bytes:
+    if codec == "DEFLATE":
+        return zlib.decompress(data)
+    from ..ops import require_ext
+
+    return require_ext().lz4_decompress(data, n_out)
+
+
 def _hadamard(x: torch.Tensor) -> torch.Tensor:
     """Unnormalised fast Walsh-Hadamard transform over the last dimension (a power of two)."""
     d = x.shape[-1]
@@ -64,7 +81,21 @@ class MseTurboQuantCodec:
         self.centroids = lloyd_max_gaussian(bits)
         self.edges = (self.centroids[1:] + self.centroids[:-1]) / 2
 
+    def _device_tables(self, device):
+        tables = self.__dict__.setdefault("_tables", {})
+        key = str(torch.device(device))
+        if key not in tables:
+            tables[key] = (self.signs.to(device), self.edges.to(device), self.centroids.to(device))
+        return tables[key]
+
     def encode(self, x: torch.Tensor) -> Encoded:
+        if x.is_cuda and 32 <= self.pdim <= 1024 and x.dtype in (torch.float32, torch.bfloat16):
+            # one kernel per tensor on the device that holds the pages (csrc/aux.cu::tq_encode_kernel); only codes and norms cross PCIe
+            from ..ops import require_ext
+
+            signs, edges, _ = self._device_tables(x.device)
+            codes, norms = require_ext().tq_encode(x.reshape(-1, self.dim).contiguous(), signs, edges, self.bits)
+            return Encoded(codes.reshape(-1).cpu(), norms.cpu(), tuple(x.shape), self.bits)
         rows = x.reshape(-1, self.dim).float().cpu()
         norms = rows.norm(dim=1)
         unit = rows / norms.clamp_min(1e-20).unsqueeze(1)
@@ -75,7 +106,14 @@ class MseTurboQuantCodec:
         codes = torch.bucketize(z, self.edges).to(torch.uint8)
         return Encoded(self._pack(codes), norms, tuple(x.shape), self.bits)
 
-    def decode(self, e: Encoded, dtype=torch.float32) -> torch.Tensor:
+    def decode(self, e: Encoded, dtype=torch.float32, device=None) -> torch.Tensor:
+        if device is not None and torch.device(device).type == "cuda" and 32 <= self.pdim <= 1024 and dtype in (torch.float32, torch.bfloat16):
+            from ..ops import require_ext
+
+            signs, _, centroids = self._device_tables(torch.device(device))
+            out = require_ext().tq_decode(e.codes.reshape(e.norms.numel(), -1).to(device), e.norms.to(device), signs, centroids, self.dim, self.bits,
+                                          dtype == torch.bfloat16)
+            return out.reshape(e.shape)
         rows = e.norms.numel()
         codes = self._unpack(e.codes, rows * self.pdim).reshape(rows, self.pdim).long()
         z = self.centroids[codes] / math.sqrt(self.pdim)
@@ -103,7 +141,7 @@ class MseTurboQuantCodec:
 
 
 def snapshot_pages(kv, pages: list[int], n_tokens: int, compression: str = "NONE", bits: int = 3) -> dict:
-    """Host copy of the K/V rows of ``pages`` for every attention layer (``NONE`` | ``LZ4`` (deflate here) | ``MSE_TURBOQUANT``)."""
+    """Host copy of the K/V rows of ``pages`` for every attention layer (``NONE`` | ``LZ4`` | ``DEFLATE`` | ``MSE_TURBOQUANT``)."""
     out = {"compression": compression, "n_tokens": n_tokens, "layers": {}}
     codec = None
     for i, k in enumerate(kv.k):
@@ -113,8 +151,8 @@ def snapshot_pages(kv, pages: list[int], n_tokens: int, compression: str = "NONE
         if compression == "MSE_TURBOQUANT":
             codec = codec or MseTurboQuantCodec(kk.shape[-1], bits)
             out["layers"][i] = (codec.encode(kk), codec.encode(vv))
-        elif compression == "LZ4":
-            raw = lambda t: (zlib.compress(t.cpu().contiguous().view(torch.uint8).numpy().tobytes(), 1), tuple(t.shape), t.dtype)  # noqa: E731
+        elif compression in ("LZ4", "DEFLATE"):
+            raw = lambda t: (block_compress(t.cpu().contiguous().view(torch.uint8).numpy().tobytes(), compression), tuple(t.shape), t.dtype)  # noqa: E731
             out["layers"][i] = (raw(kk), raw(vv))
         else:
             out["layers"][i] = (kk.cpu().clone(), vv.cpu().clone())
@@ -128,9 +166,13 @@ def restore_pages(kv, snap: dict, pages: list[int]) -> None:
     ps = kv.page_size
     for i, (ek, ev) in snap["layers"].items():
         if snap["compression"] == "MSE_TURBOQUANT":
-            kk, vv = snap["codec"].decode(ek), snap["codec"].decode(ev)
-        elif snap["compression"] == "LZ4":
-            un = lambda e: torch.frombuffer(bytearray(zlib.decompress(e[0])), dtype=torch.uint8).view(e[2]).reshape(e[1])  # noqa: E731
+            dt = kv.k[i].dtype if kv.k[i].dtype in (torch.float32, torch.bfloat16) else torch.float32
+            kk, vv = snap["codec"].decode(ek, dt, kv.device), snap["codec"].decode(ev, dt, kv.device)
+        elif snap["compression"] in ("LZ4", "DEFLATE"):
+            def un(e):
+                n_out = int(torch.tensor(e[1]).prod().item()) * torch.empty(0, dtype=e[2]).element_size()
+                return torch.frombuffer(bytearray(block_decompress(e[0], n_out, snap["compression"])), dtype=torch.uint8).view(e[2]).reshape(e[1])
+
             kk, vv = un(ek), un(ev)
         else:
             kk, vv = ek, ev

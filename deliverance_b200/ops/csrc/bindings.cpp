@@ -699,6 +699,41 @@ std::vector<Tensor> sample_rows(const Tensor& logits, const Tensor& inv_temp, co
   check_last_error("sample_rows");
   return {tok, ok};
 }
+// Exclude-top-choice picks of every row in one launch: int64 [B], -1 where XTC does not apply (not armed, or no token above the threshold).
+Tensor xtc_rows(const Tensor& logits, const Tensor& inv_temp, const Tensor& threshold, const Tensor& fire, const Tensor& special) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
+  const int B = static_cast<int>(logits.size(0)), V = static_cast<int>(logits.size(1));
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&inv_temp, &threshold, &fire}) {
+    check_cuda(*t, "xtc parameter");
+    TORCH_CHECK(t->numel() == B, "one xtc parameter per row");
+  }
+  check_cuda(special, "special ids");
+  TORCH_CHECK(inv_temp.scalar_type() == at::kFloat && threshold.scalar_type() == at::kFloat && fire.scalar_type() == at::kByte && special.scalar_type() == at::kInt,
+              "xtc parameter dtypes");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor tok = torch::empty({B}, logits.options().dtype(at::kLong));
+  dlv::launch_xtc(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, inv_temp.data_ptr<float>(), threshold.data_ptr<float>(),
+                  fire.data_ptr<uint8_t>(), special.data_ptr<int>(), static_cast<int>(special.numel()),
+                  reinterpret_cast<long long*>(tok.data_ptr<int64_t>()), cur_stream());
+  check_last_error("xtc_rows");
+  return tok;
+}
+// Log-probability of the chosen token of every row and the top_n most probable tokens: (chosen [B] f32, top ids [B, top_n] i64, top values [B, top_n] f32).
+std::vector<Tensor> logprob_rows(const Tensor& logits, const Tensor& chosen, int64_t top_n) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
+  const int B = static_cast<int>(logits.size(0)), V = static_cast<int>(logits.size(1));
+  check_cuda(chosen, "chosen");
+  TORCH_CHECK(chosen.scalar_type() == at::kLong && chosen.numel() == B && top_n >= 0 && top_n <= 64 && top_n <= V, "chosen must be int64 [B]; top_n in 0..64");
+  TORCH_CHECK(chosen.min().item<int64_t>() >= 0 && chosen.max().item<int64_t>() < V, "chosen token outside the vocabulary");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor lp = torch::empty({B}, logits.options());
+  Tensor idx = torch::empty({B, top_n}, logits.options().dtype(at::kLong));
+  Tensor val = torch::empty({B, top_n}, logits.options());
+  dlv::launch_logprobs(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, reinterpret_cast<const long long*>(chosen.data_ptr<int64_t>()),
+                       static_cast<int>(top_n), lp.data_ptr<float>(), reinterpret_cast<long long*>(idx.data_ptr<int64_t>()), val.data_ptr<float>(), cur_stream());
+  check_last_error("logprob_rows");
+  return {lp, idx, val};
+}
 void logits_post(Tensor& logits, c10::optional<Tensor> mask, double softcap, double inv_scale) {
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
   const int B = static_cast<int>(logits.size(0)), V = static_cast<int>(logits.size(1));
@@ -715,6 +750,91 @@ void logits_post(Tensor& logits, c10::optional<Tensor> mask, double softcap, dou
   dlv::launch_logits_post(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, mp, mld, static_cast<float>(softcap),
                           static_cast<float>(inv_scale), cur_stream());
   check_last_error("logits_post");
+}
+
+// ---- LoRA delta, pooling, classifier softmax, TurboQuant, LZ4 ------------------------------------------------------------------
+// y += (x @ A^T) @ Bs^T in place; x [M, K], A [r, K], Bs [N, r] (already scaled), y [M, N], all bf16, r <= 64.
+void lora_delta(const Tensor& x, const Tensor& A, const Tensor& Bs, Tensor& y) {
+  check_bf16(A, "A");
+  check_bf16(Bs, "B");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 2 == 0, "x must be bf16 [M, K]");
+  TORCH_CHECK(y.is_cuda() && y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1 && y.size(0) == x.size(0), "y must be bf16 [M, N]");
+  const int r = static_cast<int>(A.size(0));
+  TORCH_CHECK(A.dim() == 2 && A.size(1) == x.size(1) && Bs.dim() == 2 && Bs.size(0) == y.size(1) && Bs.size(1) == r && r >= 1 && r <= 64 && x.size(1) % 2 == 0,
+              "adapter shapes: A [r, K], B [N, r], r <= 64, K even");
+  c10::cuda::CUDAGuard guard(x.device());
+  dlv::launch_lora_delta(x.data_ptr(), static_cast<int>(x.stride(0)), A.data_ptr(), Bs.data_ptr(), y.data_ptr(), static_cast<int>(y.stride(0)),
+                         static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), static_cast<int>(y.size(1)), r, cur_stream());
+  check_last_error("lora_delta");
+}
+// Pools rows [start[s], start[s] + len[s]) of h [T, H] (bf16) into out [S, H] fp32. mode: 0 mean, 1 max, 2 sum, 3 first, 4 last,
+// 5 sum / sqrt(len), 6 position-weighted mean.
+Tensor pool_rows(const Tensor& h, const Tensor& start, const Tensor& len, int64_t mode, bool normalize) {
+  check_bf16(h, "h");
+  check_cuda(start, "start");
+  check_cuda(len, "len");
+  TORCH_CHECK(h.dim() == 2 && start.scalar_type() == at::kInt && len.scalar_type() == at::kInt && start.numel() == len.numel() && mode >= 0 && mode <= 6, "bad pooling arguments");
+  TORCH_CHECK((start + len).max().item<int>() <= h.size(0) && start.min().item<int>() >= 0 && len.min().item<int>() >= 0, "segments outside the hidden states");
+  c10::cuda::CUDAGuard guard(h.device());
+  Tensor out = torch::empty({start.numel(), h.size(1)}, h.options().dtype(at::kFloat));
+  dlv::launch_pool(h.data_ptr(), static_cast<int>(h.size(1)), start.data_ptr<int>(), len.data_ptr<int>(), static_cast<int>(start.numel()), static_cast<int>(mode),
+                   normalize ? 1 : 0, out.data_ptr<float>(), cur_stream());
+  check_last_error("pool_rows");
+  return out;
+}
+Tensor softmax_rows(const Tensor& x) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.scalar_type() == at::kFloat && x.dim() == 2, "x must be fp32 [rows, C]");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  dlv::launch_softmax_rows(x.data_ptr<float>(), y.data_ptr<float>(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), cur_stream());
+  check_last_error("softmax_rows");
+  return y;
+}
+// TurboQuant rows: x [rows, dim] (fp32 / bf16) -> (packed codes uint8 [rows, pdim * bits / 8], norms fp32 [rows])
+std::vector<Tensor> tq_encode(const Tensor& x, const Tensor& signs, const Tensor& edges, int64_t bits) {
+  check_cuda(x, "x");
+  check_cuda(signs, "signs");
+  check_cuda(edges, "edges");
+  TORCH_CHECK(x.dim() == 2 && (x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16), "x must be fp32 / bf16 [rows, dim]");
+  const int dim = static_cast<int>(x.size(1)), pdim = static_cast<int>(signs.numel());
+  TORCH_CHECK(pdim >= 32 && pdim <= 1024 && (pdim & (pdim - 1)) == 0 && dim <= pdim && bits >= 1 && bits <= 8, "pdim must be a power of two in 32..1024");
+  TORCH_CHECK(signs.scalar_type() == at::kFloat && edges.scalar_type() == at::kFloat && edges.numel() == (1 << bits) - 1, "signs [pdim] / edges [2^bits - 1] fp32");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor codes = torch::empty({x.size(0), pdim * bits / 8}, x.options().dtype(at::kByte));
+  Tensor norms = torch::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  dlv::launch_tq_encode(x.data_ptr(), x.scalar_type() == at::kFloat ? 0 : 1, x.size(0), dim, pdim, static_cast<int>(bits), signs.data_ptr<float>(),
+                        edges.data_ptr<float>(), codes.data_ptr<uint8_t>(), norms.data_ptr<float>(), cur_stream());
+  check_last_error("tq_encode");
+  return {codes, norms};
+}
+Tensor tq_decode(const Tensor& codes, const Tensor& norms, const Tensor& signs, const Tensor& centroids, int64_t dim, int64_t bits, bool to_bf16) {
+  check_cuda(codes, "codes");
+  check_cuda(norms, "norms");
+  check_cuda(signs, "signs");
+  check_cuda(centroids, "centroids");
+  const int pdim = static_cast<int>(signs.numel());
+  TORCH_CHECK(codes.scalar_type() == at::kByte && codes.dim() == 2 && codes.size(1) == pdim * bits / 8 && norms.scalar_type() == at::kFloat && norms.numel() == codes.size(0),
+              "codes [rows, pdim * bits / 8] uint8, norms [rows] fp32");
+  TORCH_CHECK(pdim >= 32 && pdim <= 1024 && (pdim & (pdim - 1)) == 0 && dim <= pdim && bits >= 1 && bits <= 8 && centroids.numel() == (1 << bits) &&
+                  centroids.scalar_type() == at::kFloat && signs.scalar_type() == at::kFloat, "bad codec tables");
+  c10::cuda::CUDAGuard guard(codes.device());
+  Tensor out = torch::empty({codes.size(0), dim}, codes.options().dtype(to_bf16 ? at::kBFloat16 : at::kFloat));
+  dlv::launch_tq_decode(codes.data_ptr<uint8_t>(), norms.data_ptr<float>(), codes.size(0), static_cast<int>(dim), pdim, static_cast<int>(bits), signs.data_ptr<float>(),
+                        centroids.data_ptr<float>(), out.data_ptr(), to_bf16 ? 1 : 0, cur_stream());
+  check_last_error("tq_decode");
+  return out;
+}
+py::bytes lz4_compress_bytes(const std::string& raw) {
+  std::string out(dlv::lz4_compress_bound(raw.size()), '\0');
+  const size_t n = dlv::lz4_compress(reinterpret_cast<const uint8_t*>(raw.data()), raw.size(), reinterpret_cast<uint8_t*>(&out[0]), out.size());
+  return py::bytes(out.data(), n);
+}
+py::bytes lz4_decompress_bytes(const std::string& comp, int64_t n_out) {
+  TORCH_CHECK(n_out >= 0, "bad decoded size");
+  std::string out(static_cast<size_t>(n_out), '\0');
+  dlv::lz4_decompress(reinterpret_cast<const uint8_t*>(comp.data()), comp.size(), reinterpret_cast<uint8_t*>(&out[0]), out.size());
+  return py::bytes(out);
 }
 
 // ---- MoE --------------------------------------------------------------------------------------------------------------
@@ -1131,6 +1251,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("prefill_attention", &prefill_attention);
   m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("sample_rows", &sample_rows);
+  m.def("xtc_rows", &xtc_rows);
+  m.def("lora_delta", &lora_delta);
+  m.def("pool_rows", &pool_rows);
+  m.def("softmax_rows", &softmax_rows);
+  m.def("tq_encode", &tq_encode);
+  m.def("tq_decode", &tq_decode, py::arg("codes"), py::arg("norms"), py::arg("signs"), py::arg("centroids"), py::arg("dim"), py::arg("bits"), py::arg("to_bf16") = false);
+  m.def("lz4_compress", &lz4_compress_bytes);
+  m.def("lz4_decompress", &lz4_decompress_bytes);
+  m.def("logprob_rows", &logprob_rows);
   m.def("logits_post", &logits_post, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("moe_route", &moe_route);
   m.def("moe_items", &moe_items);

@@ -142,6 +142,12 @@ void launch_logits_post(float* logits, int ld, int B, int V, const uint32_t* mas
 void launch_sample(const float* logits, int ld, int B, int V, const float* inv_temp, const long long* limits, const float* top_p,
                    const unsigned char* uniform, const float* us, long long* out_tok, int* out_ok, cudaStream_t st);
 
+// exclude-top-choice pick per row (-1: XTC does not apply) and log-probabilities (chosen token + top_n) per row; see sampling.cu
+void launch_xtc(const float* logits, int ld, int B, int V, const float* inv_temp, const float* threshold, const unsigned char* fire,
+                const int* special, int n_special, long long* out_tok, cudaStream_t st);
+void launch_logprobs(const float* logits, int ld, int B, int V, const long long* chosen, int top_n, float* out_chosen, long long* out_idx,
+                     float* out_val, cudaStream_t st);
+
 // moe.cu
 void launch_moe_route(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
                       int* perm, int* pos, cudaStream_t st);
@@ -179,6 +185,19 @@ int launch_mamba2(const void* zx, int ld, int T, int num_seqs, int I, int conv_d
                   const int* q_len, const int* positions, int n_chunks, const int* chunk_seq, const int* chunk_row0, const int* chunk_len,
                   const int* chunk_first, const int* chunk_last, const int* seq_chunk0, const int* seq_nchunks, int multi_chunk,
                   float* xbc, float* ybuf, float* chunk_state, float* chunk_decay, void* out, cudaStream_t st);
+
+// aux.cu
+void launch_lora_delta(const void* x, int ldx, const void* A, const void* Bs, void* y, int ldy, int M, int K, int N, int r, cudaStream_t st);
+void launch_pool(const void* h, int H, const int* start, const int* len, int S, int mode, int normalize, float* out, cudaStream_t st);
+void launch_softmax_rows(const float* x, float* y, int rows, int C, cudaStream_t st);
+void launch_tq_encode(const void* x, int src_dtype, long long rows, int dim, int pdim, int bits, const float* signs, const float* edges, uint8_t* codes,
+                      float* norms, cudaStream_t st);
+void launch_tq_decode(const uint8_t* codes, const float* norms, long long rows, int dim, int pdim, int bits, const float* signs, const float* centroids,
+                      void* out, int dst_dtype, cudaStream_t st);
+// lz4_block.cpp (host)
+size_t lz4_compress_bound(size_t n);
+size_t lz4_compress(const uint8_t* src, size_t n, uint8_t* dst, size_t cap);
+size_t lz4_decompress(const uint8_t* src, size_t n, uint8_t* dst, size_t n_out);
 
 // quant.cu
 void launch_q4_quantize(const void* w, int src_dtype, long long n_blocks, uint8_t* packed, float* scales, cudaStream_t st);

@@ -462,14 +462,180 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
   }
 }
 
+// ------------------------------------------------------------------------------------------------ exclude-top-choice (XTC)
+// One CTA per row. probs = softmax(logits * inv_temp). When `fire[b]` is set and at least one token has a probability above
+// `threshold[b]`: the most probable token if it is a special token, otherwise the LEAST probable token above the threshold (first
+// index on ties); -1 when XTC does not apply to the row (the caller then samples normally). Reference:
+// core/.../model/ExcludeTopChoicePicker.java:42-86.
+__global__ void __launch_bounds__(1024) xtc_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ inv_temp,
+                                                   const float* __restrict__ threshold, const unsigned char* __restrict__ fire,
+                                                   const int* __restrict__ special, int n_special, long long* __restrict__ out_tok) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float red_f[32];
+  __shared__ int red_i[32];
+  __shared__ float s_val;
+  __shared__ int s_idx;
+  const int b = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (!fire[b]) {
+    if (threadIdx.x == 0) out_tok[b] = -1;
+    return;
+  }
+  const float* row = logits + static_cast<size_t>(b) * ld;
+  const float it = inv_temp[b];
+  // block-wide (value, first index) reduction; want_max: largest value, else smallest
+  auto reduce = [&](float v, int i, bool want_max) {
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+      const bool take = want_max ? (ov > v || (ov == v && oi < i)) : (ov < v || (ov == v && oi < i));
+      if (take) { v = ov; i = oi; }
+    }
+    __syncthreads();
+    if (lane == 0) { red_f[warp] = v; red_i[warp] = i; }
+    __syncthreads();
+    if (warp == 0) {
+      v = red_f[lane];
+      i = red_i[lane];
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        const bool take = want_max ? (ov > v || (ov == v && oi < i)) : (ov < v || (ov == v && oi < i));
+        if (take) { v = ov; i = oi; }
+      }
+      if (lane == 0) { s_val = v; s_idx = i; }
+    }
+    __syncthreads();
+  };
+  float mx = -INFINITY;
+  int mi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i] * it;
+    if (v > mx) { mx = v; mi = i; }
+  }
+  reduce(mx, mi, true);
+  const float gmx = s_val;
+  const int top = s_idx;
+  if (gmx == -INFINITY) {
+    if (threadIdx.x == 0) out_tok[b] = -1;
+    return;
+  }
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) sum += __expf(row[i] * it - gmx);
+  sum = warp_sum(sum);
+  __syncthreads();
+  if (lane == 0) red_f[warp] = sum;
+  __syncthreads();
+  sum = 0.f;
+  for (int w = 0; w < 32; ++w) sum += red_f[w];
+  const float thr = threshold[b];
+  // least probable token whose probability exceeds the threshold
+  float lo = INFINITY;
+  int li = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float pr = __expf(row[i] * it - gmx) / sum;
+    if (pr > thr && pr < lo) { lo = pr; li = i; }
+  }
+  reduce(lo, li, false);
+  if (threadIdx.x == 0) {
+    long long r = -1;
+    if (s_val != INFINITY) {
+      r = s_idx;
+      for (int j = 0; j < n_special; ++j)
+        if (special[j] == top) r = top;
+    }
+    out_tok[b] = r;
+  }
+}
+
+void launch_xtc(const float* logits, int ld, int B, int V, const float* inv_temp, const float* threshold, const unsigned char* fire,
+                const int* special, int n_special, long long* out_tok, cudaStream_t st) {
+  if (B == 0) return;
+  launch_pdl(xtc_kernel, dim3(B), dim3(1024), 0, st, logits, ld, V, inv_temp, threshold, fire, special, n_special, out_tok);
+}
+
+// ------------------------------------------------------------------------------------------------ log-probabilities
+// One CTA per row: log-sum-exp of the row, the log-probability of the chosen token and the `top_n` most probable tokens (value
+// descending, first index on ties) with their log-probabilities. Reference: core/.../model/AbstractGeneratorSampler.java:135-155,
+// tensor/.../VectorTensorMathUtils.java:91-107.
+__global__ void __launch_bounds__(1024) logprob_kernel(const float* __restrict__ logits, int ld, int V, const long long* __restrict__ chosen,
+                                                       int top_n, float* __restrict__ out_chosen, long long* __restrict__ out_idx,
+                                                       float* __restrict__ out_val) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float red_f[32];
+  __shared__ int red_i[32];
+  __shared__ float s_val;
+  __shared__ int s_idx;
+  const int b = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* row = logits + static_cast<size_t>(b) * ld;
+  float prev_v = INFINITY;
+  int prev_i = -1;
+  float lse = 0.f;
+  for (int r = 0; r < (top_n < 1 ? 1 : top_n); ++r) {
+    // the largest (value, -index) strictly behind the previous pick
+    float v = -INFINITY;
+    int vi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float x = row[i];
+      const bool behind = x < prev_v || (x == prev_v && i > prev_i);
+      if (behind && (x > v || (x == v && i < vi))) { v = x; vi = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, vi, o);
+      if (ov > v || (ov == v && oi < vi)) { v = ov; vi = oi; }
+    }
+    __syncthreads();
+    if (lane == 0) { red_f[warp] = v; red_i[warp] = vi; }
+    __syncthreads();
+    if (warp == 0) {
+      v = red_f[lane];
+      vi = red_i[lane];
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, vi, o);
+        if (ov > v || (ov == v && oi < vi)) { v = ov; vi = oi; }
+      }
+      if (lane == 0) { s_val = v; s_idx = vi; }
+    }
+    __syncthreads();
+    prev_v = s_val;
+    prev_i = s_idx;
+    if (r == 0) {
+      const float mx = prev_v;
+      float sum = 0.f;
+      if (mx != -INFINITY)
+        for (int i = threadIdx.x; i < V; i += blockDim.x) sum += __expf(row[i] - mx);
+      sum = warp_sum(sum);
+      __syncthreads();
+      if (lane == 0) red_f[warp] = sum;
+      __syncthreads();
+      sum = 0.f;
+      for (int w = 0; w < 32; ++w) sum += red_f[w];
+      lse = mx + logf(sum);
+      if (threadIdx.x == 0) out_chosen[b] = row[chosen[b]] - lse;
+    }
+    if (top_n > 0 && threadIdx.x == 0) {
+      out_idx[static_cast<size_t>(b) * top_n + r] = prev_i == 0x7fffffff ? -1 : prev_i;
+      out_val[static_cast<size_t>(b) * top_n + r] = prev_v - lse;
+    }
+  }
+}
+
+void launch_logprobs(const float* logits, int ld, int B, int V, const long long* chosen, int top_n, float* out_chosen, long long* out_idx,
+                     float* out_val, cudaStream_t st) {
+  if (B == 0) return;
+  launch_pdl(logprob_kernel, dim3(B), dim3(1024), 0, st, logits, ld, V, chosen, top_n, out_chosen, out_idx, out_val);
+}
+
 void launch_sample(const float* logits, int ld, int B, int V, const float* inv_temp, const long long* limits, const float* top_p,
                    const unsigned char* uniform, const float* us, long long* out_tok, int* out_ok, cudaStream_t st) {
   if (B == 0) return;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(SampShared)));
-    attr_done = true;
-  }
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(SampShared)));
   launch_pdl(sample_kernel, dim3(B), dim3(1024), sizeof(SampShared), st, logits, ld, V, inv_temp, limits, top_p, uniform, us, out_tok, out_ok);
 }
 

@@ -414,3 +414,87 @@ def test_decode_chain_matches_separate_kernels(M, H, KV, D, hidden, inter, qk_no
     ch.run(M, pos, slots)
     torch.cuda.synchronize()
     assert torch.equal(first, bq[:M])  # fixed summation order: bit-identical repeats
+
+
+def test_xtc_and_logprob_kernels_match_torch():
+    """xtc_rows against the row-by-row torch statement of exclude-top-choice, logprob_rows against logsumexp / topk."""
+    from deliverance_b200.engine.sampler import xtc_pick
+
+    e = ops.require_ext()
+    g = torch.Generator().manual_seed(5)
+    B, V = 9, 5000
+    logits = torch.randn(B, V, generator=g) * 3
+    logits[2, 77] = 30.0  # one dominant token: nothing else is above the threshold
+    logits[4, :] = float("-inf")
+    logits[4, 10:14] = torch.tensor([1.0, 1.0, 0.5, 2.0])  # ties above the threshold: the first index wins
+    temps = [1.0, 0.7, 1.0, 1.3, 1.0, 1.0, 0.5, 1.0, 1.0]
+    thr = [0.001, 0.01, 0.1, 0.0005, 0.1, 0.002, 0.01, 0.5, 0.001]
+    fire = [1, 1, 1, 1, 1, 0, 1, 1, 1]
+    special = [int(torch.argmax(logits[8]))]  # row 8: the top token is special and is returned as is
+    got = e.xtc_rows(logits.to(DEV), torch.tensor([1 / t for t in temps], device=DEV), torch.tensor(thr, device=DEV),
+                     torch.tensor(fire, dtype=torch.uint8, device=DEV), torch.tensor(special, dtype=torch.int32, device=DEV)).cpu().tolist()
+    for b in range(B):
+        want = xtc_pick(logits[b] / temps[b], thr[b], 1.0 if fire[b] else 0.0, 0.5, frozenset(special))
+        assert got[b] == (-1 if want is None else want), (b, got[b], want)
+    assert got[8] == special[0] and got[5] == -1 and got[4] == 12
+    # log-probabilities
+    lg = logits.clone()
+    lg[4, :] = torch.randn(V, generator=g)
+    chosen = torch.randint(0, V, (B,), generator=g)
+    lp, ti, tv = e.logprob_rows(lg.to(DEV), chosen.to(DEV), 5)
+    lse = torch.logsumexp(lg, dim=-1)
+    assert torch.allclose(lp.cpu(), lg.gather(1, chosen.unsqueeze(1)).squeeze(1) - lse, atol=1e-4)
+    wv, wi = torch.topk(lg, 5, dim=-1)
+    assert torch.equal(ti.cpu(), wi) and torch.allclose(tv.cpu(), wv - lse.unsqueeze(1), atol=1e-4)
+    lp0, ti0, _ = e.logprob_rows(lg.to(DEV), chosen.to(DEV), 0)
+    assert torch.allclose(lp0.cpu(), lp.cpu()) and ti0.shape == (B, 0)
+
+
+def test_lora_pool_softmax_turboquant_kernels():
+    """The small device kernels off the hot path against their PyTorch statements."""
+    from deliverance_b200.embedding import SentenceTransformersPooling as P
+    from deliverance_b200.kv.turboquant import MseTurboQuantCodec
+
+    e = ops.require_ext()
+    g = torch.Generator().manual_seed(11)
+    # LoRA delta
+    M, K, N, r = 37, 512, 768, 16
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    A = (torch.randn(r, K, generator=g) * 0.1).to(torch.bfloat16)
+    B = (torch.randn(N, r, generator=g) * 0.1).to(torch.bfloat16)
+    y0 = (torch.randn(M, N, generator=g)).to(torch.bfloat16)
+    y = y0.clone().to(DEV)
+    e.lora_delta(x.to(DEV), A.to(DEV), B.to(DEV), y)
+    want = y0.float() + (x.float() @ A.float().t()) @ B.float().t()
+    assert _rel(y.cpu(), want) < 1e-2
+    # pooling
+    H = 384
+    lens = [5, 1, 40, 17]
+    starts = [0, 5, 6, 46]
+    h = (torch.randn(sum(lens), H, generator=g)).to(torch.bfloat16)
+    modes = {0: P.MEAN, 1: P.MAX, 3: P.CLS, 4: P.LAST_TOKEN, 5: P.MEAN_SQRT_LEN, 6: P.WEIGHTED_MEAN}
+    for mode, pool in modes.items():
+        for norm in (False, True):
+            got = e.pool_rows(h.to(DEV), torch.tensor(starts, dtype=torch.int32, device=DEV), torch.tensor(lens, dtype=torch.int32, device=DEV), mode, norm).cpu()
+            for s, (a, n) in enumerate(zip(starts, lens)):
+                w = pool.pool(h[a:a + n].float())
+                if norm:
+                    w = w / w.norm().clamp_min(1e-12)
+                assert torch.allclose(got[s], w, atol=2e-3, rtol=1e-3), (mode, norm, s)
+    got = e.pool_rows(h.to(DEV), torch.tensor(starts, dtype=torch.int32, device=DEV), torch.tensor(lens, dtype=torch.int32, device=DEV), 2, False).cpu()
+    assert torch.allclose(got[2], h[6:46].float().sum(0), atol=1e-2)
+    # softmax
+    lg = torch.randn(3, 7, generator=g) * 4
+    assert torch.allclose(e.softmax_rows(lg.to(DEV)).cpu(), torch.softmax(lg, -1), atol=1e-6)
+    # TurboQuant: device codes against the host codec (a coordinate on a bucket edge may differ by the summation order)
+    for dim, bits in ((128, 3), (64, 4), (96, 2), (256, 8)):
+        codec = MseTurboQuantCodec(dim, bits)
+        rows = (torch.randn(50, dim, generator=g) * 2).to(torch.bfloat16)
+        host = codec.encode(rows.float())
+        dev_enc = codec.encode(rows.to(DEV))
+        assert dev_enc.codes.shape == host.codes.shape and torch.allclose(dev_enc.norms, host.norms, rtol=1e-4)
+        assert (dev_enc.codes != host.codes).float().mean().item() < 0.01
+        back_host = codec.decode(host)
+        back_dev = codec.decode(host, torch.float32, DEV).cpu()
+        assert torch.allclose(back_dev, back_host, atol=1e-3, rtol=1e-3)
+        assert _rel(codec.decode(dev_enc, torch.bfloat16, DEV).cpu(), rows) < (0.6 if bits <= 2 else 0.25)

@@ -860,3 +860,27 @@ def test_prefill_roofline_counts_every_matrix_and_half_the_attention():
     assert tp8.nvlink_bytes > 0 and abs(tp8.flops * 8 / prefill_cost(cfg, 64, 2048).flops - 1) < 0.02
     r = prefill_report(cfg, 64, 2048, "jq4", 1, measured_ms=1562.0)
     assert r["bound"] == "tensor" and 0.3 < r["fraction"] < 0.7
+
+
+def test_lz4_block_format_golden_and_roundtrip():
+    """The host LZ4 codec of the extension: hand-assembled blocks of the public block format decode to the expected bytes, and
+    random / repetitive / empty inputs survive a round trip."""
+    import os
+    import random
+
+    from deliverance_b200.ops.build import load_extension
+
+    e = load_extension()
+    if e is None:
+        pytest.skip("extension not built")
+    assert e.lz4_decompress(bytes([0x50]) + b"hello", 5) == b"hello"
+    # 3 literals "abc", match offset 3 length 9 (overlapping copy), then a last sequence of one literal
+    assert e.lz4_decompress(bytes([0x35]) + b"abc" + bytes([3, 0]) + bytes([0x10]) + b"d", 13) == b"abcabcabcabcd"
+    with pytest.raises(RuntimeError):
+        e.lz4_decompress(bytes([0x35]) + b"abc" + bytes([9, 0]), 12)  # offset reaches before the output start
+    rnd = random.Random(3)
+    for data in (b"", b"x", bytes(70000), os.urandom(3000), b"the quick brown fox " * 500 + os.urandom(17),
+                 bytes(rnd.choice(b"abcd") for _ in range(30000))):
+        c = e.lz4_compress(data)
+        assert e.lz4_decompress(c, len(data)) == data
+    assert len(e.lz4_compress(bytes(70000))) < 400
