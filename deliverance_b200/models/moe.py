@@ -45,6 +45,42 @@ def moe_forward(model, i: int, lw, x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def moe_forward_sharded(model, i: int, lw, x_own: torch.Tensor, a2a, total_rows: int) -> torch.Tensor:
+    """Routed experts for token rows that are sharded over the ranks (sequence-parallel forward) with expert parallelism: every rank
+    routes its own rows, an all-to-all over peer memory carries each (token, slot) row to the rank that owns its expert, the grouped
+    expert GEMMs run there, the outputs travel back and are combined with the route weights (``parallel.fused.ExpertAllToAll``).
+    ``total_rows``: token rows of the whole batch (bounds what one rank can receive)."""
+    cfg = model.cfg
+    E, k = cfg.num_experts, cfg.experts_per_token
+    e = ops.require_ext()
+    ne = lw.n_local_experts
+    renorm = True if cfg.model_type == "mixtral" else (cfg.norm_topk_prob if cfg.router_mode == "softmax_topk" else False)
+    T = x_own.shape[0]
+    logits = ops.linear(x_own, lw.router, out_f32=True) if T else torch.zeros(0, E, device=x_own.device)
+    w, idx, counts, offsets, perm, pos = e.moe_route(logits.contiguous(), k, 0 if cfg.router_mode == "softmax_topk" else 1, bool(renorm))
+    ops._count(2)
+    max_recv = min(total_rows * k, a2a.cap * model.tp.size)
+    bn = ops.moe_token_tile(max(1, total_rows * k // model.tp.size), ne)
+    max_items = max(1, (max_recv + bn - 1) // bn + ne)
+    gu_w, down_w = lw.experts_gate_up_grouped, lw.experts_down_grouped
+
+    def run_experts(xs, local_offsets):
+        items = e.moe_items(local_offsets, 0, ne, bn, max_items)
+        ops._count()
+        if lw.fused_act_experts and bn >= 16:
+            hmid = gu_w.run_act(xs, items, bn, 1, cfg.hidden_act)
+        else:
+            hmid = ops.act_mul(gu_w.run(xs, items, bn, 1), cfg.hidden_act)
+        return down_w.run(hmid, items, bn, 1)
+
+    ret = a2a.forward(x_own, perm, offsets, k, run_experts, max_recv)
+    a2a.sent_rows += int(T * k)
+    if T == 0:
+        return x_own
+    ops._count()
+    return e.moe_combine(ret[: T * k], pos, w, T, k)
+
+
 def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
     e = ops.require_ext()
     st = model._stage

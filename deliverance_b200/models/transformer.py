@@ -394,8 +394,15 @@ class DecoderModel:
         M = int(batch.token_ids.shape[0])
         if M < self.sp_min_rows or self.cfg.model_type == "granitemoehybrid":
             return None
-        if any(lw.kind == "mamba" or lw.router is not None or lw.lora or lw.fused_act for lw in self.layers):
+        if any(lw.kind == "mamba" or lw.lora or lw.fused_act for lw in self.layers):
             return None
+        if any(lw.router is not None for lw in self.layers):
+            # mixture-of-experts layers run sequence parallel only with expert parallelism over peer memory (token rows travel to the
+            # experts' owners and back: parallel/fused.py::ExpertAllToAll)
+            ne = next(lw.n_local_experts for lw in self.layers if lw.router is not None)
+            if (self.tp.fused is None or batch.token_ids.device.type != "cuda" or not ne or ne == self.cfg.num_experts or ne > 128
+                    or self.cfg.model_type == "granitemoehybrid" or torch.cuda.is_current_stream_capturing()):
+                return None
         from ..parallel.fused import row_cut
 
         rpr, first, count = row_cut(M, self.tp.size, self.tp.rank)
@@ -447,7 +454,14 @@ class DecoderModel:
         """Feed-forward block output; ``norm_after`` as in :meth:`attention` (dense blocks only)."""
         cfg = self.cfg
         if lw.router is not None and cfg.model_type != "granitemoehybrid":
-            y = self.moe(i, lw, x)
+            if self._sp is not None:
+                from .moe import moe_forward_sharded
+
+                with self._stage("moe.forward"):
+                    a2a = self.tp.fused.expert_a2a(lw.n_local_experts, cfg.hidden_size, cfg.experts_per_token)
+                    y = moe_forward_sharded(self, i, lw, x, a2a, self._sp[0])
+            else:
+                y = self.moe(i, lw, x)
             return (y, False) if norm_after is not None else y
         if cfg.model_type == "granitemoehybrid":
             with self._stage("mlpblock.shared"):

@@ -752,6 +752,76 @@ void logits_post(Tensor& logits, c10::optional<Tensor> mask, double softcap, dou
   check_last_error("logits_post");
 }
 
+// ---- expert-parallel all-to-all -----------------------------------------------------------------------------------------
+class ExpertA2A {
+ public:
+  // recv / meta / flag / ret pointers: device addresses of every rank's areas as mapped in this process
+  ExpertA2A(int64_t rank, int64_t size, int64_t ne, int64_t cap, int64_t H, std::vector<int64_t> recv, std::vector<int64_t> meta, std::vector<int64_t> flags,
+            std::vector<int64_t> ret) : H_(static_cast<int>(H)) {
+    TORCH_CHECK(size >= 2 && size <= 8 && rank >= 0 && rank < size && ne >= 1 && ne <= 128 && cap >= 1 && H % 8 == 0, "bad all-to-all geometry");
+    TORCH_CHECK(static_cast<int64_t>(recv.size()) == size && static_cast<int64_t>(meta.size()) == size && static_cast<int64_t>(flags.size()) == size &&
+                    static_cast<int64_t>(ret.size()) == size, "one pointer per rank");
+    p_ = {};
+    p_.size = static_cast<int>(size);
+    p_.rank = static_cast<int>(rank);
+    p_.ne = static_cast<int>(ne);
+    p_.cap = static_cast<int>(cap);
+    for (int r = 0; r < size; ++r) {
+      p_.recv[r] = static_cast<unsigned long long>(recv[r]);
+      p_.meta[r] = static_cast<unsigned long long>(meta[r]);
+      p_.flags[r] = static_cast<unsigned long long>(flags[r]);
+      p_.ret[r] = static_cast<unsigned long long>(ret[r]);
+      TORCH_CHECK((p_.recv[r] & 15) == 0 && (p_.ret[r] & 15) == 0 && (p_.meta[r] & 3) == 0 && (p_.flags[r] & 3) == 0 && p_.recv[r] && p_.ret[r] && p_.meta[r] && p_.flags[r],
+                  "bad peer pointer");
+    }
+  }
+  // x [T, H] own token rows; perm / offsets from moe_route over the own tokens (offsets over ALL experts). Pushes the rows and publishes.
+  void dispatch(const Tensor& x, const Tensor& perm, const Tensor& offsets, int64_t k) {
+    check_bf16(x, "x");
+    check_cuda(perm, "perm");
+    check_cuda(offsets, "offsets");
+    TORCH_CHECK(x.dim() == 2 && x.size(1) == H_ && perm.scalar_type() == at::kInt && offsets.scalar_type() == at::kInt && perm.numel() == x.size(0) * k &&
+                    offsets.numel() == static_cast<int64_t>(p_.size) * p_.ne + 1 && perm.numel() <= p_.cap, "dispatch arguments");
+    c10::cuda::CUDAGuard guard(x.device());
+    dlv::A2AParams p = with_status(x.device().index());
+    ++epoch_;
+    dlv::launch_a2a_dispatch(&p, x.data_ptr(), perm.data_ptr<int>(), offsets.data_ptr<int>(), static_cast<int>(perm.numel()), static_cast<int>(k), H_, epoch_, cur_stream());
+    check_last_error("a2a dispatch");
+  }
+  // Waits for all sources, returns (xs [max_rows, H] rows grouped by local expert, local_offsets [ne + 1], seg [ne * size, 4]).
+  std::vector<Tensor> receive(int64_t max_rows, const Tensor& like) {
+    c10::cuda::CUDAGuard guard(like.device());
+    auto io = torch::TensorOptions().device(like.device()).dtype(torch::kInt32);
+    Tensor local_offsets = torch::zeros({p_.ne + 1}, io), seg = torch::zeros({static_cast<long>(p_.ne) * p_.size, 4}, io);
+    Tensor xs = torch::empty({max_rows, H_}, torch::TensorOptions().device(like.device()).dtype(torch::kBFloat16));
+    dlv::A2AParams p = with_status(like.device().index());
+    dlv::launch_a2a_receive(&p, epoch_, local_offsets.data_ptr<int>(), seg.data_ptr<int>(), xs.data_ptr(), static_cast<int>(max_rows), H_, cur_stream());
+    check_last_error("a2a receive");
+    return {xs, local_offsets, seg};
+  }
+  // Sends the expert outputs back to their senders and returns this rank's own return buffer [cap, H] once every rank has answered.
+  Tensor finish(const Tensor& ys, const Tensor& local_offsets, const Tensor& seg, const Tensor& ret_local) {
+    check_bf16(ys, "ys");
+    TORCH_CHECK(ys.dim() == 2 && ys.size(1) == H_ && ret_local.is_cuda() && ret_local.scalar_type() == at::kBFloat16, "finish arguments");
+    c10::cuda::CUDAGuard guard(ys.device());
+    dlv::A2AParams p = with_status(ys.device().index());
+    dlv::launch_a2a_return(&p, local_offsets.data_ptr<int>(), seg.data_ptr<int>(), ys.data_ptr(), static_cast<int>(ys.size(0)), H_, epoch_, cur_stream());
+    dlv::launch_a2a_wait(&p, epoch_, cur_stream());
+    check_last_error("a2a return");
+    return ret_local;
+  }
+
+ private:
+  dlv::A2AParams with_status(int device) {
+    dlv::A2AParams p = p_;
+    p.status = scratch_for(device).status.data_ptr<int>();
+    return p;
+  }
+  dlv::A2AParams p_;
+  int H_;
+  unsigned epoch_ = 0;
+};
+
 // ---- LoRA delta, pooling, classifier softmax, TurboQuant, LZ4 ------------------------------------------------------------------
 // y += (x @ A^T) @ Bs^T in place; x [M, K], A [r, K], Bs [N, r] (already scaled), y [M, N], all bf16, r <= 64.
 void lora_delta(const Tensor& x, const Tensor& A, const Tensor& Bs, Tensor& y) {
@@ -1204,6 +1274,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_wait_limit_ms", &TpComm::set_wait_limit_ms)
       .def("set_multicast", &TpComm::set_multicast)
       .def("has_multicast", &TpComm::has_multicast);
+  py::class_<ExpertA2A, std::shared_ptr<ExpertA2A>>(m, "ExpertA2A")
+      .def(py::init<int64_t, int64_t, int64_t, int64_t, int64_t, std::vector<int64_t>, std::vector<int64_t>, std::vector<int64_t>, std::vector<int64_t>>())
+      .def("dispatch", &ExpertA2A::dispatch)
+      .def("receive", &ExpertA2A::receive)
+      .def("finish", &ExpertA2A::finish);
   py::class_<DecodeChain, std::shared_ptr<DecodeChain>>(m, "DecodeChain")
       .def(py::init<>())
       .def("add_op", &DecodeChain::add_op, py::arg("w"), py::arg("x"), py::arg("kind"), py::arg("dep") = false, py::arg("scale_src") = -1,

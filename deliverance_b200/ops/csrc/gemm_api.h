@@ -186,6 +186,22 @@ int launch_mamba2(const void* zx, int ld, int T, int num_seqs, int I, int conv_d
                   const int* chunk_first, const int* chunk_last, const int* seq_chunk0, const int* seq_nchunks, int multi_chunk,
                   float* xbc, float* ybuf, float* chunk_state, float* chunk_decay, void* out, cudaStream_t st);
 
+// a2a.cu: expert-parallel all-to-all over peer memory (see the file comment for the protocol)
+struct A2AParams {
+  int size, rank;
+  int ne;                        // experts per rank (<= 128)
+  int cap;                       // rows of a receive region = most (token, slot) pairs one rank can send (its rows * k)
+  unsigned long long recv[8];    // every rank's receive area: bf16 [size regions][cap][H]
+  unsigned long long meta[8];    // every rank's int32 [size][2 * ne]: rows per expert and first grouped row at the sender
+  unsigned long long flags[8];   // every rank's uint32 [16]: dispatch epochs [0..8), return epochs [8..16)
+  unsigned long long ret[8];     // every rank's return buffer: bf16 [cap][H]
+  int* status;
+};
+void launch_a2a_dispatch(const A2AParams* p, const void* x, const int* perm, const int* offsets, int rows, int k, int H, unsigned epoch, cudaStream_t st);
+void launch_a2a_receive(const A2AParams* p, unsigned epoch, int* local_offsets, int* seg, void* xs, int max_rows, int H, cudaStream_t st);
+void launch_a2a_return(const A2AParams* p, const int* local_offsets, const int* seg, const void* ys, int max_rows, int H, unsigned epoch, cudaStream_t st);
+void launch_a2a_wait(const A2AParams* p, unsigned epoch, cudaStream_t st);
+
 // aux.cu
 void launch_lora_delta(const void* x, int ldx, const void* A, const void* Bs, void* y, int ldy, int M, int K, int N, int r, cudaStream_t st);
 void launch_pool(const void* h, int H, const int* start, const int* len, int S, int mode, int normalize, float* out, cudaStream_t st);

@@ -65,6 +65,42 @@ class ScatterState:
         torch.cuda.synchronize(device)
 
 
+class ExpertAllToAll:
+    """Expert-parallel dispatch / return over peer memory for token rows that are sharded over the ranks (csrc/a2a.cu). One instance
+    serves every mixture-of-experts layer of a model: ``cap`` = most (token, slot) pairs a rank can send in one forward."""
+
+    def __init__(self, tp: TensorParallelContext, device, n_local_experts: int, hidden: int, cap: int):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.tp, self.device, self.ne, self.H, self.cap = tp, torch.device(device), n_local_experts, hidden, cap
+        recv_b = tp.size * cap * hidden * 2
+        meta_b = (tp.size * 2 * n_local_experts * 4 + 15) // 16 * 16
+        flag_b = 64
+        ret_b = cap * hidden * 2
+        self.buf = symm.empty(recv_b + meta_b + flag_b + ret_b, dtype=torch.uint8, device=self.device)
+        self.buf[recv_b:recv_b + meta_b + flag_b].zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm.rendezvous(self.buf, dist.group.WORLD)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.ret_local = self.buf[recv_b + meta_b + flag_b:].view(torch.bfloat16).view(cap, hidden)
+        self.comm = ops.require_ext().ExpertA2A(tp.rank, tp.size, n_local_experts, cap, hidden, ptrs, [p + recv_b for p in ptrs],
+                                                [p + recv_b + meta_b for p in ptrs], [p + recv_b + meta_b + flag_b for p in ptrs])
+        self.sent_rows = 0   # rows this rank pushed to other ranks (NVLink traffic = rows * hidden * 2 bytes, the same again on the way back)
+        dist.barrier()
+        torch.cuda.synchronize(self.device)
+
+    def forward(self, x_own: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, k: int, run_experts, max_recv_rows: int):
+        """``x_own`` [T_own, H] with ``perm`` / ``offsets`` from the router over the own tokens. ``run_experts(xs, local_offsets)``
+        multiplies rows grouped by local expert and returns rows in the same order. Returns the return buffer: expert outputs of
+        this rank's (token, slot) pairs at their grouped row index (the layout ``moe_combine`` expects)."""
+        self.comm.dispatch(x_own.contiguous(), perm, offsets, k)
+        xs, local_offsets, seg = self.comm.receive(max_recv_rows, x_own)
+        ys = run_experts(xs, local_offsets)
+        ops._count(7)
+        return self.comm.finish(ys.contiguous(), local_offsets, seg, self.ret_local)
+
+
 class FusedTensorParallel:
     def __init__(self, tp: TensorParallelContext, device, max_rows: int = 128, max_cols: int = 8192):
         import torch.distributed as dist
@@ -137,6 +173,18 @@ class FusedTensorParallel:
         y = ops.linear(x, w) if self.tp.rank == 0 or w.bias is None else ops.linear(x, _no_bias(w))
         return self.tp.collectives.all_reduce_sum(key, y)
 
+
+    def expert_a2a(self, n_local_experts: int, hidden: int, k: int):
+        """The all-to-all state for a model's mixture-of-experts layers (created on first use; every rank must call it at the same
+        point). Sized for the largest sequence-parallel batch: ``DLV_TP_SCATTER_ROWS`` rows cut over the ranks, ``k`` slots each."""
+        key = (n_local_experts, hidden, k)
+        cache = self.__dict__.setdefault("_a2a", {})
+        if key not in cache:
+            import os
+
+            rows = int(os.environ.get("DLV_TP_SCATTER_ROWS", "8192"))
+            cache[key] = ExpertAllToAll(self.tp, self.device, n_local_experts, hidden, (row_cut(rows, self.tp.size, 0)[0] + 8) * k)
+        return cache[key]
 
     def linear_reduce_norm(self, x: torch.Tensor, w, residual: torch.Tensor, norm_w: torch.Tensor, post_w, eps: float, offset: float,
                            res_mult: float):

@@ -217,6 +217,9 @@ def main() -> int:
         toks = {}
         for name, ctx in (("single", TensorParallelContext()), ("tp_sp", tp)):
             model = DecoderModel(cfg, dev, torch.bfloat16, ctx).load(SyntheticLoader(shape, 3, True, dev, std=0.05), head_quant="Q4")
+            # a sequence-parallel forward keeps projection and rotary embedding as two kernels; the reference run does the same, so that
+            # the comparison of greedy tokens of a random-weight model (near-ties between logits) is between equal roundings
+            model.fused_rope = False
             used = []
             plan = model._sp_plan
             model._sp_plan = lambda b, plan=plan, used=used: (used.append(plan(b)), used[-1])[1]
@@ -289,6 +292,68 @@ def main() -> int:
     ok_all &= first_tok
     report(check="ep_moe_model_tokens", local_experts=local_experts[0], equal=equal, first_token_equal=first_tok, ok=first_tok,
            fused_calls=fused.stats["fused"], fallback_calls=fused.stats["fallback"])
+
+    # sequence-parallel prefill of the expert-parallel model: attention through reduce-scatter / all-gather, experts through the all-to-all
+    n_long = 256 * world + 11
+    if os.environ.get("DLV_TP_SEQ_PARALLEL") == "1" and fused.scatter is not None and n_long + 8 <= mshape["max_position_embeddings"]:
+        long_prompt = [torch.randint(0, 4096, (n_long,), generator=torch.Generator().manual_seed(98)).tolist()]
+        toks = {}
+        for name, ctx in (("single", TensorParallelContext()), ("ep_sp", tp)):
+            m2 = DecoderModel(mcfg, dev, torch.bfloat16, ctx).load(SyntheticLoader(mshape, 5, True, dev, std=0.05))
+            m2.fused_rope = False  # as above: equal roundings on both sides
+            used = []
+            plan = m2._sp_plan
+            m2._sp_plan = lambda b, plan=plan, used=used: (used.append(plan(b)), used[-1])[1]
+            ec = EngineConfig(num_pages=256, cuda_graphs=False)
+            ec.kv.enabled = False
+            rs = Engine(m2, ec, eos_ids=(-1,)).generate_batch(long_prompt, GeneratorParameters(max_tokens=4))
+            toks[name] = (rs[0].token_ids, sum(1 for u in used if u is not None))
+            torch.cuda.synchronize()
+            ops.check_status(local)
+            dist.barrier()
+        good = toks["single"][0][0] == toks["ep_sp"][0][0] and toks["ep_sp"][1] >= 1
+        ok_all &= good
+        report(check="sequence_parallel_moe_all_to_all_tokens", prompt=n_long, first_token_equal=toks["single"][0][0] == toks["ep_sp"][0][0],
+               sp_forwards=toks["ep_sp"][1], equal_tokens=toks["single"][0] == toks["ep_sp"][0], ok=good)
+
+    # ---------------------------------------------------------------- (2d) expert-parallel all-to-all: token rows sharded over the ranks
+    # The model above (expert-parallel weights on this rank) runs one mixture-of-experts layer two ways on the same rows: replicated
+    # tokens with local selection + sum over ranks, and own rows only with dispatch / return over peer memory. Router logits are
+    # biased from uniform to a Zipf(1.1) load over the experts.
+    from deliverance_b200.models.moe import moe_forward, moe_forward_sharded
+    from deliverance_b200.parallel.fused import ExpertAllToAll, row_cut
+
+    lw_moe = next(lw for lw in model.layers if lw.router is not None)
+    E_, k_ = mcfg.num_experts, mcfg.experts_per_token
+    a2a = ExpertAllToAll(tp, dev, lw_moe.n_local_experts, mcfg.hidden_size, cap=1024 * k_)
+    router_w = lw_moe.router
+    for (T_all, skew) in ((world * 40 + 3, 0.0), (world * 256, 0.0), (world * 256, 1.1)):
+        g3 = torch.Generator().manual_seed(77 + T_all)
+        x_all = (torch.randn(T_all, mcfg.hidden_size, generator=g3) * 0.5).to(torch.bfloat16).to(dev)
+        if skew > 0:  # push the routing towards a Zipf load: add log(rank^-skew) to the router logits through a bias row trick
+            bias = torch.log(torch.arange(1, E_ + 1, dtype=torch.float32) ** (-skew)) * 4.0
+            x_all[:, 0] = 0  # keep the activations as they are; the bias enters through the router weight's first column
+            saved = router_w
+            wd = router_w.dense(torch.bfloat16).clone()
+            wd[:, 0] = 0
+            lw_moe.router = LinearWeight(wd.cpu()).to(dev, torch.bfloat16)
+            lw_moe.router.bias = bias.to(dev)
+        rpr, first, count = row_cut(T_all, world, rank)
+        want = moe_forward(model, 0, lw_moe, x_all)[first:first + count]
+        sent0 = a2a.sent_rows
+        got = moe_forward_sharded(model, 0, lw_moe, x_all[first:first + count].contiguous(), a2a, T_all)
+        torch.cuda.synchronize()
+        ops.check_status(local)
+        err = ((got.float() - want.float()).norm() / want.float().norm().clamp_min(1e-9)).item() if count else 0.0
+        good = err < 5e-3
+        ok_all &= good
+        sent = a2a.sent_rows - sent0
+        report(check="ep_all_to_all_dispatch_grouped_gemm_combine", tokens=T_all, own_rows=count, zipf=skew, rel_err=err, ok=good,
+               nvlink_bytes_per_rank_a2a=2 * sent * (world - 1) // world * mcfg.hidden_size * 2,
+               nvlink_bytes_per_rank_replicated=2 * (world - 1) * T_all * mcfg.hidden_size * 2 // world)
+        if skew > 0:
+            lw_moe.router = saved
+        dist.barrier()
 
     # ---------------------------------------------------------------- (3) timing
     if a.bench:

@@ -279,7 +279,8 @@ def test_gemm_epilogue_gated_activation(M, I, K, q4, act):
 
 @pytest.mark.parametrize("M,H,KV,K,q4,qk_norm,rot_half,bias", [(1, 4, 2, 256, True, True, 64, False), (7, 32, 8, 2560, True, True, 64, False),
                                                                 (64, 32, 8, 2560, True, True, 64, False), (64, 4, 1, 2560, True, False, 64, True),
-                                                                (200, 8, 2, 512, False, True, 64, True), (33, 4, 4, 4096, False, False, 64, False)])
+                                                                (200, 8, 2, 512, False, True, 64, True), (33, 4, 4, 4096, False, False, 64, False),
+                                                                (529, 32, 8, 2560, True, True, 64, False), (700, 4, 2, 512, False, True, 64, False)])
 def test_gemm_epilogue_rope_kv(M, H, KV, K, q4, qk_norm, rot_half, bias):
     """linear_rope_kv against the two separate kernels (projection, then rope_kv) on the same inputs: query heads and the
     written cache rows must agree up to the bf16 rounding of the intermediate tensor."""

@@ -169,3 +169,41 @@ def test_fused_activation_models_gpu(tmp_path, family, monkeypatch):
     rs = eng.generate_batch(seqs, GeneratorParameters(max_tokens=8))
     ops.check_status(0)
     assert all(r.generated_tokens == 8 for r in rs)
+
+
+@pytest.mark.parametrize("family,over", [("qwen3", dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=128)),
+                                         ("llama", dict(hidden_size=512, num_attention_heads=4, num_key_value_heads=2))])
+def test_fused_rope_models_gpu(tmp_path, family, over, monkeypatch):
+    """head_dim 128 models: the q|k|v projection with norm + rotary + KV write in its epilogue (the default on CUDA) against the
+    projection followed by the separate kernel: prefill logits of two sequences (one longer than a 256-token tile) and decode."""
+    d = str(tmp_path / family)
+    write_tiny_model(d, family, seed=13, std=0.05, quantize=True, max_position_embeddings=1024, **over)
+    cfg = load_config(d)
+    assert cfg.head_dim == 128
+    monkeypatch.setenv("DLV_FUSED_ROPE", "0")
+    plain = DecoderModel(cfg, "cuda:0").load(WeightLoader(d))
+    monkeypatch.setenv("DLV_FUSED_ROPE", "auto")
+    fused = DecoderModel(cfg, "cuda:0").load(WeightLoader(d))
+    assert fused.fused_rope and not plain.fused_rope
+    g = torch.Generator().manual_seed(4)
+    seqs = [torch.randint(3, 250, (n,), generator=g).tolist() for n in (540, 33)]
+    outs, caches = [], []
+    for m in (plain, fused):
+        eng = Engine(m, EngineConfig(num_pages=128, cuda_graphs=False))
+        descr, nxt = [], 1
+        for i, t in enumerate(seqs):
+            n = (len(t) + 31) // 32
+            descr.append({"tokens": t, "start": 0, "pages": list(range(nxt, nxt + n)), "state_slot": i})
+            nxt += n
+        outs.append(m.forward(make_batch(descr, 32, m.device), eng.kv, all_rows=True).float().cpu())
+        caches.append((eng.kv.k[0].float().cpu(), eng.kv.v[0].float().cpu()))
+        ops.check_status(0)
+    assert ((caches[0][0] - caches[1][0]).norm() / caches[0][0].norm()).item() < 2e-2
+    assert ((caches[0][1] - caches[1][1]).norm() / caches[0][1].norm()).item() < 2e-2
+    rel = ((outs[0] - outs[1]).norm() / outs[0].norm()).item()
+    assert rel < 2e-2, rel
+    res = []
+    for m in (plain, fused):
+        eng = Engine(m, EngineConfig(num_pages=128, max_batch_tokens=2048))
+        res.append([r.token_ids for r in eng.generate_batch(seqs, GeneratorParameters(max_tokens=6))])
+    assert [r[0] for r in res[0]] == [r[0] for r in res[1]]

@@ -37,3 +37,6 @@ def test_two_rank_gemm_reduce_scatter():
     assert any(l.get("check") == "sequence_parallel_prefill_tokens" and l["ok"] for l in lines)
     gath = [l for l in lines if l.get("check") == "all_gather_gemm"]
     assert len(gath) == 2 and all(l["ok"] for l in gath)
+    a2a = [l for l in lines if l.get("check") == "ep_all_to_all_dispatch_grouped_gemm_combine"]
+    assert len(a2a) == 3 and all(l["ok"] for l in a2a) and any(l["zipf"] > 0 for l in a2a)
+    assert any(l.get("check") == "sequence_parallel_moe_all_to_all_tokens" and l["ok"] for l in lines)
