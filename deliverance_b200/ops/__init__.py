@@ -362,10 +362,21 @@ def prefill_tiles(q_lens: list[int], tile: int = 64) -> tuple[list[int], list[in
     return seqs, q0s
 
 
+PREFILL_TC = [os.environ.get("DLV_PREFILL_ATTN", "mma") == "tc"]  # "tc": the tcgen05 / TMA kernel; default: the mma.sync kernel
+
+
 def prefill_attention(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens, H, scale, softcap=0.0, window=0, causal=True,
-                      tile_seq=None, tile_q0=None):
-    """Ragged query rows against the paged cache (K/V of the new tokens are already in the cache)."""
+                      tile_seq=None, tile_q0=None, impl=None, q_len_host=None):
+    """Ragged query rows against the paged cache (K/V of the new tokens are already in the cache). ``impl``: ``"tc"`` = the tcgen05 /
+    TMA kernel (128-row query tiles), ``"mma"`` = the mma.sync kernel (64-row tiles); default from ``DLV_PREFILL_ATTN``."""
     if _cuda(q):
+        if (impl or ("tc" if PREFILL_TC[0] else "mma")) == "tc":
+            lens = q_len_host if q_len_host is not None else [int(v) for v in q_len.tolist()]
+            ts, t0 = prefill_tiles(list(lens), 128)
+            _count()
+            return require_ext().prefill_attention_tc(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens,
+                                                      torch.tensor(ts, dtype=torch.int32, device=q.device), torch.tensor(t0, dtype=torch.int32, device=q.device),
+                                                      H, scale, softcap, window, causal)
         if tile_seq is None:
             ts, t0 = prefill_tiles([int(v) for v in q_len.tolist()])
             tile_seq = torch.tensor(ts, dtype=torch.int32, device=q.device)

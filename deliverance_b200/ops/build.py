@@ -15,7 +15,7 @@ CSRC = os.path.join(_HERE, "csrc")
 BUILD_DIR = os.path.join(_HERE, "_build")
 NAME = "_dlv_C"
 SOURCES = ["bindings.cpp", "gemm.cu", "elementwise.cu", "attention.cu", "sampling.cu", "quant.cu", "moe.cu", "mamba.cu",
-           "comm.cu", "noalloc.cu", "chain.cu", "aux.cu", "a2a.cu", "lz4_block.cpp"]
+           "comm.cu", "noalloc.cu", "chain.cu", "aux.cu", "a2a.cu", "attention_tc.cu", "lz4_block.cpp"]
 
 CUDA_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -657,6 +657,36 @@ Tensor prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v
   return out;
 }
 
+// Same contract as prefill_attention, on the tcgen05 / TMA kernel; tile arrays cover 128 query rows per tile.
+Tensor prefill_attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables, const Tensor& q_start,
+                            const Tensor& q_len, const Tensor& ctx_lens, const Tensor& tile_seq, const Tensor& tile_q0, int64_t H, double scale,
+                            double softcap, int64_t window, bool causal) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 2 && q.stride(1) == 1, "q must be bf16 [T, H*D]");
+  TORCH_CHECK(q.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(q.data_ptr()) & 15) == 0, "q rows must be 16-byte aligned");
+  check_bf16(k_cache, "k_cache");
+  check_bf16(v_cache, "v_cache");
+  for (const Tensor* t : {&block_tables, &q_start, &q_len, &ctx_lens, &tile_seq, &tile_q0}) {
+    check_cuda(*t, "index tensor");
+    TORCH_CHECK(t->scalar_type() == at::kInt, "index tensors must be int32");
+  }
+  const int T = static_cast<int>(q.size(0));
+  const int KV = static_cast<int>(k_cache.size(1)), page = static_cast<int>(k_cache.size(2)), D = static_cast<int>(k_cache.size(3));
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes() && q.size(1) == H * D && H % KV == 0, "shape mismatch");
+  TORCH_CHECK((page == 32 || page == 64 || page == 128) && (D == 64 || D == 128 || D == 256), "page size 32 / 64 / 128 and head_dim 64 / 128 / 256");
+  TORCH_CHECK(tile_seq.numel() == tile_q0.numel(), "tile arrays differ in length");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({T, H * D}, q.options());
+  DeviceScratch& s = scratch_for(q.device().index());
+  int rc = dlv::launch_prefill_attention_tc(q.data_ptr(), q.stride(0), T, k_cache.data_ptr(), v_cache.data_ptr(), k_cache.size(0), block_tables.data_ptr<int>(),
+                                            static_cast<int>(block_tables.stride(0)), q_start.data_ptr<int>(), q_len.data_ptr<int>(), ctx_lens.data_ptr<int>(),
+                                            tile_seq.data_ptr<int>(), tile_q0.data_ptr<int>(), static_cast<int>(tile_seq.numel()), out.data_ptr(),
+                                            static_cast<int>(H), KV, D, page, static_cast<float>(scale), static_cast<float>(softcap),
+                                            static_cast<int>(window), causal ? 1 : 0, s.status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "prefill attention (tcgen05): unsupported shape");
+  check_last_error("prefill_attention_tc");
+  return out;
+}
+
 // ---- sampling ---------------------------------------------------------------------------------------------------------
 std::vector<Tensor> argmax(const Tensor& logits, c10::optional<Tensor> mask, double softcap, double inv_scale) {
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
@@ -1324,6 +1354,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attention", &decode_attention, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("block_tables"), py::arg("ctx_lens"),
         py::arg("H"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("window") = 0, py::arg("splits") = 1, py::arg("impl") = 0);
   m.def("prefill_attention", &prefill_attention);
+  m.def("prefill_attention_tc", &prefill_attention_tc);
   m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("sample_rows", &sample_rows);
   m.def("xtc_rows", &xtc_rows);

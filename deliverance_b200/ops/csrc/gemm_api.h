@@ -133,6 +133,12 @@ int launch_prefill_attention(const void* q, long long q_stride, const void* kc, 
                              int num_tiles, void* out, int H, int KV, int D, int page, float scale, float cap, int window,
                              int causal, cudaStream_t st);
 
+// attention_tc.cu: tcgen05 / TMA prefill attention; tile arrays hold 128 query rows per tile
+int launch_prefill_attention_tc(const void* q, long long q_stride, long long T, const void* kc, const void* vc, long long num_pages, const int* bt,
+                                int bt_stride, const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,
+                                int num_tiles, void* out, int H, int KV, int D, int page, float scale, float cap, int window, int causal, int* status,
+                                cudaStream_t st);
+
 // sampling.cu
 void launch_argmax(const float* logits, int ld, int B, int V, const uint32_t* mask, int mask_ld, float softcap, float inv_scale,
                    long long* out_idx, float* out_val, cudaStream_t st);

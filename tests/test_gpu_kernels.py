@@ -176,6 +176,31 @@ def test_prefill_attention(D, H, KV, softcap, window):
     assert _rel(o.cpu(), o_ref) < 1e-2
 
 
+@pytest.mark.parametrize("D,H,KV,softcap,window", [(128, 8, 2, 0.0, 0), (64, 4, 4, 0.0, 0), (256, 4, 2, 30.0, 0), (128, 4, 1, 0.0, 100), (64, 8, 2, 50.0, 37)])
+def test_prefill_attention_tcgen05(D, H, KV, softcap, window):
+    """The tcgen05 / TMEM / TMA prefill kernel against the fp32 statement: several key tiles, a chunk continuing a cached prefix,
+    ragged tails, GQA, soft-cap and sliding window; pages hold garbage beyond the context end (it must never reach the output)."""
+    seqs = [(70, 70), (300, 300), (5, 133), (130, 500), (1, 40), (257, 257)]
+    ctx = [c for _, c in seqs]
+    kc, vc, bt = _paged_setup(ctx, KV, D, seed=3)
+    ql = [q for q, _ in seqs]
+    T = sum(ql)
+    qs = [sum(ql[:i]) for i in range(len(ql))]
+    q = (torch.randn(T, H * D) * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    ti = lambda v: torch.tensor(v, dtype=torch.int32)  # noqa: E731
+    o_ref = ref.paged_attention(q.float().reshape(T, H, D), kc.float(), vc.float(), bt, ti(qs), ti(ql), ti(ctx), scale, softcap, window,
+                                True).reshape(T, H * D)
+    o = ops.prefill_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), ti(qs).to(DEV), ti(ql).to(DEV), ti(ctx).to(DEV), H, scale,
+                              softcap, window, True, impl="tc")
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert _rel(o.cpu(), o_ref) < 1e-2, _rel(o.cpu(), o_ref)
+    o2 = ops.prefill_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), ti(qs).to(DEV), ti(ql).to(DEV), ti(ctx).to(DEV), H, scale,
+                               softcap, window, True, impl="mma")
+    assert _rel(o.cpu(), o2.cpu()) < 1e-2
+
+
 def test_argmax_and_logits_post():
     B, V = 5, 151936
     logits = torch.randn(B, V, device=DEV)
