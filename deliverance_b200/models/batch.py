@@ -25,6 +25,21 @@ class ForwardBatch:
     q_len_host: list = field(default_factory=list)
     ctx_len_host: list = field(default_factory=list)
     token_types: Optional[torch.Tensor] = None  # bert
+    _tiles: dict = field(default_factory=dict)  # tile height -> (tile_seq, tile_q0) device tensors
+
+    def tiles(self, rows: int):
+        """Device tile arrays ``(tile_seq, tile_q0)`` for query tiles of ``rows`` rows (built once per height from ``q_len_host``)."""
+        if rows == 64 and self.tile_seq is not None:
+            return self.tile_seq, self.tile_q0
+        got = self._tiles.get(rows)
+        if got is None:
+            from ..ops import prefill_tiles
+
+            ts, t0 = prefill_tiles(list(self.q_len_host), rows)
+            dev = self.q_len.device
+            got = (torch.tensor(ts, dtype=torch.int32).to(dev, non_blocking=True), torch.tensor(t0, dtype=torch.int32).to(dev, non_blocking=True))
+            self._tiles[rows] = got
+        return got
 
     @property
     def num_tokens(self) -> int:

@@ -93,7 +93,7 @@ class BertModel:
             q = ops.rope_kv(qkv, batch.positions, batch.slots, None, None, None, None, kc, vc, cfg.num_heads, cfg.num_kv_heads,
                             cfg.head_dim, cfg.norm_eps, 0.0)
             a = ops.prefill_attention(q, kc, vc, batch.block_tables, batch.q_start, batch.q_len, batch.ctx_len, cfg.num_heads,
-                                      cfg.scale, 0.0, 0, False, batch.tile_seq, batch.tile_q0)
+                                      cfg.scale, 0.0, 0, False, batch.tile_seq, batch.tile_q0, tiles_for=batch.tiles)
             h = ops.layernorm(h + ops.linear(a, lw["o"]), lw["ln1"][0], lw["ln1"][1], cfg.norm_eps)
             f = ops.linear(ops.activation(ops.linear(h, lw["up"]), cfg.hidden_act), lw["down"])
             h = ops.layernorm(h + f, lw["ln2"][0], lw["ln2"][1], cfg.norm_eps)

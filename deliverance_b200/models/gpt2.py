@@ -52,7 +52,7 @@ class Gpt2Model(DecoderModel):
                                          batch.decode_splits)
             else:
                 a = ops.prefill_attention(q, k_cache, v_cache, batch.block_tables, batch.q_start, batch.q_len, batch.ctx_len,
-                                          self.n_heads, cfg.scale, 0.0, 0, True, batch.tile_seq, batch.tile_q0)
+                                          self.n_heads, cfg.scale, 0.0, 0, True, batch.tile_seq, batch.tile_q0, tiles_for=batch.tiles)
             h = h + ops.linear(a, lw.o)
             self._trace(i, "attn", h)
             x = ops.layernorm(h, lw.pre_ff_norm[0], lw.pre_ff_norm[1], cfg.norm_eps)

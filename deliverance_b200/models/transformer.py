@@ -372,7 +372,7 @@ class DecoderModel:
                                          cfg.attn_softcap, window, batch.decode_splits)
             else:
                 a = ops.prefill_attention(q, k_cache, v_cache, batch.block_tables, batch.q_start, batch.q_len, batch.ctx_len,
-                                          self.n_heads, cfg.scale, cfg.attn_softcap, window, True, batch.tile_seq, batch.tile_q0)
+                                          self.n_heads, cfg.scale, cfg.attn_softcap, window, True, batch.tile_seq, batch.tile_q0, tiles_for=batch.tiles)
         with self._stage("causalselfattention.output_projection"):
             if norm_after is not None and not lw.lora:
                 x = self._row_parallel_norm(a, lw.o, norm_after)

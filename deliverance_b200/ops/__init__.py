@@ -362,25 +362,42 @@ def prefill_tiles(q_lens: list[int], tile: int = 64) -> tuple[list[int], list[in
     return seqs, q0s
 
 
-PREFILL_TC = [os.environ.get("DLV_PREFILL_ATTN", "mma") == "tc"]  # "tc": the tcgen05 / TMA kernel; default: the mma.sync kernel
+PREFILL_ATTN = [os.environ.get("DLV_PREFILL_ATTN", "auto")]  # "auto": the tcgen05 / TMA kernel where it applies; "mma": the mma.sync kernel; "tc"
+
+
+def _prefill_tc_ok(q, k_cache) -> bool:
+    """Shapes the tcgen05 prefill kernel takes: head_dim 64 / 128 / 256, pages of 32 / 64 / 128 tokens, 16-byte aligned query rows."""
+    return (k_cache.shape[-1] in (64, 128, 256) and k_cache.shape[2] in (32, 64, 128) and q.stride(0) % 8 == 0 and q.stride(1) == 1
+            and q.data_ptr() % 16 == 0 and q.dtype == torch.bfloat16)
 
 
 def prefill_attention(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens, H, scale, softcap=0.0, window=0, causal=True,
-                      tile_seq=None, tile_q0=None, impl=None, q_len_host=None):
+                      tile_seq=None, tile_q0=None, impl=None, q_len_host=None, tiles_for=None):
     """Ragged query rows against the paged cache (K/V of the new tokens are already in the cache). ``impl``: ``"tc"`` = the tcgen05 /
-    TMA kernel (128-row query tiles), ``"mma"`` = the mma.sync kernel (64-row tiles); default from ``DLV_PREFILL_ATTN``."""
+    TMA kernel (256-row query tiles, 128 for head_dim 256), ``"mma"`` = the mma.sync kernel (64-row tiles, ``tile_seq`` / ``tile_q0``);
+    default from ``DLV_PREFILL_ATTN`` (``auto``: the tcgen05 kernel for the shapes it takes). ``tiles_for(rows)`` returns the device
+    tile arrays for a tile height (``ForwardBatch.tiles``); without it they are built from ``q_len_host`` or a read-back of ``q_len``."""
     if _cuda(q):
-        if (impl or ("tc" if PREFILL_TC[0] else "mma")) == "tc":
-            lens = q_len_host if q_len_host is not None else [int(v) for v in q_len.tolist()]
-            ts, t0 = prefill_tiles(list(lens), 128)
+        mode = impl or PREFILL_ATTN[0]
+        if mode == "tc" or (mode == "auto" and _prefill_tc_ok(q, k_cache)):
+            ext = require_ext()
+            rows = ext.prefill_tc_tile_rows(int(k_cache.shape[-1]))
+            if tiles_for is not None:
+                ts_d, t0_d = tiles_for(rows)
+            else:
+                lens = q_len_host if q_len_host is not None else [int(v) for v in q_len.tolist()]
+                ts, t0 = prefill_tiles(list(lens), rows)
+                ts_d = torch.tensor(ts, dtype=torch.int32, device=q.device)
+                t0_d = torch.tensor(t0, dtype=torch.int32, device=q.device)
             _count()
-            return require_ext().prefill_attention_tc(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens,
-                                                      torch.tensor(ts, dtype=torch.int32, device=q.device), torch.tensor(t0, dtype=torch.int32, device=q.device),
-                                                      H, scale, softcap, window, causal)
+            return ext.prefill_attention_tc(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens, ts_d, t0_d, H, scale, softcap, window, causal)
         if tile_seq is None:
-            ts, t0 = prefill_tiles([int(v) for v in q_len.tolist()])
-            tile_seq = torch.tensor(ts, dtype=torch.int32, device=q.device)
-            tile_q0 = torch.tensor(t0, dtype=torch.int32, device=q.device)
+            if tiles_for is not None:
+                tile_seq, tile_q0 = tiles_for(64)
+            else:
+                ts, t0 = prefill_tiles([int(v) for v in q_len.tolist()])
+                tile_seq = torch.tensor(ts, dtype=torch.int32, device=q.device)
+                tile_q0 = torch.tensor(t0, dtype=torch.int32, device=q.device)
         _count()
         return require_ext().prefill_attention(q, k_cache, v_cache, block_tables, q_start, q_len, ctx_lens, tile_seq, tile_q0, H, scale,
                                                softcap, window, causal)

@@ -657,7 +657,7 @@ Tensor prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v
   return out;
 }
 
-// Same contract as prefill_attention, on the tcgen05 / TMA kernel; tile arrays cover 128 query rows per tile.
+// Same contract as prefill_attention, on the tcgen05 / TMA kernel; tile arrays cover prefill_tc_tile_rows(head_dim) query rows per tile.
 Tensor prefill_attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables, const Tensor& q_start,
                             const Tensor& q_len, const Tensor& ctx_lens, const Tensor& tile_seq, const Tensor& tile_q0, int64_t H, double scale,
                             double softcap, int64_t window, bool causal) {
@@ -1355,6 +1355,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("H"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("window") = 0, py::arg("splits") = 1, py::arg("impl") = 0);
   m.def("prefill_attention", &prefill_attention);
   m.def("prefill_attention_tc", &prefill_attention_tc);
+  m.def("prefill_tc_tile_rows", &dlv::prefill_attention_tc_tile_rows);
   m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("sample_rows", &sample_rows);
   m.def("xtc_rows", &xtc_rows);

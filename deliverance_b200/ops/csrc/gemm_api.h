@@ -133,7 +133,8 @@ int launch_prefill_attention(const void* q, long long q_stride, const void* kc, 
                              int num_tiles, void* out, int H, int KV, int D, int page, float scale, float cap, int window,
                              int causal, cudaStream_t st);
 
-// attention_tc.cu: tcgen05 / TMA prefill attention; tile arrays hold 128 query rows per tile
+// attention_tc.cu: tcgen05 / TMA prefill attention; tile arrays hold prefill_attention_tc_tile_rows(D) query rows per tile
+int prefill_attention_tc_tile_rows(int D);
 int launch_prefill_attention_tc(const void* q, long long q_stride, long long T, const void* kc, const void* vc, long long num_pages, const int* bt,
                                 int bt_stride, const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,
                                 int num_tiles, void* out, int H, int KV, int D, int page, float scale, float cap, int window, int causal, int* status,
