@@ -127,9 +127,10 @@ struct GemmSmem {
   // warps, four dequant groups, kNI MMA issuers). mbarrier waits only know the PARITY of a phase, so a thread must see every
   // phase of the barriers it waits on: each ring depth is a multiple of the number of its producers and of its consumers,
   // which ties every stage to one producer and one consumer for the whole kernel.
-  static constexpr int kNI = BN <= 64 ? 4 : (BN == 128 ? 2 : 1);  // MMA-issuing warps = accumulators (see the issuer loop)
+  static constexpr int kNI = BN <= 64 ? 4 : 2;  // MMA-issuing warps (see the issuer loop)
+  static constexpr bool kSharedAcc = BN > 128;  // the issuers add into one accumulator (tensor memory has no room for two of 256 columns)
   static constexpr int kNW = Q4 ? 0 : (BN <= 64 ? 4 : 2);         // dense: W and X rings of equal depth
-  static constexpr int kAccCols = kNI * BN;
+  static constexpr int kAccCols = kSharedAcc ? BN : kNI * BN;
   static constexpr int kTmemA = kAccCols < 64 ? 64 : kAccCols;  // JQ4: the A-operand ring in tensor memory follows the accumulators
   static constexpr int kNA = 4;                                  // one stage per dequant group
   static constexpr int kNX = Q4 ? (BN <= 32 ? 8 : (BN <= 128 ? 4 : 2)) : kNW;
@@ -193,7 +194,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
   uint64_t* bar_r_full = bar_x_empty + NX;
   uint64_t* bar_r_empty = bar_r_full + NR;
   uint64_t* bar_acc = bar_r_empty + NR;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc + 1);
+  uint64_t* bar_first = bar_acc + 1;  // shared accumulator: its first k-block (the one that overwrites) has retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_first + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_last = const_cast<int*>(abort_flag) + 1;
   constexpr int NAS = Q4 ? NA : NW;  // depth of the A-operand ring
@@ -249,6 +251,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
       mbar_init(smem_u32(&bar_r_empty[s]), 4);
     }
     mbar_init(smem_u32(bar_acc), NI);
+    mbar_init(smem_u32(bar_first), 1);
     *abort_flag = 0;
     *s_last = 0;
     mbar_fence_init();
@@ -358,21 +361,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     }
   } else if (warp == 1 || warp >= 21) {
     // ---------------- MMA issuers ----------------
-    // Issuing one tcgen05.mma costs the issuing thread about 90 cycles whatever the tile shape, so with few tokens (small
-    // UMMA N) a single issuer, not the tensor pipe or the memory system, paces the kernel (8 instructions per 128-wide
-    // k-block = 0.4 us). NI warps therefore take alternate k-blocks, each into its own accumulator (columns j*BN ..), and the
-    // epilogue adds the accumulators. The whole warp follows the barriers, one lane issues.
+    // A tcgen05.mma holds its thread until the tensor pipe accepts it, the pipe queues next to nothing, and a wait on an mbarrier,
+    // even a complete one, costs the thread a few hundred cycles: a single issuer leaves the pipe idle between k-blocks (measured:
+    // groups of 8 MMAs of 128 x 128 x 16 back to back 517 cycles per group, with one satisfied wait between groups 783). NI warps
+    // therefore take alternate k-blocks, so that one feeds the pipe while another waits: each into its own accumulator (columns
+    // j*BN .., added up by the epilogue), or, where tensor memory has no room for that (BN = 256), all into one. (For the JQ4 prefill
+    // shapes the second issuer of BN = 256 changed nothing measurable: there the expansion of the weights paces the kernel.) The
+    // whole warp follows the barriers, one lane issues.
     const int issuer = warp == 1 ? 0 : warp - 20;
     if (issuer < NI) {
       constexpr uint32_t idesc = umma_idesc_bf16(kGemmBM, BN);
       const uint64_t desc_w0 = umma_desc_k_sw128(smem_u32(smem));
       const uint64_t desc_x0 = umma_desc_k_sw128(smem_u32(smem + L::kOffX));
-      const uint32_t tmem_acc = tmem_base + issuer * BN;
+      const uint32_t tmem_acc = tmem_base + (L::kSharedAcc ? 0 : issuer * BN);
       bool ok = true;
       for (int i = issuer; i < nkb; i += NI) {
         const int sa = i % NAS, sx = i % NX;
         ok = mbar_wait(smem_u32(&bar_a_full[sa]), (i / NAS) & 1, abort_flag, p.status);
         ok = ok && mbar_wait(smem_u32(&bar_x_full[sx]), (i / NX) & 1, abort_flag, p.status);
+        // one accumulator for all issuers: the others only add, and not before the k-block that overwrites it has retired
+        if (L::kSharedAcc && issuer > 0 && i == issuer) ok = ok && mbar_wait(smem_u32(bar_first), 0, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -383,7 +391,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
           for (int k4 = 0; k4 < 8; ++k4) {
             const int sub = k4 >> 2, kk = k4 & 3;
             const uint64_t db = dx + static_cast<uint64_t>((sub * (BN * 128) + kk * 32) >> 4);
-            const uint32_t acc = (i >= NI || k4 > 0) ? 1u : 0u;
+            const uint32_t acc = ((L::kSharedAcc ? i > 0 : i >= NI) || k4 > 0) ? 1u : 0u;
             if (Q4) {
               umma_bf16_ts(tmem_acc, tmem_base + L::kTmemA + sa * kGemmTmemAStage + k4 * 8, db, idesc, acc);
             } else {
@@ -393,6 +401,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
           }
           umma_commit(smem_u32(&bar_a_empty[sa]));
           umma_commit(smem_u32(&bar_x_empty[sx]));
+          if (L::kSharedAcc && i == 0) umma_commit(smem_u32(bar_first));
         }
         __syncwarp();
       }
@@ -475,7 +484,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
         const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * COLS;
         float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll 1
-        const int nacc = nkb < NI ? nkb : NI;  // issuers without a k-block never wrote their accumulator
+        const int nacc = L::kSharedAcc ? 1 : (nkb < NI ? nkb : NI);  // issuers without a k-block never wrote their accumulator
         for (int c0 = 0; c0 < COLS; c0 += CH) {
           float sum[CH];
 #pragma unroll
