@@ -109,29 +109,44 @@ class Sampler:
 
     def _sample_cuda(self, logits: torch.Tensor, rest: list) -> list[int]:
         """Rows through the histogram-select kernel (csrc/sampling.cu); rows it declines (a histogram bin too crowded, a pick in
-        the far tail) go through the sorting path."""
+        the far tail) go through the sorting path. The per-row parameters travel as one pinned ``[6, n]`` float tensor (one
+        host-to-device copy per step) and the picks come back with one read."""
         dev = logits.device
-        sub = logits.index_select(0, torch.tensor([r[0] for r in rest], device=dev)) if len(rest) != logits.shape[0] else logits
-        temps = torch.tensor([r[1] for r in rest], dtype=torch.float32)
-        args = (
-            (1.0 / temps).to(dev),
-            torch.tensor([r[2] for r in rest], dtype=torch.int64, device=dev),
-            torch.tensor([r[3] for r in rest], dtype=torch.float32, device=dev),
-            torch.tensor([r[4] for r in rest], dtype=torch.uint8, device=dev),
-            torch.tensor([r[5] for r in rest], dtype=torch.float32, device=dev),
-        )
-        tok, ok = ops.require_ext().sample_rows(sub.contiguous() if sub.stride(1) != 1 else sub, *args)
+        n = len(rest)
+        host = self._staging(n)
+        host[0] = torch.tensor([r[0] for r in rest], dtype=torch.float32)
+        host[1] = 1.0 / torch.tensor([r[1] for r in rest], dtype=torch.float32)
+        host[2] = torch.tensor([min(r[2], 1 << 24) for r in rest], dtype=torch.float32)  # limits beyond 2^24 mean "the whole vocabulary"
+        host[3] = torch.tensor([r[3] for r in rest], dtype=torch.float32)
+        host[4] = torch.tensor([1.0 if r[4] else 0.0 for r in rest], dtype=torch.float32)
+        host[5] = torch.tensor([r[5] for r in rest], dtype=torch.float32)
+        packed = host.to(dev, non_blocking=True)
+        res = ops.require_ext().sample_rows_packed(logits if logits.stride(1) == 1 else logits.contiguous(), packed).tolist()
         ops._count()
-        tok_l, ok_l = tok.tolist(), ok.tolist()
+        tok_l, ok_l = res
         bad = [i for i, o in enumerate(ok_l) if not o]
-        self.stats["kernel_rows"] += len(rest) - len(bad)
+        self.stats["kernel_rows"] += n - len(bad)
         self.stats["fallback_rows"] += len(bad)
         if bad:
             bi = torch.tensor(bad, device=dev)
-            fb = sample_top_k_top_p_batch(sub.index_select(0, bi), temps[bad].to(dev), args[1][bi], args[2][bi], args[3][bi].bool(), args[4][bi]).tolist()
+            sub = logits if n == logits.shape[0] else logits.index_select(0, packed[0].to(torch.int64))
+            fb = sample_top_k_top_p_batch(sub.index_select(0, bi), 1.0 / packed[1][bi], packed[2][bi].to(torch.int64), packed[3][bi],
+                                          packed[4][bi] > 0, packed[5][bi]).tolist()
             for i, t in zip(bad, fb):
                 tok_l[i] = t
-        return tok_l
+        return [int(t) for t in tok_l]
+
+    def _staging(self, n: int) -> torch.Tensor:
+        """Pinned host staging for the packed sampling parameters (two buffers in turn: the copy of the previous step may still be in flight)."""
+        bufs = self.__dict__.setdefault("_stage_bufs", {})
+        turn = self.__dict__.get("_stage_turn", 0) ^ 1
+        self.__dict__["_stage_turn"] = turn
+        key = (n, turn)
+        if key not in bufs:
+            if len(bufs) > 64:
+                bufs.clear()
+            bufs[key] = torch.empty((6, n), dtype=torch.float32, pin_memory=torch.cuda.is_available())
+        return bufs[key]
 
     def sample(self, logits: torch.Tensor, states: list[SamplingState]) -> tuple[list[int], list[Optional[TokenLogProb]]]:
         B, V = logits.shape

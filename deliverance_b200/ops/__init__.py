@@ -37,6 +37,8 @@ def ext():
         _ext_checked = True
         if _ext is not None and os.environ.get("DLV_GEMM_PDL", "1") == "0":
             _ext.gemm_pdl(False)
+        if _ext is not None and os.environ.get("DLV_BOUNDS_CHECK", "0") == "1":
+            _ext.set_bounds_check(True)
     return _ext
 
 
@@ -68,6 +70,24 @@ def check_status(device: Optional[int] = None) -> None:
     if code:
         names = {1: "an mbarrier wait ran out of time", 2: "a peer-flag wait ran out of time", 3: "bad kernel arguments"}
         raise RuntimeError(f"deliverance_b200 kernel status {code}: {names.get(code, 'unknown')}")
+
+
+def set_bounds_check(on: bool = True) -> None:
+    """Guard areas around every output the extension's kernels write (4 KB of a byte pattern on both sides); ``check_guards``
+    verifies them. Also switched on by ``DLV_BOUNDS_CHECK=1`` in the environment. A debugging mode: outputs cost an extra fill."""
+    e = ext()
+    if e is not None:
+        e.set_bounds_check(bool(on))
+
+
+def check_guards() -> None:
+    """Raise if a kernel wrote outside one of the outputs allocated since the last call (bounds checking must be on)."""
+    e = ext()
+    if e is None or not torch.cuda.is_available():
+        return
+    bad = e.check_guards()
+    if bad:
+        raise RuntimeError("deliverance_b200: a kernel wrote outside " + "; ".join(bad))
 
 
 # ---------------------------------------------------------------------------------------------------------- linear

@@ -37,6 +37,65 @@ int act_code(const std::string& a) {
   TORCH_CHECK(false, "unknown activation ", a);
 }
 
+// ---- output allocation with optional guard areas ---------------------------------------------------------------------
+// Bounds checking (set_bounds_check(true), or DLV_BOUNDS_CHECK=1 in the environment when the module loads): every tensor a
+// kernel of this extension writes its result into is cut out of a larger buffer, between two 4 KB guard areas filled with a byte
+// pattern. check_guards() compares all guard areas written since the last call with the pattern and reports the outputs
+// whose neighbourhood a kernel overwrote. Off (the default), an output is a plain torch::empty.
+constexpr int64_t kGuardBytes = 4096;
+constexpr uint8_t kGuardByte = 0xA5;
+struct GuardRecord {
+  Tensor buf;
+  int64_t body_bytes;
+  std::string what;
+};
+bool g_bounds_check = false;
+std::vector<GuardRecord> g_guards;
+
+Tensor new_out(c10::IntArrayRef sizes, const torch::TensorOptions& opt) {
+  if (!g_bounds_check) return torch::empty(sizes, opt);
+  const std::vector<int64_t> shape(sizes.begin(), sizes.end());  // (the caller's list is a temporary)
+  const at::ScalarType dt = c10::typeMetaToScalarType(opt.dtype());
+  int64_t n = 1;
+  for (int64_t v : shape) n *= v;
+  const int64_t body = n * static_cast<int64_t>(c10::elementSize(dt));
+  if (body == 0) return torch::empty(shape, opt);
+  const int64_t padded = (body + 255) / 256 * 256;
+  const std::vector<int64_t> total{kGuardBytes + padded + kGuardBytes};
+  Tensor buf = torch::empty(total, opt.dtype(at::kByte));
+  buf.fill_(static_cast<int64_t>(kGuardByte));
+  Tensor out = buf.narrow(0, kGuardBytes, body).view(dt).view(shape);
+  std::string what = "output " + std::to_string(g_guards.size()) + " [";
+  for (size_t i = 0; i < shape.size(); ++i) what += (i ? ", " : "") + std::to_string(shape[i]);
+  what += std::string("] ") + c10::toString(dt);
+  GuardRecord rec;
+  rec.buf = buf;
+  rec.body_bytes = body;
+  rec.what = what;
+  g_guards.push_back(std::move(rec));
+  return out;
+}
+void set_bounds_check(bool on) {
+  g_bounds_check = on;
+  if (!on) g_guards.clear();
+}
+// Names of the outputs whose guard areas no longer hold the pattern (the records are dropped either way).
+std::vector<std::string> check_guards() {
+  std::vector<std::string> bad;
+  for (auto& r : g_guards) {
+    const int64_t total = r.buf.numel();
+    Tensor lo = r.buf.narrow(0, 0, kGuardBytes), hi = r.buf.narrow(0, kGuardBytes + r.body_bytes, total - kGuardBytes - r.body_bytes);
+    if (lo.ne(kGuardByte).any().item<bool>() || hi.ne(kGuardByte).any().item<bool>()) bad.push_back(r.what);
+  }
+  g_guards.clear();
+  return bad;
+}
+// Test hook: overwrite one guard byte of the newest output from the host side, to show that check_guards() sees it.
+void poke_last_guard() {
+  TORCH_CHECK(!g_guards.empty(), "no guarded output yet");
+  g_guards.back().buf.narrow(0, kGuardBytes + g_guards.back().body_bytes + 7, 1).fill_(0);
+}
+
 // ---- per-device scratch for split-K partials, tile counters and the kernel status word ---------------------------
 struct DeviceScratch {
   Tensor ws;        // fp32
@@ -194,7 +253,7 @@ class GemmWeight {
       TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.size(0) == M && out.size(1) == desc_.N && out.stride(1) == 1, "bad out shape");
       TORCH_CHECK(out.scalar_type() == (out_f32 ? at::kFloat : at::kBFloat16), "bad out dtype");
     } else {
-      out = torch::empty({M, desc_.N}, x.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+      out = new_out({M, desc_.N}, x.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
     }
     const float* bptr = nullptr;
     if (bias.has_value()) {
@@ -224,7 +283,7 @@ class GemmWeight {
     TORCH_CHECK(desc_.N % 128 == 0, "gate|up rows must be a multiple of 128");
     c10::cuda::CUDAGuard guard(x.device());
     const int M = static_cast<int>(x.size(0));
-    Tensor out = torch::empty({M, desc_.N / 2}, x.options());
+    Tensor out = new_out({M, desc_.N / 2}, x.options());
     if (M == 0) return out;
     DeviceScratch& s = scratch_for(x.device().index());
     dlv::gemm_tc_run_act(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), out.data_ptr(), static_cast<int>(out.stride(0)), static_cast<int>(act),
@@ -242,7 +301,7 @@ class GemmWeight {
     const int64_t per = desc_.is_q4 ? ((n_per_expert + 127) / 128) * 128 : n_per_expert;
     TORCH_CHECK(n_per_expert > 0 && desc_.N % per == 0, "stacked weight rows are not a multiple of the per-expert rows");
     c10::cuda::CUDAGuard guard(xs.device());
-    Tensor out = out_opt.has_value() ? out_opt.value() : torch::empty({xs.size(0), n_per_expert}, xs.options());
+    Tensor out = out_opt.has_value() ? out_opt.value() : new_out({xs.size(0), n_per_expert}, xs.options());
     TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == xs.size(0) && out.size(1) == n_per_expert && out.stride(1) == 1, "bad out");
     if (bn <= 8) {  // decode-size groups: CUDA-core GEMV, one warp per weight row and work item
       dlv::gemv_grouped_run(&desc_, static_cast<int>(n_per_expert), xs.data_ptr(), static_cast<int>(xs.stride(0)), out.data_ptr(),
@@ -307,7 +366,7 @@ class GemmWeight {
       bptr = bias.value().data_ptr<float>();
     }
     c10::cuda::CUDAGuard guard(x.device());
-    Tensor q = torch::empty({M, H * 128}, x.options());
+    Tensor q = new_out({M, H * 128}, x.options());
     if (M == 0) return q;
     DeviceScratch& s = scratch_for(x.device().index());
     dlv::gemm_tc_run_qkv(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), q.data_ptr(), static_cast<int>(q.stride(0)), bptr, &a,
@@ -324,7 +383,7 @@ class GemmWeight {
     TORCH_CHECK(n_per_expert > 0 && n_per_expert % 128 == 0 && desc_.N % n_per_expert == 0, "gate|up rows per expert must be a multiple of 128");
     TORCH_CHECK(bn >= 16, "the fused activation needs the tensor-core tiles (token tile >= 16)");
     c10::cuda::CUDAGuard guard(xs.device());
-    Tensor out = torch::empty({xs.size(0), n_per_expert / 2}, xs.options());
+    Tensor out = new_out({xs.size(0), n_per_expert / 2}, xs.options());
     DeviceScratch& s = scratch_for(xs.device().index());
     dlv::gemm_tc_run_grouped_act(&desc_, static_cast<int>(n_per_expert), xs.data_ptr(), static_cast<int>(xs.size(0)), static_cast<int>(xs.stride(0)),
                                  out.data_ptr(), static_cast<int>(out.stride(0)), items.data_ptr<int>(), static_cast<int>(items.size(0)),
@@ -453,7 +512,7 @@ Tensor rmsnorm(const Tensor& x, const Tensor& w, double eps, double offset) {
   const int H = static_cast<int>(x.size(-1));
   TORCH_CHECK(H % 8 == 0 && w.numel() == H, "hidden size must be a multiple of 8");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor y = torch::empty_like(x);
+  Tensor y = new_out(x.sizes(), x.options());
   dlv::launch_rmsnorm(x.data_ptr(), nullptr, w.data_ptr(), y.data_ptr(), static_cast<int>(x.numel() / H), H, static_cast<float>(eps),
                       static_cast<float>(offset), 1.f, cur_stream());
   check_last_error("rmsnorm");
@@ -466,7 +525,7 @@ Tensor add_rmsnorm(const Tensor& x, Tensor& residual, const Tensor& w, double ep
   const int H = static_cast<int>(x.size(-1));
   TORCH_CHECK(H % 8 == 0 && w.numel() == H && residual.sizes() == x.sizes(), "shape mismatch");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor y = torch::empty_like(x);
+  Tensor y = new_out(x.sizes(), x.options());
   dlv::launch_rmsnorm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), y.data_ptr(), static_cast<int>(x.numel() / H), H,
                       static_cast<float>(eps), static_cast<float>(offset), static_cast<float>(res_mult), cur_stream());
   check_last_error("add_rmsnorm");
@@ -483,7 +542,7 @@ Tensor layernorm(const Tensor& x, const Tensor& w, c10::optional<Tensor> b, doub
     bp = b.value().data_ptr();
   }
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor y = torch::empty_like(x);
+  Tensor y = new_out(x.sizes(), x.options());
   dlv::launch_layernorm(x.data_ptr(), w.data_ptr(), bp, y.data_ptr(), static_cast<int>(x.numel() / H), H, static_cast<float>(eps), cur_stream());
   check_last_error("layernorm");
   return y;
@@ -493,7 +552,7 @@ Tensor act_mul(const Tensor& gate_up, const std::string& act) {
   TORCH_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 16 == 0, "gate|up width must be a multiple of 16");
   const int I = static_cast<int>(gate_up.size(1) / 2);
   c10::cuda::CUDAGuard guard(gate_up.device());
-  Tensor out = torch::empty({gate_up.size(0), I}, gate_up.options());
+  Tensor out = new_out({gate_up.size(0), I}, gate_up.options());
   dlv::launch_act_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.size(0), I, act_code(act), cur_stream());
   check_last_error("act_mul");
   return out;
@@ -501,7 +560,7 @@ Tensor act_mul(const Tensor& gate_up, const std::string& act) {
 Tensor activation(const Tensor& x, const std::string& act) {
   check_bf16(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor out = torch::empty_like(x);
+  Tensor out = new_out(x.sizes(), x.options());
   dlv::launch_act(x.data_ptr(), out.data_ptr(), x.numel(), act_code(act), cur_stream());
   check_last_error("activation");
   return out;
@@ -534,7 +593,7 @@ Tensor embedding(const Tensor& table, const Tensor& ids, double scale, c10::opti
     }
   }
   c10::cuda::CUDAGuard guard(table.device());
-  Tensor out = torch::empty({ids.numel(), H}, table.options());
+  Tensor out = new_out({ids.numel(), H}, table.options());
   dlv::launch_embedding(table.data_ptr(), ids.data_ptr<int>(), pt, pp, tt, tp, out.data_ptr(), static_cast<int>(ids.numel()), H,
                         static_cast<int>(table.size(0)), static_cast<float>(scale), cur_stream());
   check_last_error("embedding");
@@ -610,13 +669,13 @@ Tensor decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_
   TORCH_CHECK(block_tables.dim() == 2 && block_tables.size(0) >= B && ctx_lens.numel() >= B, "bad table shapes");
   TORCH_CHECK((reinterpret_cast<uintptr_t>(q.data_ptr()) & 3) == 0, "q misaligned");
   c10::cuda::CUDAGuard guard(q.device());
-  Tensor out = torch::empty({B, H * D}, q.options());
+  Tensor out = new_out({B, H * D}, q.options());
   if (splits < 1) splits = 1;
   Tensor po, pml;
   float *pop = nullptr, *pmlp = nullptr;
   if (splits > 1) {
-    po = torch::empty({B, H, splits, D}, q.options().dtype(at::kFloat));
-    pml = torch::empty({B, H, splits, 2}, q.options().dtype(at::kFloat));
+    po = new_out({B, H, splits, D}, q.options().dtype(at::kFloat));
+    pml = new_out({B, H, splits, 2}, q.options().dtype(at::kFloat));
     pop = po.data_ptr<float>();
     pmlp = pml.data_ptr<float>();
   }
@@ -645,7 +704,7 @@ Tensor prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v
   TORCH_CHECK(q.size(1) == H * D && H % KV == 0 && page % 32 == 0, "shape mismatch");
   TORCH_CHECK(tile_seq.numel() == tile_q0.numel(), "tile arrays differ in length");
   c10::cuda::CUDAGuard guard(q.device());
-  Tensor out = torch::empty({T, H * D}, q.options());
+  Tensor out = new_out({T, H * D}, q.options());
   int rc = dlv::launch_prefill_attention(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(),
                                          static_cast<int>(block_tables.stride(0)), q_start.data_ptr<int>(), q_len.data_ptr<int>(),
                                          ctx_lens.data_ptr<int>(), tile_seq.data_ptr<int>(), tile_q0.data_ptr<int>(),
@@ -675,7 +734,7 @@ Tensor prefill_attention_tc(const Tensor& q, const Tensor& k_cache, const Tensor
   TORCH_CHECK((page == 32 || page == 64 || page == 128) && (D == 64 || D == 128 || D == 256), "page size 32 / 64 / 128 and head_dim 64 / 128 / 256");
   TORCH_CHECK(tile_seq.numel() == tile_q0.numel(), "tile arrays differ in length");
   c10::cuda::CUDAGuard guard(q.device());
-  Tensor out = torch::empty({T, H * D}, q.options());
+  Tensor out = new_out({T, H * D}, q.options());
   DeviceScratch& s = scratch_for(q.device().index());
   int rc = dlv::launch_prefill_attention_tc(q.data_ptr(), q.stride(0), T, k_cache.data_ptr(), v_cache.data_ptr(), k_cache.size(0), block_tables.data_ptr<int>(),
                                             static_cast<int>(block_tables.stride(0)), q_start.data_ptr<int>(), q_len.data_ptr<int>(), ctx_lens.data_ptr<int>(),
@@ -701,8 +760,8 @@ std::vector<Tensor> argmax(const Tensor& logits, c10::optional<Tensor> mask, dou
     mld = static_cast<int>(m.size(1));
   }
   c10::cuda::CUDAGuard guard(logits.device());
-  Tensor idx = torch::empty({B}, logits.options().dtype(at::kLong));
-  Tensor val = torch::empty({B}, logits.options());
+  Tensor idx = new_out({B}, logits.options().dtype(at::kLong));
+  Tensor val = new_out({B}, logits.options());
   dlv::launch_argmax(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, mp, mld, static_cast<float>(softcap),
                      static_cast<float>(inv_scale), reinterpret_cast<long long*>(idx.data_ptr<int64_t>()), val.data_ptr<float>(), cur_stream());
   check_last_error("argmax");
@@ -729,6 +788,19 @@ std::vector<Tensor> sample_rows(const Tensor& logits, const Tensor& inv_temp, co
   check_last_error("sample_rows");
   return {tok, ok};
 }
+// The same with every per-row parameter in ONE float32 tensor [6, n] (one host-to-device copy per step instead of six): rows =
+// (row of `logits`, 1 / temperature, candidate limit, top_p, uniform flag, uniform random number). Returns int64 [2, n]: the
+// token ids and the handled flags (one device-to-host read).
+Tensor sample_rows_packed(const Tensor& logits, const Tensor& packed) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
+  check_cuda(packed, "packed sampling parameters");
+  TORCH_CHECK(packed.scalar_type() == at::kFloat && packed.dim() == 2 && packed.size(0) == 6, "packed sampling parameters must be float32 [6, n]");
+  const int64_t n = packed.size(1);
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor sub = n == logits.size(0) ? logits : logits.index_select(0, packed[0].to(at::kLong));
+  std::vector<Tensor> r = sample_rows(sub, packed[1].contiguous(), packed[2].to(at::kLong), packed[3].contiguous(), packed[4].to(at::kByte), packed[5].contiguous());
+  return torch::stack({r[0], r[1].to(at::kLong)}, 0);
+}
 // Exclude-top-choice picks of every row in one launch: int64 [B], -1 where XTC does not apply (not armed, or no token above the threshold).
 Tensor xtc_rows(const Tensor& logits, const Tensor& inv_temp, const Tensor& threshold, const Tensor& fire, const Tensor& special) {
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "logits must be fp32 [B, V]");
@@ -741,7 +813,7 @@ Tensor xtc_rows(const Tensor& logits, const Tensor& inv_temp, const Tensor& thre
   TORCH_CHECK(inv_temp.scalar_type() == at::kFloat && threshold.scalar_type() == at::kFloat && fire.scalar_type() == at::kByte && special.scalar_type() == at::kInt,
               "xtc parameter dtypes");
   c10::cuda::CUDAGuard guard(logits.device());
-  Tensor tok = torch::empty({B}, logits.options().dtype(at::kLong));
+  Tensor tok = new_out({B}, logits.options().dtype(at::kLong));
   dlv::launch_xtc(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, inv_temp.data_ptr<float>(), threshold.data_ptr<float>(),
                   fire.data_ptr<uint8_t>(), special.data_ptr<int>(), static_cast<int>(special.numel()),
                   reinterpret_cast<long long*>(tok.data_ptr<int64_t>()), cur_stream());
@@ -756,9 +828,9 @@ std::vector<Tensor> logprob_rows(const Tensor& logits, const Tensor& chosen, int
   TORCH_CHECK(chosen.scalar_type() == at::kLong && chosen.numel() == B && top_n >= 0 && top_n <= 64 && top_n <= V, "chosen must be int64 [B]; top_n in 0..64");
   TORCH_CHECK(chosen.min().item<int64_t>() >= 0 && chosen.max().item<int64_t>() < V, "chosen token outside the vocabulary");
   c10::cuda::CUDAGuard guard(logits.device());
-  Tensor lp = torch::empty({B}, logits.options());
-  Tensor idx = torch::empty({B, top_n}, logits.options().dtype(at::kLong));
-  Tensor val = torch::empty({B, top_n}, logits.options());
+  Tensor lp = new_out({B}, logits.options());
+  Tensor idx = new_out({B, top_n}, logits.options().dtype(at::kLong));
+  Tensor val = new_out({B, top_n}, logits.options());
   dlv::launch_logprobs(logits.data_ptr<float>(), static_cast<int>(logits.stride(0)), B, V, reinterpret_cast<const long long*>(chosen.data_ptr<int64_t>()),
                        static_cast<int>(top_n), lp.data_ptr<float>(), reinterpret_cast<long long*>(idx.data_ptr<int64_t>()), val.data_ptr<float>(), cur_stream());
   check_last_error("logprob_rows");
@@ -823,7 +895,7 @@ class ExpertA2A {
     c10::cuda::CUDAGuard guard(like.device());
     auto io = torch::TensorOptions().device(like.device()).dtype(torch::kInt32);
     Tensor local_offsets = torch::zeros({p_.ne + 1}, io), seg = torch::zeros({static_cast<long>(p_.ne) * p_.size, 4}, io);
-    Tensor xs = torch::empty({max_rows, H_}, torch::TensorOptions().device(like.device()).dtype(torch::kBFloat16));
+    Tensor xs = new_out({max_rows, H_}, torch::TensorOptions().device(like.device()).dtype(torch::kBFloat16));
     dlv::A2AParams p = with_status(like.device().index());
     dlv::launch_a2a_receive(&p, epoch_, local_offsets.data_ptr<int>(), seg.data_ptr<int>(), xs.data_ptr(), static_cast<int>(max_rows), H_, cur_stream());
     check_last_error("a2a receive");
@@ -876,7 +948,7 @@ Tensor pool_rows(const Tensor& h, const Tensor& start, const Tensor& len, int64_
   TORCH_CHECK(h.dim() == 2 && start.scalar_type() == at::kInt && len.scalar_type() == at::kInt && start.numel() == len.numel() && mode >= 0 && mode <= 6, "bad pooling arguments");
   TORCH_CHECK((start + len).max().item<int>() <= h.size(0) && start.min().item<int>() >= 0 && len.min().item<int>() >= 0, "segments outside the hidden states");
   c10::cuda::CUDAGuard guard(h.device());
-  Tensor out = torch::empty({start.numel(), h.size(1)}, h.options().dtype(at::kFloat));
+  Tensor out = new_out({start.numel(), h.size(1)}, h.options().dtype(at::kFloat));
   dlv::launch_pool(h.data_ptr(), static_cast<int>(h.size(1)), start.data_ptr<int>(), len.data_ptr<int>(), static_cast<int>(start.numel()), static_cast<int>(mode),
                    normalize ? 1 : 0, out.data_ptr<float>(), cur_stream());
   check_last_error("pool_rows");
@@ -886,7 +958,7 @@ Tensor softmax_rows(const Tensor& x) {
   check_cuda(x, "x");
   TORCH_CHECK(x.scalar_type() == at::kFloat && x.dim() == 2, "x must be fp32 [rows, C]");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor y = torch::empty_like(x);
+  Tensor y = new_out(x.sizes(), x.options());
   dlv::launch_softmax_rows(x.data_ptr<float>(), y.data_ptr<float>(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), cur_stream());
   check_last_error("softmax_rows");
   return y;
@@ -901,8 +973,8 @@ std::vector<Tensor> tq_encode(const Tensor& x, const Tensor& signs, const Tensor
   TORCH_CHECK(pdim >= 32 && pdim <= 1024 && (pdim & (pdim - 1)) == 0 && dim <= pdim && bits >= 1 && bits <= 8, "pdim must be a power of two in 32..1024");
   TORCH_CHECK(signs.scalar_type() == at::kFloat && edges.scalar_type() == at::kFloat && edges.numel() == (1 << bits) - 1, "signs [pdim] / edges [2^bits - 1] fp32");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor codes = torch::empty({x.size(0), pdim * bits / 8}, x.options().dtype(at::kByte));
-  Tensor norms = torch::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  Tensor codes = new_out({x.size(0), pdim * bits / 8}, x.options().dtype(at::kByte));
+  Tensor norms = new_out({x.size(0)}, x.options().dtype(at::kFloat));
   dlv::launch_tq_encode(x.data_ptr(), x.scalar_type() == at::kFloat ? 0 : 1, x.size(0), dim, pdim, static_cast<int>(bits), signs.data_ptr<float>(),
                         edges.data_ptr<float>(), codes.data_ptr<uint8_t>(), norms.data_ptr<float>(), cur_stream());
   check_last_error("tq_encode");
@@ -919,7 +991,7 @@ Tensor tq_decode(const Tensor& codes, const Tensor& norms, const Tensor& signs, 
   TORCH_CHECK(pdim >= 32 && pdim <= 1024 && (pdim & (pdim - 1)) == 0 && dim <= pdim && bits >= 1 && bits <= 8 && centroids.numel() == (1 << bits) &&
                   centroids.scalar_type() == at::kFloat && signs.scalar_type() == at::kFloat, "bad codec tables");
   c10::cuda::CUDAGuard guard(codes.device());
-  Tensor out = torch::empty({codes.size(0), dim}, codes.options().dtype(to_bf16 ? at::kBFloat16 : at::kFloat));
+  Tensor out = new_out({codes.size(0), dim}, codes.options().dtype(to_bf16 ? at::kBFloat16 : at::kFloat));
   dlv::launch_tq_decode(codes.data_ptr<uint8_t>(), norms.data_ptr<float>(), codes.size(0), static_cast<int>(dim), pdim, static_cast<int>(bits), signs.data_ptr<float>(),
                         centroids.data_ptr<float>(), out.data_ptr(), to_bf16 ? 1 : 0, cur_stream());
   check_last_error("tq_decode");
@@ -945,8 +1017,8 @@ std::vector<Tensor> moe_route(const Tensor& logits, int64_t k, int64_t mode, boo
   TORCH_CHECK(k >= 1 && k <= 16 && k <= E && E <= 1024, "unsupported top-k / expert count");
   c10::cuda::CUDAGuard guard(logits.device());
   auto io = logits.options().dtype(at::kInt);
-  Tensor w = torch::empty({T, k}, logits.options()), idx = torch::empty({T, k}, io), counts = torch::empty({E}, io);
-  Tensor offsets = torch::empty({E + 1}, io), perm = torch::empty({T * k}, io), pos = torch::empty({T * k}, io);
+  Tensor w = new_out({T, k}, logits.options()), idx = new_out({T, k}, io), counts = new_out({E}, io);
+  Tensor offsets = new_out({E + 1}, io), perm = new_out({T * k}, io), pos = new_out({T * k}, io);
   dlv::launch_moe_route(logits.data_ptr<float>(), T, E, static_cast<int>(k), static_cast<int>(mode), renorm ? 1 : 0, w.data_ptr<float>(),
                         idx.data_ptr<int>(), counts.data_ptr<int>(), offsets.data_ptr<int>(), perm.data_ptr<int>(), pos.data_ptr<int>(), cur_stream());
   check_last_error("moe_route");
@@ -956,7 +1028,7 @@ Tensor moe_items(const Tensor& offsets, int64_t e0, int64_t ne, int64_t bn, int6
   check_cuda(offsets, "offsets");
   TORCH_CHECK(offsets.scalar_type() == at::kInt && e0 >= 0 && ne >= 1 && ne <= 1024 && e0 + ne < offsets.numel() + 0 && bn >= 1 && max_items >= 1, "bad work-list arguments");
   c10::cuda::CUDAGuard guard(offsets.device());
-  Tensor items = torch::empty({max_items, 4}, offsets.options());
+  Tensor items = new_out({max_items, 4}, offsets.options());
   dlv::launch_moe_items(offsets.data_ptr<int>(), static_cast<int>(e0), static_cast<int>(ne), static_cast<int>(bn), static_cast<int>(max_items), items.data_ptr<int>(), cur_stream());
   check_last_error("moe_items");
   return items;
@@ -967,7 +1039,7 @@ Tensor moe_gather(const Tensor& x, const Tensor& perm, int64_t k, c10::optional<
   check_cuda(perm, "perm");
   TORCH_CHECK(perm.scalar_type() == at::kInt && x.dim() == 2 && x.size(1) % 8 == 0 && perm.numel() == x.size(0) * k, "bad gather arguments");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor xs = torch::empty({perm.numel(), x.size(1)}, x.options());
+  Tensor xs = new_out({perm.numel(), x.size(1)}, x.options());
   const int* off = nullptr;
   if (offsets.has_value()) {
     TORCH_CHECK(offsets.value().is_cuda() && offsets.value().scalar_type() == at::kInt && e0 + ne < offsets.value().numel(), "bad expert range");
@@ -983,7 +1055,7 @@ Tensor moe_combine(const Tensor& ys, const Tensor& pos, const Tensor& w, int64_t
   check_cuda(w, "w");
   TORCH_CHECK(pos.scalar_type() == at::kInt && w.scalar_type() == at::kFloat && pos.numel() == T * k && w.numel() == T * k && ys.size(0) == T * k && ys.size(1) % 8 == 0, "bad combine arguments");
   c10::cuda::CUDAGuard guard(ys.device());
-  Tensor out = torch::empty({T, ys.size(1)}, ys.options());
+  Tensor out = new_out({T, ys.size(1)}, ys.options());
   const int* off = nullptr;
   if (offsets.has_value()) {
     TORCH_CHECK(offsets.value().is_cuda() && offsets.value().scalar_type() == at::kInt && e0 + ne < offsets.value().numel(), "bad expert range");
@@ -1248,9 +1320,9 @@ Tensor mamba2_forward(const Tensor& zx, const Tensor& conv_w, c10::optional<Tens
   const int num_seqs = static_cast<int>(q_len.numel()), n_chunks = static_cast<int>(chunk_seq.numel());
   c10::cuda::CUDAGuard guard(zx.device());
   auto fo = zx.options().dtype(at::kFloat);
-  Tensor xbc = torch::empty({T, conv_dim}, fo), ybuf = torch::empty({T, I}, fo);
-  Tensor cstate = torch::empty({std::max(1, n_chunks), H, d_head, S}, fo), cdecay = torch::empty({std::max(1, n_chunks), H}, fo);
-  Tensor out = torch::empty({T, I}, zx.options());
+  Tensor xbc = new_out({T, conv_dim}, fo), ybuf = new_out({T, I}, fo);
+  Tensor cstate = new_out({std::max(1, n_chunks), H, d_head, S}, fo), cdecay = new_out({std::max(1, n_chunks), H}, fo);
+  Tensor out = new_out({T, I}, zx.options());
   const float* cb = conv_b.has_value() ? conv_b.value().data_ptr<float>() : nullptr;
   int rc = dlv::launch_mamba2(zx.data_ptr(), static_cast<int>(zx.stride(0)), T, num_seqs, I, conv_dim, K, static_cast<int>(H), static_cast<int>(d_head),
                               static_cast<int>(G), static_cast<int>(S), conv_w.data_ptr<float>(), cb, dt_bias.data_ptr<float>(), A_log.data_ptr<float>(),
@@ -1276,8 +1348,8 @@ std::vector<Tensor> q4_quantize(const Tensor& w) {
   auto pshape = shape, sshape = shape;
   pshape.back() = shape.back() / 2;
   sshape.back() = shape.back() / 32;
-  Tensor packed = torch::empty(pshape, w.options().dtype(at::kByte));
-  Tensor scales = torch::empty(sshape, w.options().dtype(at::kFloat));
+  Tensor packed = new_out(pshape, w.options().dtype(at::kByte));
+  Tensor scales = new_out(sshape, w.options().dtype(at::kFloat));
   dlv::launch_q4_quantize(w.data_ptr(), code, w.numel() / 32, packed.data_ptr<uint8_t>(), scales.data_ptr<float>(), cur_stream());
   check_last_error("q4_quantize");
   return {packed, scales};
@@ -1290,7 +1362,7 @@ Tensor q4_dequantize(const Tensor& packed, const Tensor& scales, bool to_bf16) {
   c10::cuda::CUDAGuard guard(packed.device());
   auto shape = packed.sizes().vec();
   shape.back() *= 2;
-  Tensor out = torch::empty(shape, packed.options().dtype(to_bf16 ? at::kBFloat16 : at::kFloat));
+  Tensor out = new_out(shape, packed.options().dtype(to_bf16 ? at::kBFloat16 : at::kFloat));
   dlv::launch_q4_dequantize(packed.data_ptr<uint8_t>(), scales.data_ptr<float>(), scales.numel(), out.data_ptr(), to_bf16 ? 1 : 0, cur_stream());
   check_last_error("q4_dequantize");
   return out;
@@ -1356,8 +1428,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("prefill_attention", &prefill_attention);
   m.def("prefill_attention_tc", &prefill_attention_tc);
   m.def("prefill_tc_tile_rows", &dlv::prefill_attention_tc_tile_rows);
+  m.def("set_bounds_check", &set_bounds_check);
+  m.def("check_guards", &check_guards);
+  m.def("poke_last_guard", &poke_last_guard);
+  m.def("guarded_empty", [](std::vector<int64_t> sizes, const Tensor& like) { return new_out(sizes, like.options()); });
   m.def("argmax", &argmax, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("sample_rows", &sample_rows);
+  m.def("sample_rows_packed", &sample_rows_packed);
   m.def("xtc_rows", &xtc_rows);
   m.def("lora_delta", &lora_delta);
   m.def("pool_rows", &pool_rows);

@@ -224,3 +224,60 @@ def test_jq4_properties_hypothesis():
     pu, su = q4_quantize(torch.randn(128, 64, generator=g))
     mixed = ops.interleave_gate_up(Q4Tensor(pg, sg, (128, 64)), Q4Tensor(pu, su, (128, 64)))
     assert torch.equal(mixed.packed[64:128], pu[:64]) and torch.equal(mixed.scales[128:192], sg[64:128]) and mixed.shape == (256, 64)
+
+
+def _reference_simd():
+    """The reference's own C kernels, compiled from an unmodified copy: from ``DLV_REFERENCE_ROOT`` (a checkout of the reference) when
+    set, else from the copy the benchmark's reference arm installed under ``baseline/_ref``; None when neither is there or gcc is missing."""
+    import shutil
+    import subprocess
+    import tempfile
+
+    from deliverance_b200.bench import reference_arm as ra
+
+    if shutil.which("gcc") is None:
+        return None
+    root = os.environ.get("DLV_REFERENCE_ROOT")
+    try:
+        if root:
+            src = os.path.join(root, "native", "src", "main", "c", "simd")
+            if not os.path.exists(os.path.join(src, "vector_simd.c")):
+                return None
+            tmp = tempfile.mkdtemp(prefix="dlv_ref_simd_")
+            for f in ra.FILES:
+                shutil.copyfile(os.path.join(src, f), os.path.join(tmp, f))
+            return ra.load(tmp)
+        if not os.path.exists(os.path.join(ra.REF_DIR, "vector_simd.c")):
+            return None
+        return ra.load()
+    except (OSError, subprocess.CalledProcessError):
+        return None
+
+
+def test_jq4_blocks_against_the_reference_c_kernel():
+    """JQ4 packing pinned by an oracle this repo did not write: the reference's ``gemm_f32_q4`` (native/src/main/c/simd/vector_simd.c:1145,
+    scalar walk of the packed nibbles and block scales) multiplies the identity by weights packed with ``q4_quantize``; the product must
+    be the transpose of ``q4_dequantize`` to rounding."""
+    lib = _reference_simd()
+    if lib is None:
+        pytest.skip("no reference C sources (set DLV_REFERENCE_ROOT or install the benchmark's reference arm) or no gcc")
+    import numpy as np
+
+    g = torch.Generator().manual_seed(11)
+    n, k = 48, 256
+    w = torch.randn(n, k, generator=g) * 0.3
+    w[5, 32:64] = 0.0      # an all-zero block
+    w[7, 3] = -4.0         # the block maximum is negative
+    packed, scales = q4_quantize(w)
+    deq = q4_dequantize(packed, scales).numpy()
+    a = np.eye(k, dtype=np.float32)
+    p_np = np.ascontiguousarray(packed.numpy())
+    s_np = np.ascontiguousarray(scales.numpy().astype(np.float32))
+    r = np.zeros((k, n), dtype=np.float32)
+    lib.gemm_f32_q4(0, a.ctypes.data, 0, s_np.ctypes.data, p_np.ctypes.data, 0, r.ctypes.data, 0, k, 0, n, k, k, k // 2, k // 32, n)
+    assert np.abs(r.T - deq).max() <= 1e-6
+    # and a real product, against the dequantised weights in fp32
+    x = torch.randn(5, k, generator=g).numpy().astype(np.float32)
+    r2 = np.zeros((5, n), dtype=np.float32)
+    lib.gemm_f32_q4(0, x.ctypes.data, 0, s_np.ctypes.data, p_np.ctypes.data, 0, r2.ctypes.data, 0, 5, 0, n, k, k, k // 2, k // 32, n)
+    assert np.abs(r2 - x @ deq.T).max() <= 1e-4

@@ -524,3 +524,52 @@ def test_lora_pool_softmax_turboquant_kernels():
         back_dev = codec.decode(host, torch.float32, DEV).cpu()
         assert torch.allclose(back_dev, back_host, atol=1e-3, rtol=1e-3)
         assert _rel(codec.decode(dev_enc, torch.bfloat16, DEV).cpu(), rows) < (0.6 if bits <= 2 else 0.25)
+
+
+def test_outputs_stay_inside_their_guard_areas():
+    """Bounds checking: every output sits between two 4 KB guard areas; after a sweep over ragged shapes (token counts around the
+    tile sizes, ragged prefill, split decode attention, norms, fused activation) no guard byte has changed. The checker itself
+    is shown to see a changed byte (written from the host, no kernel misbehaves)."""
+    ext = ops.require_ext()
+    ops.set_bounds_check(True)
+    try:
+        g = torch.Generator().manual_seed(2)
+        N, K = 384, 256
+        w = torch.randn(N, K, generator=g) * 0.05
+        p, s = q4_quantize(w)
+        lw_q = LinearWeight(Q4Tensor(p, s, (N, K))).to(DEV)
+        lw_d = LinearWeight(w.to(torch.bfloat16).to(DEV))
+        for M in (1, 5, 17, 63, 65, 129, 257, 529):
+            x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+            ops.linear(x, lw_q)
+            ops.linear(x, lw_d)
+            ops.linear(x, lw_q, out_f32=True)
+            ops.linear_act(x, lw_q, "silu")
+            wn = torch.ones(K, dtype=torch.bfloat16, device=DEV)
+            ops.rmsnorm(x, wn, 1e-6)
+            ops.add_rmsnorm(x, x.clone(), wn, 1e-6)
+        D, H, KV = 128, 8, 2
+        seqs = [(70, 70), (5, 133), (257, 257)]
+        ctx = [c for _, c in seqs]
+        kc, vc, bt = _paged_setup(ctx, KV, D, seed=5)
+        ql = [q for q, _ in seqs]
+        T = sum(ql)
+        qs = [sum(ql[:i]) for i in range(len(ql))]
+        q = (torch.randn(T, H * D, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+        ti = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
+        for impl in ("tc", "mma"):
+            ops.prefill_attention(q, kc.to(DEV), vc.to(DEV), bt.to(DEV), ti(qs), ti(ql), ti(ctx), H, 0.09, 0.0, 0, True, impl=impl)
+        B = len(ctx)
+        qd = (torch.randn(B, H * D, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+        for splits in (1, 4):
+            ops.decode_attention(qd, kc.to(DEV), vc.to(DEV), bt.to(DEV), ti(ctx), H, 0.09, 0.0, 0, splits)
+        torch.cuda.synchronize()
+        ops.check_status()
+        ops.check_guards()
+        # the checker sees a changed guard byte
+        ops.rmsnorm(x, wn, 1e-6)
+        ext.poke_last_guard()
+        with pytest.raises(RuntimeError, match="wrote outside"):
+            ops.check_guards()
+    finally:
+        ops.set_bounds_check(False)

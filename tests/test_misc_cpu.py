@@ -884,3 +884,26 @@ def test_lz4_block_format_golden_and_roundtrip():
         c = e.lz4_compress(data)
         assert e.lz4_decompress(c, len(data)) == data
     assert len(e.lz4_compress(bytes(70000))) < 400
+
+
+def test_guard_area_checker_on_host_memory():
+    """The bounds-checking allocator of the extension: an output cut out between two guard areas, the checker passes while they are
+    intact and names the output once a guard byte has changed (the change is made from the host)."""
+    from deliverance_b200 import ops
+
+    e = ops.ext()
+    if e is None:
+        pytest.skip("extension not built")
+    e.set_bounds_check(True)
+    try:
+        like = torch.zeros(2, 8, dtype=torch.bfloat16)
+        o = e.guarded_empty([5, 16], like)
+        assert tuple(o.shape) == (5, 16) and o.dtype == torch.bfloat16
+        o.fill_(1.0)
+        assert e.check_guards() == []
+        e.guarded_empty([3, 7], like)
+        e.poke_last_guard()
+        bad = e.check_guards()
+        assert len(bad) == 1 and "[3, 7]" in bad[0]
+    finally:
+        e.set_bounds_check(False)
