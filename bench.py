@@ -297,9 +297,21 @@ def main() -> int:
     if bucket is not None:
         gr = eng._graphs[bucket]
         launches_per_step = gr["launches"] + 1
+        # The context grows here as it did in (1): step i runs at the positions of the end-to-end loop's step i (the last
+        # args.steps positions of every sequence, whose pages exist already), staged on the device before the clock starts.
+        gb = gr["batch"]
+        ps_ = eng.page_size
+        back = torch.arange(args.steps - 1, -1, -1, device=gb.positions.device, dtype=torch.int32).unsqueeze(1)
+        pos_all = (gb.positions.unsqueeze(0) - back).clamp_(min=0)                                  # [steps, bucket]
+        page_all = torch.gather(gb.block_tables.unsqueeze(0).expand(args.steps, -1, -1), 2, (pos_all // ps_).long().unsqueeze(2)).squeeze(2)
+        slots_all = page_all.long() * ps_ + (pos_all % ps_).long()
+        ctx_all = torch.where(gb.ctx_len.unsqueeze(0) > 1, pos_all + 1, torch.ones_like(pos_all))  # padded rows keep their context of 1
         sync_all()
         ev0.record()
-        for _ in range(args.steps):
+        for i in range(args.steps):
+            gb.positions.copy_(pos_all[i])
+            gb.slots.copy_(slots_all[i])
+            gb.ctx_len.copy_(ctx_all[i])
             gr["graph"].replay()
             eng._greedy(gr["logits"])
         ev1.record()
@@ -313,7 +325,7 @@ def main() -> int:
 
     extras = {"prefill_tok_s": B * P / (prefill_ms / 1e3), "prefill_ms": prefill_ms, "ttft_ms_p50": ttfts[len(ttfts) // 2],
               "ttft_ms_max": ttfts[-1], "model_build_s": build_s, "weight_bytes_per_rank": model.weight_bytes(),
-              "context_at_timing": P + args.warmup + args.steps}
+              "context_at_timing": f"{P + args.warmup + 1}..{P + args.warmup + args.steps} (grows by one token per timed step in both arms)"}
 
     # ---------------------------------------------------------------- extras: batch 8 and batch 1 decode on the same engine
     if not args.no_extras:

@@ -98,7 +98,10 @@ def client_main(a) -> int:
                 valid_json += 1
             except ValueError:
                 pass
-    out = {"streams": a.streams, "completed": len(ok), "errors": [s["error"] for s in stats if "error" in s][:3], "wall_s": wall,
+    # "completed" = streams that ended without an error; "streams_with_text" = those that delivered at least one non-empty content
+    # delta (a random-weight model mostly samples ids that the byte-level fallback tokenizer decodes to nothing, so the
+    # unguided half of the load often streams no text at all; the guided half always does)
+    out = {"streams": a.streams, "completed": sum(1 for s in stats if "error" not in s), "streams_with_text": len(ok), "errors": [s["error"] for s in stats if "error" in s][:3], "wall_s": wall,
            "ttft_p50_ms": ttft[len(ttft) // 2] * 1e3 if ttft else None, "ttft_p95_ms": ttft[int(len(ttft) * 0.95)] * 1e3 if ttft else None,
            "guided_streams": sum(1 for s in ok if s["guided"]), "guided_parse_as_json": valid_json}
     print("CLIENT " + json.dumps(out), flush=True)

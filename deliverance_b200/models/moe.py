@@ -106,10 +106,15 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
     else:
         if lw.fused_act_experts:
             raise RuntimeError("interleaved expert weights need the tensor-core grouped GEMM (token tile >= 16)")
-        with st("moe.gate_up"):
-            gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
-        with st("moe.activation_multiply"):
-            hmid = ops.act_mul(gu, act)
+        hmid = None
+        if bn <= 8:
+            with st("moe.gate_up"):  # a handful of rows per expert: grouped GEMV with the gated activation in its epilogue
+                hmid = gu_w.run_gemv_act(xs, items, act)
+        if hmid is None:
+            with st("moe.gate_up"):
+                gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
+            with st("moe.activation_multiply"):
+                hmid = ops.act_mul(gu, act)
     with st("moe.down"):
         ys = down_w.run(hmid, items, bn, max(1, min(8, down_w.K // 1024)) if small else 1)
     with st("moe.combine"):

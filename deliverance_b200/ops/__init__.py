@@ -499,6 +499,19 @@ class GroupedLinearWeight:
         _count()
         return self.handle.run_grouped(xs, items, self.N, bn, splits, out)
 
+    def run_gemv_act(self, xs: torch.Tensor, items: torch.Tensor, act: str) -> Optional[torch.Tensor]:
+        """Decode-size work items (at most 8 rows each): gate|up projection with ``act(gate) * up`` in the epilogue of the mma.sync
+        grouped GEMV; the experts' rows are in plain order (gate rows, then up rows). ``None`` when the shape or the activation is
+        outside that kernel (the caller then runs projection and activation as two steps)."""
+        kind = fused_act_kind(act)
+        if kind == 0 or not self.q4:
+            return None
+        out = self.handle.run_grouped_gemv_act(xs, items, self.N, kind)
+        if out is None:
+            return None
+        _count()
+        return out
+
     def run_act(self, xs: torch.Tensor, items: torch.Tensor, bn: int, splits: int, act: str) -> torch.Tensor:
         """Grouped gate|up projection with ``act(gate) * up`` in the epilogue; the experts' rows must be in the order of
         :func:`interleave_gate_up`. Returns ``[rows, N / 2]``."""

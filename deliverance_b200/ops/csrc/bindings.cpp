@@ -316,6 +316,23 @@ class GemmWeight {
     check_last_error("grouped gemm launch");
     return out;
   }
+  // Decode-size work items (at most 8 rows each) of a gated MLP: gate | up projection with act(gate) * up in the epilogue on the
+  // mma.sync grouped GEMV (plain row order: gate rows, then up rows). Returns [rows, n_per_expert / 2], or an undefined tensor when
+  // the shape is outside that kernel.
+  Tensor run_grouped_gemv_act(const Tensor& xs, const Tensor& items, int64_t n_per_expert, int64_t act) {
+    TORCH_CHECK(xs.is_cuda() && xs.scalar_type() == at::kBFloat16 && xs.dim() == 2 && xs.size(1) == desc_.K && xs.stride(1) == 1, "xs must be bf16 [rows, K]");
+    TORCH_CHECK(xs.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(xs.data_ptr()) & 15) == 0, "xs rows must be 16-byte aligned");
+    TORCH_CHECK(items.is_cuda() && items.scalar_type() == at::kInt && items.dim() == 2 && items.size(1) == 4 && items.is_contiguous(), "items must be int32 [n, 4]");
+    const int64_t per = desc_.is_q4 ? ((n_per_expert + 127) / 128) * 128 : n_per_expert;
+    TORCH_CHECK(n_per_expert > 0 && n_per_expert % 2 == 0 && desc_.N % per == 0, "stacked weight rows are not a multiple of the per-expert rows");
+    c10::cuda::CUDAGuard guard(xs.device());
+    Tensor out = new_out({xs.size(0), n_per_expert / 2}, xs.options());
+    const bool done = dlv::gemv_grouped_act_run(&desc_, static_cast<int>(n_per_expert), xs.data_ptr(), static_cast<int>(xs.stride(0)), out.data_ptr(),
+                                                static_cast<int>(out.stride(0)), items.data_ptr<int>(), static_cast<int>(items.size(0)), static_cast<int>(act),
+                                                cur_stream());
+    check_last_error("grouped gemv (gated activation) launch");
+    return done ? out : Tensor();
+  }
   // q | k | v projection with per-head RMSNorm, rotary embedding and the paged KV write in the epilogue (head_dim 128). Returns the
   // query heads [M, H * 128]; K and V go straight into the cache rows `slots`.
   Tensor run_qkv(const Tensor& x, const Tensor& positions, const Tensor& slots, c10::optional<Tensor> q_norm_w, c10::optional<Tensor> k_norm_w,
@@ -1406,6 +1423,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("run_qkv", &GemmWeight::run_qkv)
       .def("run_grouped_act", &GemmWeight::run_grouped_act, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits"),
            py::arg("act"))
+      .def("run_grouped_gemv_act", &GemmWeight::run_grouped_gemv_act)
       .def("run_grouped", &GemmWeight::run_grouped, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits") = 1,
            py::arg("out") = py::none())
       .def_property_readonly("N", &GemmWeight::n)
@@ -1428,6 +1446,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("prefill_attention", &prefill_attention);
   m.def("prefill_attention_tc", &prefill_attention_tc);
   m.def("prefill_tc_tile_rows", &dlv::prefill_attention_tc_tile_rows);
+  m.def("gemv_simt_only", [](bool on) { dlv::g_gemv_simt_only = on; });
   m.def("set_bounds_check", &set_bounds_check);
   m.def("check_guards", &check_guards);
   m.def("poke_last_guard", &poke_last_guard);

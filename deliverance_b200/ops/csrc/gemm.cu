@@ -664,6 +664,7 @@ __global__ void __launch_bounds__(128) gemv_simt_kernel(const void* __restrict__
 // weight stream. grid (ceil(N / 32), max_items), 4 warps x 8 weight rows each (a CTA per weight row would spend more time
 // being launched than working); items as built by launch_moe_items with bn == MT.
 constexpr int kGemvRowsPerWarp = 8;
+bool g_gemv_simt_only = false;  // comparison switch: keep grouped JQ4 work items on the CUDA-core kernel
 template <int MT, bool Q4>
 __global__ void __launch_bounds__(128) gemv_grouped_kernel(const void* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
                                                            __nv_bfloat16* __restrict__ out, int ldo, int N, int K,
@@ -754,6 +755,106 @@ __global__ void __launch_bounds__(128) gemv_grouped_kernel(const void* __restric
   }
 }
 
+// ------------------------------------------------------------------------------------------------ grouped JQ4 GEMV on mma.sync
+// The CUDA-core kernel above spends ~200 instructions per 16 bytes of packed weights (nibble -> float conversion, one FMA per
+// token and element) and stays far below the HBM rate. Here a warp owns 16 weight rows of one work item and multiplies them with
+// the item's up to 8 token rows on the tensor cores (mma.sync m16n8k16, bf16 x bf16 -> fp32): the weights are the 16 x 16 A
+// operand, the tokens the 16 x 8 B operand. (tcgen05 needs 128-row tiles and several microseconds of set-up per CTA, which is what
+// rules it out for work items of one to eight rows.)
+// Operand mapping: inside a 128-wide k-block lane (g, c) = (lane / 4, lane % 4) loads the whole 32-element block c of weight rows
+// g and g + 8 (one 16-byte load each: no lane fetches less than a sector's half) and the same 32 elements of token g. Each of the
+// 8 MMAs per k-block takes 4 of those elements per lane; since A and B use the same assignment of elements to the instruction's k
+// positions, the order in which the 128 products are summed is all that differs from the plain layout.
+template <int ACT>
+__device__ __forceinline__ float gated_act(float g) {
+  if (ACT == 2) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + __expf(-g));
+}
+__device__ __forceinline__ void mma_bf16_m16n8k16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// ACT > 0 (gate | up projection of a gated MLP, N = 2 I rows: gate rows first): the warp's 16 rows are 8 gate rows and the 8 up rows
+// of the same outputs, and the epilogue stores act(gate) * up as [rows, I]: the [rows, 2 I] intermediate and the activation
+// kernel disappear. ACT: 1 = SiLU, 2 = tanh-approximated GELU, 3 = exact GELU.
+constexpr int kGemvMmaWarps = 4;
+template <int ACT>
+__global__ void __launch_bounds__(kGemvMmaWarps * 32) gemv_grouped_mma_kernel(const uint8_t* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
+                                                                               __nv_bfloat16* __restrict__ out, int ldo, int N, int K,
+                                                                               const int4* __restrict__ items) {
+  pdl_wait();
+  pdl_trigger();
+  const int4 it = items[blockIdx.y];
+  if (it.x < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  constexpr int RW = ACT > 0 ? 8 : 16;  // output rows per warp
+  const int n_out = ACT > 0 ? N / 2 : N;
+  const int n0 = (blockIdx.x * kGemvMmaWarps + warp) * RW;
+  if (n0 >= n_out) return;
+  const int r0 = it.y, cnt = min(8, it.z - it.y);
+  const int kb_total = K / 128, n_tiles = (N + 127) / 128;
+  const int nA = n0 + g, nB = ACT > 0 ? n_out + n0 + g : n0 + g + 8;  // weight rows behind accumulator rows g and g + 8
+  const int rA = nA & 127, rB = nB & 127;
+  const uint8_t* base = wdata + (static_cast<size_t>(it.x) * n_tiles + (nA >> 7)) * kb_total * kQ4StageBytes;
+  const size_t tileB = static_cast<size_t>((nB >> 7) - (nA >> 7)) * kb_total * kQ4StageBytes;
+  const uint32_t offA = rA * 64 + ((c ^ ((rA >> 1) & 3)) << 4);
+  const size_t offB = tileB + rB * 64 + ((c ^ ((rB >> 1) & 3)) << 4);
+  const uint32_t scA = 8192 + rA * 16 + c * 4;
+  const size_t scB = tileB + 8192 + rB * 16 + c * 4;
+  const bool tok = g < cnt;
+  const __nv_bfloat16* xrow = x + static_cast<size_t>(r0 + (tok ? g : 0)) * ldx + c * 32;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  // (Measured: keeping the weight loads of four k-blocks ahead in registers made the kernel slower, 86 instead of 59 us for the
+  // gate | up projection of 128 experts: the 106 registers halve the resident warps, and what limits the kernel is the issue
+  // rate of the nibble expansion, not the bytes in flight.)
+#pragma unroll 2
+  for (int kb = 0; kb < kb_total; ++kb) {
+    const uint8_t* stage = base + static_cast<size_t>(kb) * kQ4StageBytes;
+    const uint4 wa = __ldg(reinterpret_cast<const uint4*>(stage + offA));
+    const uint4 wb = __ldg(reinterpret_cast<const uint4*>(stage + offB));
+    const float sa = __ldg(reinterpret_cast<const float*>(stage + scA));
+    const float sb = __ldg(reinterpret_cast<const float*>(stage + scB));
+    uint4 xv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) xv[j] = tok ? *reinterpret_cast<const uint4*>(xrow + kb * 128 + j * 8) : make_uint4(0u, 0u, 0u, 0u);
+    const __nv_bfloat162 s2a = __float2bfloat162_rn(sa), s2b = __float2bfloat162_rn(sb);
+    const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
+    const uint32_t* xu = reinterpret_cast<const uint32_t*>(xv);  // word j = elements 2 j, 2 j + 1 of the block
+#pragma unroll
+    for (int hl = 0; hl < 2; ++hl) {
+#pragma unroll
+      for (int wd = 0; wd < 4; ++wd) {
+        // elements e0 .. e0 + 3 of the block, e0 = 16 hl + 4 wd: low (hl = 0) or high nibbles of the bytes of word wd
+        const uint32_t na = (wwa[wd] >> (4 * hl)) & 0x0F0F0F0Fu, nb = (wwb[wd] >> (4 * hl)) & 0x0F0F0F0Fu;
+        uint32_t a[4];
+        a[0] = q4_pair_to_bf162(na, 0x4140u, s2a);
+        a[1] = q4_pair_to_bf162(nb, 0x4140u, s2b);
+        a[2] = q4_pair_to_bf162(na, 0x4342u, s2a);
+        a[3] = q4_pair_to_bf162(nb, 0x4342u, s2b);
+        mma_bf16_m16n8k16(acc, a, xu[hl * 8 + 2 * wd], xu[hl * 8 + 2 * wd + 1]);
+      }
+    }
+  }
+  // accumulator: rows g and g + 8, token columns 2 c and 2 c + 1
+  const int t0 = 2 * c;
+  if (ACT > 0) {
+    // the intermediate is rounded to bf16 as the separate activation kernel sees it
+    if (t0 < cnt) out[static_cast<size_t>(r0 + t0) * ldo + n0 + g] = f2bf(gated_act<ACT>(bf2f(f2bf(acc[0]))) * bf2f(f2bf(acc[2])));
+    if (t0 + 1 < cnt) out[static_cast<size_t>(r0 + t0 + 1) * ldo + n0 + g] = f2bf(gated_act<ACT>(bf2f(f2bf(acc[1]))) * bf2f(f2bf(acc[3])));
+    return;
+  }
+  if (t0 < cnt) {
+    out[static_cast<size_t>(r0 + t0) * ldo + n0 + g] = f2bf(acc[0]);
+    out[static_cast<size_t>(r0 + t0) * ldo + n0 + g + 8] = f2bf(acc[2]);
+  }
+  if (t0 + 1 < cnt) {
+    out[static_cast<size_t>(r0 + t0 + 1) * ldo + n0 + g] = f2bf(acc[1]);
+    out[static_cast<size_t>(r0 + t0 + 1) * ldo + n0 + g + 8] = f2bf(acc[3]);
+  }
+}
+
 void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,
                       int max_items, int mt, cudaStream_t st) {
   if (max_items <= 0) return;
@@ -763,6 +864,12 @@ void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, 
   const int4* it = reinterpret_cast<const int4*>(items);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+  if (w->is_q4 && w->K % 128 == 0 && n_per_expert % 16 == 0 && mt <= 8 && !g_gemv_simt_only) {
+    const dim3 grid_mma((n_per_expert / 16 + kGemvMmaWarps - 1) / kGemvMmaWarps, max_items);
+    launch_pdl(gemv_grouped_mma_kernel<0>, grid_mma, dim3(kGemvMmaWarps * 32), 0, st, static_cast<const uint8_t*>(w->data), xp, ldx, op, ldo, n_per_expert,
+               w->K, it);
+    return;
+  }
 #define DLV_GG(MTV)                                                                                                                 \
   if (w->is_q4) launch_pdl(gemv_grouped_kernel<MTV, true>, grid, dim3(128), 0, st, w->data, xp, ldx, op, ldo, n_per_expert, w->K, it); \
   else launch_pdl(gemv_grouped_kernel<MTV, false>, grid, dim3(128), 0, st, w->data, xp, ldx, op, ldo, n_per_expert, w->K, it)
@@ -772,6 +879,23 @@ void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, 
     default: throw std::runtime_error("grouped gemv: rows per item must be 4 or 8");
   }
 #undef DLV_GG
+}
+
+// Gate | up projection of the work items (n_per_expert = 2 I weight rows per expert, gate rows first) with act(gate) * up in the
+// epilogue; out is [rows, I]. Returns false when the shape is outside the mma.sync kernel (the caller then runs the two steps).
+bool gemv_grouped_act_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items, int max_items,
+                          int act, cudaStream_t st) {
+  if (!w->is_q4 || w->K % 128 != 0 || n_per_expert % 16 != 0 || ldx % 8 != 0 || (act != 1 && act != 2) || g_gemv_simt_only) return false;
+  if (max_items <= 0) return true;
+  if (max_items > 65535) throw std::runtime_error("grouped gemv: work list too long");
+  const int inter = n_per_expert / 2;
+  const dim3 grid((inter / 8 + kGemvMmaWarps - 1) / kGemvMmaWarps, max_items);
+  const int4* it = reinterpret_cast<const int4*>(items);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+  if (act == 1) launch_pdl(gemv_grouped_mma_kernel<1>, grid, dim3(kGemvMmaWarps * 32), 0, st, static_cast<const uint8_t*>(w->data), xp, ldx, op, ldo, n_per_expert, w->K, it);
+  else launch_pdl(gemv_grouped_mma_kernel<2>, grid, dim3(kGemvMmaWarps * 32), 0, st, static_cast<const uint8_t*>(w->data), xp, ldx, op, ldo, n_per_expert, w->K, it);
+  return true;
 }
 
 void gemv_simt_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias,

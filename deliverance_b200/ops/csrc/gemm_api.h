@@ -94,6 +94,8 @@ void gemm_tc_run_grouped(const GemmWeightDesc* w, int n_per_expert, const void* 
 // CUDA-core variant for decode-size groups (at most `mt` = 4 or 8 rows per work item; items built with bn == mt)
 void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,
                       int max_items, int mt, cudaStream_t st);
+bool gemv_grouped_act_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items, int max_items,
+                          int act, cudaStream_t st);
 // Row-parallel projection whose partial tiles go straight to the rank that owns their token rows (epilogue EPI = 3, no waiting
 // inside the GEMM). Follow it with launch_scatter_reduce and launch_scatter_finish on the same stream.
 void gemm_tc_run_scatter(const GemmWeightDesc* w, const void* x, int M, int ldx, const GemmScatterArgs* a, int* status, cudaStream_t st);
@@ -135,6 +137,7 @@ int launch_prefill_attention(const void* q, long long q_stride, const void* kc, 
 
 // attention_tc.cu: tcgen05 / TMA prefill attention; tile arrays hold prefill_attention_tc_tile_rows(D) query rows per tile
 int prefill_attention_tc_tile_rows(int D);
+extern bool g_gemv_simt_only;  // gemm.cu: grouped JQ4 GEMV on CUDA cores instead of mma.sync (comparisons)
 int launch_prefill_attention_tc(const void* q, long long q_stride, long long T, const void* kc, const void* vc, long long num_pages, const int* bt,
                                 int bt_stride, const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,
                                 int num_tiles, void* out, int H, int KV, int D, int page, float scale, float cap, int window, int causal, int* status,

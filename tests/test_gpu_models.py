@@ -82,6 +82,20 @@ def test_grouped_gemm_matches_per_expert(T, E, k, N, K, e0, ne, q4):
             exp = rows @ dense[j].t()
             got = ys[lo:hi].cpu().float()
             assert ((got - exp).norm() / exp.norm().clamp_min(1e-6)).item() < 2e-2, (bn, splits, j)
+        if bn <= 8 and q4 and N % 32 == 0:
+            # the grouped GEMV with the gated activation in its epilogue: rows [0, N / 2) are the gate, [N / 2, N) the up projection
+            hm = grouped.run_gemv_act(xs, items, "silu")
+            assert hm is not None and tuple(hm.shape) == (xs.shape[0], N // 2)
+            torch.cuda.synchronize()
+            for j in range(ne):
+                lo, hi = off[e0 + j], off[e0 + j + 1]
+                if hi == lo:
+                    continue
+                rows = x[(perm.cpu()[lo:hi] // k).long()].float()
+                gu = (rows @ dense[j].t()).to(torch.bfloat16).float()
+                exp = torch.nn.functional.silu(gu[:, : N // 2]) * gu[:, N // 2:]
+                got = hm[lo:hi].cpu().float()
+                assert ((got - exp).norm() / exp.norm().clamp_min(1e-6)).item() < 3e-2, ("gemv act", bn, j)
 
 
 def _pair(tmp_path, family, **over):
