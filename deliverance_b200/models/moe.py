@@ -17,6 +17,9 @@ from .. import ops
 from ..ops import ref
 
 
+_SM_COUNT = 148  # B200
+
+
 def moe_forward(model, i: int, lw, x: torch.Tensor) -> torch.Tensor:
     """Routed experts of one layer. Under tensor parallelism the experts are split across ranks when their count divides
     (expert parallelism: tokens are replicated after the attention all-reduce, so dispatch is a local selection and the
@@ -60,7 +63,7 @@ def moe_forward_sharded(model, i: int, lw, x_own: torch.Tensor, a2a, total_rows:
     w, idx, counts, offsets, perm, pos = e.moe_route(logits.contiguous(), k, 0 if cfg.router_mode == "softmax_topk" else 1, bool(renorm))
     ops._count(2)
     max_recv = min(total_rows * k, a2a.cap * model.tp.size)
-    bn = ops.moe_token_tile(max(1, total_rows * k // model.tp.size), ne)
+    bn = ops.moe_token_tile(max(1, total_rows * k // model.tp.size), ne, lw.experts_gate_up_grouped.q4)
     max_items = max(1, (max_recv + bn - 1) // bn + ne)
     gu_w, down_w = lw.experts_gate_up_grouped, lw.experts_down_grouped
 
@@ -93,16 +96,26 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
         ops._count(2)
         rng = (offsets, e0, ne) if ep else (None, 0, 0)
         xs = e.moe_gather(x, perm, k, *rng)  # [T * k, H] rows grouped by expert (only the local experts' rows are filled)
-        bn = ops.moe_token_tile(rows if not ep else max(1, rows * ne // E), ne)
+        bn = ops.moe_token_tile(rows if not ep else max(1, rows * ne // E), ne, lw.experts_gate_up_grouped.q4)
         max_items = min((rows + bn - 1) // bn + ne, rows) if rows >= ne else rows
         max_items = max(1, max_items)
         items = e.moe_items(offsets, e0, ne, bn, max_items)
         ops._count(2)
     gu_w, down_w = lw.experts_gate_up_grouped, lw.experts_down_grouped
     small = bn <= 64  # decode-sized groups: split K so that more CTAs stream weights
+
+    def k_splits(wt) -> int:
+        """Split K only as far as the grid needs it: every split pays the tile's set-up and a reduction again, so a projection whose
+        (local experts x 128-row tiles) already fill two waves of the GPU runs unsplit."""
+        if not small:
+            return 1
+        tiles = max(1, ne) * ((wt.N + 127) // 128)
+        want = (2 * _SM_COUNT + tiles - 1) // tiles
+        return max(1, min(8, wt.K // 1024, want))
+
     if lw.fused_act_experts and bn >= 16:
         with st("moe.gate_up"):  # act(gate) * up in the grouped GEMM's epilogue (interleaved expert rows)
-            hmid = gu_w.run_act(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1, act)
+            hmid = gu_w.run_act(xs, items, bn, k_splits(gu_w), act)
     else:
         if lw.fused_act_experts:
             raise RuntimeError("interleaved expert weights need the tensor-core grouped GEMM (token tile >= 16)")
@@ -112,11 +125,11 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
                 hmid = gu_w.run_gemv_act(xs, items, act)
         if hmid is None:
             with st("moe.gate_up"):
-                gu = gu_w.run(xs, items, bn, max(1, min(8, gu_w.K // 1024)) if small else 1)
+                gu = gu_w.run(xs, items, bn, k_splits(gu_w))
             with st("moe.activation_multiply"):
                 hmid = ops.act_mul(gu, act)
     with st("moe.down"):
-        ys = down_w.run(hmid, items, bn, max(1, min(8, down_w.K // 1024)) if small else 1)
+        ys = down_w.run(hmid, items, bn, k_splits(down_w))
     with st("moe.combine"):
         fused = getattr(model.tp, "fused", None)
         if ep and fused is not None:

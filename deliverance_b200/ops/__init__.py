@@ -519,14 +519,20 @@ class GroupedLinearWeight:
         return self.handle.run_grouped_act(xs, items, self.N, bn, splits, fused_act_kind(act))
 
 
-def moe_token_tile(rows: int, local_experts: int) -> int:
+_GEMV_MIN_EXPERTS = int(os.environ.get("DLV_MOE_GEMV_MIN_EXPERTS", "1"))
+
+
+def moe_token_tile(rows: int, local_experts: int, q4: bool = True) -> int:
     """Token tile (UMMA N) of the grouped GEMM for ``rows`` routed rows spread over ``local_experts`` experts."""
     avg = rows / max(1, local_experts)
-    # CUDA-core grouped GEMV (4 or 8 rows per work item): measured faster than the tensor-core tiles only when a rank holds
-    # very many experts with a handful of rows each (128 experts x 2 rows: 23.3 vs 28.6 ms per step; 64 experts: 16.2 vs 11.9)
-    if local_experts >= 96 and avg <= 3:
+    # Grouped GEMV (4 or 8 rows per work item, mma.sync) for a handful of rows per expert: a tcgen05 tile costs several microseconds
+    # of set-up per (expert, 128 weight rows) whatever the row count. DLV_MOE_GEMV_MIN_EXPERTS restricts it to ranks with at least
+    # that many local experts (comparisons).
+    # (bf16 experts still have the CUDA-core GEMV only: worth it just for very many experts, as measured with that kernel)
+    need = _GEMV_MIN_EXPERTS if q4 else max(96, _GEMV_MIN_EXPERTS)
+    if local_experts >= need and avg <= 3:
         return 4
-    if local_experts >= 96 and avg <= 6:
+    if local_experts >= need and avg <= 6:
         return 8
     for bn in (16, 32, 64, 128):
         if avg <= bn * 0.75:
