@@ -64,6 +64,8 @@ def moe_forward_sharded(model, i: int, lw, x_own: torch.Tensor, a2a, total_rows:
     ops._count(2)
     max_recv = min(total_rows * k, a2a.cap * model.tp.size)
     bn = ops.moe_token_tile(max(1, total_rows * k // model.tp.size), ne, lw.experts_gate_up_grouped.q4)
+    if lw.fused_act_experts:
+        bn = max(bn, 16)
     max_items = max(1, (max_recv + bn - 1) // bn + ne)
     gu_w, down_w = lw.experts_gate_up_grouped, lw.experts_down_grouped
 
@@ -97,6 +99,8 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
         rng = (offsets, e0, ne) if ep else (None, 0, 0)
         xs = e.moe_gather(x, perm, k, *rng)  # [T * k, H] rows grouped by expert (only the local experts' rows are filled)
         bn = ops.moe_token_tile(rows if not ep else max(1, rows * ne // E), ne, lw.experts_gate_up_grouped.q4)
+        if lw.fused_act_experts:
+            bn = max(bn, 16)  # interleaved expert rows exist for the tensor-core grouped GEMM's epilogue only
         max_items = min((rows + bn - 1) // bn + ne, rows) if rows >= ne else rows
         max_items = max(1, max_items)
         items = e.moe_items(offsets, e0, ne, bn, max_items)

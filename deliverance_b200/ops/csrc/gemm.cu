@@ -261,6 +261,24 @@ static int pick_bn(int M) {
   return 256;
 }
 
+// Prefill sizes: 256-token tiles halve the weight traffic per FLOP, but a grid that is a little more than a whole number of waves
+// wastes most of its last wave (N = 2560, M = 2048: 160 tiles on 148 SMs). 128-token tiles cost a little more than half as much
+// each (kBn128Cost, measured) and come in twice the number, so they win where they fill the waves better.
+static int pick_bn_waves(int M, int N) {
+  const int bn = pick_bn(M);
+  if (bn != 256) return bn;
+  static const double kBn128Cost = [] {
+    const char* v = getenv("DLV_GEMM_BN128_COST");
+    return v ? atof(v) : 0.58;
+  }();
+  const int sms = gemm_num_sms();
+  const long long n_tiles = (N + kGemmBM - 1) / kGemmBM;
+  const long long t256 = n_tiles * ((M + 255) / 256), t128 = n_tiles * ((M + 127) / 128);
+  const double c256 = static_cast<double>((t256 + sms - 1) / sms), c128 = static_cast<double>((t128 + sms - 1) / sms) * kBn128Cost;
+  if (t256 <= sms) return 256;  // a single partial wave: measured no gain from smaller tiles (the split-K planner fills the SMs)
+  return c128 < 0.97 * c256 ? 128 : 256;
+}
+
 bool gemm_tp_supported(const GemmWeightDesc* w, int M, const GemmTpArgs* tp) {
   if (tp == nullptr || tp->size <= 1 || tp->size > 8) return false;
   if (w->N % 4 != 0 || M <= 0 || M > 128) return false;
@@ -275,7 +293,7 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
                  const GemmTpArgs* tp) {
   if (M <= 0) return;
   if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
-  const int BN = pick_bn(M);
+  const int BN = (tp == nullptr || tp->size <= 1) ? pick_bn_waves(M, w->N) : pick_bn(M);
   GemmParams p = {};
   p.M = M;
   p.N = w->N;
