@@ -84,6 +84,10 @@ def main() -> int:
             except Exception as e:  # noqa: BLE001
                 print(f"[server] fused tensor parallelism unavailable, using NCCL all-reduce: {e}", flush=True)
     reg = ModelRegistry()
+    if int(os.environ.get("RANK", "0")) == 0:
+        from ..parallel.gossip import observer_from_env
+
+        reg.membership = observer_from_env(f"server-{os.getpid()}")  # None unless the host's gossip agent started this process
     for d in a.model:
         b = AutoModelForCausalLM.new_builder(d).with_device(a.device).with_output_head_quantization(head_quant.get(d) or a.output_head_quantization)
         if kv is not None:

@@ -59,6 +59,7 @@ class ModelRegistry:
     generation: dict = field(default_factory=dict)  # name -> EngineRunner
     embedding: dict = field(default_factory=dict)  # name -> EmbeddingModel
     tp_status: Callable[[], dict] = lambda: {"enabled": False, "size": 1, "rank": 0}
+    membership: Optional[object] = None  # parallel.gossip.TensorParallelMembership when the deployment is gossip-managed
 
     def find(self, name: Optional[str]) -> EngineRunner:
         if not self.generation:
@@ -471,8 +472,11 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
                                                        "role": "coordinator+rank" if r == 0 else "rank"} for r in range(n)]})
 
     async def tp_gossip():
-        """Membership view. The group is fixed at launch (RANK / WORLD_SIZE), so the view is the static member list plus the
-        supervisor's restart history when one is running."""
+        """Membership view: with a gossip-managed deployment the agent's live nodes, topology, elected leader, assignment and rank
+        endpoints (reference: /tp/gossip, web/.../TensorParallelDiagnosticsController.java:22-40); otherwise the group is fixed at
+        launch (RANK / WORLD_SIZE) and the view is the static member list plus the supervisor's restart history."""
+        if registry.membership is not None:
+            return JSONResponse({"membership": "gossip", **registry.membership.diagnostics()})
         st = dict(registry.tp_status())
         out = {"membership": "static", "leader": 0, "members": list(range(int(st.get("size", 1))))}
         sf = os.environ.get("DLV_CLUSTER_STATUS_FILE")
@@ -485,9 +489,19 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         return JSONResponse(out)
 
     async def tp_assign(request: Request):
+        """Manual rank placement ``POST /tp/assign?nodeId=..&rank=..`` for a gossip deployment in manual mode (reference:
+        GossipParallelMembership.assignRankManually, core/.../tensorparallel/GossipParallelMembership.java:460-475)."""
         q = request.query_params
-        return error(409, f"rank assignment is static: ranks are fixed at launch (requested nodeId={q.get('nodeId')} rank={q.get('rank')}); "
-                          "restart the group with a different --nproc to change it")
+        m = registry.membership
+        if m is None:
+            return error(409, f"rank assignment is static: ranks are fixed at launch (requested nodeId={q.get('nodeId')} rank={q.get('rank')}); "
+                              "restart the group with a different --nproc to change it, or run the hosts under deliverance_b200.parallel.gossip")
+        try:
+            return JSONResponse(m.assign_rank(str(q.get("nodeId")), int(q.get("rank", "-1"))))
+        except RuntimeError as e:
+            return error(409, str(e))
+        except (ValueError, TypeError) as e:
+            return error(400, str(e))
 
     async def health():
         """Liveness / readiness probe (never behind authentication): 200 while every engine runner thread is alive."""
