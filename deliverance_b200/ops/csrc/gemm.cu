@@ -264,18 +264,17 @@ static int pick_bn(int M) {
 // Prefill sizes: 256-token tiles halve the weight traffic per FLOP, but a grid that is a little more than a whole number of waves
 // wastes most of its last wave (N = 2560, M = 2048: 160 tiles on 148 SMs). 128-token tiles cost a little more than half as much
 // each (kBn128Cost, measured) and come in twice the number, so they win where they fill the waves better.
+int g_gemm_force_bn = 0;  // 128 / 256: token tile for every batch of more than 128 rows (0: chosen by wave count)
 static int pick_bn_waves(int M, int N) {
   const int bn = pick_bn(M);
   if (bn != 256) return bn;
-  static const double kBn128Cost = [] {
-    const char* v = getenv("DLV_GEMM_BN128_COST");
-    return v ? atof(v) : 0.58;
-  }();
+  static const double kCost128 = [] { const char* v = getenv("DLV_GEMM_BN128_COST"); return v ? atof(v) : 0.58; }();
+  if (g_gemm_force_bn == 128 || g_gemm_force_bn == 256) return g_gemm_force_bn;  // tests and comparisons
   const int sms = gemm_num_sms();
   const long long n_tiles = (N + kGemmBM - 1) / kGemmBM;
   const long long t256 = n_tiles * ((M + 255) / 256), t128 = n_tiles * ((M + 127) / 128);
-  const double c256 = static_cast<double>((t256 + sms - 1) / sms), c128 = static_cast<double>((t128 + sms - 1) / sms) * kBn128Cost;
   if (t256 <= sms) return 256;  // a single partial wave: measured no gain from smaller tiles (the split-K planner fills the SMs)
+  const double c256 = static_cast<double>((t256 + sms - 1) / sms), c128 = static_cast<double>((t128 + sms - 1) / sms) * kCost128;
   return c128 < 0.97 * c256 ? 128 : 256;
 }
 

@@ -137,6 +137,7 @@ int launch_prefill_attention(const void* q, long long q_stride, const void* kc, 
 
 // attention_tc.cu: tcgen05 / TMA prefill attention; tile arrays hold prefill_attention_tc_tile_rows(D) query rows per tile
 int prefill_attention_tc_tile_rows(int D);
+extern int g_gemm_force_bn;    // gemm.cu: token tile for prefill-size batches (tests, comparisons)
 extern bool g_gemv_simt_only;  // gemm.cu: grouped JQ4 GEMV on CUDA cores instead of mma.sync (comparisons)
 int launch_prefill_attention_tc(const void* q, long long q_stride, long long T, const void* kc, const void* vc, long long num_pages, const int* bt,
                                 int bt_stride, const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,

@@ -573,3 +573,29 @@ def test_outputs_stay_inside_their_guard_areas():
             ops.check_guards()
     finally:
         ops.set_bounds_check(False)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("q4", [True, False])
+def test_linear_prefill_token_tiles(bn, q4):
+    """Every token tile the prefill-size GEMM can pick (128 / 256 tokens) against the
+    fp32 product, with token counts that end inside a tile."""
+    ext = ops.require_ext()
+    g = torch.Generator().manual_seed(bn)
+    N, K = 640, 1152
+    w = torch.randn(N, K, generator=g) * 0.05
+    if q4:
+        p, s = q4_quantize(w)
+        lw, wd = LinearWeight(Q4Tensor(p, s, (N, K))).to(DEV), q4_dequantize(p, s)
+    else:
+        lw, wd = LinearWeight(w.to(torch.bfloat16).to(DEV)), w.to(torch.bfloat16).float()
+    ext.gemm_force_bn(bn)
+    try:
+        for M in (129, 192, 193, 500, 1024):
+            x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+            y = ops.linear(x.to(DEV), lw)
+            torch.cuda.synchronize()
+            ops.check_status()
+            assert _rel(y.cpu().float(), x.float() @ wd.t()) < 1e-2, (bn, M)
+    finally:
+        ext.gemm_force_bn(0)
