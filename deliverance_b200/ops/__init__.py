@@ -252,6 +252,19 @@ def interleave_gate_up(gate, up, block: int = 64):
     return mix(gate, up.to(gate.dtype))
 
 
+def linear_gated(x: torch.Tensor, w: LinearWeight, act: str) -> torch.Tensor:
+    """``act(x @ Wg^T) * (x @ Wu^T)`` for a weight that holds the gate rows followed by the up rows (plain order). One kernel for
+    1..8 rows of a JQ4 weight on CUDA (the small-batch GEMV's epilogue), projection + activation kernel otherwise."""
+    if _cuda(x) and w.q4 and x.shape[0] <= 8:
+        kind = fused_act_kind(act)
+        if kind:
+            out = w.handle().run_gemv_act(x, kind)
+            if out is not None:
+                _count()
+                return out
+    return act_mul(linear(x, w), act)
+
+
 def linear_act(x: torch.Tensor, w: LinearWeight, act: str, block: int = 64) -> torch.Tensor:
     """``act(x @ Wg^T) * (x @ Wu^T)`` in one GEMM whose epilogue applies the gated activation; ``w`` holds the gate and up rows in
     the order of :func:`interleave_gate_up`. Returns ``[T, N / 2]``."""
@@ -346,6 +359,9 @@ def linear_rope_kv(x, w: LinearWeight, positions, slots, q_norm_w, k_norm_w, cos
         if D != 128:
             raise ValueError("the fused q/k/v epilogue needs head_dim 128")
         _check_full_rotary(cos, D)
+        if x.shape[0] <= 8 and w.q4 and w.handle().gemv_ok(x.shape[0], x.stride(0)):
+            # a handful of rows: the small-batch GEMV plus the stand-alone rotary kernel beat the tcgen05 tile's fixed cost
+            return rope_kv(linear(x, w), positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset)
         _count()
         return w.handle().run_qkv(x, positions.to(torch.int32), slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, eps, norm_offset, w.bias)
     return rope_kv(linear(x, w), positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset)

@@ -292,6 +292,21 @@ class GemmWeight {
     check_last_error("gemm (fused activation) launch");
     return out;
   }
+  // 1..8 token rows through the mma.sync GEMV with act(gate) * up in its epilogue: `this` holds gate | up rows in plain order
+  // (N = 2 I). Returns [M, I], or an undefined tensor when the shape is outside that kernel.
+  Tensor run_gemv_act(const Tensor& x, int64_t act) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.size(1) == desc_.K && x.stride(1) == 1, "x must be bf16 [M, K]");
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "x rows must be 16-byte aligned");
+    const int M = static_cast<int>(x.size(0));
+    if ((act != 1 && act != 2) || desc_.N % 16 != 0 || !dlv::gemv_dense_supported(&desc_, M, static_cast<int>(x.stride(0)))) return Tensor();
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor out = new_out({M, desc_.N / 2}, x.options());
+    dlv::gemv_dense_run(&desc_, x.data_ptr(), M, static_cast<int>(x.stride(0)), out.data_ptr(), static_cast<int>(out.stride(0)), false, nullptr,
+                        static_cast<int>(act), cur_stream());
+    check_last_error("gemv (gated activation) launch");
+    return out;
+  }
+  bool gemv_ok(int64_t M, int64_t ldx) const { return dlv::gemv_dense_supported(&desc_, static_cast<int>(M), static_cast<int>(ldx)); }
   // Grouped (MoE) GEMM: `this` stacks the local experts' weights (n_per_expert rows each; JQ4: whole 128-row tiles per expert),
   // xs holds rows sorted by expert, `items` comes from moe_items with the same token tile.
   Tensor run_grouped(const Tensor& xs, const Tensor& items, int64_t n_per_expert, int64_t bn, int64_t splits, c10::optional<Tensor> out_opt) {
@@ -1424,6 +1439,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("run_grouped_act", &GemmWeight::run_grouped_act, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits"),
            py::arg("act"))
       .def("run_grouped_gemv_act", &GemmWeight::run_grouped_gemv_act)
+      .def("run_gemv_act", &GemmWeight::run_gemv_act)
+      .def("gemv_ok", &GemmWeight::gemv_ok)
       .def("run_grouped", &GemmWeight::run_grouped, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits") = 1,
            py::arg("out") = py::none())
       .def_property_readonly("N", &GemmWeight::n)
@@ -1447,6 +1464,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("prefill_attention_tc", &prefill_attention_tc);
   m.def("prefill_tc_tile_rows", &dlv::prefill_attention_tc_tile_rows);
   m.def("gemv_simt_only", [](bool on) { dlv::g_gemv_simt_only = on; });
+  m.def("gemv_dense", [](bool on) { dlv::g_gemv_dense = on; });
   m.def("gemm_force_bn", [](int64_t bn) { dlv::g_gemm_force_bn = static_cast<int>(bn); });
   m.def("set_bounds_check", &set_bounds_check);
   m.def("check_guards", &check_guards);

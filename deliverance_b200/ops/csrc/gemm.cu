@@ -253,6 +253,10 @@ static void run_tc(const GemmWeightDesc* w, const void* x, int M, int ldx, GemmP
 }
 
 // Choose the token tile. Small batches take the smallest UMMA N that covers them.
+struct GemmWeightDesc;
+bool gemv_dense_supported(const GemmWeightDesc* w, int M, int ldx);
+void gemv_dense_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias, int act,
+                    cudaStream_t st);
 static int pick_bn(int M) {
   if (M <= 16) return 16;
   if (M <= 32) return 32;
@@ -292,6 +296,10 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
                  const GemmTpArgs* tp) {
   if (M <= 0) return;
   if (ldx % 8 != 0) throw std::runtime_error("activation row pitch must be a multiple of 8 elements");
+  if ((tp == nullptr || tp->size <= 1) && force_splits == 0 && gemv_dense_supported(w, M, ldx)) {
+    gemv_dense_run(w, x, M, ldx, out, ldo, out_f32, bias, 0, st);
+    return;
+  }
   const int BN = (tp == nullptr || tp->size <= 1) ? pick_bn_waves(M, w->N) : pick_bn(M);
   GemmParams p = {};
   p.M = M;
@@ -870,6 +878,108 @@ __global__ void __launch_bounds__(kGemvMmaWarps * 32) gemv_grouped_mma_kernel(co
     out[static_cast<size_t>(r0 + t0 + 1) * ldo + n0 + g] = f2bf(acc[1]);
     out[static_cast<size_t>(r0 + t0 + 1) * ldo + n0 + g + 8] = f2bf(acc[3]);
   }
+}
+
+// ------------------------------------------------------------------------------------------------ dense JQ4 GEMV for 1..8 tokens
+// The same operand mapping for an ordinary projection with at most 8 token rows (single requests and small decode batches). These
+// GEMMs move a few megabytes, so what counts is how many warps stream at once and how little is set up per launch: the tcgen05 kernel
+// pays its prologue and epilogue per CTA (10-12 us per projection at one token). One CTA per 16 weight rows (8 with the gated
+// activation), its kGemvSplit warps take interleaved k-blocks and add their partial tiles through shared memory.
+// ACT as above; OUTF: fp32 output (the output head's logits).
+constexpr int kGemvSplit = 8;
+template <int ACT, bool OUTF>
+__global__ void __launch_bounds__(kGemvSplit * 32) gemv_dense_mma_kernel(const uint8_t* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
+                                                                         void* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N, int K) {
+  __shared__ float part[kGemvSplit][32][4];
+  pdl_wait();
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  constexpr int RW = ACT > 0 ? 8 : 16;
+  const int n_out = ACT > 0 ? N / 2 : N;
+  const int n0 = blockIdx.x * RW;
+  const int kb_total = K / 128;
+  const int nA = min(n0 + g, N - 1), nB = min(ACT > 0 ? n_out + n0 + g : n0 + g + 8, N - 1);  // (rows past the end are computed and dropped)
+  const int rA = nA & 127, rB = nB & 127;
+  const uint8_t* baseA = wdata + static_cast<size_t>(nA >> 7) * kb_total * kQ4StageBytes;
+  const uint8_t* baseB = wdata + static_cast<size_t>(nB >> 7) * kb_total * kQ4StageBytes;
+  const uint32_t offA = rA * 64 + ((c ^ ((rA >> 1) & 3)) << 4), offB = rB * 64 + ((c ^ ((rB >> 1) & 3)) << 4);
+  const uint32_t scA = 8192 + rA * 16 + c * 4, scB = 8192 + rB * 16 + c * 4;
+  const bool tok = g < M;
+  const __nv_bfloat16* xrow = x + static_cast<size_t>(tok ? g : 0) * ldx + c * 32;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+  for (int kb = warp; kb < kb_total; kb += kGemvSplit) {
+    const size_t so = static_cast<size_t>(kb) * kQ4StageBytes;
+    const uint4 wa = __ldg(reinterpret_cast<const uint4*>(baseA + so + offA));
+    const uint4 wb = __ldg(reinterpret_cast<const uint4*>(baseB + so + offB));
+    const float sa = __ldg(reinterpret_cast<const float*>(baseA + so + scA));
+    const float sb = __ldg(reinterpret_cast<const float*>(baseB + so + scB));
+    uint4 xv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) xv[j] = tok ? *reinterpret_cast<const uint4*>(xrow + kb * 128 + j * 8) : make_uint4(0u, 0u, 0u, 0u);
+    const __nv_bfloat162 s2a = __float2bfloat162_rn(sa), s2b = __float2bfloat162_rn(sb);
+    const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
+    const uint32_t* xu = reinterpret_cast<const uint32_t*>(xv);
+#pragma unroll
+    for (int hl = 0; hl < 2; ++hl) {
+#pragma unroll
+      for (int wd = 0; wd < 4; ++wd) {
+        const uint32_t na = (wwa[wd] >> (4 * hl)) & 0x0F0F0F0Fu, nb = (wwb[wd] >> (4 * hl)) & 0x0F0F0F0Fu;
+        uint32_t a[4];
+        a[0] = q4_pair_to_bf162(na, 0x4140u, s2a);
+        a[1] = q4_pair_to_bf162(nb, 0x4140u, s2b);
+        a[2] = q4_pair_to_bf162(na, 0x4342u, s2a);
+        a[3] = q4_pair_to_bf162(nb, 0x4342u, s2b);
+        mma_bf16_m16n8k16(acc, a, xu[hl * 8 + 2 * wd], xu[hl * 8 + 2 * wd + 1]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) part[warp][lane][i] = acc[i];
+  __syncthreads();
+  if (warp != 0) return;
+#pragma unroll
+  for (int w2 = 1; w2 < kGemvSplit; ++w2)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] += part[w2][lane][i];
+  // accumulator: rows g and g + 8, token columns 2 c and 2 c + 1
+  auto store = [&](int t, int n, float v) {
+    if (t >= M || n >= n_out) return;
+    if (OUTF) static_cast<float*>(out)[static_cast<size_t>(t) * ldo + n] = v;
+    else static_cast<__nv_bfloat16*>(out)[static_cast<size_t>(t) * ldo + n] = f2bf(v);
+  };
+  const int t0 = 2 * c;
+  if (ACT > 0) {
+    store(t0, n0 + g, gated_act<ACT>(bf2f(f2bf(acc[0]))) * bf2f(f2bf(acc[2])));
+    store(t0 + 1, n0 + g, gated_act<ACT>(bf2f(f2bf(acc[1]))) * bf2f(f2bf(acc[3])));
+    return;
+  }
+  const float b0 = bias != nullptr && n0 + g < N ? bias[n0 + g] : 0.f, b1 = bias != nullptr && n0 + g + 8 < N ? bias[n0 + g + 8] : 0.f;
+  store(t0, n0 + g, acc[0] + b0);
+  store(t0 + 1, n0 + g, acc[1] + b0);
+  store(t0, n0 + g + 8, acc[2] + b1);
+  store(t0 + 1, n0 + g + 8, acc[3] + b1);
+}
+
+bool g_gemv_dense = true;  // small batches (<= 8 rows) of JQ4 projections on the mma.sync GEMV instead of the tcgen05 kernel
+bool gemv_dense_supported(const GemmWeightDesc* w, int M, int ldx) {
+  return g_gemv_dense && !g_gemv_simt_only && w->is_q4 && M >= 1 && M <= 8 && w->K % 128 == 0 && w->K >= 128 && ldx % 8 == 0;
+}
+// act: 0 plain (bias, bf16 or fp32 output), 1 / 2: w holds gate | up rows (N = 2 I), out is [M, I] bf16
+void gemv_dense_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias, int act,
+                    cudaStream_t st) {
+  const uint8_t* wd = static_cast<const uint8_t*>(w->data);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const dim3 block(kGemvSplit * 32);
+  if (act == 1 || act == 2) {
+    const dim3 grid((w->N / 2 + 7) / 8);
+    if (act == 1) launch_pdl(gemv_dense_mma_kernel<1, false>, grid, block, 0, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+    else launch_pdl(gemv_dense_mma_kernel<2, false>, grid, block, 0, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+    return;
+  }
+  const dim3 grid((w->N + 15) / 16);
+  if (out_f32) launch_pdl(gemv_dense_mma_kernel<0, true>, grid, block, 0, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+  else launch_pdl(gemv_dense_mma_kernel<0, false>, grid, block, 0, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
 }
 
 void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,

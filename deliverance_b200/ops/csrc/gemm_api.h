@@ -138,6 +138,10 @@ int launch_prefill_attention(const void* q, long long q_stride, const void* kc, 
 // attention_tc.cu: tcgen05 / TMA prefill attention; tile arrays hold prefill_attention_tc_tile_rows(D) query rows per tile
 int prefill_attention_tc_tile_rows(int D);
 extern int g_gemm_force_bn;    // gemm.cu: token tile for prefill-size batches (tests, comparisons)
+extern bool g_gemv_dense;      // gemm.cu: <= 8-row JQ4 projections on the mma.sync GEMV (default on)
+bool gemv_dense_supported(const GemmWeightDesc* w, int M, int ldx);
+void gemv_dense_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias, int act,
+                    cudaStream_t st);
 extern bool g_gemv_simt_only;  // gemm.cu: grouped JQ4 GEMV on CUDA cores instead of mma.sync (comparisons)
 int launch_prefill_attention_tc(const void* q, long long q_stride, long long T, const void* kc, const void* vc, long long num_pages, const int* bt,
                                 int bt_stride, const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,

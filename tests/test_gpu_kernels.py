@@ -599,3 +599,37 @@ def test_linear_prefill_token_tiles(bn, q4):
             assert _rel(y.cpu().float(), x.float() @ wd.t()) < 1e-2, (bn, M)
     finally:
         ext.gemm_force_bn(0)
+
+
+@pytest.mark.parametrize("N,K", [(2560, 4096), (384, 256), (200, 1152), (6144, 2560)])
+def test_small_batch_gemv_matches_fp32(N, K):
+    """1..8 token rows of a JQ4 projection on the mma.sync GEMV: plain (bf16 and fp32 output, bias), gated activation epilogue, and
+    agreement with the tcgen05 kernel it replaces at these sizes."""
+    ext = ops.require_ext()
+    g = torch.Generator().manual_seed(N + K)
+    w = torch.randn(N, K, generator=g) * 0.05
+    p, s = q4_quantize(w)
+    wd = q4_dequantize(p, s)
+    bias = torch.randn(N, generator=g) * 0.1
+    lw = LinearWeight(Q4Tensor(p, s, (N, K))).to(DEV)
+    lwb = LinearWeight(Q4Tensor(p, s, (N, K)), bias=bias).to(DEV)
+    for M in (1, 2, 5, 8):
+        x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+        ref_y = x.float() @ wd.t()
+        assert lw.handle().gemv_ok(M, K)
+        y = ops.linear(x.to(DEV), lw)
+        y32 = ops.linear(x.to(DEV), lwb, out_f32=True)
+        ext.gemv_dense(False)
+        try:
+            y_tc = ops.linear(x.to(DEV), lw)
+        finally:
+            ext.gemv_dense(True)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert y32.dtype == torch.float32 and _rel(y.cpu().float(), ref_y) < 1e-2 and _rel(y32.cpu(), ref_y + bias) < 1e-2
+        assert _rel(y.cpu().float(), y_tc.cpu().float()) < 1e-2
+        if N % 32 == 0:
+            h = ops.linear_gated(x.to(DEV), lw, "silu")
+            gu = ref_y.to(torch.bfloat16).float()
+            exp = torch.nn.functional.silu(gu[:, : N // 2]) * gu[:, N // 2:]
+            assert tuple(h.shape) == (M, N // 2) and _rel(h.cpu().float(), exp) < 2e-2
