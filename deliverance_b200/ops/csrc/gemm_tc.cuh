@@ -366,7 +366,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,   // dense: bf16 [N, K
     // groups of 8 MMAs of 128 x 128 x 16 back to back 517 cycles per group, with one satisfied wait between groups 783). NI warps
     // therefore take alternate k-blocks, so that one feeds the pipe while another waits: each into its own accumulator (columns
     // j*BN .., added up by the epilogue), or, where tensor memory has no room for that (BN = 256), all into one. (For the JQ4 prefill
-    // shapes the second issuer of BN = 256 changed nothing measurable: the tensor pipe is 48 % active there and the cause is not established.) The
+    // shapes the second issuer of BN = 256 changed nothing measurable: there the prologue and epilogue of the one-tile-per-CTA design, not the issuer, leave the tensor pipe idle.) The
     // whole warp follows the barriers, one lane issues.
     const int issuer = warp == 1 ? 0 : warp - 20;
     if (issuer < NI) {
