@@ -37,6 +37,8 @@ def ext():
         _ext_checked = True
         if _ext is not None and os.environ.get("DLV_GEMM_PDL", "1") == "0":
             _ext.gemm_pdl(False)
+        if _ext is not None and os.environ.get("DLV_GEMM_PERSIST", "0") == "1":
+            _ext.gemm_persist(True)
         if _ext is not None and os.environ.get("DLV_BOUNDS_CHECK", "0") == "1":
             _ext.set_bounds_check(True)
     return _ext

@@ -14,7 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 BUILD_DIR = os.path.join(_HERE, "_build")
 NAME = "_dlv_C"
-SOURCES = ["bindings.cpp", "gemm.cu", "elementwise.cu", "attention.cu", "sampling.cu", "quant.cu", "moe.cu", "mamba.cu",
+SOURCES = ["bindings.cpp", "gemm.cu", "gemm_persist.cu", "elementwise.cu", "attention.cu", "sampling.cu", "quant.cu", "moe.cu", "mamba.cu",
            "comm.cu", "noalloc.cu", "chain.cu", "aux.cu", "a2a.cu", "attention_tc.cu", "lz4_block.cpp"]
 
 CUDA_FLAGS = [

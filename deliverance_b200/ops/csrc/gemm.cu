@@ -300,6 +300,10 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
     gemv_dense_run(w, x, M, ldx, out, ldo, out_f32, bias, 0, st);
     return;
   }
+  if (g_gemm_persist && (tp == nullptr || tp->size <= 1) && force_splits == 0 && gemm_persist_supported(w, M, ldx)) {
+    gemm_persist_run(w, x, M, ldx, out, ldo, out_f32, bias, status, st);
+    return;
+  }
   const int BN = (tp == nullptr || tp->size <= 1) ? pick_bn_waves(M, w->N) : pick_bn(M);
   GemmParams p = {};
   p.M = M;

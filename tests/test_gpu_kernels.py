@@ -633,3 +633,30 @@ def test_small_batch_gemv_matches_fp32(N, K):
             gu = ref_y.to(torch.bfloat16).float()
             exp = torch.nn.functional.silu(gu[:, : N // 2]) * gu[:, N // 2:]
             assert tuple(h.shape) == (M, N // 2) and _rel(h.cpu().float(), exp) < 2e-2
+
+
+@pytest.mark.parametrize("N,K,M", [(640, 1024, 500), (384, 512, 257), (2560, 4096, 2048), (200, 256, 1000)])
+def test_persistent_prefill_gemm(N, K, M):
+    """The persistent JQ4 GEMM (many tiles per CTA, epilogue under the next tile's main loop) against the fp32 product and against
+    the one-tile-per-CTA kernel: bf16 and fp32 output, bias, ragged last token tile and last weight tile."""
+    ext = ops.require_ext()
+    g = torch.Generator().manual_seed(N + M)
+    w = torch.randn(N, K, generator=g) * 0.05
+    p, s = q4_quantize(w)
+    wd = q4_dequantize(p, s)
+    bias = torch.randn(N, generator=g) * 0.1
+    lw = LinearWeight(Q4Tensor(p, s, (N, K))).to(DEV)
+    lwb = LinearWeight(Q4Tensor(p, s, (N, K)), bias=bias).to(DEV)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    y0 = ops.linear(x.to(DEV), lw)
+    ext.gemm_persist(True)
+    try:
+        y = ops.linear(x.to(DEV), lw)
+        y32 = ops.linear(x.to(DEV), lwb, out_f32=True)
+        torch.cuda.synchronize()
+        ops.check_status()
+    finally:
+        ext.gemm_persist(False)
+    ref_y = x.float() @ wd.t()
+    assert _rel(y.cpu().float(), ref_y) < 1e-2 and _rel(y32.cpu(), ref_y + bias) < 1e-2
+    assert _rel(y.cpu().float(), y0.cpu().float()) < 1e-2
