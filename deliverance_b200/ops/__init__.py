@@ -37,8 +37,9 @@ def ext():
         _ext_checked = True
         if _ext is not None and os.environ.get("DLV_GEMM_PDL", "1") == "0":
             _ext.gemm_pdl(False)
-        if _ext is not None and os.environ.get("DLV_GEMM_PERSIST", "0") == "1":
-            _ext.gemm_persist(True)
+        persist = os.environ.get("DLV_GEMM_PERSIST", "0")
+        if _ext is not None and persist in ("1", "race"):
+            _ext.gemm_persist(True, False, persist != "race")
         if _ext is not None and os.environ.get("DLV_BOUNDS_CHECK", "0") == "1":
             _ext.set_bounds_check(True)
     return _ext

@@ -1465,7 +1465,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("prefill_tc_tile_rows", &dlv::prefill_attention_tc_tile_rows);
   m.def("gemv_simt_only", [](bool on) { dlv::g_gemv_simt_only = on; });
   m.def("gemv_dense", [](bool on) { dlv::g_gemv_dense = on; });
-  m.def("gemm_persist", [](bool on) { dlv::g_gemm_persist = on; });
+  m.def(
+      "gemm_persist",
+      [](bool on, bool all, bool ordered) {
+        dlv::g_gemm_persist = on;
+        dlv::g_gemm_persist_all = all;
+        dlv::g_gemm_persist_ordered = ordered;
+      },
+      py::arg("on"), py::arg("all") = false, py::arg("ordered") = true);
   m.def("gemm_force_bn", [](int64_t bn) { dlv::g_gemm_force_bn = static_cast<int>(bn); });
   m.def("set_bounds_check", &set_bounds_check);
   m.def("check_guards", &check_guards);

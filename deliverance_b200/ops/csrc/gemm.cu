@@ -268,6 +268,7 @@ static int pick_bn(int M) {
 // Prefill sizes: 256-token tiles halve the weight traffic per FLOP, but a grid that is a little more than a whole number of waves
 // wastes most of its last wave (N = 2560, M = 2048: 160 tiles on 148 SMs). 128-token tiles cost a little more than half as much
 // each (kBn128Cost, measured) and come in twice the number, so they win where they fill the waves better.
+bool g_gemm_persist_all = false;  // tests: the persistent kernel for every shape it supports
 int g_gemm_force_bn = 0;  // 128 / 256: token tile for every batch of more than 128 rows (0: chosen by wave count)
 static int pick_bn_waves(int M, int N) {
   const int bn = pick_bn(M);
@@ -300,7 +301,8 @@ void gemm_tc_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* o
     gemv_dense_run(w, x, M, ldx, out, ldo, out_f32, bias, 0, st);
     return;
   }
-  if (g_gemm_persist && (tp == nullptr || tp->size <= 1) && force_splits == 0 && gemm_persist_supported(w, M, ldx)) {
+  if (g_gemm_persist && (tp == nullptr || tp->size <= 1) && force_splits == 0 && g_gemm_force_bn == 0 && gemm_persist_supported(w, M, ldx) &&
+      (g_gemm_persist_all || gemm_persist_preferred(w, M))) {
     gemm_persist_run(w, x, M, ldx, out, ldo, out_f32, bias, status, st);
     return;
   }

@@ -138,9 +138,12 @@ int launch_prefill_attention(const void* q, long long q_stride, const void* kc, 
 // attention_tc.cu: tcgen05 / TMA prefill attention; tile arrays hold prefill_attention_tc_tile_rows(D) query rows per tile
 int prefill_attention_tc_tile_rows(int D);
 extern bool g_gemm_persist;    // gemm_persist.cu: prefill-size JQ4 projections on the persistent kernel (off by default)
+extern bool g_gemm_persist_ordered;  // its issuers take turns in k-block order (bit-reproducible; default) or race
 bool gemm_persist_supported(const GemmWeightDesc* w, int M, int ldx);
+bool gemm_persist_preferred(const GemmWeightDesc* w, int M);
 void gemm_persist_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias, int* status,
                       cudaStream_t st);
+extern bool g_gemm_persist_all;
 extern int g_gemm_force_bn;    // gemm.cu: token tile for prefill-size batches (tests, comparisons)
 extern bool g_gemv_dense;      // gemm.cu: <= 8-row JQ4 projections on the mma.sync GEMV (default on)
 bool gemv_dense_supported(const GemmWeightDesc* w, int M, int ldx);

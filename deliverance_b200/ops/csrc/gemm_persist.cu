@@ -10,9 +10,9 @@
 // from tensor memory to global memory while the issuers are already in the next tile.
 //   warp 0      producers: lanes 0 / 1 copy the packed-weight stage of the even / odd k-blocks, lanes 2 / 3 the activation stage
 //               (a thread can start a copy only every few hundred nanoseconds, lanes of one warp do so side by side)
-//   warps 1, 2  MMA issuers, even / odd k-blocks, both into the tile's accumulator: the owner of a tile's first k-block (always
-//               issuer 0: the number of k-blocks must be even) overwrites, and the other one does not issue into the tile before
-//               that first k-block has retired (barrier `first`)
+//   warps 1-3, 24  four MMA issuers, k-blocks g, g + 4, ..., all into the tile's accumulator: the owner of a tile's first k-block
+//               (always issuer 0: the number of k-blocks is a multiple of 4) overwrites, and the others do not issue into the
+//               tile before that first k-block has retired (barrier `first`)
 //   warps 4-19  four groups of four warps expand nibbles to bf16 pairs and store them into the tensor-memory A ring (group g takes
 //               the k-blocks g, g + 4, ...; a warp owns the TMEM lane quarter warp % 4), exactly as in gemm_tc.cuh
 //   warps 20-23 epilogue: warp % 4 = TMEM lane quarter; a thread holds one weight row (= output column) of the tile, reads its 128
@@ -22,12 +22,18 @@
 // Every wait is bounded (common.cuh); on expiry the CTA raises its abort flag, every role leaves its loop, copies and MMAs in flight
 // are given a bounded time to land, tensor memory is freed and a status word tells the host.
 //
-// Status (B200, JQ4, M = 2048 / 8192): 19456 x 2560 186 / 719 us against 204 / 747 for the one-tile kernel, 6144 x 2560 67 / 231
-// against 70 / 246, 2560 x 4096 54 / 167 against 57 / 161, 2560 x 9728 121 / 415 against 119 / 387: a few per cent either way, so the
-// dispatcher does not pick it (binding gemm_persist / DLV_GEMM_PERSIST=1 switch it on). In-kernel clocks: per k-block an issuer spends
-// about 1,070 cycles issuing (its 8 MMAs behind the other issuer's 8: the pipe is busy), 340 waiting for its operands and 310 between
-// turns, i.e. the two issuers keep the pipe 59 % busy; letting an issuer take two k-blocks per turn moved the time into the operand
-// waits (the four-stage tensor-memory ring of expanded weights) and changed nothing overall.
+// Status (B200, JQ4, M = 2048 / 8192 tokens, us; one-tile kernel in brackets), issuers racing: 6144 x 2560 61 / 224 (70 / 245),
+// 2560 x 4096 48 / 161 (57 / 160), 19456 x 2560 180 / 720 (202 / 734), 2560 x 9728 112 / 419 (127 / 368). With two issuers it only
+// matched the one-tile kernel: in-kernel clocks showed each issuer 1,070 cycles per k-block issuing (its 8 MMAs queue behind the
+// other's: the pipe is busy), 340 waiting for operands and 310 between turns, i.e. the pipe 59 % busy; four issuers cover each
+// other's turn-around. Letting an issuer take two k-blocks per turn instead moved the time into the operand waits (the four-stage
+// ring of expanded weights).
+// Racing issuers reach the one accumulator in an order that varies from launch to launch, and fp32 accumulation depends on the
+// order: repeated launches differed in the last bits. With the issuers taking turns in k-block order (a counter in shared memory;
+// the default of this kernel) the results are bit-reproducible and the gain is gone: 75 / 246, 60 / 156, 199 / 770, 129 / 344 us,
+// because the gain came from several threads having MMAs queued at the same time. The engine promises the same logits for the same
+// prompt (prefix-cache hits, replicas, tensor-parallel ranks), and the whole prefill moved by 0.6 % (99.7K against 99.1K tokens/s,
+// its chunks are 8192 tokens), so the kernel is off by default: DLV_GEMM_PERSIST=1 turns it on ordered, =race turns it on racing.
 //
 // The reference has no counterpart (its prefill multiplies token by token on the CPU: core/.../generator/MLPBlock.java and
 // native/src/main/c/simd/vector_simd.c:595).
@@ -52,7 +58,8 @@ constexpr int kPOffRaw = kPNX * kPXStage;
 constexpr int kPOffCtrl = kPOffRaw + kPNR * kPRaw;
 constexpr int kPBytes = kPOffCtrl + 1024 + 1024;  // barriers + alignment slack
 constexpr int kPTmemA = 256;                   // accumulators at columns [0, 256), A ring behind them
-constexpr int kPThreads = 768;
+constexpr int kPNI = 4;                        // MMA-issuing threads (k-blocks g, g + 4, ... each)
+constexpr int kPThreads = 800;                 // 25 warps: 72 registers per thread
 
 struct PersistParams {
   const uint8_t* wq;
@@ -61,6 +68,7 @@ struct PersistParams {
   int* status;
   int M, N, K, ldo, out_f32;
   int n_tiles, m_tiles, nkb, total_tiles;
+  int ordered;  // issuers take turns in k-block order (bit-reproducible results)
 };
 
 __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -76,9 +84,10 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
   uint64_t* bar_acc_full = bar_a_empty + kPNA;   // [2]
   uint64_t* bar_acc_empty = bar_acc_full + 2;    // [2]
   uint64_t* bar_first = bar_acc_empty + 2;       // [2]
-  uint64_t* bar_drain = bar_first + 2;           // [2] issuers' outstanding MMAs (abort path)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_drain + 2);
+  uint64_t* bar_drain = bar_first + 2;           // [kPNI] issuers' outstanding MMAs (abort path)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_drain + kPNI);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* issue_seq = abort_flag + 1;  // number of k-blocks whose MMAs have been issued (the issuers take turns in k-block order)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // tiles of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; consecutive tiles share a weight tile (m is the fast index)
@@ -101,12 +110,13 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
       mbar_init(smem_u32(&bar_a_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bar_acc_full[b]), 2);
+      mbar_init(smem_u32(&bar_acc_full[b]), kPNI);
       mbar_init(smem_u32(&bar_acc_empty[b]), 4);
       mbar_init(smem_u32(&bar_first[b]), 1);
-      mbar_init(smem_u32(&bar_drain[b]), 1);
     }
+    for (int j = 0; j < kPNI; ++j) mbar_init(smem_u32(&bar_drain[j]), 1);
     *abort_flag = 0;
+    *issue_seq = 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
@@ -168,15 +178,15 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         }
       }
     }
-  } else if (warp == 1 || warp == 2) {
+  } else if (warp == 1 || warp == 2 || warp == 3 || warp == 24) {
     // ---------------- MMA issuers (one lane each) ----------------
     if (lane == 0) {
-      const int par = warp - 1;
+      const int par = warp == 24 ? 3 : warp - 1;
       constexpr uint32_t idesc = umma_idesc_bf16(kGemmBM, kPT);
       const uint64_t desc_x0 = umma_desc_k_sw128(smem_u32(smem));
       bool ok = true;
       int it = 0, i = par;
-      for (int g = par; g < total_kb && ok; g += 2, i += 2) {
+      for (int g = par; g < total_kb && ok; g += kPNI, i += kPNI) {
         if (i >= nkb) { i -= nkb; ++it; }
         const int b = it & 1;
         if (i == par) {
@@ -189,6 +199,21 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         ok = mbar_wait(smem_u32(&bar_a_full[sa]), static_cast<uint32_t>(g / kPNA) & 1, abort_flag, p.status) &&
              mbar_wait(smem_u32(&bar_x_full[sx]), static_cast<uint32_t>(g / kPNX) & 1, abort_flag, p.status);
         if (!ok) break;
+        // Turn-taking: the MMAs of k-block g are issued after those of k-block g - 1 (by another thread). The tensor pipe executes
+        // in the order of issue, so the accumulation order is the k order and results are bit-reproducible; the issuer whose turn
+        // comes next has its operands checked already and starts the moment its predecessor has issued.
+        if (p.ordered && *issue_seq < g) {
+            const long long t0 = clock64();
+            while (*issue_seq < g) {
+                if (clock64() - t0 > kWaitLimitCycles || *abort_flag) {
+                    *abort_flag = 1;
+                    if (p.status) atomicCAS(p.status, kStatusOk, kStatusBarrierTimeout);
+                    ok = false;
+                    break;
+                }
+            }
+            if (!ok) break;
+        }
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + b * kPT;
         const uint64_t dx = desc_x0 + static_cast<uint64_t>((sx * kPXStage) >> 4);
@@ -197,10 +222,12 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
           const uint64_t db = dx + static_cast<uint64_t>(((k4 >> 2) * (kPT * 128) + (k4 & 3) * 32) >> 4);
           umma_bf16_ts(tmem_acc, tmem_base + kPTmemA + sa * kGemmTmemAStage + k4 * 8, db, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
         }
+        __threadfence_block();
+        *issue_seq = g + 1;
         umma_commit(smem_u32(&bar_a_empty[sa]));
         umma_commit(smem_u32(&bar_x_empty[sx]));
         if (i == 0) umma_commit(smem_u32(&bar_first[b]));
-        if (i + 2 >= nkb) umma_commit(smem_u32(&bar_acc_full[b]));  // this issuer's last k-block of the tile
+        if (i + kPNI >= nkb) umma_commit(smem_u32(&bar_acc_full[b]));  // this issuer's last k-block of the tile
       }
       if (!ok) {
         umma_commit(smem_u32(&bar_drain[par]));
@@ -297,11 +324,16 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
 
 }  // namespace
 
-bool g_gemm_persist = false;  // prefill-size JQ4 projections on the persistent kernel (switched by the binding gemm_persist)
+bool g_gemm_persist = false;         // prefill-size JQ4 projections on the persistent kernel (binding gemm_persist; off by default, see Status above)
+bool g_gemm_persist_ordered = true;  // its issuers take turns in k-block order; false: they race (faster, results vary in the last bits)
 
 bool gemm_persist_supported(const GemmWeightDesc* w, int M, int ldx) {
-  return w->is_q4 && w->K % 256 == 0 && w->N % 4 == 0 && ldx % 8 == 0 && w->K % 64 == 0 && M >= 256;
+  // every issuer must have the same k-blocks in every tile
+  return w->is_q4 && w->K % (kGemmBK * kPNI) == 0 && w->N % 4 == 0 && ldx % 8 == 0 && M >= 256;
 }
+// Where the racing form measured faster than the one-tile kernel (B200, four issuers): every shape at 2048 tokens by 11-16 %, wide
+// projections (6144 and 19456 rows) also at 8192 tokens by 2-9 %; narrow deep ones (2560 x 9728) lose 14 % at 8192 tokens.
+bool gemm_persist_preferred(const GemmWeightDesc* w, int M) { return M <= 4096 || w->N >= 4096; }
 
 void gemm_persist_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias, int* status,
                       cudaStream_t st) {
@@ -324,6 +356,7 @@ void gemm_persist_run(const GemmWeightDesc* w, const void* x, int M, int ldx, vo
   p.m_tiles = (M + kPT - 1) / kPT;
   p.nkb = w->K / kGemmBK;
   p.total_tiles = p.n_tiles * p.m_tiles;
+  p.ordered = g_gemm_persist_ordered ? 1 : 0;
   CUtensorMap map_x;
   encode_map_kchunks(&map_x, x, static_cast<uint64_t>(M), static_cast<uint64_t>(w->K), static_cast<uint64_t>(ldx) * 2, kPT);
   const int grid = p.total_tiles < gemm_num_sms() ? p.total_tiles : gemm_num_sms();

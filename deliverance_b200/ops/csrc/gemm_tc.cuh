@@ -127,8 +127,11 @@ struct GemmSmem {
   // warps, four dequant groups, kNI MMA issuers). mbarrier waits only know the PARITY of a phase, so a thread must see every
   // phase of the barriers it waits on: each ring depth is a multiple of the number of its producers and of its consumers,
   // which ties every stage to one producer and one consumer for the whole kernel.
-  static constexpr int kNI = BN <= 64 ? 4 : 2;  // MMA-issuing warps (see the issuer loop)
-  static constexpr bool kSharedAcc = BN > 128;  // the issuers add into one accumulator (tensor memory has no room for two of 256 columns)
+  static constexpr int kNI = BN <= 64 ? 4 : (BN == 128 ? 2 : 1);  // MMA-issuing warps (see the issuer loop)
+  // Issuers that add into ONE accumulator (the only way to have several at BN = 256, where tensor memory has no room for a second
+  // accumulator) are written out below but not used: they changed nothing measurable there, and the order in which two racing
+  // issuers' k-blocks reach the accumulator varies from launch to launch, so results were not bit-reproducible.
+  static constexpr bool kSharedAcc = false;
   static constexpr int kNW = Q4 ? 0 : (BN <= 64 ? 4 : 2);         // dense: W and X rings of equal depth
   static constexpr int kAccCols = kSharedAcc ? BN : kNI * BN;
   static constexpr int kTmemA = kAccCols < 64 ? 64 : kAccCols;  // JQ4: the A-operand ring in tensor memory follows the accumulators

@@ -635,7 +635,7 @@ def test_small_batch_gemv_matches_fp32(N, K):
             assert tuple(h.shape) == (M, N // 2) and _rel(h.cpu().float(), exp) < 2e-2
 
 
-@pytest.mark.parametrize("N,K,M", [(640, 1024, 500), (384, 512, 257), (2560, 4096, 2048), (200, 256, 1000)])
+@pytest.mark.parametrize("N,K,M", [(640, 1024, 500), (384, 512, 257), (2560, 4096, 2048), (200, 512, 1000)])
 def test_persistent_prefill_gemm(N, K, M):
     """The persistent JQ4 GEMM (many tiles per CTA, epilogue under the next tile's main loop) against the fp32 product and against
     the one-tile-per-CTA kernel: bf16 and fp32 output, bias, ragged last token tile and last weight tile."""
@@ -648,15 +648,21 @@ def test_persistent_prefill_gemm(N, K, M):
     lw = LinearWeight(Q4Tensor(p, s, (N, K))).to(DEV)
     lwb = LinearWeight(Q4Tensor(p, s, (N, K)), bias=bias).to(DEV)
     x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
-    y0 = ops.linear(x.to(DEV), lw)
-    ext.gemm_persist(True)
+    ext.gemm_persist(False)
     try:
+        y0 = ops.linear(x.to(DEV), lw)
+        ext.gemm_persist(True, True, True)  # issuers in k-block order: repeated launches are bit-identical
         y = ops.linear(x.to(DEV), lw)
+        y_again = ops.linear(x.to(DEV), lw)
         y32 = ops.linear(x.to(DEV), lwb, out_f32=True)
+        ext.gemm_persist(True, True, False)  # racing issuers: same product up to the accumulation order
+        y_race = ops.linear(x.to(DEV), lw)
         torch.cuda.synchronize()
         ops.check_status()
     finally:
         ext.gemm_persist(False)
+    assert torch.equal(y, y_again)
+    assert _rel(y_race.cpu().float(), y.cpu().float()) < 1e-2
     ref_y = x.float() @ wd.t()
     assert _rel(y.cpu().float(), ref_y) < 1e-2 and _rel(y32.cpu(), ref_y + bias) < 1e-2
     assert _rel(y.cpu().float(), y0.cpu().float()) < 1e-2
