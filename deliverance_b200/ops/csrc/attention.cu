@@ -388,7 +388,7 @@ template <int D>
 __global__ void __launch_bounds__(128, (D <= 128 ? 2 : 1)) decode_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int bt_stride,
-    const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* __restrict__ arrivals,
     int H, int KV, int page_size, float scale, float softcap, int window, int splits) {
   pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
   pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
@@ -599,13 +599,69 @@ __global__ void __launch_bounds__(128, (D <= 128 ? 2 : 1)) decode_attn_mma_kerne
       }
     }
   }
+  if (splits == 1 || arrivals == nullptr) return;  // (no arrival counters: decode_merge_kernel follows)
+
+  // ---- (opt-in; measured slower than decode_merge_kernel) merge of the splits by the CTA that finishes last for this
+  // (sequence, KV head): no second launch.
+  // Every CTA publishes its partials (fence), then counts itself in; the one that sees splits - 1 earlier arrivals puts the
+  // counter back to zero for the next launch and combines all partials in split order, so the result does not depend on
+  // which CTA came last. Nothing waits.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int prev = atomicAdd(arrivals + b * KV + kvh, 1);
+    s_last = prev == splits - 1;
+    if (s_last) arrivals[b * KV + kvh] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float* w_s = mg;  // [G][splits] weights, then [G] denominators (the warp-merge area is free again)
+  float* den_s = mg + G * splits;
+  if (G * (splits + 1) <= L::kMerge / 4) {
+    for (int r = warp; r < G; r += 4) {
+      const long long base = (static_cast<long long>(b) * H + kvh * G + r) * splits;
+      float m = -INFINITY;
+      for (int s2 = lane; s2 < splits; s2 += 32) m = fmaxf(m, __ldcg(part_ml + (base + s2) * 2));
+      m = warp_max(m);
+      float den = 0.f;
+      for (int s2 = lane; s2 < splits; s2 += 32) {
+        const float ms = __ldcg(part_ml + (base + s2) * 2);
+        const float w = (ms == -INFINITY) ? 0.f : __expf(ms - m);
+        w_s[r * splits + s2] = w;
+        den += w * __ldcg(part_ml + (base + s2) * 2 + 1);
+      }
+      den = warp_sum(den);
+      if (lane == 0) den_s[r] = den;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * (D / 2); idx += 128) {
+      const int r = idx / (D / 2), d = (idx % (D / 2)) * 2;
+      const int h = kvh * G + r;
+      const long long base = (static_cast<long long>(b) * H + h) * splits;
+      float n0 = 0.f, n1 = 0.f;
+#pragma unroll 4
+      for (int s2 = 0; s2 < splits; ++s2) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(part_o + (base + s2) * D + d));
+        const float w = w_s[r * splits + s2];
+        n0 += w * v.x;
+        n1 += w * v.y;
+      }
+      const float den = den_s[r];
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      *reinterpret_cast<uint32_t*>(out + (static_cast<long long>(b) * H + h) * D + d) = pack_bf162(n0 * inv, n1 * inv);
+    }
+  }
 }
 
 template <int D>
 static int launch_decode_mma_t(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
-                               const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int page, float scale,
-                               float cap, int window, int splits, cudaStream_t st) {
+                               const int* ctx, void* out, float* po, float* pml, int* arrivals, int B, int H, int KV, int page,
+                               float scale, float cap, int window, int splits, cudaStream_t st) {
   using L = DecodeMma<D>;
+  // the in-kernel merge keeps its weights in the warp-merge area of shared memory
+  if (splits > 1 && (H / KV) * (splits + 1) > L::kMerge / 4) arrivals = nullptr;
   static PerDeviceOnce attr_once;
   if (attr_once.first()) {
     cudaFuncSetAttribute(decode_attn_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
@@ -613,9 +669,9 @@ static int launch_decode_mma_t(const void* q, long long q_stride, const void* kc
   dim3 grid(B, KV, splits);
   launch_pdl(decode_attn_mma_kernel<D>, dim3(grid), dim3(128), L::kBytes, st, static_cast<const __nv_bfloat16*>(q), q_stride,
                                                           static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt,
-                                                          bt_stride, ctx, static_cast<__nv_bfloat16*>(out), po, pml, H, KV, page, scale, cap,
-                                                          window, splits);
-  if (splits > 1) {
+                                                          bt_stride, ctx, static_cast<__nv_bfloat16*>(out), po, pml, arrivals, H, KV, page, scale,
+                                                          cap, window, splits);
+  if (splits > 1 && arrivals == nullptr) {
     dim3 g2(B, H);
     launch_pdl(decode_merge_kernel, dim3(g2), dim3(D), 0, st, po, pml, static_cast<__nv_bfloat16*>(out), H, D, splits);
   }
@@ -624,15 +680,18 @@ static int launch_decode_mma_t(const void* q, long long q_stride, const void* kc
 
 // impl: 0 = tensor-core kernel when it applies (group <= 16, page_size % 16 == 0), 1 = CUDA-core kernel
 int launch_decode_attention_impl(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
-                                 const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int D, int page, float scale,
-                                 float cap, int window, int splits, int impl, cudaStream_t st) {
+                                 const int* ctx, void* out, float* po, float* pml, int* arrivals, int B, int H, int KV, int D, int page,
+                                 float scale, float cap, int window, int splits, int impl, cudaStream_t st) {
   if (B == 0) return 0;
   const int G = H / KV;
   if (impl == 0 && G <= 16 && page % 16 == 0 && (q_stride % 2) == 0) {
     switch (D) {
-      case 64: return launch_decode_mma_t<64>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, B, H, KV, page, scale, cap, window, splits, st);
-      case 128: return launch_decode_mma_t<128>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, B, H, KV, page, scale, cap, window, splits, st);
-      case 256: return launch_decode_mma_t<256>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, B, H, KV, page, scale, cap, window, splits, st);
+      case 64: return launch_decode_mma_t<64>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, arrivals, B, H, KV, page, scale, cap, window, splits,
+                                                st);
+      case 128: return launch_decode_mma_t<128>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, arrivals, B, H, KV, page, scale, cap, window, splits,
+                                                st);
+      case 256: return launch_decode_mma_t<256>(q, q_stride, kc, vc, bt, bt_stride, ctx, out, po, pml, arrivals, B, H, KV, page, scale, cap, window, splits,
+                                                st);
       default: return 1;
     }
   }

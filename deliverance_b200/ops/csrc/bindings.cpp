@@ -5,6 +5,7 @@
 #include <torch/extension.h>
 
 #include <memory>
+#include <mutex>
 #include <unordered_map>
 
 #include "chain_api.h"
@@ -687,6 +688,27 @@ void rope_kv(Tensor& qkv, const Tensor& positions, c10::optional<Tensor> slots, 
 
 // ---- attention ------------------------------------------------------------------------------------------------------
 // q: view [B, H*D] bf16 with arbitrary row stride (the q part of the fused qkv activation)
+// Arrival counters of the split-KV decode kernel (one per sequence and KV head; the CTA that arrives last merges the splits and
+// puts its counter back to zero, so the array stays zero between launches). One array per device, made on first use outside any
+// stream capture; launches on one device are expected on one stream at a time (the engine's), nullptr means "merge in a second
+// kernel" and is what a capture that comes before any eager call gets, as does a batch with more counters than the array holds.
+bool g_decode_merge_in_kernel = false;  // measured slower than the merge launch (see ops.set_decode_merge_in_kernel)
+constexpr int64_t kSplitCounters = 1 << 16;
+int* split_arrival_counters(int device, int64_t needed) {
+  static std::mutex mu;
+  static std::unordered_map<int, Tensor> per_device;
+  if (needed > kSplitCounters) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = per_device.find(device);
+  if (it == per_device.end()) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(cur_stream(), &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
+    Tensor t = at::zeros({kSplitCounters}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+    it = per_device.emplace(device, t).first;
+  }
+  return it->second.data_ptr<int>();
+}
+
 Tensor decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables, const Tensor& ctx_lens,
                         int64_t H, double scale, double softcap, int64_t window, int64_t splits, int64_t impl) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 2 && q.stride(1) == 1, "q must be bf16 [B, H*D]");
@@ -711,8 +733,9 @@ Tensor decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_
     pop = po.data_ptr<float>();
     pmlp = pml.data_ptr<float>();
   }
+  int* arrivals = (splits > 1 && g_decode_merge_in_kernel) ? split_arrival_counters(q.device().index(), static_cast<int64_t>(B) * KV) : nullptr;
   int rc = dlv::launch_decode_attention_impl(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(),
-                                             static_cast<int>(block_tables.stride(0)), ctx_lens.data_ptr<int>(), out.data_ptr(), pop, pmlp, B,
+                                             static_cast<int>(block_tables.stride(0)), ctx_lens.data_ptr<int>(), out.data_ptr(), pop, pmlp, arrivals, B,
                                              static_cast<int>(H), KV, D, page, static_cast<float>(scale), static_cast<float>(softcap),
                                              static_cast<int>(window), static_cast<int>(splits), static_cast<int>(impl), cur_stream());
   TORCH_CHECK(rc == 0, "decode attention: unsupported head_dim / group size (code ", rc, ")");
@@ -1473,6 +1496,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         dlv::g_gemm_persist_ordered = ordered;
       },
       py::arg("on"), py::arg("all") = false, py::arg("ordered") = true);
+  m.def("decode_merge_in_kernel", [](bool on) { g_decode_merge_in_kernel = on; });
   m.def("gemm_force_bn", [](int64_t bn) { dlv::g_gemm_force_bn = static_cast<int>(bn); });
   m.def("set_bounds_check", &set_bounds_check);
   m.def("check_guards", &check_guards);

@@ -128,8 +128,8 @@ int launch_decode_attention(const void* q, long long q_stride, const void* kc, c
                             const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int D, int page, float scale,
                             float cap, int window, int splits, cudaStream_t st);
 int launch_decode_attention_impl(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
-                                 const int* ctx, void* out, float* po, float* pml, int B, int H, int KV, int D, int page, float scale,
-                                 float cap, int window, int splits, int impl, cudaStream_t st);
+                                 const int* ctx, void* out, float* po, float* pml, int* arrivals, int B, int H, int KV, int D, int page,
+                                 float scale, float cap, int window, int splits, int impl, cudaStream_t st);
 int launch_prefill_attention(const void* q, long long q_stride, const void* kc, const void* vc, const int* bt, int bt_stride,
                              const int* q_start, const int* q_len, const int* ctx, const int* tile_seq, const int* tile_q0,
                              int num_tiles, void* out, int H, int KV, int D, int page, float scale, float cap, int window,

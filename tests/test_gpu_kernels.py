@@ -156,6 +156,31 @@ def test_decode_attention(D, H, KV, splits, softcap, window, impl):
     assert _rel(o.cpu(), o_ref) < 1e-2
 
 
+@pytest.mark.parametrize("D,H,KV,splits", [(128, 32, 8, 4), (64, 8, 4, 7), (256, 4, 2, 2), (128, 16, 1, 16)])
+def test_decode_attention_merges_splits_in_kernel(D, H, KV, splits):
+    """Split-KV decode, opt-in form: the CTA that finishes last for a (sequence, KV head) merges the splits itself. Same result as
+    the merge in a second launch, bit-identical from launch to launch (the arrival counters return to zero), splits without keys included."""
+    ctx = [1, 17, 64, 100, 257, 700, 1500]
+    kc, vc, bt = _paged_setup(ctx, KV, D, seed=5)
+    B = len(ctx)
+    q = (torch.randn(B, H * D) * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    cl = torch.tensor(ctx, dtype=torch.int32)
+    o_ref = ref.paged_attention(q.float().reshape(B, H, D), kc.float(), vc.float(), bt, torch.arange(B), torch.ones(B, dtype=torch.long),
+                                cl, scale, 0.0, 0, True).reshape(B, H * D)
+    args = (q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cl.to(DEV), H, scale, 0.0, 0, splits, 0)
+    o_two = ops.decode_attention(*args)
+    ops.set_decode_merge_in_kernel(True)
+    try:
+        outs = [ops.decode_attention(*args) for _ in range(3)]
+        torch.cuda.synchronize()
+    finally:
+        ops.set_decode_merge_in_kernel(False)
+    assert _rel(outs[0].cpu(), o_ref) < 1e-2
+    assert _rel(outs[0].cpu().float(), o_two.cpu().float()) < 4e-3
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
 @pytest.mark.parametrize("D,H,KV", [(128, 8, 2), (64, 8, 4), (256, 4, 2)])
 @pytest.mark.parametrize("softcap,window", [(0.0, 0), (50.0, 0), (0.0, 40)])
 def test_prefill_attention(D, H, KV, softcap, window):
