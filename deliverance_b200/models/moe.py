@@ -11,6 +11,8 @@ single kernels (csrc/moe.cu) and each expert GEMM is a tcgen05 launch on its con
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -18,6 +20,7 @@ from ..ops import ref
 
 
 _SM_COUNT = 148  # B200
+_ROUTE_ONE_LAUNCH = [os.environ.get("DLV_MOE_ROUTE", "fused") != "split"]  # decode-size routing in one launch ("split": the separate kernels)
 
 
 def moe_forward(model, i: int, lw, x: torch.Tensor) -> torch.Tensor:
@@ -92,19 +95,32 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
     T, H = x.shape
     rows = T * k
     ep = ne != E
+    bn = ops.moe_token_tile(rows if not ep else max(1, rows * ne // E), ne, lw.experts_gate_up_grouped.q4)
+    if lw.fused_act_experts:
+        bn = max(bn, 16)  # interleaved expert rows exist for the tensor-core grouped GEMM's epilogue only
+    max_items = min((rows + bn - 1) // bn + ne, rows) if rows >= ne else rows
+    max_items = max(1, max_items)
+    rng = None
+    xs = None
     with st("moe.route"):
-        # weights [T, k] fp32, expert ids [T, k], counts [E], offsets [E + 1], perm: grouped row -> (token * k + slot), pos: inverse
-        w, idx, counts, offsets, perm, pos = e.moe_route(logits.contiguous(), k, 0 if mode == "softmax_topk" else 1, bool(renorm))
-        ops._count(2)
+        # weights [T, k] fp32, expert ids [T, k], counts [E], offsets [E + 1], perm: grouped row -> (token * k + slot), pos: inverse,
+        # items: the grouped GEMM's work list. Decode-size batches get all of it from one launch.
+        mode_i = 0 if mode == "softmax_topk" else 1
+        routed = e.moe_route_items(logits.contiguous(), k, mode_i, bool(renorm), e0, ne, bn, max_items) if _ROUTE_ONE_LAUNCH[0] else []
+        if routed:
+            w, idx, counts, offsets, perm, pos, items = routed
+            ops._count()
+        else:
+            w, idx, counts, offsets, perm, pos = e.moe_route(logits.contiguous(), k, mode_i, bool(renorm))
+            items = e.moe_items(offsets, e0, ne, bn, max_items)
+            ops._count(3)
         rng = (offsets, e0, ne) if ep else (None, 0, 0)
-        xs = e.moe_gather(x, perm, k, *rng)  # [T * k, H] rows grouped by expert (only the local experts' rows are filled)
-        bn = ops.moe_token_tile(rows if not ep else max(1, rows * ne // E), ne, lw.experts_gate_up_grouped.q4)
-        if lw.fused_act_experts:
-            bn = max(bn, 16)  # interleaved expert rows exist for the tensor-core grouped GEMM's epilogue only
-        max_items = min((rows + bn - 1) // bn + ne, rows) if rows >= ne else rows
-        max_items = max(1, max_items)
-        items = e.moe_items(offsets, e0, ne, bn, max_items)
-        ops._count(2)
+
+    def gathered():
+        """x rows in expert-grouped order [T * k, H] (only the local experts' rows are filled)."""
+        ops._count()
+        return e.moe_gather(x, perm, k, *rng)
+
     gu_w, down_w = lw.experts_gate_up_grouped, lw.experts_down_grouped
     small = bn <= 64  # decode-sized groups: split K so that more CTAs stream weights
 
@@ -119,16 +135,19 @@ def _moe_cuda(model, lw, x, logits, E, k, mode, renorm, act, e0, ne):
 
     if lw.fused_act_experts and bn >= 16:
         with st("moe.gate_up"):  # act(gate) * up in the grouped GEMM's epilogue (interleaved expert rows)
-            hmid = gu_w.run_act(xs, items, bn, k_splits(gu_w), act)
+            hmid = gu_w.run_act(gathered(), items, bn, k_splits(gu_w), act)
     else:
         if lw.fused_act_experts:
             raise RuntimeError("interleaved expert weights need the tensor-core grouped GEMM (token tile >= 16)")
         hmid = None
         if bn <= 8:
-            with st("moe.gate_up"):  # a handful of rows per expert: grouped GEMV with the gated activation in its epilogue
-                hmid = gu_w.run_gemv_act(xs, items, act)
+            # a handful of rows per expert: grouped GEMV with the gated activation in its epilogue; it reads the token rows through
+            # the permutation, so the copy into expert order is skipped
+            with st("moe.gate_up"):
+                hmid = gu_w.run_gemv_act(x, items, act, perm, k)
         if hmid is None:
             with st("moe.gate_up"):
+                xs = gathered()
                 gu = gu_w.run(xs, items, bn, k_splits(gu_w))
             with st("moe.activation_multiply"):
                 hmid = ops.act_mul(gu, act)

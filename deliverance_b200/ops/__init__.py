@@ -535,14 +535,15 @@ class GroupedLinearWeight:
         _count()
         return self.handle.run_grouped(xs, items, self.N, bn, splits, out)
 
-    def run_gemv_act(self, xs: torch.Tensor, items: torch.Tensor, act: str) -> Optional[torch.Tensor]:
+    def run_gemv_act(self, xs: torch.Tensor, items: torch.Tensor, act: str, perm: Optional[torch.Tensor] = None, k: int = 1) -> Optional[torch.Tensor]:
         """Decode-size work items (at most 8 rows each): gate|up projection with ``act(gate) * up`` in the epilogue of the mma.sync
         grouped GEMV; the experts' rows are in plain order (gate rows, then up rows). ``None`` when the shape or the activation is
-        outside that kernel (the caller then runs projection and activation as two steps)."""
+        outside that kernel (the caller then runs projection and activation as two steps). With ``perm`` (the grouping permutation,
+        ``[tokens * k]``) ``xs`` is the ungathered ``[tokens, K]`` activation: grouped row r reads token ``perm[r] // k``."""
         kind = fused_act_kind(act)
         if kind == 0 or not self.q4:
             return None
-        out = self.handle.run_grouped_gemv_act(xs, items, self.N, kind)
+        out = self.handle.run_grouped_gemv_act(xs, items, self.N, kind, perm, k)
         if out is None:
             return None
         _count()

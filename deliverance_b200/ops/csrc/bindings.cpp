@@ -335,17 +335,27 @@ class GemmWeight {
   // Decode-size work items (at most 8 rows each) of a gated MLP: gate | up projection with act(gate) * up in the epilogue on the
   // mma.sync grouped GEMV (plain row order: gate rows, then up rows). Returns [rows, n_per_expert / 2], or an undefined tensor when
   // the shape is outside that kernel.
-  Tensor run_grouped_gemv_act(const Tensor& xs, const Tensor& items, int64_t n_per_expert, int64_t act) {
+  // With `perm` (the grouping permutation of moe_route, [rows]) and k, xs is the UNGATHERED activation [tokens, K]: grouped row r
+  // reads token perm[r] / k, and the copy into expert order is skipped.
+  Tensor run_grouped_gemv_act(const Tensor& xs, const Tensor& items, int64_t n_per_expert, int64_t act, c10::optional<Tensor> perm, int64_t k) {
     TORCH_CHECK(xs.is_cuda() && xs.scalar_type() == at::kBFloat16 && xs.dim() == 2 && xs.size(1) == desc_.K && xs.stride(1) == 1, "xs must be bf16 [rows, K]");
     TORCH_CHECK(xs.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(xs.data_ptr()) & 15) == 0, "xs rows must be 16-byte aligned");
     TORCH_CHECK(items.is_cuda() && items.scalar_type() == at::kInt && items.dim() == 2 && items.size(1) == 4 && items.is_contiguous(), "items must be int32 [n, 4]");
     const int64_t per = desc_.is_q4 ? ((n_per_expert + 127) / 128) * 128 : n_per_expert;
     TORCH_CHECK(n_per_expert > 0 && n_per_expert % 2 == 0 && desc_.N % per == 0, "stacked weight rows are not a multiple of the per-expert rows");
     c10::cuda::CUDAGuard guard(xs.device());
-    Tensor out = new_out({xs.size(0), n_per_expert / 2}, xs.options());
+    const int* map = nullptr;
+    int64_t rows = xs.size(0);
+    if (perm.has_value()) {
+      const Tensor& pm = perm.value();
+      TORCH_CHECK(pm.is_cuda() && pm.scalar_type() == at::kInt && pm.is_contiguous() && k >= 1 && pm.numel() == xs.size(0) * k, "perm must be int32 [tokens * k]");
+      map = pm.data_ptr<int>();
+      rows = pm.numel();
+    }
+    Tensor out = new_out({rows, n_per_expert / 2}, xs.options());
     const bool done = dlv::gemv_grouped_act_run(&desc_, static_cast<int>(n_per_expert), xs.data_ptr(), static_cast<int>(xs.stride(0)), out.data_ptr(),
                                                 static_cast<int>(out.stride(0)), items.data_ptr<int>(), static_cast<int>(items.size(0)), static_cast<int>(act),
-                                                cur_stream());
+                                                map, static_cast<int>(k), cur_stream());
     check_last_error("grouped gemv (gated activation) launch");
     return done ? out : Tensor();
   }
@@ -1079,6 +1089,26 @@ std::vector<Tensor> moe_route(const Tensor& logits, int64_t k, int64_t mode, boo
   check_last_error("moe_route");
   return {w, idx, counts, offsets, perm, pos};
 }
+// moe_route and moe_items of a decode-size batch in one launch: {w, idx, counts, offsets, perm, pos, items}; an empty vector when the
+// batch is too large for the single-CTA kernel (the caller then uses the two functions).
+std::vector<Tensor> moe_route_items(const Tensor& logits, int64_t k, int64_t mode, bool renorm, int64_t e0, int64_t ne, int64_t bn, int64_t max_items) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.is_contiguous(), "router logits must be fp32 [T, E]");
+  const int T = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
+  TORCH_CHECK(k >= 1 && k <= 16 && k <= E && E <= 1024, "unsupported top-k / expert count");
+  TORCH_CHECK(e0 >= 0 && ne >= 1 && e0 + ne <= E && bn >= 1 && max_items >= 1, "bad work-list arguments");
+  if (T < 1 || T > 128 || static_cast<int64_t>(T) * k > 8192) return {};  // (the launcher's limits: no allocations for a batch it refuses)
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto io = logits.options().dtype(at::kInt);
+  Tensor w = new_out({T, k}, logits.options()), idx = new_out({T, k}, io), counts = new_out({E}, io);
+  Tensor offsets = new_out({E + 1}, io), perm = new_out({T * k}, io), pos = new_out({T * k}, io), items = new_out({max_items, 4}, io);
+  const bool ok = dlv::launch_moe_route_small(logits.data_ptr<float>(), T, E, static_cast<int>(k), static_cast<int>(mode), renorm ? 1 : 0,
+                                              w.data_ptr<float>(), idx.data_ptr<int>(), counts.data_ptr<int>(), offsets.data_ptr<int>(),
+                                              perm.data_ptr<int>(), pos.data_ptr<int>(), static_cast<int>(e0), static_cast<int>(ne),
+                                              static_cast<int>(bn), static_cast<int>(max_items), items.data_ptr<int>(), cur_stream());
+  check_last_error("moe_route_items");
+  if (!ok) return {};
+  return {w, idx, counts, offsets, perm, pos, items};
+}
 Tensor moe_items(const Tensor& offsets, int64_t e0, int64_t ne, int64_t bn, int64_t max_items) {
   check_cuda(offsets, "offsets");
   TORCH_CHECK(offsets.scalar_type() == at::kInt && e0 >= 0 && ne >= 1 && ne <= 1024 && e0 + ne < offsets.numel() + 0 && bn >= 1 && max_items >= 1, "bad work-list arguments");
@@ -1461,7 +1491,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("run_qkv", &GemmWeight::run_qkv)
       .def("run_grouped_act", &GemmWeight::run_grouped_act, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits"),
            py::arg("act"))
-      .def("run_grouped_gemv_act", &GemmWeight::run_grouped_gemv_act)
+      .def("run_grouped_gemv_act", &GemmWeight::run_grouped_gemv_act, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("act"),
+           py::arg("perm") = py::none(), py::arg("k") = 1)
       .def("run_gemv_act", &GemmWeight::run_gemv_act)
       .def("gemv_ok", &GemmWeight::gemv_ok)
       .def("run_grouped", &GemmWeight::run_grouped, py::arg("xs"), py::arg("items"), py::arg("n_per_expert"), py::arg("bn"), py::arg("splits") = 1,
@@ -1517,6 +1548,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("logits_post", &logits_post, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("moe_route", &moe_route);
   m.def("moe_items", &moe_items);
+  m.def("moe_route_items", &moe_route_items);
   m.def("moe_gather", &moe_gather, py::arg("x"), py::arg("perm"), py::arg("k"), py::arg("offsets") = py::none(), py::arg("e0") = 0, py::arg("ne") = 0);
   m.def("moe_combine", &moe_combine, py::arg("ys"), py::arg("pos"), py::arg("w"), py::arg("T"), py::arg("k"), py::arg("offsets") = py::none(),
         py::arg("e0") = 0, py::arg("ne") = 0);

@@ -814,7 +814,10 @@ constexpr int kGemvMmaWarps = 4;
 template <int ACT>
 __global__ void __launch_bounds__(kGemvMmaWarps * 32) gemv_grouped_mma_kernel(const uint8_t* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
                                                                                __nv_bfloat16* __restrict__ out, int ldo, int N, int K,
-                                                                               const int4* __restrict__ items) {
+                                                                               const int4* __restrict__ items, const int* __restrict__ row_map,
+                                                                               int row_div) {
+  // row_map (optional): grouped row r reads the token row row_map[r] / row_div of x instead of row r, i.e. x is the ungathered
+  // [tokens, K] activation and row_map the grouping permutation (the copy into expert order never happens)
   pdl_wait();
   pdl_trigger();
   const int4 it = items[blockIdx.y];
@@ -835,7 +838,8 @@ __global__ void __launch_bounds__(kGemvMmaWarps * 32) gemv_grouped_mma_kernel(co
   const uint32_t scA = 8192 + rA * 16 + c * 4;
   const size_t scB = tileB + 8192 + rB * 16 + c * 4;
   const bool tok = g < cnt;
-  const __nv_bfloat16* xrow = x + static_cast<size_t>(r0 + (tok ? g : 0)) * ldx + c * 32;
+  const int xr = r0 + (tok ? g : 0);
+  const __nv_bfloat16* xrow = x + static_cast<size_t>(row_map != nullptr ? row_map[xr] / row_div : xr) * ldx + c * 32;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   // (Measured: keeping the weight loads of four k-blocks ahead in registers made the kernel slower, 86 instead of 59 us for the
   // gate | up projection of 128 experts: the 106 registers halve the resident warps, and what limits the kernel is the issue
@@ -1000,7 +1004,7 @@ void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, 
   if (w->is_q4 && w->K % 128 == 0 && n_per_expert % 16 == 0 && mt <= 8 && !g_gemv_simt_only) {
     const dim3 grid_mma((n_per_expert / 16 + kGemvMmaWarps - 1) / kGemvMmaWarps, max_items);
     launch_pdl(gemv_grouped_mma_kernel<0>, grid_mma, dim3(kGemvMmaWarps * 32), 0, st, static_cast<const uint8_t*>(w->data), xp, ldx, op, ldo, n_per_expert,
-               w->K, it);
+               w->K, it, static_cast<const int*>(nullptr), 1);
     return;
   }
 #define DLV_GG(MTV)                                                                                                                 \
@@ -1017,7 +1021,7 @@ void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, 
 // Gate | up projection of the work items (n_per_expert = 2 I weight rows per expert, gate rows first) with act(gate) * up in the
 // epilogue; out is [rows, I]. Returns false when the shape is outside the mma.sync kernel (the caller then runs the two steps).
 bool gemv_grouped_act_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items, int max_items,
-                          int act, cudaStream_t st) {
+                          int act, const int* row_map, int row_div, cudaStream_t st) {
   if (!w->is_q4 || w->K % 128 != 0 || n_per_expert % 16 != 0 || ldx % 8 != 0 || (act != 1 && act != 2) || g_gemv_simt_only) return false;
   if (max_items <= 0) return true;
   if (max_items > 65535) throw std::runtime_error("grouped gemv: work list too long");
@@ -1026,8 +1030,8 @@ bool gemv_grouped_act_run(const GemmWeightDesc* w, int n_per_expert, const void*
   const int4* it = reinterpret_cast<const int4*>(items);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
-  if (act == 1) launch_pdl(gemv_grouped_mma_kernel<1>, grid, dim3(kGemvMmaWarps * 32), 0, st, static_cast<const uint8_t*>(w->data), xp, ldx, op, ldo, n_per_expert, w->K, it);
-  else launch_pdl(gemv_grouped_mma_kernel<2>, grid, dim3(kGemvMmaWarps * 32), 0, st, static_cast<const uint8_t*>(w->data), xp, ldx, op, ldo, n_per_expert, w->K, it);
+  if (act == 1) launch_pdl(gemv_grouped_mma_kernel<1>, grid, dim3(kGemvMmaWarps * 32), 0, st, static_cast<const uint8_t*>(w->data), xp, ldx, op, ldo, n_per_expert, w->K, it, row_map, row_div);
+  else launch_pdl(gemv_grouped_mma_kernel<2>, grid, dim3(kGemvMmaWarps * 32), 0, st, static_cast<const uint8_t*>(w->data), xp, ldx, op, ldo, n_per_expert, w->K, it, row_map, row_div);
   return true;
 }
 

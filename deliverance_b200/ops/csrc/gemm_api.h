@@ -94,8 +94,9 @@ void gemm_tc_run_grouped(const GemmWeightDesc* w, int n_per_expert, const void* 
 // CUDA-core variant for decode-size groups (at most `mt` = 4 or 8 rows per work item; items built with bn == mt)
 void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,
                       int max_items, int mt, cudaStream_t st);
+// row_map / row_div (optional): grouped row r reads x row row_map[r] / row_div (x ungathered, row_map the grouping permutation)
 bool gemv_grouped_act_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items, int max_items,
-                          int act, cudaStream_t st);
+                          int act, const int* row_map, int row_div, cudaStream_t st);
 // Row-parallel projection whose partial tiles go straight to the rank that owns their token rows (epilogue EPI = 3, no waiting
 // inside the GEMM). Follow it with launch_scatter_reduce and launch_scatter_finish on the same stream.
 void gemm_tc_run_scatter(const GemmWeightDesc* w, const void* x, int M, int ldx, const GemmScatterArgs* a, int* status, cudaStream_t st);
@@ -180,6 +181,8 @@ void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, v
 void launch_moe_combine(const void* ys, const int* pos, const float* w, int T, int k, int H, void* out, const int* offsets, int e0,
                         int ne, cudaStream_t st);
 void launch_moe_items(const int* offsets, int e0, int ne, int bn, int max_items, int* items, cudaStream_t st);
+bool launch_moe_route_small(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
+                            int* perm, int* pos, int e0, int ne, int bn, int max_items, int* items, cudaStream_t st);
 
 // comm.cu: fused compute + collective kernels over peer memory (same protocol as the GEMM all-reduce epilogue)
 bool comm_rows_supported(const GemmTpArgs* tp, int rows, int H);

@@ -13,23 +13,18 @@ namespace dlv {
 
 constexpr int kMaxTopK = 16;
 
-// one warp per token; E <= 1024
-__global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int mode, int renorm,
-                                                       float* __restrict__ w_out, int* __restrict__ idx_out, int* __restrict__ counts) {
-  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
-  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (t >= T) return;
-  const float* row = logits + static_cast<size_t>(t) * E;
-  // softmax statistics over all experts (mode 0)
+// Top-k of one token by one warp (E <= 1024): softmax statistics, k rounds of "every lane proposes its best remaining expert"
+// (ties -> lower index), weights by `mode` (0: softmax over all experts, then top-k, optional renormalisation; 1: softmax over
+// the k chosen). Lane 0 stores weights and expert ids, adds to the histogram `counts` (global or shared memory) and, when
+// `idx_copy` is given, keeps a second copy of the ids there.
+__device__ __forceinline__ void moe_topk_token(const float* __restrict__ row, int E, int k, int mode, int renorm, int lane,
+                                               float* __restrict__ w_out, int* __restrict__ idx_out, int* counts, int* idx_copy) {
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
   mx = warp_max(mx);
   float den = 0.f;
   for (int e = lane; e < E; e += 32) den += __expf(row[e] - mx);
   den = warp_sum(den);
-  // iterative top-k: each round every lane proposes its best remaining expert (ties -> lower index)
   float sel_v[kMaxTopK];
   int sel_i[kMaxTopK];
   unsigned long long taken_lo = 0ull;  // bitmask of this lane's taken slots (expert e = lane + 32 * j -> bit j)
@@ -75,10 +70,109 @@ __global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__
       for (int r = 0; r < k; ++r) wts[r] /= s;
     }
     for (int r = 0; r < k; ++r) {
-      w_out[static_cast<size_t>(t) * k + r] = wts[r];
-      idx_out[static_cast<size_t>(t) * k + r] = sel_i[r];
+      w_out[r] = wts[r];
+      idx_out[r] = sel_i[r];
+      if (idx_copy != nullptr) idx_copy[r] = sel_i[r];
       atomicAdd(&counts[sel_i[r]], 1);
     }
+  }
+}
+
+// one warp per token
+__global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int mode, int renorm,
+                                                       float* __restrict__ w_out, int* __restrict__ idx_out, int* __restrict__ counts) {
+  pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
+  pdl_trigger();  // the next kernel may start its prologue (and a GEMM its weight prefetch) under this kernel's tail
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  moe_topk_token(logits + static_cast<size_t>(t) * E, E, k, mode, renorm, lane, w_out + static_cast<size_t>(t) * k,
+                 idx_out + static_cast<size_t>(t) * k, counts, nullptr);
+}
+
+// Routing of a decode-size batch in ONE launch of one CTA (32 warps): top-k per token, expert histogram and offsets, the stable
+// permutation that groups (token, slot) pairs by expert, and the grouped GEMM's work list for the local experts [e0, e0 + ne)
+// with `bn` rows per item. It replaces a memset and four launches (moe_topk, moe_sort, moe_items and, where the grouped GEMV reads
+// token rows through `perm`, moe_gather), which cost more than the work at a few hundred pairs. Shared memory: T k + 2 E + ne + 3
+// ints. Same results as the separate kernels (same tie rule, same stable order).
+constexpr int kRouteSmallMaxPairs = 8192;
+constexpr int kRouteSmallMaxTokens = 128;  // a warp takes every 32nd token: beyond a few tokens per warp the many-CTA kernels win
+__device__ __forceinline__ int warp_incl_scan(int v, int lane) {
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += n;
+  }
+  return v;
+}
+__global__ void __launch_bounds__(1024) moe_route_small_kernel(const float* __restrict__ logits, int T, int E, int k, int mode, int renorm,
+                                                               float* __restrict__ w_out, int* __restrict__ idx_out, int* __restrict__ counts,
+                                                               int* __restrict__ offsets, int* __restrict__ perm, int* __restrict__ pos, int e0,
+                                                               int ne, int bn, int max_items, int4* __restrict__ items) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ int rs[];
+  const int P = T * k;
+  int* idx_s = rs;              // [P] expert of every (token, slot) pair
+  int* cnt_s = idx_s + P;       // [E]
+  int* off_s = cnt_s + E;       // [E + 1]
+  int* first_s = off_s + E + 1; // [ne + 1] first work item of every local expert
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int e = tid; e < E; e += 1024) cnt_s[e] = 0;
+  __syncthreads();
+  for (int t = warp; t < T; t += 32)
+    moe_topk_token(logits + static_cast<size_t>(t) * E, E, k, mode, renorm, lane, w_out + static_cast<size_t>(t) * k,
+                   idx_out + static_cast<size_t>(t) * k, cnt_s, idx_s + t * k);
+  __syncthreads();
+  if (warp == 0) {  // exclusive scan of the histogram: lane l owns a contiguous chunk of experts
+    const int chunk = (E + 31) / 32, lo = min(E, lane * chunk), hi = min(E, lo + chunk);
+    int sum = 0;
+    for (int e = lo; e < hi; ++e) sum += cnt_s[e];
+    const int incl = warp_incl_scan(sum, lane);
+    int acc = incl - sum;
+    for (int e = lo; e < hi; ++e) {
+      off_s[e] = acc;
+      acc += cnt_s[e];
+    }
+    if (lane == 31) off_s[E] = incl;
+  } else if (warp == 1 && items != nullptr) {  // the same over the local experts' item counts
+    const int chunk = (ne + 31) / 32, lo = min(ne, lane * chunk), hi = min(ne, lo + chunk);
+    int sum = 0;
+    for (int e = lo; e < hi; ++e) sum += (cnt_s[e0 + e] + bn - 1) / bn;
+    const int incl = warp_incl_scan(sum, lane);
+    int acc = incl - sum;
+    for (int e = lo; e < hi; ++e) {
+      first_s[e] = acc;
+      acc += (cnt_s[e0 + e] + bn - 1) / bn;
+    }
+    if (lane == 31) first_s[ne] = incl;
+  }
+  __syncthreads();
+  for (int e = tid; e <= E; e += 1024) offsets[e] = off_s[e];
+  for (int e = tid; e < E; e += 1024) counts[e] = cnt_s[e];
+  // stable grouping: a warp takes an expert and walks the pairs 32 at a time (ballot + prefix count keeps ascending pair order)
+  for (int e = warp; e < E; e += 32) {
+    if (cnt_s[e] == 0) continue;
+    int row = off_s[e];
+    for (int p0 = 0; p0 < P; p0 += 32) {
+      const int p = p0 + lane;
+      const bool mine = p < P && idx_s[p] == e;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int r = row + __popc(m & ((1u << lane) - 1u));
+        perm[r] = p;
+        pos[p] = r;
+      }
+      row += __popc(m);
+    }
+  }
+  if (items != nullptr) {
+    for (int e = tid; e < ne; e += 1024) {
+      const int lo = off_s[e0 + e], hi = off_s[e0 + e + 1];
+      int it = first_s[e];
+      for (int r = lo; r < hi && it < max_items; r += bn, ++it) items[it] = make_int4(e, r, hi, 0);
+    }
+    for (int it = first_s[ne] + tid; it < max_items; it += 1024) items[it] = make_int4(-1, 0, 0, 0);
   }
 }
 
@@ -166,6 +260,14 @@ void launch_moe_route(const float* logits, int T, int E, int k, int mode, int re
   }
   moe_topk_kernel<<<(T + 7) / 8, 256, 0, st>>>(logits, T, E, k, mode, renorm, w, idx, counts);
   moe_sort_kernel<<<1, 1024, sizeof(int) * (E + 1), st>>>(idx, counts, T, E, k, offsets, perm, pos);
+}
+// Decode-size batches: everything of launch_moe_route + launch_moe_items in one launch. False when the batch is too large for it.
+bool launch_moe_route_small(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
+                            int* perm, int* pos, int e0, int ne, int bn, int max_items, int* items, cudaStream_t st) {
+  if (T < 1 || T > kRouteSmallMaxTokens || T * k > kRouteSmallMaxPairs || E > 1024 || ne > 1024) return false;
+  const size_t smem = sizeof(int) * (static_cast<size_t>(T) * k + 2 * E + ne + 3);
+  return launch_pdl(moe_route_small_kernel, dim3(1), dim3(1024), smem, st, logits, T, E, k, mode, renorm, w, idx, counts, offsets, perm, pos, e0,
+                    ne, bn, max_items, reinterpret_cast<int4*>(items)) == cudaSuccess;
 }
 void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, void* xs, const int* offsets, int e0, int ne,
                        cudaStream_t st) {

@@ -39,6 +39,28 @@ def test_moe_route_gather_combine(E, k, mode, renorm):
     assert ((out.cpu().float() - exp).norm() / exp.norm()).item() < 1e-2
 
 
+@pytest.mark.parametrize("T,E,k,mode,renorm,e0,ne,bn", [(1, 8, 2, 0, True, 0, 8, 4), (32, 128, 8, 0, False, 0, 128, 8), (64, 128, 8, 0, True, 32, 48, 8),
+                                                        (77, 64, 6, 1, False, 0, 64, 16), (128, 8, 2, 0, True, 4, 4, 64), (5, 1000, 16, 0, True, 0, 1000, 4)])
+def test_moe_route_in_one_launch_equals_the_separate_kernels(T, E, k, mode, renorm, e0, ne, bn):
+    """Decode-size routing (top-k, histogram, offsets, grouping permutation, work list) from the single-CTA kernel: identical to
+    moe_route + moe_items, ties between equal logits included."""
+    e = ops.require_ext()
+    g = torch.Generator().manual_seed(T * 1000 + E)
+    logits = torch.randn(T, E, generator=g)
+    logits[:, 1] = logits[:, 0]  # a tie in every row: the lower expert index wins in both
+    rows = T * k
+    max_items = max(1, min((rows + bn - 1) // bn + ne, rows) if rows >= ne else rows)
+    a = e.moe_route(logits.cuda(), k, mode, renorm)
+    items_a = e.moe_items(a[3], e0, ne, bn, max_items)
+    b = e.moe_route_items(logits.cuda(), k, mode, renorm, e0, ne, bn, max_items)
+    assert len(b) == 7
+    torch.cuda.synchronize()
+    for name, ta, tb in zip(("w", "idx", "counts", "offsets", "perm", "pos"), a, b):
+        assert torch.equal(ta, tb), name
+    assert torch.equal(items_a, b[6])
+    assert e.moe_route_items(torch.randn(129, E).cuda(), k, mode, renorm, e0, ne, bn, max_items) == []  # beyond its size: the caller falls back
+
+
 @pytest.mark.parametrize("q4", [False, True])
 @pytest.mark.parametrize("T,E,k,N,K,e0,ne", [(40, 8, 2, 256, 512, 0, 8), (64, 16, 4, 384, 1024, 4, 8), (700, 4, 2, 192, 256, 0, 4), (3, 8, 2, 128, 2048, 6, 2)])
 def test_grouped_gemm_matches_per_expert(T, E, k, N, K, e0, ne, q4):
@@ -86,7 +108,11 @@ def test_grouped_gemm_matches_per_expert(T, E, k, N, K, e0, ne, q4):
             # the grouped GEMV with the gated activation in its epilogue: rows [0, N / 2) are the gate, [N / 2, N) the up projection
             hm = grouped.run_gemv_act(xs, items, "silu")
             assert hm is not None and tuple(hm.shape) == (xs.shape[0], N // 2)
+            hm_ind = grouped.run_gemv_act(x.cuda(), items, "silu", perm, k)  # token rows read through the permutation: no gather
             torch.cuda.synchronize()
+            for j in range(ne):
+                lo, hi = off[e0 + j], off[e0 + j + 1]
+                assert torch.equal(hm_ind[lo:hi], hm[lo:hi]), ("gemv through perm", bn, j)
             for j in range(ne):
                 lo, hi = off[e0 + j], off[e0 + j + 1]
                 if hi == lo:
