@@ -894,12 +894,18 @@ __global__ void __launch_bounds__(kGemvMmaWarps * 32) gemv_grouped_mma_kernel(co
 // The same operand mapping for an ordinary projection with at most 8 token rows (single requests and small decode batches). These
 // GEMMs move a few megabytes, so what counts is how many warps stream at once and how little is set up per launch: the tcgen05 kernel
 // pays its prologue and epilogue per CTA (10-12 us per projection at one token). One CTA per 16 weight rows (8 with the gated
-// activation), its kGemvSplit warps take interleaved k-blocks and add their partial tiles through shared memory.
+// activation), its S warps take interleaved k-blocks and add their partial tiles through shared memory.
+// S (4, 8 or 16) is chosen per shape by gemv_pick_split: the time of these kernels is (waves of CTAs) x (k-blocks per warp), and
+// both are whole numbers. The gate | up projection of Qwen3-4B (1216 CTAs, 20 k-blocks) with S = 8 ran 2.05 waves of 592 resident
+// CTAs (64 registers: four CTAs of 256 threads per SM) with 3 k-blocks on the slowest warp, 9 k-block times in all; with S = 4 and
+// at most 56 registers nine CTAs of 128 threads fit per SM, all 1216 are resident at once and every warp has 5 k-blocks. Narrow
+// deep projections (160 CTAs, 32 or 76 k-blocks) take S = 16 instead: half the k-blocks per warp, still one wave.
 // ACT as above; OUTF: fp32 output (the output head's logits).
-constexpr int kGemvSplit = 8;
-template <int ACT, bool OUTF>
-__global__ void __launch_bounds__(kGemvSplit * 32) gemv_dense_mma_kernel(const uint8_t* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
-                                                                         void* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N, int K) {
+template <int ACT, bool OUTF, int S>
+__global__ void __launch_bounds__(S * 32, S == 4 ? 9 : (S == 8 ? 4 : 2)) gemv_dense_mma_kernel(const uint8_t* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
+                                                                                 void* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N,
+                                                                                 int K) {
+  constexpr int kGemvSplit = S;
   __shared__ float part[kGemvSplit][32][4];
   pdl_wait();
   pdl_trigger();
@@ -975,21 +981,50 @@ bool g_gemv_dense = true;  // small batches (<= 8 rows) of JQ4 projections on th
 bool gemv_dense_supported(const GemmWeightDesc* w, int M, int ldx) {
   return g_gemv_dense && !g_gemv_simt_only && w->is_q4 && M >= 1 && M <= 8 && w->K % 128 == 0 && w->K >= 128 && ldx % 8 == 0;
 }
+// Warps per CTA that split K: the candidate with the fewest (waves x k-blocks per warp); ties go to the wider split (more loads in flight).
+int g_gemv_force_split = 0;  // tests: 4, 8 or 16
+static int gemv_pick_split(int ctas, int kb_total) {
+  if (g_gemv_force_split == 4 || g_gemv_force_split == 8 || g_gemv_force_split == 16) return g_gemv_force_split;
+  const int sms = gemm_num_sms();
+  const int cand[3] = {4, 8, 16}, resident[3] = {9, 4, 2};  // CTAs per SM (registers: 56 x 128, 64 x 256, 64 x 512 threads)
+  int best = 8;
+  long long best_cost = -1;
+  for (int i = 0; i < 3; ++i) {
+    const long long slots = static_cast<long long>(sms) * resident[i];
+    const long long cost = ((ctas + slots - 1) / slots) * ((kb_total + cand[i] - 1) / cand[i]);
+    if (best_cost < 0 || cost <= best_cost) {
+      best_cost = cost;
+      best = cand[i];
+    }
+  }
+  return best;
+}
+template <int ACT, bool OUTF>
+static void gemv_dense_launch(int split, dim3 grid, cudaStream_t st, const uint8_t* wd, const __nv_bfloat16* xp, int ldx, void* out, int ldo, const float* bias,
+                              int M, int N, int K) {
+  cudaError_t e;
+  if (split == 4) e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 4>, grid, dim3(128), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
+  else if (split == 16) e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 16>, grid, dim3(512), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
+  else e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 8>, grid, dim3(256), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
+  if (e != cudaSuccess) throw std::runtime_error(std::string("small-batch gemv launch: ") + cudaGetErrorString(e));
+}
 // act: 0 plain (bias, bf16 or fp32 output), 1 / 2: w holds gate | up rows (N = 2 I), out is [M, I] bf16
 void gemv_dense_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias, int act,
                     cudaStream_t st) {
   const uint8_t* wd = static_cast<const uint8_t*>(w->data);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
-  const dim3 block(kGemvSplit * 32);
+  const int kb_total = w->K / 128;
   if (act == 1 || act == 2) {
     const dim3 grid((w->N / 2 + 7) / 8);
-    if (act == 1) launch_pdl(gemv_dense_mma_kernel<1, false>, grid, block, 0, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
-    else launch_pdl(gemv_dense_mma_kernel<2, false>, grid, block, 0, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+    const int split = gemv_pick_split(static_cast<int>(grid.x), kb_total);
+    if (act == 1) gemv_dense_launch<1, false>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+    else gemv_dense_launch<2, false>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
     return;
   }
   const dim3 grid((w->N + 15) / 16);
-  if (out_f32) launch_pdl(gemv_dense_mma_kernel<0, true>, grid, block, 0, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
-  else launch_pdl(gemv_dense_mma_kernel<0, false>, grid, block, 0, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+  const int split = gemv_pick_split(static_cast<int>(grid.x), kb_total);
+  if (out_f32) gemv_dense_launch<0, true>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+  else gemv_dense_launch<0, false>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
 }
 
 void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,

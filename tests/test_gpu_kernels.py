@@ -626,11 +626,20 @@ def test_linear_prefill_token_tiles(bn, q4):
         ext.gemm_force_bn(0)
 
 
+@pytest.mark.parametrize("split", [0, 4, 8, 16])
 @pytest.mark.parametrize("N,K", [(2560, 4096), (384, 256), (200, 1152), (6144, 2560)])
-def test_small_batch_gemv_matches_fp32(N, K):
+def test_small_batch_gemv_matches_fp32(N, K, split):
     """1..8 token rows of a JQ4 projection on the mma.sync GEMV: plain (bf16 and fp32 output, bias), gated activation epilogue, and
-    agreement with the tcgen05 kernel it replaces at these sizes."""
+    agreement with the tcgen05 kernel it replaces at these sizes; every number of K-splitting warps per CTA (0: chosen per shape)."""
     ext = ops.require_ext()
+    ext.gemv_force_split(split)
+    try:
+        _small_batch_gemv_case(ext, N, K)
+    finally:
+        ext.gemv_force_split(0)
+
+
+def _small_batch_gemv_case(ext, N, K):
     g = torch.Generator().manual_seed(N + K)
     w = torch.randn(N, K, generator=g) * 0.05
     p, s = q4_quantize(w)
