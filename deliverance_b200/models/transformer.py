@@ -473,7 +473,7 @@ class DecoderModel:
         if lw.fused_act:
             with self._stage("mlpblock.gate_up_projection"):
                 h = ops.linear_act(x, lw.gate_up, cfg.hidden_act)
-        elif self._sp is None and not lw.lora and x.shape[0] <= 8:
+        elif self._sp is None and not lw.lora and x.shape[0] <= ops.GEMV_MAX_ROWS:
             with self._stage("mlpblock.gate_up_projection"):  # a handful of rows: projection and gated activation in one launch
                 h = ops.linear_gated(x, lw.gate_up, cfg.hidden_act)
         else:

@@ -43,6 +43,8 @@ def ext():
         if _ext is not None and os.environ.get("DLV_DECODE_MERGE", "launch") == "kernel":
             _MERGE_IN_KERNEL[0] = True
             _ext.decode_merge_in_kernel(True)
+        if _ext is not None and os.environ.get("DLV_GEMV_MAX_ROWS", "") in ("16", "0"):  # comparisons: 9..16 rows on the GEMV too, or none
+            set_gemv_max_rows(int(os.environ["DLV_GEMV_MAX_ROWS"]))
         if _ext is not None and os.environ.get("DLV_BOUNDS_CHECK", "0") == "1":
             _ext.set_bounds_check(True)
     return _ext
@@ -261,7 +263,7 @@ def interleave_gate_up(gate, up, block: int = 64):
 def linear_gated(x: torch.Tensor, w: LinearWeight, act: str) -> torch.Tensor:
     """``act(x @ Wg^T) * (x @ Wu^T)`` for a weight that holds the gate rows followed by the up rows (plain order). One kernel for
     1..8 rows of a JQ4 weight on CUDA (the small-batch GEMV's epilogue), projection + activation kernel otherwise."""
-    if _cuda(x) and w.q4 and x.shape[0] <= 8:
+    if _cuda(x) and w.q4 and x.shape[0] <= GEMV_MAX_ROWS:
         kind = fused_act_kind(act)
         if kind:
             out = w.handle().run_gemv_act(x, kind)
@@ -365,7 +367,7 @@ def linear_rope_kv(x, w: LinearWeight, positions, slots, q_norm_w, k_norm_w, cos
         if D != 128:
             raise ValueError("the fused q/k/v epilogue needs head_dim 128")
         _check_full_rotary(cos, D)
-        if x.shape[0] <= 8 and w.q4 and w.handle().gemv_ok(x.shape[0], x.stride(0)):
+        if x.shape[0] <= GEMV_MAX_ROWS and w.q4 and w.handle().gemv_ok(x.shape[0], x.stride(0)):
             # a handful of rows: the small-batch GEMV plus the stand-alone rotary kernel beat the tcgen05 tile's fixed cost
             return rope_kv(linear(x, w), positions, slots, q_norm_w, k_norm_w, cos, sin, k_cache, v_cache, H, KV, D, eps, norm_offset)
         _count()
@@ -379,6 +381,17 @@ def decode_splits(num_seqs: int, kv_heads: int, max_ctx: int, sms: int = 148) ->
     want = max(1, (2 * sms + ctas - 1) // ctas)
     tiles = max(1, (max_ctx + 31) // 32)
     return int(max(1, min(want, tiles // 4 if tiles >= 8 else 1, 64)))
+
+
+GEMV_MAX_ROWS = 8  # JQ4 projections of at most this many token rows run on the mma.sync GEMV (16 is possible and measured slower than tcgen05)
+
+
+def set_gemv_max_rows(n: int) -> None:
+    """Most token rows of a JQ4 projection that go to the mma.sync GEMV (0, 8 or 16)."""
+    global GEMV_MAX_ROWS
+    GEMV_MAX_ROWS = int(n)
+    if _ext is not None:
+        _ext.gemv_max_rows(int(n))
 
 
 _MERGE_IN_KERNEL = [False]

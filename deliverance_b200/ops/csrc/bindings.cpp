@@ -1528,6 +1528,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       py::arg("on"), py::arg("all") = false, py::arg("ordered") = true);
   m.def("decode_merge_in_kernel", [](bool on) { g_decode_merge_in_kernel = on; });
+  m.def("gemv_max_rows", [](int64_t n) { dlv::g_gemv_max_rows = static_cast<int>(n); });
   m.def("gemv_force_split", [](int64_t s) { dlv::g_gemv_force_split = static_cast<int>(s); });
   m.def("gemm_force_bn", [](int64_t bn) { dlv::g_gemm_force_bn = static_cast<int>(bn); });
   m.def("set_bounds_check", &set_bounds_check);

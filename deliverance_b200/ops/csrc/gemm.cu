@@ -901,12 +901,18 @@ __global__ void __launch_bounds__(kGemvMmaWarps * 32) gemv_grouped_mma_kernel(co
 // at most 56 registers nine CTAs of 128 threads fit per SM, all 1216 are resident at once and every warp has 5 k-blocks. Narrow
 // deep projections (160 CTAs, 32 or 76 k-blocks) take S = 16 instead: half the k-blocks per warp, still one wave.
 // ACT as above; OUTF: fp32 output (the output head's logits).
-template <int ACT, bool OUTF, int S>
-__global__ void __launch_bounds__(S * 32, S == 4 ? 9 : (S == 8 ? 4 : 2)) gemv_dense_mma_kernel(const uint8_t* __restrict__ wdata, const __nv_bfloat16* __restrict__ x, int ldx,
-                                                                                 void* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N,
-                                                                                 int K) {
+// TG: groups of 8 token rows (1: up to 8 rows, 2: 9..16 rows; the expanded weight fragment feeds one MMA per group). Two groups
+// are tested but not used by default (g_gemv_max_rows).
+template <int S, int TG>
+constexpr int gemv_resident() {  // CTAs per SM the register budget is set for
+  return TG == 1 ? (S == 4 ? 9 : (S == 8 ? 4 : 2)) : (S == 4 ? 6 : (S == 8 ? 3 : 1));
+}
+template <int ACT, bool OUTF, int S, int TG>
+__global__ void __launch_bounds__(S * 32, gemv_resident<S, TG>()) gemv_dense_mma_kernel(const uint8_t* __restrict__ wdata, const __nv_bfloat16* __restrict__ x,
+                                                                                         int ldx, void* __restrict__ out, int ldo,
+                                                                                         const float* __restrict__ bias, int M, int N, int K) {
   constexpr int kGemvSplit = S;
-  __shared__ float part[kGemvSplit][32][4];
+  __shared__ float part[kGemvSplit][TG][32][4];
   pdl_wait();
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
@@ -920,9 +926,16 @@ __global__ void __launch_bounds__(S * 32, S == 4 ? 9 : (S == 8 ? 4 : 2)) gemv_de
   const uint8_t* baseB = wdata + static_cast<size_t>(nB >> 7) * kb_total * kQ4StageBytes;
   const uint32_t offA = rA * 64 + ((c ^ ((rA >> 1) & 3)) << 4), offB = rB * 64 + ((c ^ ((rB >> 1) & 3)) << 4);
   const uint32_t scA = 8192 + rA * 16 + c * 4, scB = 8192 + rB * 16 + c * 4;
-  const bool tok = g < M;
-  const __nv_bfloat16* xrow = x + static_cast<size_t>(tok ? g : 0) * ldx + c * 32;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  bool tok[TG];
+  const __nv_bfloat16* xrow[TG];
+  float acc[TG][4];
+#pragma unroll
+  for (int t = 0; t < TG; ++t) {
+    tok[t] = g + 8 * t < M;
+    xrow[t] = x + static_cast<size_t>(tok[t] ? g + 8 * t : 0) * ldx + c * 32;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+  }
 #pragma unroll 2
   for (int kb = warp; kb < kb_total; kb += kGemvSplit) {
     const size_t so = static_cast<size_t>(kb) * kQ4StageBytes;
@@ -930,12 +943,13 @@ __global__ void __launch_bounds__(S * 32, S == 4 ? 9 : (S == 8 ? 4 : 2)) gemv_de
     const uint4 wb = __ldg(reinterpret_cast<const uint4*>(baseB + so + offB));
     const float sa = __ldg(reinterpret_cast<const float*>(baseA + so + scA));
     const float sb = __ldg(reinterpret_cast<const float*>(baseB + so + scB));
-    uint4 xv[4];
+    uint4 xv[TG][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) xv[j] = tok ? *reinterpret_cast<const uint4*>(xrow + kb * 128 + j * 8) : make_uint4(0u, 0u, 0u, 0u);
+    for (int t = 0; t < TG; ++t)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) xv[t][j] = tok[t] ? *reinterpret_cast<const uint4*>(xrow[t] + kb * 128 + j * 8) : make_uint4(0u, 0u, 0u, 0u);
     const __nv_bfloat162 s2a = __float2bfloat162_rn(sa), s2b = __float2bfloat162_rn(sb);
     const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
-    const uint32_t* xu = reinterpret_cast<const uint32_t*>(xv);
 #pragma unroll
     for (int hl = 0; hl < 2; ++hl) {
 #pragma unroll
@@ -946,47 +960,64 @@ __global__ void __launch_bounds__(S * 32, S == 4 ? 9 : (S == 8 ? 4 : 2)) gemv_de
         a[1] = q4_pair_to_bf162(nb, 0x4140u, s2b);
         a[2] = q4_pair_to_bf162(na, 0x4342u, s2a);
         a[3] = q4_pair_to_bf162(nb, 0x4342u, s2b);
-        mma_bf16_m16n8k16(acc, a, xu[hl * 8 + 2 * wd], xu[hl * 8 + 2 * wd + 1]);
+#pragma unroll
+        for (int t = 0; t < TG; ++t) {
+          const uint32_t* xu = reinterpret_cast<const uint32_t*>(xv[t]);
+          mma_bf16_m16n8k16(acc[t], a, xu[hl * 8 + 2 * wd], xu[hl * 8 + 2 * wd + 1]);
+        }
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) part[warp][lane][i] = acc[i];
+  for (int t = 0; t < TG; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) part[warp][t][lane][i] = acc[t][i];
   __syncthreads();
   if (warp != 0) return;
 #pragma unroll
   for (int w2 = 1; w2 < kGemvSplit; ++w2)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] += part[w2][lane][i];
-  // accumulator: rows g and g + 8, token columns 2 c and 2 c + 1
+    for (int t = 0; t < TG; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[t][i] += part[w2][t][lane][i];
+  // accumulator of group t: rows g and g + 8, token columns 8 t + 2 c and 8 t + 2 c + 1
   auto store = [&](int t, int n, float v) {
     if (t >= M || n >= n_out) return;
     if (OUTF) static_cast<float*>(out)[static_cast<size_t>(t) * ldo + n] = v;
     else static_cast<__nv_bfloat16*>(out)[static_cast<size_t>(t) * ldo + n] = f2bf(v);
   };
-  const int t0 = 2 * c;
-  if (ACT > 0) {
-    store(t0, n0 + g, gated_act<ACT>(bf2f(f2bf(acc[0]))) * bf2f(f2bf(acc[2])));
-    store(t0 + 1, n0 + g, gated_act<ACT>(bf2f(f2bf(acc[1]))) * bf2f(f2bf(acc[3])));
-    return;
+  const float b0 = ACT == 0 && bias != nullptr && n0 + g < N ? bias[n0 + g] : 0.f;
+  const float b1 = ACT == 0 && bias != nullptr && n0 + g + 8 < N ? bias[n0 + g + 8] : 0.f;
+#pragma unroll
+  for (int t = 0; t < TG; ++t) {
+    const int t0 = 8 * t + 2 * c;
+    if (ACT > 0) {
+      store(t0, n0 + g, gated_act<ACT>(bf2f(f2bf(acc[t][0]))) * bf2f(f2bf(acc[t][2])));
+      store(t0 + 1, n0 + g, gated_act<ACT>(bf2f(f2bf(acc[t][1]))) * bf2f(f2bf(acc[t][3])));
+    } else {
+      store(t0, n0 + g, acc[t][0] + b0);
+      store(t0 + 1, n0 + g, acc[t][1] + b0);
+      store(t0, n0 + g + 8, acc[t][2] + b1);
+      store(t0 + 1, n0 + g + 8, acc[t][3] + b1);
+    }
   }
-  const float b0 = bias != nullptr && n0 + g < N ? bias[n0 + g] : 0.f, b1 = bias != nullptr && n0 + g + 8 < N ? bias[n0 + g + 8] : 0.f;
-  store(t0, n0 + g, acc[0] + b0);
-  store(t0 + 1, n0 + g, acc[1] + b0);
-  store(t0, n0 + g + 8, acc[2] + b1);
-  store(t0 + 1, n0 + g + 8, acc[3] + b1);
 }
 
-bool g_gemv_dense = true;  // small batches (<= 8 rows) of JQ4 projections on the mma.sync GEMV instead of the tcgen05 kernel
+bool g_gemv_dense = true;  // small batches of JQ4 projections on the mma.sync GEMV instead of the tcgen05 kernel
+// Most token rows it takes. The kernel handles up to 16 (two groups of 8), but measured on the Qwen3-4B shape at 16 sequences the
+// tcgen05 kernel is the faster one (3.12 against 3.54 ms per decode step), so the default stays at one group.
+int g_gemv_max_rows = 8;
 bool gemv_dense_supported(const GemmWeightDesc* w, int M, int ldx) {
-  return g_gemv_dense && !g_gemv_simt_only && w->is_q4 && M >= 1 && M <= 8 && w->K % 128 == 0 && w->K >= 128 && ldx % 8 == 0;
+  return g_gemv_dense && !g_gemv_simt_only && w->is_q4 && M >= 1 && M <= g_gemv_max_rows && M <= 16 && w->K % 128 == 0 && w->K >= 128 && ldx % 8 == 0;
 }
 // Warps per CTA that split K: the candidate with the fewest (waves x k-blocks per warp); ties go to the wider split (more loads in flight).
 int g_gemv_force_split = 0;  // tests: 4, 8 or 16
-static int gemv_pick_split(int ctas, int kb_total) {
+static int gemv_pick_split(int ctas, int kb_total, int tg) {
   if (g_gemv_force_split == 4 || g_gemv_force_split == 8 || g_gemv_force_split == 16) return g_gemv_force_split;
   const int sms = gemm_num_sms();
-  const int cand[3] = {4, 8, 16}, resident[3] = {9, 4, 2};  // CTAs per SM (registers: 56 x 128, 64 x 256, 64 x 512 threads)
+  const int cand[3] = {4, 8, 16};
+  const int resident[3] = {tg == 1 ? gemv_resident<4, 1>() : gemv_resident<4, 2>(), tg == 1 ? gemv_resident<8, 1>() : gemv_resident<8, 2>(),
+                           tg == 1 ? gemv_resident<16, 1>() : gemv_resident<16, 2>()};
   int best = 8;
   long long best_cost = -1;
   for (int i = 0; i < 3; ++i) {
@@ -999,32 +1030,37 @@ static int gemv_pick_split(int ctas, int kb_total) {
   }
   return best;
 }
-template <int ACT, bool OUTF>
-static void gemv_dense_launch(int split, dim3 grid, cudaStream_t st, const uint8_t* wd, const __nv_bfloat16* xp, int ldx, void* out, int ldo, const float* bias,
-                              int M, int N, int K) {
+template <int ACT, bool OUTF, int TG>
+static void gemv_dense_launch_tg(int split, dim3 grid, cudaStream_t st, const uint8_t* wd, const __nv_bfloat16* xp, int ldx, void* out, int ldo,
+                                 const float* bias, int M, int N, int K) {
   cudaError_t e;
-  if (split == 4) e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 4>, grid, dim3(128), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
-  else if (split == 16) e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 16>, grid, dim3(512), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
-  else e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 8>, grid, dim3(256), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
+  if (split == 4) e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 4, TG>, grid, dim3(128), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
+  else if (split == 16) e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 16, TG>, grid, dim3(512), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
+  else e = launch_pdl(gemv_dense_mma_kernel<ACT, OUTF, 8, TG>, grid, dim3(256), 0, st, wd, xp, ldx, out, ldo, bias, M, N, K);
   if (e != cudaSuccess) throw std::runtime_error(std::string("small-batch gemv launch: ") + cudaGetErrorString(e));
+}
+template <int ACT, bool OUTF>
+static void gemv_dense_launch(dim3 grid, cudaStream_t st, const uint8_t* wd, const __nv_bfloat16* xp, int ldx, void* out, int ldo, const float* bias,
+                              int M, int N, int K) {
+  const int tg = M > 8 ? 2 : 1;
+  const int split = gemv_pick_split(static_cast<int>(grid.x), K / 128, tg);
+  if (tg == 2) gemv_dense_launch_tg<ACT, OUTF, 2>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, N, K);
+  else gemv_dense_launch_tg<ACT, OUTF, 1>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, N, K);
 }
 // act: 0 plain (bias, bf16 or fp32 output), 1 / 2: w holds gate | up rows (N = 2 I), out is [M, I] bf16
 void gemv_dense_run(const GemmWeightDesc* w, const void* x, int M, int ldx, void* out, int ldo, bool out_f32, const float* bias, int act,
                     cudaStream_t st) {
   const uint8_t* wd = static_cast<const uint8_t*>(w->data);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
-  const int kb_total = w->K / 128;
   if (act == 1 || act == 2) {
     const dim3 grid((w->N / 2 + 7) / 8);
-    const int split = gemv_pick_split(static_cast<int>(grid.x), kb_total);
-    if (act == 1) gemv_dense_launch<1, false>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
-    else gemv_dense_launch<2, false>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+    if (act == 1) gemv_dense_launch<1, false>(grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+    else gemv_dense_launch<2, false>(grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
     return;
   }
   const dim3 grid((w->N + 15) / 16);
-  const int split = gemv_pick_split(static_cast<int>(grid.x), kb_total);
-  if (out_f32) gemv_dense_launch<0, true>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
-  else gemv_dense_launch<0, false>(split, grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+  if (out_f32) gemv_dense_launch<0, true>(grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
+  else gemv_dense_launch<0, false>(grid, st, wd, xp, ldx, out, ldo, bias, M, w->N, w->K);
 }
 
 void gemv_grouped_run(const GemmWeightDesc* w, int n_per_expert, const void* x, int ldx, void* out, int ldo, const int* items,

@@ -146,6 +146,7 @@ void gemm_persist_run(const GemmWeightDesc* w, const void* x, int M, int ldx, vo
                       cudaStream_t st);
 extern bool g_gemm_persist_all;
 extern int g_gemm_force_bn;    // gemm.cu: token tile for prefill-size batches (tests, comparisons)
+extern int g_gemv_max_rows;     // gemm.cu: most token rows the small-batch GEMV takes (default 8; up to 16)
 extern int g_gemv_force_split;  // gemm.cu: warps per CTA of the small-batch GEMV (0: chosen per shape)
 extern bool g_gemv_dense;      // gemm.cu: <= 8-row JQ4 projections on the mma.sync GEMV (default on)
 bool gemv_dense_supported(const GemmWeightDesc* w, int M, int ldx);

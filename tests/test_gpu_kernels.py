@@ -629,14 +629,16 @@ def test_linear_prefill_token_tiles(bn, q4):
 @pytest.mark.parametrize("split", [0, 4, 8, 16])
 @pytest.mark.parametrize("N,K", [(2560, 4096), (384, 256), (200, 1152), (6144, 2560)])
 def test_small_batch_gemv_matches_fp32(N, K, split):
-    """1..8 token rows of a JQ4 projection on the mma.sync GEMV: plain (bf16 and fp32 output, bias), gated activation epilogue, and
+    """1..16 token rows of a JQ4 projection on the mma.sync GEMV: plain (bf16 and fp32 output, bias), gated activation epilogue, and
     agreement with the tcgen05 kernel it replaces at these sizes; every number of K-splitting warps per CTA (0: chosen per shape)."""
     ext = ops.require_ext()
     ext.gemv_force_split(split)
+    ops.set_gemv_max_rows(16)  # the two-group form (9..16 rows) is covered too; by default it takes up to 8
     try:
         _small_batch_gemv_case(ext, N, K)
     finally:
         ext.gemv_force_split(0)
+        ops.set_gemv_max_rows(8)
 
 
 def _small_batch_gemv_case(ext, N, K):
@@ -647,10 +649,10 @@ def _small_batch_gemv_case(ext, N, K):
     bias = torch.randn(N, generator=g) * 0.1
     lw = LinearWeight(Q4Tensor(p, s, (N, K))).to(DEV)
     lwb = LinearWeight(Q4Tensor(p, s, (N, K)), bias=bias).to(DEV)
-    for M in (1, 2, 5, 8):
+    for M in (1, 2, 5, 8, 9, 13, 16):
         x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
         ref_y = x.float() @ wd.t()
-        assert lw.handle().gemv_ok(M, K)
+        assert lw.handle().gemv_ok(M, K) and not lw.handle().gemv_ok(17, K)
         y = ops.linear(x.to(DEV), lw)
         y32 = ops.linear(x.to(DEV), lwb, out_f32=True)
         ext.gemv_dense(False)
