@@ -62,7 +62,8 @@ def test_moe_route_in_one_launch_equals_the_separate_kernels(T, E, k, mode, reno
 
 
 @pytest.mark.parametrize("q4", [False, True])
-@pytest.mark.parametrize("T,E,k,N,K,e0,ne", [(40, 8, 2, 256, 512, 0, 8), (64, 16, 4, 384, 1024, 4, 8), (700, 4, 2, 192, 256, 0, 4), (3, 8, 2, 128, 2048, 6, 2)])
+@pytest.mark.parametrize("T,E,k,N,K,e0,ne", [(40, 8, 2, 256, 512, 0, 8), (64, 16, 4, 384, 1024, 4, 8), (700, 4, 2, 192, 256, 0, 4), (3, 8, 2, 128, 2048, 6, 2),
+                                             (24, 4, 2, 176, 1024, 0, 4)])  # 176 / 16 = 11 row groups: the GEMV's last CTA has an empty one
 def test_grouped_gemm_matches_per_expert(T, E, k, N, K, e0, ne, q4):
     """Grouped tcgen05 GEMM over the local experts [e0, e0 + ne) of a routed batch against a per-expert fp32 product."""
     from deliverance_b200.ckpt.jq4 import q4_dequantize, q4_quantize
@@ -104,7 +105,7 @@ def test_grouped_gemm_matches_per_expert(T, E, k, N, K, e0, ne, q4):
             exp = rows @ dense[j].t()
             got = ys[lo:hi].cpu().float()
             assert ((got - exp).norm() / exp.norm().clamp_min(1e-6)).item() < 2e-2, (bn, splits, j)
-        if bn <= 8 and q4 and N % 32 == 0:
+        if bn <= 8 and q4 and N % 16 == 0:
             # the grouped GEMV with the gated activation in its epilogue: rows [0, N / 2) are the gate, [N / 2, N) the up projection
             hm = grouped.run_gemv_act(xs, items, "silu")
             assert hm is not None and tuple(hm.shape) == (xs.shape[0], N // 2)
