@@ -22,6 +22,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures)")
     ap.add_argument("--graphs", action="store_true")
+    ap.add_argument("--prefill", action="store_true", help="profile the prefill of --batch prompts of --ctx tokens instead of decode steps")
     a = ap.parse_args()
     from deliverance_b200 import ops
     from deliverance_b200.ckpt.synthetic import SHAPES, SyntheticLoader
@@ -43,7 +44,33 @@ def main() -> int:
     eng = Engine(model, conf, eos_ids=(-1,))
     g = torch.Generator().manual_seed(0)
     for i in range(a.batch):
-        r = eng.add_request(torch.randint(0, cfg.vocab_size, (a.ctx,), generator=g).tolist(), GeneratorParameters())
+        r = eng.add_request(torch.randint(0, cfg.vocab_size, (a.ctx,), generator=g).tolist(), GeneratorParameters(max_tokens=1) if a.prefill else GeneratorParameters())
+    if a.prefill:
+        # one warm-up prefill of the same prompts (kernel attributes, scratch), then the measured one with the stage profiler on
+        torch.cuda.synchronize()
+        for timed in (False, True):
+            if timed:
+                for i in range(a.batch):
+                    eng.add_request(torch.randint(0, cfg.vocab_size, (a.ctx,), generator=g).tolist(), GeneratorParameters(max_tokens=1))
+            prof = InferenceProfiler(dev)
+            model.profiler = prof if timed else None
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            steps = 0
+            while eng.waiting or any(r.computed < len(r.fill) for r in eng.running):
+                eng.step()
+                steps += 1
+            e1.record()
+            torch.cuda.synchronize()
+            ops.check_status(0)
+            while eng.running or eng.waiting:  # let the requests finish (one more token each)
+                eng.step()
+            if timed:
+                ms = e0.elapsed_time(e1)
+                print(json.dumps({"shape": a.shape, "batch": a.batch, "prompt": a.ctx, "prefill_ms": ms, "engine_steps": steps,
+                                  "tokens_per_s": a.batch * a.ctx / ms * 1e3}))
+                prof.print_summary()
+        return 0
     while eng.waiting and eng._admit(eng.waiting[0]):
         eng.waiting.pop(0)
     for r in eng.running:

@@ -1076,6 +1076,7 @@ py::bytes lz4_decompress_bytes(const std::string& comp, int64_t n_out) {
 
 // ---- MoE --------------------------------------------------------------------------------------------------------------
 // returns weights [T, k] f32, expert ids [T, k] i32, counts [E], offsets [E+1], perm [T*k], pos [T*k]
+bool g_moe_parallel_sort = true;  // (comparisons: false keeps the single-CTA grouping for every batch size)
 std::vector<Tensor> moe_route(const Tensor& logits, int64_t k, int64_t mode, bool renorm) {
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.is_contiguous(), "router logits must be fp32 [T, E]");
   const int T = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
@@ -1084,8 +1085,12 @@ std::vector<Tensor> moe_route(const Tensor& logits, int64_t k, int64_t mode, boo
   auto io = logits.options().dtype(at::kInt);
   Tensor w = new_out({T, k}, logits.options()), idx = new_out({T, k}, io), counts = new_out({E}, io);
   Tensor offsets = new_out({E + 1}, io), perm = new_out({T * k}, io), pos = new_out({T * k}, io);
+  Tensor ws;  // per-chunk expert histograms of the parallel grouping (prefill-size batches)
+  const size_t ws_ints = g_moe_parallel_sort ? dlv::moe_route_workspace_ints(T, E, static_cast<int>(k)) : 0;
+  if (ws_ints > 0) ws = new_out({static_cast<int64_t>(ws_ints)}, io);
   dlv::launch_moe_route(logits.data_ptr<float>(), T, E, static_cast<int>(k), static_cast<int>(mode), renorm ? 1 : 0, w.data_ptr<float>(),
-                        idx.data_ptr<int>(), counts.data_ptr<int>(), offsets.data_ptr<int>(), perm.data_ptr<int>(), pos.data_ptr<int>(), cur_stream());
+                        idx.data_ptr<int>(), counts.data_ptr<int>(), offsets.data_ptr<int>(), perm.data_ptr<int>(), pos.data_ptr<int>(),
+                        ws_ints > 0 ? ws.data_ptr<int>() : nullptr, cur_stream());
   check_last_error("moe_route");
   return {w, idx, counts, offsets, perm, pos};
 }
@@ -1549,6 +1554,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("logprob_rows", &logprob_rows);
   m.def("logits_post", &logits_post, py::arg("logits"), py::arg("mask") = py::none(), py::arg("softcap") = 0.0, py::arg("inv_scale") = 1.0);
   m.def("moe_route", &moe_route);
+  m.def("moe_parallel_sort", [](bool on) { g_moe_parallel_sort = on; });
   m.def("moe_items", &moe_items);
   m.def("moe_route_items", &moe_route_items);
   m.def("moe_gather", &moe_gather, py::arg("x"), py::arg("perm"), py::arg("k"), py::arg("offsets") = py::none(), py::arg("e0") = 0, py::arg("ne") = 0);

@@ -174,8 +174,9 @@ void launch_logprobs(const float* logits, int ld, int B, int V, const long long*
                      float* out_val, cudaStream_t st);
 
 // moe.cu
+size_t moe_route_workspace_ints(int T, int E, int k);  // ints of `ws` for the parallel grouping of large batches (0: not needed)
 void launch_moe_route(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
-                      int* perm, int* pos, cudaStream_t st);
+                      int* perm, int* pos, int* ws, cudaStream_t st);
 // `range` (optional) = offsets + first local expert and the count of local experts: rows outside
 // [offsets[e0], offsets[e0 + ne]) are skipped (expert parallelism: other ranks own them)
 void launch_moe_gather(const void* x, const int* perm, int rows, int k, int H, void* xs, const int* offsets, int e0, int ne,

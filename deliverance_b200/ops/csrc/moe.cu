@@ -207,6 +207,84 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
   }
 }
 
+// The same grouping for prefill-size batches, in parallel. The single-CTA kernel above walks all T k pairs once per expert (one
+// thread each): 2.5 ms for the 65,536 pairs of an 8,192-token chunk with 128 experts, two thirds of the whole MoE block at prefill.
+// Here the pairs are cut into chunks of kSortChunk: (a) every chunk counts its pairs per expert, (b) one CTA turns the expert
+// histogram into offsets and the chunk counts into the first row of every (chunk, expert), (c) one warp per chunk hands out the
+// rows in pair order (__match_any_sync groups the lanes of one expert; the group's first lane advances the running row). The
+// order is the stable one: ascending pair index inside an expert.
+constexpr int kSortChunk = 1024;
+constexpr int kSortSerialMaxPairs = 1024;  // up to here the single-CTA kernel is used
+__global__ void __launch_bounds__(256) moe_chunk_hist_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ chunk_hist) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ int hs[];  // [E]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hs[e] = 0;
+  __syncthreads();
+  const int p0 = blockIdx.x * kSortChunk, p1 = min(P, p0 + kSortChunk);
+  for (int p = p0 + threadIdx.x; p < p1; p += blockDim.x) atomicAdd(&hs[idx[p]], 1);
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_hist[static_cast<size_t>(blockIdx.x) * E + e] = hs[e];
+}
+// chunk_hist [C, E]: counts on entry, first grouped row of the (chunk, expert) on exit
+__global__ void __launch_bounds__(1024) moe_chunk_scan_kernel(const int* __restrict__ counts, int E, int C, int* __restrict__ offsets,
+                                                              int* __restrict__ chunk_hist) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ int sh[];  // [E + 1]
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    const int chunk = (E + 31) / 32, lo = min(E, lane * chunk), hi = min(E, lo + chunk);
+    int sum = 0;
+    for (int e = lo; e < hi; ++e) sum += counts[e];
+    const int incl = warp_incl_scan(sum, lane);
+    int acc = incl - sum;
+    for (int e = lo; e < hi; ++e) {
+      sh[e] = acc;
+      acc += counts[e];
+    }
+    if (lane == 31) sh[E] = incl;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = sh[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int acc = sh[e];
+    for (int c = 0; c < C; ++c) {
+      const int h = chunk_hist[static_cast<size_t>(c) * E + e];
+      chunk_hist[static_cast<size_t>(c) * E + e] = acc;
+      acc += h;
+    }
+  }
+}
+__global__ void __launch_bounds__(32) moe_chunk_rank_kernel(const int* __restrict__ idx, int P, int E, const int* __restrict__ chunk_base,
+                                                            int* __restrict__ perm, int* __restrict__ pos) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ int rk[];  // [E] running row per expert, then [kSortChunk] the chunk's expert ids
+  int* run_s = rk;
+  int* idx_s = rk + E;
+  const int lane = threadIdx.x;
+  const int p0 = blockIdx.x * kSortChunk, n = min(P - p0, kSortChunk);
+  for (int e = lane; e < E; e += 32) run_s[e] = chunk_base[static_cast<size_t>(blockIdx.x) * E + e];
+  for (int i = lane; i < n; i += 32) idx_s[i] = idx[p0 + i];
+  __syncwarp();
+  for (int q = 0; q < n; q += 32) {
+    const int i = q + lane;
+    const bool valid = i < n;
+    const int e = valid ? idx_s[i] : -1 - lane;  // (lanes past the end each form a group of their own)
+    const unsigned m = __match_any_sync(0xffffffffu, e);
+    const int r = __popc(m & ((1u << lane) - 1u));
+    const int base = valid ? run_s[e] : 0;
+    __syncwarp();
+    if (valid && r == 0) run_s[e] = base + __popc(m);
+    __syncwarp();
+    if (valid) {
+      perm[base + r] = p0 + i;
+      pos[p0 + i] = base + r;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(128) moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ perm, int k, int H,
                                                          __nv_bfloat16* __restrict__ xs, const int* __restrict__ offsets, int e0, int ne) {
   pdl_wait();     // no-op unless launched with programmatic stream serialization: the kernel in front has completed
@@ -251,14 +329,27 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const __nv_bfloat16* _
   }
 }
 
+// Ints of workspace launch_moe_route needs for T tokens (0: none, the single-CTA grouping is used)
+size_t moe_route_workspace_ints(int T, int E, int k) {
+  const long long P = static_cast<long long>(T) * k;
+  return P > kSortSerialMaxPairs ? static_cast<size_t>((P + kSortChunk - 1) / kSortChunk) * E : 0;
+}
 void launch_moe_route(const float* logits, int T, int E, int k, int mode, int renorm, float* w, int* idx, int* counts, int* offsets,
-                      int* perm, int* pos, cudaStream_t st) {
+                      int* perm, int* pos, int* ws, cudaStream_t st) {
   cudaMemsetAsync(counts, 0, sizeof(int) * E, st);
   if (T == 0) {
     cudaMemsetAsync(offsets, 0, sizeof(int) * (E + 1), st);
     return;
   }
   moe_topk_kernel<<<(T + 7) / 8, 256, 0, st>>>(logits, T, E, k, mode, renorm, w, idx, counts);
+  const int P = T * k;
+  if (ws != nullptr && moe_route_workspace_ints(T, E, k) > 0) {
+    const int C = (P + kSortChunk - 1) / kSortChunk;
+    moe_chunk_hist_kernel<<<C, 256, sizeof(int) * E, st>>>(idx, P, E, ws);
+    moe_chunk_scan_kernel<<<1, 1024, sizeof(int) * (E + 1), st>>>(counts, E, C, offsets, ws);
+    moe_chunk_rank_kernel<<<C, 32, sizeof(int) * (E + kSortChunk), st>>>(idx, P, E, ws, perm, pos);
+    return;
+  }
   moe_sort_kernel<<<1, 1024, sizeof(int) * (E + 1), st>>>(idx, counts, T, E, k, offsets, perm, pos);
 }
 // Decode-size batches: everything of launch_moe_route + launch_moe_items in one launch. False when the batch is too large for it.

@@ -16,9 +16,10 @@ from deliverance_b200.params import GeneratorParameters
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("T", [77, 3000])  # 3000 tokens: the parallel grouping (chunks of 1024 pairs, the last one ragged)
 @pytest.mark.parametrize("E,k,mode,renorm", [(8, 2, "softmax_topk", True), (128, 8, "softmax_topk", False), (64, 6, "topk_softmax", False)])
-def test_moe_route_gather_combine(E, k, mode, renorm):
-    T, H = 77, 256
+def test_moe_route_gather_combine(E, k, mode, renorm, T):
+    H = 256
     g = torch.Generator().manual_seed(E)
     logits = torch.randn(T, E, generator=g)
     w_ref, idx_ref = ref.moe_route(logits, k, mode, renorm)
@@ -31,6 +32,14 @@ def test_moe_route_gather_combine(E, k, mode, renorm):
     assert torch.equal(flat[perm.cpu().long()], torch.sort(flat, stable=True).values)
     assert torch.equal(perm.cpu()[pos.cpu().long()], torch.arange(T * k, dtype=torch.int32))
     x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    if T > 1000:  # the single-CTA grouping gives the same arrays
+        e.moe_parallel_sort(False)
+        try:
+            serial = e.moe_route(logits.cuda(), k, 0 if mode == "softmax_topk" else 1, renorm)
+        finally:
+            e.moe_parallel_sort(True)
+        for ta, tb in zip((w, idx, counts, offsets, perm, pos), serial):
+            assert torch.equal(ta, tb)
     xs = e.moe_gather(x.cuda(), perm, k)
     assert torch.equal(xs.cpu(), x[(perm.cpu() // k).long()])
     ys = torch.randn(T * k, H, generator=g).to(torch.bfloat16)
