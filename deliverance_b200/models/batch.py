@@ -57,10 +57,20 @@ def make_batch(seqs: list[dict], page_size: int, device, max_pages: Optional[int
     """
     from ..ops import prefill_tiles
 
-    toks, pos, slots, qs, ql, cl = [], [], [], [], [], []
+    toks, pos, slots, qs, ql, cl = [], [], [], [], [], []  # toks / pos / slots: one tensor per sequence
     width = max_pages or max(1, max(len(s["pages"]) for s in seqs))
     bt = torch.zeros(len(seqs), width, dtype=torch.int32)
     row = 0
+    short: tuple[list, list, list] = ([], [], [])  # tokens / positions / slots of short sequences not yet turned into tensors
+
+    def flush_short():
+        if short[0]:
+            toks.append(torch.tensor(short[0], dtype=torch.int32))
+            pos.append(torch.tensor(short[1], dtype=torch.int32))
+            slots.append(torch.tensor(short[2], dtype=torch.int64))
+            for v in short:
+                v.clear()
+
     for i, s in enumerate(seqs):
         n = len(s["tokens"])
         start = int(s["start"])
@@ -68,22 +78,34 @@ def make_batch(seqs: list[dict], page_size: int, device, max_pages: Optional[int
         need = (start + n + page_size - 1) // page_size
         if need > len(pages):
             raise ValueError(f"sequence {i}: {need} pages needed, {len(pages)} given")
-        bt[i, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        pages_t = torch.tensor(pages, dtype=torch.int64)
+        bt[i, : len(pages)] = pages_t
         qs.append(row)
         ql.append(n)
         cl.append(start + n)
-        for j in range(n):
-            p = start + j
-            toks.append(int(s["tokens"][j]))
-            pos.append(p)
-            slots.append(pages[p // page_size] * page_size + p % page_size)
+        if n <= 16:  # decode rows and short tails: plain lists (a tensor op per sequence would cost more than the loop)
+            for j in range(n):
+                p = start + j
+                short[0].append(int(s["tokens"][j]))
+                short[1].append(p)
+                short[2].append(pages[p // page_size] * page_size + p % page_size)
+        else:
+            # vectorised: a prompt chunk has thousands of tokens, and the device waits while the host builds the next chunk
+            flush_short()
+            p = torch.arange(start, start + n, dtype=torch.int64)
+            toks.append(torch.as_tensor(s["tokens"], dtype=torch.int32))
+            pos.append(p.to(torch.int32))
+            slots.append(pages_t[p // page_size] * page_size + p % page_size)
         row += n
+    flush_short()
     is_decode = all(n == 1 for n in ql)
     last = [a + b - 1 for a, b in zip(qs, ql)]
     ts, t0 = ([], []) if is_decode else prefill_tiles(ql)
     dev = torch.device(device)
 
     def t(v, dt):
+        if v and isinstance(v[0], torch.Tensor):
+            return torch.cat(v).to(dt).to(dev, non_blocking=True)
         return torch.tensor(v, dtype=dt).to(dev, non_blocking=True)
 
     state_slots = None
