@@ -208,3 +208,32 @@ def test_fused_rope_path_composes_the_same_operators(tmp_path, monkeypatch):
     d64 = str(tmp_path / "l")
     write_tiny_model(d64, "llama", seed=8)
     assert not _ours(d64)[0].fused_rope  # head_dim 16: not eligible
+
+
+def test_make_batch_long_and_short_sequences():
+    """Positions, cache slots and token ids of a batch that mixes prompt chunks (built with tensor ops) and short rows (built from
+    lists) against the plain statement, in sequence order."""
+    from deliverance_b200.models.batch import make_batch
+
+    page = 32
+    seqs = [{"tokens": list(range(100, 700)), "start": 5, "pages": list(range(40, 60))},
+            {"tokens": [9, 8, 7], "start": 40, "pages": [300, 301]},
+            {"tokens": [1], "start": 0, "pages": [400]},
+            {"tokens": list(range(50)), "start": 31, "pages": [7, 3, 5]},
+            {"tokens": [4, 4], "start": 63, "pages": [11, 12, 13]}]
+    b = make_batch(seqs, page, "cpu")
+    pos, slots, toks, starts = [], [], [], []
+    for s in seqs:
+        starts.append(len(pos))
+        for j, tk in enumerate(s["tokens"]):
+            p = s["start"] + j
+            pos.append(p)
+            toks.append(tk)
+            slots.append(s["pages"][p // page] * page + p % page)
+    assert b.positions.tolist() == pos and b.slots.tolist() == slots and b.token_ids.tolist() == toks
+    assert b.positions.dtype == torch.int32 and b.slots.dtype == torch.int64 and b.token_ids.dtype == torch.int32
+    assert b.q_start.tolist() == starts and b.q_len.tolist() == [len(s["tokens"]) for s in seqs]
+    assert b.ctx_len.tolist() == [s["start"] + len(s["tokens"]) for s in seqs] and not b.is_decode
+    assert b.block_tables[0, :20].tolist() == list(range(40, 60)) and b.block_tables[2, 0].item() == 400
+    d = make_batch([{"tokens": [7], "start": 100, "pages": list(range(5))} for _ in range(3)], page, "cpu")
+    assert d.is_decode and d.slots.tolist() == [3 * page + 4] * 3
