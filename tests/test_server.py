@@ -286,3 +286,61 @@ def test_interrogation_game_setup_and_loop(registry):
     quit_game = g.Game(chat, lambda: "/quit", out.append)
     quit_game.case = game.case
     assert quit_game.play() == "closed"
+
+
+def test_server_command_line_end_to_end(tmp_path):
+    """``python -m deliverance_b200.server --model DIR`` as a user starts it (CPU, tiny checkpoint): the process comes up, lists the
+    model, answers a blocking and a streaming chat completion over real HTTP and exits on SIGTERM."""
+    import json
+    import signal
+    import socket
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+
+    from deliverance_b200.ckpt.tiny import write_tiny_model
+
+    d = str(tmp_path / "tinyllama")
+    write_tiny_model(d, "llama", seed=5, std=0.05)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    proc = subprocess.Popen([sys.executable, "-m", "deliverance_b200.server", "--model", d, "--device", "cpu", "--port", str(port), "--max-seqs", "4"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    base = f"http://127.0.0.1:{port}"
+
+    def call(path, body=None, timeout=60):
+        req = urllib.request.Request(base + path, data=None if body is None else json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        return urllib.request.urlopen(req, timeout=timeout)
+
+    try:
+        deadline = time.time() + 120
+        models = None
+        while time.time() < deadline and proc.poll() is None:
+            try:
+                models = json.load(call("/models", timeout=2))
+                break
+            except OSError:
+                time.sleep(0.3)
+        assert models is not None, "the server did not come up"
+        names = [m["id"] for m in models["data"]]
+        assert names == ["tinyllama"]
+        body = {"model": "tinyllama", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 0}
+        out = json.load(call("/chat/completions", body))
+        assert out["choices"][0]["finish_reason"] in ("length", "stop") and out["usage"]["completion_tokens"] <= 6
+        text = out["choices"][0]["message"]["content"]
+        lines = [ln.decode() for ln in call("/v1/chat/completions", dict(body, stream=True)) if ln.startswith(b"data: ")]
+        assert lines[-1].strip() == "data: [DONE]"
+        streamed = "".join(json.loads(ln[6:])["choices"][0]["delta"].get("content") or "" for ln in lines[:-1] if '"delta"' in ln)
+        assert streamed == text  # temperature 0: the stream carries the same text as the blocking call
+    finally:
+        if proc.poll() is None:
+            proc.send_signal(signal.SIGTERM)
+            try:
+                proc.wait(timeout=20)
+            except subprocess.TimeoutExpired:
+                proc.kill()
+                proc.wait(timeout=10)
+    assert proc.returncode is not None
