@@ -281,3 +281,26 @@ def test_jq4_blocks_against_the_reference_c_kernel():
     r2 = np.zeros((5, n), dtype=np.float32)
     lib.gemm_f32_q4(0, x.ctypes.data, 0, s_np.ctypes.data, p_np.ctypes.data, 0, r2.ctypes.data, 0, 5, 0, n, k, k, k // 2, k // 32, n)
     assert np.abs(r2 - x @ deq.T).max() <= 1e-4
+
+
+def test_quantizer_command_line_then_generate(tmp_path):
+    """``python -m deliverance_b200.ckpt.quantizer SRC OUT`` as a user runs it; the quantised directory then loads through the public
+    builder and generates, like the source directory does."""
+    import subprocess
+    import sys
+
+    from deliverance_b200.api import AutoModelForCausalLM
+    from deliverance_b200.params import GeneratorParameters
+
+    src, out = str(tmp_path / "src"), str(tmp_path / "jq4")
+    write_tiny_model(src, "llama", seed=4, std=0.05)
+    r = subprocess.run([sys.executable, "-m", "deliverance_b200.ckpt.quantizer", src, out], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "quantised" in r.stdout, r.stderr[-500:]
+    assert os.path.exists(os.path.join(out, FINISHED))
+    clm_q = AutoModelForCausalLM.new_builder(out).with_device("cpu").build()
+    clm_f = AutoModelForCausalLM.new_builder(src).with_device("cpu").build()
+    p = GeneratorParameters(max_tokens=8, temperature=0.0)
+    ids = [5, 9, 33, 17, 4]
+    a, b = clm_q.generate(ids, p), clm_f.generate(ids, p)
+    assert len(a.token_ids) == 8 and len(b.token_ids) == 8 and a.generated_tokens == 8
+    assert WeightLoader(out).is_q4("model.layers.0.mlp.down_proj.weight")
