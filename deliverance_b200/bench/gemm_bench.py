@@ -31,12 +31,16 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--impl", type=int, default=0)
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul on bf16 weights")
+    ap.add_argument("--persist", default="off", choices=["off", "ordered", "race"],
+                    help="prefill-size JQ4 shapes on the persistent kernel wherever it applies: issuers in k-block order or racing")
     a = ap.parse_args()
     from deliverance_b200 import ops
     from deliverance_b200.ckpt.safetensors_io import Q4Tensor
     from deliverance_b200.ops import LinearWeight
 
     dev = torch.device("cuda", 0)
+    if a.persist != "off":
+        ops.require_ext().gemm_persist(True, True, a.persist == "ordered")
     hbm, tf, src = peaks()
     for shp in a.shapes.split(","):
         N, K = (int(v) for v in shp.split("x"))
